@@ -1,0 +1,189 @@
+/*
+ * mlpsp.h - C ABI of the B200 (sm_100a) tile-centre render path of MLP Splatting.
+ *
+ * Drop-in boundary: these entry points stand where the reference's pybind11 extension
+ * (scannet/cuda/np_tile_kernels.cu:7224-7252) and the PyTorch culling in
+ * scannet/cumodel.py:994-1070 stand.  Plain pointers and sizes only; all array pointers are
+ * DEVICE pointers unless a comment says "host".  Inputs are borrowed and never written; outputs
+ * and scratch are allocated by the caller.  Every call is asynchronous on `stream` (a
+ * cudaStream_t passed as void*) and returns 0, or a negative MLPSP_E_* code for a host-side
+ * argument error (text via mlpsp_last_error()).  Device-side findings (capacity overflow, bad
+ * ids, scratch too small, non-finite activations, a wait that gave up) are OR-ed into a
+ * caller-owned int32 status block that the caller reads after synchronising; kernels launched
+ * after a fatal finding return without touching their outputs.
+ */
+#ifndef MLPSP_H_
+#define MLPSP_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLPSP_ABI_VERSION 1
+
+/* host-side return codes */
+#define MLPSP_OK 0
+#define MLPSP_E_ARG (-1)      /* bad argument (null pointer, size, unsupported option) */
+#define MLPSP_E_SCRATCH (-2)  /* scratch block smaller than mlpsp_frame_scratch_bytes() */
+#define MLPSP_E_CUDA (-3)     /* a CUDA runtime call failed */
+#define MLPSP_E_LIMIT (-4)    /* size beyond a documented limit */
+
+/* status block: int32 status[MLPSP_STATUS_WORDS], zeroed by the caller or by mlpsp_status_reset */
+#define MLPSP_STATUS_WORDS 16
+#define MLPSP_ST_BITS 0            /* OR of the MLPSP_ST_* bits below */
+#define MLPSP_ST_MAX_TILE_LEN 1    /* longest tile list seen by binning / validation */
+#define MLPSP_ST_PAIRS 2           /* number of (tile, primitive) candidate pairs */
+#define MLPSP_ST_WAVES 3           /* waves launched with at least one candidate window */
+#define MLPSP_ST_RECORDS_LO 4      /* MLP evaluations performed this frame (64-bit, words 4-5) */
+#define MLPSP_ST_RECORDS_HI 5
+#define MLPSP_ST_USED_LO 6         /* records consumed by compositing (64-bit, words 6-7) */
+#define MLPSP_ST_USED_HI 7
+#define MLPSP_ST_WAVE_RECORDS 8    /* largest record count of a single wave */
+#define MLPSP_ST_WORK_ITEMS 9      /* largest number of evaluator work items of a single wave */
+
+/* bits 1,2,4 match the reference validator (np_tile_kernels.cu:4499-4519) */
+#define MLPSP_ST_BAD_OFFSETS 1       /* tile_offsets not 0-based / monotone / in bounds */
+#define MLPSP_ST_TILE_CAPACITY 2     /* a tile list is longer than tile_capacity */
+#define MLPSP_ST_BAD_IDS 4           /* candidate id outside [0, n) */
+#define MLPSP_ST_PAIR_OVERFLOW 8     /* more candidate pairs than max_pairs */
+#define MLPSP_ST_RECORD_OVERFLOW 16  /* a wave produced more records than max_records */
+#define MLPSP_ST_NUMERIC 64          /* non-finite operand/activation in the fp16 evaluator */
+#define MLPSP_ST_TIMEOUT 128         /* a bounded device-side wait gave up */
+#define MLPSP_ST_FATAL (1 | 2 | 4 | 8 | 16 | 128)
+
+#define MLPSP_PRECISION_F32 0  /* scalar FP32 evaluator (np_tile_kernels.cu:312-380) */
+#define MLPSP_PRECISION_F16 1  /* fp16 operands, FP32 accumulate, tcgen05 (rgb_wmma.cuh:75-223) */
+
+#define MLPSP_GEOM_FLOATS 16   /* packed geometry floats per primitive */
+#define MLPSP_MAX_WAVES 32
+
+/* Scene parameters (borrowed).  Replaces the 15-tensor argument list of the reference entry
+ * points (np_tile_kernels.cu:5225-5247): positions/log_scales/quats arrive packed by
+ * mlpsp_pack_geometry; W1..b3, freq, att keep the reference layouts
+ * (W1[n,H,12F], b1[n,H], W2[n,H,H], b2[n,H], W3[n,4,H], b3[n,4], row-major FP32). */
+typedef struct mlpsp_scene {
+  const float* geom;      /* [n*16] from mlpsp_pack_geometry */
+  int32_t n;
+  int32_t hidden;         /* H <= 64 (FP32 evaluator), 32 (fp16 evaluator) */
+  int32_t num_freq;       /* F <= 8; encoded width IN = 12 F; fp16 evaluator needs F == 6 */
+  int32_t reserved0;
+  const float* W1; const float* b1; const float* W2; const float* b2; const float* W3; const float* b3;
+  const void* w16;        /* [n * mlpsp_packed_weight_bytes()] from mlpsp_pack_weights_f16, or NULL */
+  const float* freq;      /* [F] */
+  const float* att;       /* [F] */
+  const float* feat_attr; /* [n, feat_slots, feat_dim] or NULL */
+  int32_t feat_slots;     /* 1, 4 or 5 (np_tile_kernels.cu:6036-6075) */
+  int32_t feat_dim;       /* C <= 512 */
+  float gate_beta;        /* semantic_tetra_gates norm_beta */
+  float gate_tau;         /* semantic_tetra_gates logit_temp */
+} mlpsp_scene;
+
+/* One frame.  Replaces (rays_o, rays_d, culled_prim_indices, tile_offsets, Wimg, Himg, TW, TH,
+ * threshold) of the reference entry points plus their freshly allocated outputs. */
+typedef struct mlpsp_frame {
+  const float* rays_o;    /* [W*H,3] */
+  const float* rays_d;    /* [W*H,3], unit length (the reference passes F.normalize(ray_d)) */
+  int32_t width, height;
+  int32_t tile;           /* 8 */
+  float threshold;        /* score threshold in (0,1) */
+  int32_t tile_capacity;  /* 1536 (MLPSP_MAX_TILE_PRIMS of the reference loader) */
+  int32_t precision;      /* MLPSP_PRECISION_* */
+  const float* view;      /* HOST [16] row-major view matrix (binning only) */
+  const float* proj;      /* HOST [16] row-major projection matrix (binning only) */
+  int32_t* tile_offsets;  /* [T+1]  written by binning, read by the later stages */
+  int32_t* tile_prims;    /* [max_pairs] candidate ids, ascending inside a tile */
+  int32_t* sorted_prims;  /* [max_pairs] the same lists in tile-centre depth order */
+  int64_t max_pairs;
+  float* rgb;             /* [W*H,3] */
+  float* alpha;           /* [W*H]   */
+  float* depth_t;         /* [W*H] expected depth sum(w t)/sum(w), or NULL */
+  float* feat;            /* [W*H, feat_dim] composited features, or NULL */
+  uint64_t* mask_used;    /* [max_pairs] per pair: pixels (bit = ly*8+lx) whose record was composited, or NULL */
+  const float* bg_color;  /* HOST [3] background added as rgb + clamp(1-alpha,0,1)*bg, or NULL */
+  void* scratch;          /* mlpsp_frame_scratch_bytes() bytes, 256-byte aligned */
+  int64_t scratch_bytes;
+  int64_t max_records;    /* record capacity of one wave */
+  int32_t* status;        /* [MLPSP_STATUS_WORDS] */
+  int32_t num_waves;      /* 0 = library default schedule */
+  int32_t wave_len[MLPSP_MAX_WAVES]; /* candidates per tile processed by wave k */
+} mlpsp_frame;
+
+const char* mlpsp_last_error(void);
+int mlpsp_abi_version(void);
+/* sizeof(mlpsp_scene), sizeof(mlpsp_frame) as compiled, for bindings that mirror the structs */
+int mlpsp_struct_sizes(int32_t* scene_bytes, int32_t* frame_bytes);
+
+/* positions[n,3], log_scales[n,3], unit quats[n,4] -> geom[n*16]
+ * (the per-primitive loads of np_tile_kernels.cu:1948-1957, with exp(-2 ls) hoisted) */
+int mlpsp_pack_geometry(const float* positions, const float* log_scales, const float* quats_unit,
+                        int32_t n, float* geom, void* stream);
+
+/* out = in / max(|in|, 1e-12) per row of `dim` (3 or 4) floats: F.normalize at cumodel.py:1088,1114 */
+int mlpsp_normalize_rows(const float* in, float* out, int64_t rows, int32_t dim, void* stream);
+
+/* Bytes per primitive of the fp16 evaluator's packed weight image, and the packer.  Replaces the
+ * per-(tile, primitive) FP32->fp16 re-cast of rgb_wmma.cuh:162-176 with one cast per scene. */
+int64_t mlpsp_packed_weight_bytes(int32_t hidden, int32_t num_freq);
+int mlpsp_pack_weights_f16(const mlpsp_scene* scene, void* w16_out, void* stream);
+
+int mlpsp_status_reset(int32_t* status, void* stream);
+
+/* Scratch size for a frame of this shape. */
+int64_t mlpsp_frame_scratch_bytes(int32_t n, int32_t width, int32_t height, int32_t tile,
+                                  int64_t max_pairs, int64_t max_records);
+
+/* Screen-space culling: cumodel.py:994-1070 (overlap predicate, tile-major lists, ascending id).
+ * Writes frame->tile_offsets, frame->tile_prims; status words 1,2 and bits 2,8. */
+int mlpsp_bin_tiles(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
+
+/* validate_tile_candidate_capacity (np_tile_kernels.cu:4485-4589) for caller-supplied lists of
+ * `pairs` candidates. */
+int mlpsp_validate_tile_lists(const int32_t* tile_offsets, const int32_t* tile_prims, int32_t num_tiles,
+                              int64_t pairs, int32_t tile_capacity, int32_t n, int32_t* status,
+                              void* stream);
+
+/* Per-tile stable ascending sort by the tile-centre key (np_tile_kernels.cu:483-518, 1914-1990).
+ * Reads tile_offsets/tile_prims, writes sorted_prims; keys_out ([max_pairs], optional) receives
+ * the sorted keys. */
+int mlpsp_sort_tiles(const mlpsp_scene* scene, const mlpsp_frame* frame, float* keys_out, void* stream);
+
+/* Geometric hit mask of every pair of the sorted lists, no termination
+ * (hit_and_features_rot, np_tile_kernels.cu:659-711): mask_geo[pair] bit ly*8+lx. */
+int mlpsp_hit_masks(const mlpsp_scene* scene, const mlpsp_frame* frame, uint64_t* mask_geo, void* stream);
+
+/* Records -> per-primitive evaluation -> compositing for depth-sorted lists: the body of
+ * render_tiles_kernel_tilecenter_order (np_tile_kernels.cu:1837-2137), render_rgb_wmma_kernel
+ * (rgb_wmma.cuh:75-223), ..._with_t (5432-5718) and ..._with_feat (5794-6112). */
+int mlpsp_render_sorted(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
+
+/* bin + sort + render_sorted: what NeuralPrimitiveSceneTileCUDA.forward does per frame
+ * (cumodel.py:951-1160). */
+int mlpsp_render_frame(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
+
+/* Grouped evaluator on explicit records (the forward counterpart of primitive_gemm.py's grouped
+ * VJP): records are primitive-major, offsets[n+1] int64 as produced by group_records
+ * (primitive_csr.py:23-29); x6[R,6]; out[R,4] = (R, G, B, sigma_raw). */
+int64_t mlpsp_mlp_grouped_scratch_bytes(int64_t num_records, int32_t n);
+int mlpsp_mlp_grouped(const mlpsp_scene* scene, int32_t precision, const int64_t* offsets, const float* x6,
+                      int64_t num_records, float* out4, void* scratch, int64_t scratch_bytes,
+                      int32_t* status, void* stream);
+
+/* group_records (primitive_csr.py:23-29): stable grouping of R record ids by primitive.
+ * offsets[n+1] int64, order[R] int64 (record indices, ascending inside a group). */
+int64_t mlpsp_group_records_scratch_bytes(int64_t num_records, int32_t n);
+int mlpsp_group_records(const int32_t* primitive_ids, int64_t num_records, int32_t n, int64_t* offsets,
+                        int64_t* order, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* prepare_groups (primitive_gemm.py:186-203): split every primitive's records into segments of at
+ * most segment_size.  group_offsets[n+1] int64 is always written; primitives/starts ([G] int64) are
+ * written when non-NULL and max_groups >= G.  *num_groups_host receives G (the call synchronises). */
+int mlpsp_prepare_groups(const int64_t* offsets, int32_t n, int64_t segment_size, int64_t* group_offsets,
+                         int64_t* primitives, int64_t* starts, int64_t max_groups,
+                         int64_t* num_groups_host, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLPSP_H_ */

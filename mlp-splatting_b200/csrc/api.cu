@@ -1,0 +1,231 @@
+// C ABI entry points: argument checks, scratch carving and stage sequencing.
+#include <cmath>
+#include <cstring>
+#include "frame.cuh"
+
+namespace mlpsp {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_check(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return MLPSP_OK;
+  set_error("CUDA error in %s: %s", what, cudaGetErrorString(e));
+  return MLPSP_E_CUDA;
+}
+
+// validate_tile_candidate_capacity_kernel (np_tile_kernels.cu:4485-4520)
+__global__ void k_validate_lists(const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ prims, int T,
+                                 int64_t M, int capacity, int n, int32_t* __restrict__ status) {
+  const int64_t stride = (int64_t)blockDim.x * gridDim.x;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < T; t += stride) {
+    const int s = tile_offsets[t], e = tile_offsets[t + 1];
+    if (s < 0 || e < s || e > M || (t == 0 && s != 0) || (t == T - 1 && e != M)) {
+      atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_BAD_OFFSETS);
+      continue;
+    }
+    const int c = e - s;
+    atomicMax(status + MLPSP_ST_MAX_TILE_LEN, c);
+    if (capacity > 0 && c > capacity) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_TILE_CAPACITY);
+  }
+  bool bad = false;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M; i += stride) {
+    const int p = prims[i];
+    bad |= p < 0 || p >= n;
+  }
+  if (bad) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_BAD_IDS);
+}
+
+static int check_frame_common(const mlpsp_scene* sc, const mlpsp_frame* fr, const char* who) {
+  MLPSP_REQUIRE(sc && fr, MLPSP_E_ARG, "%s: null scene or frame", who);
+  MLPSP_REQUIRE(fr->width > 0 && fr->height > 0, MLPSP_E_ARG, "%s: image and tile dimensions must be positive", who);
+  MLPSP_REQUIRE(fr->tile == 8, MLPSP_E_ARG, "%s: only 8x8 tiles are supported", who);
+  MLPSP_REQUIRE((int64_t)fr->width * fr->height <= 2147483647LL, MLPSP_E_LIMIT,
+                "%s: image dimensions exceed int32 pixel indexing", who);
+  MLPSP_REQUIRE(fr->threshold > 0.f && fr->threshold < 1.f, MLPSP_E_ARG, "%s: threshold must be in (0,1)", who);
+  MLPSP_REQUIRE(sc->n >= 0 && (sc->n == 0 || sc->geom), MLPSP_E_ARG, "%s: scene geometry missing", who);
+  MLPSP_REQUIRE(fr->status, MLPSP_E_ARG, "%s: status block missing", who);
+  MLPSP_REQUIRE(fr->tile_offsets, MLPSP_E_ARG, "%s: tile_offsets missing", who);
+  MLPSP_REQUIRE(fr->max_pairs >= 0 && fr->max_pairs < (1ll << 31), MLPSP_E_LIMIT,
+                "%s: candidate list is too large for int32 offsets", who);
+  MLPSP_REQUIRE(fr->max_pairs == 0 || (fr->tile_prims && fr->sorted_prims), MLPSP_E_ARG, "%s: tile list buffers missing", who);
+  return MLPSP_OK;
+}
+
+static int get_scratch(const mlpsp_scene* sc, const mlpsp_frame* fr, Scratch& s, const char* who) {
+  MLPSP_REQUIRE(fr->max_records >= 0 && fr->max_records < (1ll << 31), MLPSP_E_LIMIT,
+                "%s: max_records must be below 2^31", who);
+  const Scratch q = carve_scratch(nullptr, sc->n, fr->width, fr->height, fr->tile, fr->max_pairs, fr->max_records);
+  MLPSP_REQUIRE(fr->scratch && fr->scratch_bytes >= q.bytes, MLPSP_E_SCRATCH, "%s: scratch needs %lld bytes, got %lld",
+                who, (long long)q.bytes, (long long)fr->scratch_bytes);
+  MLPSP_REQUIRE(((uintptr_t)fr->scratch & 255u) == 0, MLPSP_E_ARG, "%s: scratch must be 256-byte aligned", who);
+  s = carve_scratch(fr->scratch, sc->n, fr->width, fr->height, fr->tile, fr->max_pairs, fr->max_records);
+  return MLPSP_OK;
+}
+
+static int render_sorted_checked(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st) {
+  MLPSP_REQUIRE(fr->rays_o && fr->rays_d && fr->rgb && fr->alpha, MLPSP_E_ARG, "render: rays or outputs missing");
+  MLPSP_REQUIRE(fr->precision == MLPSP_PRECISION_F32 || fr->precision == MLPSP_PRECISION_F16, MLPSP_E_ARG,
+                "render: unknown precision %d", fr->precision);
+  MLPSP_REQUIRE(fr->num_waves >= 0 && fr->num_waves <= MLPSP_MAX_WAVES, MLPSP_E_ARG, "render: bad num_waves");
+  return launch_render_sorted(sc, fr, s, st);
+}
+
+}  // namespace mlpsp
+
+using namespace mlpsp;
+
+extern "C" const char* mlpsp_last_error(void) { return g_err; }
+extern "C" int mlpsp_abi_version(void) { return MLPSP_ABI_VERSION; }
+extern "C" int mlpsp_struct_sizes(int32_t* scene_bytes, int32_t* frame_bytes) {
+  if (scene_bytes) *scene_bytes = (int32_t)sizeof(mlpsp_scene);
+  if (frame_bytes) *frame_bytes = (int32_t)sizeof(mlpsp_frame);
+  return MLPSP_OK;
+}
+
+extern "C" int mlpsp_status_reset(int32_t* status, void* stream) {
+  MLPSP_REQUIRE(status, MLPSP_E_ARG, "mlpsp_status_reset: null pointer");
+  return cuda_check(cudaMemsetAsync(status, 0, 4 * MLPSP_STATUS_WORDS, (cudaStream_t)stream), "status_reset");
+}
+
+extern "C" int64_t mlpsp_frame_scratch_bytes(int32_t n, int32_t width, int32_t height, int32_t tile,
+                                             int64_t max_pairs, int64_t max_records) {
+  if (n < 0 || width <= 0 || height <= 0 || tile <= 0 || max_pairs < 0 || max_records < 0) return -1;
+  return carve_scratch(nullptr, n, width, height, tile, max_pairs, max_records).bytes;
+}
+
+extern "C" int mlpsp_validate_tile_lists(const int32_t* tile_offsets, const int32_t* tile_prims, int32_t num_tiles_,
+                                         int64_t pairs, int32_t tile_capacity, int32_t n, int32_t* status,
+                                         void* stream) {
+  MLPSP_REQUIRE(tile_offsets && status && num_tiles_ > 0, MLPSP_E_ARG, "validate: tile_offsets/status missing");
+  MLPSP_REQUIRE(pairs >= 0 && pairs <= 2147483647LL, MLPSP_E_LIMIT, "validate: candidate list is too large for int32 offsets");
+  MLPSP_REQUIRE(pairs == 0 || tile_prims, MLPSP_E_ARG, "validate: candidate list missing");
+  MLPSP_REQUIRE(n >= 0, MLPSP_E_LIMIT, "validate: primitive count is outside the supported int32 range");
+  const int64_t work = std::max<int64_t>(num_tiles_, pairs);
+  const int blocks = (int)std::min<int64_t>(4096, (work + 255) / 256);
+  k_validate_lists<<<blocks, 256, 0, (cudaStream_t)stream>>>(tile_offsets, tile_prims, num_tiles_, pairs,
+                                                            tile_capacity, n, status);
+  return cuda_check(cudaGetLastError(), "validate");
+}
+
+extern "C" int mlpsp_bin_tiles(const mlpsp_scene* sc, const mlpsp_frame* fr, void* stream) {
+  int rc = check_frame_common(sc, fr, "mlpsp_bin_tiles");
+  if (rc) return rc;
+  MLPSP_REQUIRE(fr->view && fr->proj, MLPSP_E_ARG, "mlpsp_bin_tiles: view/proj matrices missing");
+  Scratch s;
+  rc = get_scratch(sc, fr, s, "mlpsp_bin_tiles");
+  if (rc) return rc;
+  return launch_bin(sc, fr, s, (cudaStream_t)stream);
+}
+
+extern "C" int mlpsp_sort_tiles(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, void* stream) {
+  int rc = check_frame_common(sc, fr, "mlpsp_sort_tiles");
+  if (rc) return rc;
+  MLPSP_REQUIRE(fr->rays_o && fr->rays_d, MLPSP_E_ARG, "mlpsp_sort_tiles: rays missing");
+  return launch_sort(sc, fr, keys_out, (cudaStream_t)stream);
+}
+
+extern "C" int mlpsp_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, void* stream) {
+  int rc = check_frame_common(sc, fr, "mlpsp_hit_masks");
+  if (rc) return rc;
+  MLPSP_REQUIRE(fr->rays_o && fr->rays_d && mask_geo, MLPSP_E_ARG, "mlpsp_hit_masks: rays or output missing");
+  return launch_hit_masks(sc, fr, mask_geo, (cudaStream_t)stream);
+}
+
+extern "C" int mlpsp_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, void* stream) {
+  int rc = check_frame_common(sc, fr, "mlpsp_render_sorted");
+  if (rc) return rc;
+  Scratch s;
+  rc = get_scratch(sc, fr, s, "mlpsp_render_sorted");
+  if (rc) return rc;
+  return render_sorted_checked(sc, fr, s, (cudaStream_t)stream);
+}
+
+extern "C" int mlpsp_render_frame(const mlpsp_scene* sc, const mlpsp_frame* fr, void* stream) {
+  int rc = check_frame_common(sc, fr, "mlpsp_render_frame");
+  if (rc) return rc;
+  MLPSP_REQUIRE(fr->view && fr->proj, MLPSP_E_ARG, "mlpsp_render_frame: view/proj matrices missing");
+  MLPSP_REQUIRE(fr->rays_o && fr->rays_d, MLPSP_E_ARG, "mlpsp_render_frame: rays missing");
+  Scratch s;
+  rc = get_scratch(sc, fr, s, "mlpsp_render_frame");
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  rc = launch_bin(sc, fr, s, st);
+  if (rc) return rc;
+  rc = launch_sort(sc, fr, nullptr, st);
+  if (rc) return rc;
+  return render_sorted_checked(sc, fr, s, st);
+}
+
+// ------------------------------------------------------------ grouped evaluator on records ----
+namespace mlpsp {
+
+__global__ void k_grouped_counts(const int64_t* __restrict__ offsets, int n, int32_t* __restrict__ cnt) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) cnt[i] = (int32_t)(offsets[i + 1] - offsets[i]);
+}
+
+__global__ void k_grouped_records(const float* __restrict__ x6, int64_t R, RecIn* __restrict__ rec) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= R) return;
+  RecIn r;
+  r.rdx = x6[i * 6]; r.rdy = x6[i * 6 + 1]; r.rdz = x6[i * 6 + 2];
+  r.dx = x6[i * 6 + 3]; r.dy = x6[i * 6 + 4]; r.dz = x6[i * 6 + 5];
+  r.decay = 1.f; r.slot = (uint32_t)i;
+  rec[i] = r;
+}
+
+static Scratch grouped_layout(void* base, int64_t R, int n) {
+  Scratch s;
+  memset(&s, 0, sizeof(s));
+  char* p = (char*)base;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { char* r = p ? p + off : nullptr; off += align_up(bytes, 256); return r; };
+  s.prim_cnt = (int32_t*)take(4 * ((int64_t)n + 1));
+  s.prim_cursor = (int32_t*)take(4 * ((int64_t)n + 1));
+  s.prim_off = (int32_t*)take(4 * ((int64_t)n + 2));
+  s.scan_blk = (int32_t*)take(4 * 2 * ((int64_t)n / kScanItems + 4));
+  s.max_work = (int64_t)n + R / kRowsPerItem + 2;
+  s.work = (int2*)take(8 * s.max_work);
+  s.rec_in = (RecIn*)take(32 * std::max<int64_t>(R, 1));
+  s.counters = (int32_t*)take(4 * kNumCounters);
+  s.bytes = off;
+  return s;
+}
+
+}  // namespace mlpsp
+
+extern "C" int64_t mlpsp_mlp_grouped_scratch_bytes(int64_t num_records, int32_t n) {
+  if (num_records < 0 || n < 0) return -1;
+  return grouped_layout(nullptr, num_records, n).bytes;
+}
+
+extern "C" int mlpsp_mlp_grouped(const mlpsp_scene* sc, int32_t precision, const int64_t* offsets, const float* x6,
+                                 int64_t num_records, float* out4, void* scratch, int64_t scratch_bytes,
+                                 int32_t* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  MLPSP_REQUIRE(sc && offsets && status && num_records >= 0, MLPSP_E_ARG, "mlpsp_mlp_grouped: bad arguments");
+  MLPSP_REQUIRE(num_records < (1ll << 31), MLPSP_E_LIMIT, "mlpsp_mlp_grouped: more than 2^31-1 records");
+  MLPSP_REQUIRE(num_records == 0 || (x6 && out4), MLPSP_E_ARG, "mlpsp_mlp_grouped: null record arrays");
+  const int n = sc->n;
+  const Scratch q = grouped_layout(nullptr, num_records, n);
+  MLPSP_REQUIRE(scratch && scratch_bytes >= q.bytes, MLPSP_E_SCRATCH, "mlpsp_mlp_grouped: scratch needs %lld bytes",
+                (long long)q.bytes);
+  if (n == 0 || num_records == 0) return MLPSP_OK;
+  Scratch s = grouped_layout(scratch, num_records, n);
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.counters, 0, 4 * kNumCounters, st));
+  k_grouped_counts<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, s.prim_cnt);
+  k_grouped_records<<<(unsigned)((num_records + 255) / 256), 256, 0, st>>>(x6, num_records, s.rec_in);
+  int rc = launch_prim_scan(s, n, 0, status, st);
+  if (rc) return rc;
+  if (precision == MLPSP_PRECISION_F16)
+    return launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, kOutSigmaRaw, status, st);
+  MLPSP_REQUIRE(precision == MLPSP_PRECISION_F32, MLPSP_E_ARG, "mlpsp_mlp_grouped: unknown precision %d", precision);
+  return launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, kOutSigmaRaw, status, st);
+}

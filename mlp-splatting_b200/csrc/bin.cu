@@ -1,0 +1,304 @@
+// Geometry packing and screen-space tile binning.
+//
+// Binning restates the PyTorch culling of scannet/cumodel.py:994-1070 without the dense
+// [tiles x primitives] matrix: one thread per primitive projects its bounding circle and derives
+// the inclusive tile rectangle that satisfies the strict overlap predicate; a count pass, a scan
+// over tiles and a scatter pass build the tile-major lists, and a per-tile radix sort by id puts
+// every list in ascending primitive order (the order nonzero() gives the reference).
+#include <algorithm>
+#include "frame.cuh"
+#include "block_sort.cuh"
+
+namespace mlpsp {
+
+// ------------------------------------------------------------------ packing / normalise ----
+__global__ void k_pack_geometry(const float* __restrict__ pos, const float* __restrict__ ls,
+                                const float* __restrict__ quat, int n, float4* __restrict__ geom) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float lx = ls[i * 3], ly = ls[i * 3 + 1], lz = ls[i * 3 + 2];
+  const float sx = det_exp(lx), sy = det_exp(ly), sz = det_exp(lz);
+  geom[(size_t)i * 4 + 0] = make_float4(pos[i * 3], pos[i * 3 + 1], pos[i * 3 + 2], quat[i * 4]);
+  geom[(size_t)i * 4 + 1] = make_float4(quat[i * 4 + 1], quat[i * 4 + 2], quat[i * 4 + 3], fmaxf(fmaxf(sx, sy), sz));
+  geom[(size_t)i * 4 + 2] = make_float4(det_exp(fmul(-2.f, lx)), det_exp(fmul(-2.f, ly)), det_exp(fmul(-2.f, lz)), 0.f);
+  geom[(size_t)i * 4 + 3] = make_float4(lx, ly, lz, 0.f);
+}
+
+template <int DIM>
+__global__ void k_normalize_rows(const float* __restrict__ in, float* __restrict__ out, int64_t rows) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  float a[DIM];
+#pragma unroll
+  for (int k = 0; k < DIM; ++k) a[k] = in[i * DIM + k];
+  float s = fmul(a[0], a[0]);
+#pragma unroll
+  for (int k = 1; k < DIM; ++k) s = ffma(a[k], a[k], s);
+  const float nrm = fmaxf(__fsqrt_rn(s), 1e-12f);
+#pragma unroll
+  for (int k = 0; k < DIM; ++k) out[i * DIM + k] = fdiv(a[k], nrm);
+}
+
+// ------------------------------------------------------------------------------ binning ----
+struct BinCam {
+  float view[16];
+  float proj[16];
+  float radius_mult, focal;
+  int W, H, ts, ntx, nty;
+};
+
+__device__ __forceinline__ float dot4(const float* row, float x, float y, float z, float w) {
+  float a = fmul(row[0], x);
+  a = ffma(row[1], y, a);
+  a = ffma(row[2], z, a);
+  a = ffma(row[3], w, a);
+  return a;
+}
+
+// smallest t with (t+1)*ts > lo and largest t with t*ts < hi, clipped to [0, nt)
+__device__ __forceinline__ bool tile_span(float lo, float hi, int ts, int nt, int& t0, int& t1) {
+  if (!(lo == lo) || !(hi == hi)) return false;
+  const float fts = (float)ts;
+  int a, b;
+  if (lo < 0.f) a = 0;
+  else if (lo >= fmul((float)nt, fts)) return false;
+  else {
+    a = (int)fdiv(lo, fts);
+    while (a > 0 && (float)(a * ts) > lo) --a;
+    while ((float)((a + 1) * ts) <= lo) ++a;
+  }
+  if (hi <= 0.f) return false;
+  else if (hi > fmul((float)(nt - 1), fts)) b = nt - 1;
+  else {
+    b = (int)fdiv(hi, fts);
+    while ((float)(b * ts) >= hi) --b;
+    while (b + 1 < nt && (float)((b + 1) * ts) < hi) ++b;
+  }
+  if (a >= nt || b < 0 || a > b) return false;
+  t0 = a; t1 = b;
+  return true;
+}
+
+__device__ __forceinline__ bool prim_rect(const float4* __restrict__ geom, int p, const BinCam& c, int r[4]) {
+  const float4 g0 = __ldg(geom + (size_t)p * 4);
+  const float smax = __ldg(geom + (size_t)p * 4 + 1).w;
+  const float vx = dot4(c.view + 0, g0.x, g0.y, g0.z, 1.f);
+  const float vy = dot4(c.view + 4, g0.x, g0.y, g0.z, 1.f);
+  const float vz = dot4(c.view + 8, g0.x, g0.y, g0.z, 1.f);
+  const float vw = dot4(c.view + 12, g0.x, g0.y, g0.z, 1.f);
+  if (!(vz > 0.001f)) return false;
+  const float world_r = fmul(smax, c.radius_mult);
+  const float pix_r = fmul(fdiv(world_r, fadd(vz, 1e-8f)), c.focal);
+  const float cx = dot4(c.proj + 0, vx, vy, vz, vw);
+  const float cy = dot4(c.proj + 4, vx, vy, vz, vw);
+  float cw = dot4(c.proj + 12, vx, vy, vz, vw);
+  if (cw == 0.f) cw = fadd(cw, 1e-6f);
+  const float nx = fdiv(cx, cw), ny = fdiv(cy, cw);
+  const float sx = fmul(fmul(fadd(nx, 1.f), 0.5f), (float)c.W);
+  const float sy = fmul(fmul(fadd(ny, 1.f), 0.5f), (float)c.H);
+  if (!tile_span(fsub(sx, pix_r), fadd(sx, pix_r), c.ts, c.ntx, r[0], r[1])) return false;
+  if (!tile_span(fsub(sy, pix_r), fadd(sy, pix_r), c.ts, c.nty, r[2], r[3])) return false;
+  return true;
+}
+
+// Visit every tile of this thread's rectangle; rectangles larger than 32 tiles are walked by the
+// whole warp so one near primitive cannot serialise a thread.
+template <typename F>
+__device__ __forceinline__ void for_each_tile(bool has, int x0, int x1, int y0, int y1, int ntx, int p, F f) {
+  const int w = x1 - x0 + 1, h = y1 - y0 + 1;
+  const int area = has ? w * h : 0;
+  const bool big = area > 32;
+  if (has && !big)
+    for (int ty = y0; ty <= y1; ++ty)
+      for (int tx = x0; tx <= x1; ++tx) f(ty * ntx + tx, p);
+  unsigned bigs = __ballot_sync(0xffffffffu, big);
+  const int lane = threadIdx.x & 31;
+  while (bigs) {
+    const int src = __ffs(bigs) - 1;
+    bigs &= bigs - 1;
+    const int bx0 = __shfl_sync(0xffffffffu, x0, src), by0 = __shfl_sync(0xffffffffu, y0, src);
+    const int bw = __shfl_sync(0xffffffffu, w, src), ba = __shfl_sync(0xffffffffu, area, src);
+    const int bp = __shfl_sync(0xffffffffu, p, src);
+    for (int i = lane; i < ba; i += 32) f((by0 + i / bw) * ntx + bx0 + i % bw, bp);
+  }
+}
+
+__global__ void k_bin_count(const float4* __restrict__ geom, int n, BinCam cam, uint2* __restrict__ rect,
+                            int32_t* __restrict__ tile_cnt) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  int r[4] = {1, 0, 1, 0};
+  const bool has = (p < n) && prim_rect(geom, p, cam, r);
+  if (p < n) rect[p] = has ? make_uint2((uint32_t)r[0] | ((uint32_t)r[1] << 16), (uint32_t)r[2] | ((uint32_t)r[3] << 16))
+                           : make_uint2(1u, 1u);  // x0=1 > x1=0
+  for_each_tile(has, r[0], r[1], r[2], r[3], cam.ntx, p, [&](int t, int) { atomicAdd(tile_cnt + t, 1); });
+}
+
+__global__ void k_bin_scatter(int n, int ntx, const uint2* __restrict__ rect, const int32_t* __restrict__ tile_offsets,
+                              int32_t* __restrict__ tile_fill, int32_t* __restrict__ tile_prims,
+                              const int32_t* __restrict__ status) {
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  int x0 = 1, x1 = 0, y0 = 1, y1 = 0;
+  if (p < n) {
+    const uint2 r = rect[p];
+    x0 = r.x & 0xffff; x1 = r.x >> 16; y0 = r.y & 0xffff; y1 = r.y >> 16;
+  }
+  const bool has = (p < n) && x0 <= x1 && y0 <= y1;
+  for_each_tile(has, x0, x1, y0, y1, ntx, p, [&](int t, int q) {
+    const int slot = atomicAdd(tile_fill + t, 1);
+    tile_prims[tile_offsets[t] + slot] = q;
+  });
+}
+
+// ------------------------------------------------------------- multi-block exclusive scan ----
+__global__ void k_scan_partial(const int32_t* __restrict__ in, int64_t n, int32_t* __restrict__ blk) {
+  __shared__ int warp_sums[32];
+  const int64_t base = (int64_t)blockIdx.x * kScanItems;
+  int v = 0;
+  for (int j = 0; j < kScanItems / 1024; ++j) {
+    const int64_t i = base + threadIdx.x + j * 1024;
+    if (i < n) v += in[i];
+  }
+  int total;
+  block_exclusive_scan(v, warp_sums, total);
+  if (threadIdx.x == 0) blk[blockIdx.x] = total;
+}
+
+// single block: exclusive scan of blk[0,nblk) in place, grand total -> blk[nblk]
+__global__ void k_scan_top(int32_t* __restrict__ blk, int nblk) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < nblk; b0 += 1024) {
+    const int i = b0 + threadIdx.x;
+    const int v = (i < nblk) ? blk[i] : 0;
+    int total;
+    const int ex = block_exclusive_scan(v, warp_sums, total);
+    const int c = carry;
+    if (i < nblk) blk[i] = c + ex;
+    __syncthreads();
+    if (threadIdx.x == 0) carry = c + total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) blk[nblk] = carry;
+}
+
+// out[i] = exclusive prefix; out[n] = total.  Thread t of a block owns 4 consecutive items.
+__global__ void k_scan_final(const int32_t* __restrict__ in, int64_t n, const int32_t* __restrict__ blk,
+                             int32_t* __restrict__ out) {
+  __shared__ int warp_sums[32];
+  const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
+  int v[4], s = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[j] = (base + j < n) ? in[base + j] : 0; s += v[j]; }
+  int total;
+  int ex = block_exclusive_scan(s, warp_sums, total) + blk[blockIdx.x];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { if (base + j < n) out[base + j] = ex; ex += v[j]; }
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) out[n] = blk[gridDim.x];
+}
+
+// longest tile list, capacity check, pair total
+__global__ void k_bin_finish(const int32_t* __restrict__ tile_cnt, int T, const int32_t* __restrict__ tile_offsets,
+                             int capacity, int64_t max_pairs, int32_t* __restrict__ status,
+                             int32_t* __restrict__ counters) {
+  int mx = 0;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x) mx = max(mx, tile_cnt[t]);
+  mx = __reduce_max_sync(0xffffffffu, mx);
+  if ((threadIdx.x & 31) == 0 && mx > 0) {
+    atomicMax(status + MLPSP_ST_MAX_TILE_LEN, mx);
+    if (capacity > 0 && mx > capacity) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_TILE_CAPACITY);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    const int M = tile_offsets[T];
+    status[MLPSP_ST_PAIRS] = M;
+    counters[kCtrPairs] = M;
+    if (M < 0 || (int64_t)M > max_pairs) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_PAIR_OVERFLOW);
+  }
+}
+
+// per-tile ascending sort of candidate ids (lists no longer than CAP; longer lists were rejected)
+template <int THREADS, int CAP>
+__global__ void __launch_bounds__(THREADS) k_sort_ids(const int32_t* __restrict__ tile_offsets,
+                                                      int32_t* __restrict__ tile_prims,
+                                                      const int32_t* __restrict__ status) {
+  using Sort = BlockRadixSort<THREADS, CAP>;
+  __shared__ typename Sort::Smem sm;
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int s = tile_offsets[blockIdx.x], e = tile_offsets[blockIdx.x + 1];
+  const int n = min(e - s, CAP);
+  if (n <= 1) return;
+  for (int i = threadIdx.x; i < n; i += THREADS) {
+    const int32_t p = tile_prims[s + i];
+    sm.key[0][i] = (uint32_t)p;
+    sm.val[0][i] = p;
+  }
+  __syncthreads();
+  const int cur = Sort::sort(sm, n);
+  for (int i = threadIdx.x; i < n; i += THREADS) tile_prims[s + i] = sm.val[cur][i];
+}
+
+int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cudaStream_t st) {
+  const int nblk = (int)((n + kScanItems - 1) / kScanItems);
+  if (nblk == 0) return MLPSP_OK;
+  k_scan_partial<<<nblk, 1024, 0, st>>>(in, n, blk);
+  k_scan_top<<<1, 1024, 0, st>>>(blk, nblk);
+  k_scan_final<<<nblk, 1024, 0, st>>>(in, n, blk, out);
+  return cuda_check(cudaGetLastError(), "scan");
+}
+
+constexpr int kSortCap = 2048;  // per-tile sort capacity (>= tile capacity 1536)
+
+int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st) {
+  const int T = num_tiles(fr->width, fr->height, fr->tile);
+  BinCam cam;
+  for (int i = 0; i < 16; ++i) { cam.view[i] = fr->view[i]; cam.proj[i] = fr->proj[i]; }
+  cam.radius_mult = (float)sqrt(-2.0 * log((double)fr->threshold));
+  const float fx = (cam.proj[0] * (float)fr->width) / 2.0f;
+  const float fy = (cam.proj[5] * (float)fr->height) / 2.0f;
+  cam.focal = (fx + fy) * 0.5f;
+  cam.W = fr->width; cam.H = fr->height; cam.ts = fr->tile;
+  cam.ntx = (fr->width + fr->tile - 1) / fr->tile;
+  cam.nty = (fr->height + fr->tile - 1) / fr->tile;
+  MLPSP_REQUIRE(cam.ntx < 65536 && cam.nty < 65536, MLPSP_E_LIMIT, "tile grid beyond 65535 per axis");
+  MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
+                "tile_capacity must be in [1, %d]", kSortCap);
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_cnt, 0, 4 * (size_t)(T + 1), st));
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_fill, 0, 4 * (size_t)T, st));
+  const int n = sc->n;
+  if (n > 0) k_bin_count<<<(n + 255) / 256, 256, 0, st>>>((const float4*)sc->geom, n, cam, s.rect, s.tile_cnt);
+  int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
+  if (rc) return rc;
+  k_bin_finish<<<std::min(64, (T + 255) / 256), 256, 0, st>>>(s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
+                                                              fr->max_pairs, fr->status, s.counters);
+  if (n > 0) {
+    k_bin_scatter<<<(n + 255) / 256, 256, 0, st>>>(n, cam.ntx, s.rect, fr->tile_offsets, s.tile_fill,
+                                                   fr->tile_prims, fr->status);
+    k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);
+  }
+  return cuda_check(cudaGetLastError(), "bin");
+}
+
+}  // namespace mlpsp
+
+using namespace mlpsp;
+
+extern "C" int mlpsp_pack_geometry(const float* positions, const float* log_scales, const float* quats_unit,
+                                   int32_t n, float* geom, void* stream) {
+  MLPSP_REQUIRE(n >= 0 && (n == 0 || (positions && log_scales && quats_unit && geom)), MLPSP_E_ARG,
+                "mlpsp_pack_geometry: null pointer or negative count");
+  if (n == 0) return MLPSP_OK;
+  k_pack_geometry<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, log_scales, quats_unit, n, (float4*)geom);
+  return cuda_check(cudaGetLastError(), "pack_geometry");
+}
+
+extern "C" int mlpsp_normalize_rows(const float* in, float* out, int64_t rows, int32_t dim, void* stream) {
+  MLPSP_REQUIRE(rows >= 0 && (dim == 3 || dim == 4) && (rows == 0 || (in && out)), MLPSP_E_ARG,
+                "mlpsp_normalize_rows: dim must be 3 or 4 and pointers non-null");
+  if (rows == 0) return MLPSP_OK;
+  const unsigned blocks = (unsigned)((rows + 255) / 256);
+  if (dim == 3) k_normalize_rows<3><<<blocks, 256, 0, (cudaStream_t)stream>>>(in, out, rows);
+  else k_normalize_rows<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(in, out, rows);
+  return cuda_check(cudaGetLastError(), "normalize_rows");
+}

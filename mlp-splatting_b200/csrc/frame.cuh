@@ -1,0 +1,125 @@
+// Scratch layout of one frame and small host helpers shared by the stage launchers.
+#pragma once
+#include <algorithm>
+#include <cstdio>
+#include <cstdarg>
+#include "common.cuh"
+
+namespace mlpsp {
+
+// Rows handled by one evaluator work item (one tensor-core M tile).
+constexpr int kRowsPerItem = 128;
+// counters[] slots (device int32)
+enum Counter {
+  kCtrRecords = 0,   // records appended by the hit pass of the current wave
+  kCtrWork = 1,      // evaluator work items of the current wave
+  kCtrWorkNext = 2,  // dynamic work cursor of the evaluator
+  kCtrActive0 = 3,   // active tile count, list 0
+  kCtrActive1 = 4,   // active tile count, list 1
+  kCtrPairs = 5,     // total candidate pairs (binning)
+  kCtrScratch = 6,
+  kNumCounters = 16
+};
+
+// One evaluator input record (32 bytes): encoded-input vector, decay and the compositing slot.
+struct __align__(16) RecIn {
+  float rdx, rdy, rdz, dx;
+  float dy, dz, decay;
+  uint32_t slot;
+};
+
+struct Scratch {
+  int32_t* tile_cnt;     // [T+1]
+  int32_t* tile_fill;    // [T]
+  uint2* rect;           // [n]  (x0 | x1<<16, y0 | y1<<16); x0 > x1 marks "culled"
+  int32_t* scan_blk;     // block sums of the multi-block scans
+  float4* px_state;      // [P] (C.r, C.g, C.b, transmittance)
+  float2* px_depth;      // [P] (sum w t, sum w)
+  uint32_t* masks32;     // [2*max_pairs] evaluated-hit mask halves per pair
+  uint32_t* pair_base;   // [max_pairs] first compositing slot of the pair
+  int32_t* prim_cnt;     // [n] records per primitive in the current wave
+  int32_t* prim_cursor;  // [n]
+  int32_t* prim_off;     // [n+1]
+  int2* work;            // [max_work] (primitive, first row)
+  RecIn* rec_in;         // [max_records] primitive-major
+  float4* rec_out;       // [max_records] (R,G,B,alpha) at compositing slots
+  float* rec_t;          // [max_records] t* at compositing slots
+  float4* rec_gate;      // [max_records] feature gates at compositing slots
+  int32_t* active[2];    // [T] each
+  int32_t* counters;     // [kNumCounters]
+  int64_t max_work;
+  int64_t bytes;
+};
+
+inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+inline int num_tiles(int W, int H, int ts) { return ((W + ts - 1) / ts) * ((H + ts - 1) / ts); }
+
+constexpr int kScanItems = 4096;  // elements per block of the multi-block scans
+
+// Carve the scratch block.  base may be null (size query).
+inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t max_pairs, int64_t max_records) {
+  Scratch s;
+  char* p = static_cast<char*>(base);
+  int64_t off = 0;
+  const int64_t T = num_tiles(W, H, ts);
+  const int64_t P = (int64_t)W * H;
+  auto take = [&](int64_t bytes) { char* r = p ? p + off : nullptr; off += align_up(bytes, 256); return r; };
+  s.tile_cnt = (int32_t*)take(4 * (T + 1));
+  s.tile_fill = (int32_t*)take(4 * T);
+  s.rect = (uint2*)take(8 * (int64_t)n);
+  const int64_t nblk = (std::max<int64_t>(n, T) + kScanItems - 1) / kScanItems + 2;
+  s.scan_blk = (int32_t*)take(4 * 2 * nblk);
+  s.px_state = (float4*)take(16 * P);
+  s.px_depth = (float2*)take(8 * P);
+  s.masks32 = (uint32_t*)take(8 * max_pairs);
+  s.pair_base = (uint32_t*)take(4 * max_pairs);
+  s.prim_cnt = (int32_t*)take(4 * (int64_t)n);
+  s.prim_cursor = (int32_t*)take(4 * (int64_t)n);
+  s.prim_off = (int32_t*)take(4 * ((int64_t)n + 1));
+  s.max_work = (int64_t)n + max_records / kRowsPerItem + 2;
+  s.work = (int2*)take(8 * s.max_work);
+  s.rec_in = (RecIn*)take(32 * max_records);
+  s.rec_out = (float4*)take(16 * max_records);
+  s.rec_t = (float*)take(4 * max_records);
+  s.rec_gate = (float4*)take(16 * max_records);
+  s.active[0] = (int32_t*)take(4 * T);
+  s.active[1] = (int32_t*)take(4 * T);
+  s.counters = (int32_t*)take(4 * kNumCounters);
+  s.bytes = off;
+  return s;
+}
+
+// last-error text (thread-local) for the negative return codes
+void set_error(const char* fmt, ...);
+int cuda_check(cudaError_t e, const char* what);
+
+#define MLPSP_CUDA_OK(call)                                         \
+  do {                                                              \
+    int rc__ = ::mlpsp::cuda_check((call), #call);                  \
+    if (rc__ != 0) return rc__;                                     \
+  } while (0)
+
+#define MLPSP_REQUIRE(cond, code, ...)                              \
+  do {                                                              \
+    if (!(cond)) { ::mlpsp::set_error(__VA_ARGS__); return (code); }\
+  } while (0)
+
+// stage launchers (defined in the .cu files)
+int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
+int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st);
+int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st);
+int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
+int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
+                   const int32_t* counters, float4* rec_out, int out_mode, int32_t* status, cudaStream_t st);
+int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
+                   const int32_t* counters, float4* rec_out, int out_mode, int32_t* status, cudaStream_t st);
+
+// evaluator output modes
+constexpr int kOutAlpha = 0;     // (R,G,B, 1-exp(-softplus(o3)*decay)) scattered to rec.slot
+constexpr int kOutSigmaRaw = 1;  // (R,G,B, softplus(o3)) scattered to rec.slot
+
+// multi-block exclusive scan of per-primitive record counts plus evaluator work-item emission
+int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st);
+
+}  // namespace mlpsp

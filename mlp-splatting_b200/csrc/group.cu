@@ -1,0 +1,192 @@
+// Record grouping helpers that mirror scannet/primitive_csr.py:23-29 (group_records: stable sort of
+// record ids by primitive + bincount + cumsum) and scannet/primitive_gemm.py:186-203
+// (prepare_groups: fixed-size segments of every primitive's record range).
+//
+// group_records is a device-wide stable LSD radix sort (4-bit digits) of (primitive id, record
+// index) pairs.  A block owns 2048 consecutive items; inside it, chunks of 32 items are ranked with
+// match.any, per-(digit, chunk) counts are scanned digit-major, and a global scan of per-block digit
+// totals (digit-major, block-minor) gives every block its scatter bases, so equal ids keep their
+// record order.
+#include "frame.cuh"
+
+namespace mlpsp {
+
+int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cudaStream_t st);
+
+constexpr int kGsItems = 2048, kGsThreads = 256, kGsChunks = kGsItems / 32;
+
+__global__ void __launch_bounds__(kGsThreads) k_gs_hist(const uint32_t* __restrict__ keys, int64_t n, int shift,
+                                                        int nblocks, int32_t* __restrict__ ghist) {
+  __shared__ int h[16];
+  if (threadIdx.x < 16) h[threadIdx.x] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kGsItems;
+  for (int j = threadIdx.x; j < kGsItems; j += kGsThreads)
+    if (base + j < n) atomicAdd(&h[(keys[base + j] >> shift) & 15u], 1);
+  __syncthreads();
+  if (threadIdx.x < 16) ghist[threadIdx.x * nblocks + blockIdx.x] = h[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(kGsThreads) k_gs_scatter(
+    const uint32_t* __restrict__ keys, const uint32_t* __restrict__ vals, int64_t n, int shift, int nblocks,
+    const int32_t* __restrict__ gbase, uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out) {
+  __shared__ int cnt[16 * kGsChunks];
+  __shared__ int warp_sums[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t base = (int64_t)blockIdx.x * kGsItems;
+  for (int i = tid; i < 16 * kGsChunks; i += kGsThreads) cnt[i] = 0;
+  __syncthreads();
+  for (int c = warp; c < kGsChunks; c += kGsThreads / 32) {
+    const int64_t i = base + c * 32 + lane;
+    const bool valid = i < n;
+    const uint32_t d = valid ? ((keys[i] >> shift) & 15u) : 0xffffffffu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    if (valid && lane == __ffs(peers) - 1) cnt[d * kGsChunks + c] = __popc(peers);
+  }
+  __syncthreads();
+  constexpr int per = 16 * kGsChunks / kGsThreads;  // 4
+  int local = 0;
+#pragma unroll
+  for (int j = 0; j < per; ++j) local += cnt[tid * per + j];
+  int total;
+  int ex = block_exclusive_scan(local, warp_sums, total);
+#pragma unroll
+  for (int j = 0; j < per; ++j) { const int v = cnt[tid * per + j]; cnt[tid * per + j] = ex; ex += v; }
+  __syncthreads();
+  for (int c = warp; c < kGsChunks; c += kGsThreads / 32) {
+    const int64_t i = base + c * 32 + lane;
+    const bool valid = i < n;
+    const uint32_t k = valid ? keys[i] : 0u;
+    const uint32_t d = valid ? ((k >> shift) & 15u) : 0xffffffffu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    if (valid) {
+      const int64_t dst = (int64_t)gbase[d * nblocks + blockIdx.x] + (cnt[d * kGsChunks + c] - cnt[d * kGsChunks]) +
+                          __popc(peers & ((1u << lane) - 1u));
+      keys_out[dst] = k;
+      vals_out[dst] = vals[i];
+    }
+  }
+}
+
+__global__ void k_gs_init(const int32_t* __restrict__ ids, int64_t n, int nprim, uint32_t* __restrict__ keys,
+                          uint32_t* __restrict__ vals, int32_t* __restrict__ counts) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int32_t p = ids[i];
+  keys[i] = (uint32_t)p;
+  vals[i] = (uint32_t)i;
+  if (p >= 0 && p < nprim) atomicAdd(counts + p, 1);
+}
+
+__global__ void k_gs_finish(const uint32_t* __restrict__ vals, int64_t n, int64_t* __restrict__ order,
+                            const int32_t* __restrict__ off32, int nprim, int64_t* __restrict__ offsets) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) order[i] = (int64_t)vals[i];
+  if (i <= nprim) offsets[i] = (int64_t)off32[i];
+}
+
+__global__ void k_groups_count(const int64_t* __restrict__ offsets, int n, int64_t seg, int32_t* __restrict__ cnt) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) cnt[i] = (int32_t)((offsets[i + 1] - offsets[i] + seg - 1) / seg);
+}
+
+__global__ void k_groups_fill(const int64_t* __restrict__ offsets, int n, int64_t seg, const int32_t* __restrict__ goff32,
+                              int64_t* __restrict__ group_offsets, int64_t* __restrict__ primitives,
+                              int64_t* __restrict__ starts, int64_t max_groups) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > n) return;
+  group_offsets[i] = goff32[i];
+  if (i == n || !primitives || !starts) return;
+  const int g0 = goff32[i], g1 = goff32[i + 1];
+  for (int g = g0; g < g1; ++g)
+    if (g < max_groups) { primitives[g] = i; starts[g] = offsets[i] + (int64_t)(g - g0) * seg; }
+}
+
+// scratch: counts[n+1] | off32[n+2] | scan blocks | ghist[16*nblocks] | gbase[16*nblocks+1] | 4 x uint32[R]
+struct GsLayout { int64_t o[9]; int64_t bytes; };
+static GsLayout gs_layout(int64_t R, int n) {
+  GsLayout L;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { int64_t o = off; off += align_up(bytes, 256); return o; };
+  const int64_t nblocks = std::max<int64_t>((R + kGsItems - 1) / kGsItems, 1);
+  L.o[0] = take(4 * ((int64_t)n + 1));
+  L.o[1] = take(4 * ((int64_t)n + 2));
+  const int64_t scan_n = std::max<int64_t>((int64_t)n + 1, 16 * nblocks);
+  L.o[2] = take(4 * (scan_n / kScanItems + 4));
+  L.o[3] = take(4 * 16 * nblocks);
+  L.o[4] = take(4 * (16 * nblocks + 1));
+  for (int i = 5; i < 9; ++i) L.o[i] = take(4 * R);
+  L.bytes = off;
+  return L;
+}
+
+}  // namespace mlpsp
+
+using namespace mlpsp;
+
+extern "C" int64_t mlpsp_group_records_scratch_bytes(int64_t num_records, int32_t n) {
+  if (num_records < 0 || n < 0) return -1;
+  return gs_layout(num_records, n).bytes;
+}
+
+extern "C" int mlpsp_group_records(const int32_t* primitive_ids, int64_t num_records, int32_t n, int64_t* offsets,
+                                   int64_t* order, void* scratch, int64_t scratch_bytes, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  MLPSP_REQUIRE(num_records >= 0 && n >= 0 && offsets, MLPSP_E_ARG, "mlpsp_group_records: bad arguments");
+  MLPSP_REQUIRE(num_records < (1ll << 31), MLPSP_E_LIMIT, "mlpsp_group_records: more than 2^31-1 records");
+  MLPSP_REQUIRE(num_records == 0 || (primitive_ids && order), MLPSP_E_ARG, "mlpsp_group_records: null pointer");
+  const int64_t R = num_records;
+  const int nblocks = (int)((R + kGsItems - 1) / kGsItems);
+  GsLayout L = gs_layout(R, n);
+  MLPSP_REQUIRE(scratch && scratch_bytes >= L.bytes, MLPSP_E_SCRATCH, "mlpsp_group_records: scratch needs %lld bytes",
+                (long long)L.bytes);
+  const int64_t o_cnt = L.o[0], o_off = L.o[1], o_blk = L.o[2], o_gh = L.o[3], o_gb = L.o[4];
+  const int64_t o_k0 = L.o[5], o_k1 = L.o[6], o_v0 = L.o[7], o_v1 = L.o[8];
+  char* b = (char*)scratch;
+  int32_t* counts = (int32_t*)(b + o_cnt); int32_t* off32 = (int32_t*)(b + o_off); int32_t* blk = (int32_t*)(b + o_blk);
+  int32_t* ghist = (int32_t*)(b + o_gh); int32_t* gbase = (int32_t*)(b + o_gb);
+  uint32_t* k[2] = {(uint32_t*)(b + o_k0), (uint32_t*)(b + o_k1)};
+  uint32_t* v[2] = {(uint32_t*)(b + o_v0), (uint32_t*)(b + o_v1)};
+  MLPSP_CUDA_OK(cudaMemsetAsync(counts, 0, 4 * ((size_t)n + 1), st));
+  if (R > 0) k_gs_init<<<(unsigned)((R + 255) / 256), 256, 0, st>>>(primitive_ids, R, n, k[0], v[0], counts);
+  int rc = launch_scan_i32(counts, (int64_t)n, blk, off32, st);
+  if (rc) return rc;
+  if (n == 0) MLPSP_CUDA_OK(cudaMemsetAsync(off32, 0, 4, st));
+  int cur = 0;
+  int bits = 1;
+  while (bits < 32 && (1ll << bits) < (int64_t)std::max(n, 1)) ++bits;
+  for (int shift = 0; shift < bits && R > 0; shift += 4) {
+    k_gs_hist<<<nblocks, kGsThreads, 0, st>>>(k[cur], R, shift, nblocks, ghist);
+    rc = launch_scan_i32(ghist, 16ll * nblocks, blk, gbase, st);
+    if (rc) return rc;
+    k_gs_scatter<<<nblocks, kGsThreads, 0, st>>>(k[cur], v[cur], R, shift, nblocks, gbase, k[cur ^ 1], v[cur ^ 1]);
+    cur ^= 1;
+  }
+  const int64_t span = std::max<int64_t>(R, (int64_t)n + 1);
+  k_gs_finish<<<(unsigned)((span + 255) / 256), 256, 0, st>>>(v[cur], R, order, off32, n, offsets);
+  return cuda_check(cudaGetLastError(), "group_records");
+}
+
+extern "C" int mlpsp_prepare_groups(const int64_t* offsets, int32_t n, int64_t segment_size, int64_t* group_offsets,
+                                    int64_t* primitives, int64_t* starts, int64_t max_groups,
+                                    int64_t* num_groups_host, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  MLPSP_REQUIRE(offsets && group_offsets && n >= 0, MLPSP_E_ARG, "mlpsp_prepare_groups: null pointer");
+  MLPSP_REQUIRE(segment_size > 0, MLPSP_E_ARG, "segment_size must be a positive integer");
+  int32_t *cnt = nullptr, *goff = nullptr, *blk = nullptr;
+  const size_t bytes = 4 * ((size_t)n + 2);
+  MLPSP_CUDA_OK(cudaMallocAsync(&cnt, bytes, st));
+  MLPSP_CUDA_OK(cudaMallocAsync(&goff, bytes, st));
+  MLPSP_CUDA_OK(cudaMallocAsync(&blk, 4 * ((size_t)n / kScanItems + 4), st));
+  MLPSP_CUDA_OK(cudaMemsetAsync(goff, 0, bytes, st));
+  if (n > 0) k_groups_count<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, segment_size, cnt);
+  int rc = launch_scan_i32(cnt, n, blk, goff, st);
+  if (rc) return rc;
+  k_groups_fill<<<(n + 256) / 256, 256, 0, st>>>(offsets, n, segment_size, goff, group_offsets, primitives, starts, max_groups);
+  int32_t G = 0;
+  MLPSP_CUDA_OK(cudaMemcpyAsync(&G, goff + n, 4, cudaMemcpyDeviceToHost, st));
+  MLPSP_CUDA_OK(cudaStreamSynchronize(st));
+  if (num_groups_host) *num_groups_host = G;
+  cudaFreeAsync(cnt, st); cudaFreeAsync(goff, st); cudaFreeAsync(blk, st);
+  return cuda_check(cudaGetLastError(), "prepare_groups");
+}

@@ -1,0 +1,113 @@
+// Scalar FP32 per-primitive evaluator: positional encoding + 12F -> H -> H -> 4 MLP in the
+// operation order of the reference's scalar kernels (scannet/cuda/np_tile_kernels.cu:2047-2103):
+// layer 1 starts from the bias and accumulates (sin weight, cos weight) per (component, frequency);
+// layers 2 and 3 start from the bias and accumulate over ascending input index.
+// One CTA per work item (primitive, up to 128 of its records); the primitive's FP32 weights are
+// staged once in shared memory and every thread evaluates one record.
+#include "frame.cuh"
+
+namespace mlpsp {
+
+template <int HMAX>
+__global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32(
+    const float* __restrict__ W1, const float* __restrict__ b1, const float* __restrict__ W2,
+    const float* __restrict__ b2, const float* __restrict__ W3, const float* __restrict__ b3,
+    const float* __restrict__ freq, const float* __restrict__ att, int F, int H,
+    const RecIn* __restrict__ rec_in, const int32_t* __restrict__ prim_off, const int2* __restrict__ work,
+    int32_t* __restrict__ counters, float4* __restrict__ rec_out, int out_mode,
+    const int32_t* __restrict__ status) {
+  extern __shared__ float sW[];
+  __shared__ int s_item;
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int IN = 12 * F, half = 6 * F;
+  float* sW1 = sW;
+  float* sb1 = sW1 + H * IN;
+  float* sW2 = sb1 + H;
+  float* sb2 = sW2 + H * H;
+  float* sW3 = sb2 + H;
+  float* sb3 = sW3 + 4 * H;
+  float* sfa = sb3 + 4;  // freq[f]*att is NOT pre-multiplied: the product is v*freq*att left to right
+  const int tid = threadIdx.x;
+  const int G = counters[kCtrWork];
+  for (;;) {
+    if (tid == 0) s_item = atomicAdd(counters + kCtrWorkNext, 1);
+    __syncthreads();
+    const int item = s_item;
+    if (item >= G) break;
+    const int2 wk = work[item];
+    const int p = wk.x;
+    const int row = wk.y + tid;
+    const int cnt = prim_off[p + 1] - prim_off[p];
+    for (int i = tid; i < H * IN; i += kRowsPerItem) sW1[i] = W1[(size_t)p * H * IN + i];
+    for (int i = tid; i < H * H; i += kRowsPerItem) sW2[i] = W2[(size_t)p * H * H + i];
+    for (int i = tid; i < 4 * H; i += kRowsPerItem) sW3[i] = W3[(size_t)p * 4 * H + i];
+    for (int i = tid; i < H; i += kRowsPerItem) { sb1[i] = b1[(size_t)p * H + i]; sb2[i] = b2[(size_t)p * H + i]; }
+    if (tid < 4) sb3[tid] = b3[(size_t)p * 4 + tid];
+    if (tid < F) { sfa[tid] = freq[tid]; sfa[F + tid] = att[tid]; }
+    __syncthreads();
+    if (row < cnt) {
+      const RecIn r = rec_in[prim_off[p] + row];
+      const float v6[6] = {r.rdx, r.rdy, r.rdz, r.dx, r.dy, r.dz};
+      float h1[HMAX];
+#pragma unroll
+      for (int h = 0; h < HMAX; ++h) h1[h] = (h < H) ? sb1[h] : 0.f;
+      for (int c = 0; c < 6; ++c) {
+        for (int f = 0; f < F; ++f) {
+          const float ph = v6[c] * sfa[f] * sfa[F + f];
+          const float sn = __sinf(ph), cs = __cosf(ph);
+          const int j = c * F + f;
+#pragma unroll
+          for (int h = 0; h < HMAX; ++h) {
+            if (h < H) {
+              h1[h] = fmaf(sW1[h * IN + j], sn, h1[h]);
+              h1[h] = fmaf(sW1[h * IN + j + half], cs, h1[h]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < HMAX; ++h) h1[h] = fmaxf(h1[h], 0.f);
+      float o0 = sb3[0], o1 = sb3[1], o2 = sb3[2], o3 = sb3[3];
+      for (int q = 0; q < H; ++q) {
+        float a = sb2[q];
+#pragma unroll
+        for (int h = 0; h < HMAX; ++h) if (h < H) a = fmaf(sW2[q * H + h], h1[h], a);
+        a = fmaxf(a, 0.f);
+        // layer 3 accumulates over ascending hidden index, which is this loop's order
+        o0 = fmaf(sW3[0 * H + q], a, o0); o1 = fmaf(sW3[1 * H + q], a, o1);
+        o2 = fmaf(sW3[2 * H + q], a, o2); o3 = fmaf(sW3[3 * H + q], a, o3);
+      }
+      const float sigma_raw = softplus_fast(o3);
+      float4 out;
+      out.x = sigmoid_fast(o0); out.y = sigmoid_fast(o1); out.z = sigmoid_fast(o2);
+      out.w = (out_mode == kOutAlpha) ? (1.f - __expf(-(sigma_raw * r.decay))) : sigma_raw;
+      rec_out[r.slot] = out;
+    }
+    __syncthreads();
+  }
+}
+
+int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
+                   const int32_t* counters, float4* rec_out, int out_mode, int32_t* status, cudaStream_t st) {
+  const int H = sc->hidden, F = sc->num_freq;
+  MLPSP_REQUIRE(H >= 1 && H <= 64 && F >= 1 && F <= 8, MLPSP_E_LIMIT, "FP32 evaluator needs 1<=H<=64, 1<=F<=8");
+  MLPSP_REQUIRE(sc->W1 && sc->b1 && sc->W2 && sc->b2 && sc->W3 && sc->b3 && sc->freq && sc->att, MLPSP_E_ARG,
+                "FP32 evaluator needs the FP32 weight arrays");
+  const int IN = 12 * F;
+  const size_t smem = sizeof(float) * (size_t)(H * IN + H + H * H + H + 4 * H + 4 + 2 * F);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = sms * 8;
+  int32_t* ctr = const_cast<int32_t*>(counters);
+  if (H <= 32) {
+    k_mlp_f32<32><<<grid, kRowsPerItem, smem, st>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->freq, sc->att,
+                                                   F, H, rec_in, prim_off, work, ctr, rec_out, out_mode, status);
+  } else {
+    k_mlp_f32<64><<<grid, kRowsPerItem, smem, st>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->freq, sc->att,
+                                                   F, H, rec_in, prim_off, work, ctr, rec_out, out_mode, status);
+  }
+  return cuda_check(cudaGetLastError(), "mlp_f32");
+}
+
+}  // namespace mlpsp

@@ -1,0 +1,463 @@
+// Hit masks, primitive-major record construction (CSR), and front-to-back compositing.
+//
+// The reference walks a tile's sorted list serially and evaluates the MLP inside that walk
+// (scannet/cuda/np_tile_kernels.cu:2110-2117).  Here the walk is cut into waves of consecutive
+// list positions.  Per wave:
+//   k_hits       every still-active pixel is tested against the wave's candidates
+//                (hit_and_features_rot, np_tile_kernels.cu:659-711); one 64-bit mask per
+//                (tile, candidate) pair, record slots reserved tile-major
+//   prim scan    per-primitive record counts -> CSR offsets + evaluator work items
+//   k_fill       (pixel, primitive) records written primitive-major: the 6-vector fed to the
+//                encoder, decay, and the slot compositing will read
+//   evaluator    per-primitive MLP over its records (mlp_f32.cu / mlp_tc.cu)
+//   k_composite  per pixel, in list order, only while transmittance >= 1e-3
+//                (np_tile_kernels.cu:2025-2136); tiles with a live pixel and candidates left go
+//                on the next wave's list
+// A record evaluated in a wave but reached after its pixel terminated inside the same wave is
+// skipped by compositing, so results do not depend on the wave schedule.
+#include <algorithm>
+#include <climits>
+#include "frame.cuh"
+
+namespace mlpsp {
+
+constexpr int kWinMax = 2048;
+
+struct TilePix {
+  int pix; bool valid;
+};
+
+__device__ __forceinline__ TilePix tile_pixel(int tile, int k, int ntx, int W, int H) {
+  const int tx = tile % ntx, ty = tile / ntx;
+  const int x = tx * 8 + (k & 7), y = ty * 8 + (k >> 3);
+  TilePix r;
+  r.valid = (x < W) && (y < H);
+  r.pix = r.valid ? y * W + x : 0;
+  return r;
+}
+
+// -------------------------------------------------------------------------- frame init ----
+__global__ void k_init_pixels(int64_t P, float4* __restrict__ px_state, float2* __restrict__ px_depth,
+                              float* __restrict__ rgb, float* __restrict__ alpha, float* __restrict__ depth_t,
+                              float bgr, float bgg, float bgb) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  px_state[i] = make_float4(0.f, 0.f, 0.f, 1.f);
+  px_depth[i] = make_float2(0.f, 0.f);
+  rgb[i * 3] = bgr; rgb[i * 3 + 1] = bgg; rgb[i * 3 + 2] = bgb;
+  alpha[i] = 0.f;
+  if (depth_t) depth_t[i] = 0.f;
+}
+
+__global__ void k_init_tiles(int T, int32_t* __restrict__ active0, int32_t* __restrict__ counters) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < T) active0[t] = t;
+  if (t == 0) {
+    counters[kCtrRecords] = 0; counters[kCtrWork] = 0; counters[kCtrWorkNext] = 0;
+    counters[kCtrActive0] = T; counters[kCtrActive1] = 0;
+  }
+}
+
+// --------------------------------------------------------------------------- hit pass ----
+// 8 warps per tile: warp w owns pixel half (w & 1) and candidates (w >> 1) + 4j of the window.
+__global__ void __launch_bounds__(256) k_hits(
+    const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    float thr, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo, int hi,
+    const float4* __restrict__ px_state, uint32_t* __restrict__ masks32, uint32_t* __restrict__ pair_base,
+    int32_t* __restrict__ prim_cnt, int32_t* __restrict__ counters, int64_t max_records,
+    int32_t* __restrict__ status) {
+  __shared__ uint32_t s_m[2][kWinMax];
+  __shared__ int32_t s_pref[kWinMax];
+  __shared__ int warp_sums[32];
+  __shared__ int s_tile_base;
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  if ((int)blockIdx.x >= *active_count) return;
+  const int tile = active[blockIdx.x];
+  const int s = tile_offsets[tile];
+  const int len = tile_offsets[tile + 1] - s;
+  const int wlo = min(lo, len), whi = min(hi, len);
+  const int nwin = whi - wlo;
+  if (nwin <= 0) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int half = warp & 1;
+  const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
+  V3 o = {0.f, 0.f, 0.f}, d = {0.f, 0.f, 0.f};
+  bool act = false;
+  if (tp.valid) {
+    o = load3(rays_o, tp.pix); d = load3(rays_d, tp.pix);
+    act = px_state[tp.pix].w >= MLPSP_TERM;
+  }
+  for (int i = wlo + (warp >> 1); i < whi; i += 4) {
+    const int p = sorted_prims[s + i];
+    bool hit = false;
+    if (act && p >= 0 && p < n) {
+      Hit h;
+      hit = hit_test(load_geom(geom, p), o, d, thr, h);
+    }
+    const uint32_t m = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) s_m[half][i - wlo] = m;
+  }
+  __syncthreads();
+  int running = 0;
+  for (int j0 = 0; j0 < nwin; j0 += 256) {
+    const int j = j0 + tid;
+    const int c = (j < nwin) ? __popc(s_m[0][j]) + __popc(s_m[1][j]) : 0;
+    int total;
+    const int ex = block_exclusive_scan(c, warp_sums, total);
+    if (j < nwin) s_pref[j] = running + ex;
+    running += total;
+  }
+  if (tid == 0) {
+    const int base = running > 0 ? atomicAdd(counters + kCtrRecords, running) : 0;
+    s_tile_base = base;
+    if ((int64_t)base + running > max_records) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_RECORD_OVERFLOW);
+  }
+  __syncthreads();
+  const int base = s_tile_base;
+  for (int j = tid; j < nwin; j += 256) {
+    const uint32_t m0 = s_m[0][j], m1 = s_m[1][j];
+    masks32[2 * (size_t)(s + wlo + j)] = m0;
+    masks32[2 * (size_t)(s + wlo + j) + 1] = m1;
+    pair_base[s + wlo + j] = (uint32_t)(base + s_pref[j]);
+    const int c = __popc(m0) + __popc(m1);
+    if (c > 0) atomicAdd(prim_cnt + sorted_prims[s + wlo + j], c);
+  }
+}
+
+// Geometric hit masks of all pairs (no transmittance state): the superset the waves draw from.
+__global__ void __launch_bounds__(256) k_hit_masks_all(
+    const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    float thr, uint32_t* __restrict__ masks32, const int32_t* __restrict__ status) {
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int tile = blockIdx.x;
+  const int s = tile_offsets[tile];
+  const int len = tile_offsets[tile + 1] - s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, half = warp & 1;
+  const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
+  V3 o = {0.f, 0.f, 0.f}, d = {0.f, 0.f, 0.f};
+  if (tp.valid) { o = load3(rays_o, tp.pix); d = load3(rays_d, tp.pix); }
+  for (int i = (warp >> 1); i < len; i += 4) {
+    const int p = sorted_prims[s + i];
+    bool hit = false;
+    if (tp.valid && p >= 0 && p < n) {
+      Hit h;
+      hit = hit_test(load_geom(geom, p), o, d, thr, h);
+    }
+    const uint32_t m = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) masks32[2 * (size_t)(s + i) + half] = m;
+  }
+}
+
+// ------------------------------------------------------- per-primitive scan + work items ----
+__device__ __forceinline__ int items_of(int cnt) { return (cnt + kRowsPerItem - 1) / kRowsPerItem; }
+
+__global__ void k_prim_partial(const int32_t* __restrict__ prim_cnt, int n, int32_t* __restrict__ blk,
+                               const int32_t* __restrict__ status) {
+  __shared__ int warp_sums[32];
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
+  int a = 0, b = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (base + j < n) { const int c = prim_cnt[base + j]; a += c; b += items_of(c); }
+  int ta, tb;
+  block_exclusive_scan(a, warp_sums, ta);
+  block_exclusive_scan(b, warp_sums, tb);
+  if (threadIdx.x == 0) { blk[2 * blockIdx.x] = ta; blk[2 * blockIdx.x + 1] = tb; }
+}
+
+__global__ void k_prim_top(int32_t* __restrict__ blk, int nblk, int32_t* __restrict__ counters, int next_list,
+                           int64_t max_work, int32_t* __restrict__ status) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry_a, carry_b;
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) {
+    // after a record overflow, leave the size the wave asked for so the caller can grow its scratch
+    if (threadIdx.x == 0 && (status[MLPSP_ST_BITS] & MLPSP_ST_RECORD_OVERFLOW))
+      atomicMax(status + MLPSP_ST_WAVE_RECORDS, counters[kCtrRecords]);
+    return;
+  }
+  if (threadIdx.x == 0) { carry_a = 0; carry_b = 0; }
+  __syncthreads();
+  for (int b0 = 0; b0 < nblk; b0 += 1024) {
+    const int i = b0 + threadIdx.x;
+    const int va = (i < nblk) ? blk[2 * i] : 0, vb = (i < nblk) ? blk[2 * i + 1] : 0;
+    int ta, tb;
+    const int ea = block_exclusive_scan(va, warp_sums, ta);
+    const int eb = block_exclusive_scan(vb, warp_sums, tb);
+    const int ca = carry_a, cb = carry_b;
+    if (i < nblk) { blk[2 * i] = ca + ea; blk[2 * i + 1] = cb + eb; }
+    __syncthreads();
+    if (threadIdx.x == 0) { carry_a = ca + ta; carry_b = cb + tb; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const int R = carry_a;
+    int G = carry_b;
+    if ((int64_t)G > max_work) { G = (int)max_work; atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_RECORD_OVERFLOW); }
+    blk[2 * nblk] = R;
+    counters[kCtrWork] = G;
+    counters[kCtrWorkNext] = 0;
+    counters[kCtrRecords] = 0;
+    counters[kCtrActive0 + next_list] = 0;
+    if (R > 0) {
+      atomicAdd((unsigned long long*)(status + MLPSP_ST_RECORDS_LO), (unsigned long long)R);
+      atomicMax(status + MLPSP_ST_WAVE_RECORDS, R);
+      atomicMax(status + MLPSP_ST_WORK_ITEMS, G);
+      atomicAdd(status + MLPSP_ST_WAVES, 1);
+    }
+  }
+}
+
+__global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict__ prim_cursor, int n,
+                             const int32_t* __restrict__ blk, int32_t* __restrict__ prim_off,
+                             int2* __restrict__ work, int64_t max_work, const int32_t* __restrict__ status) {
+  __shared__ int warp_sums[32];
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
+  int c[4], a = 0, b = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    c[j] = (base + j < n) ? prim_cnt[base + j] : 0;
+    a += c[j]; b += items_of(c[j]);
+  }
+  int ta, tb;
+  int ea = block_exclusive_scan(a, warp_sums, ta) + blk[2 * blockIdx.x];
+  int eb = block_exclusive_scan(b, warp_sums, tb) + blk[2 * blockIdx.x + 1];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (base + j < n) {
+      prim_off[base + j] = ea;
+      const int it = items_of(c[j]);
+      for (int q = 0; q < it; ++q)
+        if ((int64_t)eb + q < max_work) work[eb + q] = make_int2((int)(base + j), q * kRowsPerItem);
+      ea += c[j]; eb += it;
+      prim_cnt[base + j] = 0;
+      prim_cursor[base + j] = 0;
+    }
+  }
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) prim_off[n] = blk[2 * gridDim.x];
+}
+
+int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st) {
+  const int nblk = (n + kScanItems - 1) / kScanItems;
+  if (nblk == 0) return MLPSP_OK;
+  k_prim_partial<<<nblk, 1024, 0, st>>>(s.prim_cnt, n, s.scan_blk, status);
+  k_prim_top<<<1, 1024, 0, st>>>(s.scan_blk, nblk, s.counters, next_list, s.max_work, status);
+  k_prim_final<<<nblk, 1024, 0, st>>>(s.prim_cnt, s.prim_cursor, n, s.scan_blk, s.prim_off, s.work, s.max_work, status);
+  return cuda_check(cudaGetLastError(), "prim_scan");
+}
+
+// -------------------------------------------------------------------------- fill pass ----
+// Feature gates (semantic_tetra_gates, np_tile_kernels.cu:97-124).
+__device__ __forceinline__ float4 tetra_gates(const Hit& h, float lsx, float lsy, float lsz, float beta, float tau) {
+  const float sx = det_exp(lsx), sy = det_exp(lsy), sz = det_exp(lsz);
+  const float ux = fminf(1.f, fmaxf(-1.f, h.qx / (beta * sx + 1e-6f)));
+  const float uy = fminf(1.f, fmaxf(-1.f, h.qy / (beta * sy + 1e-6f)));
+  const float uz = fminf(1.f, fmaxf(-1.f, h.qz / (beta * sz + 1e-6f)));
+  const float l0 = tau * (ux + uy + uz), l1 = tau * (ux - uy - uz);
+  const float l2 = tau * (-ux + uy - uz), l3 = tau * (-ux - uy + uz);
+  const float lm = fmaxf(fmaxf(l0, l1), fmaxf(l2, l3));
+  const float e0 = __expf(l0 - lm), e1 = __expf(l1 - lm), e2 = __expf(l2 - lm), e3 = __expf(l3 - lm);
+  const float inv = 1.f / fmaxf(e0 + e1 + e2 + e3, 1e-8f);
+  return make_float4(e0 * inv, e1 * inv, e2 * inv, e3 * inv);
+}
+
+// One warp per pair; lane l owns pixels l and l+32 of the tile.
+__global__ void __launch_bounds__(256) k_fill(
+    const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    float thr, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo, int hi,
+    const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base,
+    const int32_t* __restrict__ prim_off, int32_t* __restrict__ prim_cursor, RecIn* __restrict__ rec_in,
+    float* __restrict__ rec_t, float4* __restrict__ rec_gate, float beta, float tau,
+    const int32_t* __restrict__ status) {
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  if ((int)blockIdx.x >= *active_count) return;
+  const int tile = active[blockIdx.x];
+  const int s = tile_offsets[tile];
+  const int len = tile_offsets[tile + 1] - s;
+  const int wlo = min(lo, len), whi = min(hi, len);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  TilePix tp[2];
+  V3 o[2], d[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    tp[h] = tile_pixel(tile, h * 32 + lane, ntx, W, H);
+    o[h] = d[h] = V3{0.f, 0.f, 0.f};
+    if (tp[h].valid) { o[h] = load3(rays_o, tp[h].pix); d[h] = load3(rays_d, tp[h].pix); }
+  }
+  const uint32_t lt = (1u << lane) - 1u;
+  for (int i = wlo + warp; i < whi; i += 8) {
+    const uint32_t m0 = masks32[2 * (size_t)(s + i)], m1 = masks32[2 * (size_t)(s + i) + 1];
+    const int c0 = __popc(m0), c = c0 + __popc(m1);
+    if (c == 0) continue;
+    const int p = sorted_prims[s + i];
+    int q0 = 0;
+    if (lane == 0) q0 = prim_off[p] + atomicAdd(prim_cursor + p, c);
+    q0 = __shfl_sync(0xffffffffu, q0, 0);
+    const uint32_t slot0 = pair_base[s + i];
+    const Geom g = load_geom(geom, p);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t m = h ? m1 : m0;
+      if (!((m >> lane) & 1u)) continue;
+      const int rank = (h ? c0 : 0) + __popc(m & lt);
+      Hit ht;
+      hit_test(g, o[h], d[h], thr, ht);
+      RecIn r;
+      r.rdx = d[h].x; r.rdy = d[h].y; r.rdz = d[h].z; r.dx = ht.dx; r.dy = ht.dy; r.dz = ht.dz;
+      r.decay = ht.decay; r.slot = slot0 + rank;
+      rec_in[q0 + rank] = r;
+      if (rec_t) rec_t[slot0 + rank] = ht.t;
+      if (rec_gate) {
+        const float4 ls = __ldg(geom + (size_t)p * 4 + 3);
+        rec_gate[slot0 + rank] = tetra_gates(ht, ls.x, ls.y, ls.z, beta, tau);
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------- composite ----
+// 64 threads per tile; each warp owns 32 pixels and stops as soon as none of them is live.
+__global__ void __launch_bounds__(64) k_composite(
+    const int32_t* __restrict__ tile_offsets, int W, int H, int ntx, const int32_t* __restrict__ active,
+    const int32_t* __restrict__ active_count, int lo, int hi, const uint32_t* __restrict__ masks32,
+    const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out, const float* __restrict__ rec_t,
+    float4* __restrict__ px_state, float2* __restrict__ px_depth, float* __restrict__ rgb,
+    float* __restrict__ alpha, float* __restrict__ depth_t, uint32_t* __restrict__ mask_used32,
+    float bgr, float bgg, float bgb, int has_bg, int32_t* __restrict__ next_active,
+    int32_t* __restrict__ next_count, int32_t* __restrict__ status) {
+  __shared__ int s_live[2];
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  if ((int)blockIdx.x >= *active_count) return;
+  const int tile = active[blockIdx.x];
+  const int s = tile_offsets[tile];
+  const int len = tile_offsets[tile + 1] - s;
+  const int wlo = min(lo, len), whi = min(hi, len);
+  const int lane = threadIdx.x & 31, half = threadIdx.x >> 5;
+  const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
+  float4 st = make_float4(0.f, 0.f, 0.f, 0.f);
+  float2 dp = make_float2(0.f, 0.f);
+  if (tp.valid) { st = px_state[tp.pix]; if (depth_t) dp = px_depth[tp.pix]; }
+  bool act = tp.valid && st.w >= MLPSP_TERM;
+  const uint32_t lt = (1u << lane) - 1u;
+  int used = 0;
+  for (int i0 = wlo; i0 < whi && __any_sync(0xffffffffu, act); i0 += 32) {
+    const int idx = i0 + lane;
+    uint2 mm = make_uint2(0u, 0u);
+    uint32_t bb = 0;
+    if (idx < whi) {
+      mm = *reinterpret_cast<const uint2*>(masks32 + 2 * (size_t)(s + idx));
+      bb = pair_base[s + idx];
+    }
+    const int cnt = min(32, whi - i0);
+    for (int j = 0; j < cnt; ++j) {
+      const uint32_t m0 = __shfl_sync(0xffffffffu, mm.x, j), m1 = __shfl_sync(0xffffffffu, mm.y, j);
+      const uint32_t mine = half ? m1 : m0;
+      if (mine == 0u) continue;
+      const uint32_t b = __shfl_sync(0xffffffffu, bb, j);
+      const bool take = act && ((mine >> lane) & 1u);
+      if (take) {
+        const uint32_t slot = b + (half ? __popc(m0) : 0) + __popc(mine & lt);
+        const float4 r = rec_out[slot];
+        const float w = st.w * r.w;
+        st.x = fmaf(w, r.x, st.x); st.y = fmaf(w, r.y, st.y); st.z = fmaf(w, r.z, st.z);
+        if (depth_t) { dp.x = fmaf(w, rec_t[slot], dp.x); dp.y += w; }
+        st.w *= (1.f - r.w);
+        act = st.w >= MLPSP_TERM;
+      }
+      const uint32_t um = __ballot_sync(0xffffffffu, take);
+      if (um) {
+        if (lane == 0) { used += __popc(um); if (mask_used32) mask_used32[2 * (size_t)(s + i0 + j) + half] = um; }
+        if (!__any_sync(0xffffffffu, act)) break;
+      }
+    }
+  }
+  if (tp.valid) {
+    px_state[tp.pix] = st;
+    const float a = 1.f - st.w;
+    float r = st.x, g = st.y, b = st.z;
+    if (has_bg) {
+      const float k = fminf(fmaxf(1.f - a, 0.f), 1.f);
+      r += k * bgr; g += k * bgg; b += k * bgb;
+    }
+    rgb[(size_t)tp.pix * 3] = r; rgb[(size_t)tp.pix * 3 + 1] = g; rgb[(size_t)tp.pix * 3 + 2] = b;
+    alpha[tp.pix] = a;
+    if (depth_t) { px_depth[tp.pix] = dp; depth_t[tp.pix] = dp.x / ((dp.y > 1e-8f) ? dp.y : 1.f); }
+  }
+  const bool live = __any_sync(0xffffffffu, act);
+  if (lane == 0) {
+    s_live[half] = live;
+    if (used) atomicAdd((unsigned long long*)(status + MLPSP_ST_USED_LO), (unsigned long long)used);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && (s_live[0] | s_live[1]) && whi < len) next_active[atomicAdd(next_count, 1)] = tile;
+}
+
+// ------------------------------------------------------------------------------ driver ----
+static const int kDefaultWaves[] = {32, 32, 64, 128, 256, 512, INT_MAX};
+
+int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st) {
+  const int T = num_tiles(fr->width, fr->height, fr->tile);
+  const int ntx = (fr->width + 7) / 8;
+  k_hit_masks_all<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, sc->n, fr->tile_offsets,
+                                     fr->sorted_prims, fr->width, fr->height, ntx, fr->threshold,
+                                     (uint32_t*)mask_geo, fr->status);
+  return cuda_check(cudaGetLastError(), "hit_masks");
+}
+
+int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st) {
+  const int W = fr->width, H = fr->height;
+  const int T = num_tiles(W, H, 8);
+  const int ntx = (W + 7) / 8;
+  const int64_t P = (int64_t)W * H;
+  const int n = sc->n;
+  float bg[3] = {0.f, 0.f, 0.f};
+  const int has_bg = fr->bg_color != nullptr;
+  if (has_bg) { bg[0] = fr->bg_color[0]; bg[1] = fr->bg_color[1]; bg[2] = fr->bg_color[2]; }
+  const bool want_t = fr->depth_t != nullptr;
+  const bool want_feat = fr->feat != nullptr;
+  MLPSP_REQUIRE(!want_feat, MLPSP_E_ARG, "feature compositing is not available in this build");
+  k_init_pixels<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha,
+                                                             fr->depth_t, bg[0], bg[1], bg[2]);
+  k_init_tiles<<<(T + 255) / 256, 256, 0, st>>>(T, s.active[0], s.counters);
+  if (fr->mask_used) MLPSP_CUDA_OK(cudaMemsetAsync(fr->mask_used, 0, 8 * (size_t)fr->max_pairs, st));
+  if (n == 0) return cuda_check(cudaGetLastError(), "render_sorted");
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cnt, 0, 4 * (size_t)n, st));
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cursor, 0, 4 * (size_t)n, st));
+  const int nw = fr->num_waves > 0 ? fr->num_waves : (int)(sizeof(kDefaultWaves) / sizeof(int));
+  int lo = 0;
+  for (int w = 0; w < nw && lo < fr->tile_capacity; ++w) {
+    const int wl = fr->num_waves > 0 ? fr->wave_len[w] : kDefaultWaves[w];
+    MLPSP_REQUIRE(wl > 0, MLPSP_E_ARG, "wave_len[%d] must be positive", w);
+    int hi = (wl >= fr->tile_capacity - lo || w == nw - 1) ? fr->tile_capacity : lo + wl;
+    MLPSP_REQUIRE(hi - lo <= kWinMax, MLPSP_E_LIMIT, "wave window beyond %d candidates", kWinMax);
+    const int cur = w & 1, nxt = cur ^ 1;
+    const int32_t* act = s.active[cur];
+    const int32_t* act_n = s.counters + kCtrActive0 + cur;
+    k_hits<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, fr->sorted_prims,
+                              W, H, ntx, fr->threshold, act, act_n, lo, hi, s.px_state, s.masks32, s.pair_base,
+                              s.prim_cnt, s.counters, fr->max_records, fr->status);
+    int rc = launch_prim_scan(s, n, nxt, fr->status, st);
+    if (rc) return rc;
+    k_fill<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
+                              W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
+                              s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr, nullptr, sc->gate_beta,
+                              sc->gate_tau, fr->status);
+    if (fr->precision == MLPSP_PRECISION_F16)
+      rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, kOutAlpha, fr->status, st);
+    else
+      rc = launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, kOutAlpha, fr->status, st);
+    if (rc) return rc;
+    k_composite<<<T, 64, 0, st>>>(fr->tile_offsets, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+                                  s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
+                                  fr->alpha, fr->depth_t, (uint32_t*)fr->mask_used, bg[0], bg[1], bg[2], has_bg,
+                                  s.active[nxt], s.counters + kCtrActive0 + nxt, fr->status);
+    lo = hi;
+  }
+  return cuda_check(cudaGetLastError(), "render_sorted");
+}
+
+}  // namespace mlpsp

@@ -1,0 +1,270 @@
+"""Drop-in renderer module for the inference path of scannet/cumodel.py.
+
+`NeuralPrimitiveSceneTileCUDA` keeps the reference class's constructor arguments, parameter
+names and shapes (cumodel.py:655-743), `set_image_size`, `forward` (cumodel.py:951-1160) and the
+no-grad helpers `render_feature_map`, `render_rgb_alpha_no_grad`, `render_rgb_t_no_grad`
+(cumodel.py:1162-1525).  Rendering runs on the sm_100a kernels behind libmlpsp_b200.so; there is
+no autograd (training is out of scope) and no CPU path.
+
+Differences a caller can see:
+  * tile_size must be 8 (the reference also accepts 16 for its scalar kernels);
+  * `precision` ("fp16" default, or "fp32") selects the evaluator: fp16 matches the reference's
+    tensor-core forward (scannet/cuda/rgb_wmma.cuh), fp32 its scalar forward;
+  * culling, sorting and rendering are one asynchronous launch sequence followed by one status
+    read-back, where the reference synchronises on `tile_prim_pairs.numel()` (cumodel.py:1055) and
+    again inside its validator (np_tile_kernels.cu:4576).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+from torch import nn
+
+from . import _lib as L
+from .engine import TILE_CAPACITY, FrameRenderer, PackedScene
+
+
+class IntegratedPositionalEncoding(nn.Module):
+    """Frequencies 2^k * pi and attenuation exp(-0.5 f^2 sigma^2) (cumodel.py:132-155)."""
+
+    def __init__(self, in_dim=6, num_frequencies=10, sigma=0.01):
+        super().__init__()
+        self.in_dim, self.num_frequencies, self.sigma2 = in_dim, num_frequencies, sigma ** 2
+        self.register_buffer("freq_bands", 2.0 ** torch.linspace(0.0, num_frequencies - 1, num_frequencies) * torch.pi)
+        self.register_buffer("runtime_frequency_weights", torch.ones(num_frequencies), persistent=False)
+
+    def set_runtime_frequency_weights(self, weights):
+        with torch.no_grad():
+            self.runtime_frequency_weights.copy_(weights.to(self.runtime_frequency_weights))
+
+    def attenuation(self):
+        return torch.exp(-0.5 * (self.freq_bands ** 2) * self.sigma2) * self.runtime_frequency_weights
+
+    @property
+    def out_dim(self):
+        return self.in_dim * self.num_frequencies * 2
+
+
+class FourierFeatureEncoding(nn.Module):
+    """Frequencies 2^k, unit attenuation (cumodel.py:158-180)."""
+
+    def __init__(self, in_dim=6, num_frequencies=10):
+        super().__init__()
+        self.in_dim, self.num_frequencies = in_dim, num_frequencies
+        self.register_buffer("freq_bands", 2.0 ** torch.linspace(0.0, num_frequencies - 1, num_frequencies))
+        self.register_buffer("runtime_frequency_weights", torch.ones(num_frequencies), persistent=False)
+
+    def set_runtime_frequency_weights(self, weights):
+        with torch.no_grad():
+            self.runtime_frequency_weights.copy_(weights.to(self.runtime_frequency_weights))
+
+    def attenuation(self):
+        return self.runtime_frequency_weights.clone()
+
+    @property
+    def out_dim(self):
+        return self.in_dim * self.num_frequencies * 2
+
+
+class NeuralPrimitiveSceneTileCUDA(nn.Module):
+    """Tile-based MLP splatting renderer (inference), same call surface as the reference class."""
+
+    requires_full_image = True
+
+    def __init__(self, num_primitives=1024, hidden_dim=32, pe_frequencies=6, initial_positions=None,
+                 use_integrated_pe=True, pe_sigma: float = 0.01, min_points: int = 10, tile_size: int = 8,
+                 feature_dim_low: int = 0, feature_slots: int = 4, feature_gating_beta: float = 1.5,
+                 feature_gating_temp: float = 2.0, precision: str = "fp16"):
+        super().__init__()
+        if int(hidden_dim) > 32:
+            raise ValueError("NeuralPrimitiveSceneTileCUDA currently supports hidden_dim <= 32 "
+                             "(kernel scratch-cap tuning in backward/full path).")
+        if float(pe_sigma) <= 0.0:
+            raise ValueError("pe_sigma must be > 0.")
+        if int(tile_size) <= 0:
+            raise ValueError("tile_size must be a positive integer.")
+        if int(tile_size) not in (8, 16):
+            raise ValueError("NeuralPrimitiveSceneTileCUDA supports tile_size in {8, 16}.")
+        if int(tile_size) != 8:
+            raise ValueError("this build renders 8x8 tiles only")
+        if initial_positions is not None:
+            raise ValueError("octree initialisation from a point cloud belongs to training and is not part of this build")
+        if precision not in ("fp16", "fp32"):
+            raise ValueError("precision must be 'fp16' or 'fp32'")
+        self.num_primitives = int(num_primitives)
+        self.hidden_dim, self.pe_frequencies = int(hidden_dim), int(pe_frequencies)
+        self.use_integrated_pe, self.pe_sigma = bool(use_integrated_pe), float(pe_sigma)
+        self.image_size = None
+        self.tile_size = int(tile_size)
+        self.tile_order_mode_override = None
+        self.feature_dim_low = int(max(0, feature_dim_low))
+        self.feature_slots = int(max(1, feature_slots))
+        self.feature_gating_beta, self.feature_gating_temp = float(feature_gating_beta), float(feature_gating_temp)
+        if self.feature_dim_low > 0 and self.feature_slots not in (4, 5):
+            raise ValueError("feature_slots must be 4 (canonical) or 5 (legacy) when features are enabled.")
+        if self.feature_gating_beta <= 0.0:
+            raise ValueError("feature_gating_beta must be > 0.")
+        if self.feature_gating_temp <= 0.0:
+            raise ValueError("feature_gating_temp must be > 0.")
+        self.precision = precision
+        n, H = self.num_primitives, self.hidden_dim
+        self.positions = nn.Parameter(torch.rand(n, 3) * 2 - 1)
+        self.log_scales = nn.Parameter(torch.log(torch.ones(n) * 0.1).unsqueeze(-1).repeat(1, 3))
+        self.quats = nn.Parameter(torch.tensor([1.0, 0.0, 0.0, 0.0]).view(1, 4).repeat(n, 1))
+        self.encoder = (IntegratedPositionalEncoding(6, pe_frequencies, self.pe_sigma) if self.use_integrated_pe
+                        else FourierFeatureEncoding(6, pe_frequencies))
+        IN = self.encoder.out_dim
+        self.W1 = nn.Parameter(torch.randn(n, H, IN) * 0.01)
+        self.b1 = nn.Parameter(torch.zeros(n, H))
+        self.W2 = nn.Parameter(torch.randn(n, H, H) * 0.01)
+        self.b2 = nn.Parameter(torch.zeros(n, H))
+        self.W3 = nn.Parameter(torch.randn(n, 4, H) * 0.01)
+        self.b3 = nn.Parameter(torch.zeros(n, 4))
+        if self.feature_dim_low > 0:
+            if self.feature_slots == 5:
+                fi = torch.zeros(n, 5, self.feature_dim_low)
+                fi[:, 0, :].normal_(mean=0.0, std=0.01)
+            else:
+                fi = torch.randn(n, self.feature_slots, self.feature_dim_low) * 0.01
+            self.feat_attr = nn.Parameter(fi)
+        else:
+            self.feat_attr = None
+        self._packed = None
+        self._packed_key = None
+        self._renderers = {}
+
+    # ------------------------------------------------------------------ reference surface ----
+    def set_image_size(self, W: int, H: int):
+        self.image_size = (int(W), int(H))
+
+    def _activate_cuda_device(self) -> torch.device:
+        device = self.positions.device
+        if device.type != "cuda":
+            raise RuntimeError("NeuralPrimitiveSceneTileCUDA must be moved to a CUDA device before rendering.")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        torch.cuda.set_device(device.index)
+        return device
+
+    def _resolve_tile_order_mode(self) -> str:
+        mode = self.tile_order_mode_override
+        if mode is None or str(mode).strip() == "":
+            mode = os.environ.get("MLPSP_TILE_ORDER", "tilecenter")
+        mode = {"tile_center": "tilecenter", "tile-center": "tilecenter"}.get(str(mode).strip().lower(),
+                                                                              str(mode).strip().lower())
+        if mode not in {"tilecenter", "per_pixel"}:
+            raise ValueError(f"Unknown tile order mode: {mode}")
+        if mode != "tilecenter":
+            raise ValueError("only the tile-centre order is built; per_pixel ordering is not part of this path")
+        return mode
+
+    # --------------------------------------------------------------------------- internals ----
+    def _params(self):
+        ps = [self.positions, self.log_scales, self.quats, self.W1, self.b1, self.W2, self.b2, self.W3, self.b3]
+        if self.feat_attr is not None:
+            ps.append(self.feat_attr)
+        return ps
+
+    def packed_scene(self) -> PackedScene:
+        """Packed parameters on the module's device, rebuilt when a parameter changed in place."""
+        device = self._activate_cuda_device()
+        w = self.encoder.runtime_frequency_weights
+        key = (str(device), self.precision) + tuple((p.data_ptr(), p._version) for p in self._params()) + \
+              (w.data_ptr(), w._version)
+        if self._packed is None or self._packed_key != key:
+            with torch.no_grad():
+                freq = self.encoder.freq_bands.to(device=device, dtype=torch.float32)
+                att = self.encoder.attenuation().to(device=device, dtype=torch.float32)
+                self._packed = PackedScene(
+                    self.positions.detach(), self.log_scales.detach(), self.quats.detach(), self.W1.detach(),
+                    self.b1.detach(), self.W2.detach(), self.b2.detach(), self.W3.detach(), self.b3.detach(), freq, att,
+                    feat_attr=None if self.feat_attr is None else self.feat_attr.detach(),
+                    gate_beta=self.feature_gating_beta, gate_tau=self.feature_gating_temp, device=device,
+                    pack_f16=(self.precision == "fp16"))
+            self._packed_key = key
+        return self._packed
+
+    def _renderer(self, device) -> FrameRenderer:
+        W, H = self.image_size
+        key = (str(device), W, H)
+        if key not in self._renderers:
+            self._renderers[key] = FrameRenderer(W, H, device=device, tile_capacity=TILE_CAPACITY)
+        return self._renderers[key]
+
+    def _render(self, ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix, culled_prim_indices,
+                tile_offsets, want_depth, path_name):
+        if self.image_size is None:
+            raise ValueError("image_size must be set on NeuralPrimitiveSceneTileCUDA before calling forward.")
+        W, H = self.image_size
+        if ray_o.shape[0] != W * H:
+            raise AssertionError("Tile renderer requires full-frame rays (B == W*H)")
+        device = self._activate_cuda_device()
+        self._resolve_tile_order_mode()
+        if getattr(self, "camera_mode", "legacy-centered") == "colmap-native":
+            raise ValueError("ray-cone culling for native COLMAP cameras is not part of this build")
+        T = ((W + 7) // 8) * ((H + 7) // 8)
+        lists = None
+        if (culled_prim_indices is not None) or (tile_offsets is not None):
+            if culled_prim_indices is None or tile_offsets is None:
+                raise ValueError("Both culled_prim_indices and tile_offsets must be provided together.")
+            cp = culled_prim_indices.to(device=device, dtype=torch.int32).contiguous()
+            to = tile_offsets.to(device=device, dtype=torch.int32).contiguous()
+            if to.numel() != T + 1:
+                raise ValueError(f"tile_offsets length mismatch: got {to.numel()}, expected {T + 1}")
+            lists = (cp, to)
+        elif view_matrix is None or proj_matrix is None:
+            raise ValueError("Tile renderer requires view_matrix/proj_matrix unless external culling is provided.")
+        scene = self.packed_scene()
+        r = self._renderer(device)
+        bg = None
+        if bg_color is not None:
+            bg = torch.as_tensor(bg_color, dtype=torch.float32).detach().cpu().reshape(-1)
+            bg = bg.repeat(3) if bg.numel() == 1 else bg
+            bg = bg.numpy()
+        view = None if lists is not None else view_matrix.detach().float().cpu().numpy()
+        proj = None if lists is not None else proj_matrix.detach().float().cpu().numpy()
+        prec = L.PRECISION_F16 if (self.precision == "fp16" and scene.has_f16) else L.PRECISION_F32
+        rgb, alpha = r.render(scene, ray_o.detach().float().contiguous(), ray_d.detach().float().contiguous(),
+                              float(score_threshold), view=view, proj=proj, precision=prec, bg=bg,
+                              want_depth=want_depth, tile_lists=lists, path_name=path_name)
+        return r, rgb, alpha
+
+    # ----------------------------------------------------------------------------- public ----
+    @torch.no_grad()
+    def forward(self, ray_o, ray_d, score_threshold=1e-3, bg_color=None, view_matrix=None, proj_matrix=None,
+                culled_prim_indices=None, tile_offsets=None, return_feature: bool = False, feature_target=None):
+        """Same arguments as the reference forward (cumodel.py:951-963); returns rgb [W*H,3]
+        (a fresh tensor), or (rgb, feat) when return_feature is set and features exist."""
+        if feature_target is not None:
+            raise ValueError("CSR feature training is outside the inference render path")
+        if return_feature and self.feat_attr is None:
+            raise RuntimeError("return_feature=True requested but feat_attr is not initialized.")
+        if return_feature:
+            raise RuntimeError("the fused feature map is not available in this build yet")
+        _r, rgb, _alpha = self._render(ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix,
+                                       culled_prim_indices, tile_offsets, False, "render_tiles_forward_tilecenter")
+        return rgb.clone()
+
+    @torch.no_grad()
+    def render_rgb_alpha_no_grad(self, ray_o, ray_d, score_threshold=1e-3, bg_color=None, view_matrix=None,
+                                 proj_matrix=None, culled_prim_indices=None, tile_offsets=None):
+        """(rgb [B,3], alpha [B,1]) as cumodel.py:1196-1383 (pruning statistics are not built)."""
+        _r, rgb, alpha = self._render(ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix,
+                                      culled_prim_indices, tile_offsets, False, "render_tiles_forward_tilecenter")
+        return rgb.clone(), alpha.clone()
+
+    @torch.no_grad()
+    def render_rgb_t_no_grad(self, ray_o, ray_d, score_threshold=1e-3, bg_color=None, view_matrix=None,
+                             proj_matrix=None, culled_prim_indices=None, tile_offsets=None):
+        """(rgb, expected depth t [B,1], alpha) as cumodel.py:1385-1525."""
+        r, rgb, alpha = self._render(ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix,
+                                     culled_prim_indices, tile_offsets, True, "render_tiles_forward_tilecenter_with_t")
+        return rgb.clone(), r.depth_t.clone(), alpha.clone()
+
+    @torch.no_grad()
+    def render_feature_map(self, ray_o, ray_d, score_threshold=1e-3, view_matrix=None, proj_matrix=None,
+                           culled_prim_indices=None, tile_offsets=None):
+        if self.feat_attr is None:
+            raise RuntimeError("Feature rendering requested but feature_dim_low == 0.")
+        raise RuntimeError("the fused feature map is not available in this build yet")

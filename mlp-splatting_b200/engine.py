@@ -1,0 +1,320 @@
+"""Host side of the render path: device-resident packed scenes, per-frame scratch, status handling.
+
+PyTorch is used for device memory, streams and the host<->device copies; every computation goes
+through the C ABI of libmlpsp_b200.so (see _lib.py).  Error texts follow the reference's
+TORCH_CHECK messages (scannet/cuda/np_tile_kernels.cu:4578-4588) so callers' tests can match them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib as L
+
+TILE = 8
+TILE_CAPACITY = 1536  # MLPSP_TILE_CANDIDATE_CAPACITY default of the reference loader (cumodel.py:102-104)
+
+
+def _stream_ptr(device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _dev_f32(x, device):
+    t = torch.as_tensor(x)
+    return t.to(device=device, dtype=torch.float32).contiguous()
+
+
+def normalize_rows(x: torch.Tensor) -> torch.Tensor:
+    """x / max(|x|, 1e-12) per row (rows of 3 or 4 floats) on the tensor's CUDA device."""
+    lib = L.load()
+    x = x.contiguous().float()
+    out = torch.empty_like(x)
+    L.check(lib.mlpsp_normalize_rows(L.ptr(x), L.ptr(out), x.shape[0], x.shape[1], _stream_ptr(x.device)),
+            "mlpsp_normalize_rows")
+    return out
+
+
+class PackedScene:
+    """Scene parameters resident on one GPU in the layouts the kernels read.
+
+    Takes the reference's parameter tensors (cumodel.py:724-743): positions[n,3], log_scales[n,3],
+    quats[n,4] (any norm), W1[n,H,12F], b1[n,H], W2[n,H,H], b2[n,H], W3[n,4,H], b3[n,4], freq[F],
+    att[F] and optionally feat_attr[n,S,C].
+    """
+
+    def __init__(self, positions, log_scales, quats, W1, b1, W2, b2, W3, b3, freq, att, feat_attr=None,
+                 gate_beta=1.5, gate_tau=2.0, device="cuda", pack_f16=True):
+        lib = L.load()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("PackedScene must live on a CUDA device; there is no CPU path")
+        d = self.device
+        with torch.cuda.device(d):
+            self.positions = _dev_f32(positions, d)
+            self.log_scales = _dev_f32(log_scales, d)
+            self.quats_unit = normalize_rows(_dev_f32(quats, d))
+            self.W1, self.b1, self.W2 = _dev_f32(W1, d), _dev_f32(b1, d), _dev_f32(W2, d)
+            self.b2, self.W3, self.b3 = _dev_f32(b2, d), _dev_f32(W3, d), _dev_f32(b3, d)
+            self.freq, self.att = _dev_f32(freq, d), _dev_f32(att, d)
+            self.n = int(self.positions.shape[0])
+            self.hidden = int(self.W1.shape[1]) if self.n else 32
+            self.num_freq = int(self.freq.numel())
+            if self.n and int(self.W1.shape[2]) != 12 * self.num_freq:
+                raise ValueError("W1 input width must be 12 * num_frequencies")
+            self.geom = torch.empty((max(self.n, 1), L.GEOM_FLOATS), device=d, dtype=torch.float32)
+            L.check(lib.mlpsp_pack_geometry(L.ptr(self.positions), L.ptr(self.log_scales), L.ptr(self.quats_unit),
+                                            self.n, L.ptr(self.geom), _stream_ptr(d)), "mlpsp_pack_geometry")
+            self.feat_attr = None
+            self.feat_slots, self.feat_dim = 0, 0
+            if feat_attr is not None:
+                fa = _dev_f32(feat_attr, d)
+                if fa.dim() == 2:
+                    fa = fa[:, None, :].contiguous()
+                self.feat_attr, self.feat_slots, self.feat_dim = fa, int(fa.shape[1]), int(fa.shape[2])
+            self.gate_beta, self.gate_tau = float(gate_beta), float(gate_tau)
+            self.w16 = None
+            self.c = self._struct()
+            wbytes = int(lib.mlpsp_packed_weight_bytes(self.hidden, self.num_freq))
+            if pack_f16 and wbytes > 0 and self.n > 0:
+                self.w16 = torch.empty(self.n * wbytes, device=d, dtype=torch.uint8)
+                L.check(lib.mlpsp_pack_weights_f16(C.byref(self.c), L.ptr(self.w16), _stream_ptr(d)),
+                        "mlpsp_pack_weights_f16")
+                self.c = self._struct()
+
+    def _struct(self) -> L.Scene:
+        s = L.Scene()
+        s.geom, s.n, s.hidden, s.num_freq = L.ptr(self.geom), self.n, self.hidden, self.num_freq
+        s.W1, s.b1, s.W2, s.b2, s.W3, s.b3 = (L.ptr(t) for t in (self.W1, self.b1, self.W2, self.b2, self.W3, self.b3))
+        s.w16 = L.ptr(self.w16)
+        s.freq, s.att = L.ptr(self.freq), L.ptr(self.att)
+        s.feat_attr, s.feat_slots, s.feat_dim = L.ptr(self.feat_attr), self.feat_slots, self.feat_dim
+        s.gate_beta, s.gate_tau = self.gate_beta, self.gate_tau
+        return s
+
+    @property
+    def has_f16(self) -> bool:
+        return self.w16 is not None
+
+    def parameter_bytes(self) -> int:
+        ts = [self.geom, self.W1, self.b1, self.W2, self.b2, self.W3, self.b3, self.w16, self.feat_attr]
+        return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+
+@dataclass
+class FrameStats:
+    pairs: int
+    max_tile_len: int
+    records: int        # MLP evaluations performed
+    used: int           # records consumed by compositing
+    waves: int
+    wave_records: int
+    work_items: int
+
+
+class RenderError(RuntimeError):
+    pass
+
+
+def raise_for_status(bits: int, max_len: int, capacity: int, path_name: str):
+    """Turn status bits into the reference's error messages."""
+    if bits & L.BIT_BAD_OFFSETS:
+        raise RenderError(f"{path_name}: tile_offsets must start at zero, end at the candidate-list length, "
+                          "and be monotonic/in bounds")
+    if bits & L.BIT_TILE_CAPACITY:
+        raise RenderError(f"{path_name}: tile candidate capacity {capacity} exceeded (maximum observed tile "
+                          f"length {max_len}); refusing to truncate or use an inconsistent forward/backward order")
+    if bits & L.BIT_BAD_IDS:
+        raise RenderError(f"{path_name}: candidate primitive IDs must be in [0, num_primitives)")
+    if bits & L.BIT_TIMEOUT:
+        raise RenderError(f"{path_name}: a device-side wait gave up (status bit {L.BIT_TIMEOUT}); frame discarded")
+
+
+class FrameRenderer:
+    """Owns the scratch and output buffers for frames of one shape on one GPU."""
+
+    def __init__(self, width, height, device="cuda", tile_capacity=TILE_CAPACITY, max_pairs=None,
+                 max_records=4_000_000):
+        self.lib = L.load()
+        self.device = torch.device(device)
+        self.W, self.H = int(width), int(height)
+        self.P = self.W * self.H
+        self.T = ((self.W + TILE - 1) // TILE) * ((self.H + TILE - 1) // TILE)
+        self.capacity = int(tile_capacity)
+        self.max_pairs = int(max_pairs) if max_pairs is not None else min(self.T * self.capacity, 2**31 - 2)
+        self.max_records = int(max_records)
+        d = self.device
+        self.tile_offsets = torch.zeros(self.T + 1, device=d, dtype=torch.int32)
+        self.tile_prims = torch.empty(max(self.max_pairs, 1), device=d, dtype=torch.int32)
+        self.sorted_prims = torch.empty(max(self.max_pairs, 1), device=d, dtype=torch.int32)
+        self.rgb = torch.empty((self.P, 3), device=d, dtype=torch.float32)
+        self.alpha = torch.empty((self.P, 1), device=d, dtype=torch.float32)
+        self.depth_t = None
+        self.mask_used = None
+        self.rays_d_unit = torch.empty((self.P, 3), device=d, dtype=torch.float32)
+        self.status = torch.zeros(L.STATUS_WORDS, device=d, dtype=torch.int32)
+        self.status_host = torch.zeros(L.STATUS_WORDS, dtype=torch.int32).pin_memory()
+        self.scratch = None
+        self._scratch_key = None
+        self._view = np.zeros(16, np.float32)
+        self._proj = np.zeros(16, np.float32)
+        self._bg = np.zeros(3, np.float32)
+        self.last_stats: FrameStats | None = None
+
+    # -- buffers ------------------------------------------------------------------------------
+    def _ensure_scratch(self, n):
+        key = (n, self.max_pairs, self.max_records)
+        if self._scratch_key != key:
+            nbytes = int(self.lib.mlpsp_frame_scratch_bytes(n, self.W, self.H, TILE, self.max_pairs, self.max_records))
+            if nbytes < 0:
+                raise RuntimeError("mlpsp_frame_scratch_bytes rejected the frame shape")
+            self.scratch = None
+            self.scratch = torch.empty(nbytes + 256, device=self.device, dtype=torch.uint8)
+            self._scratch_key = key
+        return self.scratch
+
+    def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
+               want_mask_used, waves) -> L.Frame:
+        f = L.Frame()
+        f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
+        f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
+        f.tile_capacity, f.precision = self.capacity, int(precision)
+        if view is not None:
+            self._view[:] = np.asarray(view, dtype=np.float32).reshape(16)
+            self._proj[:] = np.asarray(proj, dtype=np.float32).reshape(16)
+            f.view, f.proj = self._view.ctypes.data, self._proj.ctypes.data
+        f.tile_offsets, f.tile_prims, f.sorted_prims = L.ptr(self.tile_offsets), L.ptr(self.tile_prims), L.ptr(self.sorted_prims)
+        f.max_pairs = self.max_pairs
+        f.rgb, f.alpha = L.ptr(self.rgb), L.ptr(self.alpha)
+        if want_depth:
+            if self.depth_t is None:
+                self.depth_t = torch.empty((self.P, 1), device=self.device, dtype=torch.float32)
+            f.depth_t = L.ptr(self.depth_t)
+        if want_mask_used:
+            if self.mask_used is None:
+                self.mask_used = torch.zeros(max(self.max_pairs, 1), device=self.device, dtype=torch.int64)
+            f.mask_used = L.ptr(self.mask_used)
+        if bg is not None:
+            self._bg[:] = np.asarray(bg, dtype=np.float32).reshape(-1)[:3] if np.size(bg) >= 3 else float(np.asarray(bg).reshape(-1)[0])
+            f.bg_color = self._bg.ctypes.data
+        sc = self._ensure_scratch(scene.n)
+        base = sc.data_ptr()
+        aligned = (base + 255) // 256 * 256
+        f.scratch, f.scratch_bytes = aligned, sc.numel() - (aligned - base)
+        f.max_records = self.max_records
+        f.status = L.ptr(self.status)
+        if waves:
+            f.num_waves = len(waves)
+            for i, w in enumerate(waves):
+                f.wave_len[i] = int(w)
+        return f
+
+    def _read_status(self):
+        self.status_host.copy_(self.status, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        s = self.status_host.numpy()
+        u = s.view(np.uint32)
+        rec = int(u[L.ST_RECORDS_LO]) | (int(u[L.ST_RECORDS_LO + 1]) << 32)
+        used = int(u[L.ST_USED_LO]) | (int(u[L.ST_USED_LO + 1]) << 32)
+        stats = FrameStats(int(s[L.ST_PAIRS]), int(s[L.ST_MAX_TILE_LEN]), rec, used, int(s[L.ST_WAVES]),
+                           int(s[L.ST_WAVE_RECORDS]), int(s[L.ST_WORK_ITEMS]))
+        return int(s[L.ST_BITS]), stats
+
+    def _grow(self, bits, stats):
+        """Resize after an overflow finding; returns True when the frame should be retried."""
+        if bits & L.BIT_PAIR_OVERFLOW:
+            self.max_pairs = int(stats.pairs * 1.1) + 1024
+            d = self.device
+            self.tile_prims = torch.empty(self.max_pairs, device=d, dtype=torch.int32)
+            self.sorted_prims = torch.empty(self.max_pairs, device=d, dtype=torch.int32)
+            self.mask_used = None
+            return True
+        if bits & L.BIT_RECORD_OVERFLOW:
+            self.max_records = int(max(stats.wave_records, self.max_records) * 1.25) + 4096
+            return True
+        return False
+
+    # -- stages -------------------------------------------------------------------------------
+    def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
+               bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
+               rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter"):
+        """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling)."""
+        lib, d = self.lib, self.device
+        if precision is None:
+            precision = L.PRECISION_F16 if scene.has_f16 else L.PRECISION_F32
+        with torch.cuda.device(d):
+            st = _stream_ptr(d)
+            if rays_normalized:
+                rd = rays_d
+            else:
+                L.check(lib.mlpsp_normalize_rows(L.ptr(rays_d), L.ptr(self.rays_d_unit), self.P, 3, st), "mlpsp_normalize_rows")
+                rd = self.rays_d_unit
+            for _attempt in range(4):
+                L.check(lib.mlpsp_status_reset(L.ptr(self.status), st), "mlpsp_status_reset")
+                if tile_lists is not None:
+                    prims, offs = tile_lists
+                    m = int(prims.numel())
+                    if m > self.max_pairs:
+                        self.max_pairs = m
+                        self.tile_prims = torch.empty(max(m, 1), device=d, dtype=torch.int32)
+                        self.sorted_prims = torch.empty(max(m, 1), device=d, dtype=torch.int32)
+                        self.mask_used = None
+                    self.tile_prims[:m].copy_(prims)
+                    self.tile_offsets.copy_(offs)
+                    L.check(lib.mlpsp_validate_tile_lists(L.ptr(self.tile_offsets), L.ptr(self.tile_prims), self.T, m,
+                                                          self.capacity, scene.n, L.ptr(self.status), st),
+                            "mlpsp_validate_tile_lists")
+                f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves)
+                if tile_lists is None:
+                    L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")
+                else:
+                    L.check(lib.mlpsp_sort_tiles(C.byref(scene.c), C.byref(f), None, st), "mlpsp_sort_tiles")
+                    L.check(lib.mlpsp_render_sorted(C.byref(scene.c), C.byref(f), st), "mlpsp_render_sorted")
+                if not check:
+                    return self.rgb, self.alpha
+                bits, stats = self._read_status()
+                self.last_stats = stats
+                if bits & (L.BIT_BAD_OFFSETS | L.BIT_TILE_CAPACITY | L.BIT_BAD_IDS | L.BIT_TIMEOUT):
+                    raise_for_status(bits, stats.max_tile_len, self.capacity, path_name)
+                if self._grow(bits, stats):
+                    continue
+                return self.rgb, self.alpha
+            raise RenderError(f"{path_name}: scratch kept overflowing after 4 attempts")
+
+    def bin(self, scene: PackedScene, view, proj, threshold, check=True):
+        """Binning only: returns (culled_prim_indices[M] int32, tile_offsets[T+1] int32) views."""
+        lib, d = self.lib, self.device
+        with torch.cuda.device(d):
+            st = _stream_ptr(d)
+            for _attempt in range(3):
+                L.check(lib.mlpsp_status_reset(L.ptr(self.status), st), "mlpsp_status_reset")
+                f = self._frame(scene, None, None, threshold, 0, view, proj, None, False, False, None)
+                L.check(lib.mlpsp_bin_tiles(C.byref(scene.c), C.byref(f), st), "mlpsp_bin_tiles")
+                bits, stats = self._read_status()
+                self.last_stats = stats
+                if check and (bits & L.BIT_TILE_CAPACITY):
+                    raise_for_status(bits, stats.max_tile_len, self.capacity, "mlpsp_bin_tiles")
+                if bits & L.BIT_PAIR_OVERFLOW and self._grow(bits, stats):
+                    continue
+                return self.tile_prims[:stats.pairs], self.tile_offsets
+            raise RenderError("mlpsp_bin_tiles: pair buffer kept overflowing")
+
+    def sort(self, scene: PackedScene, rays_o, rays_d_unit, pairs, want_keys=False):
+        lib, d = self.lib, self.device
+        with torch.cuda.device(d):
+            st = _stream_ptr(d)
+            f = self._frame(scene, rays_o, rays_d_unit, 0.5, 0, None, None, None, False, False, None)
+            keys = torch.empty(max(pairs, 1), device=d, dtype=torch.float32) if want_keys else None
+            L.check(lib.mlpsp_sort_tiles(C.byref(scene.c), C.byref(f), L.ptr(keys), st), "mlpsp_sort_tiles")
+            return (self.sorted_prims[:pairs], keys[:pairs]) if want_keys else self.sorted_prims[:pairs]
+
+    def hit_masks(self, scene: PackedScene, rays_o, rays_d_unit, threshold, pairs):
+        lib, d = self.lib, self.device
+        with torch.cuda.device(d):
+            st = _stream_ptr(d)
+            f = self._frame(scene, rays_o, rays_d_unit, threshold, 0, None, None, None, False, False, None)
+            out = torch.zeros(max(pairs, 1), device=d, dtype=torch.int64)
+            L.check(lib.mlpsp_hit_masks(C.byref(scene.c), C.byref(f), L.ptr(out), st), "mlpsp_hit_masks")
+            return out[:pairs]

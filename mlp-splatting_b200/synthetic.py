@@ -1,0 +1,102 @@
+"""Seeded synthetic scenes and pinhole cameras (numpy only, identical on every machine).
+
+Stand-ins for the Replica/ScanNet scenes the reference renders.  Distributions: centres uniform
+in a cube, per-axis log-normal scales, random unit quaternions, a 12F -> H -> H -> 4 MLP per
+primitive with Xavier-uniform weights rounded to binary16 (the reference's inference export stores
+MLP weights in FP16, scannet/checkpoints.py:358-359) and b3[:,3] = ln 4, which makes the centre
+opacity 1 - exp(-softplus(ln 4)) = 0.8.  Cameras follow the reference loader's ray convention
+(scannet/scannet_loader.py:397-410) and its evaluation projection (scannet/eval_rgb_psnr.py:68-93).
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+
+def _xavier(rng, n, fan_out, fan_in):
+    bound = math.sqrt(6.0 / (fan_in + fan_out))
+    w = rng.uniform(-bound, bound, size=(n, fan_out, fan_in)).astype(np.float32)
+    return w.astype(np.float16).astype(np.float32)
+
+
+def make_scene(n, seed, mu=-3.5, sigma=0.5, hidden=32, num_freq=6, extent=1.0,
+               feat_dim=0, feat_slots=4, pe_sigma=0.01):
+    """Return a dict of float32 arrays holding one scene's parameters."""
+    rng = np.random.default_rng(seed)
+    pos = rng.uniform(-extent, extent, size=(n, 3)).astype(np.float32)
+    log_scales = rng.normal(mu, sigma, size=(n, 3)).astype(np.float32)
+    q = rng.normal(0.0, 1.0, size=(n, 4))
+    q = (q / np.sqrt((q * q).sum(1, keepdims=True))).astype(np.float32)
+    IN = 12 * num_freq
+    scene = dict(
+        positions=pos, log_scales=log_scales, quats=q,
+        W1=_xavier(rng, n, hidden, IN), b1=np.zeros((n, hidden), np.float32),
+        W2=_xavier(rng, n, hidden, hidden), b2=np.zeros((n, hidden), np.float32),
+        W3=_xavier(rng, n, 4, hidden), b3=np.zeros((n, 4), np.float32),
+    )
+    scene["b3"][:, 3] = np.float32(math.log(4.0))
+    freq = (2.0 ** np.arange(num_freq, dtype=np.float64) * math.pi).astype(np.float32)
+    scene["freq"] = freq
+    scene["att"] = np.exp(-0.5 * freq.astype(np.float64) ** 2 * pe_sigma ** 2).astype(np.float32)
+    if feat_dim > 0:
+        fa = rng.normal(0.0, 0.2, size=(n, feat_slots, feat_dim)).astype(np.float32)
+        scene["feat_attr"] = fa.astype(np.float16).astype(np.float32)
+    return scene
+
+
+def make_camera(W, H, azimuth_deg=0.0, radius=3.0, fov_deg=60.0, elevation_deg=0.0):
+    """Pinhole camera on a circle around the origin, looking at it.
+
+    Returns dict(rays_o [W*H,3], rays_d [W*H,3] (not normalised), view [4,4], proj [4,4], focal).
+    """
+    az, el = math.radians(azimuth_deg), math.radians(elevation_deg)
+    eye = np.array([radius * math.sin(az) * math.cos(el), radius * math.sin(el),
+                    -radius * math.cos(az) * math.cos(el)], np.float64)
+    fwd = -eye / np.linalg.norm(eye)
+    up = np.array([0.0, 1.0, 0.0])
+    right = np.cross(up, fwd)
+    right /= np.linalg.norm(right)
+    down = np.cross(fwd, right)
+    c2w = np.eye(4)
+    c2w[:3, 0], c2w[:3, 1], c2w[:3, 2], c2w[:3, 3] = right, down, fwd, eye
+    focal = (H / 2.0) / math.tan(math.radians(fov_deg) / 2.0)
+    i, j = np.meshgrid(np.arange(W, dtype=np.float32), np.arange(H, dtype=np.float32), indexing="xy")
+    f32 = np.float32(focal)
+    dirs = np.stack([(i - np.float32(W * 0.5)) / f32, (j - np.float32(H * 0.5)) / f32,
+                     np.ones_like(i)], -1)
+    R = c2w[:3, :3].astype(np.float32)
+    rays_d = (dirs[..., None, :] * R).sum(-1).reshape(-1, 3).astype(np.float32)
+    rays_o = np.broadcast_to(c2w[:3, 3].astype(np.float32), rays_d.shape).copy()
+    view = np.linalg.inv(c2w).astype(np.float32)
+    near, far = 0.001, 100.0
+    t = (0.5 * H) / (focal + 1e-8)
+    r = t * (W / H)
+    proj = np.zeros((4, 4), np.float32)
+    proj[0, 0], proj[1, 1] = 1.0 / r, 1.0 / t
+    proj[2, 2] = -(far + near) / (far - near)
+    proj[3, 2] = 1.0
+    proj[2, 3] = -(2 * far * near) / (far - near)
+    return dict(rays_o=rays_o, rays_d=rays_d, view=view, proj=proj, focal=float(focal), W=W, H=H)
+
+
+# Named workloads.  `mu` is the one tuned knob per workload (mean of the log-scale distribution):
+# with the literal mu = -3.5 the 100k+ scenes exceed the 1,536-candidate tile capacity, which the
+# reference turns into an error, so mu is lowered until the densest tile fits.
+WORKLOADS = {
+    "tiny_2k_128x96": dict(n=2000, W=128, H=96, mu=-3.5, views=1, seed=2026),
+    "single_100k_1200x680": dict(n=100_000, W=1200, H=680, mu=-4.2, views=1, seed=2027),
+    "feature_250k_1200x680": dict(n=250_000, W=1200, H=680, mu=-4.8, views=1, seed=2028, feat_dim=512),
+    "fourview_500k_1200x680": dict(n=500_000, W=1200, H=680, mu=-5.2, views=4, seed=2029),
+    "stress_2m_1920x1080": dict(n=2_000_000, W=1920, H=1080, mu=-6.0, views=32, seed=2030, hidden=64),
+}
+
+
+def make_workload(name, **overrides):
+    cfg = dict(WORKLOADS[name])
+    cfg.update(overrides)
+    scene = make_scene(cfg["n"], cfg["seed"], mu=cfg["mu"], hidden=cfg.get("hidden", 32),
+                       feat_dim=cfg.get("feat_dim", 0))
+    views = cfg["views"]
+    cams = [make_camera(cfg["W"], cfg["H"], azimuth_deg=360.0 * v / views) for v in range(views)]
+    return scene, cams, cfg

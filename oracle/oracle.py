@@ -1,0 +1,247 @@
+"""ctypes/numpy front end of the CPU oracle (oracle/mlpsp_oracle.c).
+
+TEST INFRASTRUCTURE ONLY.  The product package never imports this module; the tests, the
+smoke check and the benchmark's CPU-baseline leg are the only callers.
+
+The functions mirror the stages of the reference renderer (scannet/cumodel.py forward and
+scannet/cuda/np_tile_kernels.cu render_tiles_kernel_tilecenter_order) and the record helpers
+(scannet/primitive_csr.py:23-29, scannet/primitive_gemm.py:186-203); each C function cites the
+lines it follows.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import build as _build
+
+_LIB = None
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        here = os.path.dirname(os.path.abspath(__file__))
+        path = os.path.join(here, "liboracle.so")
+        if not os.path.exists(path) or (os.path.exists(_build.SRC) and
+                                        os.path.getmtime(path) < os.path.getmtime(_build.SRC)):
+            path = _build.build(force=True)
+        _LIB = C.CDLL(path)
+        _LIB.orc_det_exp.restype = C.c_float
+        _LIB.orc_det_exp.argtypes = [C.c_float]
+        _LIB.orc_f16_round.restype = C.c_float
+        _LIB.orc_f16_round.argtypes = [C.c_float]
+        _LIB.orc_radius_multiplier.restype = C.c_float
+        _LIB.orc_radius_multiplier.argtypes = [C.c_float]
+        _LIB.orc_bin_count.restype = C.c_int64
+        assert _LIB.orc_sizeof_render() == C.sizeof(_Render), "render_t layout mismatch"
+    return _LIB
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _p(a, ty=C.c_float):
+    return None if a is None else a.ctypes.data_as(C.POINTER(ty))
+
+
+class _Mlp(C.Structure):
+    _fields_ = [(n, C.POINTER(C.c_float)) for n in ("W1", "b1", "W2", "b2", "W3", "b3", "freq", "att")] + \
+               [("F", C.c_int), ("H", C.c_int), ("IN", C.c_int), ("precision", C.c_int)]
+
+
+class _Render(C.Structure):
+    _fields_ = [
+        ("rays_o", C.POINTER(C.c_float)), ("rays_d", C.POINTER(C.c_float)),
+        ("geom", C.POINTER(C.c_float)), ("n", C.c_int),
+        ("tile_offsets", C.POINTER(C.c_int32)), ("sorted_prims", C.POINTER(C.c_int32)),
+        ("W", C.c_int), ("H", C.c_int), ("ts", C.c_int), ("thr", C.c_float),
+        ("mlp", _Mlp),
+        ("feat_attr", C.POINTER(C.c_float)), ("feat_slots", C.c_int), ("feat_dim", C.c_int),
+        ("beta", C.c_float), ("tau", C.c_float),
+        ("tile_begin", C.c_int), ("tile_end", C.c_int),
+        ("rgb", C.POINTER(C.c_float)), ("alpha", C.POINTER(C.c_float)),
+        ("depth_t", C.POINTER(C.c_float)), ("feat", C.POINTER(C.c_float)),
+        ("mask_geo", C.POINTER(C.c_uint64)), ("mask_used", C.POINTER(C.c_uint64)),
+        ("min_margin", C.POINTER(C.c_float)), ("rec_count", C.POINTER(C.c_int32)),
+        ("rec_offsets", C.POINTER(C.c_int64)),
+        ("rec_ids", C.POINTER(C.c_int32)), ("rec_x6", C.POINTER(C.c_float)),
+        ("rec_raw", C.POINTER(C.c_float)), ("rec_masks", C.POINTER(C.c_int32)),
+        ("rec_gates", C.POINTER(C.c_float)),
+        ("evals", C.c_int64),
+    ]
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def det_exp(x):
+    f = lib().orc_det_exp
+    return np.array([f(float(v)) for v in np.asarray(x, dtype=np.float32).ravel()], dtype=np.float32)
+
+
+def f16_round(x):
+    f = lib().orc_f16_round
+    a = np.asarray(x, dtype=np.float32)
+    return np.array([f(float(v)) for v in a.ravel()], dtype=np.float32).reshape(a.shape)
+
+
+def normalize_rows(a):
+    a = _f32(a)
+    out = np.empty_like(a)
+    lib().orc_normalize_rows(_p(a), _p(out), C.c_int64(a.shape[0]), C.c_int(a.shape[1]))
+    return out
+
+
+def pack_geometry(positions, log_scales, quats_unit):
+    pos, ls, q = _f32(positions), _f32(log_scales), _f32(quats_unit)
+    n = pos.shape[0]
+    geom = np.empty((n, 16), np.float32)
+    lib().orc_pack_geometry(_p(pos), _p(ls), _p(q), C.c_int(n), _p(geom))
+    return geom
+
+
+def bin_tiles(geom, view, proj, W, H, tile, thr):
+    """Screen-space culling (cumodel.py:994-1070): returns (culled_prim_indices, tile_offsets)."""
+    geom, view, proj = _f32(geom), _f32(view).reshape(16), _f32(proj).reshape(16)
+    T = ((W + tile - 1) // tile) * ((H + tile - 1) // tile)
+    off = np.zeros(T + 1, np.int32)
+    n = geom.shape[0]
+    total = lib().orc_bin_count(_p(geom), C.c_int(n), _p(view), _p(proj), C.c_int(W), C.c_int(H),
+                                C.c_int(tile), C.c_float(thr), _p(off, C.c_int32))
+    prims = np.empty(int(total), np.int32)
+    lib().orc_bin_fill(_p(geom), C.c_int(n), _p(view), _p(proj), C.c_int(W), C.c_int(H),
+                       C.c_int(tile), C.c_float(thr), _p(off, C.c_int32), _p(prims, C.c_int32))
+    return prims, off
+
+
+def validate_lists(tile_offsets, prims, capacity, n):
+    off, pr = _i32(tile_offsets), _i32(prims)
+    st = np.zeros(2, np.int32)
+    lib().orc_validate_lists(_p(off, C.c_int32), _p(pr, C.c_int32), C.c_int(off.size - 1), C.c_int(pr.size),
+                             C.c_int(capacity), C.c_int(n), _p(st, C.c_int32))
+    return int(st[0]), int(st[1])
+
+
+def sort_tiles(rays_o, rays_d, geom, tile_offsets, tile_prims, W, H, tile, want_keys=False):
+    ro, rd, geom = _f32(rays_o), _f32(rays_d), _f32(geom)
+    off, pr = _i32(tile_offsets), _i32(tile_prims)
+    out = np.empty_like(pr)
+    keys = np.empty(pr.size, np.float32) if want_keys else None
+    lib().orc_sort_tiles(_p(ro), _p(rd), _p(geom), C.c_int(geom.shape[0]), _p(off, C.c_int32),
+                         _p(pr, C.c_int32), C.c_int(W), C.c_int(H), C.c_int(tile), _p(out, C.c_int32), _p(keys))
+    return (out, keys) if want_keys else out
+
+
+def mlp_eval(weights, freq, att, prim_ids, x6, precision=0):
+    """(R,G,B,sigma_raw) per record: cumodel.py:183-216 / np_tile_kernels.cu:312-380."""
+    W1, b1, W2, b2, W3, b3 = [_f32(w) for w in weights]
+    freq, att, x6, ids = _f32(freq), _f32(att), _f32(x6), _i32(prim_ids)
+    out = np.empty((ids.size, 4), np.float32)
+    lib().orc_mlp_eval(_p(W1), _p(b1), _p(W2), _p(b2), _p(W3), _p(b3), _p(freq), _p(att),
+                       C.c_int(freq.size), C.c_int(W1.shape[1]), C.c_int(precision),
+                       _p(ids, C.c_int32), _p(x6), C.c_int64(ids.size), _p(out))
+    return out
+
+
+@dataclass
+class RenderResult:
+    rgb: np.ndarray
+    alpha: np.ndarray
+    depth_t: np.ndarray
+    feat: np.ndarray | None
+    mask_geo: np.ndarray | None
+    mask_used: np.ndarray | None
+    min_margin: np.ndarray
+    rec_count: np.ndarray
+    evals: int
+    records: dict | None = None
+
+
+def render(rays_o, rays_d_unit, geom, tile_offsets, sorted_prims, W, H, tile, thr, weights, freq, att,
+           precision=0, feat_attr=None, beta=1.5, tau=2.0, want_masks=True, want_records=False,
+           tile_range=None) -> RenderResult:
+    """Tile-major front-to-back render of depth-sorted tile lists (np_tile_kernels.cu:1837-2137)."""
+    ro, rd, geom = _f32(rays_o), _f32(rays_d_unit), _f32(geom)
+    off, sp = _i32(tile_offsets), _i32(sorted_prims)
+    W1, b1, W2, b2, W3, b3 = [_f32(w) for w in weights]
+    freq, att = _f32(freq), _f32(att)
+    P = W * H
+    T = off.size - 1
+    a = _Render()
+    keep = [ro, rd, geom, off, sp, W1, b1, W2, b2, W3, b3, freq, att]
+    a.rays_o, a.rays_d, a.geom, a.n = _p(ro), _p(rd), _p(geom), geom.shape[0]
+    a.tile_offsets, a.sorted_prims = _p(off, C.c_int32), _p(sp, C.c_int32)
+    a.W, a.H, a.ts, a.thr = W, H, tile, thr
+    a.mlp = _Mlp(_p(W1), _p(b1), _p(W2), _p(b2), _p(W3), _p(b3), _p(freq), _p(att),
+                 freq.size, W1.shape[1], 12 * freq.size, precision)
+    feat = None
+    if feat_attr is not None:
+        fa = _f32(feat_attr)
+        if fa.ndim == 2:
+            fa = fa[:, None, :]
+        keep.append(fa)
+        feat = np.zeros((P, fa.shape[2]), np.float32)
+        a.feat_attr, a.feat_slots, a.feat_dim, a.feat = _p(fa), fa.shape[1], fa.shape[2], _p(feat)
+    a.beta, a.tau = beta, tau
+    a.tile_begin, a.tile_end = (0, T) if tile_range is None else tile_range
+    rgb = np.zeros((P, 3), np.float32)
+    alpha = np.zeros(P, np.float32)
+    dt = np.zeros(P, np.float32)
+    marg = np.full(P, 1e30, np.float32)
+    cnt = np.zeros(P, np.int32)
+    a.rgb, a.alpha, a.depth_t, a.min_margin, a.rec_count = _p(rgb), _p(alpha), _p(dt), _p(marg), _p(cnt, C.c_int32)
+    mg = mu = None
+    if want_masks and tile == 8:
+        mg = np.zeros(sp.size, np.uint64)
+        mu = np.zeros(sp.size, np.uint64)
+        a.mask_geo, a.mask_used = _p(mg, C.c_uint64), _p(mu, C.c_uint64)
+    lib().orc_render(C.byref(a))
+    res = RenderResult(rgb, alpha, dt, feat, mg, mu, marg, cnt, int(a.evals))
+    if want_records:
+        offs = np.zeros(P + 1, np.int64)
+        np.cumsum(cnt, out=offs[1:])
+        R = int(offs[-1])
+        rec = dict(offsets=offs, ids=np.empty(R, np.int32), x6=np.empty((R, 6), np.float32),
+                   raw=np.empty((R, 8), np.float32), masks=np.empty((R, 2), np.int32),
+                   gates=np.empty((R, 4), np.float32))
+        a.rec_offsets = _p(offs, C.c_int64)
+        a.rec_ids, a.rec_x6, a.rec_raw = _p(rec["ids"], C.c_int32), _p(rec["x6"]), _p(rec["raw"])
+        a.rec_masks, a.rec_gates = _p(rec["masks"], C.c_int32), _p(rec["gates"])
+        if feat is not None:
+            feat[:] = 0
+        lib().orc_render(C.byref(a))
+        res.records = rec
+    del keep
+    return res
+
+
+# ---- record grouping: scannet/primitive_csr.py:23-29 and scannet/primitive_gemm.py:186-203 ----
+
+def group_records(primitive_ids, num_primitives):
+    """Stable grouping by primitive: (offsets int64 [N+1], order int64 [R])."""
+    ids = np.asarray(primitive_ids).astype(np.int64)
+    order = np.argsort(ids, kind="stable")
+    counts = np.bincount(ids, minlength=num_primitives)
+    offsets = np.concatenate(([0], np.cumsum(counts))).astype(np.int64)
+    return offsets, order.astype(np.int64)
+
+
+def prepare_groups(offsets, segment_size=512):
+    """Segments of at most segment_size records: (primitives [G], starts [G], group_offsets [N+1])."""
+    offsets = np.asarray(offsets, dtype=np.int64)
+    counts = -(-np.diff(offsets) // segment_size)
+    group_offsets = np.concatenate(([0], np.cumsum(counts))).astype(np.int64)
+    primitives = np.repeat(np.arange(counts.size, dtype=np.int64), counts)
+    local = np.arange(primitives.size, dtype=np.int64) - group_offsets[primitives]
+    starts = offsets[primitives] + local * segment_size
+    return primitives, starts, group_offsets

@@ -1,0 +1,95 @@
+"""Generate the golden fixtures in this directory from the reference's own Python code.
+
+Run where the reference checkout is available:
+
+    python tests/golden/make_golden.py /path/to/mlp-splatting
+
+Only device-agnostic reference functions are called, on CPU:
+  scannet.cumodel._encode_x6, _mlp_forward_indexed            -> mlp_eval.npz
+  scannet.cumodel.IntegratedPositionalEncoding                 -> encoding.npz
+  NeuralPrimitiveSceneTileCUDA.build_tilecenter_culling_from_tile_views (its device check is
+  pointed at the CPU for the call; the culling code itself is untouched)  -> culling.npz
+  scannet.primitive_csr.group_records, scannet.primitive_gemm.prepare_groups -> grouping.npz
+The scene inputs come from this repository's seeded generator, so tests can rebuild them.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+
+def main(ref_root):
+    sys.path.insert(0, ref_root)
+    import scannet.cumodel as cm
+    from scannet.primitive_csr import group_records
+    from scannet.primitive_gemm import prepare_groups
+    from mlp_splatting_b200 import synthetic as syn
+
+    torch.manual_seed(0)
+    # ---- MLP + encoding -------------------------------------------------------------------
+    out = {}
+    for tag, (F, H, n, R) in {"f6h32": (6, 32, 8, 256), "f1h1": (1, 1, 3, 16), "f4h16": (4, 16, 5, 64)}.items():
+        sc = syn.make_scene(n, seed=100 + F, hidden=H, num_freq=F)
+        rng = np.random.default_rng(7 + F)
+        x6 = rng.normal(0, 0.5, (R, 6)).astype(np.float32)
+        x6[:, :3] /= np.linalg.norm(x6[:, :3], axis=1, keepdims=True)
+        ids = rng.integers(0, n, R).astype(np.int64)
+        enc = cm._encode_x6(torch.from_numpy(x6), torch.from_numpy(sc["freq"]), torch.from_numpy(sc["att"]))
+        rgb, sig = cm._mlp_forward_indexed(enc, torch.from_numpy(ids), *[torch.from_numpy(sc[k]) for k in
+                                                                        ("W1", "b1", "W2", "b2", "W3", "b3")])
+        out[f"{tag}_x6"], out[f"{tag}_ids"] = x6, ids.astype(np.int32)
+        out[f"{tag}_enc"] = enc.numpy()
+        out[f"{tag}_out"] = torch.cat([rgb, sig], 1).numpy()
+        out[f"{tag}_cfg"] = np.array([F, H, n, 100 + F], np.int64)
+    np.savez_compressed(os.path.join(HERE, "mlp_eval.npz"), **out)
+
+    enc = cm.IntegratedPositionalEncoding(in_dim=6, num_frequencies=6, sigma=0.01)
+    att = torch.exp(-0.5 * (enc.freq_bands ** 2) * enc.sigma2) * enc.runtime_frequency_weights
+    np.savez_compressed(os.path.join(HERE, "encoding.npz"), freq=enc.freq_bands.numpy(), att=att.numpy())
+
+    # ---- culling --------------------------------------------------------------------------
+    out = {}
+    for tag, (n, W, H, mu, thr, az, seed) in {
+        "a": (500, 64, 48, -3.0, 5e-3, 0.0, 11), "b": (2000, 128, 96, -3.5, 5e-3, 30.0, 2026),
+        "c": (300, 37, 29, -2.5, 1e-3, 200.0, 13), "d": (1500, 100, 60, -3.2, 3e-3, 90.0, 14),
+    }.items():
+        sc = syn.make_scene(n, seed=seed, mu=mu)
+        cam = syn.make_camera(W, H, azimuth_deg=az)
+        model = cm.NeuralPrimitiveSceneTileCUDA(num_primitives=n)
+        with torch.no_grad():
+            model.positions.copy_(torch.from_numpy(sc["positions"]))
+            model.log_scales.copy_(torch.from_numpy(sc["log_scales"]))
+        model.set_image_size(W, H)
+        model._activate_cuda_device = lambda: torch.device("cpu")
+        T = ((W + 7) // 8) * ((H + 7) // 8)
+        ids, offs = model.build_tilecenter_culling_from_tile_views(
+            torch.zeros(T, dtype=torch.long), torch.from_numpy(cam["view"])[None], torch.from_numpy(cam["proj"]),
+            score_threshold=thr, tile_size=8)
+        out[f"{tag}_cfg"] = np.array([n, W, H, seed], np.int64)
+        out[f"{tag}_fcfg"] = np.array([mu, thr, az], np.float64)
+        out[f"{tag}_ids"], out[f"{tag}_offsets"] = ids.numpy().astype(np.int32), offs.numpy().astype(np.int32)
+    np.savez_compressed(os.path.join(HERE, "culling.npz"), **out)
+
+    # ---- grouping -------------------------------------------------------------------------
+    counts = [0, 1, 31, 32, 33, 511, 512, 513, 1700, 0]
+    ids = np.repeat(np.arange(len(counts)), counts)
+    rng = np.random.default_rng(3)
+    ids = ids[rng.permutation(ids.size)].astype(np.int32)
+    x6 = torch.arange(ids.size * 6, dtype=torch.float32).reshape(-1, 6)
+    csr = group_records(torch.from_numpy(ids), x6, x6[:, :4], len(counts))
+    out = dict(ids=ids, n=np.int64(len(counts)), offsets=csr.offsets.numpy(), order=csr.record_indices.numpy())
+    for seg in (512, 64):
+        g = prepare_groups(csr, seg)
+        out[f"seg{seg}_primitives"], out[f"seg{seg}_starts"], out[f"seg{seg}_goff"] = (
+            g.primitives.numpy(), g.starts.numpy(), g.offsets.numpy())
+    np.savez_compressed(os.path.join(HERE, "grouping.npz"), **out)
+    print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

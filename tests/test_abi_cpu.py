@@ -1,0 +1,61 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/mlpsp.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "mlpsp.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mlpsp_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from mlp_splatting_b200 import _lib
+    assert os.path.exists(_lib.LIB_PATH), "build the library first: python mlp-splatting_b200/build.py"
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    names = _declared()
+    assert len(names) >= 18
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/mlpsp.h but not exported"
+    assert set(_lib.EXPORTS) == set(names), "binding table and header disagree"
+
+
+def test_struct_layout_and_pure_host_queries():
+    from mlp_splatting_b200 import _lib
+    lib = _lib.load()   # checks ABI version and struct sizes
+    assert lib.mlpsp_frame_scratch_bytes(1000, 128, 96, 8, 10000, 50000) > 0
+    assert lib.mlpsp_frame_scratch_bytes(-1, 128, 96, 8, 10000, 50000) == -1
+    assert lib.mlpsp_group_records_scratch_bytes(1000, 10) > 0
+    assert lib.mlpsp_mlp_grouped_scratch_bytes(1000, 10) > 0
+
+
+def test_argument_errors_need_no_gpu():
+    from mlp_splatting_b200 import _lib
+    lib = _lib.load()
+    assert lib.mlpsp_normalize_rows(None, None, 4, 5, None) == -1
+    assert b"dim must be 3 or 4" in lib.mlpsp_last_error()
+    sc, fr = _lib.Scene(), _lib.Frame()
+    fr.width, fr.height, fr.tile, fr.threshold = 64, 48, 16, 0.5
+    assert lib.mlpsp_render_frame(ctypes.byref(sc), ctypes.byref(fr), None) == -1
+    assert b"8x8 tiles" in lib.mlpsp_last_error()
+
+
+def test_product_never_imports_oracle():
+    pkg = os.path.join(ROOT, "mlp-splatting_b200")
+    for dirpath, _d, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                assert "oracle" not in open(os.path.join(dirpath, f)).read().lower().replace("# oracle", ""), f
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from mlp_splatting_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libmlpsp_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
