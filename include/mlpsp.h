@@ -126,7 +126,8 @@ int mlpsp_normalize_rows(const float* in, float* out, int64_t rows, int32_t dim,
 /* Bytes per primitive of the fp16 evaluator's packed weight image, and the packer.  Replaces the
  * per-(tile, primitive) FP32->fp16 re-cast of rgb_wmma.cuh:162-176 with one cast per scene. */
 int64_t mlpsp_packed_weight_bytes(int32_t hidden, int32_t num_freq);
-int mlpsp_pack_weights_f16(const mlpsp_scene* scene, void* w16_out, void* stream);
+/* status (optional): MLPSP_ST_NUMERIC is raised when a weight or bias is not finite in fp16/FP32. */
+int mlpsp_pack_weights_f16(const mlpsp_scene* scene, void* w16_out, int32_t* status, void* stream);
 
 int mlpsp_status_reset(int32_t* status, void* stream);
 

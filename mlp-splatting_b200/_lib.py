@@ -52,7 +52,7 @@ _SIGS = {
     "mlpsp_pack_geometry": (C.c_int, [_fp, _fp, _fp, C.c_int32, _fp, _fp]),
     "mlpsp_normalize_rows": (C.c_int, [_fp, _fp, C.c_int64, C.c_int32, _fp]),
     "mlpsp_packed_weight_bytes": (C.c_int64, [C.c_int32, C.c_int32]),
-    "mlpsp_pack_weights_f16": (C.c_int, [C.POINTER(Scene), _fp, _fp]),
+    "mlpsp_pack_weights_f16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
     "mlpsp_status_reset": (C.c_int, [_fp, _fp]),
     "mlpsp_frame_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
     "mlpsp_bin_tiles": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp]),

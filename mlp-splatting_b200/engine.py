@@ -76,12 +76,20 @@ class PackedScene:
                 self.feat_attr, self.feat_slots, self.feat_dim = fa, int(fa.shape[1]), int(fa.shape[2])
             self.gate_beta, self.gate_tau = float(gate_beta), float(gate_tau)
             self.w16 = None
+            self.f16_rejected = False
             self.c = self._struct()
             wbytes = int(lib.mlpsp_packed_weight_bytes(self.hidden, self.num_freq))
             if pack_f16 and wbytes > 0 and self.n > 0:
-                self.w16 = torch.empty(self.n * wbytes, device=d, dtype=torch.uint8)
-                L.check(lib.mlpsp_pack_weights_f16(C.byref(self.c), L.ptr(self.w16), _stream_ptr(d)),
+                w16 = torch.empty(self.n * wbytes, device=d, dtype=torch.uint8)
+                st = torch.zeros(L.STATUS_WORDS, device=d, dtype=torch.int32)
+                L.check(lib.mlpsp_pack_weights_f16(C.byref(self.c), L.ptr(w16), L.ptr(st), _stream_ptr(d)),
                         "mlpsp_pack_weights_f16")
+                # weights that are not finite in binary16 keep the scene on the FP32 evaluator, which is
+                # what the reference's per-frame overflow check amounts to (rgb_wmma.cuh:162-176, 260-272)
+                if int(st[L.ST_BITS].item()) & L.BIT_NUMERIC:
+                    self.f16_rejected = True
+                else:
+                    self.w16 = w16
                 self.c = self._struct()
 
     def _struct(self) -> L.Scene:
@@ -162,6 +170,7 @@ class FrameRenderer:
         self._proj = np.zeros(16, np.float32)
         self._bg = np.zeros(3, np.float32)
         self.last_stats: FrameStats | None = None
+        self.f32_fallbacks = 0   # frames re-rendered in FP32 after an fp16 overflow
 
     # -- buffers ------------------------------------------------------------------------------
     def _ensure_scratch(self, n):
@@ -279,6 +288,12 @@ class FrameRenderer:
                 if bits & (L.BIT_BAD_OFFSETS | L.BIT_TILE_CAPACITY | L.BIT_BAD_IDS | L.BIT_TIMEOUT):
                     raise_for_status(bits, stats.max_tile_len, self.capacity, path_name)
                 if self._grow(bits, stats):
+                    continue
+                if (bits & L.BIT_NUMERIC) and precision == L.PRECISION_F16:
+                    # operand/activation overflow in binary16: render the whole frame again in scalar
+                    # FP32, as the reference does (rgb_wmma.cuh:260-272)
+                    self.f32_fallbacks += 1
+                    precision = L.PRECISION_F32
                     continue
                 return self.rgb, self.alpha
             raise RenderError(f"{path_name}: scratch kept overflowing after 4 attempts")

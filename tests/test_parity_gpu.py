@@ -64,6 +64,15 @@ def test_bin_sort_hits_bit_exact(dev, name, thr):
     scene, cam = small_case(**CASES[name])
     f = oracle_frame(scene, cam, thr, precision=0)
     ps, r = _packed(scene, dev), _renderer(cam, dev)
+    if f["status"][0]:
+        # the oracle's validator rejects this scene at this threshold; so must the GPU path, with the
+        # same worst tile length, and the tile offsets (counts) are still exact
+        from mlp_splatting_b200.engine import RenderError
+        with pytest.raises(RenderError, match=f"maximum observed tile length {f['status'][1]}\\)"):
+            r.bin(ps, cam["view"], cam["proj"], thr)
+        _prims, offs = r.bin(ps, cam["view"], cam["proj"], thr, check=False)
+        np.testing.assert_array_equal(offs.cpu().numpy(), f["tile_offsets"])
+        return
     prims, offs = r.bin(ps, cam["view"], cam["proj"], thr)
     np.testing.assert_array_equal(offs.cpu().numpy(), f["tile_offsets"])
     np.testing.assert_array_equal(prims.cpu().numpy(), f["tile_prims"])
@@ -120,6 +129,67 @@ def test_render_fp32_matches_oracle(dev, name):
     st = r.last_stats
     assert st.pairs == M and st.used == int(popcount64(used).sum())
     assert st.records >= st.used and abs(st.used - res.evals) <= 64
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_render_fp16_tensor_core_matches_oracle(dev, name):
+    """tcgen05 evaluator: fp16 operands, FP32 accumulate; image within 2e-3 of the oracle's fp16 model
+    and of the FP32 render (the tolerance the path is specified to)."""
+    scene, cam = small_case(**CASES[name])
+    thr = 5e-3
+    f16 = oracle_frame(scene, cam, thr, precision=1)
+    f32 = oracle_frame(scene, cam, thr, precision=0, want_masks=False)
+    ps, r = _packed(scene, dev, pack_f16=True), _renderer(cam, dev)
+    assert ps.has_f16
+    rgb, alpha = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), thr, view=cam["view"], proj=cam["proj"],
+                          precision=1, want_mask_used=True)
+    g_rgb, g_a = rgb.cpu().numpy(), alpha.cpu().numpy()[:, 0]
+    assert np.abs(g_rgb - f16["render"].rgb).max() <= 1e-3      # same rounding model, different sum order
+    assert np.abs(g_a - f16["render"].alpha).max() <= 1e-3
+    assert np.abs(g_rgb - f32["render"].rgb).max() <= IMG_TOL_F16
+    assert np.abs(g_a - f32["render"].alpha).max() <= IMG_TOL_F16
+    M = f16["tile_prims"].size
+    used = r.mask_used.cpu().numpy()[:M].view(np.uint64)
+    _compare_used(used, f16["render"], f16["tile_offsets"], cam, margin=5e-2)
+    assert r.f32_fallbacks == 0
+
+
+def test_grouped_forward_fp16_tensor_core(dev):
+    from mlp_splatting_b200 import primitive_gemm
+    from oracle import oracle as orc
+    n, R = 53, 20000
+    scene, _cam = small_case(n=n, seed=91)
+    rng = np.random.default_rng(4)
+    counts = rng.integers(0, 900, n)
+    counts[[3, 17]] = 0
+    counts[5], counts[6], counts[7], counts[8] = 1, 127, 128, 129
+    ids = np.repeat(np.arange(n), counts).astype(np.int32)
+    R = ids.size
+    x6 = rng.normal(0, 0.4, (R, 6)).astype(np.float32)
+    offsets = np.concatenate(([0], np.cumsum(counts))).astype(np.int64)
+    ps = _packed(scene, dev, pack_f16=True)
+    out = primitive_gemm.grouped_forward(_t(offsets, dev), _t(x6, dev), ps, dtype=torch.float16).cpu().numpy()
+    want = orc.mlp_eval([scene[k] for k in WKEYS], scene["freq"], scene["att"], ids, x6, precision=1)
+    np.testing.assert_allclose(out, want, rtol=1e-3, atol=1e-3)
+    want32 = orc.mlp_eval([scene[k] for k in WKEYS], scene["freq"], scene["att"], ids, x6, precision=0)
+    np.testing.assert_allclose(out, want32, rtol=4e-3, atol=4e-3)
+
+
+def test_fp16_overflow_falls_back_to_fp32_frame(dev):
+    """Activations beyond binary16 range: the frame is rendered again in FP32 (rgb_wmma.cuh:260-272)."""
+    scene, cam = small_case(**CASES["tiny"])
+    scene = dict(scene)
+    scene["b1"] = scene["b1"].copy()
+    scene["b1"][:, 0] = 1.0e5          # finite in FP32, overflows binary16 after ReLU
+    f32 = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    ps, r = _packed(scene, dev, pack_f16=True), _renderer(cam, dev)
+    rgb, _ = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, view=cam["view"], proj=cam["proj"], precision=1)
+    assert r.f32_fallbacks == 1
+    np.testing.assert_allclose(rgb.cpu().numpy(), f32["render"].rgb, atol=IMG_TOL_F32 * 50)
+    scene["W2"] = scene["W2"].copy()
+    scene["W2"][0, 0, 0] = 1.0e6       # not representable in binary16: the packer refuses the fp16 image
+    ps2 = _packed(scene, dev, pack_f16=True)
+    assert ps2.f16_rejected and not ps2.has_f16
 
 
 def test_wave_schedule_does_not_change_results(dev):
