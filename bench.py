@@ -1,0 +1,318 @@
+"""Benchmark of the render hot path: frames/s (and record-MLP evaluations/s) on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A step is one frame of the named workload through the whole path (binning, per-tile sort, record
+waves with the per-primitive MLP, compositing).  `value` is whole-job frames/s with the scene and
+the rays resident in HBM; `e2e` is the same frame through the public host API with the rays
+arriving from pinned host memory and the image returning to it inside the timed region.  At N > 1
+every rank renders its own view of the replicated scene (weak scaling); the scene is generated on
+rank 0 and broadcast once with NCCL.  `--impl reference` times the CPU restatement of the
+reference's algorithm (oracle/) on the host cores over a bounded band of tile rows.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WK = ("W1", "b1", "W2", "b2", "W3", "b3")
+FLOP_PER_RECORD = 6912          # 2*(72*32 + 32*32 + 32*4): algorithmic MLP work of one record
+THRESHOLD = 5e-3                # score threshold of the reference's benchmark tool
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        hot = [s for s in sm if s > 0.5 * (max(sm) if sm else 1)]
+        return dict(sm_mhz=statistics.median(hot) if hot else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_baseline(scene, cam, budget_s, steps=1, warmup=0):
+    """Oracle (CPU restatement of the reference algorithm) on a band of tile rows; frames/s scaled to a frame."""
+    from oracle import oracle as orc
+    W, H = cam["W"], cam["H"]
+    ntx, nty = (W + 7) // 8, (H + 7) // 8
+    q = orc.normalize_rows(scene["quats"])
+    rd = orc.normalize_rows(cam["rays_d"])
+    geom = orc.pack_geometry(scene["positions"], scene["log_scales"], q)
+    weights = [scene[k] for k in WK]
+
+    def frame(rows):
+        r0 = (nty - rows) // 2
+        t0 = time.perf_counter()
+        prims, off = orc.bin_tiles(geom, cam["view"], cam["proj"], W, H, 8, THRESHOLD)
+        sp = orc.sort_tiles(cam["rays_o"], rd, geom, off, prims, W, H, 8)
+        res = orc.render(cam["rays_o"], rd, geom, off, sp, W, H, 8, THRESHOLD, weights, scene["freq"], scene["att"],
+                         precision=1, want_masks=False, tile_range=(r0 * ntx, (r0 + rows) * ntx))
+        return time.perf_counter() - t0, res.evals
+
+    probe_rows = max(1, nty // 24)
+    dt, _ = frame(probe_rows)
+    rows = int(max(1, min(nty, probe_rows * budget_s / max(dt, 1e-6))))
+    times, evals = [], 0
+    for i in range(warmup + steps):
+        dt, ev = frame(rows)
+        if i >= warmup:
+            times.append(dt); evals += ev
+    mean = sum(times) / len(times)
+    frac = rows / nty
+    return dict(value=frac / mean, unit="frames/s", cores=orc.num_threads(), kind="port",
+                sample=f"{rows} of {nty} tile rows ({frac:.3f} of a frame; binning and sort of the whole frame included), "
+                       f"{len(times)} timed pass(es) of {mean:.2f} s, fp16-operand MLP model, OpenMP over tiles",
+                evals_per_s=evals / sum(times), ms_per_step=mean * 1e3)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from mlp_splatting_b200 import synthetic as syn
+    scene, cams, cfg = syn.make_workload(args.workload)
+    per_step = max(2.0, 150.0 / (args.steps + args.warmup + 1))
+    cb = cpu_baseline(scene, cams[0], per_step, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": "frames_per_sec", "value": cb["value"], "unit": "frames/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config(args.workload, cfg, 1),
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "record_mlp_evals_per_sec": cb["evals_per_s"],
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, cfg, n_gpus):
+    return {"workload": name, "primitives": cfg["n"], "width": cfg["W"], "height": cfg["H"], "tile": 8,
+            "tile_capacity": 1536, "threshold": THRESHOLD, "log_scale_mean": cfg["mu"],
+            "mlp": "72-32-32-4 fp16 weights, fp32 accumulate", "views_per_step": n_gpus,
+            "parallelism": f"view-sharded x{n_gpus}, scene replicated", "l2": "256 MB flush between timed steps"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="single_100k_1200x680")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--precision", default="fp16", choices=["fp16", "fp32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from mlp_splatting_b200 import _lib as L
+    from mlp_splatting_b200 import sharding, synthetic as syn
+    from mlp_splatting_b200.engine import FrameRenderer, PackedScene
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the render path has no CPU fallback")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = L.load()
+
+    cfg = dict(syn.WORKLOADS[args.workload])
+    scene_np = None
+    if rank == 0:
+        scene_np = syn.make_scene(cfg["n"], cfg["seed"], mu=cfg["mu"], hidden=cfg.get("hidden", 32))
+    t_b0 = time.perf_counter()
+    scene_t = sharding.broadcast_scene(scene_np, dev, src=0)
+    torch.cuda.synchronize()
+    bcast_s = time.perf_counter() - t_b0
+    prec = L.PRECISION_F16 if args.precision == "fp16" else L.PRECISION_F32
+    ps = PackedScene(*[scene_t[k] for k in ("positions", "log_scales", "quats") + WK], scene_t["freq"], scene_t["att"],
+                     device=dev, pack_f16=(prec == L.PRECISION_F16))
+    # one view per rank, on the circle of radius 3 (weak scaling: per-GPU work is fixed)
+    cam = syn.make_camera(cfg["W"], cfg["H"], azimuth_deg=360.0 * rank / max(world, 1))
+    r = FrameRenderer(cfg["W"], cfg["H"], device=dev, max_records=6_000_000)
+    ro_h = torch.from_numpy(cam["rays_o"]).pin_memory()
+    rd_h = torch.from_numpy(cam["rays_d"]).pin_memory()
+    ro, rd = ro_h.to(dev), rd_h.to(dev)
+    rd_unit = torch.empty_like(rd)
+    L.check(lib.mlpsp_normalize_rows(L.ptr(rd), L.ptr(rd_unit), r.P, 3, None), "normalize")
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    out_h = torch.empty((r.P, 4), dtype=torch.float32).pin_memory()
+
+    def frame(check=False):
+        return r.render(ps, ro, rd_unit, THRESHOLD, view=cam["view"], proj=cam["proj"], precision=prec,
+                        rays_normalized=True, check=check)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # sizing pass (grows scratch if needed), then warm-up
+    frame(check=True)
+    stats = r.last_stats
+    for _ in range(args.warmup):
+        flush.fill_(1); frame()
+    barrier()
+
+    # ---- timed region: K frames, device time per frame by CUDA events, L2 flushed between frames ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    launches0 = lib.mlpsp_kernel_launches(None, 0)
+    barrier()
+    wall0 = time.perf_counter()
+    for a, b in evs:
+        flush.fill_(1)
+        a.record(); frame(); b.record()
+    barrier()
+    wall = time.perf_counter() - wall0
+    launches = lib.mlpsp_kernel_launches(None, 0) - launches0
+    dev_ms = sum(a.elapsed_time(b) for a, b in evs)
+    clocks = sampler.stop() if rank == 0 else None
+    bits = int(r.status.cpu()[0])
+    if bits & ~L.BIT_NUMERIC:
+        raise SystemExit(f"render status bits {bits} during the timed region")
+    t = torch.tensor([dev_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms_max = float(t.item())
+    ms_per_step = dev_ms_max / args.steps
+    fps = world * args.steps / (dev_ms_max / 1e3)
+
+    # ---- per-kernel-class device time (separate pass: event pairs around every launch group) ----
+    lib.mlpsp_timing_enable(1)
+    per_class0 = (C.c_int64 * 8)()
+    lib.mlpsp_kernel_launches(per_class0, 8)
+    tsteps = min(args.steps, 10)
+    for _ in range(tsteps):
+        flush.fill_(1); frame()
+    torch.cuda.synchronize()
+    ms_cls = (C.c_float * 8)()
+    L.check(lib.mlpsp_timing_collect(ms_cls, 8), "timing_collect")
+    lib.mlpsp_timing_enable(0)
+    per_class1 = (C.c_int64 * 8)()
+    lib.mlpsp_kernel_launches(per_class1, 8)
+    classes = {}
+    for i, name in enumerate(L.KERNEL_CLASSES):
+        n_l = (per_class1[i] - per_class0[i]) / tsteps
+        classes[name] = {"ms_per_step": ms_cls[i] / tsteps, "launches_per_step": n_l}
+    pk = peaks()
+    mlp_ms = classes["mlp"]["ms_per_step"]
+    mlp_launch_ms = mlp_ms / max(classes["mlp"]["launches_per_step"], 1)
+    flops_step = stats.records * FLOP_PER_RECORD
+    achieved_tf = flops_step / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0
+    roofline = {"kernel": "k_mlp_tc (per-primitive MLP, tcgen05)", "bound": "tensor", "achieved": achieved_tf,
+                "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved_tf / pk["bf16_tflops"],
+                "peak_source": pk["source"] + " burst", "traffic": None,
+                "flop_per_launch": flops_step / max(classes["mlp"]["launches_per_step"], 1),
+                "avg_launch_ms": mlp_launch_ms, "share_of_step": mlp_ms / max(sum(c["ms_per_step"] for c in classes.values()), 1e-9)}
+
+    # ---- end to end: pinned host rays in, image out, status checked, through the public host API ----
+    def e2e_step():
+        ro.copy_(ro_h, non_blocking=True); rd.copy_(rd_h, non_blocking=True)
+        rgb, alpha = r.render(ps, ro, rd, THRESHOLD, view=cam["view"], proj=cam["proj"], precision=prec, check=True)
+        out_h[:, :3].copy_(rgb, non_blocking=True); out_h[:, 3:].copy_(alpha, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e_t = torch.tensor([time.perf_counter() - e0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e_t, op=dist.ReduceOp.MAX)
+    e2e_fps = world * args.steps / float(e_t.item())
+
+    if rank == 0:
+        line = {
+            "metric": "frames_per_sec", "value": fps, "unit": "frames/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16" if prec == L.PRECISION_F16 else "f32", "data": "synthetic",
+            "config": workload_config(args.workload, cfg, world),
+            "record_mlp_evals_per_sec": stats.records * fps,
+            "records_per_frame": {"evaluated": stats.records, "composited": stats.used, "candidate_pairs": stats.pairs,
+                                  "waves": stats.waves, "max_tile_len": stats.max_tile_len},
+            "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": 2 * r.P * 12, "d2h_bytes_per_step": r.P * 16 + 64},
+            "gpu_launches": int(launches),
+            "kernel_classes": classes,
+            "roofline": roofline,
+            "clocks": clocks,
+            "scene_broadcast_s": bcast_s if world > 1 else 0.0,
+            "wall_ms_per_step": wall * 1e3 / args.steps,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            cb = cpu_baseline(scene_np, cam, budget_s=15.0)
+            line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

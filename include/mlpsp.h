@@ -131,6 +131,17 @@ int mlpsp_pack_weights_f16(const mlpsp_scene* scene, void* w16_out, int32_t* sta
 
 int mlpsp_status_reset(int32_t* status, void* stream);
 
+/* Launch accounting.  Kernel classes: 0 bin, 1 sort, 2 hit pass, 3 per-primitive scan, 4 record fill,
+ * 5 evaluator, 6 compositing, 7 other.  mlpsp_kernel_launches returns the number of kernels this
+ * library has launched in the process (per class in per_class[0..num_classes), optional).
+ * With timing enabled every launch group is bracketed by CUDA events on its stream;
+ * mlpsp_timing_collect waits for them, adds the elapsed milliseconds per class into
+ * ms_per_class[MLPSP_KERNEL_CLASSES] and forgets them.  Not thread-safe; meant for benchmarks. */
+#define MLPSP_KERNEL_CLASSES 8
+int mlpsp_kernel_launches(int64_t* per_class, int32_t num_classes);
+int mlpsp_timing_enable(int32_t on);
+int mlpsp_timing_collect(float* ms_per_class, int32_t num_classes);
+
 /* Scratch size for a frame of this shape. */
 int64_t mlpsp_frame_scratch_bytes(int32_t n, int32_t width, int32_t height, int32_t tile,
                                   int64_t max_pairs, int64_t max_records);

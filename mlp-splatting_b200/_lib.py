@@ -19,6 +19,7 @@ BIT_PAIR_OVERFLOW, BIT_RECORD_OVERFLOW, BIT_NUMERIC, BIT_TIMEOUT = 8, 16, 64, 12
 PRECISION_F32, PRECISION_F16 = 0, 1
 MAX_WAVES = 32
 GEOM_FLOATS = 16
+KERNEL_CLASSES = ("bin", "sort", "hits", "prim_scan", "fill", "mlp", "composite", "other")
 
 _fp = C.c_void_p  # device or host pointers travel as plain addresses
 
@@ -54,6 +55,9 @@ _SIGS = {
     "mlpsp_packed_weight_bytes": (C.c_int64, [C.c_int32, C.c_int32]),
     "mlpsp_pack_weights_f16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
     "mlpsp_status_reset": (C.c_int, [_fp, _fp]),
+    "mlpsp_kernel_launches": (C.c_int, [C.POINTER(C.c_int64), C.c_int32]),
+    "mlpsp_timing_enable": (C.c_int, [C.c_int32]),
+    "mlpsp_timing_collect": (C.c_int, [C.POINTER(C.c_float), C.c_int32]),
     "mlpsp_frame_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
     "mlpsp_bin_tiles": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp]),
     "mlpsp_validate_tile_lists": (C.c_int, [_fp, _fp, C.c_int32, C.c_int64, C.c_int32, C.c_int32, _fp, _fp]),

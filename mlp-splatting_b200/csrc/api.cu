@@ -1,6 +1,7 @@
 // C ABI entry points: argument checks, scratch carving and stage sequencing.
 #include <cmath>
 #include <cstring>
+#include <vector>
 #include "frame.cuh"
 
 namespace mlpsp {
@@ -18,6 +19,33 @@ int cuda_check(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return MLPSP_OK;
   set_error("CUDA error in %s: %s", what, cudaGetErrorString(e));
   return MLPSP_E_CUDA;
+}
+
+// ---- launch accounting and optional device timing per kernel class ----
+static long long g_launches[kNumKernelClasses] = {0};
+static bool g_timing = false;
+struct TimedSpan { cudaEvent_t a, b; int cls; };
+static std::vector<TimedSpan> g_spans;
+static std::vector<cudaEvent_t> g_pool;
+
+static cudaEvent_t take_event() {
+  if (!g_pool.empty()) { cudaEvent_t e = g_pool.back(); g_pool.pop_back(); return e; }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+
+LaunchScope::LaunchScope(KernelClass k, int launches, cudaStream_t s) : slot(-1), st(s) {
+  g_launches[k] += launches;
+  if (g_timing) {
+    TimedSpan sp{take_event(), take_event(), (int)k};
+    cudaEventRecord(sp.a, st);
+    g_spans.push_back(sp);
+    slot = (int)g_spans.size() - 1;
+  }
+}
+LaunchScope::~LaunchScope() {
+  if (slot >= 0) cudaEventRecord(g_spans[slot].b, st);
 }
 
 // validate_tile_candidate_capacity_kernel (np_tile_kernels.cu:4485-4520)
@@ -89,6 +117,36 @@ extern "C" int mlpsp_struct_sizes(int32_t* scene_bytes, int32_t* frame_bytes) {
   return MLPSP_OK;
 }
 
+extern "C" int mlpsp_kernel_launches(int64_t* per_class, int32_t num_classes) {
+  long long total = 0;
+  for (int i = 0; i < kNumKernelClasses; ++i) {
+    total += g_launches[i];
+    if (per_class && i < num_classes) per_class[i] = g_launches[i];
+  }
+  return (int)(total > 2147483647LL ? 2147483647LL : total);
+}
+
+extern "C" int mlpsp_timing_enable(int32_t on) {
+  g_timing = on != 0;
+  return MLPSP_OK;
+}
+
+extern "C" int mlpsp_timing_collect(float* ms_per_class, int32_t num_classes) {
+  MLPSP_REQUIRE(ms_per_class && num_classes >= kNumKernelClasses, MLPSP_E_ARG,
+                "mlpsp_timing_collect: need room for %d classes", (int)kNumKernelClasses);
+  for (int i = 0; i < num_classes; ++i) ms_per_class[i] = 0.f;
+  for (auto& sp : g_spans) {
+    MLPSP_CUDA_OK(cudaEventSynchronize(sp.b));
+    float ms = 0.f;
+    MLPSP_CUDA_OK(cudaEventElapsedTime(&ms, sp.a, sp.b));
+    ms_per_class[sp.cls] += ms;
+    g_pool.push_back(sp.a);
+    g_pool.push_back(sp.b);
+  }
+  g_spans.clear();
+  return MLPSP_OK;
+}
+
 extern "C" int mlpsp_status_reset(int32_t* status, void* stream) {
   MLPSP_REQUIRE(status, MLPSP_E_ARG, "mlpsp_status_reset: null pointer");
   return cuda_check(cudaMemsetAsync(status, 0, 4 * MLPSP_STATUS_WORDS, (cudaStream_t)stream), "status_reset");
@@ -109,6 +167,7 @@ extern "C" int mlpsp_validate_tile_lists(const int32_t* tile_offsets, const int3
   MLPSP_REQUIRE(n >= 0, MLPSP_E_LIMIT, "validate: primitive count is outside the supported int32 range");
   const int64_t work = std::max<int64_t>(num_tiles_, pairs);
   const int blocks = (int)std::min<int64_t>(4096, (work + 255) / 256);
+  LaunchScope scope(kKMisc, 1, (cudaStream_t)stream);
   k_validate_lists<<<blocks, 256, 0, (cudaStream_t)stream>>>(tile_offsets, tile_prims, num_tiles_, pairs,
                                                             tile_capacity, n, status);
   return cuda_check(cudaGetLastError(), "validate");
@@ -220,8 +279,9 @@ extern "C" int mlpsp_mlp_grouped(const mlpsp_scene* sc, int32_t precision, const
   if (n == 0 || num_records == 0) return MLPSP_OK;
   Scratch s = grouped_layout(scratch, num_records, n);
   MLPSP_CUDA_OK(cudaMemsetAsync(s.counters, 0, 4 * kNumCounters, st));
+  { LaunchScope scope(kKMisc, 2, st);
   k_grouped_counts<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, s.prim_cnt);
-  k_grouped_records<<<(unsigned)((num_records + 255) / 256), 256, 0, st>>>(x6, num_records, s.rec_in);
+  k_grouped_records<<<(unsigned)((num_records + 255) / 256), 256, 0, st>>>(x6, num_records, s.rec_in); }
   int rc = launch_prim_scan(s, n, 0, status, st);
   if (rc) return rc;
   if (precision == MLPSP_PRECISION_F16)

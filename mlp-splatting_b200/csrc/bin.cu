@@ -267,6 +267,7 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_cnt, 0, 4 * (size_t)(T + 1), st));
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_fill, 0, 4 * (size_t)T, st));
   const int n = sc->n;
+  LaunchScope scope(kKBin, n > 0 ? 7 : 4, st);
   if (n > 0) k_bin_count<<<(n + 255) / 256, 256, 0, st>>>((const float4*)sc->geom, n, cam, s.rect, s.tile_cnt);
   int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
   if (rc) return rc;
@@ -289,6 +290,7 @@ extern "C" int mlpsp_pack_geometry(const float* positions, const float* log_scal
   MLPSP_REQUIRE(n >= 0 && (n == 0 || (positions && log_scales && quats_unit && geom)), MLPSP_E_ARG,
                 "mlpsp_pack_geometry: null pointer or negative count");
   if (n == 0) return MLPSP_OK;
+  LaunchScope scope(kKMisc, 1, (cudaStream_t)stream);
   k_pack_geometry<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, log_scales, quats_unit, n, (float4*)geom);
   return cuda_check(cudaGetLastError(), "pack_geometry");
 }
@@ -298,6 +300,7 @@ extern "C" int mlpsp_normalize_rows(const float* in, float* out, int64_t rows, i
                 "mlpsp_normalize_rows: dim must be 3 or 4 and pointers non-null");
   if (rows == 0) return MLPSP_OK;
   const unsigned blocks = (unsigned)((rows + 255) / 256);
+  LaunchScope scope(kKMisc, 1, (cudaStream_t)stream);
   if (dim == 3) k_normalize_rows<3><<<blocks, 256, 0, (cudaStream_t)stream>>>(in, out, rows);
   else k_normalize_rows<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(in, out, rows);
   return cuda_check(cudaGetLastError(), "normalize_rows");

@@ -90,6 +90,18 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   return s;
 }
 
+// Kernel classes for the launch counter and the optional per-class device timing.
+enum KernelClass { kKBin = 0, kKSort, kKHits, kKScan, kKFill, kKMlp, kKComposite, kKMisc, kNumKernelClasses };
+
+// RAII marker around the launches of one class: counts them and, when timing is enabled,
+// brackets them with CUDA events on the launching stream.
+struct LaunchScope {
+  LaunchScope(KernelClass k, int launches, cudaStream_t st);
+  ~LaunchScope();
+  int slot;
+  cudaStream_t st;
+};
+
 // last-error text (thread-local) for the negative return codes
 void set_error(const char* fmt, ...);
 int cuda_check(cudaError_t e, const char* what);

@@ -100,6 +100,7 @@ int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = sms * 8;
   int32_t* ctr = const_cast<int32_t*>(counters);
+  LaunchScope scope(kKMlp, 1, st);
   if (H <= 32) {
     k_mlp_f32<32><<<grid, kRowsPerItem, smem, st>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->freq, sc->att,
                                                    F, H, rec_in, prim_off, work, ctr, rec_out, out_mode, status);

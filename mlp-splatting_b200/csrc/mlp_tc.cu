@@ -371,6 +371,7 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   // tensor memory: 512 columns per SM / 64 per CTA = at most 8 resident CTAs; shared memory allows 6
   const int grid = sms * 6;
+  LaunchScope scope(kKMlp, 1, st);
   k_mlp_tc<<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, prim_off, work,
                                            const_cast<int32_t*>(counters), rec_out, out_mode, status);
   return cuda_check(cudaGetLastError(), "mlp_f16");
@@ -391,6 +392,7 @@ extern "C" int mlpsp_pack_weights_f16(const mlpsp_scene* sc, void* w16_out, int3
   MLPSP_REQUIRE(sc->W1 && sc->b1 && sc->W2 && sc->b2 && sc->W3 && sc->b3, MLPSP_E_ARG,
                 "mlpsp_pack_weights_f16: FP32 weights missing");
   if (sc->n == 0) return MLPSP_OK;
+  LaunchScope scope(kKMisc, 1, (cudaStream_t)stream);
   k_pack_weights<<<sc->n, 128, 0, (cudaStream_t)stream>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->n,
                                                          (char*)w16_out, status);
   return cuda_check(cudaGetLastError(), "pack_weights_f16");

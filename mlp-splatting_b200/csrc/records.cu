@@ -243,6 +243,7 @@ __global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict
 int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st) {
   const int nblk = (n + kScanItems - 1) / kScanItems;
   if (nblk == 0) return MLPSP_OK;
+  LaunchScope scope(kKScan, 3, st);
   k_prim_partial<<<nblk, 1024, 0, st>>>(s.prim_cnt, n, s.scan_blk, status);
   k_prim_top<<<1, 1024, 0, st>>>(s.scan_blk, nblk, s.counters, next_list, s.max_work, status);
   k_prim_final<<<nblk, 1024, 0, st>>>(s.prim_cnt, s.prim_cursor, n, s.scan_blk, s.prim_off, s.work, s.max_work, status);
@@ -402,6 +403,7 @@ static const int kDefaultWaves[] = {32, 32, 64, 128, 256, 512, INT_MAX};
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st) {
   const int T = num_tiles(fr->width, fr->height, fr->tile);
   const int ntx = (fr->width + 7) / 8;
+  LaunchScope scope(kKHits, 1, st);
   k_hit_masks_all<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, sc->n, fr->tile_offsets,
                                      fr->sorted_prims, fr->width, fr->height, ntx, fr->threshold,
                                      (uint32_t*)mask_geo, fr->status);
@@ -420,9 +422,12 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   const bool want_t = fr->depth_t != nullptr;
   const bool want_feat = fr->feat != nullptr;
   MLPSP_REQUIRE(!want_feat, MLPSP_E_ARG, "feature compositing is not available in this build");
-  k_init_pixels<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha,
-                                                             fr->depth_t, bg[0], bg[1], bg[2]);
-  k_init_tiles<<<(T + 255) / 256, 256, 0, st>>>(T, s.active[0], s.counters);
+  {
+    LaunchScope scope(kKMisc, 2, st);
+    k_init_pixels<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha,
+                                                               fr->depth_t, bg[0], bg[1], bg[2]);
+    k_init_tiles<<<(T + 255) / 256, 256, 0, st>>>(T, s.active[0], s.counters);
+  }
   if (fr->mask_used) MLPSP_CUDA_OK(cudaMemsetAsync(fr->mask_used, 0, 8 * (size_t)fr->max_pairs, st));
   if (n == 0) return cuda_check(cudaGetLastError(), "render_sorted");
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cnt, 0, 4 * (size_t)n, st));
@@ -437,24 +442,27 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     const int cur = w & 1, nxt = cur ^ 1;
     const int32_t* act = s.active[cur];
     const int32_t* act_n = s.counters + kCtrActive0 + cur;
+    { LaunchScope scope(kKHits, 1, st);
     k_hits<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, fr->sorted_prims,
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.px_state, s.masks32, s.pair_base,
-                              s.prim_cnt, s.counters, fr->max_records, fr->status);
+                              s.prim_cnt, s.counters, fr->max_records, fr->status); }
     int rc = launch_prim_scan(s, n, nxt, fr->status, st);
     if (rc) return rc;
+    { LaunchScope scope(kKFill, 1, st);
     k_fill<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
                               s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr, nullptr, sc->gate_beta,
-                              sc->gate_tau, fr->status);
+                              sc->gate_tau, fr->status); }
     if (fr->precision == MLPSP_PRECISION_F16)
       rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, kOutAlpha, fr->status, st);
     else
       rc = launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, kOutAlpha, fr->status, st);
     if (rc) return rc;
+    { LaunchScope scope(kKComposite, 1, st);
     k_composite<<<T, 64, 0, st>>>(fr->tile_offsets, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
                                   fr->alpha, fr->depth_t, (uint32_t*)fr->mask_used, bg[0], bg[1], bg[2], has_bg,
-                                  s.active[nxt], s.counters + kCtrActive0 + nxt, fr->status);
+                                  s.active[nxt], s.counters + kCtrActive0 + nxt, fr->status); }
     lo = hi;
   }
   return cuda_check(cudaGetLastError(), "render_sorted");

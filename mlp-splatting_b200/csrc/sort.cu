@@ -45,6 +45,7 @@ int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, c
   const int ntx = (fr->width + fr->tile - 1) / fr->tile;
   MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
                 "tile_capacity must be in [1, %d]", kSortCap);
+  LaunchScope scope(kKSort, 1, st);
   k_sort_tiles<256, kSortCap><<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, sc->n,
                                                 fr->tile_offsets, fr->tile_prims, fr->width, fr->height, fr->tile,
                                                 ntx, fr->sorted_prims, keys_out, fr->status);
