@@ -195,6 +195,20 @@ int mlpsp_prepare_groups(const int64_t* offsets, int32_t n, int64_t segment_size
                          int64_t* primitives, int64_t* starts, int64_t max_groups,
                          int64_t* num_groups_host, void* stream);
 
+/* prepare_groups for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Same arguments and results as mlpsp_prepare_groups, but it calls no cudaMalloc/cudaFree:
+ * its work arrays live in a fixed device array inside the library (about 4 MiB on every GPU that loads
+ * the library, until the process exits), which limits it to n <= MLPSP_STATIC_GROUPS_MAX_PRIMITIVES;
+ * larger n is rejected with MLPSP_E_LIMIT.  Meant for hosts whose embedding application owns all device
+ * memory and forbids allocations after start-up, or whose frame loop must avoid the device-wide
+ * synchronisation of cudaMalloc/cudaFree.  The first call on each device looks up the array's device
+ * address, so issue that first call outside any stream capture.  All calls share the array: calls that
+ * overlap on the GPU race on it, so keep them on one stream or otherwise serialised. */
+#define MLPSP_STATIC_GROUPS_MAX_PRIMITIVES 524288
+int mlpsp_prepare_groups_static(const int64_t* offsets, int32_t n, int64_t segment_size, int64_t* group_offsets,
+                                int64_t* primitives, int64_t* starts, int64_t max_groups,
+                                int64_t* num_groups_host, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -70,6 +70,7 @@ _SIGS = {
     "mlpsp_group_records_scratch_bytes": (C.c_int64, [C.c_int64, C.c_int32]),
     "mlpsp_group_records": (C.c_int, [_fp, C.c_int64, C.c_int32, _fp, _fp, _fp, C.c_int64, _fp]),
     "mlpsp_prepare_groups": (C.c_int, [_fp, C.c_int32, C.c_int64, _fp, _fp, _fp, C.c_int64, C.POINTER(C.c_int64), _fp]),
+    "mlpsp_prepare_groups_static": (C.c_int, [_fp, C.c_int32, C.c_int64, _fp, _fp, _fp, C.c_int64, C.POINTER(C.c_int64), _fp]),
 }
 
 EXPORTS = tuple(_SIGS)

@@ -190,3 +190,74 @@ extern "C" int mlpsp_prepare_groups(const int64_t* offsets, int32_t n, int64_t s
   cudaFreeAsync(cnt, st); cudaFreeAsync(goff, st); cudaFreeAsync(blk, st);
   return cuda_check(cudaGetLastError(), "prepare_groups");
 }
+
+// ------------------------------------------------------------------------------------------
+// prepare_groups for callers that must not allocate.
+//
+// mlpsp_prepare_groups above takes its three small work arrays from cudaMallocAsync.  Some hosts of
+// this library cannot do that: a renderer plugin whose embedding engine owns all device memory and
+// forbids driver allocations after start-up, or a frame loop that must not hit the implicit device
+// synchronisation and the latency of cudaMalloc/cudaFree.  For them the same computation runs on a
+// fixed scratch area that is part of the library image: a file-scope __device__ array, present on
+// every GPU that loads the library until the process exits (about 4 MiB).
+//
+// The array's name is only a host-side handle in host code, not a device address, so the device
+// address is looked up once per device with cudaGetSymbolAddress (with that device current) and
+// cached; kernels receive that pointer.  The first call on a device performs this look-up, so make
+// that first call outside any stream capture.  All calls share the one array and it keeps the
+// previous call's contents: the part that must start at zero is cleared on every call, and two
+// calls that overlap on the GPU (different streams or threads) would race on it, so serialise them.
+namespace mlpsp {
+
+constexpr int kStaticGroupsMaxPrims = MLPSP_STATIC_GROUPS_MAX_PRIMITIVES;
+constexpr int64_t kSgCntBytes = (4ll * (kStaticGroupsMaxPrims + 2) + 255) / 256 * 256;
+constexpr int64_t kSgBlkBytes = (4ll * (kStaticGroupsMaxPrims / kScanItems + 4) + 255) / 256 * 256;
+constexpr int64_t kSgBytes = 2 * kSgCntBytes + kSgBlkBytes;
+
+static __device__ __align__(256) unsigned char g_static_groups_scratch[kSgBytes];
+static void* g_static_groups_ptr[64] = {nullptr};   // device address of the array, per device ordinal
+
+static int static_groups_scratch(char** out) {
+  int dev = -1;
+  MLPSP_CUDA_OK(cudaGetDevice(&dev));
+  MLPSP_REQUIRE(dev >= 0 && dev < 64, MLPSP_E_LIMIT, "mlpsp_prepare_groups_static: device ordinal %d beyond 63", dev);
+  if (!g_static_groups_ptr[dev]) {
+    void* p = nullptr;
+    MLPSP_CUDA_OK(cudaGetSymbolAddress(&p, g_static_groups_scratch));
+    MLPSP_REQUIRE(p != nullptr, MLPSP_E_CUDA, "mlpsp_prepare_groups_static: no device address for the scratch array");
+    g_static_groups_ptr[dev] = p;
+  }
+  *out = static_cast<char*>(g_static_groups_ptr[dev]);
+  return MLPSP_OK;
+}
+
+}  // namespace mlpsp
+
+extern "C" int mlpsp_prepare_groups_static(const int64_t* offsets, int32_t n, int64_t segment_size,
+                                           int64_t* group_offsets, int64_t* primitives, int64_t* starts,
+                                           int64_t max_groups, int64_t* num_groups_host, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  MLPSP_REQUIRE(offsets && group_offsets && n >= 0, MLPSP_E_ARG, "mlpsp_prepare_groups_static: null pointer");
+  MLPSP_REQUIRE(segment_size > 0, MLPSP_E_ARG, "segment_size must be a positive integer");
+  MLPSP_REQUIRE(n <= kStaticGroupsMaxPrims, MLPSP_E_LIMIT,
+                "mlpsp_prepare_groups_static: %d primitives exceed the built-in scratch capacity of %d "
+                "(MLPSP_STATIC_GROUPS_MAX_PRIMITIVES); use mlpsp_prepare_groups", n, kStaticGroupsMaxPrims);
+  char* base = nullptr;
+  int rc = static_groups_scratch(&base);
+  if (rc) return rc;
+  int32_t* cnt = reinterpret_cast<int32_t*>(base);
+  int32_t* goff = reinterpret_cast<int32_t*>(base + kSgCntBytes);
+  int32_t* blk = reinterpret_cast<int32_t*>(base + 2 * kSgCntBytes);
+  // the prefix array must read zero where the scan does not write (n == 0) and must not show the
+  // previous call's totals
+  MLPSP_CUDA_OK(cudaMemsetAsync(goff, 0, 4 * ((size_t)n + 2), st));
+  if (n > 0) k_groups_count<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, segment_size, cnt);
+  rc = launch_scan_i32(cnt, n, blk, goff, st);
+  if (rc) return rc;
+  k_groups_fill<<<(n + 256) / 256, 256, 0, st>>>(offsets, n, segment_size, goff, group_offsets, primitives, starts, max_groups);
+  int32_t G = 0;
+  MLPSP_CUDA_OK(cudaMemcpyAsync(&G, goff + n, 4, cudaMemcpyDeviceToHost, st));
+  MLPSP_CUDA_OK(cudaStreamSynchronize(st));
+  if (num_groups_host) *num_groups_host = G;
+  return cuda_check(cudaGetLastError(), "prepare_groups_static");
+}
