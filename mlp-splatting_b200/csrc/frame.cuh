@@ -41,10 +41,12 @@ struct Scratch {
   int32_t* prim_cursor;  // [n]
   int32_t* prim_off;     // [n+1]
   int2* work;            // [max_work] (primitive, first row)
-  RecIn* rec_in;         // [max_records] primitive-major
-  float4* rec_out;       // [max_records] (R,G,B,alpha) at compositing slots
+  RecIn* rec_in;         // [max_records] primitive-major, reused by every wave
+  float4* rec_out;       // [max_records] (R,G,B,alpha) at compositing slots (slots are unique per frame)
   float* rec_t;          // [max_records] t* at compositing slots
   float4* rec_gate;      // [max_records] feature gates at compositing slots
+  float* rec_w;          // [max_records] compositing weight trans*alpha of consumed records
+  uint32_t* used32;      // [2*max_pairs] consumed-record mask halves per pair (when the caller gives none)
   int32_t* active[2];    // [T] each
   int32_t* counters;     // [kNumCounters]
   int64_t max_work;
@@ -83,6 +85,8 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.rec_out = (float4*)take(16 * max_records);
   s.rec_t = (float*)take(4 * max_records);
   s.rec_gate = (float4*)take(16 * max_records);
+  s.rec_w = (float*)take(4 * max_records);
+  s.used32 = (uint32_t*)take(8 * max_pairs);
   s.active[0] = (int32_t*)take(4 * T);
   s.active[1] = (int32_t*)take(4 * T);
   s.counters = (int32_t*)take(4 * kNumCounters);

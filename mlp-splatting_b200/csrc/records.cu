@@ -199,8 +199,7 @@ __global__ void k_prim_top(int32_t* __restrict__ blk, int nblk, int32_t* __restr
     blk[2 * nblk] = R;
     counters[kCtrWork] = G;
     counters[kCtrWorkNext] = 0;
-    counters[kCtrRecords] = 0;
-    counters[kCtrActive0 + next_list] = 0;
+    counters[kCtrActive0 + next_list] = 0;   // kCtrRecords keeps counting: compositing slots are unique per frame
     if (R > 0) {
       atomicAdd((unsigned long long*)(status + MLPSP_ST_RECORDS_LO), (unsigned long long)R);
       atomicMax(status + MLPSP_ST_WAVE_RECORDS, R);
@@ -328,7 +327,7 @@ __global__ void __launch_bounds__(64) k_composite(
     const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out, const float* __restrict__ rec_t,
     float4* __restrict__ px_state, float2* __restrict__ px_depth, float* __restrict__ rgb,
     float* __restrict__ alpha, float* __restrict__ depth_t, uint32_t* __restrict__ mask_used32,
-    float bgr, float bgg, float bgb, int has_bg, int32_t* __restrict__ next_active,
+    float* __restrict__ rec_w, float bgr, float bgg, float bgb, int has_bg, int32_t* __restrict__ next_active,
     int32_t* __restrict__ next_count, int32_t* __restrict__ status) {
   __shared__ int s_live[2];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
@@ -366,6 +365,7 @@ __global__ void __launch_bounds__(64) k_composite(
         const float w = st.w * r.w;
         st.x = fmaf(w, r.x, st.x); st.y = fmaf(w, r.y, st.y); st.z = fmaf(w, r.z, st.z);
         if (depth_t) { dp.x = fmaf(w, rec_t[slot], dp.x); dp.y += w; }
+        if (rec_w) rec_w[slot] = w;
         st.w *= (1.f - r.w);
         act = st.w >= MLPSP_TERM;
       }
@@ -397,6 +397,83 @@ __global__ void __launch_bounds__(64) k_composite(
   if (threadIdx.x == 0 && (s_live[0] | s_live[1]) && whi < len) next_active[atomicAdd(next_count, 1)] = tile;
 }
 
+// ------------------------------------------------------------------- feature compositing ----
+// out_feat[pix, :] = sum over the pixel's composited records of w * mix(p, gates)  with
+//   S = 4: mix = sum_s g_s * attr[p, s, :]      S = 5: mix = attr[p, 0, :] + sum_s g_s * attr[p, 1+s, :]
+//   S = 1: mix = attr[p, 0, :]                                     (np_tile_kernels.cu:6036-6075)
+// One CTA per tile after the last wave.  The 64 x C accumulator tile lives in shared memory; for
+// every pair that composited at least one record, the consumed pixels and their coefficients
+// w * g_s are compacted into shared memory and every thread adds its channels' contribution.
+constexpr int kFeatThreads = 256;
+
+__global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    const uint32_t* __restrict__ used32, const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base,
+    const float* __restrict__ rec_w, const float4* __restrict__ rec_gate, const float* __restrict__ feat_attr,
+    int S, int C, float* __restrict__ out_feat, const int32_t* __restrict__ status) {
+  extern __shared__ float s_acc[];                 // [64][C]
+  __shared__ float s_cw[64][5];                    // per consumed pixel: base weight + 4 gated weights
+  __shared__ int s_px[64];
+  __shared__ int s_n;
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int tile = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < 64 * C; i += kFeatThreads) s_acc[i] = 0.f;
+  const int s = tile_offsets[tile], e = tile_offsets[tile + 1];
+  __syncthreads();
+  for (int i = s; i < e; ++i) {
+    const uint32_t u0 = used32[2 * (size_t)i], u1 = used32[2 * (size_t)i + 1];
+    if ((u0 | u1) == 0u) continue;                 // uniform across the CTA
+    if (warp < 2) {
+      const uint32_t mine = warp ? u1 : u0;
+      const uint32_t m0 = masks32[2 * (size_t)i], m1 = masks32[2 * (size_t)i + 1];
+      const uint32_t hit = warp ? m1 : m0;
+      const bool take = (mine >> lane) & 1u;
+      const int pos = (warp ? __popc(u0) : 0) + __popc(mine & ((1u << lane) - 1u));
+      if (take) {
+        const uint32_t slot = pair_base[i] + (warp ? __popc(m0) : 0) + __popc(hit & ((1u << lane) - 1u));
+        const float w = rec_w[slot];
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (S > 1) g = rec_gate[slot];
+        s_px[pos] = warp * 32 + lane;
+        s_cw[pos][0] = w; s_cw[pos][1] = w * g.x; s_cw[pos][2] = w * g.y; s_cw[pos][3] = w * g.z; s_cw[pos][4] = w * g.w;
+      }
+      if (tid == 0) s_n = __popc(u0) + __popc(u1);
+    }
+    __syncthreads();
+    const int n = s_n;
+    const float* a = feat_attr + (size_t)sorted_prims[i] * S * C;
+    for (int c = tid; c < C; c += kFeatThreads) {
+      if (S == 4) {
+        const float a0 = __ldg(a + c), a1 = __ldg(a + C + c), a2 = __ldg(a + 2 * C + c), a3 = __ldg(a + 3 * C + c);
+        for (int j = 0; j < n; ++j) {
+          // w * (g0 a0 + g1 a1 + g2 a2 + g3 a3), gates folded into the weights
+          float v = s_cw[j][1] * a0;
+          v = fmaf(s_cw[j][2], a1, v); v = fmaf(s_cw[j][3], a2, v); v = fmaf(s_cw[j][4], a3, v);
+          s_acc[s_px[j] * C + c] += v;
+        }
+      } else if (S == 5) {
+        const float b = __ldg(a + c), a0 = __ldg(a + C + c), a1 = __ldg(a + 2 * C + c), a2 = __ldg(a + 3 * C + c),
+                    a3 = __ldg(a + 4 * C + c);
+        for (int j = 0; j < n; ++j) {
+          float v = s_cw[j][0] * b;
+          v = fmaf(s_cw[j][1], a0, v); v = fmaf(s_cw[j][2], a1, v); v = fmaf(s_cw[j][3], a2, v); v = fmaf(s_cw[j][4], a3, v);
+          s_acc[s_px[j] * C + c] += v;
+        }
+      } else {
+        const float b = __ldg(a + c);
+        for (int j = 0; j < n; ++j) s_acc[s_px[j] * C + c] = fmaf(s_cw[j][0], b, s_acc[s_px[j] * C + c]);
+      }
+    }
+    __syncthreads();
+  }
+  for (int k = warp; k < 64; k += kFeatThreads / 32) {
+    const TilePix tp = tile_pixel(tile, k, ntx, W, H);
+    if (!tp.valid) continue;
+    for (int c = lane; c < C; c += 32) out_feat[(size_t)tp.pix * C + c] = s_acc[k * C + c];
+  }
+}
+
 // ------------------------------------------------------------------------------ driver ----
 static const int kDefaultWaves[] = {32, 32, 64, 128, 256, 512, INT_MAX};
 
@@ -421,15 +498,24 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   if (has_bg) { bg[0] = fr->bg_color[0]; bg[1] = fr->bg_color[1]; bg[2] = fr->bg_color[2]; }
   const bool want_t = fr->depth_t != nullptr;
   const bool want_feat = fr->feat != nullptr;
-  MLPSP_REQUIRE(!want_feat, MLPSP_E_ARG, "feature compositing is not available in this build");
+  if (want_feat) {
+    MLPSP_REQUIRE(sc->feat_attr && sc->feat_dim > 0 && sc->feat_dim <= 512, MLPSP_E_ARG,
+                  "feature rendering needs feat_attr with 1..512 channels");
+    MLPSP_REQUIRE(sc->feat_slots == 1 || sc->feat_slots == 4 || sc->feat_slots == 5, MLPSP_E_ARG,
+                  "feature slots must be 1, 4 or 5");
+  }
+  uint32_t* used32 = fr->mask_used ? (uint32_t*)fr->mask_used : (want_feat ? s.used32 : nullptr);
   {
     LaunchScope scope(kKMisc, 2, st);
     k_init_pixels<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha,
                                                                fr->depth_t, bg[0], bg[1], bg[2]);
     k_init_tiles<<<(T + 255) / 256, 256, 0, st>>>(T, s.active[0], s.counters);
   }
-  if (fr->mask_used) MLPSP_CUDA_OK(cudaMemsetAsync(fr->mask_used, 0, 8 * (size_t)fr->max_pairs, st));
-  if (n == 0) return cuda_check(cudaGetLastError(), "render_sorted");
+  if (used32) MLPSP_CUDA_OK(cudaMemsetAsync(used32, 0, 8 * (size_t)fr->max_pairs, st));
+  if (n == 0) {
+    if (want_feat) MLPSP_CUDA_OK(cudaMemsetAsync(fr->feat, 0, 4 * (size_t)P * sc->feat_dim, st));
+    return cuda_check(cudaGetLastError(), "render_sorted");
+  }
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cnt, 0, 4 * (size_t)n, st));
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cursor, 0, 4 * (size_t)n, st));
   const int nw = fr->num_waves > 0 ? fr->num_waves : (int)(sizeof(kDefaultWaves) / sizeof(int));
@@ -451,7 +537,8 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     { LaunchScope scope(kKFill, 1, st);
     k_fill<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
-                              s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr, nullptr, sc->gate_beta,
+                              s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr,
+                              (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
                               sc->gate_tau, fr->status); }
     if (fr->precision == MLPSP_PRECISION_F16)
       rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, kOutAlpha, fr->status, st);
@@ -461,9 +548,21 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     { LaunchScope scope(kKComposite, 1, st);
     k_composite<<<T, 64, 0, st>>>(fr->tile_offsets, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
-                                  fr->alpha, fr->depth_t, (uint32_t*)fr->mask_used, bg[0], bg[1], bg[2], has_bg,
+                                  fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr, bg[0], bg[1], bg[2], has_bg,
                                   s.active[nxt], s.counters + kCtrActive0 + nxt, fr->status); }
     lo = hi;
+  }
+  if (want_feat) {
+    static bool attr_set = false;
+    const size_t smem = sizeof(float) * 64 * (size_t)sc->feat_dim;
+    if (!attr_set) {
+      MLPSP_CUDA_OK(cudaFuncSetAttribute(k_feature_composite, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 512 * 4));
+      attr_set = true;
+    }
+    LaunchScope scope(kKComposite, 1, st);
+    k_feature_composite<<<T, kFeatThreads, smem, st>>>(fr->tile_offsets, fr->sorted_prims, W, H, ntx, used32, s.masks32,
+                                                      s.pair_base, s.rec_w, s.rec_gate, sc->feat_attr, sc->feat_slots,
+                                                      sc->feat_dim, fr->feat, fr->status);
   }
   return cuda_check(cudaGetLastError(), "render_sorted");
 }

@@ -193,7 +193,7 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         return self._renderers[key]
 
     def _render(self, ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix, culled_prim_indices,
-                tile_offsets, want_depth, path_name):
+                tile_offsets, want_depth, path_name, want_feat=False):
         if self.image_size is None:
             raise ValueError("image_size must be set on NeuralPrimitiveSceneTileCUDA before calling forward.")
         W, H = self.image_size
@@ -227,7 +227,7 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         prec = L.PRECISION_F16 if (self.precision == "fp16" and scene.has_f16) else L.PRECISION_F32
         rgb, alpha = r.render(scene, ray_o.detach().float().contiguous(), ray_d.detach().float().contiguous(),
                               float(score_threshold), view=view, proj=proj, precision=prec, bg=bg,
-                              want_depth=want_depth, tile_lists=lists, path_name=path_name)
+                              want_depth=want_depth, tile_lists=lists, path_name=path_name, want_feat=want_feat)
         return r, rgb, alpha
 
     # ----------------------------------------------------------------------------- public ----
@@ -241,7 +241,10 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         if return_feature and self.feat_attr is None:
             raise RuntimeError("return_feature=True requested but feat_attr is not initialized.")
         if return_feature:
-            raise RuntimeError("the fused feature map is not available in this build yet")
+            r, rgb, _alpha = self._render(ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix,
+                                          culled_prim_indices, tile_offsets, False,
+                                          "render_tiles_forward_tilecenter_with_feat", want_feat=True)
+            return rgb.clone(), r.feat.clone()
         _r, rgb, _alpha = self._render(ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix,
                                        culled_prim_indices, tile_offsets, False, "render_tiles_forward_tilecenter")
         return rgb.clone()
@@ -267,4 +270,13 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
                            culled_prim_indices=None, tile_offsets=None):
         if self.feat_attr is None:
             raise RuntimeError("Feature rendering requested but feature_dim_low == 0.")
-        raise RuntimeError("the fused feature map is not available in this build yet")
+        if self.image_size is None:
+            raise ValueError("image_size must be set before calling render_feature_map.")
+        W, H = self.image_size
+        if ray_o.shape[0] != W * H:
+            raise ValueError("render_feature_map requires full-frame rays (B == W*H).")
+        _rgb, feat = self.forward(ray_o=ray_o, ray_d=ray_d, score_threshold=score_threshold, bg_color=None,
+                                  view_matrix=view_matrix, proj_matrix=proj_matrix,
+                                  culled_prim_indices=culled_prim_indices, tile_offsets=tile_offsets,
+                                  return_feature=True)
+        return feat

@@ -141,10 +141,14 @@ def raise_for_status(bits: int, max_len: int, capacity: int, path_name: str):
 
 
 class FrameRenderer:
-    """Owns the scratch and output buffers for frames of one shape on one GPU."""
+    """Owns the scratch and output buffers for frames of one shape on one GPU.
+
+    max_records is the number of MLP evaluations one frame may perform (compositing slots are unique
+    per frame); the scratch grows and the frame is rendered again when a frame needs more.
+    """
 
     def __init__(self, width, height, device="cuda", tile_capacity=TILE_CAPACITY, max_pairs=None,
-                 max_records=4_000_000):
+                 max_records=16_000_000):
         self.lib = L.load()
         self.device = torch.device(device)
         self.W, self.H = int(width), int(height)
@@ -161,6 +165,7 @@ class FrameRenderer:
         self.alpha = torch.empty((self.P, 1), device=d, dtype=torch.float32)
         self.depth_t = None
         self.mask_used = None
+        self.feat = None
         self.rays_d_unit = torch.empty((self.P, 3), device=d, dtype=torch.float32)
         self.status = torch.zeros(L.STATUS_WORDS, device=d, dtype=torch.int32)
         self.status_host = torch.zeros(L.STATUS_WORDS, dtype=torch.int32).pin_memory()
@@ -185,7 +190,7 @@ class FrameRenderer:
         return self.scratch
 
     def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
-               want_mask_used, waves) -> L.Frame:
+               want_mask_used, waves, want_feat=False) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
         f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
@@ -201,6 +206,12 @@ class FrameRenderer:
             if self.depth_t is None:
                 self.depth_t = torch.empty((self.P, 1), device=self.device, dtype=torch.float32)
             f.depth_t = L.ptr(self.depth_t)
+        if want_feat:
+            if scene.feat_attr is None:
+                raise RuntimeError("feature rendering requested but the scene has no feat_attr")
+            if self.feat is None or self.feat.shape[1] != scene.feat_dim:
+                self.feat = torch.empty((self.P, scene.feat_dim), device=self.device, dtype=torch.float32)
+            f.feat = L.ptr(self.feat)
         if want_mask_used:
             if self.mask_used is None:
                 self.mask_used = torch.zeros(max(self.max_pairs, 1), device=self.device, dtype=torch.int64)
@@ -241,14 +252,14 @@ class FrameRenderer:
             self.mask_used = None
             return True
         if bits & L.BIT_RECORD_OVERFLOW:
-            self.max_records = int(max(stats.wave_records, self.max_records) * 1.25) + 4096
+            self.max_records = int(max(stats.wave_records, self.max_records) * 2) + 4096
             return True
         return False
 
     # -- stages -------------------------------------------------------------------------------
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
-               rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter"):
+               rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False):
         """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling)."""
         lib, d = self.lib, self.device
         if precision is None:
@@ -260,7 +271,7 @@ class FrameRenderer:
             else:
                 L.check(lib.mlpsp_normalize_rows(L.ptr(rays_d), L.ptr(self.rays_d_unit), self.P, 3, st), "mlpsp_normalize_rows")
                 rd = self.rays_d_unit
-            for _attempt in range(4):
+            for _attempt in range(8):
                 L.check(lib.mlpsp_status_reset(L.ptr(self.status), st), "mlpsp_status_reset")
                 if tile_lists is not None:
                     prims, offs = tile_lists
@@ -275,7 +286,8 @@ class FrameRenderer:
                     L.check(lib.mlpsp_validate_tile_lists(L.ptr(self.tile_offsets), L.ptr(self.tile_prims), self.T, m,
                                                           self.capacity, scene.n, L.ptr(self.status), st),
                             "mlpsp_validate_tile_lists")
-                f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves)
+                f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves,
+                                want_feat=want_feat)
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")
                 else:
@@ -296,7 +308,7 @@ class FrameRenderer:
                     precision = L.PRECISION_F32
                     continue
                 return self.rgb, self.alpha
-            raise RenderError(f"{path_name}: scratch kept overflowing after 4 attempts")
+            raise RenderError(f"{path_name}: scratch kept overflowing after 8 attempts")
 
     def bin(self, scene: PackedScene, view, proj, threshold, check=True):
         """Binning only: returns (culled_prim_indices[M] int32, tile_offsets[T+1] int32) views."""
@@ -333,3 +345,68 @@ class FrameRenderer:
             out = torch.zeros(max(pairs, 1), device=d, dtype=torch.int64)
             L.check(lib.mlpsp_hit_masks(C.byref(scene.c), C.byref(f), L.ptr(out), st), "mlpsp_hit_masks")
             return out[:pairs]
+
+
+class FramePipeline:
+    """Several frames in flight on one GPU: per slot a stream, a FrameRenderer and device ray buffers.
+
+    submit() enqueues host->device ray copies, the frame and the device->host image copy on the
+    slot's stream and returns at once; wait() synchronises that stream and raises on a bad status.
+    Host arrays should be pinned so the copies overlap the previous frames' kernels.
+    """
+
+    def __init__(self, scene: PackedScene, width, height, depth=3, **renderer_kw):
+        self.scene = scene
+        d = scene.device
+        self.slots = []
+        for _ in range(int(depth)):
+            r = FrameRenderer(width, height, device=d, **renderer_kw)
+            self.slots.append(dict(r=r, stream=torch.cuda.Stream(device=d), busy=False,
+                                   ro=torch.empty((r.P, 3), device=d), rd=torch.empty((r.P, 3), device=d),
+                                   kw=None))
+        self.next_slot = 0
+
+    def submit(self, rays_o_host, rays_d_host, threshold, view, proj, out_rgb_host=None, out_alpha_host=None,
+               precision=None, bg=None):
+        i = self.next_slot
+        s = self.slots[i]
+        if s["busy"]:
+            self.wait(i)
+        self.next_slot = (i + 1) % len(self.slots)
+        r = s["r"]
+        with torch.cuda.stream(s["stream"]):
+            s["ro"].copy_(rays_o_host, non_blocking=True)
+            s["rd"].copy_(rays_d_host, non_blocking=True)
+            kw = dict(view=view, proj=proj, precision=precision, bg=bg)
+            rgb, alpha = r.render(self.scene, s["ro"], s["rd"], threshold, check=False, **kw)
+            if out_rgb_host is not None:
+                out_rgb_host.copy_(rgb, non_blocking=True)
+            if out_alpha_host is not None:
+                out_alpha_host.copy_(alpha, non_blocking=True)
+            r.status_host.copy_(r.status, non_blocking=True)
+        s["busy"], s["kw"] = True, (threshold, kw, out_rgb_host, out_alpha_host)
+        return i
+
+    def wait(self, i):
+        s = self.slots[i]
+        if not s["busy"]:
+            return
+        r = s["r"]
+        s["stream"].synchronize()
+        s["busy"] = False
+        bits = int(r.status_host[L.ST_BITS])
+        if bits == 0:
+            return
+        # rare path: overflow / error / fp16 overflow -> redo this frame synchronously with full checks
+        threshold, kw, out_rgb, out_alpha = s["kw"]
+        with torch.cuda.stream(s["stream"]):
+            rgb, alpha = r.render(self.scene, s["ro"], s["rd"], threshold, check=True, **kw)
+            if out_rgb is not None:
+                out_rgb.copy_(rgb, non_blocking=True)
+            if out_alpha is not None:
+                out_alpha.copy_(alpha, non_blocking=True)
+        s["stream"].synchronize()
+
+    def drain(self):
+        for i in range(len(self.slots)):
+            self.wait(i)

@@ -192,6 +192,25 @@ def test_fp16_overflow_falls_back_to_fp32_frame(dev):
     assert ps2.f16_rejected and not ps2.has_f16
 
 
+@pytest.mark.parametrize("slots,C", [(4, 512), (5, 96), (1, 40), (4, 33)])
+def test_feature_map_matches_oracle(dev, slots, C):
+    """Gated attribute compositing (np_tile_kernels.cu:97-124, 6036-6075): slots 1/4/5, C up to 512."""
+    from mlp_splatting_b200 import synthetic as syn
+    scene, cam = small_case(**CASES["ragged"])
+    rng = np.random.default_rng(C)
+    fa = rng.normal(0, 0.2, (scene["positions"].shape[0], slots, C)).astype(np.float32)
+    scene = dict(scene, feat_attr=fa if slots > 1 else fa[:, 0, :])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, feat=True, want_masks=False)
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    rgb, _alpha = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, view=cam["view"], proj=cam["proj"],
+                           precision=0, want_feat=True)
+    np.testing.assert_allclose(rgb.cpu().numpy(), f["render"].rgb, atol=IMG_TOL_F32)
+    got = r.feat.cpu().numpy()
+    assert got.shape == (cam["W"] * cam["H"], C)
+    np.testing.assert_allclose(got, f["render"].feat, rtol=0, atol=2e-5)
+    assert np.abs(f["render"].feat).max() > 0.05
+
+
 def test_wave_schedule_does_not_change_results(dev):
     scene, cam = small_case(**CASES["dense"])
     ps, r = _packed(scene, dev), _renderer(cam, dev)
