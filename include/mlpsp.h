@@ -108,6 +108,8 @@ typedef struct mlpsp_frame {
   int32_t* status;        /* [MLPSP_STATUS_WORDS] */
   int32_t num_waves;      /* 0 = library default schedule */
   int32_t wave_len[MLPSP_MAX_WAVES]; /* candidates per tile processed by wave k */
+  int32_t keep_records;   /* 1 = keep what mlpsp_export_records needs (ReLU masks, logits, transmittance) */
+  int32_t reserved1;
 } mlpsp_frame;
 
 const char* mlpsp_last_error(void);
@@ -173,6 +175,19 @@ int mlpsp_render_sorted(const mlpsp_scene* scene, const mlpsp_frame* frame, void
 /* bin + sort + render_sorted: what NeuralPrimitiveSceneTileCUDA.forward does per frame
  * (cumodel.py:951-1160). */
 int mlpsp_render_frame(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
+
+/* Pixel-major records of the frame just rendered with frame->keep_records = 1 on the same scratch: the
+ * 8-tensor schema of render_tiles_training_records (np_tile_kernels.cu:3138-3154, 6897-6986;
+ * training_wmma.cuh:223-256).  Records of a pixel are in compositing order and hold only the hits that
+ * were composited.  offsets[W*H+1] int64 is always written and *total_host receives the record count
+ * (the call synchronises).  ids[R] int32, x6[R,6], raw[R,8] = (R,G,B,sigma_raw,trans_before,alpha,decay,
+ * sigma_logit), relu_masks[R,2] int32, gates[R,4] are written when non-NULL and max_out >= R.
+ * max_hits: per-pixel record capacity (512 in the reference build); *worst_host receives the largest
+ * per-pixel count, negated when a pixel reached the capacity while still live (the reference's
+ * "hit capacity" error). */
+int mlpsp_export_records(const mlpsp_scene* scene, const mlpsp_frame* frame, int64_t* offsets, int32_t* ids,
+                         float* x6, float* raw, int32_t* relu_masks, float* gates, int64_t max_out,
+                         int32_t max_hits, int64_t* total_host, int32_t* worst_host, void* stream);
 
 /* Grouped evaluator on explicit records (the forward counterpart of primitive_gemm.py's grouped
  * VJP): records are primitive-major, offsets[n+1] int64 as produced by group_records

@@ -43,6 +43,7 @@ class Frame(C.Structure):
         ("rgb", _fp), ("alpha", _fp), ("depth_t", _fp), ("feat", _fp), ("mask_used", _fp), ("bg_color", _fp),
         ("scratch", _fp), ("scratch_bytes", C.c_int64), ("max_records", C.c_int64),
         ("status", _fp), ("num_waves", C.c_int32), ("wave_len", C.c_int32 * MAX_WAVES),
+        ("keep_records", C.c_int32), ("reserved1", C.c_int32),
     ]
 
 
@@ -65,6 +66,8 @@ _SIGS = {
     "mlpsp_hit_masks": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp, _fp]),
     "mlpsp_render_sorted": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp]),
     "mlpsp_render_frame": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp]),
+    "mlpsp_export_records": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64,
+                                       C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32), _fp]),
     "mlpsp_mlp_grouped_scratch_bytes": (C.c_int64, [C.c_int64, C.c_int32]),
     "mlpsp_mlp_grouped": (C.c_int, [C.POINTER(Scene), C.c_int32, _fp, _fp, C.c_int64, _fp, _fp, C.c_int64, _fp, _fp]),
     "mlpsp_group_records_scratch_bytes": (C.c_int64, [C.c_int64, C.c_int32]),

@@ -222,6 +222,20 @@ extern "C" int mlpsp_render_frame(const mlpsp_scene* sc, const mlpsp_frame* fr, 
   return render_sorted_checked(sc, fr, s, st);
 }
 
+extern "C" int mlpsp_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, int64_t* offsets, int32_t* ids,
+                                    float* x6, float* raw, int32_t* relu_masks, float* gates, int64_t max_out,
+                                    int32_t max_hits, int64_t* total_host, int32_t* worst_host, void* stream) {
+  int rc = check_frame_common(sc, fr, "mlpsp_export_records");
+  if (rc) return rc;
+  MLPSP_REQUIRE(fr->keep_records == 1, MLPSP_E_ARG, "mlpsp_export_records: the frame was not rendered with keep_records = 1");
+  MLPSP_REQUIRE(offsets && fr->rays_o && fr->rays_d, MLPSP_E_ARG, "mlpsp_export_records: offsets or rays missing");
+  Scratch s;
+  rc = get_scratch(sc, fr, s, "mlpsp_export_records");
+  if (rc) return rc;
+  return launch_export_records(sc, fr, s, offsets, ids, x6, raw, relu_masks, gates, max_out, max_hits, total_host,
+                               worst_host, (cudaStream_t)stream);
+}
+
 // ------------------------------------------------------------ grouped evaluator on records ----
 namespace mlpsp {
 
@@ -285,7 +299,7 @@ extern "C" int mlpsp_mlp_grouped(const mlpsp_scene* sc, int32_t precision, const
   int rc = launch_prim_scan(s, n, 0, status, st);
   if (rc) return rc;
   if (precision == MLPSP_PRECISION_F16)
-    return launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, kOutSigmaRaw, status, st);
+    return launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, nullptr, kOutSigmaRaw, status, st);
   MLPSP_REQUIRE(precision == MLPSP_PRECISION_F32, MLPSP_E_ARG, "mlpsp_mlp_grouped: unknown precision %d", precision);
-  return launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, kOutSigmaRaw, status, st);
+  return launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, nullptr, kOutSigmaRaw, status, st);
 }

@@ -46,6 +46,10 @@ struct Scratch {
   float* rec_t;          // [max_records] t* at compositing slots
   float4* rec_gate;      // [max_records] feature gates at compositing slots
   float* rec_w;          // [max_records] compositing weight trans*alpha of consumed records
+  float* rec_tr;         // [max_records] transmittance before the record (record export)
+  float4* rec_ext;       // [max_records] (sigma_raw, sigma_logit, relu mask 1, relu mask 2) (record export)
+  int32_t* px_cnt;       // [P+2] per-pixel record counts (record export)
+  int32_t* px_off;       // [P+2] their exclusive prefix
   uint32_t* used32;      // [2*max_pairs] consumed-record mask halves per pair (when the caller gives none)
   int32_t* active[2];    // [T] each
   int32_t* counters;     // [kNumCounters]
@@ -70,7 +74,7 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.tile_cnt = (int32_t*)take(4 * (T + 1));
   s.tile_fill = (int32_t*)take(4 * T);
   s.rect = (uint2*)take(8 * (int64_t)n);
-  const int64_t nblk = (std::max<int64_t>(n, T) + kScanItems - 1) / kScanItems + 2;
+  const int64_t nblk = (std::max<int64_t>(std::max<int64_t>(n, T), P + 1) + kScanItems - 1) / kScanItems + 2;
   s.scan_blk = (int32_t*)take(4 * 2 * nblk);
   s.px_state = (float4*)take(16 * P);
   s.px_depth = (float2*)take(8 * P);
@@ -86,6 +90,10 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.rec_t = (float*)take(4 * max_records);
   s.rec_gate = (float4*)take(16 * max_records);
   s.rec_w = (float*)take(4 * max_records);
+  s.rec_tr = (float*)take(4 * max_records);
+  s.rec_ext = (float4*)take(16 * max_records);
+  s.px_cnt = (int32_t*)take(4 * (P + 2));
+  s.px_off = (int32_t*)take(4 * (P + 2));
   s.used32 = (uint32_t*)take(8 * max_pairs);
   s.active[0] = (int32_t*)take(4 * T);
   s.active[1] = (int32_t*)take(4 * T);
@@ -126,10 +134,17 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
 int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st);
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st);
 int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
+// rec_ext (optional): per record (sigma_raw, sigma_logit, layer-1 ReLU bitmask, layer-2 ReLU bitmask)
 int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
-                   const int32_t* counters, float4* rec_out, int out_mode, int32_t* status, cudaStream_t st);
+                   const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
+                   cudaStream_t st);
 int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
-                   const int32_t* counters, float4* rec_out, int out_mode, int32_t* status, cudaStream_t st);
+                   const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
+                   cudaStream_t st);
+int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cudaStream_t st);
+int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, int64_t* offsets, int32_t* ids,
+                          float* x6, float* raw, int32_t* relu_masks, float* gates, int64_t max_out, int32_t max_hits,
+                          int64_t* total_host, int32_t* worst_host, cudaStream_t st);
 
 // evaluator output modes
 constexpr int kOutAlpha = 0;     // (R,G,B, 1-exp(-softplus(o3)*decay)) scattered to rec.slot

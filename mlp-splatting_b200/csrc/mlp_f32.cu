@@ -14,7 +14,7 @@ __global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32(
     const float* __restrict__ b2, const float* __restrict__ W3, const float* __restrict__ b3,
     const float* __restrict__ freq, const float* __restrict__ att, int F, int H,
     const RecIn* __restrict__ rec_in, const int32_t* __restrict__ prim_off, const int2* __restrict__ work,
-    int32_t* __restrict__ counters, float4* __restrict__ rec_out, int out_mode,
+    int32_t* __restrict__ counters, float4* __restrict__ rec_out, float4* __restrict__ rec_ext, int out_mode,
     const int32_t* __restrict__ status) {
   extern __shared__ float sW[];
   __shared__ int s_item;
@@ -65,13 +65,18 @@ __global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32(
           }
         }
       }
+      uint32_t m1 = 0u, m2 = 0u;
 #pragma unroll
-      for (int h = 0; h < HMAX; ++h) h1[h] = fmaxf(h1[h], 0.f);
+      for (int h = 0; h < HMAX; ++h) {
+        if (h < 32 && h1[h] > 0.f) m1 |= 1u << h;
+        h1[h] = fmaxf(h1[h], 0.f);
+      }
       float o0 = sb3[0], o1 = sb3[1], o2 = sb3[2], o3 = sb3[3];
       for (int q = 0; q < H; ++q) {
         float a = sb2[q];
 #pragma unroll
         for (int h = 0; h < HMAX; ++h) if (h < H) a = fmaf(sW2[q * H + h], h1[h], a);
+        if (q < 32 && a > 0.f) m2 |= 1u << q;
         a = fmaxf(a, 0.f);
         // layer 3 accumulates over ascending hidden index, which is this loop's order
         o0 = fmaf(sW3[0 * H + q], a, o0); o1 = fmaf(sW3[1 * H + q], a, o1);
@@ -82,13 +87,15 @@ __global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32(
       out.x = sigmoid_fast(o0); out.y = sigmoid_fast(o1); out.z = sigmoid_fast(o2);
       out.w = (out_mode == kOutAlpha) ? (1.f - __expf(-(sigma_raw * r.decay))) : sigma_raw;
       rec_out[r.slot] = out;
+      if (rec_ext) rec_ext[r.slot] = make_float4(sigma_raw, o3, __uint_as_float(m1), __uint_as_float(m2));
     }
     __syncthreads();
   }
 }
 
 int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
-                   const int32_t* counters, float4* rec_out, int out_mode, int32_t* status, cudaStream_t st) {
+                   const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
+                   cudaStream_t st) {
   const int H = sc->hidden, F = sc->num_freq;
   MLPSP_REQUIRE(H >= 1 && H <= 64 && F >= 1 && F <= 8, MLPSP_E_LIMIT, "FP32 evaluator needs 1<=H<=64, 1<=F<=8");
   MLPSP_REQUIRE(sc->W1 && sc->b1 && sc->W2 && sc->b2 && sc->W3 && sc->b3 && sc->freq && sc->att, MLPSP_E_ARG,
@@ -103,10 +110,10 @@ int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   LaunchScope scope(kKMlp, 1, st);
   if (H <= 32) {
     k_mlp_f32<32><<<grid, kRowsPerItem, smem, st>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->freq, sc->att,
-                                                   F, H, rec_in, prim_off, work, ctr, rec_out, out_mode, status);
+                                                   F, H, rec_in, prim_off, work, ctr, rec_out, rec_ext, out_mode, status);
   } else {
     k_mlp_f32<64><<<grid, kRowsPerItem, smem, st>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->freq, sc->att,
-                                                   F, H, rec_in, prim_off, work, ctr, rec_out, out_mode, status);
+                                                   F, H, rec_in, prim_off, work, ctr, rec_out, rec_ext, out_mode, status);
   }
   return cuda_check(cudaGetLastError(), "mlp_f32");
 }

@@ -125,8 +125,10 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 }
 
 // hidden layer epilogue: +bias, ReLU, fp16, write this thread's row of the next A tile
-__device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const float* bias, char* a2, int row, bool valid) {
+__device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const float* bias, char* a2, int row, bool valid,
+                                               uint32_t& relu_mask) {
   bool bad = false;
+  relu_mask = 0u;
 #pragma unroll
   for (int kc = 0; kc < 4; ++kc) {
     uint32_t w[4];
@@ -136,6 +138,8 @@ __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const 
       const float v0 = __uint_as_float(acc[j]) + bias[j], v1 = __uint_as_float(acc[j + 1]) + bias[j + 1];
       // non-finite sums, or values that round to +inf in binary16, are reported (rgb_wmma.cuh:179-181)
       bad |= !(fabsf(v0) < 65520.f) || !(fabsf(v1) < 65520.f);
+      relu_mask |= (v0 > 0.f ? 1u : 0u) << j;
+      relu_mask |= (v1 > 0.f ? 1u : 0u) << (j + 1);
       w[q] = pack_h2(fmaxf(v0, 0.f), fmaxf(v1, 0.f));
     }
     *reinterpret_cast<uint4*>(a2 + kc * (kRows * 16) + row * 16) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -146,7 +150,8 @@ __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const 
 __global__ void __launch_bounds__(kRows) k_mlp_tc(
     const char* __restrict__ w16, const float* __restrict__ freq, const float* __restrict__ att,
     const RecIn* __restrict__ rec_in, const int32_t* __restrict__ prim_off, const int2* __restrict__ work,
-    int32_t* __restrict__ counters, float4* __restrict__ rec_out, int out_mode, int32_t* __restrict__ status) {
+    int32_t* __restrict__ counters, float4* __restrict__ rec_out, float4* __restrict__ rec_ext, int out_mode,
+    int32_t* __restrict__ status) {
   extern __shared__ __align__(128) char smem[];
   char* s_w = smem;
   char* s_a1 = smem + kWeightBytes;          // 8464 is a multiple of 16
@@ -177,6 +182,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
   const float* s_bias = reinterpret_cast<const float*>(s_w + kOffBias);
   uint32_t ph_w = 0, ph_m = 0;
   bool ok = true, bad = false, copy_pending = false;
+  uint32_t relu1 = 0u, relu2 = 0u;
 
   for (;;) {
     if (tid == 0) s_misc[1] = (uint32_t)atomicAdd(counters + kCtrWorkNext, 1);
@@ -247,7 +253,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
       uint32_t acc[32];
       if (ok) {
         tmem_ld32(trow, acc);
-        bad |= hidden_to_smem(acc, s_bias, s_a2, tid, valid);
+        bad |= hidden_to_smem(acc, s_bias, s_a2, tid, valid, relu1);
       }
     }
     fence_async_smem();
@@ -269,7 +275,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
       uint32_t acc[32];
       if (ok) {
         tmem_ld32(trow + 32, acc);
-        bad |= hidden_to_smem(acc, s_bias + kH, s_a2, tid, valid);   // layer-2 MMAs have finished reading s_a2
+        bad |= hidden_to_smem(acc, s_bias + kH, s_a2, tid, valid, relu2);   // layer-2 MMAs have finished reading s_a2
       }
     }
     fence_async_smem();
@@ -299,6 +305,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
         out.x = sigmoid_fast(o0); out.y = sigmoid_fast(o1); out.z = sigmoid_fast(o2);
         out.w = (out_mode == kOutAlpha) ? (1.f - __expf(-(sigma_raw * r.decay))) : sigma_raw;
         rec_out[r.slot] = out;
+        if (rec_ext) rec_ext[r.slot] = make_float4(sigma_raw, o3, __uint_as_float(relu1), __uint_as_float(relu2));
       }
     }
     tc_fence_before();
@@ -357,7 +364,8 @@ __global__ void k_pack_weights(const float* __restrict__ W1, const float* __rest
 }
 
 int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
-                   const int32_t* counters, float4* rec_out, int out_mode, int32_t* status, cudaStream_t st) {
+                   const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
+                   cudaStream_t st) {
   MLPSP_REQUIRE(sc->hidden == kH && sc->num_freq == 6, MLPSP_E_LIMIT,
                 "fp16 evaluator is built for the 72->32->32->4 network (hidden 32, 6 frequencies)");
   MLPSP_REQUIRE(sc->w16 && sc->freq && sc->att, MLPSP_E_ARG, "fp16 evaluator needs the packed weight image");
@@ -373,7 +381,7 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   const int grid = sms * 6;
   LaunchScope scope(kKMlp, 1, st);
   k_mlp_tc<<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, prim_off, work,
-                                           const_cast<int32_t*>(counters), rec_out, out_mode, status);
+                                           const_cast<int32_t*>(counters), rec_out, rec_ext, out_mode, status);
   return cuda_check(cudaGetLastError(), "mlp_f16");
 }
 

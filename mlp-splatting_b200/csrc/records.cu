@@ -327,7 +327,8 @@ __global__ void __launch_bounds__(64) k_composite(
     const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out, const float* __restrict__ rec_t,
     float4* __restrict__ px_state, float2* __restrict__ px_depth, float* __restrict__ rgb,
     float* __restrict__ alpha, float* __restrict__ depth_t, uint32_t* __restrict__ mask_used32,
-    float* __restrict__ rec_w, float bgr, float bgg, float bgb, int has_bg, int32_t* __restrict__ next_active,
+    float* __restrict__ rec_w, float* __restrict__ rec_tr, float bgr, float bgg, float bgb, int has_bg,
+    int32_t* __restrict__ next_active,
     int32_t* __restrict__ next_count, int32_t* __restrict__ status) {
   __shared__ int s_live[2];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
@@ -366,6 +367,7 @@ __global__ void __launch_bounds__(64) k_composite(
         st.x = fmaf(w, r.x, st.x); st.y = fmaf(w, r.y, st.y); st.z = fmaf(w, r.z, st.z);
         if (depth_t) { dp.x = fmaf(w, rec_t[slot], dp.x); dp.y += w; }
         if (rec_w) rec_w[slot] = w;
+        if (rec_tr) rec_tr[slot] = st.w;
         st.w *= (1.f - r.w);
         act = st.w >= MLPSP_TERM;
       }
@@ -504,7 +506,10 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     MLPSP_REQUIRE(sc->feat_slots == 1 || sc->feat_slots == 4 || sc->feat_slots == 5, MLPSP_E_ARG,
                   "feature slots must be 1, 4 or 5");
   }
-  uint32_t* used32 = fr->mask_used ? (uint32_t*)fr->mask_used : (want_feat ? s.used32 : nullptr);
+  const bool keep = fr->keep_records == 1;
+  // record export reads the consumed masks from the scratch copy, so a caller-owned mask buffer is
+  // filled by a device copy afterwards
+  uint32_t* used32 = (keep || want_feat) ? s.used32 : (uint32_t*)fr->mask_used;
   {
     LaunchScope scope(kKMisc, 2, st);
     k_init_pixels<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha,
@@ -541,17 +546,22 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
                               sc->gate_tau, fr->status); }
     if (fr->precision == MLPSP_PRECISION_F16)
-      rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, kOutAlpha, fr->status, st);
+      rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
+                          fr->status, st);
     else
-      rc = launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, kOutAlpha, fr->status, st);
+      rc = launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
+                          fr->status, st);
     if (rc) return rc;
     { LaunchScope scope(kKComposite, 1, st);
     k_composite<<<T, 64, 0, st>>>(fr->tile_offsets, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
-                                  fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr, bg[0], bg[1], bg[2], has_bg,
+                                  fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
+                                  keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,
                                   s.active[nxt], s.counters + kCtrActive0 + nxt, fr->status); }
     lo = hi;
   }
+  if (fr->mask_used && used32 != (uint32_t*)fr->mask_used)
+    MLPSP_CUDA_OK(cudaMemcpyAsync(fr->mask_used, used32, 8 * (size_t)fr->max_pairs, cudaMemcpyDeviceToDevice, st));
   if (want_feat) {
     static bool attr_set = false;
     const size_t smem = sizeof(float) * 64 * (size_t)sc->feat_dim;
@@ -565,6 +575,120 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                                                       sc->feat_dim, fr->feat, fr->status);
   }
   return cuda_check(cudaGetLastError(), "render_sorted");
+}
+
+// ----------------------------------------------------------------------- record export ----
+// Pixel-major records in compositing order (np_tile_kernels.cu:3138-3154; training_wmma.cuh:223-256),
+// rebuilt after the frame from the consumed masks, the evaluator outputs kept per compositing slot
+// and a recomputed hit test.  Two passes like the reference: count per pixel, prefix, emit.
+template <bool EMIT>
+__global__ void __launch_bounds__(64) k_export(
+    const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    float thr, float beta, float tau, const uint32_t* __restrict__ used32, const uint32_t* __restrict__ masks32,
+    const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out, const float4* __restrict__ rec_ext,
+    const float* __restrict__ rec_tr, const float4* __restrict__ px_state, int32_t* __restrict__ px_cnt,
+    const int32_t* __restrict__ px_off, int max_hits, int32_t* __restrict__ worst, int32_t* __restrict__ ids,
+    float* __restrict__ x6, float* __restrict__ raw, int32_t* __restrict__ relu_masks, float* __restrict__ gates,
+    int64_t max_out, const int32_t* __restrict__ status) {
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int tile = blockIdx.x;
+  const int s = tile_offsets[tile], e = tile_offsets[tile + 1];
+  const int lane = threadIdx.x & 31, half = threadIdx.x >> 5;
+  const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
+  V3 o = {0.f, 0.f, 0.f}, d = {0.f, 0.f, 0.f};
+  int64_t out0 = 0;
+  if (EMIT && tp.valid) { o = load3(rays_o, tp.pix); d = load3(rays_d, tp.pix); out0 = px_off[tp.pix]; }
+  const uint32_t lt = (1u << lane) - 1u;
+  int cnt = 0;
+  for (int i0 = s; i0 < e; i0 += 32) {
+    const int idx = i0 + lane;
+    uint2 uu = make_uint2(0u, 0u);
+    if (idx < e) uu = *reinterpret_cast<const uint2*>(used32 + 2 * (size_t)idx);
+    const uint32_t any = __ballot_sync(0xffffffffu, (half ? uu.y : uu.x) != 0u);
+    if (!EMIT) {
+      // count: bit `lane` of every pair's half mask
+      uint32_t pending = any;
+      while (pending) {
+        const int j = __ffs(pending) - 1;
+        pending &= pending - 1;
+        const uint32_t mine = __shfl_sync(0xffffffffu, half ? uu.y : uu.x, j);
+        cnt += (mine >> lane) & 1u;
+      }
+      continue;
+    }
+    uint32_t pending = any;
+    while (pending) {
+      const int j = __ffs(pending) - 1;
+      pending &= pending - 1;
+      const uint32_t mine = __shfl_sync(0xffffffffu, half ? uu.y : uu.x, j);
+      if (!((mine >> lane) & 1u)) continue;
+      const int i = i0 + j;
+      const uint32_t m0 = masks32[2 * (size_t)i], m1 = masks32[2 * (size_t)i + 1];
+      const uint32_t hitm = half ? m1 : m0;
+      const uint32_t slot = pair_base[i] + (half ? __popc(m0) : 0) + __popc(hitm & lt);
+      const int p = sorted_prims[i];
+      const int64_t r = out0 + cnt;
+      ++cnt;
+      if (r >= max_out) continue;
+      Hit h;
+      hit_test(load_geom(geom, p), o, d, thr, h);
+      if (ids) ids[r] = p;
+      if (x6) { float* q = x6 + r * 6; q[0] = d.x; q[1] = d.y; q[2] = d.z; q[3] = h.dx; q[4] = h.dy; q[5] = h.dz; }
+      const float4 ro = rec_out[slot], re = rec_ext[slot];
+      if (raw) {
+        float* q = raw + r * 8;
+        q[0] = ro.x; q[1] = ro.y; q[2] = ro.z; q[3] = re.x; q[4] = rec_tr[slot]; q[5] = ro.w; q[6] = h.decay; q[7] = re.y;
+      }
+      if (relu_masks) { relu_masks[r * 2] = (int32_t)__float_as_uint(re.z); relu_masks[r * 2 + 1] = (int32_t)__float_as_uint(re.w); }
+      if (gates) {
+        const float4 ls = __ldg(geom + (size_t)p * 4 + 3);
+        const float4 g = tetra_gates(h, ls.x, ls.y, ls.z, beta, tau);
+        float* q = gates + r * 4; q[0] = g.x; q[1] = g.y; q[2] = g.z; q[3] = g.w;
+      }
+    }
+  }
+  if (!EMIT && tp.valid) {
+    px_cnt[tp.pix] = cnt;
+    atomicMax(worst, cnt);
+    const bool live = px_state[tp.pix].w >= MLPSP_TERM;
+    if (max_hits > 0 && cnt >= max_hits && (cnt > max_hits || live)) atomicOr(worst + 1, 1);
+  }
+}
+
+__global__ void k_widen_i32(const int32_t* __restrict__ in, int64_t n, int64_t* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = in[i];
+}
+
+int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, int64_t* offsets, int32_t* ids,
+                          float* x6, float* raw, int32_t* relu_masks, float* gates, int64_t max_out, int32_t max_hits,
+                          int64_t* total_host, int32_t* worst_host, cudaStream_t st) {
+  const int W = fr->width, H = fr->height, T = num_tiles(W, H, 8), ntx = (W + 7) / 8;
+  const int64_t P = (int64_t)W * H;
+  int32_t* worst = s.counters + kCtrScratch;     // [0] largest per-pixel count, [1] capacity flag
+  MLPSP_CUDA_OK(cudaMemsetAsync(worst, 0, 8, st));
+  LaunchScope scope(kKMisc, 6, st);
+  k_export<false><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
+                                    W, H, ntx, fr->threshold, sc->gate_beta, sc->gate_tau, s.used32, s.masks32,
+                                    s.pair_base, s.rec_out, s.rec_ext, s.rec_tr, s.px_state, s.px_cnt, nullptr, max_hits,
+                                    worst, nullptr, nullptr, nullptr, nullptr, nullptr, 0, fr->status);
+  int rc = launch_scan_i32(s.px_cnt, P, s.scan_blk, s.px_off, st);
+  if (rc) return rc;
+  k_widen_i32<<<(unsigned)((P + 1 + 255) / 256), 256, 0, st>>>(s.px_off, P + 1, offsets);
+  int32_t h[3] = {0, 0, 0};
+  MLPSP_CUDA_OK(cudaMemcpyAsync(&h[0], s.px_off + P, 4, cudaMemcpyDeviceToHost, st));
+  MLPSP_CUDA_OK(cudaMemcpyAsync(&h[1], worst, 8, cudaMemcpyDeviceToHost, st));
+  MLPSP_CUDA_OK(cudaStreamSynchronize(st));
+  if (total_host) *total_host = h[0];
+  if (worst_host) *worst_host = h[2] ? -h[1] : h[1];
+  if ((ids || x6 || raw || relu_masks || gates) && max_out >= h[0] && h[0] > 0) {
+    k_export<true><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
+                                     W, H, ntx, fr->threshold, sc->gate_beta, sc->gate_tau, s.used32, s.masks32,
+                                     s.pair_base, s.rec_out, s.rec_ext, s.rec_tr, s.px_state, s.px_cnt, s.px_off, max_hits,
+                                     worst, ids, x6, raw, relu_masks, gates, max_out, fr->status);
+  }
+  return cuda_check(cudaGetLastError(), "export_records");
 }
 
 }  // namespace mlpsp

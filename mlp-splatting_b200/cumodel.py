@@ -280,3 +280,29 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
                                   culled_prim_indices=culled_prim_indices, tile_offsets=tile_offsets,
                                   return_feature=True)
         return feat
+
+
+@torch.no_grad()
+def render_tiles_training_records(tensors, width, height, tile, threshold, beta, temperature, precision="float32",
+                                  max_hits=512):
+    """Forward record list with the argument list of the reference's extension entry points
+    render_tiles_training_records / render_tiles_training_records_wmma (np_tile_kernels.cu:6994,
+    training_wmma.cuh:270): `tensors` = [rays_o, rays_d (unit), positions, log_scales, quats (unit),
+    culled_prim_indices, tile_offsets, freq, att, W1, b1, W2, b2, W3, b3] (two trailing adjoint
+    placeholders are accepted and ignored).  Returns [rgb, alpha, ids, x6, raw, masks, gates, offsets].
+    precision "float32" selects the scalar evaluator, "float16" the tensor-core one."""
+    if len(tensors) not in (15, 17):
+        raise ValueError("expected the 15 scene tensors (optionally followed by two adjoint placeholders)")
+    if int(tile) != 8:
+        raise ValueError("Training WMMA requires tile8")
+    if precision not in ("float32", "float16"):
+        raise ValueError("precision must be float32 or float16")
+    ro, rd, pos, ls, q, culled, offs, freq, att, W1, b1, W2, b2, W3, b3 = tensors[:15]
+    dev = ro.device
+    scene = PackedScene(pos, ls, q, W1, b1, W2, b2, W3, b3, freq, att, gate_beta=float(beta), gate_tau=float(temperature),
+                        device=dev, pack_f16=(precision == "float16"))
+    r = FrameRenderer(int(width), int(height), device=dev, max_pairs=max(int(culled.numel()), 1))
+    prec = L.PRECISION_F16 if (precision == "float16" and scene.has_f16) else L.PRECISION_F32
+    return r.render_records(scene, ro.contiguous().float(), rd.contiguous().float(), float(threshold), max_hits=max_hits,
+                            precision=prec, tile_lists=(culled, offs), rays_normalized=True,
+                            path_name="render_tiles_training_records")

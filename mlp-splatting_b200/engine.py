@@ -175,6 +175,7 @@ class FrameRenderer:
         self._proj = np.zeros(16, np.float32)
         self._bg = np.zeros(3, np.float32)
         self.last_stats: FrameStats | None = None
+        self._last_frame = None
         self.f32_fallbacks = 0   # frames re-rendered in FP32 after an fp16 overflow
 
     # -- buffers ------------------------------------------------------------------------------
@@ -190,7 +191,7 @@ class FrameRenderer:
         return self.scratch
 
     def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
-               want_mask_used, waves, want_feat=False) -> L.Frame:
+               want_mask_used, waves, want_feat=False, keep_records=False) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
         f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
@@ -224,6 +225,7 @@ class FrameRenderer:
         aligned = (base + 255) // 256 * 256
         f.scratch, f.scratch_bytes = aligned, sc.numel() - (aligned - base)
         f.max_records = self.max_records
+        f.keep_records = 1 if keep_records else 0
         f.status = L.ptr(self.status)
         if waves:
             f.num_waves = len(waves)
@@ -259,7 +261,8 @@ class FrameRenderer:
     # -- stages -------------------------------------------------------------------------------
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
-               rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False):
+               rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False,
+               keep_records=False):
         """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling)."""
         lib, d = self.lib, self.device
         if precision is None:
@@ -287,7 +290,8 @@ class FrameRenderer:
                                                           self.capacity, scene.n, L.ptr(self.status), st),
                             "mlpsp_validate_tile_lists")
                 f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves,
-                                want_feat=want_feat)
+                                want_feat=want_feat, keep_records=keep_records)
+                self._last_frame = (f, scene)
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")
                 else:
@@ -309,6 +313,33 @@ class FrameRenderer:
                     continue
                 return self.rgb, self.alpha
             raise RenderError(f"{path_name}: scratch kept overflowing after 8 attempts")
+
+    def render_records(self, scene: PackedScene, rays_o, rays_d, threshold, max_hits=512, **kw):
+        """Render and return the reference's record list [rgb, alpha, ids, x6, raw, masks, gates, offsets]
+        (render_tiles_training_records, np_tile_kernels.cu:6897-6986): pixel-major, compositing order."""
+        lib, d = self.lib, self.device
+        rgb, alpha = self.render(scene, rays_o, rays_d, threshold, keep_records=True, **kw)
+        f, _ = self._last_frame
+        with torch.cuda.device(d):
+            st = _stream_ptr(d)
+            offsets = torch.empty(self.P + 1, device=d, dtype=torch.int64)
+            total, worst = C.c_int64(0), C.c_int32(0)
+            L.check(lib.mlpsp_export_records(C.byref(scene.c), C.byref(f), L.ptr(offsets), None, None, None, None, None, 0,
+                                             int(max_hits), C.byref(total), C.byref(worst), st), "mlpsp_export_records")
+            if worst.value < 0:
+                raise RenderError(f"render_tiles_training_records: tile-center backward hit capacity {max_hits} reached "
+                                  "before transmittance termination; refusing to return truncated records")
+            R = int(total.value)
+            ids = torch.empty(R, device=d, dtype=torch.int32)
+            x6 = torch.empty((R, 6), device=d, dtype=torch.float32)
+            raw = torch.empty((R, 8), device=d, dtype=torch.float32)
+            masks = torch.empty((R, 2), device=d, dtype=torch.int32)
+            gates = torch.empty((R, 4), device=d, dtype=torch.float32)
+            if R > 0:
+                L.check(lib.mlpsp_export_records(C.byref(scene.c), C.byref(f), L.ptr(offsets), L.ptr(ids), L.ptr(x6),
+                                                 L.ptr(raw), L.ptr(masks), L.ptr(gates), R, int(max_hits),
+                                                 C.byref(total), C.byref(worst), st), "mlpsp_export_records")
+        return [rgb.clone(), alpha.clone(), ids, x6, raw, masks, gates, offsets]
 
     def bin(self, scene: PackedScene, view, proj, threshold, check=True):
         """Binning only: returns (culled_prim_indices[M] int32, tile_offsets[T+1] int32) views."""

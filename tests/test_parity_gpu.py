@@ -211,6 +211,68 @@ def test_feature_map_matches_oracle(dev, slots, C):
     assert np.abs(f["render"].feat).max() > 0.05
 
 
+@pytest.mark.parametrize("name,precision", [("tiny", 0), ("ragged", 0), ("dense", 0), ("tiny", 1)])
+def test_record_export_matches_oracle_records(dev, name, precision):
+    """The 8-tensor record list (np_tile_kernels.cu:3138-3154) and the CSR built from it."""
+    from mlp_splatting_b200 import primitive_csr
+    from oracle import oracle as orc
+    scene, cam = small_case(**CASES[name])
+    f = oracle_frame(scene, cam, 5e-3, precision=precision, want_records=True)
+    res, rec = f["render"], f["render"].records
+    ps, r = _packed(scene, dev, pack_f16=bool(precision)), _renderer(cam, dev)
+    out = r.render_records(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, view=cam["view"], proj=cam["proj"],
+                           precision=precision)
+    rgb, alpha, ids, x6, raw, masks, gates, offsets = [t.cpu().numpy() for t in out]
+    assert ids.dtype == np.int32 and offsets.dtype == np.int64 and masks.dtype == np.int32
+    assert x6.shape == (ids.size, 6) and raw.shape == (ids.size, 8) and gates.shape == (ids.size, 4)
+    # pixels far from the 1e-3 gate must have exactly the oracle's records
+    margin = 1e-3 if precision == 0 else 5e-2
+    safe = res.min_margin >= margin
+    cnt_g, cnt_o = np.diff(offsets), np.diff(rec["offsets"])
+    assert np.array_equal(cnt_g[safe], cnt_o[safe])
+    assert (~safe).mean() < 0.05
+    pix_g = np.repeat(np.arange(cnt_g.size), cnt_g)
+    pix_o = np.repeat(np.arange(cnt_o.size), cnt_o)
+    sg, so = safe[pix_g], safe[pix_o]
+    np.testing.assert_array_equal(ids[sg], rec["ids"][so])
+    np.testing.assert_array_equal(x6[sg].view(np.uint32), rec["x6"][so].view(np.uint32))        # geometry: bit-exact
+    np.testing.assert_array_equal(raw[sg, 6].view(np.uint32), rec["raw"][so, 6].view(np.uint32))  # decay: bit-exact
+    tol = 2e-5 if precision == 0 else 2e-3
+    np.testing.assert_allclose(raw[sg][:, [0, 1, 2, 4, 5]], rec["raw"][so][:, [0, 1, 2, 4, 5]], rtol=0, atol=tol)
+    np.testing.assert_allclose(raw[sg][:, [3, 7]], rec["raw"][so][:, [3, 7]], rtol=tol * 5, atol=tol * 5)
+    np.testing.assert_allclose(gates[sg], rec["gates"][so], rtol=0, atol=1e-5)
+    np.testing.assert_allclose(gates.sum(1), 1.0, atol=1e-5)
+    if precision == 0:
+        # ReLU masks can differ only where a pre-activation is within float noise of zero
+        assert (masks[sg] != rec["masks"][so]).mean() < 1e-3
+    np.testing.assert_array_equal(x6[:, :3].view(np.uint32), f["rays_d_unit"][pix_g].view(np.uint32))
+    # CSR of the exported records: offsets and order identical to the oracle's grouping of the same ids
+    n = ps.n
+    g_off, g_order = primitive_csr.group_order(out[2], n)
+    o_off, o_order = orc.group_records(ids, n)
+    np.testing.assert_array_equal(g_off.cpu().numpy(), o_off)
+    np.testing.assert_array_equal(g_order.cpu().numpy(), o_order)
+    if safe.all():
+        np.testing.assert_array_equal(o_off, orc.group_records(rec["ids"], n)[0])
+
+
+def test_record_export_through_reference_argument_list(dev):
+    from mlp_splatting_b200.cumodel import render_tiles_training_records
+    from mlp_splatting_b200.engine import RenderError, normalize_rows
+    scene, cam = small_case(**CASES["tiny"])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_records=True)
+    tensors = [_t(cam["rays_o"], dev), _t(f["rays_d_unit"], dev), _t(scene["positions"], dev), _t(scene["log_scales"], dev),
+               normalize_rows(_t(scene["quats"], dev)), _t(f["tile_prims"], dev), _t(f["tile_offsets"], dev),
+               _t(scene["freq"], dev), _t(scene["att"], dev)] + [_t(scene[k], dev) for k in WKEYS]
+    out = render_tiles_training_records(tensors, cam["W"], cam["H"], 8, 5e-3, 1.5, 2.0)
+    assert len(out) == 8 and int(out[7][-1]) == out[2].numel() == f["render"].records["ids"].size
+    np.testing.assert_allclose(out[0].cpu().numpy(), f["render"].rgb, atol=IMG_TOL_F32)
+    with pytest.raises(RenderError, match="hit capacity 4 reached"):
+        render_tiles_training_records(tensors, cam["W"], cam["H"], 8, 5e-3, 1.5, 2.0, max_hits=4)
+    with pytest.raises(ValueError, match="requires tile8"):
+        render_tiles_training_records(tensors, cam["W"], cam["H"], 16, 5e-3, 1.5, 2.0)
+
+
 def test_wave_schedule_does_not_change_results(dev):
     scene, cam = small_case(**CASES["dense"])
     ps, r = _packed(scene, dev), _renderer(cam, dev)
