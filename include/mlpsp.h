@@ -109,7 +109,9 @@ typedef struct mlpsp_frame {
   int32_t num_waves;      /* 0 = library default schedule */
   int32_t wave_len[MLPSP_MAX_WAVES]; /* candidates per tile processed by wave k */
   int32_t keep_records;   /* 1 = keep what mlpsp_export_records needs (ReLU masks, logits, transmittance) */
-  int32_t reserved1;
+  int32_t sort_key;       /* 0 = t* of the tile-centre ray (np_tile_kernels.cu:483-518), the order of the forward,
+                             feature and record kernels; 1 = Euclidean depth (c - o).d along that ray, the order
+                             of render_tiles_kernel_tilecenter_order_with_t (np_tile_kernels.cu:5538-5543) */
 } mlpsp_frame;
 
 const char* mlpsp_last_error(void);

@@ -43,7 +43,7 @@ class Frame(C.Structure):
         ("rgb", _fp), ("alpha", _fp), ("depth_t", _fp), ("feat", _fp), ("mask_used", _fp), ("bg_color", _fp),
         ("scratch", _fp), ("scratch_bytes", C.c_int64), ("max_records", C.c_int64),
         ("status", _fp), ("num_waves", C.c_int32), ("wave_len", C.c_int32 * MAX_WAVES),
-        ("keep_records", C.c_int32), ("reserved1", C.c_int32),
+        ("keep_records", C.c_int32), ("sort_key", C.c_int32),
     ]
 
 

@@ -215,9 +215,9 @@ extern "C" int mlpsp_render_frame(const mlpsp_scene* sc, const mlpsp_frame* fr, 
   rc = get_scratch(sc, fr, s, "mlpsp_render_frame");
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  rc = launch_bin(sc, fr, s, st);
+  rc = launch_bin(sc, fr, s, st, /*order_lists=*/false);
   if (rc) return rc;
-  rc = launch_sort(sc, fr, nullptr, st);
+  rc = launch_sort(sc, fr, nullptr, st, /*unordered_input=*/true);
   if (rc) return rc;
   return render_sorted_checked(sc, fr, s, st);
 }

@@ -250,7 +250,7 @@ int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cu
 
 constexpr int kSortCap = 2048;  // per-tile sort capacity (>= tile capacity 1536)
 
-int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st) {
+int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st, bool order_lists) {
   const int T = num_tiles(fr->width, fr->height, fr->tile);
   BinCam cam;
   for (int i = 0; i < 16; ++i) { cam.view[i] = fr->view[i]; cam.proj[i] = fr->proj[i]; }
@@ -267,7 +267,7 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_cnt, 0, 4 * (size_t)(T + 1), st));
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_fill, 0, 4 * (size_t)T, st));
   const int n = sc->n;
-  LaunchScope scope(kKBin, n > 0 ? 7 : 4, st);
+  LaunchScope scope(kKBin, n > 0 ? (order_lists ? 7 : 6) : 4, st);
   if (n > 0) k_bin_count<<<(n + 255) / 256, 256, 0, st>>>((const float4*)sc->geom, n, cam, s.rect, s.tile_cnt);
   int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
   if (rc) return rc;
@@ -276,7 +276,7 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
   if (n > 0) {
     k_bin_scatter<<<(n + 255) / 256, 256, 0, st>>>(n, cam.ntx, s.rect, fr->tile_offsets, s.tile_fill,
                                                    fr->tile_prims, fr->status);
-    k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);
+    if (order_lists) k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);
   }
   return cuda_check(cudaGetLastError(), "bin");
 }

@@ -96,6 +96,14 @@ __device__ __forceinline__ float tile_key(const Geom& g, V3 o, V3 d) {
   return (t > 0.f) ? t : MLPSP_SENTINEL_KEY;
 }
 
+// Euclidean depth of the centre along the tile-centre ray: the ordering key of the reference's
+// expected-depth kernel (np_tile_kernels.cu:5538-5543).
+__device__ __forceinline__ float tile_key_euclid(const Geom& g, V3 o, V3 d) {
+  const float vx = fsub(g.cx, o.x), vy = fsub(g.cy, o.y), vz = fsub(g.cz, o.z);
+  const float t = ffma(vx, d.x, ffma(vy, d.y, fmul(vz, d.z)));
+  return (t > 0.f) ? t : MLPSP_SENTINEL_KEY;
+}
+
 struct Hit { float t, dx, dy, dz, qx, qy, qz, decay; };
 
 // Rotated-ellipsoid closest approach (np_tile_kernels.cu:659-711).
@@ -115,6 +123,18 @@ __device__ __forceinline__ bool hit_test(const Geom& g, V3 o, V3 d, float thr, H
   const float decay = det_exp(fmul(-0.5f, r2));
   h.t = t; h.dx = dd.x; h.dy = dd.y; h.dz = dd.z; h.qx = q.x; h.qy = q.y; h.qz = q.z; h.decay = decay;
   return decay > thr;
+}
+
+// Cheap necessary condition for a hit: the centre's distance to the ray's line must be below the
+// bounding radius.  With r^2 = sum q_k^2 m_k >= |c - p|^2 / smax^2 >= perp^2 / smax^2 for every point p
+// of the line, decay > thr needs perp^2 < smax^2 * (-2 ln thr).  bound2 carries a 2 % margin, far
+// above any rounding error here, so a rejected pair is one the full test also rejects and the
+// decisions stay identical to evaluating hit_test everywhere.  NaNs fall through to the full test.
+__device__ __forceinline__ bool surely_misses(const Geom& g, V3 o, V3 d, float bound2) {
+  const float vx = g.cx - o.x, vy = g.cy - o.y, vz = g.cz - o.z;
+  const float te = vx * d.x + vy * d.y + vz * d.z;
+  const float wx = vx - te * d.x, wy = vy - te * d.y, wz = vz - te * d.z;
+  return (wx * wx + wy * wy + wz * wz) > bound2 * (g.smax * g.smax);
 }
 
 __device__ __forceinline__ V3 load3(const float* __restrict__ p, int64_t i) {

@@ -130,8 +130,10 @@ int cuda_check(cudaError_t e, const char* what);
   } while (0)
 
 // stage launchers (defined in the .cu files)
-int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
-int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st);
+// order_lists = false leaves every tile list in scatter order for a following launch_sort(unordered_input = true)
+int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st, bool order_lists = true);
+int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st,
+                bool unordered_input = false);
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st);
 int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
 // rec_ext (optional): per record (sigma_raw, sigma_logit, layer-1 ReLU bitmask, layer-2 ReLU bitmask)

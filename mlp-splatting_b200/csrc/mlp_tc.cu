@@ -125,6 +125,7 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 }
 
 // hidden layer epilogue: +bias, ReLU, fp16, write this thread's row of the next A tile
+template <bool KEEP>
 __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const float* bias, char* a2, int row, bool valid,
                                                uint32_t& relu_mask) {
   bool bad = false;
@@ -138,8 +139,10 @@ __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const 
       const float v0 = __uint_as_float(acc[j]) + bias[j], v1 = __uint_as_float(acc[j + 1]) + bias[j + 1];
       // non-finite sums, or values that round to +inf in binary16, are reported (rgb_wmma.cuh:179-181)
       bad |= !(fabsf(v0) < 65520.f) || !(fabsf(v1) < 65520.f);
-      relu_mask |= (v0 > 0.f ? 1u : 0u) << j;
-      relu_mask |= (v1 > 0.f ? 1u : 0u) << (j + 1);
+      if (KEEP) {
+        relu_mask |= (v0 > 0.f ? 1u : 0u) << j;
+        relu_mask |= (v1 > 0.f ? 1u : 0u) << (j + 1);
+      }
       w[q] = pack_h2(fmaxf(v0, 0.f), fmaxf(v1, 0.f));
     }
     *reinterpret_cast<uint4*>(a2 + kc * (kRows * 16) + row * 16) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -147,6 +150,7 @@ __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const 
   return bad && valid;
 }
 
+template <bool KEEP>
 __global__ void __launch_bounds__(kRows) k_mlp_tc(
     const char* __restrict__ w16, const float* __restrict__ freq, const float* __restrict__ att,
     const RecIn* __restrict__ rec_in, const int32_t* __restrict__ prim_off, const int2* __restrict__ work,
@@ -253,7 +257,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
       uint32_t acc[32];
       if (ok) {
         tmem_ld32(trow, acc);
-        bad |= hidden_to_smem(acc, s_bias, s_a2, tid, valid, relu1);
+        bad |= hidden_to_smem<KEEP>(acc, s_bias, s_a2, tid, valid, relu1);
       }
     }
     fence_async_smem();
@@ -275,7 +279,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
       uint32_t acc[32];
       if (ok) {
         tmem_ld32(trow + 32, acc);
-        bad |= hidden_to_smem(acc, s_bias + kH, s_a2, tid, valid, relu2);   // layer-2 MMAs have finished reading s_a2
+        bad |= hidden_to_smem<KEEP>(acc, s_bias + kH, s_a2, tid, valid, relu2);   // layer-2 MMAs have finished reading s_a2
       }
     }
     fence_async_smem();
@@ -305,7 +309,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
         out.x = sigmoid_fast(o0); out.y = sigmoid_fast(o1); out.z = sigmoid_fast(o2);
         out.w = (out_mode == kOutAlpha) ? (1.f - __expf(-(sigma_raw * r.decay))) : sigma_raw;
         rec_out[r.slot] = out;
-        if (rec_ext) rec_ext[r.slot] = make_float4(sigma_raw, o3, __uint_as_float(relu1), __uint_as_float(relu2));
+        if (KEEP) rec_ext[r.slot] = make_float4(sigma_raw, o3, __uint_as_float(relu1), __uint_as_float(relu2));
       }
     }
     tc_fence_before();
@@ -371,7 +375,8 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   MLPSP_REQUIRE(sc->w16 && sc->freq && sc->att, MLPSP_E_ARG, "fp16 evaluator needs the packed weight image");
   static bool attr_set = false;
   if (!attr_set) {
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attr_set = true;
   }
   int dev = 0, sms = 148;
@@ -380,8 +385,12 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   // tensor memory: 512 columns per SM / 64 per CTA = at most 8 resident CTAs; shared memory allows 6
   const int grid = sms * 6;
   LaunchScope scope(kKMlp, 1, st);
-  k_mlp_tc<<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, prim_off, work,
-                                           const_cast<int32_t*>(counters), rec_out, rec_ext, out_mode, status);
+  if (rec_ext)
+    k_mlp_tc<true><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, prim_off, work,
+                                                   const_cast<int32_t*>(counters), rec_out, rec_ext, out_mode, status);
+  else
+    k_mlp_tc<false><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, prim_off, work,
+                                                    const_cast<int32_t*>(counters), rec_out, rec_ext, out_mode, status);
   return cuda_check(cudaGetLastError(), "mlp_f16");
 }
 

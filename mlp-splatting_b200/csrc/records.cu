@@ -17,11 +17,15 @@
 // skipped by compositing, so results do not depend on the wave schedule.
 #include <algorithm>
 #include <climits>
+#include <cmath>
 #include "frame.cuh"
 
 namespace mlpsp {
 
 constexpr int kWinMax = 2048;
+
+// squared bounding radius in units of the largest scale, with the 2 % margin surely_misses() relies on
+static inline float miss_bound2(float thr) { return (float)(-2.0 * log((double)thr) * 1.02); }
 
 struct TilePix {
   int pix; bool valid;
@@ -63,8 +67,8 @@ __global__ void k_init_tiles(int T, int32_t* __restrict__ active0, int32_t* __re
 __global__ void __launch_bounds__(256) k_hits(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
-    float thr, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo, int hi,
-    const float4* __restrict__ px_state, uint32_t* __restrict__ masks32, uint32_t* __restrict__ pair_base,
+    float thr, float bound2, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo,
+    int hi, const float4* __restrict__ px_state, uint32_t* __restrict__ masks32, uint32_t* __restrict__ pair_base,
     int32_t* __restrict__ prim_cnt, int32_t* __restrict__ counters, int64_t max_records,
     int32_t* __restrict__ status) {
   __shared__ uint32_t s_m[2][kWinMax];
@@ -72,15 +76,16 @@ __global__ void __launch_bounds__(256) k_hits(
   __shared__ int warp_sums[32];
   __shared__ int s_tile_base;
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
-  if ((int)blockIdx.x >= *active_count) return;
-  const int tile = active[blockIdx.x];
+  const int n_active = *active_count;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int half = warp & 1;
+  for (int slot_i = blockIdx.x; slot_i < n_active; slot_i += gridDim.x) {
+  const int tile = active[slot_i];
   const int s = tile_offsets[tile];
   const int len = tile_offsets[tile + 1] - s;
   const int wlo = min(lo, len), whi = min(hi, len);
   const int nwin = whi - wlo;
-  if (nwin <= 0) return;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int half = warp & 1;
+  if (nwin <= 0) continue;
   const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
   V3 o = {0.f, 0.f, 0.f}, d = {0.f, 0.f, 0.f};
   bool act = false;
@@ -92,8 +97,11 @@ __global__ void __launch_bounds__(256) k_hits(
     const int p = sorted_prims[s + i];
     bool hit = false;
     if (act && p >= 0 && p < n) {
-      Hit h;
-      hit = hit_test(load_geom(geom, p), o, d, thr, h);
+      const Geom g = load_geom(geom, p);
+      if (!surely_misses(g, o, d, bound2)) {
+        Hit h;
+        hit = hit_test(g, o, d, thr, h);
+      }
     }
     const uint32_t m = __ballot_sync(0xffffffffu, hit);
     if (lane == 0) s_m[half][i - wlo] = m;
@@ -123,13 +131,15 @@ __global__ void __launch_bounds__(256) k_hits(
     const int c = __popc(m0) + __popc(m1);
     if (c > 0) atomicAdd(prim_cnt + sorted_prims[s + wlo + j], c);
   }
+  __syncthreads();   // shared arrays are reused by the next tile of this CTA
+  }
 }
 
 // Geometric hit masks of all pairs (no transmittance state): the superset the waves draw from.
 __global__ void __launch_bounds__(256) k_hit_masks_all(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
-    float thr, uint32_t* __restrict__ masks32, const int32_t* __restrict__ status) {
+    float thr, float bound2, uint32_t* __restrict__ masks32, const int32_t* __restrict__ status) {
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int tile = blockIdx.x;
   const int s = tile_offsets[tile];
@@ -142,8 +152,11 @@ __global__ void __launch_bounds__(256) k_hit_masks_all(
     const int p = sorted_prims[s + i];
     bool hit = false;
     if (tp.valid && p >= 0 && p < n) {
-      Hit h;
-      hit = hit_test(load_geom(geom, p), o, d, thr, h);
+      const Geom g = load_geom(geom, p);
+      if (!surely_misses(g, o, d, bound2)) {
+        Hit h;
+        hit = hit_test(g, o, d, thr, h);
+      }
     }
     const uint32_t m = __ballot_sync(0xffffffffu, hit);
     if (lane == 0) masks32[2 * (size_t)(s + i) + half] = m;
@@ -264,7 +277,9 @@ __device__ __forceinline__ float4 tetra_gates(const Hit& h, float lsx, float lsy
   return make_float4(e0 * inv, e1 * inv, e2 * inv, e3 * inv);
 }
 
-// One warp per pair; lane l owns pixels l and l+32 of the tile.
+// One CTA per active tile.  Pairs with hits reserve their primitive-major range (one atomic per pair),
+// then threads walk the tile's RECORDS (not its pixels): record r of the tile-wave belongs to the pair
+// found by binary search in the slot prefix, and to the pixel of the (r - prefix)-th set mask bit.
 __global__ void __launch_bounds__(256) k_fill(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
@@ -273,49 +288,69 @@ __global__ void __launch_bounds__(256) k_fill(
     const int32_t* __restrict__ prim_off, int32_t* __restrict__ prim_cursor, RecIn* __restrict__ rec_in,
     float* __restrict__ rec_t, float4* __restrict__ rec_gate, float beta, float tau,
     const int32_t* __restrict__ status) {
+  __shared__ uint32_t s_m[2][kWinMax];
+  __shared__ int32_t s_pref[kWinMax + 1];   // slot of the pair's first record, relative to the tile-wave
+  __shared__ int32_t s_q0[kWinMax];         // primitive-major position of the pair's first record
+  __shared__ float s_ray[64][6];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
-  if ((int)blockIdx.x >= *active_count) return;
-  const int tile = active[blockIdx.x];
+  const int n_active = *active_count;
+  const int tid = threadIdx.x;
+  for (int slot_i = blockIdx.x; slot_i < n_active; slot_i += gridDim.x) {
+  const int tile = active[slot_i];
   const int s = tile_offsets[tile];
   const int len = tile_offsets[tile + 1] - s;
   const int wlo = min(lo, len), whi = min(hi, len);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  TilePix tp[2];
-  V3 o[2], d[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    tp[h] = tile_pixel(tile, h * 32 + lane, ntx, W, H);
-    o[h] = d[h] = V3{0.f, 0.f, 0.f};
-    if (tp[h].valid) { o[h] = load3(rays_o, tp[h].pix); d[h] = load3(rays_d, tp[h].pix); }
+  const int nwin = whi - wlo;
+  if (nwin <= 0) continue;
+  if (tid < 64) {
+    const TilePix tp = tile_pixel(tile, tid, ntx, W, H);
+    V3 o = {0.f, 0.f, 0.f}, d = {0.f, 0.f, 0.f};
+    if (tp.valid) { o = load3(rays_o, tp.pix); d = load3(rays_d, tp.pix); }
+    s_ray[tid][0] = o.x; s_ray[tid][1] = o.y; s_ray[tid][2] = o.z;
+    s_ray[tid][3] = d.x; s_ray[tid][4] = d.y; s_ray[tid][5] = d.z;
   }
-  const uint32_t lt = (1u << lane) - 1u;
-  for (int i = wlo + warp; i < whi; i += 8) {
-    const uint32_t m0 = masks32[2 * (size_t)(s + i)], m1 = masks32[2 * (size_t)(s + i) + 1];
-    const int c0 = __popc(m0), c = c0 + __popc(m1);
-    if (c == 0) continue;
-    const int p = sorted_prims[s + i];
+  const uint32_t slot_base = pair_base[s + wlo];
+  for (int j = tid; j < nwin; j += 256) {
+    const uint32_t m0 = masks32[2 * (size_t)(s + wlo + j)], m1 = masks32[2 * (size_t)(s + wlo + j) + 1];
+    s_m[0][j] = m0; s_m[1][j] = m1;
+    s_pref[j] = (int32_t)(pair_base[s + wlo + j] - slot_base);
+    const int c = __popc(m0) + __popc(m1);
     int q0 = 0;
-    if (lane == 0) q0 = prim_off[p] + atomicAdd(prim_cursor + p, c);
-    q0 = __shfl_sync(0xffffffffu, q0, 0);
-    const uint32_t slot0 = pair_base[s + i];
-    const Geom g = load_geom(geom, p);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t m = h ? m1 : m0;
-      if (!((m >> lane) & 1u)) continue;
-      const int rank = (h ? c0 : 0) + __popc(m & lt);
-      Hit ht;
-      hit_test(g, o[h], d[h], thr, ht);
-      RecIn r;
-      r.rdx = d[h].x; r.rdy = d[h].y; r.rdz = d[h].z; r.dx = ht.dx; r.dy = ht.dy; r.dz = ht.dz;
-      r.decay = ht.decay; r.slot = slot0 + rank;
-      rec_in[q0 + rank] = r;
-      if (rec_t) rec_t[slot0 + rank] = ht.t;
-      if (rec_gate) {
-        const float4 ls = __ldg(geom + (size_t)p * 4 + 3);
-        rec_gate[slot0 + rank] = tetra_gates(ht, ls.x, ls.y, ls.z, beta, tau);
-      }
+    if (c > 0) {
+      const int p = sorted_prims[s + wlo + j];
+      q0 = prim_off[p] + atomicAdd(prim_cursor + p, c);
     }
+    s_q0[j] = q0;
+    if (j == nwin - 1) s_pref[nwin] = s_pref[j] + c;
+  }
+  __syncthreads();
+  const int total = s_pref[nwin];
+  for (int r = tid; r < total; r += 256) {
+    int a = 0, b = nwin - 1;                 // largest j with s_pref[j] <= r (empty pairs share a prefix
+    while (a < b) {                          //  with their successor, so the last such j is the owner)
+      const int mid = (a + b + 1) >> 1;
+      if (s_pref[mid] <= r) a = mid; else b = mid - 1;
+    }
+    const int j = a, k = r - s_pref[a];
+    const uint32_t m0 = s_m[0][j], m1 = s_m[1][j];
+    const int c0 = __popc(m0);
+    const int px = (k < c0) ? (int)__fns(m0, 0, k + 1) : 32 + (int)__fns(m1, 0, k - c0 + 1);
+    const int p = sorted_prims[s + wlo + j];
+    const V3 o = {s_ray[px][0], s_ray[px][1], s_ray[px][2]}, d = {s_ray[px][3], s_ray[px][4], s_ray[px][5]};
+    Hit ht;
+    hit_test(load_geom(geom, p), o, d, thr, ht);
+    const uint32_t slot = slot_base + (uint32_t)r;
+    RecIn rec;
+    rec.rdx = d.x; rec.rdy = d.y; rec.rdz = d.z; rec.dx = ht.dx; rec.dy = ht.dy; rec.dz = ht.dz;
+    rec.decay = ht.decay; rec.slot = slot;
+    rec_in[s_q0[j] + k] = rec;
+    if (rec_t) rec_t[slot] = ht.t;
+    if (rec_gate) {
+      const float4 ls = __ldg(geom + (size_t)p * 4 + 3);
+      rec_gate[slot] = tetra_gates(ht, ls.x, ls.y, ls.z, beta, tau);
+    }
+  }
+  __syncthreads();   // shared arrays are reused by the next tile of this CTA
   }
 }
 
@@ -332,8 +367,9 @@ __global__ void __launch_bounds__(64) k_composite(
     int32_t* __restrict__ next_count, int32_t* __restrict__ status) {
   __shared__ int s_live[2];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
-  if ((int)blockIdx.x >= *active_count) return;
-  const int tile = active[blockIdx.x];
+  const int n_active = *active_count;
+  for (int slot_i = blockIdx.x; slot_i < n_active; slot_i += gridDim.x) {
+  const int tile = active[slot_i];
   const int s = tile_offsets[tile];
   const int len = tile_offsets[tile + 1] - s;
   const int wlo = min(lo, len), whi = min(hi, len);
@@ -397,6 +433,8 @@ __global__ void __launch_bounds__(64) k_composite(
   }
   __syncthreads();
   if (threadIdx.x == 0 && (s_live[0] | s_live[1]) && whi < len) next_active[atomicAdd(next_count, 1)] = tile;
+  __syncthreads();
+  }
 }
 
 // ------------------------------------------------------------------- feature compositing ----
@@ -485,7 +523,7 @@ int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mas
   LaunchScope scope(kKHits, 1, st);
   k_hit_masks_all<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, sc->n, fr->tile_offsets,
                                      fr->sorted_prims, fr->width, fr->height, ntx, fr->threshold,
-                                     (uint32_t*)mask_geo, fr->status);
+                                     miss_bound2(fr->threshold), (uint32_t*)mask_geo, fr->status);
   return cuda_check(cudaGetLastError(), "hit_masks");
 }
 
@@ -523,6 +561,12 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   }
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cnt, 0, 4 * (size_t)n, st));
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cursor, 0, 4 * (size_t)n, st));
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // CTAs walk the active-tile list with a grid stride, so a wave with few (or no) live tiles costs a
+  // launch of a few thousand CTAs, not one per tile of the image
+  const int wave_grid = std::min(T, sms * 16);
   const int nw = fr->num_waves > 0 ? fr->num_waves : (int)(sizeof(kDefaultWaves) / sizeof(int));
   int lo = 0;
   for (int w = 0; w < nw && lo < fr->tile_capacity; ++w) {
@@ -534,13 +578,14 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     const int32_t* act = s.active[cur];
     const int32_t* act_n = s.counters + kCtrActive0 + cur;
     { LaunchScope scope(kKHits, 1, st);
-    k_hits<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, fr->sorted_prims,
-                              W, H, ntx, fr->threshold, act, act_n, lo, hi, s.px_state, s.masks32, s.pair_base,
+    k_hits<<<wave_grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, fr->sorted_prims,
+                              W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
+                              s.masks32, s.pair_base,
                               s.prim_cnt, s.counters, fr->max_records, fr->status); }
     int rc = launch_prim_scan(s, n, nxt, fr->status, st);
     if (rc) return rc;
     { LaunchScope scope(kKFill, 1, st);
-    k_fill<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
+    k_fill<<<wave_grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
                               s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr,
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
@@ -553,7 +598,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                           fr->status, st);
     if (rc) return rc;
     { LaunchScope scope(kKComposite, 1, st);
-    k_composite<<<T, 64, 0, st>>>(fr->tile_offsets, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+    k_composite<<<std::min(T, sms * 32), 64, 0, st>>>(fr->tile_offsets, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
                                   fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
                                   keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,

@@ -9,11 +9,14 @@ namespace mlpsp {
 
 constexpr int kSortCap = 2048;
 
-template <int THREADS, int CAP>
+// IDSORT: the incoming list is in arbitrary order (straight from the binning scatter); it is first put
+// in ascending id order (written back as the canonical tile list), then sorted by key, in one kernel.
+template <int THREADS, int CAP, bool IDSORT>
 __global__ void __launch_bounds__(THREADS) k_sort_tiles(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
-    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_prims, int W, int H, int ts, int ntx,
-    int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, const int32_t* __restrict__ status) {
+    const int32_t* __restrict__ tile_offsets, int32_t* __restrict__ tile_prims, int W, int H, int ts, int ntx,
+    int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode,
+    const int32_t* __restrict__ status) {
   using Sort = BlockRadixSort<THREADS, CAP>;
   __shared__ typename Sort::Smem sm;
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
@@ -25,10 +28,24 @@ __global__ void __launch_bounds__(THREADS) k_sort_tiles(
   const int cx = min(tx * ts + (ts >> 1), W - 1), cy = min(ty * ts + (ts >> 1), H - 1);
   const int64_t pc = (int64_t)cy * W + cx;
   const V3 o = load3(rays_o, pc), d = load3(rays_d, pc);
+  int src = 0;
+  if (IDSORT) {
+    for (int i = threadIdx.x; i < len; i += THREADS) {
+      const int32_t p = tile_prims[s + i];
+      sm.key[0][i] = (uint32_t)p;
+      sm.val[0][i] = p;
+    }
+    __syncthreads();
+    src = Sort::sort(sm, len);
+    for (int i = threadIdx.x; i < len; i += THREADS) tile_prims[s + i] = sm.val[src][i];
+  }
   for (int i = threadIdx.x; i < len; i += THREADS) {
-    const int p = tile_prims[s + i];
+    const int p = IDSORT ? sm.val[src][i] : tile_prims[s + i];
     float key = MLPSP_SENTINEL_KEY;
-    if (p >= 0 && p < n) key = tile_key(load_geom(geom, p), o, d);
+    if (p >= 0 && p < n) {
+      const Geom g = load_geom(geom, p);
+      key = key_mode ? tile_key_euclid(g, o, d) : tile_key(g, o, d);
+    }
     sm.key[0][i] = __float_as_uint(key);
     sm.val[0][i] = p;
   }
@@ -40,15 +57,22 @@ __global__ void __launch_bounds__(THREADS) k_sort_tiles(
   }
 }
 
-int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st) {
+int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st, bool unordered_input) {
   const int T = num_tiles(fr->width, fr->height, fr->tile);
   const int ntx = (fr->width + fr->tile - 1) / fr->tile;
   MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
                 "tile_capacity must be in [1, %d]", kSortCap);
   LaunchScope scope(kKSort, 1, st);
-  k_sort_tiles<256, kSortCap><<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, sc->n,
-                                                fr->tile_offsets, fr->tile_prims, fr->width, fr->height, fr->tile,
-                                                ntx, fr->sorted_prims, keys_out, fr->status);
+  if (unordered_input)
+    k_sort_tiles<256, kSortCap, true><<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, sc->n,
+                                                        fr->tile_offsets, fr->tile_prims, fr->width, fr->height,
+                                                        fr->tile, ntx, fr->sorted_prims, keys_out, fr->sort_key,
+                                                        fr->status);
+  else
+    k_sort_tiles<256, kSortCap, false><<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, sc->n,
+                                                         fr->tile_offsets, fr->tile_prims, fr->width, fr->height,
+                                                         fr->tile, ntx, fr->sorted_prims, keys_out, fr->sort_key,
+                                                         fr->status);
   return cuda_check(cudaGetLastError(), "sort_tiles");
 }
 

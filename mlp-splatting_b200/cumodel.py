@@ -193,7 +193,7 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         return self._renderers[key]
 
     def _render(self, ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix, culled_prim_indices,
-                tile_offsets, want_depth, path_name, want_feat=False):
+                tile_offsets, want_depth, path_name, want_feat=False, sort_key=0):
         if self.image_size is None:
             raise ValueError("image_size must be set on NeuralPrimitiveSceneTileCUDA before calling forward.")
         W, H = self.image_size
@@ -227,7 +227,8 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         prec = L.PRECISION_F16 if (self.precision == "fp16" and scene.has_f16) else L.PRECISION_F32
         rgb, alpha = r.render(scene, ray_o.detach().float().contiguous(), ray_d.detach().float().contiguous(),
                               float(score_threshold), view=view, proj=proj, precision=prec, bg=bg,
-                              want_depth=want_depth, tile_lists=lists, path_name=path_name, want_feat=want_feat)
+                              want_depth=want_depth, tile_lists=lists, path_name=path_name, want_feat=want_feat,
+                              sort_key=sort_key)
         return r, rgb, alpha
 
     # ----------------------------------------------------------------------------- public ----
@@ -260,9 +261,12 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
     @torch.no_grad()
     def render_rgb_t_no_grad(self, ray_o, ray_d, score_threshold=1e-3, bg_color=None, view_matrix=None,
                              proj_matrix=None, culled_prim_indices=None, tile_offsets=None):
-        """(rgb, expected depth t [B,1], alpha) as cumodel.py:1385-1525."""
+        """(rgb, expected depth t [B,1], alpha) as cumodel.py:1385-1525.  The reference's expected-depth
+        kernel orders a tile by Euclidean depth along the tile-centre ray (np_tile_kernels.cu:5538-5543),
+        not by t*, so this call does too."""
         r, rgb, alpha = self._render(ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix,
-                                     culled_prim_indices, tile_offsets, True, "render_tiles_forward_tilecenter_with_t")
+                                     culled_prim_indices, tile_offsets, True, "render_tiles_forward_tilecenter_with_t",
+                                     sort_key=1)
         return rgb.clone(), r.depth_t.clone(), alpha.clone()
 
     @torch.no_grad()

@@ -191,7 +191,7 @@ class FrameRenderer:
         return self.scratch
 
     def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
-               want_mask_used, waves, want_feat=False, keep_records=False) -> L.Frame:
+               want_mask_used, waves, want_feat=False, keep_records=False, sort_key=0) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
         f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
@@ -226,6 +226,7 @@ class FrameRenderer:
         f.scratch, f.scratch_bytes = aligned, sc.numel() - (aligned - base)
         f.max_records = self.max_records
         f.keep_records = 1 if keep_records else 0
+        f.sort_key = int(sort_key)
         f.status = L.ptr(self.status)
         if waves:
             f.num_waves = len(waves)
@@ -262,7 +263,7 @@ class FrameRenderer:
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
                rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False,
-               keep_records=False):
+               keep_records=False, sort_key=0):
         """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling)."""
         lib, d = self.lib, self.device
         if precision is None:
@@ -290,7 +291,7 @@ class FrameRenderer:
                                                           self.capacity, scene.n, L.ptr(self.status), st),
                             "mlpsp_validate_tile_lists")
                 f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves,
-                                want_feat=want_feat, keep_records=keep_records)
+                                want_feat=want_feat, keep_records=keep_records, sort_key=sort_key)
                 self._last_frame = (f, scene)
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")
@@ -359,11 +360,11 @@ class FrameRenderer:
                 return self.tile_prims[:stats.pairs], self.tile_offsets
             raise RenderError("mlpsp_bin_tiles: pair buffer kept overflowing")
 
-    def sort(self, scene: PackedScene, rays_o, rays_d_unit, pairs, want_keys=False):
+    def sort(self, scene: PackedScene, rays_o, rays_d_unit, pairs, want_keys=False, sort_key=0):
         lib, d = self.lib, self.device
         with torch.cuda.device(d):
             st = _stream_ptr(d)
-            f = self._frame(scene, rays_o, rays_d_unit, 0.5, 0, None, None, None, False, False, None)
+            f = self._frame(scene, rays_o, rays_d_unit, 0.5, 0, None, None, None, False, False, None, sort_key=sort_key)
             keys = torch.empty(max(pairs, 1), device=d, dtype=torch.float32) if want_keys else None
             L.check(lib.mlpsp_sort_tiles(C.byref(scene.c), C.byref(f), L.ptr(keys), st), "mlpsp_sort_tiles")
             return (self.sorted_prims[:pairs], keys[:pairs]) if want_keys else self.sorted_prims[:pairs]

@@ -30,6 +30,9 @@ def build(ref_root="/root/reference", verbose=False):
     from torch.utils.cpp_extension import load
     load(name=NAME, sources=[src], build_directory=OUT, verbose=verbose, is_python_module=True,
          extra_cuda_cflags=["-DMLPSP_MAX_TILE_PRIMS=1536", "-lineinfo"], with_cuda=True)
+    obj = os.path.join(OUT, "np_tile_kernels.cuda.o")   # only the module travels to the GPU box
+    if os.path.exists(so) and os.path.exists(obj):
+        os.remove(obj)
     return so if os.path.exists(so) else None
 
 

@@ -149,6 +149,13 @@ static inline float tile_key(const float* g, v3 o, v3 d) {
   return (t > 0.f) ? t : ORC_SENTINEL;
 }
 
+/* Euclidean key of render_tiles_kernel_tilecenter_order_with_t (np_tile_kernels.cu:5538-5543) */
+static inline float tile_key_euclid(const float* g, v3 o, v3 d) {
+  const float vx = g[0] - o.x, vy = g[1] - o.y, vz = g[2] - o.z;
+  const float t = fmaf(vx, d.x, fmaf(vy, d.y, vz * d.z));
+  return (t > 0.f) ? t : ORC_SENTINEL;
+}
+
 typedef struct { float t, dx, dy, dz, qx, qy, qz, decay; } hit_t;
 
 /* rotated-ellipsoid closest approach (np_tile_kernels.cu:659-711) */
@@ -289,7 +296,7 @@ static inline v3 ld3(const float* p, int64_t i) { v3 r = { p[i*3], p[i*3+1], p[i
 /* per-tile stable ascending sort by the tile-centre key; keys_out may be NULL */
 void orc_sort_tiles(const float* rays_o, const float* rays_d, const float* geom, int n,
                     const int32_t* tile_offsets, const int32_t* tile_prims, int W, int H, int ts,
-                    int32_t* sorted_prims, float* keys_out) {
+                    int32_t* sorted_prims, float* keys_out, int key_mode) {
   const int ntx = (W + ts - 1) / ts, nty = (H + ts - 1) / ts;
   #pragma omp parallel for schedule(dynamic, 8)
   for (int tile = 0; tile < ntx * nty; ++tile) {
@@ -304,7 +311,7 @@ void orc_sort_tiles(const float* rays_o, const float* rays_d, const float* geom,
     for (int i = s; i < e; ++i) {
       const int p = tile_prims[i];
       float k = ORC_SENTINEL;
-      if (p >= 0 && p < n) k = tile_key(geom + (size_t)p * 16, o, d);
+      if (p >= 0 && p < n) k = key_mode ? tile_key_euclid(geom + (size_t)p * 16, o, d) : tile_key(geom + (size_t)p * 16, o, d);
       it[i - s].key = k; it[i - s].pos = i - s; it[i - s].id = p;
     }
     qsort(it, (size_t)(e - s), sizeof(sort_item), cmp_item);

@@ -132,13 +132,14 @@ def validate_lists(tile_offsets, prims, capacity, n):
     return int(st[0]), int(st[1])
 
 
-def sort_tiles(rays_o, rays_d, geom, tile_offsets, tile_prims, W, H, tile, want_keys=False):
+def sort_tiles(rays_o, rays_d, geom, tile_offsets, tile_prims, W, H, tile, want_keys=False, key_mode=0):
     ro, rd, geom = _f32(rays_o), _f32(rays_d), _f32(geom)
     off, pr = _i32(tile_offsets), _i32(tile_prims)
     out = np.empty_like(pr)
     keys = np.empty(pr.size, np.float32) if want_keys else None
     lib().orc_sort_tiles(_p(ro), _p(rd), _p(geom), C.c_int(geom.shape[0]), _p(off, C.c_int32),
-                         _p(pr, C.c_int32), C.c_int(W), C.c_int(H), C.c_int(tile), _p(out, C.c_int32), _p(keys))
+                         _p(pr, C.c_int32), C.c_int(W), C.c_int(H), C.c_int(tile), _p(out, C.c_int32), _p(keys),
+                         C.c_int(key_mode))
     return (out, keys) if want_keys else out
 
 

@@ -18,7 +18,7 @@ def oracle_inputs(scene, cam):
 
 
 def oracle_frame(scene, cam, thr, precision=0, tile=8, capacity=1536, want_records=False, feat=False,
-                 want_masks=True):
+                 want_masks=True, key_mode=0):
     """bin -> validate -> sort -> render on the CPU oracle; returns a dict of every stage's output."""
     W, H = cam["W"], cam["H"]
     geom, rd = oracle_inputs(scene, cam)
@@ -27,7 +27,7 @@ def oracle_frame(scene, cam, thr, precision=0, tile=8, capacity=1536, want_recor
     out = dict(geom=geom, rays_d_unit=rd, tile_prims=prims, tile_offsets=off, status=(bits, mx))
     if bits:
         return out
-    sp, keys = orc.sort_tiles(cam["rays_o"], rd, geom, off, prims, W, H, tile, want_keys=True)
+    sp, keys = orc.sort_tiles(cam["rays_o"], rd, geom, off, prims, W, H, tile, want_keys=True, key_mode=key_mode)
     res = orc.render(cam["rays_o"], rd, geom, off, sp, W, H, tile, thr, [scene[k] for k in WKEYS],
                      scene["freq"], scene["att"], precision=precision,
                      feat_attr=scene.get("feat_attr") if feat else None, want_masks=want_masks,

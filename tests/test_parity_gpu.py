@@ -86,6 +86,24 @@ def test_bin_sort_hits_bit_exact(dev, name, thr):
     np.testing.assert_array_equal(mg, f["render"].mask_geo)
 
 
+def test_euclidean_sort_key_bit_exact(dev):
+    """sort_key=1: the ordering of the reference's expected-depth kernel (np_tile_kernels.cu:5538-5543)."""
+    scene, cam = small_case(**CASES["dense"])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, key_mode=1)
+    f0 = oracle_frame(scene, cam, 5e-3, precision=0, key_mode=0, want_masks=False)
+    assert not np.array_equal(f["sorted_prims"], f0["sorted_prims"])
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    prims, _offs = r.bin(ps, cam["view"], cam["proj"], 5e-3)
+    sp, keys = r.sort(ps, _t(cam["rays_o"], dev), _t(f["rays_d_unit"], dev), int(prims.numel()), want_keys=True, sort_key=1)
+    np.testing.assert_array_equal(keys.cpu().numpy().view(np.uint32), f["keys"].view(np.uint32))
+    np.testing.assert_array_equal(sp.cpu().numpy(), f["sorted_prims"])
+    rgb, _ = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, view=cam["view"], proj=cam["proj"],
+                      precision=0, want_depth=True, sort_key=1)
+    np.testing.assert_allclose(rgb.cpu().numpy(), f["render"].rgb, atol=IMG_TOL_F32)
+    vis = f["render"].alpha > 1e-3
+    np.testing.assert_allclose(r.depth_t.cpu().numpy()[vis, 0], f["render"].depth_t[vis], rtol=1e-4, atol=1e-4)
+
+
 def _compare_used(mask_gpu, res, tile_offsets, cam, margin):
     """Exact equality of consumed-record masks outside pixels the oracle flags as borderline."""
     W, H = cam["W"], cam["H"]
@@ -400,7 +418,9 @@ def test_module_surface_matches_reference_class(dev):
     rgb2, t, alpha = m.render_rgb_t_no_grad(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3,
                                             view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
     assert alpha.shape == (cam["W"] * cam["H"], 1) and t.shape == alpha.shape
-    np.testing.assert_allclose(alpha.cpu().numpy()[:, 0], f["render"].alpha, atol=IMG_TOL_F32)
+    fe = oracle_frame(scene, cam, 5e-3, precision=0, key_mode=1, want_masks=False)   # the expected-depth kernel's order
+    np.testing.assert_allclose(alpha.cpu().numpy()[:, 0], fe["render"].alpha, atol=IMG_TOL_F32)
+    np.testing.assert_allclose(rgb2.cpu().numpy(), fe["render"].rgb, atol=IMG_TOL_F32)
     # in-place parameter edits are picked up (packed scene is re-keyed on tensor versions)
     with torch.no_grad():
         m.b3[:, 3] -= 5.0
