@@ -35,7 +35,7 @@ constexpr int kWeightBytes = kOffBias + 4 * (kH + kH + 4);  // 8464, a multiple 
 constexpr int kRows = kRowsPerItem;      // 128 = MMA M
 constexpr int kA1Bytes = (kK1 / 8) * kRows * 16;  // 20480: [10][128][8 halves]
 constexpr int kA2Bytes = (kH / 8) * kRows * 16;   // 8192:  [4][128][8 halves]
-constexpr int kSmemBytes = kWeightBytes + kA1Bytes + kA2Bytes + 64;
+constexpr int kSmemBytes = kWeightBytes + kA1Bytes + 64;   // the hidden-activation tile reuses the layer-1 A tile
 constexpr int kTmemCols = 64;            // D1 [0,32)  D2 [32,64)  D3 reuses [0,16)
 constexpr int kSpinLimit = 1 << 20;
 
@@ -124,21 +124,26 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// hidden layer epilogue: +bias, ReLU, fp16, write this thread's row of the next A tile
+// hidden layer epilogue: +bias, ReLU, fp16, write this thread's row of the next A tile.
+// Returns the largest |pre-activation| as an unsigned bit pattern (NaN and inf compare above every
+// finite value), so the caller needs one comparison per layer to detect a non-finite sum or one that
+// rounds to +inf in binary16 (rgb_wmma.cuh:179-181 checks the same two conditions per element).
 template <bool KEEP>
-__device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const float* bias, char* a2, int row, bool valid,
-                                               uint32_t& relu_mask) {
-  bool bad = false;
+__device__ __forceinline__ uint32_t hidden_to_smem(const uint32_t (&acc)[32], const float* bias, char* a2, int row,
+                                                   uint32_t& relu_mask) {
+  uint32_t worst = 0u;
   relu_mask = 0u;
 #pragma unroll
   for (int kc = 0; kc < 4; ++kc) {
+    const float4 b0 = *reinterpret_cast<const float4*>(bias + kc * 8);
+    const float4 b1 = *reinterpret_cast<const float4*>(bias + kc * 8 + 4);
+    const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
     uint32_t w[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int j = kc * 8 + q * 2;
-      const float v0 = __uint_as_float(acc[j]) + bias[j], v1 = __uint_as_float(acc[j + 1]) + bias[j + 1];
-      // non-finite sums, or values that round to +inf in binary16, are reported (rgb_wmma.cuh:179-181)
-      bad |= !(fabsf(v0) < 65520.f) || !(fabsf(v1) < 65520.f);
+      const float v0 = __uint_as_float(acc[j]) + bb[q * 2], v1 = __uint_as_float(acc[j + 1]) + bb[q * 2 + 1];
+      worst = max(worst, max(__float_as_uint(v0) & 0x7fffffffu, __float_as_uint(v1) & 0x7fffffffu));
       if (KEEP) {
         relu_mask |= (v0 > 0.f ? 1u : 0u) << j;
         relu_mask |= (v1 > 0.f ? 1u : 0u) << (j + 1);
@@ -147,8 +152,10 @@ __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const 
     }
     *reinterpret_cast<uint4*>(a2 + kc * (kRows * 16) + row * 16) = make_uint4(w[0], w[1], w[2], w[3]);
   }
-  return bad && valid;
+  return worst;
 }
+
+constexpr uint32_t kHalfOverflowBits = 0x477ff000u;   // 65520.0f: the smallest magnitude that rounds to inf in binary16
 
 template <bool KEEP>
 __global__ void __launch_bounds__(kRows) k_mlp_tc(
@@ -159,8 +166,8 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
   extern __shared__ __align__(128) char smem[];
   char* s_w = smem;
   char* s_a1 = smem + kWeightBytes;          // 8464 is a multiple of 16
-  char* s_a2 = s_a1 + kA1Bytes;
-  uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_a2 + kA2Bytes);   // [0] weights, [1] mma
+  char* s_a2 = s_a1;                         // written only after the layer-1 MMAs have finished reading s_a1
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_a1 + kA1Bytes);   // [0] weights, [1] mma
   uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2);        // [0] tmem base, [1] work item
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -209,16 +216,17 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
     if (valid) r = rec_in[pbase + wk.y + tid];
     {
       const float v6[6] = {r.rdx, r.rdy, r.rdz, r.dx, r.dy, r.dz};
+      // rows past the end of the primitive's records encode the zero vector; their results are never stored
       float sn[36], cs[36];
 #pragma unroll
-      for (int c = 0; c < 6; ++c)
+      for (int c = 0; c < 6; ++c) {
+        bad |= valid && !(fabsf(v6[c]) < 1.0e30f);   // a finite input gives finite phases (freq * att <= 101)
 #pragma unroll
         for (int f = 0; f < 6; ++f) {
           const float ph = v6[c] * fr[f] * at[f];
-          sn[c * 6 + f] = valid ? __sinf(ph) : 0.f;
-          cs[c * 6 + f] = valid ? __cosf(ph) : 0.f;
-          bad |= valid && !(fabsf(ph) < 3.0e38f);
+          __sincosf(ph, &sn[c * 6 + f], &cs[c * 6 + f]);
         }
+      }
       // k index: 0..35 sin block, 36..71 cos block, 72..79 zero (np_tile_kernels.cu:329-343)
 #pragma unroll
       for (int kc = 0; kc < 10; ++kc) {
@@ -257,7 +265,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
       uint32_t acc[32];
       if (ok) {
         tmem_ld32(trow, acc);
-        bad |= hidden_to_smem<KEEP>(acc, s_bias, s_a2, tid, valid, relu1);
+        bad |= valid && hidden_to_smem<KEEP>(acc, s_bias, s_a2, tid, relu1) >= kHalfOverflowBits;
       }
     }
     fence_async_smem();
@@ -279,7 +287,7 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
       uint32_t acc[32];
       if (ok) {
         tmem_ld32(trow + 32, acc);
-        bad |= hidden_to_smem<KEEP>(acc, s_bias + kH, s_a2, tid, valid, relu2);   // layer-2 MMAs have finished reading s_a2
+        bad |= valid && hidden_to_smem<KEEP>(acc, s_bias + kH, s_a2, tid, relu2) >= kHalfOverflowBits;   // layer-2 MMAs have finished reading s_a2
       }
     }
     fence_async_smem();
@@ -382,8 +390,9 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // tensor memory: 512 columns per SM / 64 per CTA = at most 8 resident CTAs; shared memory allows 6
-  const int grid = sms * 6;
+  // tensor memory: 512 columns per SM / 64 per CTA = at most 8 resident CTAs; shared memory and
+  // registers (64 per thread) allow 7
+  const int grid = sms * 7;
   LaunchScope scope(kKMlp, 1, st);
   if (rec_ext)
     k_mlp_tc<true><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, prim_off, work,
