@@ -51,7 +51,9 @@ extern "C" {
 #define MLPSP_ST_RECORD_OVERFLOW 16  /* a wave produced more records than max_records */
 #define MLPSP_ST_NUMERIC 64          /* non-finite operand/activation in the fp16 evaluator */
 #define MLPSP_ST_TIMEOUT 128         /* a bounded device-side wait gave up */
-#define MLPSP_ST_FATAL (1 | 2 | 4 | 8 | 16 | 128)
+#define MLPSP_ST_TILE_ORIGINS 256    /* ray-cone culling: a tile's rays do not share one origin */
+#define MLPSP_ST_CONE_TOO_WIDE 512   /* ray-cone culling: a tile's ray cone spans >= 90 degrees */
+#define MLPSP_ST_FATAL (1 | 2 | 4 | 8 | 16 | 128 | 256 | 512)
 
 #define MLPSP_PRECISION_F32 0  /* scalar FP32 evaluator (np_tile_kernels.cu:312-380) */
 #define MLPSP_PRECISION_F16 1  /* fp16 operands, FP32 accumulate, tcgen05 (rgb_wmma.cuh:75-223) */
@@ -153,6 +155,20 @@ int64_t mlpsp_frame_scratch_bytes(int32_t n, int32_t width, int32_t height, int3
 /* Screen-space culling: cumodel.py:994-1070 (overlap predicate, tile-major lists, ascending id).
  * Writes frame->tile_offsets, frame->tile_prims; status words 1,2 and bits 2,8. */
 int mlpsp_bin_tiles(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
+
+/* Culling for mosaic frames whose tiles come from different views
+ * (build_tilecenter_culling_from_tile_views, cumodel.py:838-949): tile t uses view tile_view_ids[t]
+ * (device int32[T], values in [0, num_views)); view_matrices is HOST [num_views*16] row-major;
+ * frame->proj is shared by all views, frame->view is ignored. */
+int mlpsp_bin_tiles_mosaic(const mlpsp_scene* scene, const mlpsp_frame* frame, const int32_t* tile_view_ids,
+                           const float* view_matrices, int32_t num_views, void* stream);
+
+/* Conservative culling from the actual rays, for cameras a projection matrix cannot describe
+ * (ray_cone_candidates, scannet/camera.py:102-146): per tile the cone around its 64 rays (pixels
+ * clamped to the image), per primitive its enclosing sphere of radius max scale * sqrt(-2 ln thr);
+ * a primitive is kept when the sphere touches the cone.  Reads frame->rays_o and frame->rays_d (any
+ * length; normalised inside), writes frame->tile_offsets / tile_prims (ascending id). */
+int mlpsp_bin_tiles_raycone(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
 
 /* validate_tile_candidate_capacity (np_tile_kernels.cu:4485-4589) for caller-supplied lists of
  * `pairs` candidates. */

@@ -16,6 +16,7 @@ ST_BITS, ST_MAX_TILE_LEN, ST_PAIRS, ST_WAVES = 0, 1, 2, 3
 ST_RECORDS_LO, ST_USED_LO, ST_WAVE_RECORDS, ST_WORK_ITEMS = 4, 6, 8, 9
 BIT_BAD_OFFSETS, BIT_TILE_CAPACITY, BIT_BAD_IDS = 1, 2, 4
 BIT_PAIR_OVERFLOW, BIT_RECORD_OVERFLOW, BIT_NUMERIC, BIT_TIMEOUT = 8, 16, 64, 128
+BIT_TILE_ORIGINS, BIT_CONE_TOO_WIDE = 256, 512
 PRECISION_F32, PRECISION_F16 = 0, 1
 MAX_WAVES = 32
 GEOM_FLOATS = 16
@@ -61,6 +62,8 @@ _SIGS = {
     "mlpsp_timing_collect": (C.c_int, [C.POINTER(C.c_float), C.c_int32]),
     "mlpsp_frame_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
     "mlpsp_bin_tiles": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp]),
+    "mlpsp_bin_tiles_mosaic": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp, _fp, C.c_int32, _fp]),
+    "mlpsp_bin_tiles_raycone": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp]),
     "mlpsp_validate_tile_lists": (C.c_int, [_fp, _fp, C.c_int32, C.c_int64, C.c_int32, C.c_int32, _fp, _fp]),
     "mlpsp_sort_tiles": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp, _fp]),
     "mlpsp_hit_masks": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp, _fp]),

@@ -183,6 +183,28 @@ extern "C" int mlpsp_bin_tiles(const mlpsp_scene* sc, const mlpsp_frame* fr, voi
   return launch_bin(sc, fr, s, (cudaStream_t)stream);
 }
 
+extern "C" int mlpsp_bin_tiles_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const int32_t* tile_view_ids,
+                                      const float* view_matrices, int32_t num_views, void* stream) {
+  int rc = check_frame_common(sc, fr, "mlpsp_bin_tiles_mosaic");
+  if (rc) return rc;
+  MLPSP_REQUIRE(fr->proj && view_matrices && tile_view_ids, MLPSP_E_ARG, "mlpsp_bin_tiles_mosaic: matrices or tile views missing");
+  MLPSP_REQUIRE(num_views > 0, MLPSP_E_ARG, "view_matrices must contain at least one view");
+  Scratch s;
+  rc = get_scratch(sc, fr, s, "mlpsp_bin_tiles_mosaic");
+  if (rc) return rc;
+  return launch_bin_mosaic(sc, fr, s, tile_view_ids, view_matrices, num_views, (cudaStream_t)stream);
+}
+
+extern "C" int mlpsp_bin_tiles_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, void* stream) {
+  int rc = check_frame_common(sc, fr, "mlpsp_bin_tiles_raycone");
+  if (rc) return rc;
+  MLPSP_REQUIRE(fr->rays_o && fr->rays_d, MLPSP_E_ARG, "mlpsp_bin_tiles_raycone: rays missing");
+  Scratch s;
+  rc = get_scratch(sc, fr, s, "mlpsp_bin_tiles_raycone");
+  if (rc) return rc;
+  return launch_bin_raycone(sc, fr, s, (cudaStream_t)stream);
+}
+
 extern "C" int mlpsp_sort_tiles(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, void* stream) {
   int rc = check_frame_common(sc, fr, "mlpsp_sort_tiles");
   if (rc) return rc;

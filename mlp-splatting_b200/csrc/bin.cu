@@ -150,6 +150,30 @@ __global__ void k_bin_scatter(int n, int ntx, const uint2* __restrict__ rect, co
   });
 }
 
+// Mosaic frames: every tile is drawn from one of K views (build_tilecenter_culling_from_tile_views,
+// scannet/cumodel.py:838-949).  blockIdx.y selects the view; a primitive's rectangle under that view
+// contributes only the tiles assigned to it.
+constexpr int kViewBatch = 8;
+struct BinCams { BinCam cam[kViewBatch]; };
+
+template <bool SCATTER>
+__global__ void k_bin_views(const float4* __restrict__ geom, int n, BinCams cams, int view0,
+                            const int32_t* __restrict__ tile_view, int32_t* __restrict__ tile_cnt,
+                            const int32_t* __restrict__ tile_offsets, int32_t* __restrict__ tile_prims,
+                            const int32_t* __restrict__ status) {
+  if (SCATTER && (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL)) return;
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  const BinCam& cam = cams.cam[blockIdx.y];
+  const int view = view0 + blockIdx.y;
+  int r[4] = {1, 0, 1, 0};
+  const bool has = (p < n) && prim_rect(geom, p, cam, r);
+  for_each_tile(has, r[0], r[1], r[2], r[3], cam.ntx, p, [&](int t, int q) {
+    if (tile_view[t] != view) return;
+    if (SCATTER) tile_prims[tile_offsets[t] + atomicAdd(tile_cnt + t, 1)] = q;
+    else atomicAdd(tile_cnt + t, 1);
+  });
+}
+
 // ------------------------------------------------------------- multi-block exclusive scan ----
 __global__ void k_scan_partial(const int32_t* __restrict__ in, int64_t n, int32_t* __restrict__ blk) {
   __shared__ int warp_sums[32];
@@ -279,6 +303,171 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
     if (order_lists) k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);
   }
   return cuda_check(cudaGetLastError(), "bin");
+}
+
+// ------------------------------------------------------------------- ray-cone culling ----
+// scannet/camera.py:102-146.  One thread per tile builds the cone of the tile's 64 rays (pixel
+// coordinates clamped to the image, sums in pixel order); one thread per primitive then walks a
+// chunk of tiles whose cones sit in shared memory.
+struct Cone { float ox, oy, oz, ax, ay, az, cos_t, sin_t; };
+
+__device__ __forceinline__ void normalize3(float x, float y, float z, float& nx, float& ny, float& nz) {
+  const float s = ffma(z, z, ffma(y, y, fmul(x, x)));
+  const float nrm = fmaxf(__fsqrt_rn(s), 1e-12f);
+  nx = fdiv(x, nrm); ny = fdiv(y, nrm); nz = fdiv(z, nrm);
+}
+
+__global__ void k_tile_cones(const float* __restrict__ rays_o, const float* __restrict__ rays_d, int W, int H, int ntx,
+                             int T, Cone* __restrict__ cones, int32_t* __restrict__ status) {
+  const int tile = blockIdx.x * blockDim.x + threadIdx.x;
+  if (tile >= T) return;
+  const int tx = tile % ntx, ty = tile / ntx;
+  float sx = 0.f, sy = 0.f, sz = 0.f;
+  const int64_t p0 = (int64_t)min(ty * 8, H - 1) * W + min(tx * 8, W - 1);
+  const V3 o0 = load3(rays_o, p0);
+  bool bad_origin = false;
+  for (int k = 0; k < 64; ++k) {
+    const int64_t pix = (int64_t)min(ty * 8 + (k >> 3), H - 1) * W + min(tx * 8 + (k & 7), W - 1);
+    const V3 o = load3(rays_o, pix), d = load3(rays_d, pix);
+    bad_origin |= fabsf(fsub(o.x, o0.x)) > 1e-6f || fabsf(fsub(o.y, o0.y)) > 1e-6f || fabsf(fsub(o.z, o0.z)) > 1e-6f;
+    float nx, ny, nz;
+    normalize3(d.x, d.y, d.z, nx, ny, nz);
+    sx = fadd(sx, nx); sy = fadd(sy, ny); sz = fadd(sz, nz);
+  }
+  float ax, ay, az;
+  normalize3(fdiv(sx, 64.f), fdiv(sy, 64.f), fdiv(sz, 64.f), ax, ay, az);
+  float cmin = 2.f;
+  for (int k = 0; k < 64; ++k) {
+    const int64_t pix = (int64_t)min(ty * 8 + (k >> 3), H - 1) * W + min(tx * 8 + (k & 7), W - 1);
+    const V3 d = load3(rays_d, pix);
+    float nx, ny, nz;
+    normalize3(d.x, d.y, d.z, nx, ny, nz);
+    cmin = fminf(cmin, ffma(nz, az, ffma(ny, ay, fmul(nx, ax))));
+  }
+  cmin = fminf(1.f, fmaxf(-1.f, cmin));
+  Cone c;
+  c.ox = o0.x; c.oy = o0.y; c.oz = o0.z; c.ax = ax; c.ay = ay; c.az = az; c.cos_t = cmin;
+  c.sin_t = __fsqrt_rn(fmaxf(fsub(1.f, fmul(cmin, cmin)), 0.f));
+  cones[tile] = c;
+  if (bad_origin) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_TILE_ORIGINS);
+  if (!(cmin > 0.f)) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_CONE_TOO_WIDE);
+}
+
+__device__ __forceinline__ bool cone_keeps(const Cone& c, float px, float py, float pz, float radius) {
+  const float dx = fsub(px, c.ox), dy = fsub(py, c.oy), dz = fsub(pz, c.oz);
+  const float dist = __fsqrt_rn(ffma(dz, dz, ffma(dy, dy, fmul(dx, dx))));
+  const float dc = fmaxf(dist, 1e-20f);
+  const float ratio = fminf(1.f, fmaxf(0.f, fdiv(radius, dc)));
+  const float cos_b = fdiv(ffma(dz, c.az, ffma(dy, c.ay, fmul(dx, c.ax))), dc);
+  const float bound = fsub(fmul(c.cos_t, __fsqrt_rn(fmaxf(fsub(1.f, fmul(ratio, ratio)), 0.f))), fmul(c.sin_t, ratio));
+  return (dist <= radius) || (cos_b >= fsub(bound, 2e-6f));
+}
+
+constexpr int kConeChunk = 128;   // tiles per block, as the reference's tile_chunk
+
+template <bool SCATTER>
+__global__ void __launch_bounds__(256) k_cone_bin(const float4* __restrict__ geom, int n, const Cone* __restrict__ cones,
+                                                  int T, float radius_mult, int32_t* __restrict__ tile_cnt,
+                                                  const int32_t* __restrict__ tile_offsets,
+                                                  int32_t* __restrict__ tile_prims, const int32_t* __restrict__ status) {
+  __shared__ Cone s_cone[kConeChunk];
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int t0 = blockIdx.y * kConeChunk, nt = min(kConeChunk, T - t0);
+  for (int i = threadIdx.x; i < nt; i += 256) s_cone[i] = cones[t0 + i];
+  __syncthreads();
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  float px = 0.f, py = 0.f, pz = 0.f, radius = -1.f;
+  if (p < n) {
+    const float4 g0 = __ldg(geom + (size_t)p * 4);
+    px = g0.x; py = g0.y; pz = g0.z;
+    radius = fadd(fmul(fmul(__ldg(geom + (size_t)p * 4 + 1).w, radius_mult), 1.00001f), 1e-7f);
+  }
+  const int lane = threadIdx.x & 31;
+  for (int i = 0; i < nt; ++i) {
+    const bool keep = (p < n) && cone_keeps(s_cone[i], px, py, pz, radius);
+    const uint32_t m = __ballot_sync(0xffffffffu, keep);
+    if (m == 0u) continue;
+    int base = 0;
+    if (lane == 0) base = atomicAdd(tile_cnt + t0 + i, __popc(m));
+    if (SCATTER) {
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (keep) tile_prims[tile_offsets[t0 + i] + base + __popc(m & ((1u << lane) - 1u))] = p;
+    }
+  }
+}
+
+int launch_bin_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st) {
+  const int T = num_tiles(fr->width, fr->height, fr->tile);
+  const int ntx = (fr->width + 7) / 8;
+  MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
+                "tile_capacity must be in [1, %d]", kSortCap);
+  MLPSP_REQUIRE(sizeof(Cone) * (size_t)T <= 16 * (size_t)fr->width * fr->height, MLPSP_E_LIMIT, "cone scratch too small");
+  Cone* cones = reinterpret_cast<Cone*>(s.px_state);   // 32 B per tile inside the 16 B per pixel state array
+  const float rm = (float)sqrt(-2.0 * log((double)fr->threshold));
+  const int n = sc->n;
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_cnt, 0, 4 * (size_t)(T + 1), st));
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_fill, 0, 4 * (size_t)T, st));
+  LaunchScope scope(kKBin, 8, st);
+  k_tile_cones<<<(T + 127) / 128, 128, 0, st>>>(fr->rays_o, fr->rays_d, fr->width, fr->height, ntx, T, cones, fr->status);
+  const dim3 grid((std::max(n, 1) + 255) / 256, (T + kConeChunk - 1) / kConeChunk);
+  if (n > 0) k_cone_bin<false><<<grid, 256, 0, st>>>((const float4*)sc->geom, n, cones, T, rm, s.tile_cnt, nullptr, nullptr, fr->status);
+  int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
+  if (rc) return rc;
+  k_bin_finish<<<std::min(64, (T + 255) / 256), 256, 0, st>>>(s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
+                                                              fr->max_pairs, fr->status, s.counters);
+  if (n > 0) {
+    k_cone_bin<true><<<grid, 256, 0, st>>>((const float4*)sc->geom, n, cones, T, rm, s.tile_fill, fr->tile_offsets,
+                                           fr->tile_prims, fr->status);
+    k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);
+  }
+  return cuda_check(cudaGetLastError(), "bin_raycone");
+}
+
+static BinCam make_cam(const mlpsp_frame* fr, const float* view) {
+  BinCam cam;
+  for (int i = 0; i < 16; ++i) { cam.view[i] = view[i]; cam.proj[i] = fr->proj[i]; }
+  cam.radius_mult = (float)sqrt(-2.0 * log((double)fr->threshold));
+  const float fx = (cam.proj[0] * (float)fr->width) / 2.0f;
+  const float fy = (cam.proj[5] * (float)fr->height) / 2.0f;
+  cam.focal = (fx + fy) * 0.5f;
+  cam.W = fr->width; cam.H = fr->height; cam.ts = fr->tile;
+  cam.ntx = (fr->width + fr->tile - 1) / fr->tile;
+  cam.nty = (fr->height + fr->tile - 1) / fr->tile;
+  return cam;
+}
+
+int launch_bin_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, const int32_t* tile_view,
+                      const float* views_host, int num_views, cudaStream_t st) {
+  const int T = num_tiles(fr->width, fr->height, fr->tile);
+  MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
+                "tile_capacity must be in [1, %d]", kSortCap);
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_cnt, 0, 4 * (size_t)(T + 1), st));
+  MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_fill, 0, 4 * (size_t)T, st));
+  const int n = sc->n;
+  const int batches = (num_views + kViewBatch - 1) / kViewBatch;
+  LaunchScope scope(kKBin, 2 * batches + 5, st);
+  auto pass = [&](bool scatter) {
+    for (int v0 = 0; v0 < num_views && n > 0; v0 += kViewBatch) {
+      BinCams cams;
+      const int nv = std::min(kViewBatch, num_views - v0);
+      for (int v = 0; v < nv; ++v) cams.cam[v] = make_cam(fr, views_host + 16 * (size_t)(v0 + v));
+      const dim3 grid((n + 255) / 256, nv);
+      if (scatter)
+        k_bin_views<true><<<grid, 256, 0, st>>>((const float4*)sc->geom, n, cams, v0, tile_view, s.tile_fill,
+                                                fr->tile_offsets, fr->tile_prims, fr->status);
+      else
+        k_bin_views<false><<<grid, 256, 0, st>>>((const float4*)sc->geom, n, cams, v0, tile_view, s.tile_cnt,
+                                                 fr->tile_offsets, fr->tile_prims, fr->status);
+    }
+  };
+  pass(false);
+  int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
+  if (rc) return rc;
+  k_bin_finish<<<std::min(64, (T + 255) / 256), 256, 0, st>>>(s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
+                                                              fr->max_pairs, fr->status, s.counters);
+  pass(true);
+  if (n > 0) k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);
+  return cuda_check(cudaGetLastError(), "bin_mosaic");
 }
 
 }  // namespace mlpsp

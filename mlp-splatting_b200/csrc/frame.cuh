@@ -132,6 +132,9 @@ int cuda_check(cudaError_t e, const char* what);
 // stage launchers (defined in the .cu files)
 // order_lists = false leaves every tile list in scatter order for a following launch_sort(unordered_input = true)
 int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st, bool order_lists = true);
+int launch_bin_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, const int32_t* tile_view,
+                      const float* views_host, int num_views, cudaStream_t st);
+int launch_bin_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
 int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st,
                 bool unordered_input = false);
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st);

@@ -201,10 +201,16 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
             raise AssertionError("Tile renderer requires full-frame rays (B == W*H)")
         device = self._activate_cuda_device()
         self._resolve_tile_order_mode()
-        if getattr(self, "camera_mode", "legacy-centered") == "colmap-native":
-            raise ValueError("ray-cone culling for native COLMAP cameras is not part of this build")
         T = ((W + 7) // 8) * ((H + 7) // 8)
         lists = None
+        if getattr(self, "camera_mode", "legacy-centered") == "colmap-native":
+            if (culled_prim_indices is not None) or (tile_offsets is not None):
+                raise ValueError("Native camera culling must be derived from the actual rays")
+            from .camera import ray_cone_candidates
+            culled_prim_indices, tile_offsets = ray_cone_candidates(
+                ray_o.detach().float().contiguous(), ray_d.detach().float().contiguous(), self.positions.detach(),
+                self.log_scales.detach(), W, H, 8, float(score_threshold), scene=self.packed_scene(),
+                renderer=self._renderer(device))
         if (culled_prim_indices is not None) or (tile_offsets is not None):
             if culled_prim_indices is None or tile_offsets is None:
                 raise ValueError("Both culled_prim_indices and tile_offsets must be provided together.")
@@ -230,6 +236,36 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
                               want_depth=want_depth, tile_lists=lists, path_name=path_name, want_feat=want_feat,
                               sort_key=sort_key)
         return r, rgb, alpha
+
+    @torch.no_grad()
+    def build_tilecenter_culling_from_tile_views(self, tile_view_ids, view_matrices, proj_matrix,
+                                                 score_threshold: float = 1e-3, tile_size=None):
+        """Tile->primitive lists for a mosaic frame (per-tile view assignment), cumodel.py:838-949.
+        Returns (culled_prim_indices int32 [M], tile_offsets int32 [T+1]), ascending id inside a tile."""
+        if getattr(self, "camera_mode", "legacy-centered") == "colmap-native":
+            return None, None
+        if self.image_size is None:
+            raise ValueError("image_size must be set before building tile culling.")
+        device = self._activate_cuda_device()
+        ts = int(self.tile_size if tile_size is None else tile_size)
+        if ts <= 0:
+            raise ValueError("tile_size must be a positive integer.")
+        if ts != 8:
+            raise ValueError("this build renders 8x8 tiles only")
+        W, H = self.image_size
+        T = ((W + 7) // 8) * ((H + 7) // 8)
+        tv = torch.as_tensor(tile_view_ids).reshape(-1)
+        if tv.numel() != T:
+            raise ValueError(f"tile_view_ids length mismatch: got {tv.numel()}, expected {T}")
+        vm = torch.as_tensor(view_matrices)
+        if vm.ndim != 3 or tuple(vm.shape[1:]) != (4, 4):
+            raise ValueError("view_matrices must have shape (K,4,4)")
+        if int(vm.shape[0]) <= 0:
+            raise ValueError("view_matrices must contain at least one view")
+        prims, offs = self._renderer(device).bin_mosaic(self.packed_scene(), tv, vm.detach().float().cpu().numpy(),
+                                                        torch.as_tensor(proj_matrix).detach().float().cpu().numpy(),
+                                                        float(score_threshold))
+        return prims.clone(), offs.clone()
 
     # ----------------------------------------------------------------------------- public ----
     @torch.no_grad()

@@ -360,6 +360,53 @@ class FrameRenderer:
                 return self.tile_prims[:stats.pairs], self.tile_offsets
             raise RenderError("mlpsp_bin_tiles: pair buffer kept overflowing")
 
+    def bin_mosaic(self, scene: PackedScene, tile_view_ids, view_matrices, proj, threshold):
+        """Culling for a mosaic frame: tile t is seen from view tile_view_ids[t] (cumodel.py:838-949)."""
+        lib, d = self.lib, self.device
+        tv = torch.as_tensor(tile_view_ids).to(device=d, dtype=torch.int32).reshape(-1).contiguous()
+        if tv.numel() != self.T:
+            raise ValueError(f"tile_view_ids length mismatch: got {tv.numel()}, expected {self.T}")
+        views = np.ascontiguousarray(np.asarray(view_matrices, dtype=np.float32).reshape(-1, 16))
+        if views.shape[0] <= 0:
+            raise ValueError("view_matrices must contain at least one view")
+        if int(tv.min()) < 0 or int(tv.max()) >= views.shape[0]:
+            raise ValueError("tile_view_ids contains out-of-range view indices")
+        with torch.cuda.device(d):
+            st = _stream_ptr(d)
+            for _attempt in range(3):
+                L.check(lib.mlpsp_status_reset(L.ptr(self.status), st), "mlpsp_status_reset")
+                f = self._frame(scene, None, None, threshold, 0, views[0], proj, None, False, False, None)
+                L.check(lib.mlpsp_bin_tiles_mosaic(C.byref(scene.c), C.byref(f), L.ptr(tv), views.ctypes.data,
+                                                   views.shape[0], st), "mlpsp_bin_tiles_mosaic")
+                bits, stats = self._read_status()
+                self.last_stats = stats
+                if bits & L.BIT_TILE_CAPACITY:
+                    raise_for_status(bits, stats.max_tile_len, self.capacity, "mlpsp_bin_tiles_mosaic")
+                if bits & L.BIT_PAIR_OVERFLOW and self._grow(bits, stats):
+                    continue
+                return self.tile_prims[:stats.pairs], self.tile_offsets
+            raise RenderError("mlpsp_bin_tiles_mosaic: pair buffer kept overflowing")
+
+    def bin_raycone(self, scene: PackedScene, rays_o, rays_d, threshold):
+        """Ray-cone culling from the actual rays (scannet/camera.py:102-146): (ids, offsets, status bits)."""
+        lib, d = self.lib, self.device
+        with torch.cuda.device(d):
+            st = _stream_ptr(d)
+            for _attempt in range(3):
+                L.check(lib.mlpsp_status_reset(L.ptr(self.status), st), "mlpsp_status_reset")
+                f = self._frame(scene, rays_o, rays_d, threshold, 0, None, None, None, False, False, None)
+                L.check(lib.mlpsp_bin_tiles_raycone(C.byref(scene.c), C.byref(f), st), "mlpsp_bin_tiles_raycone")
+                bits, stats = self._read_status()
+                self.last_stats = stats
+                if bits & (L.BIT_TILE_ORIGINS | L.BIT_CONE_TOO_WIDE):
+                    return self.tile_prims[:0], self.tile_offsets, bits
+                if bits & L.BIT_TILE_CAPACITY:
+                    raise_for_status(bits, stats.max_tile_len, self.capacity, "mlpsp_bin_tiles_raycone")
+                if bits & L.BIT_PAIR_OVERFLOW and self._grow(bits, stats):
+                    continue
+                return self.tile_prims[:stats.pairs], self.tile_offsets, bits
+            raise RenderError("mlpsp_bin_tiles_raycone: pair buffer kept overflowing")
+
     def sort(self, scene: PackedScene, rays_o, rays_d_unit, pairs, want_keys=False, sort_key=0):
         lib, d = self.lib, self.device
         with torch.cuda.device(d):

@@ -270,6 +270,108 @@ void orc_bin_fill(const float* geom, int n, const float* view, const float* proj
   free(cur);
 }
 
+/* mosaic culling (cumodel.py:838-949): tile t is seen from view tile_view[t]; count (prims NULL) or fill */
+int64_t orc_bin_mosaic(const float* geom, int n, const float* views, int num_views, const int32_t* tile_view,
+                       const float* proj, int W, int H, int ts, float thr, int32_t* tile_offsets, int32_t* tile_prims) {
+  const int ntx = (W + ts - 1) / ts, nty = (H + ts - 1) / ts;
+  const int T = ntx * nty;
+  const float rm = orc_radius_multiplier(thr);
+  int32_t* cur = (int32_t*)calloc((size_t)T + 1, sizeof(int32_t));
+  if (tile_prims) memcpy(cur, tile_offsets, sizeof(int32_t) * (size_t)T);
+  for (int p = 0; p < n; ++p)
+    for (int v = 0; v < num_views; ++v) {
+      int r[4];
+      if (!prim_rect(geom + (size_t)p * 16, views + 16 * (size_t)v, proj, W, H, ts, rm, ntx, nty, r)) continue;
+      for (int ty = r[2]; ty <= r[3]; ++ty)
+        for (int tx = r[0]; tx <= r[1]; ++tx) {
+          const int t = ty * ntx + tx;
+          if (tile_view[t] != v) continue;
+          if (tile_prims) tile_prims[cur[t]++] = p; else cur[t]++;
+        }
+    }
+  int64_t acc = 0;
+  if (!tile_prims) {
+    for (int t = 0; t < T; ++t) { tile_offsets[t] = (int32_t)acc; acc += cur[t]; }
+    tile_offsets[T] = (int32_t)acc;
+  }
+  free(cur);
+  return acc;
+}
+
+/* ---- ray-cone culling (scannet/camera.py:102-146) ---- */
+static inline void nrm3(float x, float y, float z, float* o) {
+  const float s = fmaf(z, z, fmaf(y, y, x * x));
+  const float n = fmaxf(sqrtf(s), 1e-12f);
+  o[0] = x / n; o[1] = y / n; o[2] = z / n;
+}
+
+/* returns status bits: 256 = a tile's rays have different origins, 512 = a cone spans >= 90 degrees.
+ * tile_prims NULL: count pass (fills tile_offsets, returns total via *total). */
+int orc_bin_raycone(const float* geom, int n, const float* rays_o, const float* rays_d, int W, int H, float thr,
+                    int32_t* tile_offsets, int32_t* tile_prims, int64_t* total) {
+  const int ntx = (W + 7) / 8, nty = (H + 7) / 8, T = ntx * nty;
+  const float rm = orc_radius_multiplier(thr);
+  int status = 0;
+  float* cone = (float*)malloc(sizeof(float) * 8 * (size_t)T);
+  for (int t = 0; t < T; ++t) {
+    const int tx = t % ntx, ty = t / ntx;
+    float sx = 0.f, sy = 0.f, sz = 0.f, d[3];
+    int64_t p0 = 0;
+    for (int k = 0; k < 64; ++k) {
+      int x = tx * 8 + (k & 7), y = ty * 8 + (k >> 3);
+      if (x > W - 1) x = W - 1;
+      if (y > H - 1) y = H - 1;
+      const int64_t pix = (int64_t)y * W + x;
+      if (k == 0) p0 = pix;
+      for (int c = 0; c < 3; ++c) if (fabsf(rays_o[pix*3+c] - rays_o[p0*3+c]) > 1e-6f) status |= 256;
+      nrm3(rays_d[pix*3], rays_d[pix*3+1], rays_d[pix*3+2], d);
+      sx = sx + d[0]; sy = sy + d[1]; sz = sz + d[2];
+    }
+    float a[3];
+    nrm3(sx / 64.f, sy / 64.f, sz / 64.f, a);
+    float cmin = 2.f;
+    for (int k = 0; k < 64; ++k) {
+      int x = tx * 8 + (k & 7), y = ty * 8 + (k >> 3);
+      if (x > W - 1) x = W - 1;
+      if (y > H - 1) y = H - 1;
+      const int64_t pix = (int64_t)y * W + x;
+      nrm3(rays_d[pix*3], rays_d[pix*3+1], rays_d[pix*3+2], d);
+      cmin = fminf(cmin, fmaf(d[2], a[2], fmaf(d[1], a[1], d[0] * a[0])));
+    }
+    cmin = fminf(1.f, fmaxf(-1.f, cmin));
+    if (!(cmin > 0.f)) status |= 512;
+    float* c = cone + (size_t)t * 8;
+    c[0] = rays_o[p0*3]; c[1] = rays_o[p0*3+1]; c[2] = rays_o[p0*3+2]; c[3] = a[0]; c[4] = a[1]; c[5] = a[2];
+    c[6] = cmin; c[7] = sqrtf(fmaxf(1.f - cmin * cmin, 0.f));
+  }
+  int64_t acc = 0;
+  if (!status) {
+    for (int t = 0; t < T; ++t) {
+      const float* c = cone + (size_t)t * 8;
+      if (!tile_prims) tile_offsets[t] = (int32_t)acc;
+      int64_t w = tile_prims ? tile_offsets[t] : 0;
+      for (int p = 0; p < n; ++p) {
+        const float* g = geom + (size_t)p * 16;
+        const float radius = (g[7] * rm) * 1.00001f + 1e-7f;
+        const float dx = g[0] - c[0], dy = g[1] - c[1], dz = g[2] - c[2];
+        const float dist = sqrtf(fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
+        const float dc = fmaxf(dist, 1e-20f);
+        const float ratio = fminf(1.f, fmaxf(0.f, radius / dc));
+        const float cos_b = fmaf(dz, c[5], fmaf(dy, c[4], dx * c[3])) / dc;
+        const float bound = c[6] * sqrtf(fmaxf(1.f - ratio * ratio, 0.f)) - c[7] * ratio;
+        if ((dist <= radius) || (cos_b >= bound - 2e-6f)) {
+          if (tile_prims) tile_prims[w++] = p;
+          ++acc;
+        }
+      }
+    }
+    if (!tile_prims) tile_offsets[T] = (int32_t)acc;
+  }
+  free(cone);
+  if (total) *total = acc;
+  return status;
+}
+
 /* list validation (np_tile_kernels.cu:4485-4520): bit1 offsets, bit2 capacity, bit4 ids */
 void orc_validate_lists(const int32_t* tile_offsets, const int32_t* prims, int T, int M, int capacity,
                         int n, int32_t status[2]) {

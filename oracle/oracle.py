@@ -37,6 +37,7 @@ def lib():
         _LIB.orc_radius_multiplier.restype = C.c_float
         _LIB.orc_radius_multiplier.argtypes = [C.c_float]
         _LIB.orc_bin_count.restype = C.c_int64
+        _LIB.orc_bin_mosaic.restype = C.c_int64
         assert _LIB.orc_sizeof_render() == C.sizeof(_Render), "render_t layout mismatch"
     return _LIB
 
@@ -122,6 +123,33 @@ def bin_tiles(geom, view, proj, W, H, tile, thr):
     lib().orc_bin_fill(_p(geom), C.c_int(n), _p(view), _p(proj), C.c_int(W), C.c_int(H),
                        C.c_int(tile), C.c_float(thr), _p(off, C.c_int32), _p(prims, C.c_int32))
     return prims, off
+
+
+def bin_tiles_mosaic(geom, views, tile_view_ids, proj, W, H, tile, thr):
+    """Per-tile-view culling (cumodel.py:838-949): returns (culled_prim_indices, tile_offsets)."""
+    geom, views, proj = _f32(geom), _f32(views).reshape(-1, 16), _f32(proj).reshape(16)
+    tv = _i32(tile_view_ids)
+    off = np.zeros(tv.size + 1, np.int32)
+    args = (_p(geom), C.c_int(geom.shape[0]), _p(views), C.c_int(views.shape[0]), _p(tv, C.c_int32), _p(proj),
+            C.c_int(W), C.c_int(H), C.c_int(tile), C.c_float(thr), _p(off, C.c_int32))
+    total = lib().orc_bin_mosaic(*args, None)
+    prims = np.empty(int(total), np.int32)
+    lib().orc_bin_mosaic(*args, _p(prims, C.c_int32))
+    return prims, off
+
+
+def ray_cone_candidates(rays_o, rays_d, geom, W, H, thr):
+    """Ray-cone culling (scannet/camera.py:102-146): returns (ids, offsets, status bits)."""
+    ro, rd, geom = _f32(rays_o), _f32(rays_d), _f32(geom)
+    T = ((W + 7) // 8) * ((H + 7) // 8)
+    off = np.zeros(T + 1, np.int32)
+    total = C.c_int64(0)
+    args = (_p(geom), C.c_int(geom.shape[0]), _p(ro), _p(rd), C.c_int(W), C.c_int(H), C.c_float(thr), _p(off, C.c_int32))
+    st = lib().orc_bin_raycone(*args, None, C.byref(total))
+    prims = np.empty(int(total.value), np.int32)
+    if st == 0:
+        lib().orc_bin_raycone(*args, _p(prims, C.c_int32), C.byref(total))
+    return prims, off, int(st)
 
 
 def validate_lists(tile_offsets, prims, capacity, n):

@@ -9,6 +9,8 @@ Only device-agnostic reference functions are called, on CPU:
   scannet.cumodel.IntegratedPositionalEncoding                 -> encoding.npz
   NeuralPrimitiveSceneTileCUDA.build_tilecenter_culling_from_tile_views (its device check is
   pointed at the CPU for the call; the culling code itself is untouched)  -> culling.npz
+  the same method with four views and a random tile->view map                 -> mosaic.npz
+  scannet.camera.ray_cone_candidates                                           -> raycone.npz
   scannet.primitive_csr.group_records, scannet.primitive_gemm.prepare_groups -> grouping.npz
 The scene inputs come from this repository's seeded generator, so tests can rebuild them.
 """
@@ -74,6 +76,43 @@ def main(ref_root):
         out[f"{tag}_fcfg"] = np.array([mu, thr, az], np.float64)
         out[f"{tag}_ids"], out[f"{tag}_offsets"] = ids.numpy().astype(np.int32), offs.numpy().astype(np.int32)
     np.savez_compressed(os.path.join(HERE, "culling.npz"), **out)
+
+    # ---- mosaic culling: every tile drawn from one of four views -----------------------------
+    out = {}
+    for tag, (n, W, H, mu, thr, seed) in {"m1": (2000, 128, 96, -3.5, 5e-3, 2026), "m2": (800, 67, 45, -3.0, 1e-3, 21)}.items():
+        sc = syn.make_scene(n, seed=seed, mu=mu)
+        cams = [syn.make_camera(W, H, azimuth_deg=90.0 * k) for k in range(4)]
+        T = ((W + 7) // 8) * ((H + 7) // 8)
+        tv = np.random.default_rng(seed).integers(0, 4, T).astype(np.int64)
+        model = cm.NeuralPrimitiveSceneTileCUDA(num_primitives=n)
+        with torch.no_grad():
+            model.positions.copy_(torch.from_numpy(sc["positions"]))
+            model.log_scales.copy_(torch.from_numpy(sc["log_scales"]))
+        model.set_image_size(W, H)
+        model._activate_cuda_device = lambda: torch.device("cpu")
+        views = torch.from_numpy(np.stack([c["view"] for c in cams]))
+        ids, offs = model.build_tilecenter_culling_from_tile_views(torch.from_numpy(tv), views,
+                                                                   torch.from_numpy(cams[0]["proj"]),
+                                                                   score_threshold=thr, tile_size=8)
+        out[f"{tag}_cfg"] = np.array([n, W, H, seed], np.int64)
+        out[f"{tag}_fcfg"] = np.array([mu, thr], np.float64)
+        out[f"{tag}_tile_views"] = tv.astype(np.int32)
+        out[f"{tag}_ids"], out[f"{tag}_offsets"] = ids.numpy().astype(np.int32), offs.numpy().astype(np.int32)
+    np.savez_compressed(os.path.join(HERE, "mosaic.npz"), **out)
+
+    # ---- ray-cone culling (scannet/camera.py:102-146) --------------------------------------
+    from scannet.camera import ray_cone_candidates
+    out = {}
+    for tag, (n, W, H, mu, thr, az, seed) in {"r1": (2000, 128, 96, -3.5, 5e-3, 20.0, 2026),
+                                              "r2": (700, 45, 38, -2.8, 1e-3, 250.0, 8)}.items():
+        sc = syn.make_scene(n, seed=seed, mu=mu)
+        cam = syn.make_camera(W, H, azimuth_deg=az)
+        ids, offs = ray_cone_candidates(torch.from_numpy(cam["rays_o"]), torch.from_numpy(cam["rays_d"]),
+                                        torch.from_numpy(sc["positions"]), torch.from_numpy(sc["log_scales"]), W, H, 8, thr)
+        out[f"{tag}_cfg"] = np.array([n, W, H, seed], np.int64)
+        out[f"{tag}_fcfg"] = np.array([mu, thr, az], np.float64)
+        out[f"{tag}_ids"], out[f"{tag}_offsets"] = ids.numpy().astype(np.int32), offs.numpy().astype(np.int32)
+    np.savez_compressed(os.path.join(HERE, "raycone.npz"), **out)
 
     # ---- grouping -------------------------------------------------------------------------
     counts = [0, 1, 31, 32, 33, 511, 512, 513, 1700, 0]

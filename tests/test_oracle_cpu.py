@@ -68,6 +68,56 @@ def test_binning_matches_reference_culling(golden_dir, tag):
     np.testing.assert_array_equal(prims, canon)
 
 
+@pytest.mark.parametrize("tag", ["m1", "m2"])
+def test_mosaic_binning_matches_reference_culling(golden_dir, tag):
+    """build_tilecenter_culling_from_tile_views with four views and a random tile->view map."""
+    g = np.load(os.path.join(golden_dir, "mosaic.npz"))
+    n, W, H, seed = [int(v) for v in g[f"{tag}_cfg"]]
+    mu, thr = [float(v) for v in g[f"{tag}_fcfg"]]
+    sc = syn.make_scene(n, seed=seed, mu=mu)
+    cams = [syn.make_camera(W, H, azimuth_deg=90.0 * k) for k in range(4)]
+    geom = orc.pack_geometry(sc["positions"], sc["log_scales"], orc.normalize_rows(sc["quats"]))
+    prims, off = orc.bin_tiles_mosaic(geom, np.stack([c["view"] for c in cams]), g[f"{tag}_tile_views"],
+                                      cams[0]["proj"], W, H, 8, thr)
+    np.testing.assert_array_equal(off, g[f"{tag}_offsets"])
+    tile_of = np.repeat(np.arange(off.size - 1), np.diff(off))
+    ref_ids = g[f"{tag}_ids"]
+    np.testing.assert_array_equal(prims, ref_ids[np.lexsort((ref_ids, tile_of))])
+    assert prims.size > 1000
+
+
+@pytest.mark.parametrize("tag", ["r1", "r2"])
+def test_ray_cone_culling_matches_reference(golden_dir, tag):
+    """ray_cone_candidates (scannet/camera.py:102-146).  The reference reduces the 64 ray directions of a
+    tile with torch ops whose summation order is not specified, so candidates within float noise of the
+    cone bound may differ: the sets must agree except for a handful of such pairs, and the oracle must
+    never drop a primitive the exact renderer hits."""
+    g = np.load(os.path.join(golden_dir, "raycone.npz"))
+    n, W, H, seed = [int(v) for v in g[f"{tag}_cfg"]]
+    mu, thr, az = [float(v) for v in g[f"{tag}_fcfg"]]
+    sc = syn.make_scene(n, seed=seed, mu=mu)
+    cam = syn.make_camera(W, H, azimuth_deg=az)
+    geom = orc.pack_geometry(sc["positions"], sc["log_scales"], orc.normalize_rows(sc["quats"]))
+    ids, off, st = orc.ray_cone_candidates(cam["rays_o"], cam["rays_d"], geom, W, H, thr)
+    assert st == 0
+    T = off.size - 1
+    mine = set(zip(np.repeat(np.arange(T), np.diff(off)).tolist(), ids.tolist()))
+    ref_off = g[f"{tag}_offsets"]
+    ref = set(zip(np.repeat(np.arange(T), np.diff(ref_off)).tolist(), g[f"{tag}_ids"].tolist()))
+    assert len(mine ^ ref) <= max(2, len(ref) // 5000), (len(mine), len(ref), len(mine ^ ref))
+    # conservative: contains every pair of the screen-space lists that has a geometric hit
+    rd = orc.normalize_rows(cam["rays_d"])
+    p2, o2 = orc.bin_tiles(geom, cam["view"], cam["proj"], W, H, 8, thr)
+    sp = orc.sort_tiles(cam["rays_o"], rd, geom, o2, p2, W, H, 8)
+    res = orc.render(cam["rays_o"], rd, geom, o2, sp, W, H, 8, thr, [sc[k] for k in WKEYS], sc["freq"], sc["att"])
+    tile_of = np.repeat(np.arange(T), np.diff(o2))
+    hit_pairs = set(zip(tile_of[res.mask_geo != 0].tolist(), sp[res.mask_geo != 0].tolist()))
+    assert hit_pairs <= mine
+    # mixed origins inside a tile are refused
+    ro = cam["rays_o"].copy(); ro[3, 0] += 0.5
+    assert orc.ray_cone_candidates(ro, cam["rays_d"], geom, W, H, thr)[2] & 256
+
+
 def test_grouping_matches_reference(golden_dir):
     """group_records (scannet/primitive_csr.py:23-29), prepare_groups (scannet/primitive_gemm.py:186-203)."""
     g = np.load(os.path.join(golden_dir, "grouping.npz"))

@@ -86,6 +86,79 @@ def test_bin_sort_hits_bit_exact(dev, name, thr):
     np.testing.assert_array_equal(mg, f["render"].mask_geo)
 
 
+def test_mosaic_culling_bit_exact_and_renders(dev):
+    """Per-tile view assignment (cumodel.py:838-949): lists equal the oracle's; the mosaic renders."""
+    from mlp_splatting_b200 import synthetic as syn
+    from mlp_splatting_b200.cumodel import NeuralPrimitiveSceneTileCUDA
+    from oracle import oracle as orc
+    W, H, n, thr = 128, 96, 2000, 5e-3
+    scene = syn.make_scene(n, seed=2026)
+    cams = [syn.make_camera(W, H, azimuth_deg=90.0 * k) for k in range(4)]
+    T = ((W + 7) // 8) * ((H + 7) // 8)
+    tv = np.random.default_rng(3).integers(0, 4, T).astype(np.int32)
+    views = np.stack([c["view"] for c in cams])
+    geom = orc.pack_geometry(scene["positions"], scene["log_scales"], orc.normalize_rows(scene["quats"]))
+    want_p, want_o = orc.bin_tiles_mosaic(geom, views, tv, cams[0]["proj"], W, H, 8, thr)
+    m = NeuralPrimitiveSceneTileCUDA(num_primitives=n, precision="fp32").to(dev)
+    with torch.no_grad():
+        for k in ("positions", "log_scales", "quats") + WKEYS:
+            getattr(m, k).copy_(_t(scene[k], dev))
+    m.set_image_size(W, H)
+    ids, offs = m.build_tilecenter_culling_from_tile_views(_t(tv, dev), _t(views, dev), _t(cams[0]["proj"], dev), thr)
+    np.testing.assert_array_equal(offs.cpu().numpy(), want_o)
+    np.testing.assert_array_equal(ids.cpu().numpy(), want_p)
+    # mosaic rays: every tile takes its rays from its own view (tile boundaries = view boundaries here)
+    ntx = (W + 7) // 8
+    ro = np.zeros((W * H, 3), np.float32); rd = np.zeros((W * H, 3), np.float32)
+    pix = np.arange(W * H); tile_of_pix = (pix // W // 8) * ntx + (pix % W) // 8
+    for k, c in enumerate(cams):
+        sel = tv[tile_of_pix] == k
+        ro[sel], rd[sel] = c["rays_o"][sel], c["rays_d"][sel]
+    rgb = m(_t(ro, dev), _t(rd, dev), score_threshold=thr, culled_prim_indices=ids, tile_offsets=offs)
+    rdn = orc.normalize_rows(rd)
+    sp = orc.sort_tiles(ro, rdn, geom, want_o, want_p, W, H, 8)
+    res = orc.render(ro, rdn, geom, want_o, sp, W, H, 8, thr, [scene[k] for k in WKEYS], scene["freq"], scene["att"],
+                     precision=0, want_masks=False)
+    np.testing.assert_allclose(rgb.cpu().numpy(), res.rgb, atol=IMG_TOL_F32)
+    with pytest.raises(ValueError, match="out-of-range view indices"):
+        m.build_tilecenter_culling_from_tile_views(_t(tv + 9, dev), _t(views, dev), _t(cams[0]["proj"], dev), thr)
+
+
+def test_ray_cone_culling_bit_exact_and_native_camera_mode(dev):
+    """ray_cone_candidates (scannet/camera.py:102-146) and forward() in colmap-native camera mode."""
+    from mlp_splatting_b200.camera import ray_cone_candidates
+    from mlp_splatting_b200.cumodel import NeuralPrimitiveSceneTileCUDA
+    from oracle import oracle as orc
+    scene, cam = small_case(**CASES["ragged"])
+    geom = orc.pack_geometry(scene["positions"], scene["log_scales"], orc.normalize_rows(scene["quats"]))
+    want_ids, want_off, st = orc.ray_cone_candidates(cam["rays_o"], cam["rays_d"], geom, cam["W"], cam["H"], 5e-3)
+    assert st == 0
+    ids, offs = ray_cone_candidates(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), _t(scene["positions"], dev),
+                                    _t(scene["log_scales"], dev), cam["W"], cam["H"], 8, 5e-3)
+    np.testing.assert_array_equal(offs.cpu().numpy(), want_off)
+    np.testing.assert_array_equal(ids.cpu().numpy(), want_ids)
+    ro = cam["rays_o"].copy(); ro[5, 1] += 0.25
+    with pytest.raises(ValueError, match="single camera origin"):
+        ray_cone_candidates(_t(ro, dev), _t(cam["rays_d"], dev), _t(scene["positions"], dev), _t(scene["log_scales"], dev),
+                            cam["W"], cam["H"], 8, 5e-3)
+    m = NeuralPrimitiveSceneTileCUDA(num_primitives=scene["positions"].shape[0], precision="fp32").to(dev)
+    with torch.no_grad():
+        for k in ("positions", "log_scales", "quats") + WKEYS:
+            getattr(m, k).copy_(_t(scene[k], dev))
+    m.set_image_size(cam["W"], cam["H"])
+    m.camera_mode = "colmap-native"
+    rgb = m(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3)
+    rdn = orc.normalize_rows(cam["rays_d"])
+    sp = orc.sort_tiles(cam["rays_o"], rdn, geom, want_off, want_ids, cam["W"], cam["H"], 8)
+    res = orc.render(cam["rays_o"], rdn, geom, want_off, sp, cam["W"], cam["H"], 8, 5e-3, [scene[k] for k in WKEYS],
+                     scene["freq"], scene["att"], precision=0, want_masks=False)
+    np.testing.assert_allclose(rgb.cpu().numpy(), res.rgb, atol=IMG_TOL_F32)
+    # the screen-space circle is not conservative under perspective, the cone test is: the cone lists can
+    # only add coverage
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    assert (res.alpha >= f["render"].alpha - 1e-5).all()
+
+
 def test_euclidean_sort_key_bit_exact(dev):
     """sort_key=1: the ordering of the reference's expected-depth kernel (np_tile_kernels.cu:5538-5543)."""
     scene, cam = small_case(**CASES["dense"])
