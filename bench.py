@@ -140,10 +140,14 @@ def run_reference(args):
 
 
 def workload_config(name, cfg, n_gpus):
+    views = int(cfg["views"])
     return {"workload": name, "primitives": cfg["n"], "width": cfg["W"], "height": cfg["H"], "tile": 8,
             "tile_capacity": 1536, "threshold": THRESHOLD, "log_scale_mean": cfg["mu"],
-            "mlp": "72-32-32-4 fp16 weights, fp32 accumulate", "views_per_step": n_gpus,
-            "parallelism": f"view-sharded x{n_gpus}, scene replicated", "l2": "256 MB flush between timed steps"}
+            "mlp": "72-32-32-4 fp16 weights, fp32 accumulate", "views_per_step": n_gpus if views == 1 else views,
+            "feature_channels": cfg.get("feat_dim", 0),
+            "parallelism": (f"one view per GPU x{n_gpus}" if views == 1 else f"{views} views shared by {n_gpus} GPU(s) by view, then by tile-row band")
+                           + ", scene replicated",
+            "l2": "256 MB flush between timed steps"}
 
 
 def main():
@@ -180,27 +184,46 @@ def main():
     cfg = dict(syn.WORKLOADS[args.workload])
     scene_np = None
     if rank == 0:
-        scene_np = syn.make_scene(cfg["n"], cfg["seed"], mu=cfg["mu"], hidden=cfg.get("hidden", 32))
+        scene_np = syn.make_scene(cfg["n"], cfg["seed"], mu=cfg["mu"], hidden=cfg.get("hidden", 32),
+                                  feat_dim=cfg.get("feat_dim", 0))
     t_b0 = time.perf_counter()
     scene_t = sharding.broadcast_scene(scene_np, dev, src=0)
     torch.cuda.synchronize()
     bcast_s = time.perf_counter() - t_b0
     prec = L.PRECISION_F16 if args.precision == "fp16" else L.PRECISION_F32
     ps = PackedScene(*[scene_t[k] for k in ("positions", "log_scales", "quats") + WK], scene_t["freq"], scene_t["att"],
-                     device=dev, pack_f16=(prec == L.PRECISION_F16))
-    # one view per rank, on the circle of radius 3 (weak scaling: per-GPU work is fixed)
-    cam = syn.make_camera(cfg["W"], cfg["H"], azimuth_deg=360.0 * rank / max(world, 1))
+                     feat_attr=scene_t.get("feat_attr"), device=dev, pack_f16=(prec == L.PRECISION_F16))
+    # Work units of this rank.  Single-view workloads: one view per rank on the circle of radius 3 (weak
+    # scaling, per-GPU work fixed).  Multi-view workloads: the workload's views are shared between the
+    # ranks, by view and then by band of tile rows (strong scaling, total work fixed).
+    nviews = int(cfg["views"])
+    nty = (cfg["H"] + 7) // 8
+    want_feat = cfg.get("feat_dim", 0) > 0
+    if nviews == 1:
+        units = [(syn.make_camera(cfg["W"], cfg["H"], azimuth_deg=360.0 * rank / max(world, 1)), None)]
+        frames_per_step, scaling = world, "weak"
+    else:
+        units = [(syn.make_camera(cfg["W"], cfg["H"], azimuth_deg=360.0 * v / nviews), (r0, r1) if (r0, r1) != (0, nty) else None)
+                 for v, r0, r1 in sharding.assign(nviews, nty, world, rank)]
+        frames_per_step, scaling = nviews, "strong"
+    cam = units[0][0] if units else syn.make_camera(cfg["W"], cfg["H"])
     r = FrameRenderer(cfg["W"], cfg["H"], device=dev)
+    dev_rays = []
+    for c, _rows in units:
+        rd_dev = torch.from_numpy(c["rays_d"]).to(dev)
+        rd_u = torch.empty_like(rd_dev)
+        L.check(lib.mlpsp_normalize_rows(L.ptr(rd_dev), L.ptr(rd_u), r.P, 3, None), "normalize")
+        dev_rays.append((torch.from_numpy(c["rays_o"]).to(dev), rd_u))
     ro_h = torch.from_numpy(cam["rays_o"]).pin_memory()
     rd_h = torch.from_numpy(cam["rays_d"]).pin_memory()
-    ro, rd = ro_h.to(dev), rd_h.to(dev)
-    rd_unit = torch.empty_like(rd)
-    L.check(lib.mlpsp_normalize_rows(L.ptr(rd), L.ptr(rd_unit), r.P, 3, None), "normalize")
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
     def frame(check=False):
-        return r.render(ps, ro, rd_unit, THRESHOLD, view=cam["view"], proj=cam["proj"], precision=prec,
-                        rays_normalized=True, check=check)
+        out = None
+        for (c, rows), (ro_u, rd_u) in zip(units, dev_rays):
+            out = r.render(ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=prec,
+                           rays_normalized=True, check=check, tile_rows=rows, want_feat=want_feat)
+        return out
 
     def barrier():
         if world > 1:
@@ -210,6 +233,13 @@ def main():
     # sizing pass (grows scratch if needed), then warm-up
     frame(check=True)
     stats = r.last_stats
+    if nviews > 1:   # per-step totals over this rank's units
+        tot_rec = tot_used = 0
+        for (c, rows), (ro_u, rd_u) in zip(units, dev_rays):
+            r.render(ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=prec, rays_normalized=True,
+                     tile_rows=rows, want_feat=want_feat)
+            tot_rec += r.last_stats.records; tot_used += r.last_stats.used
+        stats.records, stats.used = tot_rec, tot_used
     for _ in range(args.warmup):
         flush.fill_(1); frame()
     barrier()
@@ -238,7 +268,10 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms_max = float(t.item())
     ms_per_step = dev_ms_max / args.steps
-    fps = world * args.steps / (dev_ms_max / 1e3)
+    fps = frames_per_step * args.steps / (dev_ms_max / 1e3)
+    rec_t = torch.tensor([float(stats.records), float(stats.used)], dtype=torch.float64, device=dev)
+    if world > 1 and nviews > 1:
+        dist.all_reduce(rec_t)   # records of the whole step (all views), summed over ranks
 
     # ---- per-kernel-class device time (separate pass: event pairs around every launch group) ----
     lib.mlpsp_timing_enable(1)
@@ -277,10 +310,15 @@ def main():
     outs = [(torch.empty((r.P, 3), dtype=torch.float32).pin_memory(), torch.empty((r.P, 1), dtype=torch.float32).pin_memory())
             for _ in range(depth)]
 
+    host_rays = [(torch.from_numpy(c["rays_o"]).pin_memory(), torch.from_numpy(c["rays_d"]).pin_memory()) for c, _ in units]
+
     def e2e_run(k):
-        for i in range(k):
-            o = outs[i % depth]
-            pipe.submit(ro_h, rd_h, THRESHOLD, cam["view"], cam["proj"], out_rgb_host=o[0], out_alpha_host=o[1], precision=prec)
+        j = 0
+        for _i in range(k):
+            for (c, rows), (roh, rdh) in zip(units, host_rays):
+                o = outs[j % depth]; j += 1
+                pipe.submit(roh, rdh, THRESHOLD, c["view"], c["proj"], out_rgb_host=o[0], out_alpha_host=o[1],
+                            precision=prec, tile_rows=rows)
         pipe.drain()
 
     e2e_run(2 * depth)
@@ -291,19 +329,21 @@ def main():
     e_t = torch.tensor([time.perf_counter() - e0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e_t, op=dist.ReduceOp.MAX)
-    e2e_fps = world * args.steps / float(e_t.item())
-    e2e_err = float((outs[(args.steps - 1) % depth][0].to(dev) - r.rgb).abs().max())   # same view: must reproduce the resident-input frame
+    e2e_fps = frames_per_step * args.steps / float(e_t.item())
+    last = (args.steps * max(len(units), 1) - 1) % depth
+    e2e_err = float((outs[last][0].to(dev) - r.rgb).abs().max()) if units else 0.0   # must reproduce the resident-input frame
 
     if rank == 0:
         line = {
             "metric": "frames_per_sec", "value": fps, "unit": "frames/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "f16" if prec == L.PRECISION_F16 else "f32", "data": "synthetic",
             "config": workload_config(args.workload, cfg, world),
-            "record_mlp_evals_per_sec": stats.records * fps,
+            "record_mlp_evals_per_sec": float(rec_t[0]) * (fps / frames_per_step if nviews > 1 else fps),
             "records_per_frame": {"evaluated": stats.records, "composited": stats.used, "candidate_pairs": stats.pairs,
                                   "waves": stats.waves, "max_tile_len": stats.max_tile_len},
-            "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": 2 * r.P * 12, "d2h_bytes_per_step": r.P * 16 + 64,
+            "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": 2 * r.P * 12 * max(len(units), 1),
+                    "d2h_bytes_per_step": (r.P * 16 + 64) * max(len(units), 1),
                     "frames_in_flight": depth, "max_abs_diff_vs_resident_frame": e2e_err},
             "gpu_launches": int(launches),
             "kernel_classes": classes,

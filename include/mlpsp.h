@@ -114,6 +114,9 @@ typedef struct mlpsp_frame {
   int32_t sort_key;       /* 0 = t* of the tile-centre ray (np_tile_kernels.cu:483-518), the order of the forward,
                              feature and record kernels; 1 = Euclidean depth (c - o).d along that ray, the order
                              of render_tiles_kernel_tilecenter_order_with_t (np_tile_kernels.cu:5538-5543) */
+  int32_t tile_row_begin; /* binning keeps only tile rows [tile_row_begin, tile_row_end); both 0 = the whole image. */
+  int32_t tile_row_end;   /* Used to share one view between GPUs by bands of tile rows: tiles outside the band get
+                             empty lists and their pixels the background. */
 } mlpsp_frame;
 
 const char* mlpsp_last_error(void);

@@ -45,6 +45,7 @@ class Frame(C.Structure):
         ("scratch", _fp), ("scratch_bytes", C.c_int64), ("max_records", C.c_int64),
         ("status", _fp), ("num_waves", C.c_int32), ("wave_len", C.c_int32 * MAX_WAVES),
         ("keep_records", C.c_int32), ("sort_key", C.c_int32),
+        ("tile_row_begin", C.c_int32), ("tile_row_end", C.c_int32),
     ]
 
 

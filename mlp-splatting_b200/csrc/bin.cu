@@ -45,6 +45,7 @@ struct BinCam {
   float proj[16];
   float radius_mult, focal;
   int W, H, ts, ntx, nty;
+  int row0, row1;   // tile rows kept: [row0, row1)
 };
 
 __device__ __forceinline__ float dot4(const float* row, float x, float y, float z, float w) {
@@ -98,7 +99,9 @@ __device__ __forceinline__ bool prim_rect(const float4* __restrict__ geom, int p
   const float sy = fmul(fmul(fadd(ny, 1.f), 0.5f), (float)c.H);
   if (!tile_span(fsub(sx, pix_r), fadd(sx, pix_r), c.ts, c.ntx, r[0], r[1])) return false;
   if (!tile_span(fsub(sy, pix_r), fadd(sy, pix_r), c.ts, c.nty, r[2], r[3])) return false;
-  return true;
+  r[2] = max(r[2], c.row0);
+  r[3] = min(r[3], c.row1 - 1);
+  return r[2] <= r[3];
 }
 
 // Visit every tile of this thread's rectangle; rectangles larger than 32 tiles are walked by the
@@ -285,6 +288,12 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
   cam.W = fr->width; cam.H = fr->height; cam.ts = fr->tile;
   cam.ntx = (fr->width + fr->tile - 1) / fr->tile;
   cam.nty = (fr->height + fr->tile - 1) / fr->tile;
+  cam.row0 = 0; cam.row1 = cam.nty;
+  if (fr->tile_row_begin != 0 || fr->tile_row_end != 0) {
+    MLPSP_REQUIRE(fr->tile_row_begin >= 0 && fr->tile_row_begin <= fr->tile_row_end && fr->tile_row_end <= cam.nty,
+                  MLPSP_E_ARG, "tile row band [%d,%d) outside [0,%d]", fr->tile_row_begin, fr->tile_row_end, cam.nty);
+    cam.row0 = fr->tile_row_begin; cam.row1 = fr->tile_row_end;
+  }
   MLPSP_REQUIRE(cam.ntx < 65536 && cam.nty < 65536, MLPSP_E_LIMIT, "tile grid beyond 65535 per axis");
   MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
                 "tile_capacity must be in [1, %d]", kSortCap);
@@ -433,6 +442,7 @@ static BinCam make_cam(const mlpsp_frame* fr, const float* view) {
   cam.W = fr->width; cam.H = fr->height; cam.ts = fr->tile;
   cam.ntx = (fr->width + fr->tile - 1) / fr->tile;
   cam.nty = (fr->height + fr->tile - 1) / fr->tile;
+  cam.row0 = 0; cam.row1 = cam.nty;
   return cam;
 }
 

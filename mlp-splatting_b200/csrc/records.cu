@@ -445,64 +445,129 @@ __global__ void __launch_bounds__(64) k_composite(
 // every pair that composited at least one record, the consumed pixels and their coefficients
 // w * g_s are compacted into shared memory and every thread adds its channels' contribution.
 constexpr int kFeatThreads = 256;
+constexpr int kFeatBatch = 256;    // consumed records staged per barrier (one per thread)
+constexpr int kFeatChan = 256;     // channels per CTA: (tile, channel block) pairs make the grid
 
+// Shared memory: [64][CB] accumulators, then the tile's consumed masks and their record prefix.
 __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
     const uint32_t* __restrict__ used32, const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base,
     const float* __restrict__ rec_w, const float4* __restrict__ rec_gate, const float* __restrict__ feat_attr,
-    int S, int C, float* __restrict__ out_feat, const int32_t* __restrict__ status) {
-  extern __shared__ float s_acc[];                 // [64][C]
-  __shared__ float s_cw[64][5];                    // per consumed pixel: base weight + 4 gated weights
-  __shared__ int s_px[64];
-  __shared__ int s_n;
+    int S, int C, int CB, float* __restrict__ out_feat, const int32_t* __restrict__ status) {
+  extern __shared__ float s_acc[];                 // [64][CB]
+  __shared__ uint32_t s_u[2][kWinMax];             // consumed masks of the tile's pairs
+  __shared__ int32_t s_pref[kWinMax + 1];          // records before pair i
+  __shared__ float s_cw[kFeatBatch][5];            // per staged record: base weight + 4 gated weights
+  __shared__ int s_px[kFeatBatch];                 // its pixel
+  __shared__ int s_pr[kFeatBatch];                 // its primitive
+  __shared__ int s_run[kFeatBatch + 1];            // first staged record of every run of equal primitives
+  __shared__ int s_nruns;
+  __shared__ int warp_sums[32];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
-  const int tile = blockIdx.x;
+  const int tile = blockIdx.x, c0 = blockIdx.y * CB;
+  const int nc = min(CB, C - c0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < 64 * C; i += kFeatThreads) s_acc[i] = 0.f;
-  const int s = tile_offsets[tile], e = tile_offsets[tile + 1];
+  for (int i = tid; i < 64 * CB; i += kFeatThreads) s_acc[i] = 0.f;
+  const int s = tile_offsets[tile];
+  const int len = min(tile_offsets[tile + 1] - s, kWinMax);
+  int running = 0;
+  for (int j0 = 0; j0 < len; j0 += kFeatThreads) {
+    const int j = j0 + tid;
+    uint32_t u0 = 0u, u1 = 0u;
+    if (j < len) { u0 = used32[2 * (size_t)(s + j)]; u1 = used32[2 * (size_t)(s + j) + 1]; s_u[0][j] = u0; s_u[1][j] = u1; }
+    int total;
+    const int ex = block_exclusive_scan(__popc(u0) + __popc(u1), warp_sums, total);
+    if (j < len) s_pref[j] = running + ex;
+    running += total;
+  }
+  if (tid == 0) s_pref[len] = running;
   __syncthreads();
-  for (int i = s; i < e; ++i) {
-    const uint32_t u0 = used32[2 * (size_t)i], u1 = used32[2 * (size_t)i + 1];
-    if ((u0 | u1) == 0u) continue;                 // uniform across the CTA
-    if (warp < 2) {
-      const uint32_t mine = warp ? u1 : u0;
-      const uint32_t m0 = masks32[2 * (size_t)i], m1 = masks32[2 * (size_t)i + 1];
-      const uint32_t hit = warp ? m1 : m0;
-      const bool take = (mine >> lane) & 1u;
-      const int pos = (warp ? __popc(u0) : 0) + __popc(mine & ((1u << lane) - 1u));
-      if (take) {
-        const uint32_t slot = pair_base[i] + (warp ? __popc(m0) : 0) + __popc(hit & ((1u << lane) - 1u));
-        const float w = rec_w[slot];
-        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (S > 1) g = rec_gate[slot];
-        s_px[pos] = warp * 32 + lane;
-        s_cw[pos][0] = w; s_cw[pos][1] = w * g.x; s_cw[pos][2] = w * g.y; s_cw[pos][3] = w * g.z; s_cw[pos][4] = w * g.w;
+  const int n_tot = running;
+  for (int b0 = 0; b0 < n_tot; b0 += kFeatBatch) {
+    const int n = min(kFeatBatch, n_tot - b0);
+    if (tid < n) {
+      const int r = b0 + tid;
+      int a = 0, b = len - 1;                  // largest pair index with s_pref <= r (see k_fill)
+      while (a < b) {
+        const int mid = (a + b + 1) >> 1;
+        if (s_pref[mid] <= r) a = mid; else b = mid - 1;
       }
-      if (tid == 0) s_n = __popc(u0) + __popc(u1);
+      const int k = r - s_pref[a];
+      const uint32_t u0 = s_u[0][a], u1 = s_u[1][a];
+      const int cu0 = __popc(u0);
+      const int px = (k < cu0) ? (int)__fns(u0, 0, k + 1) : 32 + (int)__fns(u1, 0, k - cu0 + 1);
+      const uint32_t m0 = masks32[2 * (size_t)(s + a)], m1 = masks32[2 * (size_t)(s + a) + 1];
+      const uint32_t slot = pair_base[s + a] +
+                            (px < 32 ? __popc(m0 & ((1u << px) - 1u)) : __popc(m0) + __popc(m1 & ((1u << (px - 32)) - 1u)));
+      const float w = rec_w[slot];
+      float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (S > 1) g = rec_gate[slot];
+      s_px[tid] = px;
+      const int prim = sorted_prims[s + a];
+      s_pr[tid] = prim;
+      s_cw[tid][0] = w; s_cw[tid][1] = w * g.x; s_cw[tid][2] = w * g.y; s_cw[tid][3] = w * g.z; s_cw[tid][4] = w * g.w;
+      // the first record of a pair asks L2 for the pair's attribute rows of this channel block
+      if (k == 0 || tid == 0) {
+        const char* rows = reinterpret_cast<const char*>(feat_attr + (size_t)prim * S * C + c0);
+        for (int sl = 0; sl < S; ++sl)
+          for (int b = 0; b < nc * 4; b += 128)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(rows + (size_t)sl * C * 4 + b));
+      }
     }
     __syncthreads();
-    const int n = s_n;
-    const float* a = feat_attr + (size_t)sorted_prims[i] * S * C;
-    for (int c = tid; c < C; c += kFeatThreads) {
-      if (S == 4) {
-        const float a0 = __ldg(a + c), a1 = __ldg(a + C + c), a2 = __ldg(a + 2 * C + c), a3 = __ldg(a + 3 * C + c);
-        for (int j = 0; j < n; ++j) {
-          // w * (g0 a0 + g1 a1 + g2 a2 + g3 a3), gates folded into the weights
-          float v = s_cw[j][1] * a0;
-          v = fmaf(s_cw[j][2], a1, v); v = fmaf(s_cw[j][3], a2, v); v = fmaf(s_cw[j][4], a3, v);
-          s_acc[s_px[j] * C + c] += v;
+    // runs of equal primitives (block-wide compaction of the run heads)
+    {
+      const bool head = tid < n && (tid == 0 || s_pr[tid] != s_pr[tid - 1]);
+      int total;
+      const int pos = block_exclusive_scan(head ? 1 : 0, warp_sums, total);
+      if (head) s_run[pos] = tid;
+      if (tid == 0) { s_run[total] = n; s_nruns = total; }
+    }
+    __syncthreads();
+    const int nruns = s_nruns;
+    // thread owns channel c0 + tid; the attribute rows of run r + 2 are requested before run r is
+    // accumulated, so their latency overlaps two runs of arithmetic
+    for (int c = tid; c < nc; c += kFeatThreads) {
+      auto load_rows = [&](int r, float (&a)[5]) {
+        a[0] = a[1] = a[2] = a[3] = a[4] = 0.f;
+        if (r >= nruns) return;
+        const float* src = feat_attr + (size_t)s_pr[s_run[r]] * S * C + c0 + c;
+        a[0] = __ldg(src);
+        if (S >= 4) { a[1] = __ldg(src + C); a[2] = __ldg(src + 2 * C); a[3] = __ldg(src + 3 * C); }
+        if (S == 5) a[4] = __ldg(src + 4 * C);
+      };
+      float a_cur[5], a_n1[5], a_n2[5];
+      load_rows(0, a_cur);
+      load_rows(1, a_n1);
+      for (int r = 0; r < nruns; ++r) {
+        load_rows(r + 2, a_n2);
+        const int j0 = s_run[r], j1 = s_run[r + 1];
+        auto contribution = [&](int j) {
+          float v;
+          if (S == 4) {
+            v = s_cw[j][1] * a_cur[0];
+            v = fmaf(s_cw[j][2], a_cur[1], v); v = fmaf(s_cw[j][3], a_cur[2], v); v = fmaf(s_cw[j][4], a_cur[3], v);
+          } else if (S == 5) {
+            v = s_cw[j][0] * a_cur[0];
+            v = fmaf(s_cw[j][1], a_cur[1], v); v = fmaf(s_cw[j][2], a_cur[2], v);
+            v = fmaf(s_cw[j][3], a_cur[3], v); v = fmaf(s_cw[j][4], a_cur[4], v);
+          } else {
+            v = s_cw[j][0] * a_cur[0];
+          }
+          return v;
+        };
+        int j = j0;
+        // records of one pair touch distinct pixels: four accumulator cells are loaded together
+        for (; j + 4 <= j1; j += 4) {
+          float* q0 = s_acc + s_px[j] * CB + c; float* q1 = s_acc + s_px[j + 1] * CB + c;
+          float* q2 = s_acc + s_px[j + 2] * CB + c; float* q3 = s_acc + s_px[j + 3] * CB + c;
+          const float v0 = contribution(j), v1 = contribution(j + 1), v2 = contribution(j + 2), v3 = contribution(j + 3);
+          const float x0 = *q0, x1 = *q1, x2 = *q2, x3 = *q3;
+          *q0 = x0 + v0; *q1 = x1 + v1; *q2 = x2 + v2; *q3 = x3 + v3;
         }
-      } else if (S == 5) {
-        const float b = __ldg(a + c), a0 = __ldg(a + C + c), a1 = __ldg(a + 2 * C + c), a2 = __ldg(a + 3 * C + c),
-                    a3 = __ldg(a + 4 * C + c);
-        for (int j = 0; j < n; ++j) {
-          float v = s_cw[j][0] * b;
-          v = fmaf(s_cw[j][1], a0, v); v = fmaf(s_cw[j][2], a1, v); v = fmaf(s_cw[j][3], a2, v); v = fmaf(s_cw[j][4], a3, v);
-          s_acc[s_px[j] * C + c] += v;
-        }
-      } else {
-        const float b = __ldg(a + c);
-        for (int j = 0; j < n; ++j) s_acc[s_px[j] * C + c] = fmaf(s_cw[j][0], b, s_acc[s_px[j] * C + c]);
+        for (; j < j1; ++j) s_acc[s_px[j] * CB + c] += contribution(j);
+#pragma unroll
+        for (int q = 0; q < 5; ++q) { a_cur[q] = a_n1[q]; a_n1[q] = a_n2[q]; }
       }
     }
     __syncthreads();
@@ -510,7 +575,7 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
   for (int k = warp; k < 64; k += kFeatThreads / 32) {
     const TilePix tp = tile_pixel(tile, k, ntx, W, H);
     if (!tp.valid) continue;
-    for (int c = lane; c < C; c += 32) out_feat[(size_t)tp.pix * C + c] = s_acc[k * C + c];
+    for (int c = lane; c < nc; c += 32) out_feat[(size_t)tp.pix * C + c0 + c] = s_acc[k * CB + c];
   }
 }
 
@@ -609,15 +674,17 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     MLPSP_CUDA_OK(cudaMemcpyAsync(fr->mask_used, used32, 8 * (size_t)fr->max_pairs, cudaMemcpyDeviceToDevice, st));
   if (want_feat) {
     static bool attr_set = false;
-    const size_t smem = sizeof(float) * 64 * (size_t)sc->feat_dim;
+    const int CB = std::min(sc->feat_dim, kFeatChan);
+    const size_t smem = sizeof(float) * 64 * (size_t)CB;
     if (!attr_set) {
-      MLPSP_CUDA_OK(cudaFuncSetAttribute(k_feature_composite, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 512 * 4));
+      MLPSP_CUDA_OK(cudaFuncSetAttribute(k_feature_composite, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * kFeatChan * 4));
       attr_set = true;
     }
     LaunchScope scope(kKComposite, 1, st);
-    k_feature_composite<<<T, kFeatThreads, smem, st>>>(fr->tile_offsets, fr->sorted_prims, W, H, ntx, used32, s.masks32,
-                                                      s.pair_base, s.rec_w, s.rec_gate, sc->feat_attr, sc->feat_slots,
-                                                      sc->feat_dim, fr->feat, fr->status);
+    const dim3 grid(T, (sc->feat_dim + CB - 1) / CB);
+    k_feature_composite<<<grid, kFeatThreads, smem, st>>>(fr->tile_offsets, fr->sorted_prims, W, H, ntx, used32, s.masks32,
+                                                         s.pair_base, s.rec_w, s.rec_gate, sc->feat_attr, sc->feat_slots,
+                                                         sc->feat_dim, CB, fr->feat, fr->status);
   }
   return cuda_check(cudaGetLastError(), "render_sorted");
 }

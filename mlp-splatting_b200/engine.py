@@ -191,7 +191,7 @@ class FrameRenderer:
         return self.scratch
 
     def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
-               want_mask_used, waves, want_feat=False, keep_records=False, sort_key=0) -> L.Frame:
+               want_mask_used, waves, want_feat=False, keep_records=False, sort_key=0, tile_rows=None) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
         f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
@@ -227,6 +227,8 @@ class FrameRenderer:
         f.max_records = self.max_records
         f.keep_records = 1 if keep_records else 0
         f.sort_key = int(sort_key)
+        if tile_rows is not None:
+            f.tile_row_begin, f.tile_row_end = int(tile_rows[0]), int(tile_rows[1])
         f.status = L.ptr(self.status)
         if waves:
             f.num_waves = len(waves)
@@ -263,7 +265,7 @@ class FrameRenderer:
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
                rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False,
-               keep_records=False, sort_key=0):
+               keep_records=False, sort_key=0, tile_rows=None):
         """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling)."""
         lib, d = self.lib, self.device
         if precision is None:
@@ -291,7 +293,7 @@ class FrameRenderer:
                                                           self.capacity, scene.n, L.ptr(self.status), st),
                             "mlpsp_validate_tile_lists")
                 f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves,
-                                want_feat=want_feat, keep_records=keep_records, sort_key=sort_key)
+                                want_feat=want_feat, keep_records=keep_records, sort_key=sort_key, tile_rows=tile_rows)
                 self._last_frame = (f, scene)
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")
@@ -446,7 +448,7 @@ class FramePipeline:
         self.next_slot = 0
 
     def submit(self, rays_o_host, rays_d_host, threshold, view, proj, out_rgb_host=None, out_alpha_host=None,
-               precision=None, bg=None):
+               precision=None, bg=None, tile_rows=None):
         i = self.next_slot
         s = self.slots[i]
         if s["busy"]:
@@ -456,7 +458,7 @@ class FramePipeline:
         with torch.cuda.stream(s["stream"]):
             s["ro"].copy_(rays_o_host, non_blocking=True)
             s["rd"].copy_(rays_d_host, non_blocking=True)
-            kw = dict(view=view, proj=proj, precision=precision, bg=bg)
+            kw = dict(view=view, proj=proj, precision=precision, bg=bg, tile_rows=tile_rows)
             rgb, alpha = r.render(self.scene, s["ro"], s["rd"], threshold, check=False, **kw)
             if out_rgb_host is not None:
                 out_rgb_host.copy_(rgb, non_blocking=True)

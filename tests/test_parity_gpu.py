@@ -159,6 +159,26 @@ def test_ray_cone_culling_bit_exact_and_native_camera_mode(dev):
     assert (res.alpha >= f["render"].alpha - 1e-5).all()
 
 
+def test_tile_row_band_renders_only_its_rows(dev):
+    """Band sharding of one view: a band equals the same rows of the full frame, the rest is background."""
+    scene, cam = small_case(**CASES["tiny"])
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    ro, rd = _t(cam["rays_o"], dev), _t(cam["rays_d"], dev)
+    full, _ = r.render(ps, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"], precision=0)
+    full = full.cpu().numpy().reshape(cam["H"], cam["W"], 3).copy()
+    nty = (cam["H"] + 7) // 8
+    from mlp_splatting_b200 import sharding
+    acc = np.zeros_like(full)
+    for rank in range(3):
+        r0, r1 = sharding.tile_rows_for_rank(nty, 3, rank)
+        part, _ = r.render(ps, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"], precision=0, tile_rows=(r0, r1))
+        part = part.cpu().numpy().reshape(cam["H"], cam["W"], 3)
+        np.testing.assert_array_equal(part[r0 * 8:r1 * 8], full[r0 * 8:r1 * 8])
+        assert not part[:r0 * 8].any() and not part[r1 * 8:].any()
+        acc += part
+    np.testing.assert_array_equal(acc, full)
+
+
 def test_euclidean_sort_key_bit_exact(dev):
     """sort_key=1: the ordering of the reference's expected-depth kernel (np_tile_kernels.cu:5538-5543)."""
     scene, cam = small_case(**CASES["dense"])
