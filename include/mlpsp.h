@@ -194,7 +194,9 @@ int mlpsp_hit_masks(const mlpsp_scene* scene, const mlpsp_frame* frame, uint64_t
 int mlpsp_render_sorted(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
 
 /* bin + sort + render_sorted: what NeuralPrimitiveSceneTileCUDA.forward does per frame
- * (cumodel.py:951-1160). */
+ * (cumodel.py:951-1160).  Here frame->tile_prims is left in binning scatter order (the per-tile sort
+ * breaks depth ties by id, which gives the same sorted_prims as sorting the ascending-id lists);
+ * call mlpsp_bin_tiles when the ascending-id lists themselves are wanted. */
 int mlpsp_render_frame(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
 
 /* Pixel-major records of the frame just rendered with frame->keep_records = 1 on the same scratch: the

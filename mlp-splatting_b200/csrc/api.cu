@@ -209,7 +209,11 @@ extern "C" int mlpsp_sort_tiles(const mlpsp_scene* sc, const mlpsp_frame* fr, fl
   int rc = check_frame_common(sc, fr, "mlpsp_sort_tiles");
   if (rc) return rc;
   MLPSP_REQUIRE(fr->rays_o && fr->rays_d, MLPSP_E_ARG, "mlpsp_sort_tiles: rays missing");
-  return launch_sort(sc, fr, keys_out, (cudaStream_t)stream);
+  Scratch s;
+  rc = get_scratch(sc, fr, s, "mlpsp_sort_tiles");
+  if (rc) return rc;
+  // the active-tile list of the wave loop is free while the lists are being sorted
+  return launch_sort(sc, fr, keys_out, (cudaStream_t)stream, false, s.active[1], s.counters + kCtrScratch + 2);
 }
 
 extern "C" int mlpsp_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, void* stream) {
@@ -239,7 +243,7 @@ extern "C" int mlpsp_render_frame(const mlpsp_scene* sc, const mlpsp_frame* fr, 
   cudaStream_t st = (cudaStream_t)stream;
   rc = launch_bin(sc, fr, s, st, /*order_lists=*/false);
   if (rc) return rc;
-  rc = launch_sort(sc, fr, nullptr, st, /*unordered_input=*/true);
+  rc = launch_sort(sc, fr, nullptr, st, /*unordered_input=*/true, s.active[1], s.counters + kCtrScratch + 2);
   if (rc) return rc;
   return render_sorted_checked(sc, fr, s, st);
 }

@@ -135,8 +135,9 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
 int launch_bin_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, const int32_t* tile_view,
                       const float* views_host, int num_views, cudaStream_t st);
 int launch_bin_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
-int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st,
-                bool unordered_input = false);
+// long_list [T] / long_count [1]: device scratch for the tiles that take the block-wide sort
+int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st, bool unordered_input,
+                int32_t* long_list, int32_t* long_count);
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st);
 int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
 // rec_ext (optional): per record (sigma_raw, sigma_logit, layer-1 ReLU bitmask, layer-2 ReLU bitmask)
