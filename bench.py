@@ -131,7 +131,7 @@ def run_reference(args):
         "impl": "reference", "metric": "frames_per_sec", "value": cb["value"], "unit": "frames/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": workload_config(args.workload, cfg, 1),
+        "config": workload_config(args.workload, cfg, 1, args.encoder),
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "record_mlp_evals_per_sec": cb["evals_per_s"],
@@ -139,9 +139,9 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(name, cfg, n_gpus):
+def workload_config(name, cfg, n_gpus, encoder="integrated"):
     views = int(cfg["views"])
-    return {"workload": name, "primitives": cfg["n"], "width": cfg["W"], "height": cfg["H"], "tile": 8,
+    return {"workload": name, "encoder": encoder, "primitives": cfg["n"], "width": cfg["W"], "height": cfg["H"], "tile": 8,
             "tile_capacity": 1536, "threshold": THRESHOLD, "log_scale_mean": cfg["mu"],
             "mlp": "72-32-32-4 fp16 weights, fp32 accumulate", "views_per_step": n_gpus if views == 1 else views,
             "feature_channels": cfg.get("feat_dim", 0),
@@ -159,6 +159,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="fp16", choices=["fp16", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--encoder", default="integrated", choices=["integrated", "fourier"],
+                    help="integrated: the reference default (bands attenuated by exp(-f^2 sigma^2 / 2), sigma 0.01); "
+                         "fourier: unattenuated power-of-two bands")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -185,7 +188,7 @@ def main():
     scene_np = None
     if rank == 0:
         scene_np = syn.make_scene(cfg["n"], cfg["seed"], mu=cfg["mu"], hidden=cfg.get("hidden", 32),
-                                  feat_dim=cfg.get("feat_dim", 0))
+                                  feat_dim=cfg.get("feat_dim", 0), pe_sigma=0.01 if args.encoder == "integrated" else 0.0)
     t_b0 = time.perf_counter()
     scene_t = sharding.broadcast_scene(scene_np, dev, src=0)
     torch.cuda.synchronize()
@@ -340,9 +343,9 @@ def main():
             "metric": "frames_per_sec", "value": fps, "unit": "frames/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "f16" if prec == L.PRECISION_F16 else "f32", "data": "synthetic",
-            "config": workload_config(args.workload, cfg, world),
+            "config": workload_config(args.workload, cfg, world, args.encoder),
             "record_mlp_evals_per_sec": float(rec_t[0]) * (fps / frames_per_step if nviews > 1 else fps),
-            "records_per_frame": {"evaluated": stats.records, "composited": stats.used, "candidate_pairs": stats.pairs,
+            "records_per_frame": {"evaluated": stats.records, "composited": stats.used, "candidate_pairs": stats.pairs, "evaluator_blocks": stats.work_total,
                                   "waves": stats.waves, "max_tile_len": stats.max_tile_len},
             "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": 2 * r.P * 12 * max(len(units), 1),
                     "d2h_bytes_per_step": (r.P * 16 + 64) * max(len(units), 1),

@@ -42,6 +42,7 @@ extern "C" {
 #define MLPSP_ST_USED_HI 7
 #define MLPSP_ST_WAVE_RECORDS 8    /* largest record count of a single wave */
 #define MLPSP_ST_WORK_ITEMS 9      /* largest number of evaluator work items of a single wave */
+#define MLPSP_ST_WORK_TOTAL 10     /* evaluator work items (128-row blocks) of the whole frame */
 
 /* bits 1,2,4 match the reference validator (np_tile_kernels.cu:4499-4519) */
 #define MLPSP_ST_BAD_OFFSETS 1       /* tile_offsets not 0-based / monotone / in bounds */

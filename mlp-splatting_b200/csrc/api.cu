@@ -291,7 +291,7 @@ static Scratch grouped_layout(void* base, int64_t R, int n) {
   s.prim_off = (int32_t*)take(4 * ((int64_t)n + 2));
   s.scan_blk = (int32_t*)take(4 * 2 * ((int64_t)n / kScanItems + 4));
   s.max_work = (int64_t)n + R / kRowsPerItem + 2;
-  s.work = (int2*)take(8 * s.max_work);
+  s.work = (int4*)take(16 * s.max_work);
   s.rec_in = (RecIn*)take(32 * std::max<int64_t>(R, 1));
   s.counters = (int32_t*)take(4 * kNumCounters);
   s.bytes = off;

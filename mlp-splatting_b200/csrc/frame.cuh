@@ -40,7 +40,7 @@ struct Scratch {
   int32_t* prim_cnt;     // [n] records per primitive in the current wave
   int32_t* prim_cursor;  // [n]
   int32_t* prim_off;     // [n+1]
-  int2* work;            // [max_work] (primitive, first row)
+  int4* work;            // [max_work] (primitive, first record, rows, 0)
   RecIn* rec_in;         // [max_records] primitive-major, reused by every wave
   float4* rec_out;       // [max_records] (R,G,B,alpha) at compositing slots (slots are unique per frame)
   float* rec_t;          // [max_records] t* at compositing slots
@@ -84,7 +84,7 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.prim_cursor = (int32_t*)take(4 * (int64_t)n);
   s.prim_off = (int32_t*)take(4 * ((int64_t)n + 1));
   s.max_work = (int64_t)n + max_records / kRowsPerItem + 2;
-  s.work = (int2*)take(8 * s.max_work);
+  s.work = (int4*)take(16 * s.max_work);
   s.rec_in = (RecIn*)take(32 * max_records);
   s.rec_out = (float4*)take(16 * max_records);
   s.rec_t = (float*)take(4 * max_records);
@@ -141,10 +141,10 @@ int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, c
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st);
 int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
 // rec_ext (optional): per record (sigma_raw, sigma_logit, layer-1 ReLU bitmask, layer-2 ReLU bitmask)
-int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
+int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
                    cudaStream_t st);
-int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
+int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
                    cudaStream_t st);
 int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cudaStream_t st);

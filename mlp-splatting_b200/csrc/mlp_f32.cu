@@ -13,7 +13,7 @@ __global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32(
     const float* __restrict__ W1, const float* __restrict__ b1, const float* __restrict__ W2,
     const float* __restrict__ b2, const float* __restrict__ W3, const float* __restrict__ b3,
     const float* __restrict__ freq, const float* __restrict__ att, int F, int H,
-    const RecIn* __restrict__ rec_in, const int32_t* __restrict__ prim_off, const int2* __restrict__ work,
+    const RecIn* __restrict__ rec_in, const int32_t* __restrict__ prim_off, const int4* __restrict__ work,
     int32_t* __restrict__ counters, float4* __restrict__ rec_out, float4* __restrict__ rec_ext, int out_mode,
     const int32_t* __restrict__ status) {
   extern __shared__ float sW[];
@@ -34,10 +34,8 @@ __global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32(
     __syncthreads();
     const int item = s_item;
     if (item >= G) break;
-    const int2 wk = work[item];
+    const int4 wk = work[item];
     const int p = wk.x;
-    const int row = wk.y + tid;
-    const int cnt = prim_off[p + 1] - prim_off[p];
     for (int i = tid; i < H * IN; i += kRowsPerItem) sW1[i] = W1[(size_t)p * H * IN + i];
     for (int i = tid; i < H * H; i += kRowsPerItem) sW2[i] = W2[(size_t)p * H * H + i];
     for (int i = tid; i < 4 * H; i += kRowsPerItem) sW3[i] = W3[(size_t)p * 4 * H + i];
@@ -45,8 +43,8 @@ __global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32(
     if (tid < 4) sb3[tid] = b3[(size_t)p * 4 + tid];
     if (tid < F) { sfa[tid] = freq[tid]; sfa[F + tid] = att[tid]; }
     __syncthreads();
-    if (row < cnt) {
-      const RecIn r = rec_in[prim_off[p] + row];
+    if (tid < wk.z) {
+      const RecIn r = rec_in[wk.y + tid];
       const float v6[6] = {r.rdx, r.rdy, r.rdz, r.dx, r.dy, r.dz};
       float h1[HMAX];
 #pragma unroll
@@ -93,7 +91,7 @@ __global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32(
   }
 }
 
-int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
+int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
                    cudaStream_t st) {
   const int H = sc->hidden, F = sc->num_freq;

@@ -26,18 +26,18 @@ namespace mlpsp {
 constexpr int kK1 = 80;                  // 72 encoded inputs padded to a multiple of 16
 constexpr int kH = 32;
 constexpr int kN3 = 16;                  // 4 outputs padded to the smallest N
-constexpr int kOffW1 = 0;                // [10 k-chunks][32 rows][8 halves]
+constexpr int kOffW1 = 0;                // [10 k-chunks][32 rows][8 halves]: chunks 0..7 of K in the order of enc_k(),
+                                         // an all-zero chunk, then chunk 8 (see the last layer-1 MMA)
 constexpr int kOffW2 = kOffW1 + (kK1 / 8) * kH * 16;   // 5120: [4][32][8]
 constexpr int kOffW3 = kOffW2 + (kH / 8) * kH * 16;    // 7168: [4][16][8]
 constexpr int kOffBias = kOffW3 + (kH / 8) * kN3 * 16; // 8192: b1[32] b2[32] b3[4] fp32
 constexpr int kWeightBytes = kOffBias + 4 * (kH + kH + 4);  // 8464, a multiple of 16
 
 constexpr int kRows = kRowsPerItem;      // 128 = MMA M
-constexpr int kA1Bytes = (kK1 / 8) * kRows * 16;  // 20480: [10][128][8 halves]
+constexpr int kA1Bytes = 9 * kRows * 16;          // 18432: [9 k-chunks][128][8 halves], 72 encoded inputs
 constexpr int kA2Bytes = (kH / 8) * kRows * 16;   // 8192:  [4][128][8 halves]
 constexpr int kSmemBytes = kWeightBytes + kA1Bytes + 64;   // the hidden-activation tile reuses the layer-1 A tile
 constexpr int kTmemCols = 64;            // D1 [0,32)  D2 [32,64)  D3 reuses [0,16)
-constexpr int kSpinLimit = 1 << 20;
 
 // -------------------------------------------------------------------------- PTX helpers ----
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -48,22 +48,35 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One poll of the barrier's phase; the hardware may park the thread for up to kSuspendNs before it
+// answers, so a waiting warp costs a handful of instructions instead of a spin loop.
+constexpr uint32_t kSuspendNs = 20000u;
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // a wait gives up after one second
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendNs) : "memory");
   return ok != 0;
 }
-// bounded wait: false when the phase did not complete within kSpinLimit polls
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// bounded wait: false when the phase did not complete within kWaitLimitNs
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
+  const unsigned long long t0 = global_ns();
+  do {
     if (mbar_try(bar, parity)) return true;
-    if (i > 32) __nanosleep(64);
-  }
+  } while (global_ns() - t0 < kWaitLimitNs);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity);
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -119,19 +132,35 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// (max(a, 0), max(b, 0)) rounded to binary16 (RN) in one conversion; a in the low half
+__device__ __forceinline__ uint32_t pack_h2_relu(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   const __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// hidden layer epilogue: +bias, ReLU, fp16, write this thread's row of the next A tile.
-// Returns the largest |pre-activation| as an unsigned bit pattern (NaN and inf compare above every
-// finite value), so the caller needs one comparison per layer to detect a non-finite sum or one that
-// rounds to +inf in binary16 (rgb_wmma.cuh:179-181 checks the same two conditions per element).
+// Position of an encoded input inside the K dimension of layer 1.  The reference orders K as
+// [sin(c,f) for c, f][cos(c,f) for c, f] (np_tile_kernels.cu:329-343); a dot product does not care, so
+// the A tile and the packed W1 rows both use an order in which the six (sin, cos) pairs of one input
+// coordinate are contiguous and two coordinates fill exactly three 16-byte chunks:
+//   k' = 12 c + 4 (f / 2) + 2 is_cos + (f % 2).
+__host__ __device__ constexpr int enc_k(int c, int f, int is_cos) { return 12 * c + 4 * (f >> 1) + 2 * is_cos + (f & 1); }
+__host__ __device__ constexpr int enc_k_of_reference(int k) {
+  return k >= 72 ? k : enc_k((k % 36) / 6, (k % 36) % 6, k / 36);
+}
+
+// hidden layer epilogue: +bias, ReLU, fp16 (RN), write this thread's row of the next A tile.
+// Returns true when an activation rounded to +inf in binary16.  The FP32 sums themselves are always
+// finite: operands are finite fp16 values, so |sum| <= 80 * 65504^2 (rgb_wmma.cuh:179-181 checks for a
+// non-finite or fp16-overflowing activation per element).
 template <bool KEEP>
-__device__ __forceinline__ uint32_t hidden_to_smem(const uint32_t (&acc)[32], const float* bias, char* a2, int row,
-                                                   uint32_t& relu_mask) {
-  uint32_t worst = 0u;
+__device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const float* bias, char* a2, int row,
+                                               uint32_t& relu_mask) {
+  __half2 top = __floats2half2_rn(0.f, 0.f);
   relu_mask = 0u;
 #pragma unroll
   for (int kc = 0; kc < 4; ++kc) {
@@ -143,42 +172,93 @@ __device__ __forceinline__ uint32_t hidden_to_smem(const uint32_t (&acc)[32], co
     for (int q = 0; q < 4; ++q) {
       const int j = kc * 8 + q * 2;
       const float v0 = __uint_as_float(acc[j]) + bb[q * 2], v1 = __uint_as_float(acc[j + 1]) + bb[q * 2 + 1];
-      worst = max(worst, max(__float_as_uint(v0) & 0x7fffffffu, __float_as_uint(v1) & 0x7fffffffu));
       if (KEEP) {
         relu_mask |= (v0 > 0.f ? 1u : 0u) << j;
         relu_mask |= (v1 > 0.f ? 1u : 0u) << (j + 1);
       }
-      w[q] = pack_h2(fmaxf(v0, 0.f), fmaxf(v1, 0.f));
+      w[q] = pack_h2_relu(v0, v1);
+      top = __hmax2(top, *reinterpret_cast<const __half2*>(&w[q]));
     }
     *reinterpret_cast<uint4*>(a2 + kc * (kRows * 16) + row * 16) = make_uint4(w[0], w[1], w[2], w[3]);
   }
-  return worst;
+  return __hisinf(__low2half(top)) || __hisinf(__high2half(top));
 }
 
-constexpr uint32_t kHalfOverflowBits = 0x477ff000u;   // 65520.0f: the smallest magnitude that rounds to inf in binary16
+// Encode one record into this thread's row of the layer-1 A tile (K order of enc_k()).  mult[f] is
+// freq[f] * att[f].  LADDER: every band is exactly twice the one before, so the phases are exact
+// doublings of the first and sin / cos of the higher bands follow from the double-angle identities
+// (2 special-function evaluations per coordinate instead of 12).  Returns true for a non-finite input.
+template <bool LADDER>
+__device__ __forceinline__ bool encode_row(const RecIn& r, const float (&mult)[6], char* row_ptr) {
+  const float v6[6] = {r.rdx, r.rdy, r.rdz, r.dx, r.dy, r.dz};
+  bool bad = false;
+#pragma unroll
+  for (int cp = 0; cp < 3; ++cp) {
+    uint32_t w[12];
+#pragma unroll
+    for (int d = 0; d < 2; ++d) {
+      const float v = v6[cp * 2 + d];
+      bad |= !(fabsf(v) < 1.0e30f);   // a finite input gives finite phases (freq * att <= 101)
+      float sn[6], cs[6];
+      if (LADDER) {
+        __sincosf(v * mult[0], &sn[0], &cs[0]);
+#pragma unroll
+        for (int f = 1; f < 6; ++f) {
+          const float t = sn[f - 1] + sn[f - 1];
+          sn[f] = t * cs[f - 1];
+          cs[f] = fmaf(-t, sn[f - 1], 1.0f);
+        }
+      } else {
+#pragma unroll
+        for (int f = 0; f < 6; ++f) __sincosf(v * mult[f], &sn[f], &cs[f]);
+      }
+#pragma unroll
+      for (int g = 0; g < 3; ++g) {
+        w[d * 6 + g * 2] = pack_h2(sn[2 * g], sn[2 * g + 1]);
+        w[d * 6 + g * 2 + 1] = pack_h2(cs[2 * g], cs[2 * g + 1]);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 3; ++q)
+      *reinterpret_cast<uint4*>(row_ptr + (cp * 3 + q) * (kRows * 16)) =
+          make_uint4(w[q * 4], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
+  }
+  return bad;
+}
 
+// One work item = (primitive, first record, rows <= 128).  Items are dealt to CTAs round-robin
+// (item = blockIdx.x + k * gridDim.x): all items cost about the same, and a fixed deal lets a CTA
+// fetch the next item's descriptor, its record and -- as soon as the MMAs that read them have
+// finished -- the next primitive's W1 and W2 blocks while the current item is still being evaluated,
+// so the only global-memory latency left on an item's critical path is the 1.3 KB copy of W3 + biases.
 template <bool KEEP>
-__global__ void __launch_bounds__(kRows) k_mlp_tc(
+__global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
     const char* __restrict__ w16, const float* __restrict__ freq, const float* __restrict__ att,
-    const RecIn* __restrict__ rec_in, const int32_t* __restrict__ prim_off, const int2* __restrict__ work,
-    int32_t* __restrict__ counters, float4* __restrict__ rec_out, float4* __restrict__ rec_ext, int out_mode,
+    const RecIn* __restrict__ rec_in, const int4* __restrict__ work,
+    const int32_t* __restrict__ counters, float4* __restrict__ rec_out, float4* __restrict__ rec_ext, int out_mode,
     int32_t* __restrict__ status) {
   extern __shared__ __align__(128) char smem[];
   char* s_w = smem;
   char* s_a1 = smem + kWeightBytes;          // 8464 is a multiple of 16
   char* s_a2 = s_a1;                         // written only after the layer-1 MMAs have finished reading s_a1
   uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_a1 + kA1Bytes);   // [0] weights, [1] mma
-  uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2);        // [0] tmem base, [1] work item
+  uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2);        // [0] tmem base
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = counters[kCtrWork];
-  if ((int)blockIdx.x >= G) return;          // more CTAs than work: leave before touching tensor memory
+  int item = blockIdx.x;
+  if (item >= G) return;                     // more CTAs than work: leave before touching tensor memory
   const uint32_t bar_w = smem_u32(&s_bar[0]), bar_m = smem_u32(&s_bar[1]);
+  const uint32_t a1 = smem_u32(s_a1), a2 = smem_u32(s_a2), wb = smem_u32(s_w);
+  int4 wk = __ldg(work + item);
   if (tid == 0) {
     mbar_init(bar_w, 1);
     mbar_init(bar_m, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
+    // the first item's whole weight image
+    mbar_expect_tx(bar_w, kWeightBytes);
+    bulk_g2s(wb, w16 + (size_t)wk.x * kWeightBytes, kWeightBytes, bar_w);
   }
   if (warp == 0) tmem_alloc(smem_u32(&s_misc[0]), kTmemCols);
   tc_fence_before();
@@ -186,60 +266,39 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
   tc_fence_after();
   const uint32_t tmem = s_misc[0];
   const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
-  float fr[6], at[6];
+  // phase multipliers freq[f] * att[f]; when every band is exactly twice the one before (equal
+  // attenuation: FourierFeatureEncoding's bands, cumodel.py:163) the encoder takes the double-angle route
+  float mult[6];
+  bool ladder = true;
 #pragma unroll
-  for (int f = 0; f < 6; ++f) { fr[f] = __ldg(freq + f); at[f] = __ldg(att + f); }
-  const uint32_t a1 = smem_u32(s_a1), a2 = smem_u32(s_a2), wb = smem_u32(s_w);
+  for (int f = 0; f < 6; ++f) mult[f] = __ldg(freq + f) * __ldg(att + f);
+#pragma unroll
+  for (int f = 1; f < 6; ++f) ladder = ladder && mult[f] == 2.0f * mult[f - 1];
   const float* s_bias = reinterpret_cast<const float*>(s_w + kOffBias);
   uint32_t ph_w = 0, ph_m = 0;
-  bool ok = true, bad = false, copy_pending = false;
+  bool ok = true, bad = false, copy_pending = true;
   uint32_t relu1 = 0u, relu2 = 0u;
+  RecIn r;
+  r.rdx = r.rdy = r.rdz = r.dx = r.dy = r.dz = 0.f; r.decay = 0.f; r.slot = 0u;
+  if (tid < wk.z) r = rec_in[wk.y + tid];
 
   for (;;) {
-    if (tid == 0) s_misc[1] = (uint32_t)atomicAdd(counters + kCtrWorkNext, 1);
-    __syncthreads();                          // also: previous item's reads of s_w / s_a* are done
-    const int item = (int)s_misc[1];
-    if (item >= G) break;
-    const int2 wk = work[item];
-    const int p = wk.x;
-    const int pbase = prim_off[p];
-    const int nrows = min(kRows, prim_off[p + 1] - pbase - wk.y);
-    if (tid == 0) {
-      mbar_expect_tx(bar_w, kWeightBytes);
-      bulk_g2s(wb, w16 + (size_t)p * kWeightBytes, kWeightBytes, bar_w);
-    }
-    copy_pending = true;
-    // ---- encode this thread's record into the layer-1 A tile ----
+    const int nrows = wk.z;
     const bool valid = tid < nrows;
-    RecIn r;
-    r.rdx = r.rdy = r.rdz = r.dx = r.dy = r.dz = 0.f; r.decay = 0.f; r.slot = 0u;
-    if (valid) r = rec_in[pbase + wk.y + tid];
-    {
-      const float v6[6] = {r.rdx, r.rdy, r.rdz, r.dx, r.dy, r.dz};
-      // rows past the end of the primitive's records encode the zero vector; their results are never stored
-      float sn[36], cs[36];
-#pragma unroll
-      for (int c = 0; c < 6; ++c) {
-        bad |= valid && !(fabsf(v6[c]) < 1.0e30f);   // a finite input gives finite phases (freq * att <= 101)
-#pragma unroll
-        for (int f = 0; f < 6; ++f) {
-          const float ph = v6[c] * fr[f] * at[f];
-          __sincosf(ph, &sn[c * 6 + f], &cs[c * 6 + f]);
-        }
-      }
-      // k index: 0..35 sin block, 36..71 cos block, 72..79 zero (np_tile_kernels.cu:329-343)
-#pragma unroll
-      for (int kc = 0; kc < 10; ++kc) {
-        uint32_t w[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int j0 = kc * 8 + q * 2, j1 = j0 + 1;
-          const float e0 = j0 < 36 ? sn[j0] : (j0 < 72 ? cs[j0 - 36] : 0.f);
-          const float e1 = j1 < 36 ? sn[j1] : (j1 < 72 ? cs[j1 - 36] : 0.f);
-          w[q] = pack_h2(e0, e1);
-        }
-        *reinterpret_cast<uint4*>(s_a1 + kc * (kRows * 16) + tid * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+    // MMA rows are independent and rows past the end of the primitive's records are never stored, so a
+    // warp whose 32 rows are all past the end skips the encoding and the epilogues (its rows of the
+    // operand tiles keep whatever they held) and only takes part in the barriers
+    const bool warp_live = warp * 32 < nrows;
+    const int next = item + (int)gridDim.x;
+    const bool has_next = next < G;
+    int4 wk_next = make_int4(0, 0, 0, 0);
+    const float decay = r.decay;
+    const uint32_t slot = r.slot;
+    // ---- encode this thread's record into the layer-1 A tile ----
+    if (warp_live) {
+      // rows past the end inside a live warp hold the zero record; their results are never stored
+      const bool nonfinite = ladder ? encode_row<true>(r, mult, s_a1 + tid * 16) : encode_row<false>(r, mult, s_a1 + tid * 16);
+      bad |= nonfinite;
     }
     fence_async_smem();
     {
@@ -249,23 +308,38 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
     }
     tc_fence_before();
     if (!__syncthreads_and(ok)) { ok = false; break; }
-    // ---- layer 1: D1[128x32] = A1[128x80] . W1^T ----
+    // ---- layer 1: D1[128x32] = A1[128x72] . W1^T ----
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
-      for (int ks = 0; ks < kK1 / 16; ++ks)
+      for (int ks = 0; ks < 4; ++ks)
         mma_f16(tmem, smem_desc(a1 + ks * 2 * (kRows * 16), kRows * 16, 128),
                 smem_desc(wb + kOffW1 + ks * 2 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH), ks > 0);
+      // K = 64..79: the weight image holds a zero chunk and then chunk 8; the A operand pairs them with
+      // chunk 7 (any finite values: they meet zeros) and chunk 8, so no padded A chunk is stored
+      mma_f16(tmem, smem_desc(a1 + 7 * (kRows * 16), kRows * 16, 128),
+              smem_desc(wb + kOffW1 + 8 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH), 1u);
       mma_commit(bar_m);
     }
+    // the next item's descriptor and record are requested behind the proxy fence (which would otherwise
+    // wait for them); their latency hides under the layers of this item
+    if (has_next) wk_next = __ldg(work + next);
     ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph_m) && ok);   // warp-uniform: tcgen05.ld is .sync.aligned
     ph_m ^= 1u;
     tc_fence_after();
+    r.rdx = r.rdy = r.rdz = r.dx = r.dy = r.dz = 0.f; r.decay = 0.f; r.slot = 0u;
+    if (tid < wk_next.z) r = rec_in[wk_next.y + tid];
+    if (tid == 0 && has_next && ok) {
+      // W1 is no longer read: start the next primitive's image with its W1 block
+      mbar_expect_tx(bar_w, kWeightBytes);
+      bulk_g2s(wb + kOffW1, w16 + (size_t)wk_next.x * kWeightBytes + kOffW1, kOffW2 - kOffW1, bar_w);
+    }
+    if (has_next && ok) copy_pending = true;
     {
       uint32_t acc[32];
-      if (ok) {
+      if (ok && warp_live) {
         tmem_ld32(trow, acc);
-        bad |= valid && hidden_to_smem<KEEP>(acc, s_bias, s_a2, tid, relu1) >= kHalfOverflowBits;
+        bad |= hidden_to_smem<KEEP>(acc, s_bias, s_a2, tid, relu1) && valid;
       }
     }
     fence_async_smem();
@@ -283,11 +357,13 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
     ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph_m) && ok);   // warp-uniform: tcgen05.ld is .sync.aligned
     ph_m ^= 1u;
     tc_fence_after();
+    if (tid == 0 && has_next && ok)
+      bulk_g2s(wb + kOffW2, w16 + (size_t)wk_next.x * kWeightBytes + kOffW2, kOffW3 - kOffW2, bar_w);
     {
       uint32_t acc[32];
-      if (ok) {
+      if (ok && warp_live) {
         tmem_ld32(trow + 32, acc);
-        bad |= valid && hidden_to_smem<KEEP>(acc, s_bias + kH, s_a2, tid, relu2) >= kHalfOverflowBits;   // layer-2 MMAs have finished reading s_a2
+        bad |= hidden_to_smem<KEEP>(acc, s_bias + kH, s_a2, tid, relu2) && valid;   // layer-2 MMAs have finished reading s_a2
       }
     }
     fence_async_smem();
@@ -305,29 +381,35 @@ __global__ void __launch_bounds__(kRows) k_mlp_tc(
     ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph_m) && ok);   // warp-uniform: tcgen05.ld is .sync.aligned
     ph_m ^= 1u;
     tc_fence_after();
-    if (ok) {
+    if (ok && warp_live) {
       uint32_t o[4];
       tmem_ld4(trow, o);
       if (valid) {
         const float o0 = __uint_as_float(o[0]) + s_bias[2 * kH + 0], o1 = __uint_as_float(o[1]) + s_bias[2 * kH + 1];
         const float o2 = __uint_as_float(o[2]) + s_bias[2 * kH + 2], o3 = __uint_as_float(o[3]) + s_bias[2 * kH + 3];
-        bad |= !(fabsf(o0) < 3.0e38f) || !(fabsf(o1) < 3.0e38f) || !(fabsf(o2) < 3.0e38f) || !(fabsf(o3) < 3.0e38f);
         const float sigma_raw = softplus_fast(o3);
         float4 out;
         out.x = sigmoid_fast(o0); out.y = sigmoid_fast(o1); out.z = sigmoid_fast(o2);
-        out.w = (out_mode == kOutAlpha) ? (1.f - __expf(-(sigma_raw * r.decay))) : sigma_raw;
-        rec_out[r.slot] = out;
-        if (KEEP) rec_ext[r.slot] = make_float4(sigma_raw, o3, __uint_as_float(relu1), __uint_as_float(relu2));
+        out.w = (out_mode == kOutAlpha) ? (1.f - __expf(-(sigma_raw * decay))) : sigma_raw;
+        rec_out[slot] = out;
+        if (KEEP) rec_ext[slot] = make_float4(sigma_raw, o3, __uint_as_float(relu1), __uint_as_float(relu2));
       }
     }
     tc_fence_before();
+    // every thread is past its reads of the biases, W3 and the operand tiles of this item
     if (!__syncthreads_and(ok)) { ok = false; break; }
+    if (!has_next) break;
+    if (tid == 0)
+      bulk_g2s(wb + kOffW3, w16 + (size_t)wk_next.x * kWeightBytes + kOffW3, kWeightBytes - kOffW3, bar_w);
+    item = next;
+    wk = wk_next;
   }
 
   if (!ok) {
     if (tid == 0) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_TIMEOUT);
-    // our own bulk copy may still be in flight: give it a bounded chance to land before the CTA's
-    // shared memory is released
+    // our own bulk copies may still be in flight: give them a bounded chance to land before the CTA's
+    // shared memory is released (an image whose last block was never requested cannot complete; the
+    // wait then simply runs out)
     if (copy_pending) mbar_wait(bar_w, ph_w);
   }
   if (bad) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_NUMERIC);
@@ -352,7 +434,9 @@ __global__ void k_pack_weights(const float* __restrict__ W1, const float* __rest
     const int h = i / kK1, k = i % kK1;
     const __half v = __float2half_rn(k < 72 ? W1[(size_t)p * kH * 72 + h * 72 + k] : 0.f);
     bad |= __hisinf(v) || __hisnan(v);
-    w1[(k >> 3) * (kH * 8) + h * 8 + (k & 7)] = v;
+    const int kk = enc_k_of_reference(k);
+    const int chunk = (kk >> 3) == 8 ? 9 : ((kk >> 3) == 9 ? 8 : (kk >> 3));   // zero chunk before the last real one
+    w1[chunk * (kH * 8) + h * 8 + (kk & 7)] = v;
   }
   for (int i = threadIdx.x; i < kH * kH; i += blockDim.x) {
     const int h = i / kH, k = i % kH;
@@ -375,7 +459,7 @@ __global__ void k_pack_weights(const float* __restrict__ W1, const float* __rest
   if (bad && status) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_NUMERIC);
 }
 
-int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int2* work,
+int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
                    cudaStream_t st) {
   MLPSP_REQUIRE(sc->hidden == kH && sc->num_freq == 6, MLPSP_E_LIMIT,
@@ -390,16 +474,17 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // tensor memory: 512 columns per SM / 64 per CTA = at most 8 resident CTAs; shared memory and
-  // registers (64 per thread) allow 7
-  const int grid = sms * 7;
+  // tensor memory: 512 columns per SM / 64 per CTA = at most 8 resident CTAs; shared memory
+  // (8 x 28 KB) and registers (64 per thread) allow the same 8
+  const int grid = sms * (rec_ext ? 6 : 8);   // the record-export variant keeps two more words per row
+  (void)prim_off;
   LaunchScope scope(kKMlp, 1, st);
   if (rec_ext)
-    k_mlp_tc<true><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, prim_off, work,
-                                                   const_cast<int32_t*>(counters), rec_out, rec_ext, out_mode, status);
+    k_mlp_tc<true><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, work,
+                                                   counters, rec_out, rec_ext, out_mode, status);
   else
-    k_mlp_tc<false><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, prim_off, work,
-                                                    const_cast<int32_t*>(counters), rec_out, rec_ext, out_mode, status);
+    k_mlp_tc<false><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, work,
+                                                    counters, rec_out, rec_ext, out_mode, status);
   return cuda_check(cudaGetLastError(), "mlp_f16");
 }
 

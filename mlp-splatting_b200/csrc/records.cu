@@ -217,6 +217,7 @@ __global__ void k_prim_top(int32_t* __restrict__ blk, int nblk, int32_t* __restr
       atomicAdd((unsigned long long*)(status + MLPSP_ST_RECORDS_LO), (unsigned long long)R);
       atomicMax(status + MLPSP_ST_WAVE_RECORDS, R);
       atomicMax(status + MLPSP_ST_WORK_ITEMS, G);
+      atomicAdd(status + MLPSP_ST_WORK_TOTAL, G);
       atomicAdd(status + MLPSP_ST_WAVES, 1);
     }
   }
@@ -224,7 +225,7 @@ __global__ void k_prim_top(int32_t* __restrict__ blk, int nblk, int32_t* __restr
 
 __global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict__ prim_cursor, int n,
                              const int32_t* __restrict__ blk, int32_t* __restrict__ prim_off,
-                             int2* __restrict__ work, int64_t max_work, const int32_t* __restrict__ status) {
+                             int4* __restrict__ work, int64_t max_work, const int32_t* __restrict__ status) {
   __shared__ int warp_sums[32];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
@@ -243,7 +244,8 @@ __global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict
       prim_off[base + j] = ea;
       const int it = items_of(c[j]);
       for (int q = 0; q < it; ++q)
-        if ((int64_t)eb + q < max_work) work[eb + q] = make_int2((int)(base + j), q * kRowsPerItem);
+        if ((int64_t)eb + q < max_work)
+          work[eb + q] = make_int4((int)(base + j), ea + q * kRowsPerItem, min(kRowsPerItem, c[j] - q * kRowsPerItem), 0);
       ea += c[j]; eb += it;
       prim_cnt[base + j] = 0;
       prim_cursor[base + j] = 0;

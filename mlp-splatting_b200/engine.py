@@ -120,6 +120,7 @@ class FrameStats:
     waves: int
     wave_records: int
     work_items: int
+    work_total: int = 0   # 128-row evaluator blocks of the whole frame
 
 
 class RenderError(RuntimeError):
@@ -244,7 +245,7 @@ class FrameRenderer:
         rec = int(u[L.ST_RECORDS_LO]) | (int(u[L.ST_RECORDS_LO + 1]) << 32)
         used = int(u[L.ST_USED_LO]) | (int(u[L.ST_USED_LO + 1]) << 32)
         stats = FrameStats(int(s[L.ST_PAIRS]), int(s[L.ST_MAX_TILE_LEN]), rec, used, int(s[L.ST_WAVES]),
-                           int(s[L.ST_WAVE_RECORDS]), int(s[L.ST_WORK_ITEMS]))
+                           int(s[L.ST_WAVE_RECORDS]), int(s[L.ST_WORK_ITEMS]), int(s[L.ST_WORK_TOTAL]))
         return int(s[L.ST_BITS]), stats
 
     def _grow(self, bits, stats):
