@@ -345,7 +345,7 @@ def main():
             "vs_baseline": None, "dtype": "f16" if prec == L.PRECISION_F16 else "f32", "data": "synthetic",
             "config": workload_config(args.workload, cfg, world, args.encoder),
             "record_mlp_evals_per_sec": float(rec_t[0]) * (fps / frames_per_step if nviews > 1 else fps),
-            "records_per_frame": {"evaluated": stats.records, "composited": stats.used, "candidate_pairs": stats.pairs, "evaluator_blocks": stats.work_total,
+            "records_per_frame": {"evaluated": stats.records, "composited": stats.used, "candidate_pairs": stats.pairs, "pairs_after_tile_pretest": stats.pairs_kept, "evaluator_blocks": stats.work_total,
                                   "waves": stats.waves, "max_tile_len": stats.max_tile_len},
             "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": 2 * r.P * 12 * max(len(units), 1),
                     "d2h_bytes_per_step": (r.P * 16 + 64) * max(len(units), 1),

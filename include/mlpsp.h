@@ -43,6 +43,7 @@ extern "C" {
 #define MLPSP_ST_WAVE_RECORDS 8    /* largest record count of a single wave */
 #define MLPSP_ST_WORK_ITEMS 9      /* largest number of evaluator work items of a single wave */
 #define MLPSP_ST_WORK_TOTAL 10     /* evaluator work items (128-row blocks) of the whole frame */
+#define MLPSP_ST_PAIRS_KEPT 11     /* mlpsp_render_frame: candidate pairs left after the tile pre-test */
 
 /* bits 1,2,4 match the reference validator (np_tile_kernels.cu:4499-4519) */
 #define MLPSP_ST_BAD_OFFSETS 1       /* tile_offsets not 0-based / monotone / in bounds */
@@ -118,6 +119,13 @@ typedef struct mlpsp_frame {
   int32_t tile_row_begin; /* binning keeps only tile rows [tile_row_begin, tile_row_end); both 0 = the whole image. */
   int32_t tile_row_end;   /* Used to share one view between GPUs by bands of tile rows: tiles outside the band get
                              empty lists and their pixels the background. */
+  int32_t tile_pretest;   /* mlpsp_render_frame only.  0 = before sorting, drop every candidate that no ray of its
+                             tile can hit (a conservative ellipsoid-against-tile test with no reference
+                             counterpart; the image is the same, the lists the wave kernels walk are shorter);
+                             it is skipped when mask_used is requested, so that those masks stay aligned with the
+                             full sorted lists.  1 = never drop.  With the test on, sorted_prims holds the kept
+                             candidates of every tile in depth order followed by -1 entries. */
+  int32_t reserved1;
 } mlpsp_frame;
 
 const char* mlpsp_last_error(void);
@@ -197,7 +205,8 @@ int mlpsp_render_sorted(const mlpsp_scene* scene, const mlpsp_frame* frame, void
 /* bin + sort + render_sorted: what NeuralPrimitiveSceneTileCUDA.forward does per frame
  * (cumodel.py:951-1160).  Here frame->tile_prims is left in binning scatter order (the per-tile sort
  * breaks depth ties by id, which gives the same sorted_prims as sorting the ascending-id lists);
- * call mlpsp_bin_tiles when the ascending-id lists themselves are wanted. */
+ * call mlpsp_bin_tiles when the ascending-id lists themselves are wanted.  See frame->tile_pretest for
+ * what sorted_prims holds afterwards. */
 int mlpsp_render_frame(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
 
 /* Pixel-major records of the frame just rendered with frame->keep_records = 1 on the same scratch: the

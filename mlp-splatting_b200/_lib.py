@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libmlpsp_b200.so")
 
 STATUS_WORDS = 16
 ST_BITS, ST_MAX_TILE_LEN, ST_PAIRS, ST_WAVES = 0, 1, 2, 3
-ST_RECORDS_LO, ST_USED_LO, ST_WAVE_RECORDS, ST_WORK_ITEMS, ST_WORK_TOTAL = 4, 6, 8, 9, 10
+ST_RECORDS_LO, ST_USED_LO, ST_WAVE_RECORDS, ST_WORK_ITEMS, ST_WORK_TOTAL, ST_PAIRS_KEPT = 4, 6, 8, 9, 10, 11
 BIT_BAD_OFFSETS, BIT_TILE_CAPACITY, BIT_BAD_IDS = 1, 2, 4
 BIT_PAIR_OVERFLOW, BIT_RECORD_OVERFLOW, BIT_NUMERIC, BIT_TIMEOUT = 8, 16, 64, 128
 BIT_TILE_ORIGINS, BIT_CONE_TOO_WIDE = 256, 512
@@ -46,6 +46,7 @@ class Frame(C.Structure):
         ("status", _fp), ("num_waves", C.c_int32), ("wave_len", C.c_int32 * MAX_WAVES),
         ("keep_records", C.c_int32), ("sort_key", C.c_int32),
         ("tile_row_begin", C.c_int32), ("tile_row_end", C.c_int32),
+        ("tile_pretest", C.c_int32), ("reserved1", C.c_int32),
     ]
 
 

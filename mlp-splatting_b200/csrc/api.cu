@@ -97,12 +97,13 @@ static int get_scratch(const mlpsp_scene* sc, const mlpsp_frame* fr, Scratch& s,
   return MLPSP_OK;
 }
 
-static int render_sorted_checked(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st) {
+static int render_sorted_checked(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st,
+                                 bool lists_refined = false) {
   MLPSP_REQUIRE(fr->rays_o && fr->rays_d && fr->rgb && fr->alpha, MLPSP_E_ARG, "render: rays or outputs missing");
   MLPSP_REQUIRE(fr->precision == MLPSP_PRECISION_F32 || fr->precision == MLPSP_PRECISION_F16, MLPSP_E_ARG,
                 "render: unknown precision %d", fr->precision);
   MLPSP_REQUIRE(fr->num_waves >= 0 && fr->num_waves <= MLPSP_MAX_WAVES, MLPSP_E_ARG, "render: bad num_waves");
-  return launch_render_sorted(sc, fr, s, st);
+  return launch_render_sorted(sc, fr, s, st, lists_refined);
 }
 
 }  // namespace mlpsp
@@ -243,9 +244,12 @@ extern "C" int mlpsp_render_frame(const mlpsp_scene* sc, const mlpsp_frame* fr, 
   cudaStream_t st = (cudaStream_t)stream;
   rc = launch_bin(sc, fr, s, st, /*order_lists=*/false);
   if (rc) return rc;
-  rc = launch_sort(sc, fr, nullptr, st, /*unordered_input=*/true, s.active[1], s.counters + kCtrScratch + 2);
+  // consumed-record masks are indexed by position in the full sorted list, so the pre-test stays off for them
+  const bool pretest = fr->tile_pretest == 0 && fr->mask_used == nullptr && fr->tile == 8;
+  rc = launch_sort(sc, fr, nullptr, st, /*unordered_input=*/true, s.active[1], s.counters + kCtrScratch + 2,
+                   pretest ? s.tile_frame : nullptr, pretest ? s.tile_len : nullptr);
   if (rc) return rc;
-  return render_sorted_checked(sc, fr, s, st);
+  return render_sorted_checked(sc, fr, s, st, pretest);
 }
 
 extern "C" int mlpsp_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, int64_t* offsets, int32_t* ids,

@@ -137,6 +137,84 @@ __device__ __forceinline__ bool surely_misses(const Geom& g, V3 o, V3 d, float b
   return (wx * wx + wy * wy + wz * wz) > bound2 * (g.smax * g.smax);
 }
 
+// ---- per-tile ray frame and the (tile, primitive) pre-test of the fused frame path ----
+// All rays of a tile leave one origin o; with an orthonormal frame (a, u, v), a along the tile's mean
+// direction, every ray direction is a + alpha u + beta v up to scale (alpha = d.u / d.a, beta = d.v / d.a),
+// and the tile's 64 rays lie inside the rectangle [a0, a1] x [b0, b1] of those coordinates (slightly
+// inflated).  a0 > a1 marks a tile without such a frame (several origins, a ray more than 60 degrees off the
+// mean, non-finite input): no candidate of it is ever rejected.
+struct TileFrame {
+  float ox, oy, oz, a0;
+  float ax, ay, az, a1;
+  float ux, uy, uz, b0;
+  float vx, vy, vz, b1;
+};
+
+__device__ __forceinline__ float quad_min_1d(float A, float B, float C, float lo, float hi) {
+  // min over [lo, hi] of A t^2 + 2 B t + C
+  const float qlo = fmaf(fmaf(A, lo, 2.f * B), lo, C), qhi = fmaf(fmaf(A, hi, 2.f * B), hi, C);
+  float m = fminf(qlo, qhi);
+  if (A > 0.f) {
+    const float t = fminf(fmaxf(-B / A, lo), hi);
+    m = fminf(m, fmaf(fmaf(A, t, 2.f * B), t, C));
+  }
+  return m;
+}
+
+// True only when no ray of the tile's rectangle can reach decay > thr against this primitive, i.e. when
+// every such line stays outside the ellipsoid r^2 <= K0 = -2 ln thr.  In the primitive's whitened frame
+// (rotate by R^T, divide axis k by exp(ls_k)) the ellipsoid is the sphere of radius sqrt(K0) around the
+// origin and a line from x with direction e meets it iff |x cross e|^2 <= K0 |e|^2.  Both sides are
+// quadratic in (alpha, beta), so q = |x cross e|^2 - K |e|^2 is minimised exactly over the rectangle
+// (stationary point, four edges).  K carries a 0.2 % margin and tol bounds the rounding of this test and of
+// hit_test (which works in world space, where a position error of a few ulps of |c - o| is magnified by the
+// largest inverse scale), so a rejected pair is one hit_test rejects for every pixel of the tile and the
+// rendered result does not depend on the pre-test.  Any NaN makes the test answer false.
+__device__ __forceinline__ bool tile_surely_misses(const Geom& g, const TileFrame& f, float K0) {
+  if (!(f.a0 <= f.a1)) return false;
+  const float isx = __fsqrt_rn(g.mx), isy = __fsqrt_rn(g.my), isz = __fsqrt_rn(g.mz);
+  const V3 v = {g.cx - f.ox, g.cy - f.oy, g.cz - f.oz};
+  V3 x = rot_conj(g.qw, g.qx, g.qy, g.qz, v);
+  V3 e0 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{f.ax, f.ay, f.az});
+  V3 e1 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{f.ux, f.uy, f.uz});
+  V3 e2 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{f.vx, f.vy, f.vz});
+  x.x *= isx; x.y *= isy; x.z *= isz;
+  e0.x *= isx; e0.y *= isy; e0.z *= isz;
+  e1.x *= isx; e1.y *= isy; e1.z *= isz;
+  e2.x *= isx; e2.y *= isy; e2.z *= isz;
+  const V3 w0 = {x.y * e0.z - x.z * e0.y, x.z * e0.x - x.x * e0.z, x.x * e0.y - x.y * e0.x};
+  const V3 w1 = {x.y * e1.z - x.z * e1.y, x.z * e1.x - x.x * e1.z, x.x * e1.y - x.y * e1.x};
+  const V3 w2 = {x.y * e2.z - x.z * e2.y, x.z * e2.x - x.x * e2.z, x.x * e2.y - x.y * e2.x};
+  const float K = K0 * 1.002f;
+  const float e00 = e0.x * e0.x + e0.y * e0.y + e0.z * e0.z;
+  const float e11 = e1.x * e1.x + e1.y * e1.y + e1.z * e1.z;
+  const float e22 = e2.x * e2.x + e2.y * e2.y + e2.z * e2.z;
+  const float a11 = (w1.x * w1.x + w1.y * w1.y + w1.z * w1.z) - K * e11;
+  const float a22 = (w2.x * w2.x + w2.y * w2.y + w2.z * w2.z) - K * e22;
+  const float a12 = (w1.x * w2.x + w1.y * w2.y + w1.z * w2.z) - K * (e1.x * e2.x + e1.y * e2.y + e1.z * e2.z);
+  const float b1 = (w0.x * w1.x + w0.y * w1.y + w0.z * w1.z) - K * (e0.x * e1.x + e0.y * e1.y + e0.z * e1.z);
+  const float b2 = (w0.x * w2.x + w0.y * w2.y + w0.z * w2.z) - K * (e0.x * e2.x + e0.y * e2.y + e0.z * e2.z);
+  const float c0 = (w0.x * w0.x + w0.y * w0.y + w0.z * w0.z) - K * e00;
+  if (!(fabsf(a11) + fabsf(a22) + fabsf(a12) + fabsf(b1) + fabsf(b2) + fabsf(c0) < 3.0e38f)) return false;
+  // edges alpha = a0 / a1 (quadratics in beta) and beta = b0 / b1 (quadratics in alpha)
+  float m = quad_min_1d(a22, fmaf(a12, f.a0, b2), fmaf(fmaf(a11, f.a0, 2.f * b1), f.a0, c0), f.b0, f.b1);
+  m = fminf(m, quad_min_1d(a22, fmaf(a12, f.a1, b2), fmaf(fmaf(a11, f.a1, 2.f * b1), f.a1, c0), f.b0, f.b1));
+  m = fminf(m, quad_min_1d(a11, fmaf(a12, f.b0, b1), fmaf(fmaf(a22, f.b0, 2.f * b2), f.b0, c0), f.a0, f.a1));
+  m = fminf(m, quad_min_1d(a11, fmaf(a12, f.b1, b1), fmaf(fmaf(a22, f.b1, 2.f * b2), f.b1, c0), f.a0, f.a1));
+  const float det = a11 * a22 - a12 * a12;
+  if (a11 > 0.f && det > 0.f) {
+    const float al = (a12 * b2 - a22 * b1) / det, be = (a12 * b1 - a11 * b2) / det;
+    if (al >= f.a0 && al <= f.a1 && be >= f.b0 && be <= f.b1) m = fminf(m, fmaf(b1, al, fmaf(b2, be, c0)));
+  }
+  const float ismax = fmaxf(isx, fmaxf(isy, isz));
+  const float dist = __fsqrt_rn(v.x * v.x + v.y * v.y + v.z * v.z);
+  // largest |e| over the rectangle
+  const float emax = __fsqrt_rn(e00) + fmaxf(fabsf(f.a0), fabsf(f.a1)) * __fsqrt_rn(e11) +
+                     fmaxf(fabsf(f.b0), fabsf(f.b1)) * __fsqrt_rn(e22);
+  const float tol = (2e-5f * __fsqrt_rn(K0) * dist * ismax + 1e-4f * K0) * emax * emax;
+  return m > tol;
+}
+
 __device__ __forceinline__ V3 load3(const float* __restrict__ p, int64_t i) {
   V3 r = { __ldg(p + i * 3), __ldg(p + i * 3 + 1), __ldg(p + i * 3 + 2) };
   return r;

@@ -52,6 +52,8 @@ struct Scratch {
   int32_t* px_off;       // [P+2] their exclusive prefix
   uint32_t* used32;      // [2*max_pairs] consumed-record mask halves per pair (when the caller gives none)
   int32_t* active[2];    // [T] each
+  TileFrame* tile_frame; // [T] ray frame of every tile (tile pre-test of the fused frame path)
+  int32_t* tile_len;     // [T] candidates per tile that the wave kernels traverse
   int32_t* counters;     // [kNumCounters]
   int64_t max_work;
   int64_t bytes;
@@ -98,6 +100,8 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.active[0] = (int32_t*)take(4 * T);
   s.active[1] = (int32_t*)take(4 * T);
   s.counters = (int32_t*)take(4 * kNumCounters);
+  s.tile_frame = (TileFrame*)take(64 * T);
+  s.tile_len = (int32_t*)take(4 * T);
   s.bytes = off;
   return s;
 }
@@ -136,10 +140,14 @@ int launch_bin_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratc
                       const float* views_host, int num_views, cudaStream_t st);
 int launch_bin_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
 // long_list [T] / long_count [1]: device scratch for the tiles that take the block-wide sort
+// frames / tile_len (both or neither): drop the candidates no ray of the tile can hit before sorting; the
+// dropped tail of every list is filled with -1 and tile_len receives the number of candidates kept
 int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st, bool unordered_input,
-                int32_t* long_list, int32_t* long_count);
+                int32_t* long_list, int32_t* long_count, TileFrame* frames = nullptr, int32_t* tile_len = nullptr);
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st);
-int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
+// lists_refined: s.tile_len already holds the traversal length of every tile (written by launch_sort)
+int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st,
+                         bool lists_refined = false);
 // rec_ext (optional): per record (sigma_raw, sigma_logit, layer-1 ReLU bitmask, layer-2 ReLU bitmask)
 int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,

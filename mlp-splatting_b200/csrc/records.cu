@@ -53,9 +53,14 @@ __global__ void k_init_pixels(int64_t P, float4* __restrict__ px_state, float2* 
   if (depth_t) depth_t[i] = 0.f;
 }
 
-__global__ void k_init_tiles(int T, int32_t* __restrict__ active0, int32_t* __restrict__ counters) {
+// tile_len (when not already written by the sort's tile pre-test) = the length of the caller's list
+__global__ void k_init_tiles(int T, int32_t* __restrict__ active0, int32_t* __restrict__ counters,
+                             const int32_t* __restrict__ tile_offsets, int32_t* __restrict__ tile_len, int lists_refined) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < T) active0[t] = t;
+  if (t < T) {
+    active0[t] = t;
+    if (!lists_refined) tile_len[t] = tile_offsets[t + 1] - tile_offsets[t];
+  }
   if (t == 0) {
     counters[kCtrRecords] = 0; counters[kCtrWork] = 0; counters[kCtrWorkNext] = 0;
     counters[kCtrActive0] = T; counters[kCtrActive1] = 0;
@@ -66,7 +71,7 @@ __global__ void k_init_tiles(int T, int32_t* __restrict__ active0, int32_t* __re
 // 8 warps per tile: warp w owns pixel half (w & 1) and candidates (w >> 1) + 4j of the window.
 __global__ void __launch_bounds__(256) k_hits(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
-    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
     float thr, float bound2, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo,
     int hi, const float4* __restrict__ px_state, uint32_t* __restrict__ masks32, uint32_t* __restrict__ pair_base,
     int32_t* __restrict__ prim_cnt, int32_t* __restrict__ counters, int64_t max_records,
@@ -82,7 +87,7 @@ __global__ void __launch_bounds__(256) k_hits(
   for (int slot_i = blockIdx.x; slot_i < n_active; slot_i += gridDim.x) {
   const int tile = active[slot_i];
   const int s = tile_offsets[tile];
-  const int len = tile_offsets[tile + 1] - s;
+  const int len = tile_len[tile];
   const int wlo = min(lo, len), whi = min(hi, len);
   const int nwin = whi - wlo;
   if (nwin <= 0) continue;
@@ -284,7 +289,7 @@ __device__ __forceinline__ float4 tetra_gates(const Hit& h, float lsx, float lsy
 // found by binary search in the slot prefix, and to the pixel of the (r - prefix)-th set mask bit.
 __global__ void __launch_bounds__(256) k_fill(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom,
-    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
     float thr, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo, int hi,
     const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base,
     const int32_t* __restrict__ prim_off, int32_t* __restrict__ prim_cursor, RecIn* __restrict__ rec_in,
@@ -300,7 +305,7 @@ __global__ void __launch_bounds__(256) k_fill(
   for (int slot_i = blockIdx.x; slot_i < n_active; slot_i += gridDim.x) {
   const int tile = active[slot_i];
   const int s = tile_offsets[tile];
-  const int len = tile_offsets[tile + 1] - s;
+  const int len = tile_len[tile];
   const int wlo = min(lo, len), whi = min(hi, len);
   const int nwin = whi - wlo;
   if (nwin <= 0) continue;
@@ -359,7 +364,7 @@ __global__ void __launch_bounds__(256) k_fill(
 // --------------------------------------------------------------------------- composite ----
 // 64 threads per tile; each warp owns 32 pixels and stops as soon as none of them is live.
 __global__ void __launch_bounds__(64) k_composite(
-    const int32_t* __restrict__ tile_offsets, int W, int H, int ntx, const int32_t* __restrict__ active,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, int W, int H, int ntx, const int32_t* __restrict__ active,
     const int32_t* __restrict__ active_count, int lo, int hi, const uint32_t* __restrict__ masks32,
     const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out, const float* __restrict__ rec_t,
     float4* __restrict__ px_state, float2* __restrict__ px_depth, float* __restrict__ rgb,
@@ -373,7 +378,7 @@ __global__ void __launch_bounds__(64) k_composite(
   for (int slot_i = blockIdx.x; slot_i < n_active; slot_i += gridDim.x) {
   const int tile = active[slot_i];
   const int s = tile_offsets[tile];
-  const int len = tile_offsets[tile + 1] - s;
+  const int len = tile_len[tile];
   const int wlo = min(lo, len), whi = min(hi, len);
   const int lane = threadIdx.x & 31, half = threadIdx.x >> 5;
   const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
@@ -452,7 +457,7 @@ constexpr int kFeatChan = 256;     // channels per CTA: (tile, channel block) pa
 
 // Shared memory: [64][CB] accumulators, then the tile's consumed masks and their record prefix.
 __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
-    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
     const uint32_t* __restrict__ used32, const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base,
     const float* __restrict__ rec_w, const float4* __restrict__ rec_gate, const float* __restrict__ feat_attr,
     int S, int C, int CB, float* __restrict__ out_feat, const int32_t* __restrict__ status) {
@@ -471,7 +476,7 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < 64 * CB; i += kFeatThreads) s_acc[i] = 0.f;
   const int s = tile_offsets[tile];
-  const int len = min(tile_offsets[tile + 1] - s, kWinMax);
+  const int len = min(tile_len[tile], kWinMax);
   int running = 0;
   for (int j0 = 0; j0 < len; j0 += kFeatThreads) {
     const int j = j0 + tid;
@@ -594,7 +599,8 @@ int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mas
   return cuda_check(cudaGetLastError(), "hit_masks");
 }
 
-int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st) {
+int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st,
+                         bool lists_refined) {
   const int W = fr->width, H = fr->height;
   const int T = num_tiles(W, H, 8);
   const int ntx = (W + 7) / 8;
@@ -619,7 +625,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     LaunchScope scope(kKMisc, 2, st);
     k_init_pixels<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha,
                                                                fr->depth_t, bg[0], bg[1], bg[2]);
-    k_init_tiles<<<(T + 255) / 256, 256, 0, st>>>(T, s.active[0], s.counters);
+    k_init_tiles<<<(T + 255) / 256, 256, 0, st>>>(T, s.active[0], s.counters, fr->tile_offsets, s.tile_len, lists_refined ? 1 : 0);
   }
   if (used32) MLPSP_CUDA_OK(cudaMemsetAsync(used32, 0, 8 * (size_t)fr->max_pairs, st));
   if (n == 0) {
@@ -645,14 +651,14 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     const int32_t* act = s.active[cur];
     const int32_t* act_n = s.counters + kCtrActive0 + cur;
     { LaunchScope scope(kKHits, 1, st);
-    k_hits<<<wave_grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, fr->sorted_prims,
+    k_hits<<<wave_grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
                               s.prim_cnt, s.counters, fr->max_records, fr->status); }
     int rc = launch_prim_scan(s, n, nxt, fr->status, st);
     if (rc) return rc;
     { LaunchScope scope(kKFill, 1, st);
-    k_fill<<<wave_grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
+    k_fill<<<wave_grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
                               s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr,
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
@@ -665,7 +671,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                           fr->status, st);
     if (rc) return rc;
     { LaunchScope scope(kKComposite, 1, st);
-    k_composite<<<std::min(T, sms * 32), 64, 0, st>>>(fr->tile_offsets, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+    k_composite<<<std::min(T, sms * 32), 64, 0, st>>>(fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
                                   fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
                                   keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,
@@ -684,7 +690,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     }
     LaunchScope scope(kKComposite, 1, st);
     const dim3 grid(T, (sc->feat_dim + CB - 1) / CB);
-    k_feature_composite<<<grid, kFeatThreads, smem, st>>>(fr->tile_offsets, fr->sorted_prims, W, H, ntx, used32, s.masks32,
+    k_feature_composite<<<grid, kFeatThreads, smem, st>>>(fr->tile_offsets, s.tile_len, fr->sorted_prims, W, H, ntx, used32, s.masks32,
                                                          s.pair_base, s.rec_w, s.rec_gate, sc->feat_attr, sc->feat_slots,
                                                          sc->feat_dim, CB, fr->feat, fr->status);
   }
@@ -698,7 +704,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
 template <bool EMIT>
 __global__ void __launch_bounds__(64) k_export(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom,
-    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
     float thr, float beta, float tau, const uint32_t* __restrict__ used32, const uint32_t* __restrict__ masks32,
     const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out, const float4* __restrict__ rec_ext,
     const float* __restrict__ rec_tr, const float4* __restrict__ px_state, int32_t* __restrict__ px_cnt,
@@ -707,7 +713,7 @@ __global__ void __launch_bounds__(64) k_export(
     int64_t max_out, const int32_t* __restrict__ status) {
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int tile = blockIdx.x;
-  const int s = tile_offsets[tile], e = tile_offsets[tile + 1];
+  const int s = tile_offsets[tile], e = s + tile_len[tile];
   const int lane = threadIdx.x & 31, half = threadIdx.x >> 5;
   const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
   V3 o = {0.f, 0.f, 0.f}, d = {0.f, 0.f, 0.f};
@@ -783,7 +789,7 @@ int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Sc
   int32_t* worst = s.counters + kCtrScratch;     // [0] largest per-pixel count, [1] capacity flag
   MLPSP_CUDA_OK(cudaMemsetAsync(worst, 0, 8, st));
   LaunchScope scope(kKMisc, 6, st);
-  k_export<false><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
+  k_export<false><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                                     W, H, ntx, fr->threshold, sc->gate_beta, sc->gate_tau, s.used32, s.masks32,
                                     s.pair_base, s.rec_out, s.rec_ext, s.rec_tr, s.px_state, s.px_cnt, nullptr, max_hits,
                                     worst, nullptr, nullptr, nullptr, nullptr, nullptr, 0, fr->status);
@@ -797,7 +803,7 @@ int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Sc
   if (total_host) *total_host = h[0];
   if (worst_host) *worst_host = h[2] ? -h[1] : h[1];
   if ((ids || x6 || raw || relu_masks || gates) && max_out >= h[0] && h[0] > 0) {
-    k_export<true><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, fr->sorted_prims,
+    k_export<true><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                                      W, H, ntx, fr->threshold, sc->gate_beta, sc->gate_tau, s.used32, s.masks32,
                                      s.pair_base, s.rec_out, s.rec_ext, s.rec_tr, s.px_state, s.px_cnt, s.px_off, max_hits,
                                      worst, ids, x6, raw, relu_masks, gates, max_out, fr->status);

@@ -3,7 +3,8 @@
 // Keys are positive floats (or the 1e30 sentinel), so their bit patterns order like the values and the
 // sort runs on the raw bits: a bitonic network in shared memory over the 64-bit composite (key bits,
 // tie-break); lists of up to 512 candidates are sorted by one warp (eight tiles per CTA), longer
-// lists by a whole CTA.
+// lists by a whole CTA.  In the fused frame path the sort also drops the candidates that no ray of the tile
+// can hit (tile_surely_misses) before they are sorted.
 #include "frame.cuh"
 
 namespace mlpsp {
@@ -44,66 +45,39 @@ __device__ __forceinline__ void warp_bitonic(T* buf) {
   }
 }
 
-// One warp sorts one tile of at most N candidates in its own slice of shared memory by the
-// composite (depth key bits, tie-break).  FROM_SCATTER: the list comes straight from the binning
-// scatter in arbitrary order and holds distinct ids, so the id itself is the tie-break: the result is
-// the stable sort of the ascending-id list, and the id is read back from the sorted composite.
-// Otherwise the tie-break is the position in the caller's list (stable sort of that list).
-template <int N, bool FROM_SCATTER>
-__device__ __forceinline__ void warp_sort_tile(unsigned long long* buf, const float4* __restrict__ geom, int n,
-                                               const int32_t* tile_prims, int32_t* __restrict__ sorted_prims,
-                                               float* __restrict__ keys_out, int s, int len, V3 o, V3 d, int key_mode) {
-  const int lane = threadIdx.x & 31;
-#pragma unroll
-  for (int i0 = 0; i0 < N; i0 += 32) {
-    const int i = i0 + lane;
-    unsigned long long kv = ~0ull;
-    if (i < len) {
-      const int p = tile_prims[s + i];
-      float key = MLPSP_SENTINEL_KEY;
-      if (p >= 0 && p < n) {
-        const Geom g = load_geom(geom, p);
-        key = key_mode ? tile_key_euclid(g, o, d) : tile_key(g, o, d);
-      }
-      kv = ((unsigned long long)__float_as_uint(key) << 32) | (unsigned long long)(uint32_t)(FROM_SCATTER ? p : i);
-    }
-    buf[i] = kv;
+// Composite of one candidate: (depth key bits << 32) | tie-break.  FROM_SCATTER: the list comes straight
+// from the binning scatter in arbitrary order and holds distinct ids, so the id itself is the tie-break
+// (the result is the stable sort of the ascending-id list) and the id is read back from the sorted
+// composite.  Otherwise the tie-break is the position in the caller's list (stable sort of that list).
+// With a tile frame, a candidate that no ray of the tile can hit (tile_surely_misses) is dropped: keep
+// comes back false.
+template <bool FROM_SCATTER>
+__device__ __forceinline__ unsigned long long make_composite(const float4* __restrict__ geom, int n, int p, int i, V3 o,
+                                                             V3 d, int key_mode, const TileFrame* tf, float K0,
+                                                             bool& keep) {
+  float key = MLPSP_SENTINEL_KEY;
+  keep = true;
+  if (p >= 0 && p < n) {
+    const Geom g = load_geom(geom, p);
+    if (tf && tile_surely_misses(g, *tf, K0)) keep = false;
+    key = key_mode ? tile_key_euclid(g, o, d) : tile_key(g, o, d);
   }
-  __syncwarp();
-  warp_bitonic<unsigned long long, N>(buf);
-  for (int i = lane; i < len; i += 32) {
-    const unsigned long long kv = buf[i];
-    sorted_prims[s + i] = FROM_SCATTER ? (int32_t)(uint32_t)kv : tile_prims[s + (int)(uint32_t)kv];
-    if (keys_out) keys_out[s + i] = __uint_as_float((uint32_t)(kv >> 32));
-  }
+  return ((unsigned long long)__float_as_uint(key) << 32) | (unsigned long long)(uint32_t)(FROM_SCATTER ? p : i);
 }
 
-// Block-wide path for long lists: the same bitonic network run by 256 threads on N = 1024 or 2048 slots.
-template <int THREADS, int N, bool FROM_SCATTER>
-__device__ __forceinline__ void block_sort_tile(unsigned long long* buf, const float4* __restrict__ geom, int n,
-                                                const int32_t* tile_prims, int32_t* __restrict__ sorted_prims,
-                                                float* __restrict__ keys_out, int s, int len, V3 o, V3 d, int key_mode) {
-  for (int i = threadIdx.x; i < N; i += THREADS) {
-    unsigned long long kv = ~0ull;
-    if (i < len) {
-      const int p = tile_prims[s + i];
-      float key = MLPSP_SENTINEL_KEY;
-      if (p >= 0 && p < n) {
-        const Geom g = load_geom(geom, p);
-        key = key_mode ? tile_key_euclid(g, o, d) : tile_key(g, o, d);
-      }
-      kv = ((unsigned long long)__float_as_uint(key) << 32) | (unsigned long long)(uint32_t)(FROM_SCATTER ? p : i);
+template <bool FROM_SCATTER>
+__device__ __forceinline__ void write_sorted(const unsigned long long* buf, const int32_t* tile_prims,
+                                             int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int s,
+                                             int kept, int len, int first, int step) {
+  for (int i = first; i < len; i += step) {
+    if (i < kept) {
+      const unsigned long long kv = buf[i];
+      sorted_prims[s + i] = FROM_SCATTER ? (int32_t)(uint32_t)kv : tile_prims[s + (int)(uint32_t)kv];
+      if (keys_out) keys_out[s + i] = __uint_as_float((uint32_t)(kv >> 32));
+    } else {
+      sorted_prims[s + i] = -1;   // dropped by the tile pre-test: never traversed (the tile's length is kept)
     }
-    buf[i] = kv;
   }
-  __syncthreads();
-  warp_bitonic<unsigned long long, N, THREADS>(buf);
-  for (int i = threadIdx.x; i < len; i += THREADS) {
-    const unsigned long long kv = buf[i];
-    sorted_prims[s + i] = FROM_SCATTER ? (int32_t)(uint32_t)kv : tile_prims[s + (int)(uint32_t)kv];
-    if (keys_out) keys_out[s + i] = __uint_as_float((uint32_t)(kv >> 32));
-  }
-  __syncthreads();
 }
 
 constexpr int kTilesPerCta = 8;
@@ -117,7 +91,8 @@ __global__ void __launch_bounds__(256) k_sort_tiles(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* tile_prims, int W, int H, int ts, int ntx, int T, int cap,
     int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode, int32_t* __restrict__ long_list,
-    int32_t* __restrict__ long_count, const int32_t* __restrict__ status) {
+    int32_t* __restrict__ long_count, const TileFrame* __restrict__ frames, float K0, int32_t* __restrict__ tile_len,
+    int32_t* __restrict__ status) {
   __shared__ __align__(16) unsigned long long s_buf[kTilesPerCta * kWarpSortMax];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -125,7 +100,7 @@ __global__ void __launch_bounds__(256) k_sort_tiles(
   if (tile >= T) return;
   const int s = tile_offsets[tile];
   const int len = min(tile_offsets[tile + 1] - s, cap);
-  if (len <= 0) return;
+  if (len <= 0) { if (tile_len && lane == 0) tile_len[tile] = 0; return; }
   if (len > kWarpSortMax) {
     if (lane == 0) long_list[atomicAdd(long_count, 1)] = tile;
     return;
@@ -135,23 +110,47 @@ __global__ void __launch_bounds__(256) k_sort_tiles(
   const int64_t pc = (int64_t)cy * W + cx;
   const V3 o = load3(rays_o, pc), d = load3(rays_d, pc);
   unsigned long long* buf = s_buf + warp * kWarpSortMax;
-  if (len <= 64) warp_sort_tile<64, IDSORT>(buf, geom, n, tile_prims, sorted_prims, keys_out, s, len, o, d, key_mode);
-  else if (len <= 128) warp_sort_tile<128, IDSORT>(buf, geom, n, tile_prims, sorted_prims, keys_out, s, len, o, d, key_mode);
-  else if (len <= 256) warp_sort_tile<256, IDSORT>(buf, geom, n, tile_prims, sorted_prims, keys_out, s, len, o, d, key_mode);
-  else warp_sort_tile<512, IDSORT>(buf, geom, n, tile_prims, sorted_prims, keys_out, s, len, o, d, key_mode);
+  TileFrame tf;
+  if (frames) tf = frames[tile];
+  int kept = 0;
+  for (int i0 = 0; i0 < len; i0 += 32) {
+    const int i = i0 + lane;
+    bool keep = false;
+    unsigned long long kv = ~0ull;
+    if (i < len) kv = make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode, frames ? &tf : nullptr, K0, keep);
+    const uint32_t m = __ballot_sync(0xffffffffu, keep);
+    if (keep) buf[kept + __popc(m & ((1u << lane) - 1u))] = kv;
+    kept += __popc(m);
+  }
+  const int N = kept <= 32 ? 32 : (kept <= 64 ? 64 : (kept <= 128 ? 128 : (kept <= 256 ? 256 : 512)));
+  for (int i = kept + lane; i < N; i += 32) buf[i] = ~0ull;
+  __syncwarp();
+  if (N == 32) warp_bitonic<unsigned long long, 32>(buf);
+  else if (N == 64) warp_bitonic<unsigned long long, 64>(buf);
+  else if (N == 128) warp_bitonic<unsigned long long, 128>(buf);
+  else if (N == 256) warp_bitonic<unsigned long long, 256>(buf);
+  else warp_bitonic<unsigned long long, 512>(buf);
+  write_sorted<IDSORT>(buf, tile_prims, sorted_prims, keys_out, s, kept, len, lane, 32);
+  if (tile_len && lane == 0) {
+    tile_len[tile] = kept;
+    if (kept) atomicAdd(status + MLPSP_ST_PAIRS_KEPT, kept);
+  }
 }
 
-// Long lists: one CTA per tile of long_list (grid-stride), block-wide radix sort.
+// Long lists: one CTA per tile of long_list (grid-stride), the same bitonic network run by the whole CTA
+// on the candidates that survive the tile pre-test.
 template <int THREADS, int CAP, bool IDSORT>
 __global__ void __launch_bounds__(THREADS) k_sort_long(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* tile_prims, int W, int H, int ts, int ntx,
     int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode,
     const int32_t* __restrict__ long_list, const int32_t* __restrict__ long_count,
-    const int32_t* __restrict__ status) {
+    const TileFrame* __restrict__ frames, float K0, int32_t* __restrict__ tile_len, int32_t* __restrict__ status) {
   __shared__ __align__(16) unsigned long long s_buf[CAP];
+  __shared__ int s_kept;
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int count = *long_count;
+  const int lane = threadIdx.x & 31;
   for (int q = blockIdx.x; q < count; q += gridDim.x) {
     const int tile = long_list[q];
     const int s = tile_offsets[tile];
@@ -160,44 +159,149 @@ __global__ void __launch_bounds__(THREADS) k_sort_long(
     const int cx = min(tx * ts + (ts >> 1), W - 1), cy = min(ty * ts + (ts >> 1), H - 1);
     const int64_t pc = (int64_t)cy * W + cx;
     const V3 o = load3(rays_o, pc), d = load3(rays_d, pc);
-    if (len <= CAP / 2)
-      block_sort_tile<THREADS, CAP / 2, IDSORT>(s_buf, geom, n, tile_prims, sorted_prims, keys_out, s, len, o, d, key_mode);
-    else
-      block_sort_tile<THREADS, CAP, IDSORT>(s_buf, geom, n, tile_prims, sorted_prims, keys_out, s, len, o, d, key_mode);
+    TileFrame tf;
+    if (frames) tf = frames[tile];
+    if (threadIdx.x == 0) s_kept = 0;
+    __syncthreads();
+    for (int i0 = 0; i0 < len; i0 += THREADS) {
+      const int i = i0 + threadIdx.x;
+      bool keep = false;
+      unsigned long long kv = ~0ull;
+      if (i < len) kv = make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode, frames ? &tf : nullptr, K0, keep);
+      // one shared-memory atomic per warp; the order inside the buffer is irrelevant before the sort
+      const uint32_t m = __ballot_sync(0xffffffffu, keep);
+      int base = 0;
+      if (lane == 0 && m) base = atomicAdd(&s_kept, __popc(m));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (keep) s_buf[base + __popc(m & ((1u << lane) - 1u))] = kv;
+    }
+    __syncthreads();
+    const int kept = s_kept;
+    const int N = kept <= CAP / 8 ? CAP / 8 : (kept <= CAP / 4 ? CAP / 4 : (kept <= CAP / 2 ? CAP / 2 : CAP));
+    for (int i = kept + threadIdx.x; i < N; i += THREADS) s_buf[i] = ~0ull;
+    __syncthreads();
+    if (N == CAP / 8) warp_bitonic<unsigned long long, CAP / 8, THREADS>(s_buf);
+    else if (N == CAP / 4) warp_bitonic<unsigned long long, CAP / 4, THREADS>(s_buf);
+    else if (N == CAP / 2) warp_bitonic<unsigned long long, CAP / 2, THREADS>(s_buf);
+    else warp_bitonic<unsigned long long, CAP, THREADS>(s_buf);
+    write_sorted<IDSORT>(s_buf, tile_prims, sorted_prims, keys_out, s, kept, len, threadIdx.x, THREADS);
+    if (tile_len && threadIdx.x == 0) {
+      tile_len[tile] = kept;
+      if (kept) atomicAdd(status + MLPSP_ST_PAIRS_KEPT, kept);
+    }
+    __syncthreads();
+  }
+}
+
+// ---- per-tile ray frames for the tile pre-test: one warp per tile, two pixels per lane ----
+__global__ void __launch_bounds__(256) k_tile_frames(const float* __restrict__ rays_o, const float* __restrict__ rays_d,
+                                                     int W, int H, int ntx, int T, TileFrame* __restrict__ frames) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x * 8 + warp;
+  if (tile >= T) return;
+  const int tx = tile % ntx, ty = tile / ntx;
+  V3 dd[2];
+  bool same = true;
+  const int64_t p0 = (int64_t)min(ty * 8, H - 1) * W + min(tx * 8, W - 1);
+  const V3 o0 = load3(rays_o, p0);
+  float sx = 0.f, sy = 0.f, sz = 0.f;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int k = h * 32 + lane;
+    // pixels past the image edge repeat the edge pixel: they add no new ray
+    const int64_t pix = (int64_t)min(ty * 8 + (k >> 3), H - 1) * W + min(tx * 8 + (k & 7), W - 1);
+    const V3 o = load3(rays_o, pix);
+    dd[h] = load3(rays_d, pix);
+    same = same && o.x == o0.x && o.y == o0.y && o.z == o0.z;
+    sx += dd[h].x; sy += dd[h].y; sz += dd[h].z;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    sx += __shfl_xor_sync(0xffffffffu, sx, off);
+    sy += __shfl_xor_sync(0xffffffffu, sy, off);
+    sz += __shfl_xor_sync(0xffffffffu, sz, off);
+  }
+  const float inv = rsqrtf(sx * sx + sy * sy + sz * sz);
+  const float ax = sx * inv, ay = sy * inv, az = sz * inv;
+  // u: the image's x direction made orthogonal to a (direction of pixel 7 minus pixel 0 of the first row);
+  // a fixed axis when the tile is one pixel wide
+  const int64_t p7 = (int64_t)min(ty * 8, H - 1) * W + min(tx * 8 + 7, W - 1);
+  const V3 d0 = load3(rays_d, p0), d7 = load3(rays_d, p7);
+  float ux = d7.x - d0.x, uy = d7.y - d0.y, uz = d7.z - d0.z;
+  if (!(ux * ux + uy * uy + uz * uz > 1e-12f)) {
+    ux = fabsf(ax) < 0.57f ? 1.f : 0.f; uy = fabsf(ax) < 0.57f ? 0.f : 1.f; uz = 0.f;
+  }
+  const float ua = ux * ax + uy * ay + uz * az;
+  ux -= ua * ax; uy -= ua * ay; uz -= ua * az;
+  const float uinv = rsqrtf(ux * ux + uy * uy + uz * uz);
+  ux *= uinv; uy *= uinv; uz *= uinv;
+  const float vx = ay * uz - az * uy, vy = az * ux - ax * uz, vz = ax * uy - ay * ux;
+  float a0 = 3e38f, a1 = -3e38f, b0 = 3e38f, b1 = -3e38f, cmin = 3e38f;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float da = dd[h].x * ax + dd[h].y * ay + dd[h].z * az;
+    const float al = (dd[h].x * ux + dd[h].y * uy + dd[h].z * uz) / da;
+    const float be = (dd[h].x * vx + dd[h].y * vy + dd[h].z * vz) / da;
+    const float len2 = dd[h].x * dd[h].x + dd[h].y * dd[h].y + dd[h].z * dd[h].z;
+    cmin = fminf(cmin, da * rsqrtf(len2));
+    same = same && (al == al) && (be == be) && fabsf(al) < 1e6f && fabsf(be) < 1e6f;
+    a0 = fminf(a0, al); a1 = fmaxf(a1, al); b0 = fminf(b0, be); b1 = fmaxf(b1, be);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    a0 = fminf(a0, __shfl_xor_sync(0xffffffffu, a0, off)); a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, off));
+    b0 = fminf(b0, __shfl_xor_sync(0xffffffffu, b0, off)); b1 = fmaxf(b1, __shfl_xor_sync(0xffffffffu, b1, off));
+    cmin = fminf(cmin, __shfl_xor_sync(0xffffffffu, cmin, off));
+  }
+  same = __all_sync(0xffffffffu, same);
+  const bool ok = same && cmin > 0.5f && (ax == ax) && (ux == ux) && fabsf(o0.x) < 1e30f && fabsf(o0.y) < 1e30f &&
+                  fabsf(o0.z) < 1e30f;
+  if (lane == 0) {
+    TileFrame f;
+    // inflate the rectangle: rounding of the coordinates themselves
+    const float pa = 1e-5f + 1e-3f * (a1 - a0), pb = 1e-5f + 1e-3f * (b1 - b0);
+    f.ox = o0.x; f.oy = o0.y; f.oz = o0.z; f.ax = ax; f.ay = ay; f.az = az;
+    f.ux = ux; f.uy = uy; f.uz = uz; f.vx = vx; f.vy = vy; f.vz = vz;
+    f.a0 = ok ? a0 - pa : 1.f; f.a1 = ok ? a1 + pa : -1.f;
+    f.b0 = b0 - pb; f.b1 = b1 + pb;
+    frames[tile] = f;
   }
 }
 
 int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st, bool unordered_input,
-                int32_t* long_list, int32_t* long_count) {
+                int32_t* long_list, int32_t* long_count, TileFrame* frames, int32_t* tile_len) {
   const int T = num_tiles(fr->width, fr->height, fr->tile);
   const int ntx = (fr->width + fr->tile - 1) / fr->tile;
   MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
                 "tile_capacity must be in [1, %d]", kSortCap);
   MLPSP_REQUIRE(long_list && long_count, MLPSP_E_ARG, "sort: scratch for the long-tile list missing");
+  MLPSP_REQUIRE(!frames || (tile_len && fr->tile == 8), MLPSP_E_ARG, "sort: the tile pre-test needs 8x8 tiles and a length array");
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   MLPSP_CUDA_OK(cudaMemsetAsync(long_count, 0, 4, st));
-  LaunchScope scope(kKSort, 2, st);
+  LaunchScope scope(kKSort, frames ? 3 : 2, st);
+  const float K0 = (float)(-2.0 * log((double)fr->threshold));
+  if (frames) k_tile_frames<<<(T + 7) / 8, 256, 0, st>>>(fr->rays_o, fr->rays_d, fr->width, fr->height, ntx, T, frames);
   const int grid = (T + kTilesPerCta - 1) / kTilesPerCta;
   const int grid_long = std::min(T, sms * 6);
   const float4* geom = (const float4*)sc->geom;
   if (unordered_input) {
     k_sort_tiles<true><<<grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
                                              fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out,
-                                             fr->sort_key, long_list, long_count, fr->status);
+                                             fr->sort_key, long_list, long_count, frames, K0, tile_len, fr->status);
     k_sort_long<256, kSortCap, true><<<grid_long, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
                                                                fr->tile_prims, fr->width, fr->height, fr->tile, ntx,
                                                                fr->sorted_prims, keys_out, fr->sort_key, long_list,
-                                                               long_count, fr->status);
+                                                               long_count, frames, K0, tile_len, fr->status);
   } else {
     k_sort_tiles<false><<<grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
                                               fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out,
-                                              fr->sort_key, long_list, long_count, fr->status);
+                                              fr->sort_key, long_list, long_count, frames, K0, tile_len, fr->status);
     k_sort_long<256, kSortCap, false><<<grid_long, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
                                                                 fr->tile_prims, fr->width, fr->height, fr->tile, ntx,
                                                                 fr->sorted_prims, keys_out, fr->sort_key, long_list,
-                                                                long_count, fr->status);
+                                                                long_count, frames, K0, tile_len, fr->status);
   }
   return cuda_check(cudaGetLastError(), "sort_tiles");
 }

@@ -121,6 +121,7 @@ class FrameStats:
     wave_records: int
     work_items: int
     work_total: int = 0   # 128-row evaluator blocks of the whole frame
+    pairs_kept: int = 0   # candidate pairs left after the tile pre-test (0 when it did not run)
 
 
 class RenderError(RuntimeError):
@@ -192,7 +193,8 @@ class FrameRenderer:
         return self.scratch
 
     def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
-               want_mask_used, waves, want_feat=False, keep_records=False, sort_key=0, tile_rows=None) -> L.Frame:
+               want_mask_used, waves, want_feat=False, keep_records=False, sort_key=0, tile_rows=None,
+               tile_pretest=True) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
         f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
@@ -228,6 +230,7 @@ class FrameRenderer:
         f.max_records = self.max_records
         f.keep_records = 1 if keep_records else 0
         f.sort_key = int(sort_key)
+        f.tile_pretest = 0 if tile_pretest else 1
         if tile_rows is not None:
             f.tile_row_begin, f.tile_row_end = int(tile_rows[0]), int(tile_rows[1])
         f.status = L.ptr(self.status)
@@ -245,7 +248,7 @@ class FrameRenderer:
         rec = int(u[L.ST_RECORDS_LO]) | (int(u[L.ST_RECORDS_LO + 1]) << 32)
         used = int(u[L.ST_USED_LO]) | (int(u[L.ST_USED_LO + 1]) << 32)
         stats = FrameStats(int(s[L.ST_PAIRS]), int(s[L.ST_MAX_TILE_LEN]), rec, used, int(s[L.ST_WAVES]),
-                           int(s[L.ST_WAVE_RECORDS]), int(s[L.ST_WORK_ITEMS]), int(s[L.ST_WORK_TOTAL]))
+                           int(s[L.ST_WAVE_RECORDS]), int(s[L.ST_WORK_ITEMS]), int(s[L.ST_WORK_TOTAL]), int(s[L.ST_PAIRS_KEPT]))
         return int(s[L.ST_BITS]), stats
 
     def _grow(self, bits, stats):
@@ -266,8 +269,10 @@ class FrameRenderer:
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
                rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False,
-               keep_records=False, sort_key=0, tile_rows=None):
-        """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling)."""
+               keep_records=False, sort_key=0, tile_rows=None, tile_pretest=True):
+        """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling).
+
+        tile_pretest=False keeps every binned candidate in the lists the wave kernels walk (same image)."""
         lib, d = self.lib, self.device
         if precision is None:
             precision = L.PRECISION_F16 if scene.has_f16 else L.PRECISION_F32
@@ -294,7 +299,8 @@ class FrameRenderer:
                                                           self.capacity, scene.n, L.ptr(self.status), st),
                             "mlpsp_validate_tile_lists")
                 f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves,
-                                want_feat=want_feat, keep_records=keep_records, sort_key=sort_key, tile_rows=tile_rows)
+                                want_feat=want_feat, keep_records=keep_records, sort_key=sort_key, tile_rows=tile_rows,
+                                tile_pretest=tile_pretest)
                 self._last_frame = (f, scene)
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")

@@ -522,3 +522,51 @@ def test_module_surface_matches_reference_class(dev):
     assert float((rgb3 - rgb).abs().max()) > 1e-2
     with pytest.raises(RuntimeError, match="must be moved to a CUDA device"):
         NeuralPrimitiveSceneTileCUDA(num_primitives=4)._activate_cuda_device()
+
+
+@pytest.mark.parametrize("name", ["tiny", "dense", "ragged", "one_tile"])
+def test_tile_pretest_drops_only_pairs_without_hits(dev, name):
+    """The fused frame path drops, before sorting, candidates that no ray of the tile can hit.
+
+    The kept candidates must be the full sorted list minus the dropped ones, in the same order; every
+    dropped pair must have an empty geometric hit mask; and the image must not change by a single bit."""
+    from mlp_splatting_b200 import _lib as L
+    from mlp_splatting_b200.engine import normalize_rows
+    scene, cam = small_case(**CASES[name])
+    thr = 5e-3
+    ps, r = _packed(scene, dev, pack_f16=True), _renderer(cam, dev)
+    ro, rd = _t(cam["rays_o"], dev), _t(cam["rays_d"], dev)
+    prims, offs = r.bin(ps, cam["view"], cam["proj"], thr)
+    M = int(prims.numel())
+    rdu = normalize_rows(rd)
+    full = r.sort(ps, ro, rdu, M).clone().cpu().numpy()
+    geo = r.hit_masks(ps, ro, rdu, thr, M).cpu().numpy().view(np.uint64)
+    offs_h = offs.cpu().numpy()
+    for prec in (L.PRECISION_F32, L.PRECISION_F16):
+        out = {}
+        for pre in (True, False):
+            rgb, a = r.render(ps, ro, rd, thr, view=cam["view"], proj=cam["proj"], precision=prec, tile_pretest=pre)
+            out[pre] = (rgb.clone(), a.clone(), r.last_stats)
+        on, off = out[True], out[False]
+        assert torch.equal(on[0], off[0]) and torch.equal(on[1], off[1])
+        assert on[2].used == off[2].used and on[2].pairs == off[2].pairs == M
+        assert 0 < on[2].pairs_kept <= M and off[2].pairs_kept == 0
+    # lists left behind by a pre-tested frame
+    r.render(ps, ro, rd, thr, view=cam["view"], proj=cam["proj"], precision=L.PRECISION_F32, tile_pretest=True)
+    kept_total = r.last_stats.pairs_kept
+    sp = r.sorted_prims[:M].cpu().numpy()
+    n_kept = 0
+    for t in range(len(offs_h) - 1):
+        s, e = int(offs_h[t]), int(offs_h[t + 1])
+        lst = sp[s:e]
+        k = int((lst >= 0).sum())
+        assert (lst[:k] >= 0).all() and (lst[k:] == -1).all()
+        n_kept += k
+        kept_set = set(lst[:k].tolist())
+        ref = full[s:e]
+        keep_mask = np.array([p in kept_set for p in ref.tolist()], dtype=bool)
+        np.testing.assert_array_equal(ref[keep_mask], lst[:k])          # same order as the full sort
+        assert not geo[s:e][~keep_mask].any()                            # dropped pairs never hit
+    assert n_kept == kept_total
+    if name != "one_tile":
+        assert kept_total < M    # the test is not vacuous on these scenes
