@@ -186,53 +186,25 @@ __global__ void k_prim_partial(const int32_t* __restrict__ prim_cnt, int n, int3
   if (threadIdx.x == 0) { blk[2 * blockIdx.x] = ta; blk[2 * blockIdx.x + 1] = tb; }
 }
 
-__global__ void k_prim_top(int32_t* __restrict__ blk, int nblk, int32_t* __restrict__ counters, int next_list,
-                           int64_t max_work, int32_t* __restrict__ status) {
+// Second pass: every block sums the partial totals of the blocks before it (a few hundred at most), scans
+// its own 4096 counts, writes the CSR offsets and the evaluator's work items and clears the counts for the
+// next wave; the last block also publishes the wave's totals.
+__global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict__ prim_cursor, int n,
+                             const int32_t* __restrict__ blk, int32_t* __restrict__ prim_off,
+                             int4* __restrict__ work, int64_t max_work, int32_t* __restrict__ counters, int next_list,
+                             int32_t* __restrict__ status) {
   __shared__ int warp_sums[32];
-  __shared__ int carry_a, carry_b;
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) {
     // after a record overflow, leave the size the wave asked for so the caller can grow its scratch
-    if (threadIdx.x == 0 && (status[MLPSP_ST_BITS] & MLPSP_ST_RECORD_OVERFLOW))
+    if (blockIdx.x == 0 && threadIdx.x == 0 && (status[MLPSP_ST_BITS] & MLPSP_ST_RECORD_OVERFLOW))
       atomicMax(status + MLPSP_ST_WAVE_RECORDS, counters[kCtrRecords]);
     return;
   }
-  if (threadIdx.x == 0) { carry_a = 0; carry_b = 0; }
-  __syncthreads();
-  for (int b0 = 0; b0 < nblk; b0 += 1024) {
-    const int i = b0 + threadIdx.x;
-    const int va = (i < nblk) ? blk[2 * i] : 0, vb = (i < nblk) ? blk[2 * i + 1] : 0;
-    int ta, tb;
-    const int ea = block_exclusive_scan(va, warp_sums, ta);
-    const int eb = block_exclusive_scan(vb, warp_sums, tb);
-    const int ca = carry_a, cb = carry_b;
-    if (i < nblk) { blk[2 * i] = ca + ea; blk[2 * i + 1] = cb + eb; }
-    __syncthreads();
-    if (threadIdx.x == 0) { carry_a = ca + ta; carry_b = cb + tb; }
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) {
-    const int R = carry_a;
-    int G = carry_b;
-    if ((int64_t)G > max_work) { G = (int)max_work; atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_RECORD_OVERFLOW); }
-    blk[2 * nblk] = R;
-    counters[kCtrWork] = G;
-    counters[kCtrWorkNext] = 0;
-    counters[kCtrActive0 + next_list] = 0;   // kCtrRecords keeps counting: compositing slots are unique per frame
-    if (R > 0) {
-      atomicAdd((unsigned long long*)(status + MLPSP_ST_RECORDS_LO), (unsigned long long)R);
-      atomicMax(status + MLPSP_ST_WAVE_RECORDS, R);
-      atomicMax(status + MLPSP_ST_WORK_ITEMS, G);
-      atomicAdd(status + MLPSP_ST_WORK_TOTAL, G);
-      atomicAdd(status + MLPSP_ST_WAVES, 1);
-    }
-  }
-}
-
-__global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict__ prim_cursor, int n,
-                             const int32_t* __restrict__ blk, int32_t* __restrict__ prim_off,
-                             int4* __restrict__ work, int64_t max_work, const int32_t* __restrict__ status) {
-  __shared__ int warp_sums[32];
-  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  int pa = 0, pb = 0;
+  for (int i = threadIdx.x; i < (int)blockIdx.x; i += blockDim.x) { pa += blk[2 * i]; pb += blk[2 * i + 1]; }
+  int base_a, base_b;
+  block_exclusive_scan(pa, warp_sums, base_a);
+  block_exclusive_scan(pb, warp_sums, base_b);
   const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
   int c[4], a = 0, b = 0;
 #pragma unroll
@@ -241,8 +213,8 @@ __global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict
     a += c[j]; b += items_of(c[j]);
   }
   int ta, tb;
-  int ea = block_exclusive_scan(a, warp_sums, ta) + blk[2 * blockIdx.x];
-  int eb = block_exclusive_scan(b, warp_sums, tb) + blk[2 * blockIdx.x + 1];
+  int ea = block_exclusive_scan(a, warp_sums, ta) + base_a;
+  int eb = block_exclusive_scan(b, warp_sums, tb) + base_b;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     if (base + j < n) {
@@ -256,16 +228,31 @@ __global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict
       prim_cursor[base + j] = 0;
     }
   }
-  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) prim_off[n] = blk[2 * gridDim.x];
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+    const int R = base_a + ta;
+    int G = base_b + tb;
+    if ((int64_t)G > max_work) { G = (int)max_work; atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_RECORD_OVERFLOW); }
+    prim_off[n] = R;
+    counters[kCtrWork] = G;
+    counters[kCtrWorkNext] = 0;
+    counters[kCtrActive0 + next_list] = 0;   // kCtrRecords keeps counting: compositing slots are unique per frame
+    if (R > 0) {
+      atomicAdd((unsigned long long*)(status + MLPSP_ST_RECORDS_LO), (unsigned long long)R);
+      atomicMax(status + MLPSP_ST_WAVE_RECORDS, R);
+      atomicMax(status + MLPSP_ST_WORK_ITEMS, G);
+      atomicAdd(status + MLPSP_ST_WORK_TOTAL, G);
+      atomicAdd(status + MLPSP_ST_WAVES, 1);
+    }
+  }
 }
 
 int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st) {
   const int nblk = (n + kScanItems - 1) / kScanItems;
   if (nblk == 0) return MLPSP_OK;
-  LaunchScope scope(kKScan, 3, st);
+  LaunchScope scope(kKScan, 2, st);
   k_prim_partial<<<nblk, 1024, 0, st>>>(s.prim_cnt, n, s.scan_blk, status);
-  k_prim_top<<<1, 1024, 0, st>>>(s.scan_blk, nblk, s.counters, next_list, s.max_work, status);
-  k_prim_final<<<nblk, 1024, 0, st>>>(s.prim_cnt, s.prim_cursor, n, s.scan_blk, s.prim_off, s.work, s.max_work, status);
+  k_prim_final<<<nblk, 1024, 0, st>>>(s.prim_cnt, s.prim_cursor, n, s.scan_blk, s.prim_off, s.work, s.max_work, s.counters,
+                                     next_list, status);
   return cuda_check(cudaGetLastError(), "prim_scan");
 }
 
@@ -587,7 +574,9 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
 }
 
 // ------------------------------------------------------------------------------ driver ----
-static const int kDefaultWaves[] = {32, 32, 64, 128, 256, 512, INT_MAX};
+// after the tile pre-test a tile's list rarely holds more than a few hundred candidates, and few tiles
+// need more than the first hundred: the tail wave takes whatever is left
+static const int kDefaultWaves[] = {32, 32, 64, 128, 256, INT_MAX};
 
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st) {
   const int T = num_tiles(fr->width, fr->height, fr->tile);
