@@ -242,12 +242,12 @@ extern "C" int mlpsp_render_frame(const mlpsp_scene* sc, const mlpsp_frame* fr, 
   rc = get_scratch(sc, fr, s, "mlpsp_render_frame");
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  rc = launch_bin(sc, fr, s, st, /*order_lists=*/false);
-  if (rc) return rc;
   // consumed-record masks are indexed by position in the full sorted list, so the pre-test stays off for them
   const bool pretest = fr->tile_pretest == 0 && fr->mask_used == nullptr && fr->tile == 8;
+  rc = launch_bin(sc, fr, s, st, /*order_lists=*/false, pretest);
+  if (rc) return rc;
   rc = launch_sort(sc, fr, nullptr, st, /*unordered_input=*/true, s.active[1], s.counters + kCtrScratch + 2,
-                   pretest ? s.tile_frame : nullptr, pretest ? s.tile_len : nullptr);
+                   pretest ? s.tile_len : nullptr);
   if (rc) return rc;
   return render_sorted_checked(sc, fr, s, st, pretest);
 }

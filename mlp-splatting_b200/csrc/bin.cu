@@ -126,30 +126,95 @@ __device__ __forceinline__ void for_each_tile(bool has, int x0, int x1, int y0, 
   }
 }
 
-__global__ void k_bin_count(const float4* __restrict__ geom, int n, BinCam cam, uint2* __restrict__ rect,
-                            int32_t* __restrict__ tile_cnt) {
+// Warp-flattened walk over the tiles of 32 rectangles.  Lane l brings rectangle l (none when !has); the
+// rectangles' tiles form one list of `total` items that the lanes share evenly: item i belongs to the
+// rectangle j with pref[j] <= i < pref[j + 1].  Iterations are independent, so the atomics of several
+// of them are in flight at once, whatever the sizes of the individual rectangles.
+struct WarpRects { int pref[33]; int x0[32], y0[32], w[32], p[32]; };
+struct WarpWhiten { PrimWhiten w[8]; };   // whitening maps of a warp's primitives (pre-tested scatter)
+
+template <typename F>
+__device__ __forceinline__ void for_each_tile_flat(bool has, int x0, int x1, int y0, int y1, int ntx, int p,
+                                                   WarpRects& wr, F f) {
+  const int lane = threadIdx.x & 31;
+  const int w = x1 - x0 + 1;
+  const int area = has ? w * (y1 - y0 + 1) : 0;
+  int inc = area;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += v;
+  }
+  const int total = __shfl_sync(0xffffffffu, inc, 31);
+  if (lane == 0) wr.pref[0] = 0;
+  wr.pref[lane + 1] = inc;
+  wr.x0[lane] = x0; wr.y0[lane] = y0; wr.w[lane] = w; wr.p[lane] = p;
+  __syncwarp();
+#pragma unroll 4
+  for (int i = lane; i < total; i += 32) {
+    int j = 0;
+#pragma unroll
+    for (int step = 16; step > 0; step >>= 1)
+      if (wr.pref[j + step] <= i) j += step;
+    const int k = i - wr.pref[j], bw = wr.w[j];
+    const int row = k / bw;
+    f((wr.y0[j] + row) * ntx + wr.x0[j] + (k - row * bw), wr.p[j]);
+  }
+  __syncwarp();
+}
+
+__global__ void __launch_bounds__(256) k_bin_count(const float4* __restrict__ geom, int n, BinCam cam,
+                                                   uint2* __restrict__ rect, int32_t* __restrict__ tile_cnt) {
+  __shared__ WarpRects s_wr[8];
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   int r[4] = {1, 0, 1, 0};
   const bool has = (p < n) && prim_rect(geom, p, cam, r);
   if (p < n) rect[p] = has ? make_uint2((uint32_t)r[0] | ((uint32_t)r[1] << 16), (uint32_t)r[2] | ((uint32_t)r[3] << 16))
                            : make_uint2(1u, 1u);  // x0=1 > x1=0
-  for_each_tile(has, r[0], r[1], r[2], r[3], cam.ntx, p, [&](int t, int) { atomicAdd(tile_cnt + t, 1); });
+  for_each_tile_flat(has, r[0], r[1], r[2], r[3], cam.ntx, p, s_wr[threadIdx.x >> 5],
+                     [&](int t, int) { atomicAdd(tile_cnt + t, 1); });
 }
 
-__global__ void k_bin_scatter(int n, int ntx, const uint2* __restrict__ rect, const int32_t* __restrict__ tile_offsets,
-                              int32_t* __restrict__ tile_fill, int32_t* __restrict__ tile_prims,
-                              const int32_t* __restrict__ status) {
+// PRETEST: a (tile, primitive) pair that no ray of the tile can hit (tile_surely_misses) is not
+// written; tile_fill then ends as the number of candidates kept per tile, packed at the front of the
+// tile's span of tile_prims (the span itself keeps the size the count pass gave it).
+// PPW primitives per warp: the pre-tested variant does a few hundred instructions and three dependent memory
+// round trips per pair, so it spreads the pairs over four times as many warps.
+template <bool PRETEST, int PPW>
+__global__ void __launch_bounds__(256) k_bin_scatter(int n, int ntx, const uint2* __restrict__ rect,
+                                                     const int32_t* __restrict__ tile_offsets,
+                                                     int32_t* __restrict__ tile_fill, int32_t* __restrict__ tile_prims,
+                                                     const float4* __restrict__ geom,
+                                                     const TileFrame* __restrict__ frames, float K0,
+                                                     const int32_t* __restrict__ status) {
+  __shared__ WarpRects s_wr[8];
+  __shared__ WarpWhiten s_ww[PRETEST ? 8 : 1];
+  static_assert(!PRETEST || PPW <= 8, "WarpWhiten holds eight maps per warp");
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gwarp = blockIdx.x * 8 + warp;
+  const int p = gwarp * PPW + lane;
   int x0 = 1, x1 = 0, y0 = 1, y1 = 0;
-  if (p < n) {
+  const bool mine = lane < PPW && p < n;
+  if (mine) {
     const uint2 r = rect[p];
     x0 = r.x & 0xffff; x1 = r.x >> 16; y0 = r.y & 0xffff; y1 = r.y >> 16;
   }
-  const bool has = (p < n) && x0 <= x1 && y0 <= y1;
-  for_each_tile(has, x0, x1, y0, y1, ntx, p, [&](int t, int q) {
+  const bool has = mine && x0 <= x1 && y0 <= y1;
+  if (PRETEST && has) s_ww[warp].w[lane] = make_whiten(load_geom(geom, p));
+  // (for_each_tile_flat synchronises the warp before the first item is read)
+  for_each_tile_flat(has, x0, x1, y0, y1, ntx, PRETEST ? lane : p, s_wr[warp], [&](int t, int q) {
+    int id = q;
+    if (PRETEST) {
+      // q is the lane that brought the primitive: its map sits in shared memory
+      const float4* fp = reinterpret_cast<const float4*>(frames + t);
+      const float4 f0 = __ldg(fp), f1 = __ldg(fp + 1), f2 = __ldg(fp + 2), f3 = __ldg(fp + 3);
+      const TileFrame f = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w, f2.x, f2.y, f2.z, f2.w, f3.x, f3.y, f3.z, f3.w};
+      if (tile_surely_misses(s_ww[warp].w[q], f, K0)) return;
+      id = gwarp * PPW + q;
+    }
     const int slot = atomicAdd(tile_fill + t, 1);
-    tile_prims[tile_offsets[t] + slot] = q;
+    tile_prims[tile_offsets[t] + slot] = id;
   });
 }
 
@@ -277,7 +342,8 @@ int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cu
 
 constexpr int kSortCap = 2048;  // per-tile sort capacity (>= tile capacity 1536)
 
-int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st, bool order_lists) {
+int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st, bool order_lists,
+               bool pretest) {
   const int T = num_tiles(fr->width, fr->height, fr->tile);
   BinCam cam;
   for (int i = 0; i < 16; ++i) { cam.view[i] = fr->view[i]; cam.proj[i] = fr->proj[i]; }
@@ -297,18 +363,29 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
   MLPSP_REQUIRE(cam.ntx < 65536 && cam.nty < 65536, MLPSP_E_LIMIT, "tile grid beyond 65535 per axis");
   MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
                 "tile_capacity must be in [1, %d]", kSortCap);
+  MLPSP_REQUIRE(!(pretest && order_lists), MLPSP_E_ARG, "bin: the tile pre-test leaves the lists in scatter order");
+  MLPSP_REQUIRE(!pretest || (fr->tile == 8 && fr->rays_o && fr->rays_d), MLPSP_E_ARG,
+                "bin: the tile pre-test needs 8x8 tiles and the frame's rays");
+  // with the pre-test the per-tile fill counters are the traversal lengths the wave kernels read
+  int32_t* fill = pretest ? s.tile_len : s.tile_fill;
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_cnt, 0, 4 * (size_t)(T + 1), st));
-  MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_fill, 0, 4 * (size_t)T, st));
+  MLPSP_CUDA_OK(cudaMemsetAsync(fill, 0, 4 * (size_t)T, st));
   const int n = sc->n;
-  LaunchScope scope(kKBin, n > 0 ? (order_lists ? 7 : 6) : 4, st);
+  LaunchScope scope(kKBin, (n > 0 ? (order_lists ? 7 : 6) : 4) + (pretest ? 1 : 0), st);
+  if (pretest) launch_tile_frames(fr, s.tile_frame, st);
   if (n > 0) k_bin_count<<<(n + 255) / 256, 256, 0, st>>>((const float4*)sc->geom, n, cam, s.rect, s.tile_cnt);
   int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
   if (rc) return rc;
   k_bin_finish<<<std::min(64, (T + 255) / 256), 256, 0, st>>>(s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
                                                               fr->max_pairs, fr->status, s.counters);
   if (n > 0) {
-    k_bin_scatter<<<(n + 255) / 256, 256, 0, st>>>(n, cam.ntx, s.rect, fr->tile_offsets, s.tile_fill,
-                                                   fr->tile_prims, fr->status);
+    if (pretest)
+      k_bin_scatter<true, 8><<<(n + 63) / 64, 256, 0, st>>>(n, cam.ntx, s.rect, fr->tile_offsets, fill, fr->tile_prims,
+                                                           (const float4*)sc->geom, s.tile_frame,
+                                                           (float)(-2.0 * log((double)fr->threshold)), fr->status);
+    else
+      k_bin_scatter<false, 32><<<(n + 255) / 256, 256, 0, st>>>(n, cam.ntx, s.rect, fr->tile_offsets, fill, fr->tile_prims,
+                                                            nullptr, nullptr, 0.f, fr->status);
     if (order_lists) k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);
   }
   return cuda_check(cudaGetLastError(), "bin");

@@ -143,7 +143,7 @@ __device__ __forceinline__ bool surely_misses(const Geom& g, V3 o, V3 d, float b
 // and the tile's 64 rays lie inside the rectangle [a0, a1] x [b0, b1] of those coordinates (slightly
 // inflated).  a0 > a1 marks a tile without such a frame (several origins, a ray more than 60 degrees off the
 // mean, non-finite input): no candidate of it is ever rejected.
-struct TileFrame {
+struct __align__(16) TileFrame {
   float ox, oy, oz, a0;
   float ax, ay, az, a1;
   float ux, uy, uz, b0;
@@ -155,10 +155,36 @@ __device__ __forceinline__ float quad_min_1d(float A, float B, float C, float lo
   const float qlo = fmaf(fmaf(A, lo, 2.f * B), lo, C), qhi = fmaf(fmaf(A, hi, 2.f * B), hi, C);
   float m = fminf(qlo, qhi);
   if (A > 0.f) {
-    const float t = fminf(fmaxf(-B / A, lo), hi);
+    const float t = fminf(fmaxf(__fdividef(-B, A), lo), hi);
     m = fminf(m, fmaf(fmaf(A, t, 2.f * B), t, C));
   }
   return m;
+}
+
+// Whitening map of one primitive: x -> diag(1 / exp(ls)) R^T x as a 3x3 matrix (row-major), its centre, the
+// largest inverse scale.  Built once per primitive, used for every tile of its rectangle.
+struct PrimWhiten { float m[9]; float cx, cy, cz, ismax; };
+
+__device__ __forceinline__ PrimWhiten make_whiten(const Geom& g) {
+  PrimWhiten w;
+  const float is[3] = {sqrtf(g.mx), sqrtf(g.my), sqrtf(g.mz)};
+  const V3 c0 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{1.f, 0.f, 0.f});
+  const V3 c1 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{0.f, 1.f, 0.f});
+  const V3 c2 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{0.f, 0.f, 1.f});
+  w.m[0] = c0.x * is[0]; w.m[1] = c1.x * is[0]; w.m[2] = c2.x * is[0];
+  w.m[3] = c0.y * is[1]; w.m[4] = c1.y * is[1]; w.m[5] = c2.y * is[1];
+  w.m[6] = c0.z * is[2]; w.m[7] = c1.z * is[2]; w.m[8] = c2.z * is[2];
+  w.cx = g.cx; w.cy = g.cy; w.cz = g.cz;
+  w.ismax = fmaxf(is[0], fmaxf(is[1], is[2]));
+  return w;
+}
+
+__device__ __forceinline__ V3 whiten(const PrimWhiten& w, float x, float y, float z) {
+  V3 r;
+  r.x = fmaf(w.m[0], x, fmaf(w.m[1], y, w.m[2] * z));
+  r.y = fmaf(w.m[3], x, fmaf(w.m[4], y, w.m[5] * z));
+  r.z = fmaf(w.m[6], x, fmaf(w.m[7], y, w.m[8] * z));
+  return r;
 }
 
 // True only when no ray of the tile's rectangle can reach decay > thr against this primitive, i.e. when
@@ -168,20 +194,16 @@ __device__ __forceinline__ float quad_min_1d(float A, float B, float C, float lo
 // quadratic in (alpha, beta), so q = |x cross e|^2 - K |e|^2 is minimised exactly over the rectangle
 // (stationary point, four edges).  K carries a 0.2 % margin and tol bounds the rounding of this test and of
 // hit_test (which works in world space, where a position error of a few ulps of |c - o| is magnified by the
-// largest inverse scale), so a rejected pair is one hit_test rejects for every pixel of the tile and the
+// largest inverse scale); both are orders of magnitude above the error of the approximate divisions and
+// square roots used here.  So a rejected pair is one hit_test rejects for every pixel of the tile, and the
 // rendered result does not depend on the pre-test.  Any NaN makes the test answer false.
-__device__ __forceinline__ bool tile_surely_misses(const Geom& g, const TileFrame& f, float K0) {
+__device__ __forceinline__ bool tile_surely_misses(const PrimWhiten& pw, const TileFrame& f, float K0) {
   if (!(f.a0 <= f.a1)) return false;
-  const float isx = __fsqrt_rn(g.mx), isy = __fsqrt_rn(g.my), isz = __fsqrt_rn(g.mz);
-  const V3 v = {g.cx - f.ox, g.cy - f.oy, g.cz - f.oz};
-  V3 x = rot_conj(g.qw, g.qx, g.qy, g.qz, v);
-  V3 e0 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{f.ax, f.ay, f.az});
-  V3 e1 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{f.ux, f.uy, f.uz});
-  V3 e2 = rot_conj(g.qw, g.qx, g.qy, g.qz, V3{f.vx, f.vy, f.vz});
-  x.x *= isx; x.y *= isy; x.z *= isz;
-  e0.x *= isx; e0.y *= isy; e0.z *= isz;
-  e1.x *= isx; e1.y *= isy; e1.z *= isz;
-  e2.x *= isx; e2.y *= isy; e2.z *= isz;
+  const float vx = pw.cx - f.ox, vy = pw.cy - f.oy, vz = pw.cz - f.oz;
+  const V3 x = whiten(pw, vx, vy, vz);
+  const V3 e0 = whiten(pw, f.ax, f.ay, f.az);
+  const V3 e1 = whiten(pw, f.ux, f.uy, f.uz);
+  const V3 e2 = whiten(pw, f.vx, f.vy, f.vz);
   const V3 w0 = {x.y * e0.z - x.z * e0.y, x.z * e0.x - x.x * e0.z, x.x * e0.y - x.y * e0.x};
   const V3 w1 = {x.y * e1.z - x.z * e1.y, x.z * e1.x - x.x * e1.z, x.x * e1.y - x.y * e1.x};
   const V3 w2 = {x.y * e2.z - x.z * e2.y, x.z * e2.x - x.x * e2.z, x.x * e2.y - x.y * e2.x};
@@ -196,6 +218,7 @@ __device__ __forceinline__ bool tile_surely_misses(const Geom& g, const TileFram
   const float b2 = (w0.x * w2.x + w0.y * w2.y + w0.z * w2.z) - K * (e0.x * e2.x + e0.y * e2.y + e0.z * e2.z);
   const float c0 = (w0.x * w0.x + w0.y * w0.y + w0.z * w0.z) - K * e00;
   if (!(fabsf(a11) + fabsf(a22) + fabsf(a12) + fabsf(b1) + fabsf(b2) + fabsf(c0) < 3.0e38f)) return false;
+  if (c0 <= 0.f) return false;   // the tile's central direction already reaches the ellipsoid
   // edges alpha = a0 / a1 (quadratics in beta) and beta = b0 / b1 (quadratics in alpha)
   float m = quad_min_1d(a22, fmaf(a12, f.a0, b2), fmaf(fmaf(a11, f.a0, 2.f * b1), f.a0, c0), f.b0, f.b1);
   m = fminf(m, quad_min_1d(a22, fmaf(a12, f.a1, b2), fmaf(fmaf(a11, f.a1, 2.f * b1), f.a1, c0), f.b0, f.b1));
@@ -203,15 +226,15 @@ __device__ __forceinline__ bool tile_surely_misses(const Geom& g, const TileFram
   m = fminf(m, quad_min_1d(a11, fmaf(a12, f.b1, b1), fmaf(fmaf(a22, f.b1, 2.f * b2), f.b1, c0), f.a0, f.a1));
   const float det = a11 * a22 - a12 * a12;
   if (a11 > 0.f && det > 0.f) {
-    const float al = (a12 * b2 - a22 * b1) / det, be = (a12 * b1 - a11 * b2) / det;
+    const float rdet = __fdividef(1.f, det);
+    const float al = (a12 * b2 - a22 * b1) * rdet, be = (a12 * b1 - a11 * b2) * rdet;
     if (al >= f.a0 && al <= f.a1 && be >= f.b0 && be <= f.b1) m = fminf(m, fmaf(b1, al, fmaf(b2, be, c0)));
   }
-  const float ismax = fmaxf(isx, fmaxf(isy, isz));
-  const float dist = __fsqrt_rn(v.x * v.x + v.y * v.y + v.z * v.z);
+  const float dist = sqrtf(vx * vx + vy * vy + vz * vz);
   // largest |e| over the rectangle
-  const float emax = __fsqrt_rn(e00) + fmaxf(fabsf(f.a0), fabsf(f.a1)) * __fsqrt_rn(e11) +
-                     fmaxf(fabsf(f.b0), fabsf(f.b1)) * __fsqrt_rn(e22);
-  const float tol = (2e-5f * __fsqrt_rn(K0) * dist * ismax + 1e-4f * K0) * emax * emax;
+  const float emax = sqrtf(e00) + fmaxf(fabsf(f.a0), fabsf(f.a1)) * sqrtf(e11) +
+                     fmaxf(fabsf(f.b0), fabsf(f.b1)) * sqrtf(e22);
+  const float tol = (2e-5f * sqrtf(K0) * dist * pw.ismax + 1e-4f * K0) * emax * emax;
   return m > tol;
 }
 

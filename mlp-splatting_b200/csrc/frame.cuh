@@ -134,16 +134,21 @@ int cuda_check(cudaError_t e, const char* what);
   } while (0)
 
 // stage launchers (defined in the .cu files)
-// order_lists = false leaves every tile list in scatter order for a following launch_sort(unordered_input = true)
-int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st, bool order_lists = true);
+// order_lists = false leaves every tile list in scatter order for a following launch_sort(unordered_input = true).
+// pretest: write only the (tile, primitive) pairs that some ray of the tile can hit; s.tile_len receives the
+// number kept per tile (they sit at the front of the tile's span), tile_offsets stay those of the full lists.
+int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st, bool order_lists = true,
+               bool pretest = false);
+// ray frame of every 8x8 tile (TileFrame), from the frame's rays
+void launch_tile_frames(const mlpsp_frame* fr, TileFrame* frames, cudaStream_t st);
 int launch_bin_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, const int32_t* tile_view,
                       const float* views_host, int num_views, cudaStream_t st);
 int launch_bin_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
 // long_list [T] / long_count [1]: device scratch for the tiles that take the block-wide sort
-// frames / tile_len (both or neither): drop the candidates no ray of the tile can hit before sorting; the
-// dropped tail of every list is filled with -1 and tile_len receives the number of candidates kept
+// list_len (optional): candidates actually present at the front of every tile's span (pre-tested binning);
+// the rest of the span is filled with -1 in sorted_prims
 int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st, bool unordered_input,
-                int32_t* long_list, int32_t* long_count, TileFrame* frames = nullptr, int32_t* tile_len = nullptr);
+                int32_t* long_list, int32_t* long_count, const int32_t* list_len = nullptr);
 int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mask_geo, cudaStream_t st);
 // lists_refined: s.tile_len already holds the traversal length of every tile (written by launch_sort)
 int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st,

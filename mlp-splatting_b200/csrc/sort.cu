@@ -3,8 +3,7 @@
 // Keys are positive floats (or the 1e30 sentinel), so their bit patterns order like the values and the
 // sort runs on the raw bits: a bitonic network in shared memory over the 64-bit composite (key bits,
 // tie-break); lists of up to 512 candidates are sorted by one warp (eight tiles per CTA), longer
-// lists by a whole CTA.  In the fused frame path the sort also drops the candidates that no ray of the tile
-// can hit (tile_surely_misses) before they are sorted.
+// lists by a whole CTA.
 #include "frame.cuh"
 
 namespace mlpsp {
@@ -49,33 +48,30 @@ __device__ __forceinline__ void warp_bitonic(T* buf) {
 // from the binning scatter in arbitrary order and holds distinct ids, so the id itself is the tie-break
 // (the result is the stable sort of the ascending-id list) and the id is read back from the sorted
 // composite.  Otherwise the tie-break is the position in the caller's list (stable sort of that list).
-// With a tile frame, a candidate that no ray of the tile can hit (tile_surely_misses) is dropped: keep
-// comes back false.
 template <bool FROM_SCATTER>
 __device__ __forceinline__ unsigned long long make_composite(const float4* __restrict__ geom, int n, int p, int i, V3 o,
-                                                             V3 d, int key_mode, const TileFrame* tf, float K0,
-                                                             bool& keep) {
+                                                             V3 d, int key_mode) {
   float key = MLPSP_SENTINEL_KEY;
-  keep = true;
   if (p >= 0 && p < n) {
     const Geom g = load_geom(geom, p);
-    if (tf && tile_surely_misses(g, *tf, K0)) keep = false;
     key = key_mode ? tile_key_euclid(g, o, d) : tile_key(g, o, d);
   }
   return ((unsigned long long)__float_as_uint(key) << 32) | (unsigned long long)(uint32_t)(FROM_SCATTER ? p : i);
 }
 
+// sorted_prims[s .. s + len) = the sorted list; [s + len, s + span) = -1 (span > len only after a
+// pre-tested binning, whose dropped pairs leave the end of the tile's span unused)
 template <bool FROM_SCATTER>
 __device__ __forceinline__ void write_sorted(const unsigned long long* buf, const int32_t* tile_prims,
                                              int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int s,
-                                             int kept, int len, int first, int step) {
-  for (int i = first; i < len; i += step) {
-    if (i < kept) {
+                                             int len, int span, int first, int step) {
+  for (int i = first; i < span; i += step) {
+    if (i < len) {
       const unsigned long long kv = buf[i];
       sorted_prims[s + i] = FROM_SCATTER ? (int32_t)(uint32_t)kv : tile_prims[s + (int)(uint32_t)kv];
       if (keys_out) keys_out[s + i] = __uint_as_float((uint32_t)(kv >> 32));
     } else {
-      sorted_prims[s + i] = -1;   // dropped by the tile pre-test: never traversed (the tile's length is kept)
+      sorted_prims[s + i] = -1;
     }
   }
 }
@@ -84,25 +80,28 @@ constexpr int kTilesPerCta = 8;
 constexpr int kWarpSortMax = 512;
 
 // Short lists: one warp per tile, eight tiles per CTA.  Tiles with more than kWarpSortMax candidates
-// are appended to long_list for k_sort_long, so that each of them gets a CTA of its own (they hold
-// most of the candidates and sit next to each other in the image).
+// are appended to long_list for k_sort_long, so that each of them gets a CTA of its own.
 template <bool IDSORT>
 __global__ void __launch_bounds__(256) k_sort_tiles(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* tile_prims, int W, int H, int ts, int ntx, int T, int cap,
     int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode, int32_t* __restrict__ long_list,
-    int32_t* __restrict__ long_count, const TileFrame* __restrict__ frames, float K0, int32_t* __restrict__ tile_len,
-    int32_t* __restrict__ status) {
+    int32_t* __restrict__ long_count, const int32_t* __restrict__ list_len, int32_t* __restrict__ status) {
   __shared__ __align__(16) unsigned long long s_buf[kTilesPerCta * kWarpSortMax];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x * kTilesPerCta + warp;
   if (tile >= T) return;
   const int s = tile_offsets[tile];
-  const int len = min(tile_offsets[tile + 1] - s, cap);
-  if (len <= 0) { if (tile_len && lane == 0) tile_len[tile] = 0; return; }
+  const int span = min(tile_offsets[tile + 1] - s, cap);
+  const int len = list_len ? min(list_len[tile], span) : span;
+  if (list_len && lane == 0 && len > 0) atomicAdd(status + MLPSP_ST_PAIRS_KEPT, len);
   if (len > kWarpSortMax) {
     if (lane == 0) long_list[atomicAdd(long_count, 1)] = tile;
+    return;
+  }
+  if (len <= 0) {
+    for (int i = lane; i < span; i += 32) sorted_prims[s + i] = -1;
     return;
   }
   const int tx = tile % ntx, ty = tile / ntx;
@@ -110,85 +109,45 @@ __global__ void __launch_bounds__(256) k_sort_tiles(
   const int64_t pc = (int64_t)cy * W + cx;
   const V3 o = load3(rays_o, pc), d = load3(rays_d, pc);
   unsigned long long* buf = s_buf + warp * kWarpSortMax;
-  TileFrame tf;
-  if (frames) tf = frames[tile];
-  int kept = 0;
-  for (int i0 = 0; i0 < len; i0 += 32) {
-    const int i = i0 + lane;
-    bool keep = false;
-    unsigned long long kv = ~0ull;
-    if (i < len) kv = make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode, frames ? &tf : nullptr, K0, keep);
-    const uint32_t m = __ballot_sync(0xffffffffu, keep);
-    if (keep) buf[kept + __popc(m & ((1u << lane) - 1u))] = kv;
-    kept += __popc(m);
-  }
-  const int N = kept <= 32 ? 32 : (kept <= 64 ? 64 : (kept <= 128 ? 128 : (kept <= 256 ? 256 : 512)));
-  for (int i = kept + lane; i < N; i += 32) buf[i] = ~0ull;
+  const int N = len <= 32 ? 32 : (len <= 64 ? 64 : (len <= 128 ? 128 : (len <= 256 ? 256 : 512)));
+  for (int i = lane; i < N; i += 32)
+    buf[i] = (i < len) ? make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode) : ~0ull;
   __syncwarp();
   if (N == 32) warp_bitonic<unsigned long long, 32>(buf);
   else if (N == 64) warp_bitonic<unsigned long long, 64>(buf);
   else if (N == 128) warp_bitonic<unsigned long long, 128>(buf);
   else if (N == 256) warp_bitonic<unsigned long long, 256>(buf);
   else warp_bitonic<unsigned long long, 512>(buf);
-  write_sorted<IDSORT>(buf, tile_prims, sorted_prims, keys_out, s, kept, len, lane, 32);
-  if (tile_len && lane == 0) {
-    tile_len[tile] = kept;
-    if (kept) atomicAdd(status + MLPSP_ST_PAIRS_KEPT, kept);
-  }
+  write_sorted<IDSORT>(buf, tile_prims, sorted_prims, keys_out, s, len, span, lane, 32);
 }
 
-// Long lists: one CTA per tile of long_list (grid-stride), the same bitonic network run by the whole CTA
-// on the candidates that survive the tile pre-test.
+// Long lists: one CTA per tile of long_list (grid-stride), the same bitonic network run by the whole CTA.
 template <int THREADS, int CAP, bool IDSORT>
 __global__ void __launch_bounds__(THREADS) k_sort_long(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* tile_prims, int W, int H, int ts, int ntx,
     int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode,
     const int32_t* __restrict__ long_list, const int32_t* __restrict__ long_count,
-    const TileFrame* __restrict__ frames, float K0, int32_t* __restrict__ tile_len, int32_t* __restrict__ status) {
+    const int32_t* __restrict__ list_len, const int32_t* __restrict__ status) {
   __shared__ __align__(16) unsigned long long s_buf[CAP];
-  __shared__ int s_kept;
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int count = *long_count;
-  const int lane = threadIdx.x & 31;
   for (int q = blockIdx.x; q < count; q += gridDim.x) {
     const int tile = long_list[q];
     const int s = tile_offsets[tile];
-    const int len = min(tile_offsets[tile + 1] - s, CAP);
+    const int span = min(tile_offsets[tile + 1] - s, CAP);
+    const int len = list_len ? min(list_len[tile], span) : span;
     const int tx = tile % ntx, ty = tile / ntx;
     const int cx = min(tx * ts + (ts >> 1), W - 1), cy = min(ty * ts + (ts >> 1), H - 1);
     const int64_t pc = (int64_t)cy * W + cx;
     const V3 o = load3(rays_o, pc), d = load3(rays_d, pc);
-    TileFrame tf;
-    if (frames) tf = frames[tile];
-    if (threadIdx.x == 0) s_kept = 0;
+    const int N = len <= CAP / 2 ? CAP / 2 : CAP;
+    for (int i = threadIdx.x; i < N; i += THREADS)
+      s_buf[i] = (i < len) ? make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode) : ~0ull;
     __syncthreads();
-    for (int i0 = 0; i0 < len; i0 += THREADS) {
-      const int i = i0 + threadIdx.x;
-      bool keep = false;
-      unsigned long long kv = ~0ull;
-      if (i < len) kv = make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode, frames ? &tf : nullptr, K0, keep);
-      // one shared-memory atomic per warp; the order inside the buffer is irrelevant before the sort
-      const uint32_t m = __ballot_sync(0xffffffffu, keep);
-      int base = 0;
-      if (lane == 0 && m) base = atomicAdd(&s_kept, __popc(m));
-      base = __shfl_sync(0xffffffffu, base, 0);
-      if (keep) s_buf[base + __popc(m & ((1u << lane) - 1u))] = kv;
-    }
-    __syncthreads();
-    const int kept = s_kept;
-    const int N = kept <= CAP / 8 ? CAP / 8 : (kept <= CAP / 4 ? CAP / 4 : (kept <= CAP / 2 ? CAP / 2 : CAP));
-    for (int i = kept + threadIdx.x; i < N; i += THREADS) s_buf[i] = ~0ull;
-    __syncthreads();
-    if (N == CAP / 8) warp_bitonic<unsigned long long, CAP / 8, THREADS>(s_buf);
-    else if (N == CAP / 4) warp_bitonic<unsigned long long, CAP / 4, THREADS>(s_buf);
-    else if (N == CAP / 2) warp_bitonic<unsigned long long, CAP / 2, THREADS>(s_buf);
+    if (N == CAP / 2) warp_bitonic<unsigned long long, CAP / 2, THREADS>(s_buf);
     else warp_bitonic<unsigned long long, CAP, THREADS>(s_buf);
-    write_sorted<IDSORT>(s_buf, tile_prims, sorted_prims, keys_out, s, kept, len, threadIdx.x, THREADS);
-    if (tile_len && threadIdx.x == 0) {
-      tile_len[tile] = kept;
-      if (kept) atomicAdd(status + MLPSP_ST_PAIRS_KEPT, kept);
-    }
+    write_sorted<IDSORT>(s_buf, tile_prims, sorted_prims, keys_out, s, len, span, threadIdx.x, THREADS);
     __syncthreads();
   }
 }
@@ -268,40 +227,43 @@ __global__ void __launch_bounds__(256) k_tile_frames(const float* __restrict__ r
   }
 }
 
+void launch_tile_frames(const mlpsp_frame* fr, TileFrame* frames, cudaStream_t st) {
+  const int T = num_tiles(fr->width, fr->height, 8);
+  const int ntx = (fr->width + 7) / 8;
+  k_tile_frames<<<(T + 7) / 8, 256, 0, st>>>(fr->rays_o, fr->rays_d, fr->width, fr->height, ntx, T, frames);
+}
+
 int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st, bool unordered_input,
-                int32_t* long_list, int32_t* long_count, TileFrame* frames, int32_t* tile_len) {
+                int32_t* long_list, int32_t* long_count, const int32_t* list_len) {
   const int T = num_tiles(fr->width, fr->height, fr->tile);
   const int ntx = (fr->width + fr->tile - 1) / fr->tile;
   MLPSP_REQUIRE(fr->tile_capacity > 0 && fr->tile_capacity <= kSortCap, MLPSP_E_LIMIT,
                 "tile_capacity must be in [1, %d]", kSortCap);
   MLPSP_REQUIRE(long_list && long_count, MLPSP_E_ARG, "sort: scratch for the long-tile list missing");
-  MLPSP_REQUIRE(!frames || (tile_len && fr->tile == 8), MLPSP_E_ARG, "sort: the tile pre-test needs 8x8 tiles and a length array");
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   MLPSP_CUDA_OK(cudaMemsetAsync(long_count, 0, 4, st));
-  LaunchScope scope(kKSort, frames ? 3 : 2, st);
-  const float K0 = (float)(-2.0 * log((double)fr->threshold));
-  if (frames) k_tile_frames<<<(T + 7) / 8, 256, 0, st>>>(fr->rays_o, fr->rays_d, fr->width, fr->height, ntx, T, frames);
+  LaunchScope scope(kKSort, 2, st);
   const int grid = (T + kTilesPerCta - 1) / kTilesPerCta;
   const int grid_long = std::min(T, sms * 6);
   const float4* geom = (const float4*)sc->geom;
   if (unordered_input) {
     k_sort_tiles<true><<<grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
                                              fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out,
-                                             fr->sort_key, long_list, long_count, frames, K0, tile_len, fr->status);
+                                             fr->sort_key, long_list, long_count, list_len, fr->status);
     k_sort_long<256, kSortCap, true><<<grid_long, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
                                                                fr->tile_prims, fr->width, fr->height, fr->tile, ntx,
                                                                fr->sorted_prims, keys_out, fr->sort_key, long_list,
-                                                               long_count, frames, K0, tile_len, fr->status);
+                                                               long_count, list_len, fr->status);
   } else {
     k_sort_tiles<false><<<grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
                                               fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out,
-                                              fr->sort_key, long_list, long_count, frames, K0, tile_len, fr->status);
+                                              fr->sort_key, long_list, long_count, list_len, fr->status);
     k_sort_long<256, kSortCap, false><<<grid_long, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
                                                                 fr->tile_prims, fr->width, fr->height, fr->tile, ntx,
                                                                 fr->sorted_prims, keys_out, fr->sort_key, long_list,
-                                                                long_count, frames, K0, tile_len, fr->status);
+                                                                long_count, list_len, fr->status);
   }
   return cuda_check(cudaGetLastError(), "sort_tiles");
 }
