@@ -119,6 +119,48 @@ def cpu_baseline(scene, cam, budget_s, steps=1, warmup=0):
                 evals_per_s=evals / sum(times), ms_per_step=mean * 1e3)
 
 
+def reference_cuda_kernels(scene, cam, steps):
+    """Device time of the reference's own CUDA kernels (compiled unmodified for sm_100a by oracle/build_ref.py)
+    on this workload, given tile lists from the oracle's binning.  Extra evidence only: the reference arm's
+    value stays the CPU number.  Returns None when the module or a GPU is missing."""
+    try:
+        import torch
+        from oracle import build_ref
+        from oracle import oracle as orc
+        if not torch.cuda.is_available():
+            return None
+        mod = build_ref.load_module()
+        if mod is None:
+            return None
+        dev = torch.device("cuda", 0)
+        W, H = cam["W"], cam["H"]
+        q = orc.normalize_rows(scene["quats"])
+        rd = orc.normalize_rows(cam["rays_d"])
+        geom = orc.pack_geometry(scene["positions"], scene["log_scales"], q)
+        prims, off = orc.bin_tiles(geom, cam["view"], cam["proj"], W, H, 8, THRESHOLD)
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+        x = [t(cam["rays_o"]), t(rd), t(scene["positions"]), t(scene["log_scales"]), t(q), t(prims), t(off),
+             t(scene["freq"]), t(scene["att"])] + [t(scene[k]) for k in WK]
+        out = {"note": "reference kernels, unmodified, sm_100a build; culling (dense PyTorch in the reference) not "
+                       "included; CUDA events, L2 not flushed"}
+        for name, call in (("render_tiles_forward_tilecenter", lambda: mod.render_tiles_forward_tilecenter(*x, W, H, 8, 8, THRESHOLD)),
+                           ("render_tiles_rgb_wmma_f16", lambda: mod.render_tiles_rgb_wmma(x, W, H, THRESHOLD, False))):
+            for _ in range(2):
+                call()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(max(1, steps)):
+                call()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / max(1, steps)
+            out[name] = {"ms_per_frame": ms, "frames_per_s": 1e3 / ms}
+        return out
+    except Exception as exc:   # evidence only: never fail the arm over it
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -127,6 +169,7 @@ def run_reference(args):
     scene, cams, cfg = syn.make_workload(args.workload)
     per_step = max(2.0, 150.0 / (args.steps + args.warmup + 1))
     cb = cpu_baseline(scene, cams[0], per_step, steps=args.steps, warmup=args.warmup)
+    ref_gpu = reference_cuda_kernels(scene, cams[0], min(args.steps, 5))
     line = {
         "impl": "reference", "metric": "frames_per_sec", "value": cb["value"], "unit": "frames/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
@@ -136,6 +179,8 @@ def run_reference(args):
         "e2e": {"value": cb["value"], "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "record_mlp_evals_per_sec": cb["evals_per_s"],
     }
+    if ref_gpu is not None:
+        line["reference_cuda_kernels"] = ref_gpu
     print(json.dumps(line), flush=True)
 
 
