@@ -119,7 +119,7 @@ typedef struct mlpsp_frame {
   int32_t tile_row_begin; /* binning keeps only tile rows [tile_row_begin, tile_row_end); both 0 = the whole image. */
   int32_t tile_row_end;   /* Used to share one view between GPUs by bands of tile rows: tiles outside the band get
                              empty lists and their pixels the background. */
-  int32_t tile_pretest;   /* mlpsp_render_frame only.  0 = before sorting, drop every candidate that no ray of its
+  int32_t tile_pretest;   /* mlpsp_render_frame only.  0 = while binning, drop every candidate that no ray of its
                              tile can hit (a conservative ellipsoid-against-tile test with no reference
                              counterpart; the image is the same, the lists the wave kernels walk are shorter);
                              it is skipped when mask_used is requested, so that those masks stay aligned with the
