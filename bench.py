@@ -350,6 +350,20 @@ def main():
                 "peak_source": pk["source"] + " burst", "traffic": None,
                 "flop_per_launch": flops_step / max(classes["mlp"]["launches_per_step"], 1),
                 "avg_launch_ms": mlp_launch_ms, "share_of_step": mlp_ms / max(sum(c["ms_per_step"] for c in classes.values()), 1e-9)}
+    # Algorithmic bytes of the evaluator: 32 B in + 16 B out per record, one 8,464-byte weight image per work item.
+    n_launch = max(classes["mlp"]["launches_per_step"], 1)
+    alg_bytes = stats.records * 48 + stats.work_total * 8464
+    roofline["hbm_view"] = {"algorithmic_bytes_per_launch": alg_bytes / n_launch,
+                            "achieved_gbs": alg_bytes / (mlp_ms / 1e3) / 1e9 if mlp_ms > 0 else 0.0,
+                            "peak_gbs": pk["hbm_gbs"],
+                            "frac": (alg_bytes / (mlp_ms / 1e3) / 1e9 / pk["hbm_gbs"]) if mlp_ms > 0 else 0.0}
+    if args.workload == "single_100k_1200x680" and prec == L.PRECISION_F16 and args.encoder == "integrated" and nviews == 1:
+        # one ncu capture of the three busy evaluator launches of a frame of this workload: DRAM read + write bytes
+        # 386.7 + 272.7 + 86.5 MB; the other launches of the six-wave schedule move nothing
+        roofline["traffic"] = (386.7e6 + 272.7e6 + 86.5e6) / n_launch
+        roofline["traffic_unit"] = "bytes per launch: ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over a frame's evaluator launches"
+        roofline["ncu_pipes_pct"] = {"tensor": 10.2, "special_function": 48.0, "issue": 57.0, "dram": 16.6,
+                                     "source": "profiles/k_mlp_tc_single_100k_1200x680.md (largest wave)"}
 
     # ---- end to end: pinned host rays in, image out, status checked, through the public host API.
     # Three frames are kept in flight (FramePipeline): every step still copies its own rays to the device

@@ -125,6 +125,32 @@ __device__ __forceinline__ bool hit_test(const Geom& g, V3 o, V3 d, float thr, H
   return decay > thr;
 }
 
+// The same geometry for a pair that is already known to hit: t, the offset c - p, its local-frame image
+// and decay as plain float values for the evaluator and the compositor.  No decision hangs on them, so
+// the compiler may fuse and the hardware reciprocal / exponential are used.
+__device__ __forceinline__ V3 rot_conj_fast(float qw, float qx, float qy, float qz, V3 v) {
+  const float tx = 2.f * (qz * v.y - qy * v.z), ty = 2.f * (qx * v.z - qz * v.x), tz = 2.f * (qy * v.x - qx * v.y);
+  V3 r;
+  r.x = v.x + qw * tx + (qz * ty - qy * tz);
+  r.y = v.y + qw * ty + (qx * tz - qz * tx);
+  r.z = v.z + qw * tz + (qy * tx - qx * ty);
+  return r;
+}
+
+__device__ __forceinline__ void hit_values_fast(const Geom& g, V3 o, V3 d, Hit& h) {
+  const V3 v = {g.cx - o.x, g.cy - o.y, g.cz - o.z};
+  const V3 vl = rot_conj_fast(g.qw, g.qx, g.qy, g.qz, v);
+  const V3 dl = rot_conj_fast(g.qw, g.qx, g.qy, g.qz, d);
+  const float denom = dl.x * dl.x * g.mx + dl.y * dl.y * g.my + dl.z * dl.z * g.mz;
+  const float numer = dl.x * vl.x * g.mx + dl.y * vl.y * g.my + dl.z * vl.z * g.mz;
+  const float t = __fdividef(numer, denom);
+  const V3 dd = {g.cx - (o.x + t * d.x), g.cy - (o.y + t * d.y), g.cz - (o.z + t * d.z)};
+  const V3 q = rot_conj_fast(g.qw, g.qx, g.qy, g.qz, dd);
+  const float r2 = fmaxf(q.x * q.x * g.mx + q.y * q.y * g.my + q.z * q.z * g.mz, 0.f);
+  h.t = t; h.dx = dd.x; h.dy = dd.y; h.dz = dd.z; h.qx = q.x; h.qy = q.y; h.qz = q.z;
+  h.decay = __expf(-0.5f * r2);
+}
+
 // Cheap necessary condition for a hit: the centre's distance to the ray's line must be below the
 // bounding radius.  With r^2 = sum q_k^2 m_k >= |c - p|^2 / smax^2 >= perp^2 / smax^2 for every point p
 // of the line, decay > thr needs perp^2 < smax^2 * (-2 ln thr).  bound2 carries a 2 % margin, far

@@ -332,7 +332,10 @@ __global__ void __launch_bounds__(256) k_fill(
     const int p = sorted_prims[s + wlo + j];
     const V3 o = {s_ray[px][0], s_ray[px][1], s_ray[px][2]}, d = {s_ray[px][3], s_ray[px][4], s_ray[px][5]};
     Hit ht;
-    hit_test(load_geom(geom, p), o, d, thr, ht);
+    // the pair is known to hit: values only.  The feature gates divide the local offset by the scales, which
+    // magnifies its rounding, so frames with features keep the decision-grade arithmetic.
+    if (rec_gate) hit_test(load_geom(geom, p), o, d, thr, ht);
+    else hit_values_fast(load_geom(geom, p), o, d, ht);
     const uint32_t slot = slot_base + (uint32_t)r;
     RecIn rec;
     rec.rdx = d.x; rec.rdy = d.y; rec.rdz = d.z; rec.dx = ht.dx; rec.dy = ht.dy; rec.dz = ht.dz;
