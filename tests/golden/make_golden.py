@@ -12,6 +12,9 @@ Only device-agnostic reference functions are called, on CPU:
   the same method with four views and a random tile->view map                 -> mosaic.npz
   scannet.camera.ray_cone_candidates                                           -> raycone.npz
   scannet.primitive_csr.group_records, scannet.primitive_gemm.prepare_groups -> grouping.npz
+  scannet.checkpoints.make_inference_checkpoint, restore_scene_state_dict,
+  infer_scene_spec on a wrapped training state with prefixes, old MLP names and five feature slots
+                                                                              -> checkpoint.pt
 The scene inputs come from this repository's seeded generator, so tests can rebuild them.
 """
 import os
@@ -130,5 +133,31 @@ def main(ref_root):
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 
+def checkpoint_fixture(ref_root):
+    """A small training-state checkpoint in the reference's messiest accepted form, and what the reference's
+    own export / restore functions make of it."""
+    sys.path.insert(0, ref_root)
+    from scannet import checkpoints as ck
+    from mlp_splatting_b200 import synthetic as syn
+    sc = syn.make_scene(8, seed=77, hidden=32, num_freq=6, feat_dim=8, feat_slots=5)
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in sc.items()}
+    raw = {"module.positions": t["positions"], "module.log_scales": t["log_scales"], "module._orig_mod.quats": t["quats"],
+           "module.mlps.lin1.weight": t["W1"], "module.mlps.lin1.bias": t["b1"], "module.mlps.lin2.weight": t["W2"],
+           "module.mlps.lin2.bias": t["b2"], "module.mlps.lin3.weight": t["W3"], "module.mlps.lin3.bias": t["b3"],
+           "module.feat_attr": t["feat_attr"], "module.encoder.freq_bands": t["freq"]}
+    training = {"scene_state_dict": raw, "optimizer_state_dict": {"state": {}}, "metadata": {"iteration": 123},
+                "feature_slots": 5}
+    exported = ck.make_inference_checkpoint(training, storage_precision="mixed", target_feature_slots=4)
+    restored = ck.restore_scene_state_dict(exported["scene_state_dict"])
+    spec = ck.infer_scene_spec(exported["scene_state_dict"])
+    torch.save({"training": training, "exported": exported, "restored": restored,
+                "spec": {k: int(getattr(spec, k)) for k in ("num_primitives", "hidden_dim", "encoded_dim", "pe_frequencies",
+                                                              "feature_dim", "feature_slots")}},
+               os.path.join(HERE, "checkpoint.pt"))
+
+
 if __name__ == "__main__":
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    main(root)
+    checkpoint_fixture(root)
     main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -570,3 +570,26 @@ def test_tile_pretest_drops_only_pairs_without_hits(dev, name):
     assert n_kept == kept_total
     if name != "one_tile":
         assert kept_total < M    # the test is not vacuous on these scenes
+
+
+def test_checkpoint_loads_into_the_renderer(dev):
+    """An inference export (FP16 MLP storage, FP32 geometry; scannet/checkpoints.py:320-382) loaded through
+    checkpoints.load_packed_scene / scene_module_from_checkpoint renders what the same tensors render directly."""
+    import os
+    from mlp_splatting_b200 import checkpoints as ck
+    scene, cam = small_case(**CASES["tiny"])
+    state = {k: torch.from_numpy(np.ascontiguousarray(scene[k])) for k in ("positions", "log_scales", "quats") + tuple(WKEYS)}
+    exported = ck.export_inference_state({"scene_state_dict": {"module." + k: v for k, v in state.items()}})
+    assert exported["scene_state_dict"]["W1"].dtype == torch.float16
+    ps_a = ck.load_packed_scene(exported, dev)
+    ps_b = _packed(scene, dev, pack_f16=True)
+    r = _renderer(cam, dev)
+    ro, rd = _t(cam["rays_o"], dev), _t(cam["rays_d"], dev)
+    rgb_a, al_a = [t.clone() for t in r.render(ps_a, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"])]
+    rgb_b, al_b = r.render(ps_b, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"])
+    # FP16 storage rounds the biases (the synthetic weights themselves are fp16-representable)
+    assert (rgb_a - rgb_b).abs().max().item() <= 2e-3 and (al_a - al_b).abs().max().item() <= 2e-3
+    module = ck.scene_module_from_checkpoint(exported, device=dev)
+    module.set_image_size(cam["W"], cam["H"])
+    rgb_m = module(ro, rd, score_threshold=5e-3, view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
+    assert (rgb_m.reshape(-1, 3) - rgb_a).abs().max().item() <= 2e-3   # its encoder rebuilds the bands on its own
