@@ -126,6 +126,16 @@ typedef struct mlpsp_frame {
                              full sorted lists.  1 = never drop.  With the test on, sorted_prims holds the kept
                              candidates of every tile in depth order followed by -1 entries. */
   int32_t reserved1;
+  /* Per-primitive contribution statistics of render_tiles_kernel_tilecenter_stats (np_tile_kernels.cu:2143-2500),
+   * all NULL or all set; the five [n] arrays are accumulated into, never reset.  With w = trans * alpha of a
+   * composited record: sum_w += w; max_w = max(max_w, w); hits += (w > 1e-8); for w > 0.1: contrib += 1 and
+   * sum_werr += w * L1(colour after this record - gt_rgb). */
+  const float* gt_rgb;    /* [width*height, 3] */
+  float* stat_sum_w;
+  float* stat_max_w;
+  int32_t* stat_hits;
+  float* stat_sum_werr;
+  int32_t* stat_contrib;
 } mlpsp_frame;
 
 const char* mlpsp_last_error(void);

@@ -261,7 +261,7 @@ def scene_module_from_checkpoint(path_or_checkpoint, device=None, **module_kwarg
     kw.update(module_kwargs)
     scene = NeuralPrimitiveSceneTileCUDA(**kw)
     own = scene.state_dict()
-    missing = [k for k in own if k not in state and not k.startswith("encoder.")]
+    missing = [k for k, _ in scene.named_parameters() if k not in state]
     if missing:
         raise KeyError(f"checkpoint lacks {missing}")
     scene.load_state_dict({k: v for k, v in state.items() if k in own}, strict=False)

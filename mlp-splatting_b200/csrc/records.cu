@@ -353,7 +353,14 @@ __global__ void __launch_bounds__(256) k_fill(
 
 // --------------------------------------------------------------------------- composite ----
 // 64 threads per tile; each warp owns 32 pixels and stops as soon as none of them is live.
+struct PrimStats {
+  const float* gt_rgb; const int32_t* sorted_prims;
+  float* sum_w; float* max_w; int32_t* hits; float* sum_werr; int32_t* contrib;
+};
+
+template <bool STATS>
 __global__ void __launch_bounds__(64) k_composite(
+    PrimStats ps,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, int W, int H, int ntx, const int32_t* __restrict__ active,
     const int32_t* __restrict__ active_count, int lo, int hi, const uint32_t* __restrict__ masks32,
     const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out, const float* __restrict__ rec_t,
@@ -378,6 +385,8 @@ __global__ void __launch_bounds__(64) k_composite(
   bool act = tp.valid && st.w >= MLPSP_TERM;
   const uint32_t lt = (1u << lane) - 1u;
   int used = 0;
+  float gtr = 0.f, gtg = 0.f, gtb = 0.f;
+  if (STATS && tp.valid) { gtr = ps.gt_rgb[(size_t)tp.pix * 3]; gtg = ps.gt_rgb[(size_t)tp.pix * 3 + 1]; gtb = ps.gt_rgb[(size_t)tp.pix * 3 + 2]; }
   for (int i0 = wlo; i0 < whi && __any_sync(0xffffffffu, act); i0 += 32) {
     const int idx = i0 + lane;
     uint2 mm = make_uint2(0u, 0u);
@@ -393,11 +402,16 @@ __global__ void __launch_bounds__(64) k_composite(
       if (mine == 0u) continue;
       const uint32_t b = __shfl_sync(0xffffffffu, bb, j);
       const bool take = act && ((mine >> lane) & 1u);
+      float sw = 0.f, swerr = 0.f;
       if (take) {
         const uint32_t slot = b + (half ? __popc(m0) : 0) + __popc(mine & lt);
         const float4 r = rec_out[slot];
         const float w = st.w * r.w;
         st.x = fmaf(w, r.x, st.x); st.y = fmaf(w, r.y, st.y); st.z = fmaf(w, r.z, st.z);
+        if (STATS) {
+          sw = w;
+          if (w > 1e-1f) swerr = w * (fabsf(st.x - gtr) + fabsf(st.y - gtg) + fabsf(st.z - gtb));
+        }
         if (depth_t) { dp.x = fmaf(w, rec_t[slot], dp.x); dp.y += w; }
         if (rec_w) rec_w[slot] = w;
         if (rec_tr) rec_tr[slot] = st.w;
@@ -405,6 +419,25 @@ __global__ void __launch_bounds__(64) k_composite(
         act = st.w >= MLPSP_TERM;
       }
       const uint32_t um = __ballot_sync(0xffffffffu, take);
+      if (STATS && um) {
+        // this half-tile's share of the pair's statistics: one atomic per array
+        const int n_hit = __popc(__ballot_sync(0xffffffffu, sw > 1e-8f));
+        const int n_con = __popc(__ballot_sync(0xffffffffu, sw > 1e-1f));
+        float tsum = sw, tmax = sw, terr = swerr;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          tsum += __shfl_xor_sync(0xffffffffu, tsum, o);
+          tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+          terr += __shfl_xor_sync(0xffffffffu, terr, o);
+        }
+        if (lane == 0) {
+          const int p = ps.sorted_prims[s + i0 + j];
+          atomicAdd(ps.sum_w + p, tsum);
+          atomicMax(reinterpret_cast<int*>(ps.max_w + p), __float_as_int(tmax));   // w >= 0: bit order = value order
+          if (n_hit) atomicAdd(ps.hits + p, n_hit);
+          if (n_con) { atomicAdd(ps.contrib + p, n_con); atomicAdd(ps.sum_werr + p, terr); }
+        }
+      }
       if (um) {
         if (lane == 0) { used += __popc(um); if (mask_used32) mask_used32[2 * (size_t)(s + i0 + j) + half] = um; }
         if (!__any_sync(0xffffffffu, act)) break;
@@ -610,6 +643,12 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                   "feature slots must be 1, 4 or 5");
   }
   const bool keep = fr->keep_records == 1;
+  const bool want_stats = fr->stat_sum_w != nullptr;
+  if (want_stats)
+    MLPSP_REQUIRE(fr->gt_rgb && fr->stat_max_w && fr->stat_hits && fr->stat_sum_werr && fr->stat_contrib, MLPSP_E_ARG,
+                  "contribution statistics need gt_rgb and all five per-primitive arrays");
+  const PrimStats pstats = {fr->gt_rgb, fr->sorted_prims, fr->stat_sum_w, fr->stat_max_w, fr->stat_hits,
+                            fr->stat_sum_werr, fr->stat_contrib};
   // record export reads the consumed masks from the scratch copy, so a caller-owned mask buffer is
   // filled by a device copy afterwards
   uint32_t* used32 = (keep || want_feat) ? s.used32 : (uint32_t*)fr->mask_used;
@@ -663,7 +702,14 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                           fr->status, st);
     if (rc) return rc;
     { LaunchScope scope(kKComposite, 1, st);
-    k_composite<<<std::min(T, sms * 32), 64, 0, st>>>(fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+    if (want_stats)
+      k_composite<true><<<std::min(T, sms * 32), 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+                                  s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
+                                  fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
+                                  keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,
+                                  s.active[nxt], s.counters + kCtrActive0 + nxt, fr->status);
+    else
+    k_composite<false><<<std::min(T, sms * 32), 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
                                   fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
                                   keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,

@@ -130,6 +130,9 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
             self.feat_attr = nn.Parameter(fi)
         else:
             self.feat_attr = None
+        for name, dt in (("stat_sum_w", torch.float32), ("stat_max_w", torch.float32), ("stat_hits", torch.int32),
+                         ("stat_contrib_count", torch.int32), ("stat_sum_werr", torch.float32)):
+            self.register_buffer(name, torch.zeros(n, dtype=dt))
         self._packed = None
         self._packed_key = None
         self._renderers = {}
@@ -193,7 +196,7 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         return self._renderers[key]
 
     def _render(self, ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix, culled_prim_indices,
-                tile_offsets, want_depth, path_name, want_feat=False, sort_key=0):
+                tile_offsets, want_depth, path_name, want_feat=False, sort_key=0, stats=None):
         if self.image_size is None:
             raise ValueError("image_size must be set on NeuralPrimitiveSceneTileCUDA before calling forward.")
         W, H = self.image_size
@@ -234,7 +237,7 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         rgb, alpha = r.render(scene, ray_o.detach().float().contiguous(), ray_d.detach().float().contiguous(),
                               float(score_threshold), view=view, proj=proj, precision=prec, bg=bg,
                               want_depth=want_depth, tile_lists=lists, path_name=path_name, want_feat=want_feat,
-                              sort_key=sort_key)
+                              sort_key=sort_key, prim_stats=stats)
         return r, rgb, alpha
 
     @torch.no_grad()
@@ -288,11 +291,47 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
 
     @torch.no_grad()
     def render_rgb_alpha_no_grad(self, ray_o, ray_d, score_threshold=1e-3, bg_color=None, view_matrix=None,
-                                 proj_matrix=None, culled_prim_indices=None, tile_offsets=None):
-        """(rgb [B,3], alpha [B,1]) as cumodel.py:1196-1383 (pruning statistics are not built)."""
+                                 proj_matrix=None, collect_w_stats=False, gt_rgb=None, culled_prim_indices=None,
+                                 tile_offsets=None):
+        """(rgb [B,3], alpha [B,1]) as cumodel.py:1196-1383.  collect_w_stats accumulates the per-primitive
+        contribution statistics w = T * alpha into stat_sum_w / stat_max_w / stat_hits / stat_sum_werr /
+        stat_contrib_count, which needs the ground-truth image."""
+        if getattr(self, "camera_mode", "legacy-centered") == "colmap-native":
+            raise NotImplementedError("Native camera statistics rendering is not implemented; use forward for RGB/features")
+        stats = None
+        if collect_w_stats:
+            if self.image_size is None:
+                raise ValueError("image_size must be set on NeuralPrimitiveSceneTileCUDA before calling render_rgb_alpha_no_grad.")
+            B = self.image_size[0] * self.image_size[1]
+            if gt_rgb is None:
+                raise ValueError("collect_w_stats=True requires gt_rgb (shape=(B,3), B=W*H) to compute pixel_error inside the CUDA kernel.")
+            if gt_rgb.dim() != 2 or gt_rgb.shape[0] != B or gt_rgb.shape[1] != 3:
+                raise ValueError(f"gt_rgb must have shape (B,3) with B=W*H={B}, got {tuple(gt_rgb.shape)}")
+            device = self._activate_cuda_device()
+            gt = gt_rgb.to(device=device, dtype=torch.float32).contiguous()
+            for name, dt in (("stat_sum_w", torch.float32), ("stat_max_w", torch.float32), ("stat_hits", torch.int32),
+                             ("stat_sum_werr", torch.float32), ("stat_contrib_count", torch.int32)):
+                buf = getattr(self, name, None)
+                if buf is None or buf.numel() != self.num_primitives or buf.device != device:
+                    setattr(self, name, torch.zeros(self.num_primitives, dtype=dt, device=device))
+            stats = (gt, self.stat_sum_w, self.stat_max_w, self.stat_hits, self.stat_sum_werr, self.stat_contrib_count)
+        # the reference's statistics kernel orders a tile by the Euclidean depth of the centres along the
+        # tile-centre ray (np_tile_kernels.cu:2248-2256), its plain forward by t*: both are kept
         _r, rgb, alpha = self._render(ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix,
-                                      culled_prim_indices, tile_offsets, False, "render_tiles_forward_tilecenter")
+                                      culled_prim_indices, tile_offsets, False, "render_tiles_forward_tilecenter",
+                                      stats=stats, sort_key=1 if stats is not None else 0)
         return rgb.clone(), alpha.clone()
+
+    @torch.no_grad()
+    def reset_w_stats(self):
+        """Zero the per-primitive contribution statistics (cumodel.py:764-774)."""
+        dev = self.positions.device
+        n = self.positions.shape[0]
+        self.stat_sum_w = torch.zeros(n, device=dev, dtype=torch.float32)
+        self.stat_hits = torch.zeros(n, device=dev, dtype=torch.int32)
+        self.stat_max_w = torch.zeros(n, device=dev, dtype=torch.float32)
+        self.stat_sum_werr = torch.zeros(n, device=dev, dtype=torch.float32)
+        self.stat_contrib_count = torch.zeros(n, device=dev, dtype=torch.int32)
 
     @torch.no_grad()
     def render_rgb_t_no_grad(self, ray_o, ray_d, score_threshold=1e-3, bg_color=None, view_matrix=None,

@@ -194,7 +194,7 @@ class FrameRenderer:
 
     def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
                want_mask_used, waves, want_feat=False, keep_records=False, sort_key=0, tile_rows=None,
-               tile_pretest=True) -> L.Frame:
+               tile_pretest=True, prim_stats=None) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
         f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
@@ -231,6 +231,10 @@ class FrameRenderer:
         f.keep_records = 1 if keep_records else 0
         f.sort_key = int(sort_key)
         f.tile_pretest = 0 if tile_pretest else 1
+        if prim_stats is not None:
+            gt, sum_w, max_w, hits, sum_werr, contrib = prim_stats
+            f.gt_rgb, f.stat_sum_w, f.stat_max_w = L.ptr(gt), L.ptr(sum_w), L.ptr(max_w)
+            f.stat_hits, f.stat_sum_werr, f.stat_contrib = L.ptr(hits), L.ptr(sum_werr), L.ptr(contrib)
         if tile_rows is not None:
             f.tile_row_begin, f.tile_row_end = int(tile_rows[0]), int(tile_rows[1])
         f.status = L.ptr(self.status)
@@ -269,10 +273,12 @@ class FrameRenderer:
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
                rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False,
-               keep_records=False, sort_key=0, tile_rows=None, tile_pretest=True):
+               keep_records=False, sort_key=0, tile_rows=None, tile_pretest=True, prim_stats=None):
         """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling).
 
-        tile_pretest=False keeps every binned candidate in the lists the wave kernels walk (same image)."""
+        tile_pretest=False keeps every binned candidate in the lists the wave kernels walk (same image).
+        prim_stats=(gt_rgb [P,3] f32, sum_w, max_w [n] f32, hits [n] i32, sum_werr [n] f32, contrib [n] i32): device
+        tensors that receive the per-primitive contribution statistics of this frame (accumulated, not reset)."""
         lib, d = self.lib, self.device
         if precision is None:
             precision = L.PRECISION_F16 if scene.has_f16 else L.PRECISION_F32
@@ -300,7 +306,7 @@ class FrameRenderer:
                             "mlpsp_validate_tile_lists")
                 f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves,
                                 want_feat=want_feat, keep_records=keep_records, sort_key=sort_key, tile_rows=tile_rows,
-                                tile_pretest=tile_pretest)
+                                tile_pretest=tile_pretest, prim_stats=prim_stats)
                 self._last_frame = (f, scene)
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")

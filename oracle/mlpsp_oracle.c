@@ -549,6 +549,10 @@ typedef struct {
   /* record emission (second call, with rec_offsets from rec_count) */
   const int64_t* rec_offsets;
   int32_t* rec_ids; float* rec_x6; float* rec_raw; int32_t* rec_masks; float* rec_gates;
+  /* per-primitive contribution statistics of render_tiles_kernel_tilecenter_stats (np_tile_kernels.cu:2143-2500),
+     accumulated into the caller's arrays; all NULL or all set */
+  const float* gt_rgb;                        /* [P,3] */
+  float *stat_sum_w, *stat_max_w; int32_t* stat_hits; float* stat_sum_werr; int32_t* stat_contrib;   /* [N] */
   int64_t evals;                              /* out: MLP evaluations performed */
 } render_t;
 
@@ -574,6 +578,7 @@ void orc_render(render_t* a) {
     for (int i = s; i < e; ++i) {
       const int p = a->sorted_prims[i];
       uint64_t mg = 0, mu = 0;
+      float t_sum_w = 0.f, t_max_w = 0.f, t_sum_werr = 0.f; int t_hits = 0, t_contrib = 0;
       if (p >= 0 && p < a->n) {
         const float* g = a->geom + (size_t)p * 16;
         for (int k = 0; k < npx; ++k) {
@@ -602,6 +607,15 @@ void orc_render(render_t* a) {
           }
           C[k][0] = fmaf(w, mo.R, C[k][0]); C[k][1] = fmaf(w, mo.G, C[k][1]); C[k][2] = fmaf(w, mo.B, C[k][2]);
           tacc[k] = fmaf(w, h.t, tacc[k]); wacc[k] += w;
+          if (a->stat_sum_w) {
+            /* np_tile_kernels.cu:2391-2410: hit when w > 1e-8, "significant" when w > 0.1; the error is the L1
+               distance of the partial colour after this record to the ground truth */
+            const float* gt = a->gt_rgb + pixi[k] * 3;
+            const float err = fabsf(C[k][0] - gt[0]) + fabsf(C[k][1] - gt[1]) + fabsf(C[k][2] - gt[2]);
+            t_sum_w += w; if (w > t_max_w) t_max_w = w;
+            if (w > 1e-8f) ++t_hits;
+            if (w > 1e-1f) { ++t_contrib; t_sum_werr += w * err; }
+          }
           if (a->feat) {
             const int Cf = a->feat_dim, S = a->feat_slots;
             float* dst = a->feat + pixi[k] * Cf;
@@ -626,6 +640,13 @@ void orc_render(render_t* a) {
       }
       if (a->mask_geo) a->mask_geo[i] = mg;
       if (a->mask_used) a->mask_used[i] = mu;
+      if (a->stat_sum_w && mu) {
+        #pragma omp critical(orc_stats)
+        {
+          a->stat_sum_w[p] += t_sum_w; if (t_max_w > a->stat_max_w[p]) a->stat_max_w[p] = t_max_w;
+          a->stat_hits[p] += t_hits; a->stat_sum_werr[p] += t_sum_werr; a->stat_contrib[p] += t_contrib;
+        }
+      }
       if (alive) {
         int any = 0;
         for (int k = 0; k < npx; ++k) any |= (valid[k] && trans[k] >= ORC_TERM);

@@ -77,6 +77,8 @@ class _Render(C.Structure):
         ("rec_ids", C.POINTER(C.c_int32)), ("rec_x6", C.POINTER(C.c_float)),
         ("rec_raw", C.POINTER(C.c_float)), ("rec_masks", C.POINTER(C.c_int32)),
         ("rec_gates", C.POINTER(C.c_float)),
+        ("gt_rgb", C.POINTER(C.c_float)), ("stat_sum_w", C.POINTER(C.c_float)), ("stat_max_w", C.POINTER(C.c_float)),
+        ("stat_hits", C.POINTER(C.c_int32)), ("stat_sum_werr", C.POINTER(C.c_float)), ("stat_contrib", C.POINTER(C.c_int32)),
         ("evals", C.c_int64),
     ]
 
@@ -194,11 +196,12 @@ class RenderResult:
     rec_count: np.ndarray
     evals: int
     records: dict | None = None
+    stats: dict | None = None
 
 
 def render(rays_o, rays_d_unit, geom, tile_offsets, sorted_prims, W, H, tile, thr, weights, freq, att,
            precision=0, feat_attr=None, beta=1.5, tau=2.0, want_masks=True, want_records=False,
-           tile_range=None) -> RenderResult:
+           tile_range=None, gt_rgb=None) -> RenderResult:
     """Tile-major front-to-back render of depth-sorted tile lists (np_tile_kernels.cu:1837-2137)."""
     ro, rd, geom = _f32(rays_o), _f32(rays_d_unit), _f32(geom)
     off, sp = _i32(tile_offsets), _i32(sorted_prims)
@@ -234,8 +237,20 @@ def render(rays_o, rays_d_unit, geom, tile_offsets, sorted_prims, W, H, tile, th
         mg = np.zeros(sp.size, np.uint64)
         mu = np.zeros(sp.size, np.uint64)
         a.mask_geo, a.mask_used = _p(mg, C.c_uint64), _p(mu, C.c_uint64)
+    stats = None
+    if gt_rgb is not None:
+        # per-primitive contribution statistics (np_tile_kernels.cu:2143-2500), starting from zero
+        gt = _f32(gt_rgb).reshape(P, 3)
+        keep.append(gt)
+        n = geom.shape[0]
+        stats = dict(sum_w=np.zeros(n, np.float32), max_w=np.zeros(n, np.float32), hits=np.zeros(n, np.int32),
+                     sum_werr=np.zeros(n, np.float32), contrib=np.zeros(n, np.int32))
+        a.gt_rgb = _p(gt)
+        a.stat_sum_w, a.stat_max_w, a.stat_hits = _p(stats["sum_w"]), _p(stats["max_w"]), _p(stats["hits"], C.c_int32)
+        a.stat_sum_werr, a.stat_contrib = _p(stats["sum_werr"]), _p(stats["contrib"], C.c_int32)
     lib().orc_render(C.byref(a))
     res = RenderResult(rgb, alpha, dt, feat, mg, mu, marg, cnt, int(a.evals))
+    res.stats = stats
     if want_records:
         offs = np.zeros(P + 1, np.int64)
         np.cumsum(cnt, out=offs[1:])

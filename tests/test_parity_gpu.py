@@ -593,3 +593,43 @@ def test_checkpoint_loads_into_the_renderer(dev):
     module.set_image_size(cam["W"], cam["H"])
     rgb_m = module(ro, rd, score_threshold=5e-3, view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
     assert (rgb_m.reshape(-1, 3) - rgb_a).abs().max().item() <= 2e-3   # its encoder rebuilds the bands on its own
+
+
+@pytest.mark.parametrize("name", ["tiny", "dense"])
+def test_contribution_statistics_match_oracle(dev, name):
+    """Per-primitive w statistics of render_rgb_alpha_no_grad(collect_w_stats=True)
+    (cumodel.py:1196-1383; np_tile_kernels.cu:2143-2500): counts exact away from their thresholds, sums to 1e-4."""
+    from mlp_splatting_b200.cumodel import NeuralPrimitiveSceneTileCUDA
+    from oracle import oracle as orc
+    from tests.helpers import oracle_inputs
+    scene, cam = small_case(**CASES[name])
+    n = scene["positions"].shape[0]
+    gt = np.random.default_rng(5).uniform(0, 1, (cam["W"] * cam["H"], 3)).astype(np.float32)
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False, key_mode=1)   # the statistics kernel's order
+    geom, rdu = oracle_inputs(scene, cam)
+    res = orc.render(cam["rays_o"], rdu, geom, f["tile_offsets"], f["sorted_prims"], cam["W"], cam["H"], 8, 5e-3,
+                     [scene[k] for k in WKEYS], scene["freq"], scene["att"], precision=0, want_masks=False, gt_rgb=gt)
+    m = NeuralPrimitiveSceneTileCUDA(num_primitives=n, precision="fp32").to(dev)
+    with torch.no_grad():
+        for k in ("positions", "log_scales", "quats") + WKEYS:
+            getattr(m, k).copy_(_t(scene[k], dev))
+    m.set_image_size(cam["W"], cam["H"])
+    args = (_t(cam["rays_o"], dev), _t(cam["rays_d"], dev))
+    kw = dict(score_threshold=5e-3, view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
+    with pytest.raises(ValueError, match="requires gt_rgb"):
+        m.render_rgb_alpha_no_grad(*args, collect_w_stats=True, **kw)
+    rgb, alpha = m.render_rgb_alpha_no_grad(*args, collect_w_stats=True, gt_rgb=_t(gt, dev), **kw)
+    np.testing.assert_allclose(rgb.cpu().numpy(), res.rgb, atol=IMG_TOL_F32)
+    st = res.stats
+    np.testing.assert_allclose(m.stat_sum_w.cpu().numpy(), st["sum_w"], rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(m.stat_max_w.cpu().numpy(), st["max_w"], rtol=0, atol=2e-5)
+    np.testing.assert_allclose(m.stat_sum_werr.cpu().numpy(), st["sum_werr"], rtol=1e-3, atol=2e-3)
+    # a count can differ only where some record's w sits at its threshold (1e-8 / 0.1) to within the float tolerance
+    assert np.abs(m.stat_hits.cpu().numpy() - st["hits"]).sum() <= max(2, int(2e-4 * st["hits"].sum()))
+    assert np.abs(m.stat_contrib_count.cpu().numpy() - st["contrib"]).sum() <= max(2, int(1e-3 * st["contrib"].sum()))
+    assert st["hits"].sum() > 1000 and st["contrib"].sum() > 100
+    # a second frame accumulates; reset clears
+    m.render_rgb_alpha_no_grad(*args, collect_w_stats=True, gt_rgb=_t(gt, dev), **kw)
+    np.testing.assert_allclose(m.stat_sum_w.cpu().numpy(), 2 * st["sum_w"], rtol=1e-4, atol=2e-4)
+    m.reset_w_stats()
+    assert int(m.stat_hits.sum()) == 0 and float(m.stat_max_w.max()) == 0.0

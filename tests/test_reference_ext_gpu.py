@@ -132,3 +132,30 @@ def test_feature_map_matches_reference_kernel(ref):
     rgb, _ = r.render(ps, x[0], x[1], 5e-3, precision=0, tile_lists=(x[5], x[6]), rays_normalized=True, want_feat=True)
     assert (rgb - rgb_r).abs().max().item() <= 1e-4
     assert (r.feat - feat_r).abs().max().item() <= 1e-4
+
+
+def test_contribution_statistics_match_reference_kernel(ref):
+    """render_tiles_forward_tilecenter_stats (np_tile_kernels.cu:5349-5430): the statistics kernel itself."""
+    dev = torch.device("cuda", 0)
+    scene, cam = small_case(**CASES["tiny"])
+    n = scene["positions"].shape[0]
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    x = _inputs(scene, cam, f, dev)
+    gt = torch.rand((cam["W"] * cam["H"], 3), device=dev, generator=torch.Generator(device=dev).manual_seed(3))
+    sw, mw = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    hits = torch.zeros(n, device=dev, dtype=torch.int32)
+    swe, cc = torch.zeros(n, device=dev), torch.zeros(n, device=dev, dtype=torch.int32)
+    F = int(x[7].numel())
+    rgb_r, alpha_r = ref.render_tiles_forward_tilecenter_stats(
+        x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], x[8], F, x[9], x[10], x[11], x[12], x[13], x[14],
+        int(x[9].shape[0]), int(x[9].shape[1]), int(x[9].shape[2]), cam["W"], cam["H"], 8, 8, 5e-3, gt, sw, mw, hits, swe, cc)
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    s2 = (gt, torch.zeros_like(sw), torch.zeros_like(mw), torch.zeros_like(hits), torch.zeros_like(swe), torch.zeros_like(cc))
+    rgb, alpha = r.render(ps, x[0], x[1], 5e-3, precision=0, tile_lists=(x[5], x[6]), rays_normalized=True, prim_stats=s2,
+                          sort_key=1)   # this kernel sorts by Euclidean depth on the tile-centre ray (np_tile_kernels.cu:2248-2256)
+    assert (rgb - rgb_r).abs().max().item() <= 1e-4
+    assert torch.allclose(s2[1], sw, rtol=1e-4, atol=1e-4) and torch.allclose(s2[2], mw, rtol=0, atol=5e-5)
+    assert torch.allclose(s2[4], swe, rtol=1e-3, atol=3e-3)
+    assert (s2[3] - hits).abs().sum().item() <= max(2, int(2e-4 * hits.sum().item()))
+    assert (s2[5] - cc).abs().sum().item() <= max(2, int(1e-3 * cc.sum().item()))
+    assert hits.sum().item() > 1000
