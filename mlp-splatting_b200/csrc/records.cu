@@ -396,51 +396,70 @@ __global__ void __launch_bounds__(64) k_composite(
       bb = pair_base[s + idx];
     }
     const int cnt = min(32, whi - i0);
-    for (int j = 0; j < cnt; ++j) {
-      const uint32_t m0 = __shfl_sync(0xffffffffu, mm.x, j), m1 = __shfl_sync(0xffffffffu, mm.y, j);
-      const uint32_t mine = half ? m1 : m0;
-      if (mine == 0u) continue;
-      const uint32_t b = __shfl_sync(0xffffffffu, bb, j);
-      const bool take = act && ((mine >> lane) & 1u);
-      float sw = 0.f, swerr = 0.f;
-      if (take) {
-        const uint32_t slot = b + (half ? __popc(m0) : 0) + __popc(mine & lt);
-        const float4 r = rec_out[slot];
-        const float w = st.w * r.w;
-        st.x = fmaf(w, r.x, st.x); st.y = fmaf(w, r.y, st.y); st.z = fmaf(w, r.z, st.z);
-        if (STATS) {
-          sw = w;
-          if (w > 1e-1f) swerr = w * (fabsf(st.x - gtr) + fabsf(st.y - gtg) + fabsf(st.z - gtb));
-        }
-        if (depth_t) { dp.x = fmaf(w, rec_t[slot], dp.x); dp.y += w; }
-        if (rec_w) rec_w[slot] = w;
-        if (rec_tr) rec_tr[slot] = st.w;
-        st.w *= (1.f - r.w);
-        act = st.w >= MLPSP_TERM;
-      }
-      const uint32_t um = __ballot_sync(0xffffffffu, take);
-      if (STATS && um) {
-        // this half-tile's share of the pair's statistics: one atomic per array
-        const int n_hit = __popc(__ballot_sync(0xffffffffu, sw > 1e-8f));
-        const int n_con = __popc(__ballot_sync(0xffffffffu, sw > 1e-1f));
-        float tsum = sw, tmax = sw, terr = swerr;
+    bool stop = false;
+    // four pairs at a time: the records a lane may need are requested first (whether its pixel is still live or
+    // not), then blended in list order, so the gathers of a batch overlap instead of forming a chain
+    for (int j0 = 0; j0 < cnt && !stop; j0 += 4) {
+      float4 rr[4];
+      uint32_t slot4[4], m04[4], mine4[4];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          tsum += __shfl_xor_sync(0xffffffffu, tsum, o);
-          tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
-          terr += __shfl_xor_sync(0xffffffffu, terr, o);
-        }
-        if (lane == 0) {
-          const int p = ps.sorted_prims[s + i0 + j];
-          atomicAdd(ps.sum_w + p, tsum);
-          atomicMax(reinterpret_cast<int*>(ps.max_w + p), __float_as_int(tmax));   // w >= 0: bit order = value order
-          if (n_hit) atomicAdd(ps.hits + p, n_hit);
-          if (n_con) { atomicAdd(ps.contrib + p, n_con); atomicAdd(ps.sum_werr + p, terr); }
-        }
+      for (int u = 0; u < 4; ++u) {
+        const int j = min(j0 + u, 31);
+        const uint32_t m0 = __shfl_sync(0xffffffffu, mm.x, j), m1 = __shfl_sync(0xffffffffu, mm.y, j);
+        const uint32_t b = __shfl_sync(0xffffffffu, bb, j);
+        const uint32_t mine = (j0 + u < cnt) ? (half ? m1 : m0) : 0u;
+        m04[u] = m0; mine4[u] = mine;
+        slot4[u] = b + (half ? __popc(m0) : 0) + __popc(mine & lt);
+        rr[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if ((mine >> lane) & 1u) rr[u] = rec_out[slot4[u]];
       }
-      if (um) {
-        if (lane == 0) { used += __popc(um); if (mask_used32) mask_used32[2 * (size_t)(s + i0 + j) + half] = um; }
-        if (!__any_sync(0xffffffffu, act)) break;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + u;
+        const uint32_t mine = mine4[u];
+        if (stop || mine == 0u) continue;
+        const bool take = act && ((mine >> lane) & 1u);
+        float sw = 0.f, swerr = 0.f;
+        if (take) {
+          const uint32_t slot = slot4[u];
+          const float4 r = rr[u];
+          const float w = st.w * r.w;
+          st.x = fmaf(w, r.x, st.x); st.y = fmaf(w, r.y, st.y); st.z = fmaf(w, r.z, st.z);
+          if (STATS) {
+            sw = w;
+            if (w > 1e-1f) swerr = w * (fabsf(st.x - gtr) + fabsf(st.y - gtg) + fabsf(st.z - gtb));
+          }
+          if (depth_t) { dp.x = fmaf(w, rec_t[slot], dp.x); dp.y += w; }
+          if (rec_w) rec_w[slot] = w;
+          if (rec_tr) rec_tr[slot] = st.w;
+          st.w *= (1.f - r.w);
+          act = st.w >= MLPSP_TERM;
+        }
+        const uint32_t um = __ballot_sync(0xffffffffu, take);
+        if (STATS && um) {
+          // this half-tile's share of the pair's statistics: one atomic per array
+          const int n_hit = __popc(__ballot_sync(0xffffffffu, sw > 1e-8f));
+          const int n_con = __popc(__ballot_sync(0xffffffffu, sw > 1e-1f));
+          float tsum = sw, tmax = sw, terr = swerr;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            tsum += __shfl_xor_sync(0xffffffffu, tsum, o);
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+            terr += __shfl_xor_sync(0xffffffffu, terr, o);
+          }
+          if (lane == 0) {
+            const int p = ps.sorted_prims[s + i0 + j];
+            atomicAdd(ps.sum_w + p, tsum);
+            atomicMax(reinterpret_cast<int*>(ps.max_w + p), __float_as_int(tmax));   // w >= 0: bit order = value order
+            if (n_hit) atomicAdd(ps.hits + p, n_hit);
+            if (n_con) { atomicAdd(ps.contrib + p, n_con); atomicAdd(ps.sum_werr + p, terr); }
+          }
+        }
+        if (um) {
+          if (lane == 0) { used += __popc(um); if (mask_used32) mask_used32[2 * (size_t)(s + i0 + j) + half] = um; }
+          if (!__any_sync(0xffffffffu, act)) stop = true;
+        }
+        (void)m04;
       }
     }
   }
