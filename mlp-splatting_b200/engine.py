@@ -269,6 +269,19 @@ class FrameRenderer:
             return True
         return False
 
+    # Wave schedule carried from frame to frame.  The library's default schedule ends in waves that most frames
+    # never need; each of them still costs its launches.  After a frame whose status has been read, the next
+    # frame is given the waves that one used plus a single catch-all wave, which keeps any frame correct (the
+    # image does not depend on the schedule) and costs one idle wave instead of several.
+    DEFAULT_WAVES = (32, 32, 64, 128, 256)
+
+    def _adapt_waves(self, waves_used: int):
+        n = int(waves_used)
+        if n <= 0 or n > len(self.DEFAULT_WAVES):
+            self._auto_waves = None
+        else:
+            self._auto_waves = list(self.DEFAULT_WAVES[:n]) + [self.capacity]
+
     # -- stages -------------------------------------------------------------------------------
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
@@ -282,6 +295,9 @@ class FrameRenderer:
         lib, d = self.lib, self.device
         if precision is None:
             precision = L.PRECISION_F16 if scene.has_f16 else L.PRECISION_F32
+        auto = waves is None
+        if auto:
+            waves = getattr(self, "_auto_waves", None)
         with torch.cuda.device(d):
             st = _stream_ptr(d)
             if rays_normalized:
@@ -317,6 +333,8 @@ class FrameRenderer:
                     return self.rgb, self.alpha
                 bits, stats = self._read_status()
                 self.last_stats = stats
+                if auto and bits == 0:
+                    self._adapt_waves(stats.waves)
                 if bits & (L.BIT_BAD_OFFSETS | L.BIT_TILE_CAPACITY | L.BIT_BAD_IDS | L.BIT_TIMEOUT):
                     raise_for_status(bits, stats.max_tile_len, self.capacity, path_name)
                 if self._grow(bits, stats):
@@ -490,6 +508,7 @@ class FramePipeline:
         s["busy"] = False
         bits = int(r.status_host[L.ST_BITS])
         if bits == 0:
+            r._adapt_waves(int(r.status_host[L.ST_WAVES]))
             return
         # rare path: overflow / error / fp16 overflow -> redo this frame synchronously with full checks
         threshold, kw, out_rgb, out_alpha = s["kw"]
