@@ -144,7 +144,7 @@ void launch_tile_frames(const mlpsp_frame* fr, TileFrame* frames, cudaStream_t s
 int launch_bin_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, const int32_t* tile_view,
                       const float* views_host, int num_views, cudaStream_t st);
 int launch_bin_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st);
-// long_list [T] / long_count [1]: device scratch for the tiles that take the block-wide sort
+// long_list [T] / long_count [2]: device scratch (tiles that take the block-wide sort, their number, a tile cursor)
 // list_len (optional): candidates actually present at the front of every tile's span (pre-tested binning);
 // the rest of the span is filled with -1 in sorted_prims
 int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, cudaStream_t st, bool unordered_input,

@@ -82,7 +82,7 @@ constexpr int kWarpSortMax = 512;
 // Short lists: one warp per tile, eight tiles per CTA.  Tiles with more than kWarpSortMax candidates
 // are appended to long_list for k_sort_long, so that each of them gets a CTA of its own.
 template <bool IDSORT>
-__global__ void __launch_bounds__(256) k_sort_tiles(
+__global__ void __launch_bounds__(256, 4) k_sort_tiles(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* tile_prims, int W, int H, int ts, int ntx, int T, int cap,
     int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode, int32_t* __restrict__ long_list,
@@ -90,7 +90,12 @@ __global__ void __launch_bounds__(256) k_sort_tiles(
   __shared__ __align__(16) unsigned long long s_buf[kTilesPerCta * kWarpSortMax];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x * kTilesPerCta + warp;
+  // warps draw tiles from a shared cursor (long_count[1]): list lengths differ by two orders of magnitude, and
+  // a fixed deal would leave most warps of a CTA waiting for the one with the longest list
+  for (;;) {
+  int tile = 0;
+  if (lane == 0) tile = atomicAdd(long_count + 1, 1);
+  tile = __shfl_sync(0xffffffffu, tile, 0);
   if (tile >= T) return;
   const int s = tile_offsets[tile];
   const int span = min(tile_offsets[tile + 1] - s, cap);
@@ -98,11 +103,11 @@ __global__ void __launch_bounds__(256) k_sort_tiles(
   if (list_len && lane == 0 && len > 0) atomicAdd(status + MLPSP_ST_PAIRS_KEPT, len);
   if (len > kWarpSortMax) {
     if (lane == 0) long_list[atomicAdd(long_count, 1)] = tile;
-    return;
+    continue;
   }
   if (len <= 0) {
     for (int i = lane; i < span; i += 32) sorted_prims[s + i] = -1;
-    return;
+    continue;
   }
   const int tx = tile % ntx, ty = tile / ntx;
   const int cx = min(tx * ts + (ts >> 1), W - 1), cy = min(ty * ts + (ts >> 1), H - 1);
@@ -119,6 +124,8 @@ __global__ void __launch_bounds__(256) k_sort_tiles(
   else if (N == 256) warp_bitonic<unsigned long long, 256>(buf);
   else warp_bitonic<unsigned long long, 512>(buf);
   write_sorted<IDSORT>(buf, tile_prims, sorted_prims, keys_out, s, len, span, lane, 32);
+  __syncwarp();   // the slice is reused by this warp's next tile
+  }
 }
 
 // Long lists: one CTA per tile of long_list (grid-stride), the same bitonic network run by the whole CTA.
@@ -243,9 +250,9 @@ int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, c
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  MLPSP_CUDA_OK(cudaMemsetAsync(long_count, 0, 4, st));
+  MLPSP_CUDA_OK(cudaMemsetAsync(long_count, 0, 8, st));   // [0] long tiles, [1] tile cursor of k_sort_tiles
   LaunchScope scope(kKSort, 2, st);
-  const int grid = (T + kTilesPerCta - 1) / kTilesPerCta;
+  const int grid = std::min((T + kTilesPerCta - 1) / kTilesPerCta, sms * 4);
   const int grid_long = std::min(T, sms * 6);
   const float4* geom = (const float4*)sc->geom;
   if (unordered_input) {
