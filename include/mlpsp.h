@@ -59,6 +59,7 @@ extern "C" {
 
 #define MLPSP_PRECISION_F32 0  /* scalar FP32 evaluator (np_tile_kernels.cu:312-380) */
 #define MLPSP_PRECISION_F16 1  /* fp16 operands, FP32 accumulate, tcgen05 (rgb_wmma.cuh:75-223) */
+#define MLPSP_PRECISION_BF16 2 /* bfloat16 operands (the bf16 flag of render_tiles_rgb_wmma, rgb_wmma.cuh:225), same kernel */
 
 #define MLPSP_GEOM_FLOATS 16   /* packed geometry floats per primitive */
 #define MLPSP_MAX_WAVES 32
@@ -82,6 +83,7 @@ typedef struct mlpsp_scene {
   int32_t feat_dim;       /* C <= 512 */
   float gate_beta;        /* semantic_tetra_gates norm_beta */
   float gate_tau;         /* semantic_tetra_gates logit_temp */
+  const void* wbf16;      /* the same image with bfloat16 operands, from mlpsp_pack_weights_bf16, or NULL */
 } mlpsp_scene;
 
 /* One frame.  Replaces (rays_o, rays_d, culled_prim_indices, tile_offsets, Wimg, Himg, TW, TH,
@@ -156,6 +158,8 @@ int mlpsp_normalize_rows(const float* in, float* out, int64_t rows, int32_t dim,
 int64_t mlpsp_packed_weight_bytes(int32_t hidden, int32_t num_freq);
 /* status (optional): MLPSP_ST_NUMERIC is raised when a weight or bias is not finite in fp16/FP32. */
 int mlpsp_pack_weights_f16(const mlpsp_scene* scene, void* w16_out, int32_t* status, void* stream);
+/* The same image with bfloat16 operands (same size and layout); no reference kernel casts per scene either. */
+int mlpsp_pack_weights_bf16(const mlpsp_scene* scene, void* wbf16_out, int32_t* status, void* stream);
 
 int mlpsp_status_reset(int32_t* status, void* stream);
 

@@ -17,7 +17,7 @@ ST_RECORDS_LO, ST_USED_LO, ST_WAVE_RECORDS, ST_WORK_ITEMS, ST_WORK_TOTAL, ST_PAI
 BIT_BAD_OFFSETS, BIT_TILE_CAPACITY, BIT_BAD_IDS = 1, 2, 4
 BIT_PAIR_OVERFLOW, BIT_RECORD_OVERFLOW, BIT_NUMERIC, BIT_TIMEOUT = 8, 16, 64, 128
 BIT_TILE_ORIGINS, BIT_CONE_TOO_WIDE = 256, 512
-PRECISION_F32, PRECISION_F16 = 0, 1
+PRECISION_F32, PRECISION_F16, PRECISION_BF16 = 0, 1, 2
 MAX_WAVES = 32
 GEOM_FLOATS = 16
 KERNEL_CLASSES = ("bin", "sort", "hits", "prim_scan", "fill", "mlp", "composite", "other")
@@ -31,6 +31,7 @@ class Scene(C.Structure):
         ("W1", _fp), ("b1", _fp), ("W2", _fp), ("b2", _fp), ("W3", _fp), ("b3", _fp),
         ("w16", _fp), ("freq", _fp), ("att", _fp), ("feat_attr", _fp),
         ("feat_slots", C.c_int32), ("feat_dim", C.c_int32), ("gate_beta", C.c_float), ("gate_tau", C.c_float),
+        ("wbf16", _fp),
     ]
 
 
@@ -60,6 +61,7 @@ _SIGS = {
     "mlpsp_normalize_rows": (C.c_int, [_fp, _fp, C.c_int64, C.c_int32, _fp]),
     "mlpsp_packed_weight_bytes": (C.c_int64, [C.c_int32, C.c_int32]),
     "mlpsp_pack_weights_f16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
+    "mlpsp_pack_weights_bf16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
     "mlpsp_status_reset": (C.c_int, [_fp, _fp]),
     "mlpsp_kernel_launches": (C.c_int, [C.POINTER(C.c_int64), C.c_int32]),
     "mlpsp_timing_enable": (C.c_int, [C.c_int32]),

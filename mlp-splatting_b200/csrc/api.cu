@@ -100,7 +100,8 @@ static int get_scratch(const mlpsp_scene* sc, const mlpsp_frame* fr, Scratch& s,
 static int render_sorted_checked(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st,
                                  bool lists_refined = false) {
   MLPSP_REQUIRE(fr->rays_o && fr->rays_d && fr->rgb && fr->alpha, MLPSP_E_ARG, "render: rays or outputs missing");
-  MLPSP_REQUIRE(fr->precision == MLPSP_PRECISION_F32 || fr->precision == MLPSP_PRECISION_F16, MLPSP_E_ARG,
+  MLPSP_REQUIRE(fr->precision == MLPSP_PRECISION_F32 || fr->precision == MLPSP_PRECISION_F16 ||
+                    fr->precision == MLPSP_PRECISION_BF16, MLPSP_E_ARG,
                 "render: unknown precision %d", fr->precision);
   MLPSP_REQUIRE(fr->num_waves >= 0 && fr->num_waves <= MLPSP_MAX_WAVES, MLPSP_E_ARG, "render: bad num_waves");
   return launch_render_sorted(sc, fr, s, st, lists_refined);
@@ -328,8 +329,9 @@ extern "C" int mlpsp_mlp_grouped(const mlpsp_scene* sc, int32_t precision, const
   k_grouped_records<<<(unsigned)((num_records + 255) / 256), 256, 0, st>>>(x6, num_records, s.rec_in); }
   int rc = launch_prim_scan(s, n, 0, status, st);
   if (rc) return rc;
-  if (precision == MLPSP_PRECISION_F16)
-    return launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, nullptr, kOutSigmaRaw, status, st);
+  if (precision == MLPSP_PRECISION_F16 || precision == MLPSP_PRECISION_BF16)
+    return launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, nullptr, kOutSigmaRaw, status, st,
+                          precision == MLPSP_PRECISION_BF16);
   MLPSP_REQUIRE(precision == MLPSP_PRECISION_F32, MLPSP_E_ARG, "mlpsp_mlp_grouped: unknown precision %d", precision);
   return launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, nullptr, kOutSigmaRaw, status, st);
 }

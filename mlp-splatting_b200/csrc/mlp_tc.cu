@@ -19,6 +19,7 @@
 // Every wait on an mbarrier is bounded; when one gives up the CTA raises MLPSP_ST_TIMEOUT, waits
 // (bounded) for its own bulk copy, frees its tensor memory and returns.
 #include "frame.cuh"
+#include <cuda_bf16.h>
 
 namespace mlpsp {
 
@@ -101,8 +102,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
          (1ull << 46);
 }
 // instruction descriptor: D = F32, A = B = F16, both K-major, dense
-__host__ __device__ constexpr uint32_t instr_desc(int M, int N) {
-  return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+// (BF16: A and B formats, bits 7 and 10, switch from F16 to BF16)
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool bf16 = false) {
+  return (1u << 4) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
   asm volatile(
@@ -132,15 +134,20 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// (max(a, 0), max(b, 0)) rounded to binary16 (RN) in one conversion; a in the low half
+// (max(a, 0), max(b, 0)) rounded (RN) to binary16 or bfloat16 in one conversion; a in the low half
+template <bool BF16>
 __device__ __forceinline__ uint32_t pack_h2_relu(float a, float b) {
   uint32_t r;
-  asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  if (BF16) asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
   return r;
 }
+template <bool BF16>
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
-  const __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&h);
+  uint32_t r;
+  if (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
 }
 
 // Position of an encoded input inside the K dimension of layer 1.  The reference orders K as
@@ -157,10 +164,12 @@ __host__ __device__ constexpr int enc_k_of_reference(int k) {
 // Returns true when an activation rounded to +inf in binary16.  The FP32 sums themselves are always
 // finite: operands are finite fp16 values, so |sum| <= 80 * 65504^2 (rgb_wmma.cuh:179-181 checks for a
 // non-finite or fp16-overflowing activation per element).
-template <bool KEEP>
+template <bool KEEP, bool BF16>
 __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const float* bias, char* a2, int row,
                                                uint32_t& relu_mask) {
-  __half2 top = __floats2half2_rn(0.f, 0.f);
+  // running maximum of the packed activations (they are >= 0 after the ReLU, so for both formats the bit
+  // patterns order like the values and one unsigned 16-bit-lane maximum serves either)
+  uint32_t top = 0u;
   relu_mask = 0u;
 #pragma unroll
   for (int kc = 0; kc < 4; ++kc) {
@@ -176,19 +185,21 @@ __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], const 
         relu_mask |= (v0 > 0.f ? 1u : 0u) << j;
         relu_mask |= (v1 > 0.f ? 1u : 0u) << (j + 1);
       }
-      w[q] = pack_h2_relu(v0, v1);
-      top = __hmax2(top, *reinterpret_cast<const __half2*>(&w[q]));
+      w[q] = pack_h2_relu<BF16>(v0, v1);
+      top = __vmaxu2(top, w[q]);
     }
     *reinterpret_cast<uint4*>(a2 + kc * (kRows * 16) + row * 16) = make_uint4(w[0], w[1], w[2], w[3]);
   }
-  return __hisinf(__low2half(top)) || __hisinf(__high2half(top));
+  // +inf (or the canonical NaN a non-finite sum converts to) in either lane
+  const uint32_t inf16 = BF16 ? 0x7f80u : 0x7c00u;
+  return (top & 0xffffu) >= inf16 || (top >> 16) >= inf16;
 }
 
 // Encode one record into this thread's row of the layer-1 A tile (K order of enc_k()).  mult[f] is
 // freq[f] * att[f].  LADDER: every band is exactly twice the one before, so the phases are exact
 // doublings of the first and sin / cos of the higher bands follow from the double-angle identities
 // (2 special-function evaluations per coordinate instead of 12).  Returns true for a non-finite input.
-template <bool LADDER>
+template <bool LADDER, bool BF16>
 __device__ __forceinline__ bool encode_row(const RecIn& r, const float (&mult)[6], char* row_ptr) {
   const float v6[6] = {r.rdx, r.rdy, r.rdz, r.dx, r.dy, r.dz};
   bool bad = false;
@@ -214,8 +225,8 @@ __device__ __forceinline__ bool encode_row(const RecIn& r, const float (&mult)[6
       }
 #pragma unroll
       for (int g = 0; g < 3; ++g) {
-        w[d * 6 + g * 2] = pack_h2(sn[2 * g], sn[2 * g + 1]);
-        w[d * 6 + g * 2 + 1] = pack_h2(cs[2 * g], cs[2 * g + 1]);
+        w[d * 6 + g * 2] = pack_h2<BF16>(sn[2 * g], sn[2 * g + 1]);
+        w[d * 6 + g * 2 + 1] = pack_h2<BF16>(cs[2 * g], cs[2 * g + 1]);
       }
     }
 #pragma unroll
@@ -231,7 +242,7 @@ __device__ __forceinline__ bool encode_row(const RecIn& r, const float (&mult)[6
 // fetch the next item's descriptor, its record and -- as soon as the MMAs that read them have
 // finished -- the next primitive's W1 and W2 blocks while the current item is still being evaluated,
 // so the only global-memory latency left on an item's critical path is the 1.3 KB copy of W3 + biases.
-template <bool KEEP>
+template <bool KEEP, bool BF16>
 __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
     const char* __restrict__ w16, const float* __restrict__ freq, const float* __restrict__ att,
     const RecIn* __restrict__ rec_in, const int4* __restrict__ work,
@@ -297,7 +308,8 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
     // ---- encode this thread's record into the layer-1 A tile ----
     if (warp_live) {
       // rows past the end inside a live warp hold the zero record; their results are never stored
-      const bool nonfinite = ladder ? encode_row<true>(r, mult, s_a1 + tid * 16) : encode_row<false>(r, mult, s_a1 + tid * 16);
+      const bool nonfinite = ladder ? encode_row<true, BF16>(r, mult, s_a1 + tid * 16)
+                                    : encode_row<false, BF16>(r, mult, s_a1 + tid * 16);
       bad |= nonfinite;
     }
     fence_async_smem();
@@ -314,11 +326,11 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         mma_f16(tmem, smem_desc(a1 + ks * 2 * (kRows * 16), kRows * 16, 128),
-                smem_desc(wb + kOffW1 + ks * 2 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH), ks > 0);
+                smem_desc(wb + kOffW1 + ks * 2 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH, BF16), ks > 0);
       // K = 64..79: the weight image holds a zero chunk and then chunk 8; the A operand pairs them with
       // chunk 7 (any finite values: they meet zeros) and chunk 8, so no padded A chunk is stored
       mma_f16(tmem, smem_desc(a1 + 7 * (kRows * 16), kRows * 16, 128),
-              smem_desc(wb + kOffW1 + 8 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH), 1u);
+              smem_desc(wb + kOffW1 + 8 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH, BF16), 1u);
       mma_commit(bar_m);
     }
     // the next item's descriptor and record are requested behind the proxy fence (which would otherwise
@@ -339,7 +351,7 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
       uint32_t acc[32];
       if (ok && warp_live) {
         tmem_ld32(trow, acc);
-        bad |= hidden_to_smem<KEEP>(acc, s_bias, s_a2, tid, relu1) && valid;
+        bad |= hidden_to_smem<KEEP, BF16>(acc, s_bias, s_a2, tid, relu1) && valid;
       }
     }
     fence_async_smem();
@@ -351,7 +363,7 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
 #pragma unroll
       for (int ks = 0; ks < kH / 16; ++ks)
         mma_f16(tmem + 32, smem_desc(a2 + ks * 2 * (kRows * 16), kRows * 16, 128),
-                smem_desc(wb + kOffW2 + ks * 2 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH), ks > 0);
+                smem_desc(wb + kOffW2 + ks * 2 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH, BF16), ks > 0);
       mma_commit(bar_m);
     }
     ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph_m) && ok);   // warp-uniform: tcgen05.ld is .sync.aligned
@@ -363,7 +375,7 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
       uint32_t acc[32];
       if (ok && warp_live) {
         tmem_ld32(trow + 32, acc);
-        bad |= hidden_to_smem<KEEP>(acc, s_bias + kH, s_a2, tid, relu2) && valid;   // layer-2 MMAs have finished reading s_a2
+        bad |= hidden_to_smem<KEEP, BF16>(acc, s_bias + kH, s_a2, tid, relu2) && valid;   // layer-2 MMAs have finished reading s_a2
       }
     }
     fence_async_smem();
@@ -375,7 +387,7 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
 #pragma unroll
       for (int ks = 0; ks < kH / 16; ++ks)
         mma_f16(tmem, smem_desc(a2 + ks * 2 * (kRows * 16), kRows * 16, 128),
-                smem_desc(wb + kOffW3 + ks * 2 * (kN3 * 16), kN3 * 16, 128), instr_desc(kRows, kN3), ks > 0);
+                smem_desc(wb + kOffW3 + ks * 2 * (kN3 * 16), kN3 * 16, 128), instr_desc(kRows, kN3, BF16), ks > 0);
       mma_commit(bar_m);
     }
     ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph_m) && ok);   // warp-uniform: tcgen05.ld is .sync.aligned
@@ -419,35 +431,45 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
 }
 
 // ------------------------------------------------------------------------------ packing ----
+template <bool BF16>
+__device__ __forceinline__ uint16_t to_lp(float x, bool& bad) {
+  if (BF16) {
+    const __nv_bfloat16 v = __float2bfloat16_rn(x);
+    bad |= __hisinf(v) || __hisnan(v);
+    return *reinterpret_cast<const uint16_t*>(&v);
+  }
+  const __half v = __float2half_rn(x);
+  bad |= __hisinf(v) || __hisnan(v);
+  return *reinterpret_cast<const uint16_t*>(&v);
+}
+
+template <bool BF16>
 __global__ void k_pack_weights(const float* __restrict__ W1, const float* __restrict__ b1, const float* __restrict__ W2,
                                const float* __restrict__ b2, const float* __restrict__ W3, const float* __restrict__ b3,
                                int n, char* __restrict__ out, int32_t* __restrict__ status) {
   const int p = blockIdx.x;
   if (p >= n) return;
   char* dst = out + (size_t)p * kWeightBytes;
-  __half* w1 = reinterpret_cast<__half*>(dst + kOffW1);
-  __half* w2 = reinterpret_cast<__half*>(dst + kOffW2);
-  __half* w3 = reinterpret_cast<__half*>(dst + kOffW3);
+  uint16_t* w1 = reinterpret_cast<uint16_t*>(dst + kOffW1);
+  uint16_t* w2 = reinterpret_cast<uint16_t*>(dst + kOffW2);
+  uint16_t* w3 = reinterpret_cast<uint16_t*>(dst + kOffW3);
   float* bias = reinterpret_cast<float*>(dst + kOffBias);
   bool bad = false;
   for (int i = threadIdx.x; i < kH * kK1; i += blockDim.x) {
     const int h = i / kK1, k = i % kK1;
-    const __half v = __float2half_rn(k < 72 ? W1[(size_t)p * kH * 72 + h * 72 + k] : 0.f);
-    bad |= __hisinf(v) || __hisnan(v);
+    const uint16_t v = to_lp<BF16>(k < 72 ? W1[(size_t)p * kH * 72 + h * 72 + k] : 0.f, bad);
     const int kk = enc_k_of_reference(k);
     const int chunk = (kk >> 3) == 8 ? 9 : ((kk >> 3) == 9 ? 8 : (kk >> 3));   // zero chunk before the last real one
     w1[chunk * (kH * 8) + h * 8 + (kk & 7)] = v;
   }
   for (int i = threadIdx.x; i < kH * kH; i += blockDim.x) {
     const int h = i / kH, k = i % kH;
-    const __half v = __float2half_rn(W2[(size_t)p * kH * kH + i]);
-    bad |= __hisinf(v) || __hisnan(v);
+    const uint16_t v = to_lp<BF16>(W2[(size_t)p * kH * kH + i], bad);
     w2[(k >> 3) * (kH * 8) + h * 8 + (k & 7)] = v;
   }
   for (int i = threadIdx.x; i < kN3 * kH; i += blockDim.x) {
     const int h = i / kH, k = i % kH;
-    const __half v = __float2half_rn(h < 4 ? W3[(size_t)p * 4 * kH + h * kH + k] : 0.f);
-    bad |= __hisinf(v) || __hisnan(v);
+    const uint16_t v = to_lp<BF16>(h < 4 ? W3[(size_t)p * 4 * kH + h * kH + k] : 0.f, bad);
     w3[(k >> 3) * (kN3 * 8) + h * 8 + (k & 7)] = v;
   }
   for (int i = threadIdx.x; i < kH; i += blockDim.x) {
@@ -461,14 +483,18 @@ __global__ void k_pack_weights(const float* __restrict__ W1, const float* __rest
 
 int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
-                   cudaStream_t st) {
+                   cudaStream_t st, bool bf16) {
   MLPSP_REQUIRE(sc->hidden == kH && sc->num_freq == 6, MLPSP_E_LIMIT,
                 "fp16 evaluator is built for the 72->32->32->4 network (hidden 32, 6 frequencies)");
-  MLPSP_REQUIRE(sc->w16 && sc->freq && sc->att, MLPSP_E_ARG, "fp16 evaluator needs the packed weight image");
+  const char* image = (const char*)(bf16 ? sc->wbf16 : sc->w16);
+  MLPSP_REQUIRE(image && sc->freq && sc->att, MLPSP_E_ARG, "%s evaluator needs the packed weight image",
+                bf16 ? "bf16" : "fp16");
   static bool attr_set = false;
   if (!attr_set) {
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attr_set = true;
   }
   int dev = 0, sms = 148;
@@ -479,12 +505,12 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   const int grid = sms * (rec_ext ? 6 : 8);   // the record-export variant keeps two more words per row
   (void)prim_off;
   LaunchScope scope(kKMlp, 1, st);
-  if (rec_ext)
-    k_mlp_tc<true><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, work,
-                                                   counters, rec_out, rec_ext, out_mode, status);
-  else
-    k_mlp_tc<false><<<grid, kRows, kSmemBytes, st>>>((const char*)sc->w16, sc->freq, sc->att, rec_in, work,
-                                                    counters, rec_out, rec_ext, out_mode, status);
+#define MLPSP_LAUNCH_TC(KEEP, BF)                                                                          \
+  k_mlp_tc<KEEP, BF><<<grid, kRows, kSmemBytes, st>>>(image, sc->freq, sc->att, rec_in, work, counters, rec_out, \
+                                                      rec_ext, out_mode, status)
+  if (rec_ext) { if (bf16) MLPSP_LAUNCH_TC(true, true); else MLPSP_LAUNCH_TC(true, false); }
+  else { if (bf16) MLPSP_LAUNCH_TC(false, true); else MLPSP_LAUNCH_TC(false, false); }
+#undef MLPSP_LAUNCH_TC
   return cuda_check(cudaGetLastError(), "mlp_f16");
 }
 
@@ -496,15 +522,26 @@ extern "C" int64_t mlpsp_packed_weight_bytes(int32_t hidden, int32_t num_freq) {
   return (hidden == kH && num_freq == 6) ? kWeightBytes : 0;
 }
 
-extern "C" int mlpsp_pack_weights_f16(const mlpsp_scene* sc, void* w16_out, int32_t* status, void* stream) {
-  MLPSP_REQUIRE(sc && w16_out, MLPSP_E_ARG, "mlpsp_pack_weights_f16: null pointer");
+static int pack_weights(const mlpsp_scene* sc, void* out, int32_t* status, void* stream, bool bf16, const char* who) {
+  MLPSP_REQUIRE(sc && out, MLPSP_E_ARG, "%s: null pointer", who);
   MLPSP_REQUIRE(sc->hidden == kH && sc->num_freq == 6, MLPSP_E_LIMIT,
-                "mlpsp_pack_weights_f16: only the 72->32->32->4 network has a packed fp16 image");
-  MLPSP_REQUIRE(sc->W1 && sc->b1 && sc->W2 && sc->b2 && sc->W3 && sc->b3, MLPSP_E_ARG,
-                "mlpsp_pack_weights_f16: FP32 weights missing");
+                "%s: only the 72->32->32->4 network has a packed image", who);
+  MLPSP_REQUIRE(sc->W1 && sc->b1 && sc->W2 && sc->b2 && sc->W3 && sc->b3, MLPSP_E_ARG, "%s: FP32 weights missing", who);
   if (sc->n == 0) return MLPSP_OK;
   LaunchScope scope(kKMisc, 1, (cudaStream_t)stream);
-  k_pack_weights<<<sc->n, 128, 0, (cudaStream_t)stream>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->n,
-                                                         (char*)w16_out, status);
-  return cuda_check(cudaGetLastError(), "pack_weights_f16");
+  if (bf16)
+    k_pack_weights<true><<<sc->n, 128, 0, (cudaStream_t)stream>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->n,
+                                                                 (char*)out, status);
+  else
+    k_pack_weights<false><<<sc->n, 128, 0, (cudaStream_t)stream>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->n,
+                                                                  (char*)out, status);
+  return cuda_check(cudaGetLastError(), who);
+}
+
+extern "C" int mlpsp_pack_weights_f16(const mlpsp_scene* sc, void* w16_out, int32_t* status, void* stream) {
+  return pack_weights(sc, w16_out, status, stream, false, "mlpsp_pack_weights_f16");
+}
+
+extern "C" int mlpsp_pack_weights_bf16(const mlpsp_scene* sc, void* wbf16_out, int32_t* status, void* stream) {
+  return pack_weights(sc, wbf16_out, status, stream, true, "mlpsp_pack_weights_bf16");
 }

@@ -713,9 +713,9 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                               s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr,
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
                               sc->gate_tau, fr->status); }
-    if (fr->precision == MLPSP_PRECISION_F16)
+    if (fr->precision == MLPSP_PRECISION_F16 || fr->precision == MLPSP_PRECISION_BF16)
       rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
-                          fr->status, st);
+                          fr->status, st, fr->precision == MLPSP_PRECISION_BF16);
     else
       rc = launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
                           fr->status, st);

@@ -90,8 +90,8 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
             raise ValueError("this build renders 8x8 tiles only")
         if initial_positions is not None:
             raise ValueError("octree initialisation from a point cloud belongs to training and is not part of this build")
-        if precision not in ("fp16", "fp32"):
-            raise ValueError("precision must be 'fp16' or 'fp32'")
+        if precision not in ("fp16", "bf16", "fp32"):
+            raise ValueError("precision must be 'fp16', 'bf16' or 'fp32'")
         self.num_primitives = int(num_primitives)
         self.hidden_dim, self.pe_frequencies = int(hidden_dim), int(pe_frequencies)
         self.use_integrated_pe, self.pe_sigma = bool(use_integrated_pe), float(pe_sigma)
@@ -184,7 +184,7 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
                     self.b1.detach(), self.W2.detach(), self.b2.detach(), self.W3.detach(), self.b3.detach(), freq, att,
                     feat_attr=None if self.feat_attr is None else self.feat_attr.detach(),
                     gate_beta=self.feature_gating_beta, gate_tau=self.feature_gating_temp, device=device,
-                    pack_f16=(self.precision == "fp16"))
+                    pack_f16=(self.precision == "fp16"), pack_bf16=(self.precision == "bf16"))
             self._packed_key = key
         return self._packed
 
@@ -233,7 +233,11 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
             bg = bg.numpy()
         view = None if lists is not None else view_matrix.detach().float().cpu().numpy()
         proj = None if lists is not None else proj_matrix.detach().float().cpu().numpy()
-        prec = L.PRECISION_F16 if (self.precision == "fp16" and scene.has_f16) else L.PRECISION_F32
+        prec = L.PRECISION_F32
+        if self.precision == "fp16" and scene.has_f16:
+            prec = L.PRECISION_F16
+        elif self.precision == "bf16" and scene.has_bf16:
+            prec = L.PRECISION_BF16
         rgb, alpha = r.render(scene, ray_o.detach().float().contiguous(), ray_d.detach().float().contiguous(),
                               float(score_threshold), view=view, proj=proj, precision=prec, bg=bg,
                               want_depth=want_depth, tile_lists=lists, path_name=path_name, want_feat=want_feat,

@@ -46,7 +46,7 @@ class PackedScene:
     """
 
     def __init__(self, positions, log_scales, quats, W1, b1, W2, b2, W3, b3, freq, att, feat_attr=None,
-                 gate_beta=1.5, gate_tau=2.0, device="cuda", pack_f16=True):
+                 gate_beta=1.5, gate_tau=2.0, device="cuda", pack_f16=True, pack_bf16=False):
         lib = L.load()
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -76,6 +76,7 @@ class PackedScene:
                 self.feat_attr, self.feat_slots, self.feat_dim = fa, int(fa.shape[1]), int(fa.shape[2])
             self.gate_beta, self.gate_tau = float(gate_beta), float(gate_tau)
             self.w16 = None
+            self.wbf16 = None
             self.f16_rejected = False
             self.c = self._struct()
             wbytes = int(lib.mlpsp_packed_weight_bytes(self.hidden, self.num_freq))
@@ -91,12 +92,22 @@ class PackedScene:
                 else:
                     self.w16 = w16
                 self.c = self._struct()
+            if pack_bf16 and wbytes > 0 and self.n > 0:
+                # the same image with bfloat16 operands (the bf16 flag of render_tiles_rgb_wmma, rgb_wmma.cuh:225)
+                wb = torch.empty(self.n * wbytes, device=d, dtype=torch.uint8)
+                st = torch.zeros(L.STATUS_WORDS, device=d, dtype=torch.int32)
+                L.check(lib.mlpsp_pack_weights_bf16(C.byref(self.c), L.ptr(wb), L.ptr(st), _stream_ptr(d)),
+                        "mlpsp_pack_weights_bf16")
+                if not (int(st[L.ST_BITS].item()) & L.BIT_NUMERIC):
+                    self.wbf16 = wb
+                self.c = self._struct()
 
     def _struct(self) -> L.Scene:
         s = L.Scene()
         s.geom, s.n, s.hidden, s.num_freq = L.ptr(self.geom), self.n, self.hidden, self.num_freq
         s.W1, s.b1, s.W2, s.b2, s.W3, s.b3 = (L.ptr(t) for t in (self.W1, self.b1, self.W2, self.b2, self.W3, self.b3))
         s.w16 = L.ptr(self.w16)
+        s.wbf16 = L.ptr(self.wbf16)
         s.freq, s.att = L.ptr(self.freq), L.ptr(self.att)
         s.feat_attr, s.feat_slots, s.feat_dim = L.ptr(self.feat_attr), self.feat_slots, self.feat_dim
         s.gate_beta, s.gate_tau = self.gate_beta, self.gate_tau
@@ -106,8 +117,12 @@ class PackedScene:
     def has_f16(self) -> bool:
         return self.w16 is not None
 
+    @property
+    def has_bf16(self) -> bool:
+        return self.wbf16 is not None
+
     def parameter_bytes(self) -> int:
-        ts = [self.geom, self.W1, self.b1, self.W2, self.b2, self.W3, self.b3, self.w16, self.feat_attr]
+        ts = [self.geom, self.W1, self.b1, self.W2, self.b2, self.W3, self.b3, self.w16, self.wbf16, self.feat_attr]
         return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
 
@@ -339,7 +354,7 @@ class FrameRenderer:
                     raise_for_status(bits, stats.max_tile_len, self.capacity, path_name)
                 if self._grow(bits, stats):
                     continue
-                if (bits & L.BIT_NUMERIC) and precision == L.PRECISION_F16:
+                if (bits & L.BIT_NUMERIC) and precision in (L.PRECISION_F16, L.PRECISION_BF16):
                     # operand/activation overflow in binary16: render the whole frame again in scalar
                     # FP32, as the reference does (rgb_wmma.cuh:260-272)
                     self.f32_fallbacks += 1

@@ -86,6 +86,19 @@ static inline float f16_round(float x) {
 }
 float orc_f16_round(float x) { return f16_round(x); }
 
+/* round-to-nearest-even float -> bfloat16 -> float (the top 16 bits of the binary32 pattern) */
+static inline float bf16_round(float x) {
+  union { float f; uint32_t u; } v = { x };
+  if ((v.u & 0x7fffffffu) >= 0x7f800000u) return x;     /* inf / nan */
+  const uint32_t rem = v.u & 0xffffu;
+  v.u &= 0xffff0000u;
+  if (rem > 0x8000u || (rem == 0x8000u && (v.u & 0x10000u))) v.u += 0x10000u;   /* may carry into inf: correct */
+  return v.f;
+}
+float orc_bf16_round(float x) { return bf16_round(x); }
+/* operand rounding of the tensor-core contract: precision 1 = binary16, 2 = bfloat16 (rgb_wmma.cuh:23-73) */
+static inline float lp_round(float x, int precision) { return precision == 2 ? bf16_round(x) : f16_round(x); }
+
 /* ------------------------------------------------------------------------ geometry ---- */
 typedef struct { float x, y, z; } v3;
 
@@ -477,27 +490,28 @@ static void mlp_eval(const mlp_t* m, int p, const float v6[6], mlp_out* o) {
       out[c] = a;
     }
   } else {
-    /* tensor-core contract: operands rounded to binary16, FP32 accumulate from zero over
-     * ascending k, FP32 bias added afterwards, hidden activations re-rounded to binary16 */
+    /* tensor-core contract: operands rounded to binary16 (precision 1) or bfloat16 (precision 2), FP32
+     * accumulate from zero over ascending k, FP32 bias added afterwards, hidden activations re-rounded */
+    const int pr = m->precision;
     float e16[2 * 6 * ORC_MAXF];
-    for (int j = 0; j < IN; ++j) e16[j] = f16_round(enc[j]);
+    for (int j = 0; j < IN; ++j) e16[j] = lp_round(enc[j], pr);
     for (int h = 0; h < H; ++h) {
       float a = 0.f;
-      for (int j = 0; j < IN; ++j) a = fmaf(f16_round(W1[h * IN + j]), e16[j], a);
+      for (int j = 0; j < IN; ++j) a = fmaf(lp_round(W1[h * IN + j], pr), e16[j], a);
       a = a + b1[h];
       if (a > 0.f && h < 32) m1 |= 1u << h;
-      h1[h] = f16_round(fmaxf(a, 0.f));
+      h1[h] = lp_round(fmaxf(a, 0.f), pr);
     }
     for (int q = 0; q < H; ++q) {
       float a = 0.f;
-      for (int h = 0; h < H; ++h) a = fmaf(f16_round(W2[q * H + h]), h1[h], a);
+      for (int h = 0; h < H; ++h) a = fmaf(lp_round(W2[q * H + h], pr), h1[h], a);
       a = a + b2[q];
       if (a > 0.f && q < 32) m2 |= 1u << q;
-      h2[q] = f16_round(fmaxf(a, 0.f));
+      h2[q] = lp_round(fmaxf(a, 0.f), pr);
     }
     for (int c = 0; c < 4; ++c) {
       float a = 0.f;
-      for (int h = 0; h < H; ++h) a = fmaf(f16_round(W3[c * H + h]), h2[h], a);
+      for (int h = 0; h < H; ++h) a = fmaf(lp_round(W3[c * H + h], pr), h2[h], a);
       out[c] = a + b3[c];
     }
   }

@@ -633,3 +633,26 @@ def test_contribution_statistics_match_oracle(dev, name):
     np.testing.assert_allclose(m.stat_sum_w.cpu().numpy(), 2 * st["sum_w"], rtol=1e-4, atol=2e-4)
     m.reset_w_stats()
     assert int(m.stat_hits.sum()) == 0 and float(m.stat_max_w.max()) == 0.0
+
+
+@pytest.mark.parametrize("name", ["tiny", "dense"])
+def test_bf16_operands_match_oracle_model(dev, name):
+    """bfloat16 operands on the same tcgen05 kernel (the bf16 flag of render_tiles_rgb_wmma, rgb_wmma.cuh:225):
+    against the oracle's bf16 operand model, and loosely against the FP32 frame (bf16 keeps 8 mantissa bits)."""
+    from mlp_splatting_b200 import _lib as L
+    from mlp_splatting_b200.engine import PackedScene
+    scene, cam = small_case(**CASES[name])
+    f = oracle_frame(scene, cam, 5e-3, precision=2, want_masks=False)
+    f32 = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    ps = PackedScene(scene["positions"], scene["log_scales"], scene["quats"], *[scene[k] for k in WKEYS],
+                     scene["freq"], scene["att"], device=dev, pack_f16=False, pack_bf16=True)
+    assert ps.has_bf16 and not ps.has_f16
+    r = _renderer(cam, dev)
+    rgb, alpha = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, view=cam["view"], proj=cam["proj"],
+                          precision=L.PRECISION_BF16)
+    got = rgb.cpu().numpy()
+    d_model = np.abs(got - f["render"].rgb)
+    d_f32 = np.abs(got - f32["render"].rgb)
+    assert d_model.max() <= 1.5e-2 and d_model.mean() <= 3e-4, (d_model.max(), d_model.mean())
+    assert d_f32.max() <= 5e-2 and d_f32.mean() <= 2e-3, (d_f32.max(), d_f32.mean())
+    assert r.f32_fallbacks == 0

@@ -159,3 +159,21 @@ def test_contribution_statistics_match_reference_kernel(ref):
     assert (s2[3] - hits).abs().sum().item() <= max(2, int(2e-4 * hits.sum().item()))
     assert (s2[5] - cc).abs().sum().item() <= max(2, int(1e-3 * cc.sum().item()))
     assert hits.sum().item() > 1000
+
+
+def test_bf16_forward_matches_reference_wmma_kernel(ref):
+    """render_tiles_rgb_wmma with bf16=True (rgb_wmma.cuh:225) vs the bfloat16 operand mode of this library."""
+    from mlp_splatting_b200 import _lib as L
+    from mlp_splatting_b200.engine import PackedScene
+    dev = torch.device("cuda", 0)
+    scene, cam = small_case(**CASES["tiny"])
+    f = oracle_frame(scene, cam, 5e-3, precision=2, want_masks=False)
+    x = _inputs(scene, cam, f, dev)
+    rgb_r, alpha_r = ref.render_tiles_rgb_wmma(x, cam["W"], cam["H"], 5e-3, True)
+    ps = PackedScene(scene["positions"], scene["log_scales"], scene["quats"], *[scene[k] for k in WKEYS],
+                     scene["freq"], scene["att"], device=dev, pack_f16=False, pack_bf16=True)
+    r = _renderer(cam, dev)
+    rgb, alpha = r.render(ps, x[0], x[1], 5e-3, precision=L.PRECISION_BF16, tile_lists=(x[5], x[6]), rays_normalized=True)
+    d = (rgb - rgb_r).abs()
+    assert d.max().item() <= 1.5e-2 and d.mean().item() <= 3e-4, (d.max().item(), d.mean().item())
+    assert (alpha - alpha_r).abs().max().item() <= 1.5e-2
