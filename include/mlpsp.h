@@ -271,6 +271,32 @@ int mlpsp_prepare_groups_static(const int64_t* offsets, int32_t n, int64_t segme
                                 int64_t* primitives, int64_t* starts, int64_t max_groups,
                                 int64_t* num_groups_host, void* stream);
 
+/* ---- backward side of the record path (training callers) ---- */
+
+/* Reverse compositing over saved records: primitive_records_reverse (scannet/cuda/primitive_records.cuh:3-74).
+ * ids[R], offsets[pixels+1] (int64, pixel-major records in compositing order), x6[R,6], raw[R,8] as written by
+ * mlpsp_export_records; log_scales[n,3], quats[n,4] (unit); grad_rgb[pixels,3], grad_t[pixels] (adjoint of the
+ * final transmittance).  Writes d4[R,4] (adjoints of the four pre-activation MLP outputs) and the position /
+ * log-scale / quaternion gradients [n,3] [n,3] [n,4], which are zeroed first. */
+int mlpsp_records_reverse(const int32_t* ids, const int64_t* offsets, const float* x6, const float* raw,
+                          const float* log_scales, const float* quats, const float* grad_rgb, const float* grad_t,
+                          int64_t pixels, int32_t n, float* d4, float* grad_pos, float* grad_log_scales,
+                          float* grad_quats, void* stream);
+
+/* Floats per primitive of the packed gradient row: W1[32,72] b1[32] W2[32,32] b2[32] W3[4,32] b3[4] = 3,524. */
+int64_t mlpsp_grouped_gradient_floats(void);
+
+/* Per-primitive MLP weight gradients from primitive-major records: grouped_weight_gradients in its FP32 operand
+ * mode (scannet/primitive_gemm.py:101-279; the PyTorch statement is scannet/primitive_csr.py:33-58).
+ * offsets[n+1] / x6[R,6] / d4[R,4] / relu_masks[R,2] (or NULL: signs are recomputed) are a PrimitiveCSR; seg_prim,
+ * seg_start [G] and seg_offsets [n+1] are a prepared group layout (mlpsp_prepare_groups) with segment_size records
+ * per segment.  partial [G, 3524] is scratch; result [n, 3524]; *nonfinite becomes 1 when a sum is not finite.
+ * loss_scale multiplies the adjoints before and divides the sums after (1 for FP32). */
+int mlpsp_grouped_weight_gradients(const mlpsp_scene* scene, const int64_t* offsets, const float* x6, const float* d4,
+                                   const int32_t* relu_masks, const int64_t* seg_prim, const int64_t* seg_start,
+                                   const int64_t* seg_offsets, int64_t num_segments, int32_t segment_size,
+                                   float loss_scale, float* partial, float* result, int32_t* nonfinite, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

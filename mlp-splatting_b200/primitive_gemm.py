@@ -117,3 +117,82 @@ def grouped_forward(csr_offsets, x6, scene, *, dtype=torch.float16):
     if bits & L.BIT_NUMERIC:
         raise RuntimeError("grouped_forward: non-finite operand or activation in the fp16 evaluator")
     return out
+
+
+# ---- grouped backward: per-primitive weight gradients (scannet/primitive_gemm.py:52-279) ----
+_SAFETY_STATS = {"calls": 0, "mixed_calls": 0, "fp32_fallbacks": 0, "fp32_nonfinite_failures": 0}
+
+
+def get_grouped_vjp_safety_stats(*, reset=False):
+    """Process-local counters for run reports; resetting is explicit (primitive_gemm.py:55-62)."""
+    snapshot = dict(_SAFETY_STATS)
+    if reset:
+        for key in _SAFETY_STATS:
+            _SAFETY_STATS[key] = 0
+    return snapshot
+
+
+@torch.no_grad()
+def grouped_weight_gradients(csr, freq, attenuation, weights, *, dtype=torch.float16, segment_size=512, block_size=32,
+                             loss_scale=None, groups=None):
+    """[dW1, db1, dW2, db2, dW3, db3] of the 72->32->32->4 per-primitive MLP from primitive-major records.
+
+    Same arguments, checks and error texts as the reference function.  This build evaluates every operand dtype
+    in IEEE FP32 (the reference's float32 mode): float16 / bfloat16 requests are accepted and are
+    at least as accurate as the reference's mixed modes are required to be; loss_scale is applied and removed
+    as there.  A non-finite sum raises FloatingPointError and no gradients are returned."""
+    import math
+    w1, b1, w2, b2, w3, b3 = weights
+    n = len(w1)
+    if [tuple(w.shape[1:]) for w in weights] != [(32, 72), (32,), (32, 32), (32,), (4, 32), (4,)]:
+        raise ValueError("grouped backward requires the 72→32→32→4 architecture")
+    if any(len(w) != n for w in weights) or csr.offsets.numel() != n + 1:
+        raise ValueError("CSR offsets and all master tensors must have the same primitive count")
+    if csr.x6.ndim != 2 or csr.x6.shape[1] != 6 or csr.grad4.shape != (len(csr.x6), 4):
+        raise ValueError("CSR inputs/adjoints must have shapes (records,6) and (records,4)")
+    if freq.numel() != 6 or attenuation.numel() != 6:
+        raise ValueError("grouped backward requires six positional frequencies")
+    if dtype not in [torch.float32, torch.float16, torch.bfloat16]:
+        raise ValueError("unsupported GEMM operand dtype")
+    if block_size not in (32, 64) or segment_size <= 0 or segment_size % block_size:
+        raise ValueError("segment size must be a positive multiple of the 32/64-row block")
+    for tensor in [csr.offsets, csr.x6, csr.grad4, freq, attenuation, *weights]:
+        if not tensor.is_cuda or not tensor.is_contiguous() or tensor.device != w1.device:
+            raise ValueError("all inputs must be contiguous tensors on one CUDA device")
+    if any(t.dtype != torch.float32 for t in [csr.x6, csr.grad4, freq, attenuation, *weights]):
+        raise ValueError("master weights, records and encoding parameters must be FP32")
+    if csr.relu_masks is not None and (
+            csr.relu_masks.dtype != torch.int32 or not csr.relu_masks.is_contiguous()
+            or csr.relu_masks.device != w1.device or csr.relu_masks.shape != (len(csr.x6), 2)):
+        raise ValueError("saved ReLU masks must be contiguous CUDA int32 with shape (records,2)")
+    groups = resolve_groups(csr, segment_size, groups)
+    scale = float(4096 if dtype == torch.float16 else 1) if loss_scale is None else float(loss_scale)
+    if not math.isfinite(scale) or scale <= 0:
+        raise ValueError("loss_scale must be finite and strictly positive")
+    _SAFETY_STATS["calls"] += 1
+    _SAFETY_STATS["mixed_calls"] += int(dtype != torch.float32)
+    lib = L.load()
+    dev = w1.device
+    glen = int(lib.mlpsp_grouped_gradient_floats())
+    G = int(groups.primitives.numel())
+    partial = torch.empty((max(G, 1), glen), device=dev, dtype=torch.float32)
+    result = torch.empty((n, glen), device=dev, dtype=torch.float32)
+    nonfinite = torch.zeros((), device=dev, dtype=torch.int32)
+    sc = L.Scene()
+    sc.n, sc.hidden, sc.num_freq = n, 32, 6
+    sc.W1, sc.b1, sc.W2, sc.b2, sc.W3, sc.b3 = (L.ptr(t) for t in weights)
+    sc.freq, sc.att = L.ptr(freq), L.ptr(attenuation)
+    with torch.cuda.device(dev):
+        st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        L.check(lib.mlpsp_grouped_weight_gradients(
+            C.byref(sc), L.ptr(csr.offsets), L.ptr(csr.x6), L.ptr(csr.grad4), L.ptr(csr.relu_masks), L.ptr(groups.primitives),
+            L.ptr(groups.starts), L.ptr(groups.offsets), G, int(segment_size), scale, L.ptr(partial), L.ptr(result),
+            L.ptr(nonfinite), st), "mlpsp_grouped_weight_gradients")
+    if bool(nonfinite.item()):
+        _SAFETY_STATS["fp32_nonfinite_failures"] += 1
+        raise FloatingPointError(
+            "[CSR safety] IEEE FP32 MLP VJP is nonfinite; no gradients were returned "
+            "and Adam must not step. Inspect the saved model, records and loss. "
+            f"Safety counters: {get_grouped_vjp_safety_stats()}")
+    sizes = [2304, 32, 1024, 32, 128, 4]
+    return [v.reshape(w.shape).contiguous() for v, w in zip(result.split(sizes, dim=1), weights)]

@@ -15,6 +15,8 @@ Only device-agnostic reference functions are called, on CPU:
   scannet.checkpoints.make_inference_checkpoint, restore_scene_state_dict,
   infer_scene_spec on a wrapped training state with prefixes, old MLP names and five feature slots
                                                                               -> checkpoint.pt
+  scannet.primitive_csr.reference_weight_gradients; torch autograd through the compositing formulas
+                                                                              -> backward.npz
 The scene inputs come from this repository's seeded generator, so tests can rebuild them.
 """
 import os
@@ -156,8 +158,94 @@ def checkpoint_fixture(ref_root):
                os.path.join(HERE, "checkpoint.pt"))
 
 
+def backward_fixtures(ref_root):
+    """backward.npz: (1) per-primitive weight gradients from the reference's own PyTorch statement
+    (scannet.primitive_csr.reference_weight_gradients) on the record counts its test uses
+    (tests/test_primitive_csr.py:91-134); (2) reverse compositing adjoints by torch autograd through the
+    compositing and decay formulas (np_tile_kernels.cu:659-711, 2025-2136), the independent check of
+    primitive_records_reverse."""
+    sys.path.insert(0, ref_root)
+    from scannet.primitive_csr import PrimitiveCSR, reference_weight_gradients
+    from scannet.cumodel import _encode_x6
+    out = {}
+    g = torch.Generator().manual_seed(92)
+    counts = torch.tensor([0, 1, 31, 32, 33, 511, 512, 513, 1700, 0])
+    ids = torch.repeat_interleave(torch.arange(10, dtype=torch.int32), counts)
+    R = int(ids.numel())
+    x6 = torch.randn((R, 6), generator=g) * .2
+    d3 = torch.randn((R, 4), generator=g)
+    freq = 2. ** torch.arange(6, dtype=torch.float32)
+    att = torch.exp(-.5 * freq.square() * 1.e-4)
+    weights = [torch.randn((10, *shape), generator=g) * .1 for shape in [(32, 72), (32,), (32, 32), (32,), (4, 32), (4,)]]
+    offsets = torch.cat((counts.new_zeros(1), counts.cumsum(0))).to(torch.int64)
+    masks = torch.zeros((R, 2), dtype=torch.int32)
+    bit = 1 << torch.arange(32, dtype=torch.int64)
+    for p in range(10):
+        b, e = int(offsets[p]), int(offsets[p + 1])
+        if b == e:
+            continue
+        enc = _encode_x6(x6[b:e], freq, att)
+        h1 = torch.relu(enc @ weights[0][p].T + weights[1][p])
+        h2 = torch.relu(h1 @ weights[2][p].T + weights[3][p])
+        masks[b:e, 0] = ((h1 > 0) * bit).sum(1).to(torch.int32)
+        masks[b:e, 1] = ((h2 > 0) * bit).sum(1).to(torch.int32)
+    csr = PrimitiveCSR(offsets, torch.arange(R), x6, d3, masks)
+    expected = reference_weight_gradients(csr, freq, att, weights)
+    out.update(vjp_offsets=offsets.numpy(), vjp_x6=x6.numpy(), vjp_d3=d3.numpy(), vjp_masks=masks.numpy(),
+               vjp_freq=freq.numpy(), vjp_att=att.numpy())
+    for k, w, e in zip(("W1", "b1", "W2", "b2", "W3", "b3"), weights, expected):
+        out["vjp_" + k] = w.numpy()
+        out["vjp_g" + k] = e.numpy()
+
+    # ---- reverse compositing by autograd ----
+    g = torch.Generator().manual_seed(5)
+    n, pixels = 6, 40
+    per_px = torch.randint(0, 7, (pixels,), generator=g)
+    per_px[3] = 0
+    offs = torch.cat((per_px.new_zeros(1), per_px.cumsum(0))).to(torch.int64)
+    R = int(offs[-1])
+    rid = torch.randint(0, n, (R,), generator=g).to(torch.int32)
+    logit = (torch.randn((R, 4), generator=g)).double().requires_grad_(True)
+    dvec = (torch.randn((R, 3), generator=g) * .05).double().requires_grad_(True)
+    ls = (torch.randn((n, 3), generator=g) * .3 - 3.0).double().requires_grad_(True)
+    qt = torch.randn((n, 4), generator=g).double()
+    qt = (qt / qt.norm(dim=1, keepdim=True)).requires_grad_(True)
+    grgb = torch.randn((pixels, 3), generator=g).double()
+    gt = torch.randn((pixels,), generator=g).double()
+    w_, x_, y_, z_ = qt[rid.long()].unbind(1)
+    Rm = torch.stack([1 - 2 * (y_ * y_ + z_ * z_), 2 * (x_ * y_ - w_ * z_), 2 * (x_ * z_ + w_ * y_),
+                      2 * (x_ * y_ + w_ * z_), 1 - 2 * (x_ * x_ + z_ * z_), 2 * (y_ * z_ - w_ * x_),
+                      2 * (x_ * z_ - w_ * y_), 2 * (y_ * z_ + w_ * x_), 1 - 2 * (x_ * x_ + y_ * y_)], 1).view(R, 3, 3)
+    qloc = torch.einsum("rij,ri->rj", Rm, dvec)                       # R^T d
+    m = torch.exp(-2 * ls[rid.long()])
+    decay = torch.exp(-0.5 * (qloc * qloc * m).sum(1))
+    rgbv = torch.sigmoid(logit[:, :3])
+    sraw = torch.nn.functional.softplus(logit[:, 3])
+    alpha = 1 - torch.exp(-sraw * decay)
+    loss = 0.
+    trans_before = torch.zeros(R, dtype=torch.double)
+    for px in range(pixels):
+        T = torch.ones((), dtype=torch.double)
+        C = torch.zeros(3, dtype=torch.double)
+        for r in range(int(offs[px]), int(offs[px + 1])):
+            trans_before[r] = T.detach()
+            C = C + T * alpha[r] * rgbv[r]
+            T = T * (1 - alpha[r])
+        loss = loss + (grgb[px] * C).sum() + gt[px] * T
+    loss.backward()
+    gp = torch.zeros((n, 3), dtype=torch.double).index_add_(0, rid.long(), dvec.grad)
+    raw = torch.stack([rgbv[:, 0], rgbv[:, 1], rgbv[:, 2], sraw, trans_before, alpha, decay, logit[:, 3]], 1).detach()
+    x6r = torch.cat([torch.zeros((R, 3), dtype=torch.double), dvec.detach()], 1)
+    out.update(rev_ids=rid.numpy(), rev_offsets=offs.numpy(), rev_x6=x6r.float().numpy(), rev_raw=raw.float().numpy(),
+               rev_logs=ls.detach().float().numpy(), rev_quats=qt.detach().float().numpy(),
+               rev_grgb=grgb.float().numpy(), rev_gt=gt.float().numpy(), rev_d4=logit.grad.float().numpy(),
+               rev_gp=gp.float().numpy(), rev_gs=ls.grad.float().numpy(), rev_gq=qt.grad.float().numpy())
+    np.savez_compressed(os.path.join(HERE, "backward.npz"), **out)
+
+
 if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     main(root)
     checkpoint_fixture(root)
+    backward_fixtures(root)
     main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
