@@ -28,7 +28,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WK = ("W1", "b1", "W2", "b2", "W3", "b3")
-FLOP_PER_RECORD = 6912          # 2*(72*32 + 32*32 + 32*4): algorithmic MLP work of one record
+FLOP_PER_RECORD = 6912          # 2*(72*32 + 32*32 + 32*4): algorithmic MLP work of one record (hidden 32)
+
+
+def flop_per_record(hidden):
+    return 2 * (72 * hidden + hidden * hidden + hidden * 4)     # 17,920 at hidden 64
 THRESHOLD = 5e-3                # score threshold of the reference's benchmark tool
 
 
@@ -188,7 +192,7 @@ def workload_config(name, cfg, n_gpus, encoder="integrated"):
     views = int(cfg["views"])
     return {"workload": name, "encoder": encoder, "primitives": cfg["n"], "width": cfg["W"], "height": cfg["H"], "tile": 8,
             "tile_capacity": 1536, "threshold": THRESHOLD, "log_scale_mean": cfg["mu"],
-            "mlp": "72-32-32-4 fp16 weights, fp32 accumulate", "views_per_step": n_gpus if views == 1 else views,
+            "mlp": f"72-{cfg.get('hidden', 32)}-{cfg.get('hidden', 32)}-4 fp16 weights, fp32 accumulate", "views_per_step": n_gpus if views == 1 else views,
             "feature_channels": cfg.get("feat_dim", 0),
             "parallelism": (f"one view per GPU x{n_gpus} (azimuth 90 deg x (rank mod 4))" if views == 1 else f"{views} views shared by {n_gpus} GPU(s) by view, then by tile-row band")
                            + ", scene replicated",
@@ -343,7 +347,8 @@ def main():
     pk = peaks()
     mlp_ms = classes["mlp"]["ms_per_step"]
     mlp_launch_ms = mlp_ms / max(classes["mlp"]["launches_per_step"], 1)
-    flops_step = stats.records * FLOP_PER_RECORD
+    hidden = int(cfg.get("hidden", 32))
+    flops_step = stats.records * flop_per_record(hidden)
     achieved_tf = flops_step / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0
     roofline = {"kernel": "k_mlp_tc (per-primitive MLP, tcgen05)", "bound": "tensor", "achieved": achieved_tf,
                 "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved_tf / pk["bf16_tflops"],
@@ -352,7 +357,7 @@ def main():
                 "avg_launch_ms": mlp_launch_ms, "share_of_step": mlp_ms / max(sum(c["ms_per_step"] for c in classes.values()), 1e-9)}
     # Algorithmic bytes of the evaluator: 32 B in + 16 B out per record, one 8,464-byte weight image per work item.
     n_launch = max(classes["mlp"]["launches_per_step"], 1)
-    alg_bytes = stats.records * 48 + stats.work_total * 8464
+    alg_bytes = stats.records * 48 + stats.work_total * (8464 if hidden == 32 else 21008)
     roofline["hbm_view"] = {"algorithmic_bytes_per_launch": alg_bytes / n_launch,
                             "achieved_gbs": alg_bytes / (mlp_ms / 1e3) / 1e9 if mlp_ms > 0 else 0.0,
                             "peak_gbs": pk["hbm_gbs"],

@@ -23,22 +23,30 @@
 
 namespace mlpsp {
 
-// ---- packed weight image (bytes, per primitive) for H = 32, F = 6 ----
+// ---- packed weight image (bytes, per primitive) for F = 6 and hidden width H = 32 or 64 ----
 constexpr int kK1 = 80;                  // 72 encoded inputs padded to a multiple of 16
-constexpr int kH = 32;
 constexpr int kN3 = 16;                  // 4 outputs padded to the smallest N
-constexpr int kOffW1 = 0;                // [10 k-chunks][32 rows][8 halves]: chunks 0..7 of K in the order of enc_k(),
-                                         // an all-zero chunk, then chunk 8 (see the last layer-1 MMA)
-constexpr int kOffW2 = kOffW1 + (kK1 / 8) * kH * 16;   // 5120: [4][32][8]
-constexpr int kOffW3 = kOffW2 + (kH / 8) * kH * 16;    // 7168: [4][16][8]
-constexpr int kOffBias = kOffW3 + (kH / 8) * kN3 * 16; // 8192: b1[32] b2[32] b3[4] fp32
-constexpr int kWeightBytes = kOffBias + 4 * (kH + kH + 4);  // 8464, a multiple of 16
-
 constexpr int kRows = kRowsPerItem;      // 128 = MMA M
 constexpr int kA1Bytes = 9 * kRows * 16;          // 18432: [9 k-chunks][128][8 halves], 72 encoded inputs
-constexpr int kA2Bytes = (kH / 8) * kRows * 16;   // 8192:  [4][128][8 halves]
-constexpr int kSmemBytes = kWeightBytes + kA1Bytes + 64;   // the hidden-activation tile reuses the layer-1 A tile
-constexpr int kTmemCols = 64;            // D1 [0,32)  D2 [32,64)  D3 reuses [0,16)
+
+template <int H>
+struct Net {
+  static_assert(H == 32 || H == 64, "hidden width of the tensor-core evaluator");
+  // W1: [10 k-chunks][H rows][8 halves]: chunks 0..7 of K in the order of enc_k(), an all-zero chunk, then
+  // chunk 8 (see the last layer-1 MMA); W2: [H/8][H][8]; W3: [H/8][16][8] (rows 4..15 zero); b1[H] b2[H] b3[4] FP32
+  static constexpr int kOffW1 = 0;
+  static constexpr int kOffW2 = kOffW1 + (kK1 / 8) * H * 16;
+  static constexpr int kOffW3 = kOffW2 + (H / 8) * H * 16;
+  static constexpr int kOffBias = kOffW3 + (H / 8) * kN3 * 16;
+  static constexpr int kWeightBytes = kOffBias + 4 * (H + H + 4);   // 8,464 (H = 32) / 21,008 (H = 64), multiples of 16
+  static constexpr int kA2Bytes = (H / 8) * kRows * 16;             // hidden tile, reuses the layer-1 A tile
+  static_assert(kA2Bytes <= kA1Bytes && kWeightBytes % 16 == 0, "tile aliasing / bulk-copy granularity");
+  static constexpr int kSmemBytes = kWeightBytes + kA1Bytes + 64;
+  static constexpr int kTmemCols = 2 * H;   // D1 [0,H)  D2 [H,2H)  D3 reuses [0,16)
+  // resident CTAs per SM: H = 32: shared memory (28 KB), registers (64) and tensor memory (64 columns) all give 8;
+  // H = 64: tensor memory (128 columns) gives 4
+  static constexpr int kCtas = H == 32 ? 8 : 4;
+};
 
 // -------------------------------------------------------------------------- PTX helpers ----
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -242,15 +250,17 @@ __device__ __forceinline__ bool encode_row(const RecIn& r, const float (&mult)[6
 // fetch the next item's descriptor, its record and -- as soon as the MMAs that read them have
 // finished -- the next primitive's W1 and W2 blocks while the current item is still being evaluated,
 // so the only global-memory latency left on an item's critical path is the 1.3 KB copy of W3 + biases.
-template <bool KEEP, bool BF16>
-__global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
+template <bool KEEP, bool BF16, int H>
+__global__ void __launch_bounds__(kRows, KEEP ? 6 : Net<H>::kCtas) k_mlp_tc(
     const char* __restrict__ w16, const float* __restrict__ freq, const float* __restrict__ att,
     const RecIn* __restrict__ rec_in, const int4* __restrict__ work,
     const int32_t* __restrict__ counters, float4* __restrict__ rec_out, float4* __restrict__ rec_ext, int out_mode,
     int32_t* __restrict__ status) {
+  using N = Net<H>;
+  static_assert(!KEEP || H == 32, "the record export keeps 32-bit ReLU masks");
   extern __shared__ __align__(128) char smem[];
   char* s_w = smem;
-  char* s_a1 = smem + kWeightBytes;          // 8464 is a multiple of 16
+  char* s_a1 = smem + N::kWeightBytes;
   char* s_a2 = s_a1;                         // written only after the layer-1 MMAs have finished reading s_a1
   uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_a1 + kA1Bytes);   // [0] weights, [1] mma
   uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2);        // [0] tmem base
@@ -268,10 +278,10 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
     // the first item's whole weight image
-    mbar_expect_tx(bar_w, kWeightBytes);
-    bulk_g2s(wb, w16 + (size_t)wk.x * kWeightBytes, kWeightBytes, bar_w);
+    mbar_expect_tx(bar_w, N::kWeightBytes);
+    bulk_g2s(wb, w16 + (size_t)wk.x * N::kWeightBytes, N::kWeightBytes, bar_w);
   }
-  if (warp == 0) tmem_alloc(smem_u32(&s_misc[0]), kTmemCols);
+  if (warp == 0) tmem_alloc(smem_u32(&s_misc[0]), N::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -285,7 +295,7 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
   for (int f = 0; f < 6; ++f) mult[f] = __ldg(freq + f) * __ldg(att + f);
 #pragma unroll
   for (int f = 1; f < 6; ++f) ladder = ladder && mult[f] == 2.0f * mult[f - 1];
-  const float* s_bias = reinterpret_cast<const float*>(s_w + kOffBias);
+  const float* s_bias = reinterpret_cast<const float*>(s_w + N::kOffBias);
   uint32_t ph_w = 0, ph_m = 0;
   bool ok = true, bad = false, copy_pending = true;
   uint32_t relu1 = 0u, relu2 = 0u;
@@ -326,11 +336,11 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         mma_f16(tmem, smem_desc(a1 + ks * 2 * (kRows * 16), kRows * 16, 128),
-                smem_desc(wb + kOffW1 + ks * 2 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH, BF16), ks > 0);
+                smem_desc(wb + N::kOffW1 + ks * 2 * (H * 16), H * 16, 128), instr_desc(kRows, H, BF16), ks > 0);
       // K = 64..79: the weight image holds a zero chunk and then chunk 8; the A operand pairs them with
       // chunk 7 (any finite values: they meet zeros) and chunk 8, so no padded A chunk is stored
       mma_f16(tmem, smem_desc(a1 + 7 * (kRows * 16), kRows * 16, 128),
-              smem_desc(wb + kOffW1 + 8 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH, BF16), 1u);
+              smem_desc(wb + N::kOffW1 + 8 * (H * 16), H * 16, 128), instr_desc(kRows, H, BF16), 1u);
       mma_commit(bar_m);
     }
     // the next item's descriptor and record are requested behind the proxy fence (which would otherwise
@@ -343,15 +353,16 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
     if (tid < wk_next.z) r = rec_in[wk_next.y + tid];
     if (tid == 0 && has_next && ok) {
       // W1 is no longer read: start the next primitive's image with its W1 block
-      mbar_expect_tx(bar_w, kWeightBytes);
-      bulk_g2s(wb + kOffW1, w16 + (size_t)wk_next.x * kWeightBytes + kOffW1, kOffW2 - kOffW1, bar_w);
+      mbar_expect_tx(bar_w, N::kWeightBytes);
+      bulk_g2s(wb + N::kOffW1, w16 + (size_t)wk_next.x * N::kWeightBytes + N::kOffW1, N::kOffW2 - N::kOffW1, bar_w);
     }
     if (has_next && ok) copy_pending = true;
-    {
-      uint32_t acc[32];
-      if (ok && warp_live) {
-        tmem_ld32(trow, acc);
-        bad |= hidden_to_smem<KEEP, BF16>(acc, s_bias, s_a2, tid, relu1) && valid;
+    if (ok && warp_live) {
+#pragma unroll
+      for (int part = 0; part < H / 32; ++part) {       // 32 accumulator columns = 4 K-chunks of the hidden tile at a time
+        uint32_t acc[32];
+        tmem_ld32(trow + part * 32, acc);
+        bad |= hidden_to_smem<KEEP, BF16>(acc, s_bias + part * 32, s_a2 + part * 4 * (kRows * 16), tid, relu1) && valid;
       }
     }
     fence_async_smem();
@@ -361,21 +372,22 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
-      for (int ks = 0; ks < kH / 16; ++ks)
-        mma_f16(tmem + 32, smem_desc(a2 + ks * 2 * (kRows * 16), kRows * 16, 128),
-                smem_desc(wb + kOffW2 + ks * 2 * (kH * 16), kH * 16, 128), instr_desc(kRows, kH, BF16), ks > 0);
+      for (int ks = 0; ks < H / 16; ++ks)
+        mma_f16(tmem + H, smem_desc(a2 + ks * 2 * (kRows * 16), kRows * 16, 128),
+                smem_desc(wb + N::kOffW2 + ks * 2 * (H * 16), H * 16, 128), instr_desc(kRows, H, BF16), ks > 0);
       mma_commit(bar_m);
     }
     ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph_m) && ok);   // warp-uniform: tcgen05.ld is .sync.aligned
     ph_m ^= 1u;
     tc_fence_after();
     if (tid == 0 && has_next && ok)
-      bulk_g2s(wb + kOffW2, w16 + (size_t)wk_next.x * kWeightBytes + kOffW2, kOffW3 - kOffW2, bar_w);
-    {
-      uint32_t acc[32];
-      if (ok && warp_live) {
-        tmem_ld32(trow + 32, acc);
-        bad |= hidden_to_smem<KEEP, BF16>(acc, s_bias + kH, s_a2, tid, relu2) && valid;   // layer-2 MMAs have finished reading s_a2
+      bulk_g2s(wb + N::kOffW2, w16 + (size_t)wk_next.x * N::kWeightBytes + N::kOffW2, N::kOffW3 - N::kOffW2, bar_w);
+    if (ok && warp_live) {                              // layer-2 MMAs have finished reading s_a2
+#pragma unroll
+      for (int part = 0; part < H / 32; ++part) {
+        uint32_t acc[32];
+        tmem_ld32(trow + H + part * 32, acc);
+        bad |= hidden_to_smem<KEEP, BF16>(acc, s_bias + H + part * 32, s_a2 + part * 4 * (kRows * 16), tid, relu2) && valid;
       }
     }
     fence_async_smem();
@@ -385,9 +397,9 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
-      for (int ks = 0; ks < kH / 16; ++ks)
+      for (int ks = 0; ks < H / 16; ++ks)
         mma_f16(tmem, smem_desc(a2 + ks * 2 * (kRows * 16), kRows * 16, 128),
-                smem_desc(wb + kOffW3 + ks * 2 * (kN3 * 16), kN3 * 16, 128), instr_desc(kRows, kN3, BF16), ks > 0);
+                smem_desc(wb + N::kOffW3 + ks * 2 * (kN3 * 16), kN3 * 16, 128), instr_desc(kRows, kN3, BF16), ks > 0);
       mma_commit(bar_m);
     }
     ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph_m) && ok);   // warp-uniform: tcgen05.ld is .sync.aligned
@@ -397,8 +409,8 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
       uint32_t o[4];
       tmem_ld4(trow, o);
       if (valid) {
-        const float o0 = __uint_as_float(o[0]) + s_bias[2 * kH + 0], o1 = __uint_as_float(o[1]) + s_bias[2 * kH + 1];
-        const float o2 = __uint_as_float(o[2]) + s_bias[2 * kH + 2], o3 = __uint_as_float(o[3]) + s_bias[2 * kH + 3];
+        const float o0 = __uint_as_float(o[0]) + s_bias[2 * H + 0], o1 = __uint_as_float(o[1]) + s_bias[2 * H + 1];
+        const float o2 = __uint_as_float(o[2]) + s_bias[2 * H + 2], o3 = __uint_as_float(o[3]) + s_bias[2 * H + 3];
         const float sigma_raw = softplus_fast(o3);
         float4 out;
         out.x = sigmoid_fast(o0); out.y = sigmoid_fast(o1); out.z = sigmoid_fast(o2);
@@ -412,7 +424,7 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
     if (!__syncthreads_and(ok)) { ok = false; break; }
     if (!has_next) break;
     if (tid == 0)
-      bulk_g2s(wb + kOffW3, w16 + (size_t)wk_next.x * kWeightBytes + kOffW3, kWeightBytes - kOffW3, bar_w);
+      bulk_g2s(wb + N::kOffW3, w16 + (size_t)wk_next.x * N::kWeightBytes + N::kOffW3, N::kWeightBytes - N::kOffW3, bar_w);
     item = next;
     wk = wk_next;
   }
@@ -427,7 +439,7 @@ __global__ void __launch_bounds__(kRows, KEEP ? 6 : 8) k_mlp_tc(
   if (bad) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_NUMERIC);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_free(tmem, kTmemCols);
+  if (warp == 0) tmem_free(tmem, N::kTmemCols);
 }
 
 // ------------------------------------------------------------------------------ packing ----
@@ -443,75 +455,92 @@ __device__ __forceinline__ uint16_t to_lp(float x, bool& bad) {
   return *reinterpret_cast<const uint16_t*>(&v);
 }
 
-template <bool BF16>
+template <bool BF16, int H>
 __global__ void k_pack_weights(const float* __restrict__ W1, const float* __restrict__ b1, const float* __restrict__ W2,
                                const float* __restrict__ b2, const float* __restrict__ W3, const float* __restrict__ b3,
                                int n, char* __restrict__ out, int32_t* __restrict__ status) {
   const int p = blockIdx.x;
   if (p >= n) return;
-  char* dst = out + (size_t)p * kWeightBytes;
-  uint16_t* w1 = reinterpret_cast<uint16_t*>(dst + kOffW1);
-  uint16_t* w2 = reinterpret_cast<uint16_t*>(dst + kOffW2);
-  uint16_t* w3 = reinterpret_cast<uint16_t*>(dst + kOffW3);
-  float* bias = reinterpret_cast<float*>(dst + kOffBias);
+  using N = Net<H>;
+  char* dst = out + (size_t)p * N::kWeightBytes;
+  uint16_t* w1 = reinterpret_cast<uint16_t*>(dst + N::kOffW1);
+  uint16_t* w2 = reinterpret_cast<uint16_t*>(dst + N::kOffW2);
+  uint16_t* w3 = reinterpret_cast<uint16_t*>(dst + N::kOffW3);
+  float* bias = reinterpret_cast<float*>(dst + N::kOffBias);
   bool bad = false;
-  for (int i = threadIdx.x; i < kH * kK1; i += blockDim.x) {
+  for (int i = threadIdx.x; i < H * kK1; i += blockDim.x) {
     const int h = i / kK1, k = i % kK1;
-    const uint16_t v = to_lp<BF16>(k < 72 ? W1[(size_t)p * kH * 72 + h * 72 + k] : 0.f, bad);
+    const uint16_t v = to_lp<BF16>(k < 72 ? W1[(size_t)p * H * 72 + h * 72 + k] : 0.f, bad);
     const int kk = enc_k_of_reference(k);
     const int chunk = (kk >> 3) == 8 ? 9 : ((kk >> 3) == 9 ? 8 : (kk >> 3));   // zero chunk before the last real one
-    w1[chunk * (kH * 8) + h * 8 + (kk & 7)] = v;
+    w1[chunk * (H * 8) + h * 8 + (kk & 7)] = v;
   }
-  for (int i = threadIdx.x; i < kH * kH; i += blockDim.x) {
-    const int h = i / kH, k = i % kH;
-    const uint16_t v = to_lp<BF16>(W2[(size_t)p * kH * kH + i], bad);
-    w2[(k >> 3) * (kH * 8) + h * 8 + (k & 7)] = v;
+  for (int i = threadIdx.x; i < H * H; i += blockDim.x) {
+    const int h = i / H, k = i % H;
+    const uint16_t v = to_lp<BF16>(W2[(size_t)p * H * H + i], bad);
+    w2[(k >> 3) * (H * 8) + h * 8 + (k & 7)] = v;
   }
-  for (int i = threadIdx.x; i < kN3 * kH; i += blockDim.x) {
-    const int h = i / kH, k = i % kH;
-    const uint16_t v = to_lp<BF16>(h < 4 ? W3[(size_t)p * 4 * kH + h * kH + k] : 0.f, bad);
+  for (int i = threadIdx.x; i < kN3 * H; i += blockDim.x) {
+    const int h = i / H, k = i % H;
+    const uint16_t v = to_lp<BF16>(h < 4 ? W3[(size_t)p * 4 * H + h * H + k] : 0.f, bad);
     w3[(k >> 3) * (kN3 * 8) + h * 8 + (k & 7)] = v;
   }
-  for (int i = threadIdx.x; i < kH; i += blockDim.x) {
-    bias[i] = b1[(size_t)p * kH + i];
-    bias[kH + i] = b2[(size_t)p * kH + i];
-    bad |= !isfinite(bias[i]) || !isfinite(bias[kH + i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    bias[i] = b1[(size_t)p * H + i];
+    bias[H + i] = b2[(size_t)p * H + i];
+    bad |= !isfinite(bias[i]) || !isfinite(bias[H + i]);
   }
-  if (threadIdx.x < 4) { bias[2 * kH + threadIdx.x] = b3[(size_t)p * 4 + threadIdx.x]; bad |= !isfinite(bias[2 * kH + threadIdx.x]); }
+  if (threadIdx.x < 4) { bias[2 * H + threadIdx.x] = b3[(size_t)p * 4 + threadIdx.x]; bad |= !isfinite(bias[2 * H + threadIdx.x]); }
   if (bad && status) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_NUMERIC);
 }
 
-int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
-                   const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
-                   cudaStream_t st, bool bf16) {
-  MLPSP_REQUIRE(sc->hidden == kH && sc->num_freq == 6, MLPSP_E_LIMIT,
-                "fp16 evaluator is built for the 72->32->32->4 network (hidden 32, 6 frequencies)");
-  const char* image = (const char*)(bf16 ? sc->wbf16 : sc->w16);
-  MLPSP_REQUIRE(image && sc->freq && sc->att, MLPSP_E_ARG, "%s evaluator needs the packed weight image",
-                bf16 ? "bf16" : "fp16");
+template <int H>
+static int launch_tc(const mlpsp_scene* sc, const char* image, const RecIn* rec_in, const int4* work,
+                     const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
+                     cudaStream_t st, bool bf16) {
+  using N = Net<H>;
   static bool attr_set = false;
   if (!attr_set) {
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<false, false, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, N::kSmemBytes));
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<false, true, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, N::kSmemBytes));
+    if (H == 32) {
+      MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<true, false, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, Net<32>::kSmemBytes));
+      MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<true, true, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, Net<32>::kSmemBytes));
+    }
     attr_set = true;
   }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // tensor memory: 512 columns per SM / 64 per CTA = at most 8 resident CTAs; shared memory
-  // (8 x 28 KB) and registers (64 per thread) allow the same 8
-  const int grid = sms * (rec_ext ? 6 : 8);   // the record-export variant keeps two more words per row
-  (void)prim_off;
+  const int grid = sms * (rec_ext ? 6 : N::kCtas);   // the record-export variant keeps two more words per row
   LaunchScope scope(kKMlp, 1, st);
-#define MLPSP_LAUNCH_TC(KEEP, BF)                                                                          \
-  k_mlp_tc<KEEP, BF><<<grid, kRows, kSmemBytes, st>>>(image, sc->freq, sc->att, rec_in, work, counters, rec_out, \
-                                                      rec_ext, out_mode, status)
-  if (rec_ext) { if (bf16) MLPSP_LAUNCH_TC(true, true); else MLPSP_LAUNCH_TC(true, false); }
-  else { if (bf16) MLPSP_LAUNCH_TC(false, true); else MLPSP_LAUNCH_TC(false, false); }
-#undef MLPSP_LAUNCH_TC
+  if (rec_ext) {
+    MLPSP_REQUIRE(H == 32, MLPSP_E_LIMIT, "record export needs hidden width 32 (32-bit ReLU masks)");
+    if (bf16) k_mlp_tc<true, true, 32><<<grid, kRows, Net<32>::kSmemBytes, st>>>(image, sc->freq, sc->att, rec_in, work, counters,
+                                                                               rec_out, rec_ext, out_mode, status);
+    else k_mlp_tc<true, false, 32><<<grid, kRows, Net<32>::kSmemBytes, st>>>(image, sc->freq, sc->att, rec_in, work, counters,
+                                                                            rec_out, rec_ext, out_mode, status);
+  } else {
+    if (bf16) k_mlp_tc<false, true, H><<<grid, kRows, N::kSmemBytes, st>>>(image, sc->freq, sc->att, rec_in, work, counters,
+                                                                          rec_out, rec_ext, out_mode, status);
+    else k_mlp_tc<false, false, H><<<grid, kRows, N::kSmemBytes, st>>>(image, sc->freq, sc->att, rec_in, work, counters,
+                                                                       rec_out, rec_ext, out_mode, status);
+  }
   return cuda_check(cudaGetLastError(), "mlp_f16");
+}
+
+int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
+                   const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
+                   cudaStream_t st, bool bf16) {
+  MLPSP_REQUIRE((sc->hidden == 32 || sc->hidden == 64) && sc->num_freq == 6, MLPSP_E_LIMIT,
+                "the tensor-core evaluator is built for 72->H->H->4 networks with H = 32 or 64 (6 frequencies)");
+  const char* image = (const char*)(bf16 ? sc->wbf16 : sc->w16);
+  MLPSP_REQUIRE(image && sc->freq && sc->att, MLPSP_E_ARG, "%s evaluator needs the packed weight image",
+                bf16 ? "bf16" : "fp16");
+  (void)prim_off;
+  if (sc->hidden == 64)
+    return launch_tc<64>(sc, image, rec_in, work, counters, rec_out, rec_ext, out_mode, status, st, bf16);
+  return launch_tc<32>(sc, image, rec_in, work, counters, rec_out, rec_ext, out_mode, status, st, bf16);
 }
 
 }  // namespace mlpsp
@@ -519,22 +548,23 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
 using namespace mlpsp;
 
 extern "C" int64_t mlpsp_packed_weight_bytes(int32_t hidden, int32_t num_freq) {
-  return (hidden == kH && num_freq == 6) ? kWeightBytes : 0;
+  if (num_freq != 6) return 0;
+  return hidden == 32 ? Net<32>::kWeightBytes : (hidden == 64 ? Net<64>::kWeightBytes : 0);
 }
 
 static int pack_weights(const mlpsp_scene* sc, void* out, int32_t* status, void* stream, bool bf16, const char* who) {
   MLPSP_REQUIRE(sc && out, MLPSP_E_ARG, "%s: null pointer", who);
-  MLPSP_REQUIRE(sc->hidden == kH && sc->num_freq == 6, MLPSP_E_LIMIT,
-                "%s: only the 72->32->32->4 network has a packed image", who);
+  MLPSP_REQUIRE((sc->hidden == 32 || sc->hidden == 64) && sc->num_freq == 6, MLPSP_E_LIMIT,
+                "%s: only 72->H->H->4 networks with H = 32 or 64 have a packed image", who);
   MLPSP_REQUIRE(sc->W1 && sc->b1 && sc->W2 && sc->b2 && sc->W3 && sc->b3, MLPSP_E_ARG, "%s: FP32 weights missing", who);
   if (sc->n == 0) return MLPSP_OK;
-  LaunchScope scope(kKMisc, 1, (cudaStream_t)stream);
-  if (bf16)
-    k_pack_weights<true><<<sc->n, 128, 0, (cudaStream_t)stream>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->n,
-                                                                 (char*)out, status);
-  else
-    k_pack_weights<false><<<sc->n, 128, 0, (cudaStream_t)stream>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->n,
-                                                                  (char*)out, status);
+  cudaStream_t st = (cudaStream_t)stream;
+  LaunchScope scope(kKMisc, 1, st);
+#define MLPSP_PACK(BF, HH)                                                                                         \
+  k_pack_weights<BF, HH><<<sc->n, 128, 0, st>>>(sc->W1, sc->b1, sc->W2, sc->b2, sc->W3, sc->b3, sc->n, (char*)out, status)
+  if (sc->hidden == 64) { if (bf16) MLPSP_PACK(true, 64); else MLPSP_PACK(false, 64); }
+  else { if (bf16) MLPSP_PACK(true, 32); else MLPSP_PACK(false, 32); }
+#undef MLPSP_PACK
   return cuda_check(cudaGetLastError(), who);
 }
 

@@ -89,6 +89,8 @@ WORKLOADS = {
     "feature_250k_1200x680": dict(n=250_000, W=1200, H=680, mu=-4.8, views=1, seed=2028, feat_dim=512),
     "fourview_500k_1200x680": dict(n=500_000, W=1200, H=680, mu=-5.2, views=4, seed=2029),
     "stress_2m_1920x1080": dict(n=2_000_000, W=1920, H=1080, mu=-6.4, views=32, seed=2030, hidden=32),
+    # the stress configuration's 64-wide hidden layers on a scene whose FP32 masters (36 KB per primitive) stay small
+    "hidden64_250k_1200x680": dict(n=250_000, W=1200, H=680, mu=-4.8, views=1, seed=2031, hidden=64),
 }
 
 

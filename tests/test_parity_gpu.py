@@ -656,3 +656,23 @@ def test_bf16_operands_match_oracle_model(dev, name):
     assert d_model.max() <= 1.5e-2 and d_model.mean() <= 3e-4, (d_model.max(), d_model.mean())
     assert d_f32.max() <= 5e-2 and d_f32.mean() <= 2e-3, (d_f32.max(), d_f32.mean())
     assert r.f32_fallbacks == 0
+
+
+def test_hidden_64_tensor_core_evaluator(dev):
+    """72-64-64-4 networks (the stress configuration's width; the reference itself stops at 32) on the tcgen05
+    evaluator: against the CPU restatement's fp16 operand model and the FP32 frame."""
+    from mlp_splatting_b200 import _lib as L
+    scene, cam = small_case(**dict(CASES["tiny"], hidden=64))
+    f16 = oracle_frame(scene, cam, 5e-3, precision=1, want_masks=False)
+    f32 = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    ps, r = _packed(scene, dev, pack_f16=True), _renderer(cam, dev)
+    assert ps.has_f16 and ps.hidden == 64
+    ro, rd = _t(cam["rays_o"], dev), _t(cam["rays_d"], dev)
+    rgb, alpha = r.render(ps, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"], precision=L.PRECISION_F16)
+    got = rgb.cpu().numpy()
+    assert np.abs(got - f16["render"].rgb).max() <= 1e-3
+    assert np.abs(got - f32["render"].rgb).max() <= IMG_TOL_F16
+    assert np.abs(alpha.cpu().numpy()[:, 0] - f16["render"].alpha).max() <= 1e-3
+    rgb32, _ = r.render(ps, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"], precision=L.PRECISION_F32)
+    np.testing.assert_allclose(rgb32.cpu().numpy(), f32["render"].rgb, atol=IMG_TOL_F32)
+    assert r.f32_fallbacks == 0
