@@ -127,7 +127,9 @@ typedef struct mlpsp_frame {
                              it is skipped when mask_used is requested, so that those masks stay aligned with the
                              full sorted lists.  1 = never drop.  With the test on, sorted_prims holds the kept
                              candidates of every tile in depth order followed by -1 entries. */
-  int32_t reserved1;
+  int32_t tail_hint;      /* 1 = the last wave is expected to find no work (a host that carries the wave schedule
+                             from frame to frame knows): its kernels are launched with one CTA per SM instead of
+                             full grids.  Whatever work it does find is still done; only its speed changes. */
   /* Per-primitive contribution statistics of render_tiles_kernel_tilecenter_stats (np_tile_kernels.cu:2143-2500),
    * all NULL or all set; the five [n] arrays are accumulated into, never reset.  With w = trans * alpha of a
    * composited record: sum_w += w; max_w = max(max_w, w); hits += (w > 1e-8); for w > 0.1: contrib += 1 and

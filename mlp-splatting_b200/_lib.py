@@ -47,7 +47,7 @@ class Frame(C.Structure):
         ("status", _fp), ("num_waves", C.c_int32), ("wave_len", C.c_int32 * MAX_WAVES),
         ("keep_records", C.c_int32), ("sort_key", C.c_int32),
         ("tile_row_begin", C.c_int32), ("tile_row_end", C.c_int32),
-        ("tile_pretest", C.c_int32), ("reserved1", C.c_int32),
+        ("tile_pretest", C.c_int32), ("tail_hint", C.c_int32),
         ("gt_rgb", _fp), ("stat_sum_w", _fp), ("stat_max_w", _fp), ("stat_hits", _fp), ("stat_sum_werr", _fp),
         ("stat_contrib", _fp),
     ]

@@ -86,6 +86,19 @@ __device__ __forceinline__ float ab_terms(const Geom& g, V3 o, V3 d, float& nume
   return denom;
 }
 
+// ab_terms with the local-frame offset vl = R^T (c - o) supplied by the caller: for rays that share one origin it
+// is the same three numbers for every ray, bit for bit, whichever thread computes them.
+__device__ __forceinline__ float ab_terms_vl(const Geom& g, V3 vl, V3 d, float& numer) {
+  const V3 dl = rot_conj(g.qw, g.qx, g.qy, g.qz, d);
+  const float denom = ffma(fmul(dl.x, dl.x), g.mx, ffma(fmul(dl.y, dl.y), g.my, fmul(fmul(dl.z, dl.z), g.mz)));
+  numer = ffma(fmul(dl.x, vl.x), g.mx, ffma(fmul(dl.y, vl.y), g.my, fmul(fmul(dl.z, vl.z), g.mz)));
+  return denom;
+}
+__device__ __forceinline__ V3 local_offset(const Geom& g, V3 o) {
+  V3 v = { fsub(g.cx, o.x), fsub(g.cy, o.y), fsub(g.cz, o.z) };
+  return rot_conj(g.qw, g.qx, g.qy, g.qz, v);
+}
+
 // Tile-centre ordering key (np_tile_kernels.cu:483-518): t* on the tile-centre ray, 1e30 when the
 // ray is degenerate for this primitive or t* <= 0.
 __device__ __forceinline__ float tile_key(const Geom& g, V3 o, V3 d) {
@@ -106,10 +119,12 @@ __device__ __forceinline__ float tile_key_euclid(const Geom& g, V3 o, V3 d) {
 
 struct Hit { float t, dx, dy, dz, qx, qy, qz, decay; };
 
-// Rotated-ellipsoid closest approach (np_tile_kernels.cu:659-711).
-__device__ __forceinline__ bool hit_test(const Geom& g, V3 o, V3 d, float thr, Hit& h) {
+// Rotated-ellipsoid closest approach (np_tile_kernels.cu:659-711).  HAVE_VL: vl = local_offset(g, o) comes from
+// the caller (same operations, same bits).
+template <bool HAVE_VL>
+__device__ __forceinline__ bool hit_test_t(const Geom& g, V3 o, V3 d, V3 vl, float thr, Hit& h) {
   float numer;
-  const float denom = ab_terms(g, o, d, numer);
+  const float denom = HAVE_VL ? ab_terms_vl(g, vl, d, numer) : ab_terms(g, o, d, numer);
   if (denom <= 1e-20f) return false;
   const float t = fdiv(numer, denom);
   if (!(t > 0.f)) return false;
@@ -123,6 +138,9 @@ __device__ __forceinline__ bool hit_test(const Geom& g, V3 o, V3 d, float thr, H
   const float decay = det_exp(fmul(-0.5f, r2));
   h.t = t; h.dx = dd.x; h.dy = dd.y; h.dz = dd.z; h.qx = q.x; h.qy = q.y; h.qz = q.z; h.decay = decay;
   return decay > thr;
+}
+__device__ __forceinline__ bool hit_test(const Geom& g, V3 o, V3 d, float thr, Hit& h) {
+  return hit_test_t<false>(g, o, d, V3{0.f, 0.f, 0.f}, thr, h);
 }
 
 // The same geometry for a pair that is already known to hit: t, the offset c - p, its local-frame image

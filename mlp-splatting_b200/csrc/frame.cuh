@@ -154,13 +154,14 @@ int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mas
 int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, cudaStream_t st,
                          bool lists_refined = false);
 // rec_ext (optional): per record (sigma_raw, sigma_logit, layer-1 ReLU bitmask, layer-2 ReLU bitmask)
+// grid_cap > 0 limits the number of CTAs (a wave that is expected to be idle)
 int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
-                   cudaStream_t st);
+                   cudaStream_t st, int grid_cap = 0);
 // bf16: bfloat16 operands (sc->wbf16) instead of binary16 (sc->w16)
 int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
-                   cudaStream_t st, bool bf16 = false);
+                   cudaStream_t st, bool bf16 = false, int grid_cap = 0);
 int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cudaStream_t st);
 int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, int64_t* offsets, int32_t* ids,
                           float* x6, float* raw, int32_t* relu_masks, float* gates, int64_t max_out, int32_t max_hits,

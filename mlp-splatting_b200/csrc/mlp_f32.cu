@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(kRowsPerItem) k_mlp_f32_std(
 
 int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
-                   cudaStream_t st) {
+                   cudaStream_t st, int grid_cap) {
   const int H = sc->hidden, F = sc->num_freq;
   MLPSP_REQUIRE(H >= 1 && H <= 64 && F >= 1 && F <= 8, MLPSP_E_LIMIT, "FP32 evaluator needs 1<=H<=64, 1<=F<=8");
   MLPSP_REQUIRE(sc->W1 && sc->b1 && sc->W2 && sc->b2 && sc->W3 && sc->b3 && sc->freq && sc->att, MLPSP_E_ARG,
@@ -210,7 +210,7 @@ int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int grid = sms * 8;
+  const int grid = grid_cap > 0 ? std::min(grid_cap, sms * 8) : sms * 8;
   int32_t* ctr = const_cast<int32_t*>(counters);
   LaunchScope scope(kKMlp, 1, st);
   if (H == kSH && F == kSF) {

@@ -98,18 +98,41 @@ __global__ void __launch_bounds__(256) k_hits(
     o = load3(rays_o, tp.pix); d = load3(rays_d, tp.pix);
     act = px_state[tp.pix].w >= MLPSP_TERM;
   }
-  for (int i = wlo + (warp >> 1); i < whi; i += 4) {
-    const int p = sorted_prims[s + i];
-    bool hit = false;
-    if (act && p >= 0 && p < n) {
-      const Geom g = load_geom(geom, p);
-      if (!surely_misses(g, o, d, bound2)) {
-        Hit h;
-        hit = hit_test(g, o, d, thr, h);
-      }
+  // The 32 rays of this warp normally leave one origin; then R^T (c - o) is a per-candidate constant, computed by
+  // one lane per candidate for a batch of 32 candidates and handed round by shuffles (same operations on the
+  // same inputs: same bits as computing it in every lane).
+  const uint32_t vmask = __ballot_sync(0xffffffffu, tp.valid);
+  V3 o0 = o;
+  bool uni = false;
+  if (vmask) {
+    const int src = __ffs(vmask) - 1;
+    o0.x = __shfl_sync(0xffffffffu, o.x, src); o0.y = __shfl_sync(0xffffffffu, o.y, src); o0.z = __shfl_sync(0xffffffffu, o.z, src);
+    uni = __all_sync(0xffffffffu, !tp.valid || (o.x == o0.x && o.y == o0.y && o.z == o0.z));
+  }
+  for (int b0 = wlo + (warp >> 1); b0 < whi; b0 += 128) {
+    const int il = b0 + 4 * lane;
+    int pl = -1;
+    V3 vll = {0.f, 0.f, 0.f};
+    if (il < whi) {
+      pl = sorted_prims[s + il];
+      if (uni && pl >= 0 && pl < n) vll = local_offset(load_geom(geom, pl), o0);
     }
-    const uint32_t m = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) s_m[half][i - wlo] = m;
+    const int cnt = min(32, (whi - b0 + 3) >> 2);
+    for (int t = 0; t < cnt; ++t) {
+      const int i = b0 + 4 * t;
+      const int p = __shfl_sync(0xffffffffu, pl, t);
+      const V3 vl = {__shfl_sync(0xffffffffu, vll.x, t), __shfl_sync(0xffffffffu, vll.y, t), __shfl_sync(0xffffffffu, vll.z, t)};
+      bool hit = false;
+      if (act && p >= 0 && p < n) {
+        const Geom g = load_geom(geom, p);
+        if (!surely_misses(g, o, d, bound2)) {
+          Hit h;
+          hit = uni ? hit_test_t<true>(g, o, d, vl, thr, h) : hit_test_t<false>(g, o, d, vl, thr, h);
+        }
+      }
+      const uint32_t m = __ballot_sync(0xffffffffu, hit);
+      if (lane == 0) s_m[half][i - wlo] = m;
+    }
   }
   __syncthreads();
   int running = 0;
@@ -698,37 +721,42 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     int hi = (wl >= fr->tile_capacity - lo || w == nw - 1) ? fr->tile_capacity : lo + wl;
     MLPSP_REQUIRE(hi - lo <= kWinMax, MLPSP_E_LIMIT, "wave window beyond %d candidates", kWinMax);
     const int cur = w & 1, nxt = cur ^ 1;
+    // a last wave the caller expects to be idle: one CTA per SM walks whatever is left
+    const bool idle_tail = fr->tail_hint == 1 && hi == fr->tile_capacity && w > 0;
+    const int grid_hits = idle_tail ? sms : wave_grid;
+    const int grid_comp = idle_tail ? sms : std::min(T, sms * 32);
+    const int cap_mlp = idle_tail ? sms : 0;
     const int32_t* act = s.active[cur];
     const int32_t* act_n = s.counters + kCtrActive0 + cur;
     { LaunchScope scope(kKHits, 1, st);
-    k_hits<<<wave_grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+    k_hits<<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
                               s.prim_cnt, s.counters, fr->max_records, fr->status); }
     int rc = launch_prim_scan(s, n, nxt, fr->status, st);
     if (rc) return rc;
     { LaunchScope scope(kKFill, 1, st);
-    k_fill<<<wave_grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+    k_fill<<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
                               s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr,
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
                               sc->gate_tau, fr->status); }
     if (fr->precision == MLPSP_PRECISION_F16 || fr->precision == MLPSP_PRECISION_BF16)
       rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
-                          fr->status, st, fr->precision == MLPSP_PRECISION_BF16);
+                          fr->status, st, fr->precision == MLPSP_PRECISION_BF16, cap_mlp);
     else
       rc = launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
-                          fr->status, st);
+                          fr->status, st, cap_mlp);
     if (rc) return rc;
     { LaunchScope scope(kKComposite, 1, st);
     if (want_stats)
-      k_composite<true><<<std::min(T, sms * 32), 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+      k_composite<true><<<grid_comp, 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
                                   fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
                                   keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,
                                   s.active[nxt], s.counters + kCtrActive0 + nxt, fr->status);
     else
-    k_composite<false><<<std::min(T, sms * 32), 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+    k_composite<false><<<grid_comp, 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
                                   fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
                                   keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,

@@ -209,7 +209,7 @@ class FrameRenderer:
 
     def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
                want_mask_used, waves, want_feat=False, keep_records=False, sort_key=0, tile_rows=None,
-               tile_pretest=True, prim_stats=None) -> L.Frame:
+               tile_pretest=True, prim_stats=None, tail_hint=False) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
         f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
@@ -246,6 +246,7 @@ class FrameRenderer:
         f.keep_records = 1 if keep_records else 0
         f.sort_key = int(sort_key)
         f.tile_pretest = 0 if tile_pretest else 1
+        f.tail_hint = 1 if tail_hint else 0
         if prim_stats is not None:
             gt, sum_w, max_w, hits, sum_werr, contrib = prim_stats
             f.gt_rgb, f.stat_sum_w, f.stat_max_w = L.ptr(gt), L.ptr(sum_w), L.ptr(max_w)
@@ -337,7 +338,7 @@ class FrameRenderer:
                             "mlpsp_validate_tile_lists")
                 f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves,
                                 want_feat=want_feat, keep_records=keep_records, sort_key=sort_key, tile_rows=tile_rows,
-                                tile_pretest=tile_pretest, prim_stats=prim_stats)
+                                tile_pretest=tile_pretest, prim_stats=prim_stats, tail_hint=auto and waves is not None)
                 self._last_frame = (f, scene)
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")
