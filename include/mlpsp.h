@@ -299,6 +299,39 @@ int mlpsp_grouped_weight_gradients(const mlpsp_scene* scene, const int64_t* offs
                                    const int64_t* seg_offsets, int64_t num_segments, int32_t segment_size,
                                    float loss_scale, float* partial, float* result, int32_t* nonfinite, void* stream);
 
+/* ---- the step after the feature map: feature decoder and text query ---- */
+
+/* The reference's FeatureUpsampleDecoder (scannet/feature_decoder.py:5-19): conv 1x1 -> ReLU -> conv 3x3 (zero
+ * padding 1) -> ReLU -> conv 1x1, weights in torch Conv2d layout (device pointers, FP32):
+ * W1 [hidden, in_dim] (net.0), W2 [hidden, hidden, 3, 3] (net.2), W3 [out_dim, hidden] (net.4).
+ * text [num_classes, out_dim] are the (unnormalised) text embeddings of a query, or NULL. */
+typedef struct mlpsp_decoder {
+  int32_t in_dim, hidden, out_dim, num_classes;
+  const float *W1, *b1, *W2, *b2, *W3, *b3;
+  const float* text;
+} mlpsp_decoder;
+
+/* Bytes of the packed binary16 image of a decoder (0: sizes outside the limits: in_dim <= 128, hidden 32 / 64 /
+ * 96 / 128, at most 768 outputs or classes).  mode 0: the image computes the decoded features; mode 1: the last
+ * layer is folded with the normalised text embeddings (text^ W3, text^ b3) and the image computes class scores. */
+int64_t mlpsp_decoder_packed_bytes(const mlpsp_decoder* dec, int32_t mode);
+int mlpsp_pack_decoder(const mlpsp_decoder* dec, int32_t mode, void* packed, int32_t* status, void* stream);
+
+/* Run the decoder over a pixel-major feature map feat [height*width, in_dim] (what mlpsp_render_frame writes into
+ * frame.feat) on the tensor cores: binary16 operands, FP32 accumulation, FP32 bias (the contract of the
+ * tensor-core MLP).  mode 0 writes out [height*width, out_dim] = decoder(feat) (feature_decoder.py:18-19 with the
+ * permutes of eval_lseg_table2.py:1221-1225 folded away); mode 1 writes labels [height*width] (int64) =
+ * _classify_feature_map(decoder(feat), text) (eval_lseg_table2.py:622-641) without forming the wide map.
+ * Inputs or activations beyond binary16 range raise MLPSP_ST_NUMERIC in status. */
+int mlpsp_decode_features(const mlpsp_decoder* dec, int32_t mode, const void* packed, const float* feat,
+                          int32_t width, int32_t height, float* out, int64_t* labels, int32_t* status, void* stream);
+
+/* Text query of a full-width feature map in FP32: _classify_feature_map (eval_lseg_table2.py:622-641), for scenes
+ * whose rendered feature already has the text embedding's width (no decoder, eval_lseg_table2.py:754-755).
+ * feat [pixels, dim], text [num_classes, dim], labels [pixels] (int64); dim <= 1024, num_classes <= 1024. */
+int mlpsp_classify_features(const float* feat, int64_t pixels, int32_t dim, const float* text, int32_t num_classes,
+                            int64_t* labels, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

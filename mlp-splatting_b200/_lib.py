@@ -53,6 +53,11 @@ class Frame(C.Structure):
     ]
 
 
+class Decoder(C.Structure):
+    _fields_ = [("in_dim", C.c_int32), ("hidden", C.c_int32), ("out_dim", C.c_int32), ("num_classes", C.c_int32),
+                ("W1", _fp), ("b1", _fp), ("W2", _fp), ("b2", _fp), ("W3", _fp), ("b3", _fp), ("text", _fp)]
+
+
 _SIGS = {
     "mlpsp_last_error": (C.c_char_p, []),
     "mlpsp_abi_version": (C.c_int, []),
@@ -66,6 +71,10 @@ _SIGS = {
     "mlpsp_grouped_gradient_floats": (C.c_int64, []),
     "mlpsp_grouped_weight_gradients": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64, C.c_int32,
                                                  C.c_float, _fp, _fp, _fp, _fp]),
+    "mlpsp_decoder_packed_bytes": (C.c_int64, [C.POINTER(Decoder), C.c_int32]),
+    "mlpsp_pack_decoder": (C.c_int, [C.POINTER(Decoder), C.c_int32, _fp, _fp, _fp]),
+    "mlpsp_decode_features": (C.c_int, [C.POINTER(Decoder), C.c_int32, _fp, _fp, C.c_int32, C.c_int32, _fp, _fp, _fp, _fp]),
+    "mlpsp_classify_features": (C.c_int, [_fp, C.c_int64, C.c_int32, _fp, C.c_int32, _fp, _fp]),
     "mlpsp_status_reset": (C.c_int, [_fp, _fp]),
     "mlpsp_kernel_launches": (C.c_int, [C.POINTER(C.c_int64), C.c_int32]),
     "mlpsp_timing_enable": (C.c_int, [C.c_int32]),

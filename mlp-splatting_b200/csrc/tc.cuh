@@ -34,7 +34,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 // bounded wait: false when the phase did not complete within kWaitLimitNs
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
   const unsigned long long t0 = global_ns();
   do {
     if (mbar_try(bar, parity)) return true;

@@ -113,6 +113,27 @@ class PackedScene:
         s.gate_beta, s.gate_tau = self.gate_beta, self.gate_tau
         return s
 
+    def with_text_query(self, text_feature) -> "PackedScene":
+        """A view of this scene whose per-primitive features are projected onto the normalised text embeddings
+        text_feature [C, feat_dim]: feat_attr' = feat_attr . text^T, [n, S, C].  Compositing is linear in the
+        features, so the feature map rendered from the view is the map of class scores f . t^_c, and its
+        per-pixel arg-max equals _classify_feature_map on the full-width map (scannet/eval_lseg_table2.py:622-641;
+        the per-pixel normalisation there is one positive factor).  Geometry and MLP weights are shared."""
+        import copy
+        if self.feat_attr is None:
+            raise RuntimeError("Scene has no semantic feature branch (feat_attr).")
+        t = _dev_f32(text_feature, self.device)
+        if t.ndim != 2 or int(t.shape[1]) != self.feat_dim:
+            raise ValueError(f"Feature dim mismatch between rendered feature ({self.feat_dim}) and text embedding "
+                             f"({int(t.shape[1]) if t.ndim == 2 else tuple(t.shape)}).")
+        tn = t / t.norm(dim=1, keepdim=True).clamp_min(1e-12)
+        view = copy.copy(self)
+        with torch.cuda.device(self.device):
+            view.feat_attr = torch.matmul(self.feat_attr, tn.t()).contiguous()
+        view.feat_dim = int(t.shape[0])
+        view.c = view._struct()
+        return view
+
     @property
     def has_f16(self) -> bool:
         return self.w16 is not None

@@ -102,3 +102,30 @@ def make_workload(name, **overrides):
     views = cfg["views"]
     cams = [make_camera(cfg["W"], cfg["H"], azimuth_deg=360.0 * v / views) for v in range(views)]
     return scene, cams, cfg
+
+
+def make_decoder(in_dim, hidden, out_dim, num_classes=0, seed=0):
+    """Seeded weights of a 1x1 -> 3x3 -> 1x1 feature decoder in torch Conv2d layout (uniform +-1/sqrt(fan_in), the
+    scale of torch's default initialisation) and, with num_classes > 0, text embeddings [num_classes, out_dim]."""
+    rng = np.random.default_rng(seed)
+
+    def u(shape, fan_in):
+        b = 1.0 / np.sqrt(fan_in)
+        return rng.uniform(-b, b, size=shape).astype(np.float32)
+
+    w = {"net.0.weight": u((hidden, in_dim, 1, 1), in_dim), "net.0.bias": u((hidden,), in_dim),
+         "net.2.weight": u((hidden, hidden, 3, 3), hidden * 9), "net.2.bias": u((hidden,), hidden * 9),
+         "net.4.weight": u((out_dim, hidden, 1, 1), hidden), "net.4.bias": u((out_dim,), hidden)}
+    text = rng.normal(0.0, 1.0, size=(num_classes, out_dim)).astype(np.float32) if num_classes > 0 else None
+    return w, text
+
+
+def make_feature_map(width, height, dim, seed=0, scale=0.5):
+    """Seeded low-dimensional feature map [height, width, dim] with smooth structure plus noise."""
+    rng = np.random.default_rng(seed)
+    yy, xx = np.meshgrid(np.arange(height, dtype=np.float32), np.arange(width, dtype=np.float32), indexing="ij")
+    ph = rng.uniform(0, 6.28, size=(dim,)).astype(np.float32)
+    fx = rng.uniform(0.02, 0.3, size=(dim,)).astype(np.float32)
+    fy = rng.uniform(0.02, 0.3, size=(dim,)).astype(np.float32)
+    base = np.sin(xx[..., None] * fx + yy[..., None] * fy + ph)
+    return (scale * (base + 0.3 * rng.normal(size=base.shape))).astype(np.float32)

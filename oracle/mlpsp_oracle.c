@@ -688,3 +688,105 @@ int orc_num_threads(void) {
   return 1;
 #endif
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * Feature decoder and text query: the step that follows the feature map.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Conv 1x1 -> ReLU -> conv 3x3 (zero padding 1) -> ReLU -> conv 1x1 (scannet/feature_decoder.py:5-19), on a
+ * pixel-major map x[H][W][Cin] as the renderer writes it (the reference permutes to NCHW first,
+ * scannet/eval_lseg_table2.py:1221-1225).  Weights in torch Conv2d layout: W1 [Ch][Cin], W2 [Ch][Ch][3][3],
+ * W3 [Cout][Ch].  precision 0: FP32 throughout; 1 / 2: inputs, weights and hidden activations rounded to
+ * binary16 / bfloat16, FP32 accumulation from zero, FP32 bias added afterwards (the tensor-core contract of
+ * scannet/cuda/rgb_wmma.cuh:75-223 applied to this network).  out[H*W][Cout]. */
+void orc_decode_features(const float* x, int W, int H, int Cin, int Ch, int Cout,
+                         const float* W1, const float* b1, const float* W2, const float* b2,
+                         const float* W3, const float* b3, int precision, float* out) {
+  const int64_t P = (int64_t)W * H;
+  float* h1 = (float*)malloc(sizeof(float) * (size_t)P * Ch);
+  float* h2 = (float*)malloc(sizeof(float) * (size_t)P * Ch);
+  float* w1 = (float*)malloc(sizeof(float) * (size_t)Ch * Cin);
+  float* w2 = (float*)malloc(sizeof(float) * (size_t)Ch * Ch * 9);
+  float* w3 = (float*)malloc(sizeof(float) * (size_t)Cout * Ch);
+  for (int64_t i = 0; i < (int64_t)Ch * Cin; ++i) w1[i] = precision ? lp_round(W1[i], precision) : W1[i];
+  for (int64_t i = 0; i < (int64_t)Ch * Ch * 9; ++i) w2[i] = precision ? lp_round(W2[i], precision) : W2[i];
+  for (int64_t i = 0; i < (int64_t)Cout * Ch; ++i) w3[i] = precision ? lp_round(W3[i], precision) : W3[i];
+#pragma omp parallel for schedule(static)
+  for (int64_t p = 0; p < P; ++p) {
+    for (int j = 0; j < Ch; ++j) {
+      float acc = 0.0f;
+      for (int k = 0; k < Cin; ++k) {
+        const float v = precision ? lp_round(x[p * Cin + k], precision) : x[p * Cin + k];
+        acc += v * w1[(int64_t)j * Cin + k];
+      }
+      acc += b1[j];
+      acc = acc > 0.0f ? acc : 0.0f;
+      h1[p * Ch + j] = precision ? lp_round(acc, precision) : acc;
+    }
+  }
+#pragma omp parallel for schedule(static)
+  for (int64_t p = 0; p < P; ++p) {
+    const int py = (int)(p / W), px = (int)(p % W);
+    for (int j = 0; j < Ch; ++j) {
+      float acc = 0.0f;
+      for (int dy = -1; dy <= 1; ++dy) {
+        const int y = py + dy;
+        if (y < 0 || y >= H) continue;
+        for (int dx = -1; dx <= 1; ++dx) {
+          const int xx = px + dx;
+          if (xx < 0 || xx >= W) continue;
+          const float* hrow = h1 + ((int64_t)y * W + xx) * Ch;
+          const float* wrow = w2 + (int64_t)j * Ch * 9 + (dy + 1) * 3 + (dx + 1);
+          for (int k = 0; k < Ch; ++k) acc += hrow[k] * wrow[(int64_t)k * 9];
+        }
+      }
+      acc += b2[j];
+      acc = acc > 0.0f ? acc : 0.0f;
+      h2[p * Ch + j] = precision ? lp_round(acc, precision) : acc;
+    }
+  }
+#pragma omp parallel for schedule(static)
+  for (int64_t p = 0; p < P; ++p) {
+    for (int j = 0; j < Cout; ++j) {
+      float acc = 0.0f;
+      for (int k = 0; k < Ch; ++k) acc += h2[p * Ch + k] * w3[(int64_t)j * Ch + k];
+      out[p * Cout + j] = acc + b3[j];
+    }
+  }
+  free(h1); free(h2); free(w1); free(w2); free(w3);
+}
+
+/* Text query of a feature map (scannet/eval_lseg_table2.py:622-641): rows of both sides divided by
+ * max(||row||, 1e-12) (torch.nn.functional.normalize), logits = feature . text, label = index of the first
+ * maximum.  margin (optional) = best logit - second best (0 with a single class). */
+void orc_classify_features(const float* feat, int64_t P, int D, const float* text, int C,
+                           int64_t* labels, float* margin) {
+  float* tn = (float*)malloc(sizeof(float) * (size_t)C * D);
+  for (int c = 0; c < C; ++c) {
+    double s = 0.0;
+    for (int k = 0; k < D; ++k) s += (double)text[(int64_t)c * D + k] * text[(int64_t)c * D + k];
+    float nrm = (float)sqrt(s);
+    if (nrm < 1e-12f) nrm = 1e-12f;
+    for (int k = 0; k < D; ++k) tn[(int64_t)c * D + k] = text[(int64_t)c * D + k] / nrm;
+  }
+#pragma omp parallel for schedule(static)
+  for (int64_t p = 0; p < P; ++p) {
+    const float* f = feat + p * D;
+    double s = 0.0;
+    for (int k = 0; k < D; ++k) s += (double)f[k] * f[k];
+    float nrm = (float)sqrt(s);
+    if (nrm < 1e-12f) nrm = 1e-12f;
+    float best = 0.0f, second = 0.0f;
+    int arg = -1;
+    for (int c = 0; c < C; ++c) {
+      float acc = 0.0f;
+      for (int k = 0; k < D; ++k) acc += (f[k] / nrm) * tn[(int64_t)c * D + k];
+      if (arg < 0) { best = acc; arg = c; second = -3.0e38f; }
+      else if (acc > best) { second = best; best = acc; arg = c; }
+      else if (acc > second) second = acc;
+    }
+    labels[p] = arg;
+    if (margin) margin[p] = C > 1 ? best - second : 0.0f;
+  }
+  free(tn);
+}

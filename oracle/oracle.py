@@ -289,3 +289,34 @@ def prepare_groups(offsets, segment_size=512):
     local = np.arange(primitives.size, dtype=np.int64) - group_offsets[primitives]
     starts = offsets[primitives] + local * segment_size
     return primitives, starts, group_offsets
+
+
+def decode_features(x_hwc, weights, precision=0):
+    """FeatureUpsampleDecoder on a pixel-major map x [H, W, Cin] (scannet/feature_decoder.py:5-19).
+    weights: dict with net.0/2/4 .weight/.bias in torch Conv2d layout (numpy).  Returns [H, W, Cout] float32.
+    precision 1 / 2: binary16 / bfloat16 operands and hidden activations, FP32 accumulation."""
+    x = _f32(x_hwc)
+    H, W, Cin = x.shape
+    W1, b1 = _f32(weights["net.0.weight"]).reshape(-1, Cin), _f32(weights["net.0.bias"])
+    Ch = W1.shape[0]
+    W2, b2 = _f32(weights["net.2.weight"]).reshape(Ch, Ch, 3, 3), _f32(weights["net.2.bias"])
+    W3, b3 = _f32(weights["net.4.weight"]).reshape(-1, Ch), _f32(weights["net.4.bias"])
+    Cout = W3.shape[0]
+    out = np.empty((H, W, Cout), np.float32)
+    lib().orc_decode_features(_p(x), C.c_int(W), C.c_int(H), C.c_int(Cin), C.c_int(Ch), C.c_int(Cout),
+                              _p(W1), _p(b1), _p(W2), _p(b2), _p(W3), _p(b3), C.c_int(precision), _p(out))
+    return out
+
+
+def classify_features(feat, text):
+    """_classify_feature_map (scannet/eval_lseg_table2.py:622-641) on feat [..., D] and text [C, D].
+    Returns (labels int64 [...], margin float32 [...] = best cosine logit - second best)."""
+    f = _f32(feat)
+    t = _f32(text)
+    D = f.shape[-1]
+    P = f.size // D
+    labels = np.empty(P, np.int64)
+    margin = np.empty(P, np.float32)
+    lib().orc_classify_features(_p(f), C.c_int64(P), C.c_int(D), _p(t), C.c_int(t.shape[0]),
+                                labels.ctypes.data_as(C.POINTER(C.c_int64)), _p(margin))
+    return labels.reshape(f.shape[:-1]), margin.reshape(f.shape[:-1])

@@ -17,6 +17,8 @@ Only device-agnostic reference functions are called, on CPU:
                                                                               -> checkpoint.pt
   scannet.primitive_csr.reference_weight_gradients; torch autograd through the compositing formulas
                                                                               -> backward.npz
+  scannet.feature_decoder.FeatureUpsampleDecoder, scannet.eval_lseg_table2._classify_feature_map
+                                                                              -> decoder.npz
 The scene inputs come from this repository's seeded generator, so tests can rebuild them.
 """
 import os
@@ -158,6 +160,32 @@ def checkpoint_fixture(ref_root):
                os.path.join(HERE, "checkpoint.pt"))
 
 
+DECODER_CASES = {"small": dict(in_dim=24, hidden=32, out_dim=40, classes=7, W=13, H=9, seed=41, keep=1),
+                 "lseg": dict(in_dim=128, hidden=128, out_dim=512, classes=20, W=20, H=19, seed=42, keep=16)}
+
+
+def decoder_fixture(ref_root):
+    """decoder.npz: the reference decoder and text query on seeded weights and maps (tests rebuild the inputs from
+    the same seeds); of the decoded map every keep-th channel is stored."""
+    sys.path.insert(0, ref_root)
+    import importlib
+    from scannet.feature_decoder import FeatureUpsampleDecoder
+    ev = importlib.import_module("scannet.eval_lseg_table2")
+    from mlp_splatting_b200 import synthetic as syn
+    out = {}
+    for tag, c in DECODER_CASES.items():
+        w, text = syn.make_decoder(c["in_dim"], c["hidden"], c["out_dim"], c["classes"], seed=c["seed"])
+        x = syn.make_feature_map(c["W"], c["H"], c["in_dim"], seed=c["seed"] + 100)
+        dec = FeatureUpsampleDecoder(c["in_dim"], c["out_dim"], c["hidden"]).eval()
+        dec.load_state_dict({k: torch.from_numpy(v) for k, v in w.items()})
+        with torch.no_grad():
+            y = dec(torch.from_numpy(x).permute(2, 0, 1).unsqueeze(0).float()).squeeze(0).permute(1, 2, 0).contiguous()
+            lab = ev._classify_feature_map(y, torch.from_numpy(text))
+        out[f"{tag}_decoded"] = y.numpy()[..., ::c["keep"]].copy()
+        out[f"{tag}_labels"] = lab.numpy().astype(np.int64)
+    np.savez_compressed(os.path.join(HERE, "decoder.npz"), **out)
+
+
 def backward_fixtures(ref_root):
     """backward.npz: (1) per-primitive weight gradients from the reference's own PyTorch statement
     (scannet.primitive_csr.reference_weight_gradients) on the record counts its test uses
@@ -244,8 +272,9 @@ def backward_fixtures(ref_root):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    main(root)
-    checkpoint_fixture(root)
-    backward_fixtures(root)
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/mlp-splatting [fixture ...]")
+    root = sys.argv[1]
+    makers = {"main": main, "checkpoint": checkpoint_fixture, "backward": backward_fixtures, "decoder": decoder_fixture}
+    for name in (sys.argv[2:] or list(makers)):
+        makers[name](root)
