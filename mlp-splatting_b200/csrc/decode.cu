@@ -36,12 +36,13 @@ namespace mlpsp {
 constexpr int kDecTileW = 8, kDecTileH = 16;                       // 128 output pixels = MMA M
 constexpr int kHaloW = kDecTileW + 2, kHaloH = kDecTileH + 2;
 constexpr int kHaloPx = kHaloW * kHaloH;                           // 180
-constexpr int kDecThreads = 256;
+constexpr int kDecThreads = 512;
+constexpr int kColGroups = kDecThreads / 128;                        // warps that share a tensor-memory lane quarter split the columns
 constexpr int kDecBlock = 32768;                                   // one weight block: <= 128 x 128 halves
-constexpr int kDecRing = 2;
+constexpr int kDecRing = 3;
 constexpr int kStagePitch = 36;                                    // floats per pixel row of an output staging tile
 constexpr int kDecPieces = 8;                                      // bulk copies per weight block (block sizes are multiples of 1 KB)
-constexpr int kDecSub = 2;                                         // tiles that share one pass over the weights
+constexpr int kDecSub = 1;                                         // tiles that share one pass over the weights
 constexpr int kDecMaxBlocks = 16;                                  // per pass: W1, 9 taps, <= 6 output chunks
 constexpr int kDecMaxDim = 128;                                    // input and hidden width limit
 constexpr int kDecMaxOut = 768;
@@ -58,15 +59,15 @@ constexpr int32_t kDecMagic = 0x44454331;
 // shared-memory plan (bytes)
 constexpr int kDecH1Bytes = (kDecMaxDim / 8) * kHaloPx * 16;          // 46,080: one hidden tile with halo
 constexpr int kSmRing = 0;
-constexpr int kSmA0 = kSmRing + kDecRing * kDecBlock;                 //  65,536
+constexpr int kSmA0 = kSmRing + kDecRing * kDecBlock;                 //  98,304
 constexpr int kA0Pitch = kHaloPx + 1;                                 // 16-byte units between K chunks of the input tile (odd)
 constexpr int kSmH1 = kSmA0 + (kDecMaxDim / 8) * kA0Pitch * 16;       // +46,336
-constexpr int kSmBias = kSmH1 + kDecSub * kDecH1Bytes;                // +92,160
+constexpr int kSmBias = kSmH1 + kDecSub * kDecH1Bytes;                // +46,080
 constexpr int kSmHdr = kSmBias + 4 * (2 * kDecMaxDim + kDecMaxOut);   // + 4,096
 constexpr int kSmBar = kSmHdr + 256;
 constexpr int kSmMisc = kSmBar + 16 * 8;
 constexpr int kSmArg = kSmMisc + 64;                                  // [2][128] (value, index) pairs
-constexpr int kDecSmem = kSmArg + kDecSub * 128 * 8;
+constexpr int kDecSmem = kSmArg + kDecSub * kColGroups * 128 * 8;
 static_assert(kDecSmem <= 227 * 1024, "shared memory of the decoder");
 
 static int round_up(int v, int m) { return (v + m - 1) / m * m; }
@@ -180,18 +181,19 @@ __global__ void k_fold_text(const float* __restrict__ text, const float* __restr
 // Input tile with halo -> binary16 A operand [K1/8][kA0Pitch][8] in shared memory.  Consecutive lanes take
 // consecutive 32-byte pieces of a pixel's feature row (coalesced); the odd pitch spreads the 16-byte stores
 // of one pixel's chunks over all banks.  Loads are issued four units ahead of their conversion.
+// Threads t = 0..nthr-1 of the CTA share the tile.
 __device__ __forceinline__ bool load_input_tile(const float* __restrict__ feat, int W, int H, int Cin, int K1,
-                                                int ty0, int tx0, char* s_a0, int tid) {
+                                                int ty0, int tx0, char* s_a0, int t, int nthr) {
   // unit u = (halo pixel r, 16-byte chunk kc), chunk fastest; the chunk count is padded to a power of two so that
   // the split is a shift and a mask
   const int nk = K1 >> 3, lg = nk > 8 ? 4 : (nk > 4 ? 3 : (nk > 2 ? 2 : 1)), units = kHaloPx << lg;
   const bool vec = (Cin & 7) == 0;
   bool bad = false;
-  for (int u0 = tid; u0 < units; u0 += 4 * kDecThreads) {
+  for (int u0 = t; u0 < units; u0 += 4 * nthr) {
     float4 lo[4], hi[4];
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-      const int u = u0 + b * kDecThreads;
+      const int u = u0 + b * nthr;
       lo[b] = hi[b] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (u < units) {
         const int r = u >> lg, kc = u & ((1 << lg) - 1);
@@ -214,7 +216,7 @@ __device__ __forceinline__ bool load_input_tile(const float* __restrict__ feat, 
     }
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-      const int u = u0 + b * kDecThreads;
+      const int u = u0 + b * nthr;
       const int r = u >> lg, kc = u & ((1 << lg) - 1);
       if (u < units && kc < nk) {
         uint4 w;
@@ -296,6 +298,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
   const int total_blocks = n_my * NB;
   const int out_chunks = (n_pad + 127) >> 7;
   const uint32_t idesc_h = instr_desc(128, Ch);
+  // decoded features leave through a staging tile in the input tile's space, so only a text query can fetch the
+  // next input early
+  static_assert(kDecSub == 1, "the early fetch of the next input assumes one tile per pass");
+  const bool prefetch = classify;
   int issued = 0, landed = 0;            // issuing thread only: copies requested / copies waited for
   uint32_t ph_m = 0, ph_o = 0;
   bool ok = true, bad = false;
@@ -343,7 +349,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
     }
     // ---- per sub-tile: input, layer 1 over the 180 halo pixels, hidden tile ----
     for (int sb = 0; sb < kDecSub; ++sb) {
-      bad |= load_input_tile(feat, W, H, Cin, K1, ty0[sb], tx0[sb], smem + kSmA0, tid);
+      if (!prefetch || it == 0) bad |= load_input_tile(feat, W, H, Cin, K1, ty0[sb], tx0[sb], smem + kSmA0, tid, kDecThreads);
       fence_async_smem();
       tc_fence_before();
       if (!__syncthreads_and(ok)) { ok = false; break; }
@@ -371,7 +377,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
           const int hy = r / kHaloW, hx = r - hy * kHaloW;
           const int y = ty0[sb] + hy - 1, x = tx0[sb] + hx - 1;
           const bool inside = y >= 0 && y < H && x >= 0 && x < W;   // outside: the 3x3 convolution's zero padding
-          for (int cc = hsel; cc < (Ch >> 5); cc += 2) {
+          for (int cc = hsel; cc < (Ch >> 5); cc += kColGroups) {
             uint32_t acc[32];
             tmem_ld32(trow + mt * 128 + cc * 32, acc);
 #pragma unroll
@@ -388,8 +394,16 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
       if (!__syncthreads_and(ok)) { ok = false; break; }
     }
     if (!ok) break;
-    // ---- layer 2: nine taps, each weight block serves both sub-tiles; columns [256 + 128 sb, .. + Ch) ----
-    if (tid == 0) {
+    // ---- layer 2: nine taps, each weight block serves every sub-tile; columns [256 + 128 sb, .. + Ch) ----
+    // While one lane issues them, the other fifteen warps fetch the next tile's input: layer 1 has finished
+    // reading the input tile, and nothing else uses its space in a text query.
+    if (warp != 0) {
+      if (prefetch && it + 1 < n_my) {
+        const int nt = ((int)blockIdx.x + (it + 1) * (int)gridDim.x) * kDecSub;
+        bad |= load_input_tile(feat, W, H, Cin, K1, (nt / tiles_x) * kDecTileH, (nt % tiles_x) * kDecTileW, smem + kSmA0,
+                               tid - 32, kDecThreads - 32);
+      }
+    } else if (tid == 0) {
       for (int tap = 0; tap < 9 && ok; ++tap) {
         const int g = gbase + 1 + tap;
         const uint32_t wb = acquire(g);
@@ -409,7 +423,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
     const int m = q * 32 + lane;                       // this thread's output pixel of either sub-tile
     if (ok) {
       for (int sb = 0; sb < kDecSub; ++sb)
-        for (int cc = hsel; cc < (Ch >> 5); cc += 2) {
+        for (int cc = hsel; cc < (Ch >> 5); cc += kColGroups) {
           uint32_t acc[32];
           tmem_ld32(trow + 256 + sb * 128 + cc * 32, acc);
 #pragma unroll
@@ -449,7 +463,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
       if (ok) {
 #pragma unroll
         for (int sb = 0; sb < kDecSub; ++sb) {
-          for (int cc = hsel; cc < (nc >> 5); cc += 2) {
+          // decoded features: the first eight warps only (one staging tile each)
+          for (int cc = hsel; cc < (nc >> 5) && (classify || hsel < 2); cc += classify ? kColGroups : 2) {
             uint32_t acc[32];
             tmem_ld32(trow + sb * 128 + cc * 32, acc);
             const int col0 = c * 128 + cc * 32;
@@ -498,20 +513,21 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
     }
     if (!ok) break;
     if (classify) {
-      // the two column interleaves of a pixel meet here; the lower class index wins a tie
-      if (hsel == 1) {
+      // the column interleaves of a pixel meet here; the lower class index wins a tie
 #pragma unroll
-        for (int sb = 0; sb < kDecSub; ++sb) s_arg[sb * 128 + m] = make_float2(best[sb], __int_as_float(arg[sb]));
-      }
+      for (int sb = 0; sb < kDecSub; ++sb) s_arg[(sb * kColGroups + hsel) * 128 + m] = make_float2(best[sb], __int_as_float(arg[sb]));
       __syncthreads();
       if (hsel == 0) {
 #pragma unroll
         for (int sb = 0; sb < kDecSub; ++sb) {
           const int py = ty0[sb] + (m >> 3), px = tx0[sb] + (m & 7);
-          const float2 o = s_arg[sb * 128 + m];
-          const int oa = __float_as_int(o.y);
+          float bv = best[sb];
           int a = arg[sb];
-          if (o.x > best[sb] || (o.x == best[sb] && oa < a)) a = oa;
+          for (int g = 1; g < kColGroups; ++g) {
+            const float2 o = s_arg[(sb * kColGroups + g) * 128 + m];
+            const int oa = __float_as_int(o.y);
+            if (o.x > bv || (o.x == bv && oa < a)) { bv = o.x; a = oa; }
+          }
           if (py < H && px < W) labels[(int64_t)py * W + px] = a;
         }
       }
@@ -532,100 +548,129 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
 }
 
 // ------------------------------------------------------- text query of a full-width feature map ----
-// A block takes 8 * PIX pixels at a time (PIX per warp): each lane keeps a strided slice of its warp's feature
-// rows in registers (rows read once, coalesced); the normalised text rows pass through shared memory a group of
-// classes at a time, shared by the block's pixels; the PIX dot products of a class are reduced across the warp by
-// a transposing butterfly (9 shuffles for 8 sums).  logit = f . t_c / max(|t_c|, 1e-12); the per-pixel
-// normalisation is one positive factor for all classes and does not enter the comparison (an all-zero row gives
-// label 0 either way).  The first maximum wins, like torch.argmax.
+// logits [P x C] = feat [P x D] . text^T [D x C] as a register-tiled FP32 product on the CUDA cores: a block owns
+// 128 pixels and walks the classes in tiles of CT; per step of 16 feature channels the two operand tiles are
+// staged k-major in shared memory (next step's global loads in flight meanwhile) and each thread accumulates
+// 4 pixels x CT/8 classes from 16-byte shared loads (the class values are a warp-wide broadcast).
+// logit = (f . t_c) / max(|t_c|, 1e-12); the per-pixel normalisation of the reference is one positive factor for
+// all classes and does not enter the comparison (an all-zero row gives label 0 either way).  The first maximum
+// wins, like torch.argmax: threads hold ascending classes, class groups and class tiles are merged in ascending
+// order, and only a strictly larger logit replaces the winner.
 constexpr int kMaxClasses = 1024;
-constexpr int kQueryTextBytes = 192 * 1024;   // shared memory for text rows: all classes when they fit
-template <int KPL, int PIX>
+constexpr int kQM = 128, kQK = 16, kQPitchA = kQM + 4;
+template <int CT>
 __global__ void __launch_bounds__(256) k_classify_features(const float* __restrict__ feat, int64_t P, int D,
                                                            const float* __restrict__ text, int C,
-                                                           long long* __restrict__ labels, int text_bytes) {
-  static_assert(PIX == 8 || PIX == 4, "butterfly width");
-  extern __shared__ float s_text[];        // [group][D]
+                                                           long long* __restrict__ labels) {
+  constexpr int TN = CT / 8, kPitchB = CT + 4;
+  __shared__ __align__(16) float s_a[2][kQK][kQPitchA];
+  __shared__ __align__(16) float s_b[2][kQK][kPitchB];
   __shared__ float s_inv[kMaxClasses];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __shared__ float s_val[8][kQM];
+  __shared__ int s_idx[8][kQM];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   for (int c = warp; c < C; c += 8) {
     float ss = 0.f;
     for (int k = lane; k < D; k += 32) { const float v = __ldg(text + (int64_t)c * D + k); ss = fmaf(v, v, ss); }
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (lane == 0) s_inv[c] = 1.0f / fmaxf(sqrtf(ss), 1e-12f);
   }
-  const int group = max(1, min(C, text_bytes / (4 * D)));
-  const bool resident = group >= C;      // every class fits: the text is staged once, not per pixel batch
-  bool staged = false;
-  // the pixel whose total this lane ends up holding after the butterfly
-  const int mine = PIX == 8 ? ((lane >> 4 & 1) * 4 + (lane >> 3 & 1) * 2 + (lane >> 2 & 1)) : ((lane >> 4 & 1) * 2 + (lane >> 3 & 1));
-  for (int64_t b0 = (int64_t)blockIdx.x * 8 * PIX; b0 < P; b0 += (int64_t)gridDim.x * 8 * PIX) {
-    const int64_t p0 = b0 + warp * PIX;
-    float f[PIX][KPL];
-#pragma unroll
-    for (int i = 0; i < PIX; ++i)
-#pragma unroll
-      for (int j = 0; j < KPL; ++j) {
-        const int k = lane + 32 * j;
-        f[i][j] = (p0 + i < P && k < D) ? __ldg(feat + (p0 + i) * D + k) : 0.f;
-      }
-    float best = -3.0e38f;
-    int arg = 0;
-    for (int c0 = 0; c0 < C; c0 += group) {
-      const int gc = min(group, C - c0);
-      if (!(resident && staged)) {
-        __syncthreads();                   // the previous group is no longer being read; the norms are written
-        // the group's rows are one contiguous span of the text matrix
-        const float* src = text + (int64_t)c0 * D;
-        if ((D & 3) == 0) {
-          const int n4 = gc * D / 4;
-#pragma unroll 8
-          for (int i = threadIdx.x; i < n4; i += 256) {
-            float4 v = __ldg(reinterpret_cast<const float4*>(src) + i);
-            const float inv = s_inv[c0 + (i * 4) / D];
-            v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
-            reinterpret_cast<float4*>(s_text)[i] = v;
-          }
-        } else {
-#pragma unroll 8
-          for (int i = threadIdx.x; i < gc * D; i += 256) s_text[i] = __ldg(src + i) * s_inv[c0 + i / D];
-        }
-        __syncthreads();
-        staged = true;
-      }
-      for (int c = 0; c < gc; ++c) {
-        const float* t = s_text + c * D;
-        float v[PIX];
-#pragma unroll
-        for (int i = 0; i < PIX; ++i) v[i] = 0.f;
-#pragma unroll
-        for (int j = 0; j < KPL; ++j) {
-          if (32 * j < D) {
-            const int k = lane + 32 * j;
-            const float tv = k < D ? t[k] : 0.f;
-#pragma unroll
-            for (int i = 0; i < PIX; ++i) v[i] = fmaf(f[i][j], tv, v[i]);
-          }
-        }
-        // transposing butterfly: after the step over lane bit b each lane keeps half of its sums
-#pragma unroll
-        for (int w = PIX / 2, bit = 16; w >= 1; w >>= 1, bit >>= 1) {
-          const bool up = (lane & bit) != 0;
-#pragma unroll
-          for (int i = 0; i < w; ++i) {
-            const float send = up ? v[i] : v[i + w], keep = up ? v[i + w] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
-          }
-        }
-        float a = v[0];
-        if (PIX == 4) a += __shfl_xor_sync(0xffffffffu, a, 4);
-        a += __shfl_xor_sync(0xffffffffu, a, 2);
-        a += __shfl_xor_sync(0xffffffffu, a, 1);
-        if (a > best) { best = a; arg = c0 + c; }
+  const int64_t p0 = (int64_t)blockIdx.x * kQM;
+  const bool vec = (D & 3) == 0;
+  const int lk = (t & 3) * 4;                 // this thread's 4 channels of a 16-channel step
+  const int lrow = t >> 2;                    // pixel (two: +0, +64) or class row it loads
+  const int steps = (D + kQK - 1) / kQK;
+  // one 16-byte piece of a row, zero beyond the row's end or the matrix's
+  auto fetch = [&](const float* base, int64_t row, int64_t rows, int k) -> float4 {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < rows) {
+      const float* src = base + row * D + k;
+      if (vec) { if (k < D) v = __ldg(reinterpret_cast<const float4*>(src)); }
+      else {
+        if (k < D) v.x = __ldg(src);
+        if (k + 1 < D) v.y = __ldg(src + 1);
+        if (k + 2 < D) v.z = __ldg(src + 2);
+        if (k + 3 < D) v.w = __ldg(src + 3);
       }
     }
-    if ((lane & (PIX == 8 ? 3 : 7)) == 0 && p0 + mine < P) labels[p0 + mine] = arg;
+    return v;
+  };
+  auto put = [&](float (*dst)[kQPitchA], int col, const float4& v) {
+    dst[lk][col] = v.x; dst[lk + 1][col] = v.y; dst[lk + 2][col] = v.z; dst[lk + 3][col] = v.w;
+  };
+  auto put_b = [&](float (*dst)[kPitchB], int col, const float4& v) {
+    dst[lk][col] = v.x; dst[lk + 1][col] = v.y; dst[lk + 2][col] = v.z; dst[lk + 3][col] = v.w;
+  };
+  float run_val = -3.0e38f;                    // threads 0..127: the winner so far of pixel p0 + t
+  int run_idx = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < C; c0 += CT) {
+    float acc[4][TN];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    float4 ra0 = fetch(feat, p0 + lrow, P, lk), ra1 = fetch(feat, p0 + lrow + 64, P, lk);
+    float4 rb = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (lrow < CT) rb = fetch(text, c0 + lrow, C, lk);
+    put(s_a[0], lrow, ra0); put(s_a[0], lrow + 64, ra1);
+    if (lrow < CT) put_b(s_b[0], lrow, rb);
+    __syncthreads();
+    for (int st = 0; st < steps; ++st) {
+      const int cur = st & 1;
+      if (st + 1 < steps) {
+        const int k = (st + 1) * kQK + lk;
+        ra0 = fetch(feat, p0 + lrow, P, k); ra1 = fetch(feat, p0 + lrow + 64, P, k);
+        if (lrow < CT) rb = fetch(text, c0 + lrow, C, k);
+      }
+#pragma unroll
+      for (int k = 0; k < kQK; ++k) {
+        const float4 a = *reinterpret_cast<const float4*>(&s_a[cur][k][lane * 4]);
+        float b[TN];
+#pragma unroll
+        for (int j = 0; j < TN; j += 4) {
+          const float4 bv = *reinterpret_cast<const float4*>(&s_b[cur][k][warp * TN + j]);
+          b[j] = bv.x; b[j + 1] = bv.y; b[j + 2] = bv.z; b[j + 3] = bv.w;
+        }
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+          acc[0][j] = fmaf(a.x, b[j], acc[0][j]); acc[1][j] = fmaf(a.y, b[j], acc[1][j]);
+          acc[2][j] = fmaf(a.z, b[j], acc[2][j]); acc[3][j] = fmaf(a.w, b[j], acc[3][j]);
+        }
+      }
+      if (st + 1 < steps) {
+        put(s_a[cur ^ 1], lrow, ra0); put(s_a[cur ^ 1], lrow + 64, ra1);
+        if (lrow < CT) put_b(s_b[cur ^ 1], lrow, rb);
+      }
+      __syncthreads();
+    }
+    // this thread's best class per pixel, then the eight class groups of the tile in ascending order
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float bv = -3.0e38f;
+      int bi = 0;
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        const int c = c0 + warp * TN + j;
+        if (c < C) {
+          const float v = acc[i][j] * s_inv[c];
+          if (v > bv) { bv = v; bi = c; }
+        }
+      }
+      s_val[warp][lane * 4 + i] = bv;
+      s_idx[warp][lane * 4 + i] = bi;
+    }
+    __syncthreads();
+    if (t < kQM) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const float v = s_val[g][t];
+        if (v > run_val) { run_val = v; run_idx = s_idx[g][t]; }
+      }
+    }
+    __syncthreads();
   }
+  if (t < kQM && p0 + t < P) labels[p0 + t] = run_idx;
 }
 
 }  // namespace mlpsp
@@ -699,32 +744,17 @@ extern "C" int mlpsp_classify_features(const float* feat, int64_t pixels, int32_
                                        int32_t num_classes, int64_t* labels, void* stream) {
   MLPSP_REQUIRE(feat && text && labels, MLPSP_E_ARG, "mlpsp_classify_features: null pointer");
   MLPSP_REQUIRE(pixels >= 0 && dim > 0 && num_classes > 0, MLPSP_E_ARG, "mlpsp_classify_features: bad sizes");
-  MLPSP_REQUIRE(dim <= 1024 && num_classes <= kMaxClasses, MLPSP_E_LIMIT,
-                "mlpsp_classify_features: at most 1024 feature channels and %d classes", kMaxClasses);
+  MLPSP_REQUIRE(num_classes <= kMaxClasses && pixels <= (int64_t)kQM * 0x7fffffff, MLPSP_E_LIMIT,
+                "mlpsp_classify_features: at most %d classes", kMaxClasses);
   if (pixels == 0) return MLPSP_OK;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  static bool attr_set = false;
-  if (!attr_set) {
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_classify_features<8, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQueryTextBytes));
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_classify_features<16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQueryTextBytes));
-    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_classify_features<32, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQueryTextBytes));
-    attr_set = true;
-  }
   cudaStream_t st = (cudaStream_t)stream;
   LaunchScope scope(kKMisc, 1, st);
   long long* lab = reinterpret_cast<long long*>(labels);
-  const int64_t need = (int64_t)num_classes * dim * 4;
-  const int tb = (int)std::min<int64_t>(kQueryTextBytes, std::max<int64_t>(need, 4 * dim));
-  // every block walks the same number of pixel batches in step with its text groups
-  if (dim <= 512) {
-    const int grid = (int)std::min<int64_t>((pixels + 63) / 64, (int64_t)sms * 2);
-    if (dim <= 256) k_classify_features<8, 8><<<grid, 256, tb, st>>>(feat, pixels, dim, text, num_classes, lab, tb);
-    else k_classify_features<16, 8><<<grid, 256, tb, st>>>(feat, pixels, dim, text, num_classes, lab, tb);
-  } else {
-    const int grid = (int)std::min<int64_t>((pixels + 31) / 32, (int64_t)sms * 2);
-    k_classify_features<32, 4><<<grid, 256, tb, st>>>(feat, pixels, dim, text, num_classes, lab, tb);
-  }
+  const int grid = (int)((pixels + kQM - 1) / kQM);
+  if (num_classes <= 32) k_classify_features<32><<<grid, 256, 0, st>>>(feat, pixels, dim, text, num_classes, lab);
+  else k_classify_features<64><<<grid, 256, 0, st>>>(feat, pixels, dim, text, num_classes, lab);
   return cuda_check(cudaGetLastError(), "mlpsp_classify_features");
 }
