@@ -36,7 +36,7 @@ namespace mlpsp {
 constexpr int kDecTileW = 8, kDecTileH = 16;                       // 128 output pixels = MMA M
 constexpr int kHaloW = kDecTileW + 2, kHaloH = kDecTileH + 2;
 constexpr int kHaloPx = kHaloW * kHaloH;                           // 180
-constexpr int kDecThreads = 512;
+constexpr int kDecThreads = 256;
 constexpr int kColGroups = kDecThreads / 128;                        // warps that share a tensor-memory lane quarter split the columns
 constexpr int kDecBlock = 32768;                                   // one weight block: <= 128 x 128 halves
 constexpr int kDecRing = 3;
@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
     }
     if (!ok) break;
     // ---- layer 2: nine taps, each weight block serves every sub-tile; columns [256 + 128 sb, .. + Ch) ----
-    // While one lane issues them, the other fifteen warps fetch the next tile's input: layer 1 has finished
+    // While one lane issues them, the other warps fetch the next tile's input: layer 1 has finished
     // reading the input tile, and nothing else uses its space in a text query.
     if (warp != 0) {
       if (prefetch && it + 1 < n_my) {
