@@ -194,6 +194,12 @@ def workload_config(name, cfg, n_gpus, encoder="integrated"):
             "tile_capacity": 1536, "threshold": THRESHOLD, "log_scale_mean": cfg["mu"],
             "mlp": f"72-{cfg.get('hidden', 32)}-{cfg.get('hidden', 32)}-4 fp16 weights, fp32 accumulate", "views_per_step": n_gpus if views == 1 else views,
             "feature_channels": cfg.get("feat_dim", 0),
+            "after_feature_map": (f"decoder {cfg['feat_dim']}-{cfg['decoder']['hidden']}-{cfg['decoder']['out_dim']} (1x1, 3x3, 1x1) + "
+                                  f"{cfg['decoder']['classes']}-class text query, labels per pixel; not part of the e2e arm"
+                                  if cfg.get("decoder") else
+                                  (f"{cfg['text_query']['classes']}-class text query by projecting the scene's features onto the "
+                                   "normalised embeddings once; class scores composited, labels per pixel; not part of the e2e arm"
+                                   if cfg.get("text_query") else None)),
             "parallelism": (f"one view per GPU x{n_gpus} (azimuth 90 deg x (rank mod 4))" if views == 1 else f"{views} views shared by {n_gpus} GPU(s) by view, then by tile-row band")
                            + ", scene replicated",
             "l2": "256 MB flush between timed steps"}
@@ -272,11 +278,34 @@ def main():
     rd_h = torch.from_numpy(cam["rays_d"]).pin_memory()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
+    # the step after the feature map, for workloads that name a decoder: decoder + text query in one kernel
+    dec = text = labels = None
+    if cfg.get("decoder"):
+        from mlp_splatting_b200.feature_decoder import FeatureUpsampleDecoder
+        dc = cfg["decoder"]
+        dw, dtext = syn.make_decoder(cfg["feat_dim"], dc["hidden"], dc["out_dim"], dc["classes"], seed=dc["seed"])
+        dec = FeatureUpsampleDecoder(cfg["feat_dim"], dc["out_dim"], dc["hidden"], device=dev)
+        dec.load_state_dict({k: torch.from_numpy(v) for k, v in dw.items()})
+        text = torch.from_numpy(dtext).to(dev)
+
+    score_dim = 0
+    if cfg.get("text_query"):
+        from mlp_splatting_b200.feature_decoder import score_labels
+        tq = cfg["text_query"]
+        qtext = torch.from_numpy(np.random.default_rng(tq["seed"]).normal(size=(tq["classes"], cfg["feat_dim"])).astype(np.float32))
+        ps = ps.with_text_query(qtext)
+        score_dim = tq["classes"]
+
     def frame(check=False):
+        nonlocal labels
         out = None
         for (c, rows), (ro_u, rd_u) in zip(units, dev_rays):
             out = r.render(ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=prec,
                            rays_normalized=True, check=check, tile_rows=rows, want_feat=want_feat)
+            if dec is not None:
+                labels = dec.classify(r.feat.view(cfg["H"], cfg["W"], cfg["feat_dim"]), text, check=check)
+            if score_dim:
+                labels = score_labels(r.feat.view(cfg["H"], cfg["W"], score_dim))
         return out
 
     def barrier():

@@ -18,6 +18,7 @@ import torch
 
 from . import _lib as L
 
+_EYES = {}
 _KEYS = ("net.0.weight", "net.0.bias", "net.2.weight", "net.2.bias", "net.4.weight", "net.4.bias")
 
 
@@ -55,7 +56,10 @@ def score_labels(scores_hwc: torch.Tensor) -> torch.Tensor:
     PackedScene.with_text_query(); labels [H, W] int64."""
     if scores_hwc.ndim != 3:
         raise ValueError(f"scores_hwc must be 3D, got {tuple(scores_hwc.shape)}")
-    eye = torch.eye(int(scores_hwc.shape[2]), device=scores_hwc.device, dtype=torch.float32)
+    key = (int(scores_hwc.shape[2]), scores_hwc.device)
+    eye = _EYES.get(key)
+    if eye is None:
+        eye = _EYES[key] = torch.eye(key[0], device=key[1], dtype=torch.float32)
     return classify_feature_map(scores_hwc, eye)
 
 

@@ -87,6 +87,13 @@ WORKLOADS = {
     "tiny_2k_128x96": dict(n=2000, W=128, H=96, mu=-3.5, views=1, seed=2026),
     "single_100k_1200x680": dict(n=100_000, W=1200, H=680, mu=-4.2, views=1, seed=2027),
     "feature_250k_1200x680": dict(n=250_000, W=1200, H=680, mu=-4.8, views=1, seed=2028, feat_dim=512),
+    # low-dimensional features, the 3-layer decoder and a 20-class text query after the feature map
+    "query_250k_1200x680": dict(n=250_000, W=1200, H=680, mu=-4.8, views=1, seed=2028, feat_dim=128,
+                                decoder=dict(hidden=128, out_dim=512, classes=20, seed=2032)),
+    # full-width (512-channel) features queried by 20 text embeddings: the scene is projected onto the normalised
+    # embeddings once and class scores are composited instead of features
+    "textquery_250k_1200x680": dict(n=250_000, W=1200, H=680, mu=-4.8, views=1, seed=2028, feat_dim=512,
+                                    text_query=dict(classes=20, seed=2033)),
     "fourview_500k_1200x680": dict(n=500_000, W=1200, H=680, mu=-5.2, views=4, seed=2029),
     "stress_2m_1920x1080": dict(n=2_000_000, W=1920, H=1080, mu=-6.4, views=32, seed=2030, hidden=32),
     # the stress configuration's 64-wide hidden layers on a scene whose FP32 masters (36 KB per primitive) stay small
