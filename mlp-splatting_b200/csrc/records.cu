@@ -597,9 +597,17 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
     }
     __syncthreads();
     const int nruns = s_nruns;
-    // thread owns channel c0 + tid; the attribute rows of run r + 2 are requested before run r is
-    // accumulated, so their latency overlaps two runs of arithmetic
-    for (int c = tid; c < nc; c += kFeatThreads) {
+    // A thread owns one channel; with fewer than 256 channels in the block, RL threads of a warp share a channel
+    // and split the records of a run between them (one primitive touches a pixel at most once, so the records
+    // of a run hit distinct accumulator cells; runs follow one another in warp lockstep).  The attribute rows
+    // of run r + 2 are requested before run r is accumulated, so their latency overlaps two runs of arithmetic.
+    int RL = 1;
+    while (RL < 32 && 2 * RL * nc <= kFeatThreads) RL *= 2;
+    const int CPW = 32 / RL, rl = lane / CPW;
+    uint32_t wmask = 0xffffffffu;              // lanes of this warp that still own a channel
+    for (int c = warp * CPW + lane % CPW;; c += (kFeatThreads / 32) * CPW) {
+      wmask = __ballot_sync(wmask, c < nc);
+      if (c >= nc) break;
       auto load_rows = [&](int r, float (&a)[5]) {
         a[0] = a[1] = a[2] = a[3] = a[4] = 0.f;
         if (r >= nruns) return;
@@ -628,16 +636,17 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
           }
           return v;
         };
-        int j = j0;
+        int j = j0 + rl;
         // records of one pair touch distinct pixels: four accumulator cells are loaded together
-        for (; j + 4 <= j1; j += 4) {
-          float* q0 = s_acc + s_px[j] * CB + c; float* q1 = s_acc + s_px[j + 1] * CB + c;
-          float* q2 = s_acc + s_px[j + 2] * CB + c; float* q3 = s_acc + s_px[j + 3] * CB + c;
-          const float v0 = contribution(j), v1 = contribution(j + 1), v2 = contribution(j + 2), v3 = contribution(j + 3);
+        for (; j + 3 * RL < j1; j += 4 * RL) {
+          float* q0 = s_acc + s_px[j] * CB + c; float* q1 = s_acc + s_px[j + RL] * CB + c;
+          float* q2 = s_acc + s_px[j + 2 * RL] * CB + c; float* q3 = s_acc + s_px[j + 3 * RL] * CB + c;
+          const float v0 = contribution(j), v1 = contribution(j + RL), v2 = contribution(j + 2 * RL), v3 = contribution(j + 3 * RL);
           const float x0 = *q0, x1 = *q1, x2 = *q2, x3 = *q3;
           *q0 = x0 + v0; *q1 = x1 + v1; *q2 = x2 + v2; *q3 = x3 + v3;
         }
-        for (; j < j1; ++j) s_acc[s_px[j] * CB + c] += contribution(j);
+        for (; j < j1; j += RL) s_acc[s_px[j] * CB + c] += contribution(j);
+        if (RL > 1) __syncwarp(wmask);
 #pragma unroll
         for (int q = 0; q < 5; ++q) { a_cur[q] = a_n1[q]; a_n1[q] = a_n2[q]; }
       }
