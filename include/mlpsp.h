@@ -51,6 +51,7 @@ extern "C" {
 #define MLPSP_ST_BAD_IDS 4           /* candidate id outside [0, n) */
 #define MLPSP_ST_PAIR_OVERFLOW 8     /* more candidate pairs than max_pairs */
 #define MLPSP_ST_RECORD_OVERFLOW 16  /* a wave produced more records than max_records */
+#define MLPSP_ST_PIXEL_HITS 32       /* per-pixel ordering: a pixel met more than 256 primitives */
 #define MLPSP_ST_NUMERIC 64          /* non-finite operand/activation in the fp16 evaluator */
 #define MLPSP_ST_TIMEOUT 128         /* a bounded device-side wait gave up */
 #define MLPSP_ST_TILE_ORIGINS 256    /* ray-cone culling: a tile's rays do not share one origin */
@@ -60,6 +61,7 @@ extern "C" {
 #define MLPSP_PRECISION_F32 0  /* scalar FP32 evaluator (np_tile_kernels.cu:312-380) */
 #define MLPSP_PRECISION_F16 1  /* fp16 operands, FP32 accumulate, tcgen05 (rgb_wmma.cuh:75-223) */
 #define MLPSP_PRECISION_BF16 2 /* bfloat16 operands (the bf16 flag of render_tiles_rgb_wmma, rgb_wmma.cuh:225), same kernel */
+#define MLPSP_ORDER_PER_PIXEL 2 /* value of mlpsp_frame.sort_key for per-pixel exact ordering */
 
 #define MLPSP_GEOM_FLOATS 16   /* packed geometry floats per primitive */
 #define MLPSP_MAX_WAVES 32
@@ -117,7 +119,11 @@ typedef struct mlpsp_frame {
   int32_t keep_records;   /* 1 = keep what mlpsp_export_records needs (ReLU masks, logits, transmittance) */
   int32_t sort_key;       /* 0 = t* of the tile-centre ray (np_tile_kernels.cu:483-518), the order of the forward,
                              feature and record kernels; 1 = Euclidean depth (c - o).d along that ray, the order
-                             of render_tiles_kernel_tilecenter_order_with_t (np_tile_kernels.cu:5538-5543) */
+                             of render_tiles_kernel_tilecenter_order_with_t (np_tile_kernels.cu:5538-5543);
+                             2 (MLPSP_ORDER_PER_PIXEL) = per-pixel exact ordering, render_tiles_kernel_with_sort
+                             (np_tile_kernels.cu:714-926): every pixel blends its own hits in the order of its own
+                             hit distances; rgb and alpha only, every hit is evaluated (size max_records for all
+                             hits of the frame), more than 256 hits in a pixel raise MLPSP_ST_PIXEL_HITS */
   int32_t tile_row_begin; /* binning keeps only tile rows [tile_row_begin, tile_row_end); both 0 = the whole image. */
   int32_t tile_row_end;   /* Used to share one view between GPUs by bands of tile rows: tiles outside the band get
                              empty lists and their pixels the background. */

@@ -17,6 +17,8 @@ ST_RECORDS_LO, ST_USED_LO, ST_WAVE_RECORDS, ST_WORK_ITEMS, ST_WORK_TOTAL, ST_PAI
 BIT_BAD_OFFSETS, BIT_TILE_CAPACITY, BIT_BAD_IDS = 1, 2, 4
 BIT_PAIR_OVERFLOW, BIT_RECORD_OVERFLOW, BIT_NUMERIC, BIT_TIMEOUT = 8, 16, 64, 128
 BIT_TILE_ORIGINS, BIT_CONE_TOO_WIDE = 256, 512
+BIT_PIXEL_HITS = 32
+ORDER_PER_PIXEL = 2
 PRECISION_F32, PRECISION_F16, PRECISION_BF16 = 0, 1, 2
 MAX_WAVES = 32
 GEOM_FLOATS = 16

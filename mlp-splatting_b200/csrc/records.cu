@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(256) k_fill(
     float thr, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo, int hi,
     const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base,
     const int32_t* __restrict__ prim_off, int32_t* __restrict__ prim_cursor, RecIn* __restrict__ rec_in,
-    float* __restrict__ rec_t, float4* __restrict__ rec_gate, float beta, float tau,
+    float* __restrict__ rec_t, float4* __restrict__ rec_gate, float beta, float tau, int exact_hits,
     const int32_t* __restrict__ status) {
   __shared__ uint32_t s_m[2][kWinMax];
   __shared__ int32_t s_pref[kWinMax + 1];   // slot of the pair's first record, relative to the tile-wave
@@ -357,7 +357,8 @@ __global__ void __launch_bounds__(256) k_fill(
     Hit ht;
     // the pair is known to hit: values only.  The feature gates divide the local offset by the scales, which
     // magnifies its rounding, so frames with features keep the decision-grade arithmetic.
-    if (rec_gate) hit_test(load_geom(geom, p), o, d, thr, ht);
+    // Per-pixel ordering sorts by t: its order must be the decision-grade one too.
+    if (rec_gate || exact_hits) hit_test(load_geom(geom, p), o, d, thr, ht);
     else hit_values_fast(load_geom(geom, p), o, d, ht);
     const uint32_t slot = slot_base + (uint32_t)r;
     RecIn rec;
@@ -506,6 +507,76 @@ __global__ void __launch_bounds__(64) k_composite(
   __syncthreads();
   if (threadIdx.x == 0 && (s_live[0] | s_live[1]) && whi < len) next_active[atomicAdd(next_count, 1)] = tile;
   __syncthreads();
+  }
+}
+
+// --------------------------------------------------------------- per-pixel exact ordering ----
+// render_tiles_kernel_with_sort (np_tile_kernels.cu:714-926): every pixel sorts its own hits by its own hit
+// distance and blends them front to back.  Here the hits of all pixels have been found and evaluated in one
+// wave (no pixel is gated by transmittance, as the order is not known yet); a thread per pixel collects its
+// (t, record slot) pairs in list order -- at most kPixelHits, one more raises MLPSP_ST_PIXEL_HITS and the pixel
+// blends what it has, as the reference's kernel does before its wrapper raises -- sorts them with the
+// reference's stable insertion sort (ties keep list order) and blends until the transmittance falls below 1e-3.
+constexpr int kPixelHits = 256;
+__global__ void __launch_bounds__(64) k_composite_per_pixel(
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, int T, int W, int H, int ntx,
+    const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out,
+    const float* __restrict__ rec_t, float* __restrict__ rgb, float* __restrict__ alpha, float bgr, float bgg, float bgb,
+    int has_bg, int32_t* __restrict__ status) {
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int lane = threadIdx.x & 31, half = threadIdx.x >> 5;
+  const uint32_t lt = (1u << lane) - 1u;
+  for (int tile = blockIdx.x; tile < T; tile += gridDim.x) {
+    const int s = tile_offsets[tile], len = tile_len[tile];
+    const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
+    float key[kPixelHits];
+    uint32_t slot[kPixelHits];
+    int cnt = 0;
+    bool over = false;
+    int used = 0;
+    for (int i = 0; i < len && !over; ++i) {
+      const uint32_t m0 = masks32[2 * (size_t)(s + i)], m1 = masks32[2 * (size_t)(s + i) + 1];
+      const uint32_t mine = half ? m1 : m0;
+      if (tp.valid && ((mine >> lane) & 1u)) {
+        if (cnt < kPixelHits) {
+          const uint32_t sl = pair_base[s + i] + (half ? __popc(m0) : 0) + __popc(mine & lt);
+          key[cnt] = rec_t[sl];
+          slot[cnt] = sl;
+          ++cnt;
+        } else {
+          over = true;
+        }
+      }
+    }
+    if (over) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_PIXEL_HITS);
+    for (int i = 1; i < cnt; ++i) {
+      const float kt = key[i];
+      const uint32_t ks = slot[i];
+      int j = i - 1;
+      while (j >= 0 && key[j] > kt) { key[j + 1] = key[j]; slot[j + 1] = slot[j]; --j; }
+      key[j + 1] = kt;
+      slot[j + 1] = ks;
+    }
+    float cr = 0.f, cg = 0.f, cb = 0.f, trans = 1.f;
+    for (int i = 0; i < cnt; ++i) {
+      const float4 r = rec_out[slot[i]];
+      const float w = trans * r.w;
+      cr = fmaf(w, r.x, cr); cg = fmaf(w, r.y, cg); cb = fmaf(w, r.z, cb);
+      trans *= (1.f - r.w);
+      ++used;
+      if (trans < MLPSP_TERM) break;
+    }
+    if (tp.valid) {
+      const float a = 1.f - trans;
+      if (has_bg) {
+        const float k = fminf(fmaxf(1.f - a, 0.f), 1.f);
+        cr += k * bgr; cg += k * bgg; cb += k * bgb;
+      }
+      rgb[(size_t)tp.pix * 3] = cr; rgb[(size_t)tp.pix * 3 + 1] = cg; rgb[(size_t)tp.pix * 3 + 2] = cb;
+      alpha[tp.pix] = a;
+    }
+    for (int o = 16; o > 0; o >>= 1) used += __shfl_xor_sync(0xffffffffu, used, o);
+    if (lane == 0 && used) atomicAdd((unsigned long long*)(status + MLPSP_ST_USED_LO), (unsigned long long)used);
   }
 }
 
@@ -695,6 +766,12 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   }
   const bool keep = fr->keep_records == 1;
   const bool want_stats = fr->stat_sum_w != nullptr;
+  const bool per_pixel = fr->sort_key == MLPSP_ORDER_PER_PIXEL;
+  if (per_pixel) {
+    MLPSP_REQUIRE(!want_feat && !keep && !want_stats && !fr->mask_used && !want_t, MLPSP_E_ARG,
+                  "per-pixel ordering renders rgb and alpha only");
+    MLPSP_REQUIRE(fr->tile_capacity <= kWinMax, MLPSP_E_LIMIT, "per-pixel ordering needs tile_capacity <= %d", kWinMax);
+  }
   if (want_stats)
     MLPSP_REQUIRE(fr->gt_rgb && fr->stat_max_w && fr->stat_hits && fr->stat_sum_werr && fr->stat_contrib, MLPSP_E_ARG,
                   "contribution statistics need gt_rgb and all five per-primitive arrays");
@@ -722,10 +799,11 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   // CTAs walk the active-tile list with a grid stride, so a wave with few (or no) live tiles costs a
   // launch of a few thousand CTAs, not one per tile of the image
   const int wave_grid = std::min(T, sms * 16);
-  const int nw = fr->num_waves > 0 ? fr->num_waves : (int)(sizeof(kDefaultWaves) / sizeof(int));
+  // per-pixel ordering: one wave over the whole lists, every pixel live
+  const int nw = per_pixel ? 1 : (fr->num_waves > 0 ? fr->num_waves : (int)(sizeof(kDefaultWaves) / sizeof(int)));
   int lo = 0;
   for (int w = 0; w < nw && lo < fr->tile_capacity; ++w) {
-    const int wl = fr->num_waves > 0 ? fr->wave_len[w] : kDefaultWaves[w];
+    const int wl = per_pixel ? fr->tile_capacity : (fr->num_waves > 0 ? fr->wave_len[w] : kDefaultWaves[w]);
     MLPSP_REQUIRE(wl > 0, MLPSP_E_ARG, "wave_len[%d] must be positive", w);
     int hi = (wl >= fr->tile_capacity - lo || w == nw - 1) ? fr->tile_capacity : lo + wl;
     MLPSP_REQUIRE(hi - lo <= kWinMax, MLPSP_E_LIMIT, "wave window beyond %d candidates", kWinMax);
@@ -747,9 +825,9 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     { LaunchScope scope(kKFill, 1, st);
     k_fill<<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
-                              s.prim_cursor, s.rec_in, want_t ? s.rec_t : nullptr,
+                              s.prim_cursor, s.rec_in, (want_t || per_pixel) ? s.rec_t : nullptr,
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
-                              sc->gate_tau, fr->status); }
+                              sc->gate_tau, per_pixel ? 1 : 0, fr->status); }
     if (fr->precision == MLPSP_PRECISION_F16 || fr->precision == MLPSP_PRECISION_BF16)
       rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
                           fr->status, st, fr->precision == MLPSP_PRECISION_BF16, cap_mlp);
@@ -757,6 +835,13 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
       rc = launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
                           fr->status, st, cap_mlp);
     if (rc) return rc;
+    if (per_pixel) {
+      LaunchScope scope(kKComposite, 1, st);
+      k_composite_per_pixel<<<std::min(T, sms * 32), 64, 0, st>>>(fr->tile_offsets, s.tile_len, T, W, H, ntx, s.masks32, s.pair_base,
+                                                                 s.rec_out, s.rec_t, fr->rgb, fr->alpha, bg[0], bg[1], bg[2],
+                                                                 has_bg, fr->status);
+      break;
+    }
     { LaunchScope scope(kKComposite, 1, st);
     if (want_stats)
       k_composite<true><<<grid_comp, 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,

@@ -54,7 +54,10 @@ __device__ __forceinline__ unsigned long long make_composite(const float4* __res
   float key = MLPSP_SENTINEL_KEY;
   if (p >= 0 && p < n) {
     const Geom g = load_geom(geom, p);
-    key = key_mode ? tile_key_euclid(g, o, d) : tile_key(g, o, d);
+    // key_mode 2 (per-pixel ordering): the pixels sort their own hits later and fall back on the list order for
+    // equal hit distances (rays that start inside several primitives meet them all at t = 0), so the list keeps
+    // the order it was given, or ascending ids when it comes from the binning scatter
+    key = key_mode == 2 ? 0.f : (key_mode ? tile_key_euclid(g, o, d) : tile_key(g, o, d));
   }
   return ((unsigned long long)__float_as_uint(key) << 32) | (unsigned long long)(uint32_t)(FROM_SCATTER ? p : i);
 }

@@ -158,8 +158,6 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
                                                                               str(mode).strip().lower())
         if mode not in {"tilecenter", "per_pixel"}:
             raise ValueError(f"Unknown tile order mode: {mode}")
-        if mode != "tilecenter":
-            raise ValueError("only the tile-centre order is built; per_pixel ordering is not part of this path")
         return mode
 
     # --------------------------------------------------------------------------- internals ----
@@ -203,7 +201,12 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         if ray_o.shape[0] != W * H:
             raise AssertionError("Tile renderer requires full-frame rays (B == W*H)")
         device = self._activate_cuda_device()
-        self._resolve_tile_order_mode()
+        if self._resolve_tile_order_mode() == "per_pixel":
+            # render_tiles_forward (np_tile_kernels.cu:714-926): every pixel blends its own hits in its own order
+            if want_depth or want_feat or stats is not None:
+                raise ValueError("per_pixel ordering renders rgb and alpha only here; use MLPSP_TILE_ORDER=tilecenter "
+                                 "for depth, feature maps and contribution statistics")
+            sort_key = L.ORDER_PER_PIXEL
         T = ((W + 7) // 8) * ((H + 7) // 8)
         lists = None
         if getattr(self, "camera_mode", "legacy-centered") == "colmap-native":

@@ -370,12 +370,15 @@ class FrameRenderer:
                     return self.rgb, self.alpha
                 bits, stats = self._read_status()
                 self.last_stats = stats
-                if auto and bits == 0:
+                if auto and bits == 0 and sort_key != L.ORDER_PER_PIXEL:
                     self._adapt_waves(stats.waves)
                 if bits & (L.BIT_BAD_OFFSETS | L.BIT_TILE_CAPACITY | L.BIT_BAD_IDS | L.BIT_TIMEOUT):
                     raise_for_status(bits, stats.max_tile_len, self.capacity, path_name)
                 if self._grow(bits, stats):
                     continue
+                if bits & L.BIT_PIXEL_HITS:
+                    raise RenderError(f"{path_name}: per-pixel intersection capacity 256 exceeded; "
+                                      "refusing to return a silently truncated result")
                 if (bits & L.BIT_NUMERIC) and precision in (L.PRECISION_F16, L.PRECISION_BF16):
                     # operand/activation overflow in binary16: render the whole frame again in scalar
                     # FP32, as the reference does (rgb_wmma.cuh:260-272)

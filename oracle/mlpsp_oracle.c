@@ -790,3 +790,53 @@ void orc_classify_features(const float* feat, int64_t P, int D, const float* tex
   }
   free(tn);
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * Per-pixel exact ordering (render_tiles_kernel_with_sort, np_tile_kernels.cu:714-926): every pixel gathers
+ * its own hits from its tile's candidate list (at most 256; one more sets *overflow and the pixel blends the
+ * 256 it has, as the kernel's loop does before its wrapper raises), sorts them by its own hit distance t with
+ * a stable insertion sort (ties keep list order) and blends front to back until the transmittance falls
+ * below 1e-3.  prims is the tile's list in any order.
+ * ------------------------------------------------------------------------------------------- */
+void orc_render_per_pixel(const float* rays_o, const float* rays_d, const float* geom, int n,
+                          const int32_t* tile_offsets, const int32_t* prims, int W, int H, int ts, float thr,
+                          const mlp_t* mlp, float* rgb, float* alpha, int32_t* hits_per_pixel, int32_t* overflow) {
+  const int ntx = (W + ts - 1) / ts;
+  int any_overflow = 0;
+  #pragma omp parallel for schedule(dynamic, 64) reduction(|:any_overflow)
+  for (int64_t pix = 0; pix < (int64_t)W * H; ++pix) {
+    const int x = (int)(pix % W), y = (int)(pix / W);
+    const int tile = (y / ts) * ntx + x / ts;
+    const v3 o = ld3(rays_o, pix), d = ld3(rays_d, pix);
+    float ht[256]; int hp[256]; hit_t hh[256];
+    int cnt = 0;
+    for (int i = tile_offsets[tile]; i < tile_offsets[tile + 1]; ++i) {
+      const int p = prims[i];
+      if (p < 0 || p >= n) continue;
+      hit_t h;
+      if (!hit_test(geom + (size_t)p * 16, o, d, thr, &h)) continue;
+      if (cnt >= 256) { any_overflow = 1; break; }
+      ht[cnt] = h.t; hp[cnt] = p; hh[cnt] = h; ++cnt;
+    }
+    if (hits_per_pixel) hits_per_pixel[pix] = cnt;
+    for (int i = 1; i < cnt; ++i) {
+      const float kt = ht[i]; const int kp = hp[i]; const hit_t kh = hh[i];
+      int j = i - 1;
+      while (j >= 0 && ht[j] > kt) { ht[j + 1] = ht[j]; hp[j + 1] = hp[j]; hh[j + 1] = hh[j]; --j; }
+      ht[j + 1] = kt; hp[j + 1] = kp; hh[j + 1] = kh;
+    }
+    float C0 = 0.f, C1 = 0.f, C2 = 0.f, trans = 1.f;
+    for (int i = 0; i < cnt; ++i) {
+      const float v6[6] = { d.x, d.y, d.z, hh[i].dx, hh[i].dy, hh[i].dz };
+      mlp_out mo; mlp_eval(mlp, hp[i], v6, &mo);
+      const float al = 1.f - expf(-(mo.sigma_raw * hh[i].decay));
+      const float w = trans * al;
+      C0 = fmaf(w, mo.R, C0); C1 = fmaf(w, mo.G, C1); C2 = fmaf(w, mo.B, C2);
+      trans *= (1.f - al);
+      if (trans < ORC_TERM) break;
+    }
+    rgb[pix * 3] = C0; rgb[pix * 3 + 1] = C1; rgb[pix * 3 + 2] = C2;
+    alpha[pix] = 1.f - trans;
+  }
+  if (overflow) *overflow = any_overflow;
+}

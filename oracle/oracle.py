@@ -320,3 +320,23 @@ def classify_features(feat, text):
     lib().orc_classify_features(_p(f), C.c_int64(P), C.c_int(D), _p(t), C.c_int(t.shape[0]),
                                 labels.ctypes.data_as(C.POINTER(C.c_int64)), _p(margin))
     return labels.reshape(f.shape[:-1]), margin.reshape(f.shape[:-1])
+
+
+def render_per_pixel(rays_o, rays_d_unit, geom, tile_offsets, prims, W, H, tile, thr, weights, freq, att, precision=0):
+    """Per-pixel exact ordering (render_tiles_kernel_with_sort, np_tile_kernels.cu:714-926).
+    Returns (rgb [P,3], alpha [P], hits per pixel [P], overflow flag)."""
+    ro, rd, geom = _f32(rays_o), _f32(rays_d_unit), _f32(geom)
+    off, sp = _i32(tile_offsets), _i32(prims)
+    W1, b1, W2, b2, W3, b3 = [_f32(w) for w in weights]
+    freq, att = _f32(freq), _f32(att)
+    mlp = _Mlp(_p(W1), _p(b1), _p(W2), _p(b2), _p(W3), _p(b3), _p(freq), _p(att),
+               freq.size, W1.shape[1], 12 * freq.size, precision)
+    P = W * H
+    rgb = np.zeros((P, 3), np.float32)
+    alpha = np.zeros(P, np.float32)
+    hits = np.zeros(P, np.int32)
+    ovf = C.c_int32(0)
+    lib().orc_render_per_pixel(_p(ro), _p(rd), _p(geom), C.c_int(geom.shape[0]), _p(off, C.c_int32), _p(sp, C.c_int32),
+                               C.c_int(W), C.c_int(H), C.c_int(tile), C.c_float(thr), C.byref(mlp), _p(rgb), _p(alpha),
+                               _p(hits, C.c_int32), C.byref(ovf))
+    return rgb, alpha, hits, bool(ovf.value)

@@ -195,3 +195,42 @@ def test_overflowing_scene_reports_capacity():
     f = oracle_frame(scene, cam, 5e-3)
     bits, mx = f["status"]
     assert bits == 2 and mx > 1536
+
+
+def test_per_pixel_order_oracle_invariants():
+    """Per-pixel exact ordering (np_tile_kernels.cu:714-926): hit counts are the popcounts of the geometric hit masks,
+    the order of the candidate list only matters for equal hit distances, a pixel that sees a single primitive
+    composites it exactly like the tile-centre order, and the 257th hit raises the overflow flag.  (The blend
+    itself is pinned on the GPU against the reference's own render_tiles_forward kernel.)"""
+    from tests.helpers import WKEYS, popcount64
+    scene, cam = small_case(n=1200, W=64, H=48, mu=-3.4, seed=5)
+    f = oracle_frame(scene, cam, 5e-3, precision=0)
+    r = f["render"]
+    W, H = cam["W"], cam["H"]
+    args = (cam["rays_o"], f["rays_d_unit"], f["geom"], f["tile_offsets"])
+    tail = (W, H, 8, 5e-3, [scene[k] for k in WKEYS], scene["freq"], scene["att"])
+    rgb, alpha, hits, ovf = orc.render_per_pixel(*args, f["tile_prims"], *tail)
+    assert not ovf and int(hits.sum()) == int(popcount64(r.mask_geo).sum())
+    # hits per pixel from the masks: bit ly*8+lx of every pair of the pixel's tile
+    ntx = (W + 7) // 8
+    per_px = np.zeros(W * H, np.int64)
+    tile_of_pair = np.repeat(np.arange(f["tile_offsets"].size - 1), np.diff(f["tile_offsets"]))
+    for k in range(64):
+        lx, ly = k % 8, k // 8
+        x = (tile_of_pair % ntx) * 8 + lx
+        y = (tile_of_pair // ntx) * 8 + ly
+        ok = ((r.mask_geo >> np.uint64(k)) & np.uint64(1)).astype(bool) & (x < W) & (y < H)
+        np.add.at(per_px, (y * W + x)[ok], 1)
+    np.testing.assert_array_equal(per_px, hits)
+    # the depth-sorted list gives the same image unless hit distances tie
+    rgb2, alpha2, _h, _o = orc.render_per_pixel(*args, f["sorted_prims"], *tail)
+    assert np.abs(rgb2 - rgb).max() < 1e-6 and np.abs(alpha2 - alpha).max() < 1e-6
+    single = hits == 1
+    assert single.sum() > 50
+    np.testing.assert_array_equal(rgb[single], r.rgb[single])
+    assert 0.0 <= alpha.min() and alpha.max() <= 1.0
+    scene, cam = small_case(n=1400, W=48, H=32, mu=-1.7, seed=32, az=250.0)
+    f = oracle_frame(scene, cam, 5e-3, want_masks=False)
+    *_x, hits, ovf = orc.render_per_pixel(cam["rays_o"], f["rays_d_unit"], f["geom"], f["tile_offsets"], f["tile_prims"],
+                                          cam["W"], cam["H"], 8, 5e-3, [scene[k] for k in WKEYS], scene["freq"], scene["att"])
+    assert ovf and hits.max() == 256

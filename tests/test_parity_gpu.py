@@ -676,3 +676,82 @@ def test_hidden_64_tensor_core_evaluator(dev):
     rgb32, _ = r.render(ps, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"], precision=L.PRECISION_F32)
     np.testing.assert_allclose(rgb32.cpu().numpy(), f32["render"].rgb, atol=IMG_TOL_F32)
     assert r.f32_fallbacks == 0
+
+
+@pytest.mark.parametrize("name,precision", [("tiny", 0), ("ragged", 0), ("dense", 0), ("one_tile", 0), ("tiny", 1)])
+def test_per_pixel_order_matches_oracle(dev, name, precision):
+    """Per-pixel exact ordering (render_tiles_kernel_with_sort, np_tile_kernels.cu:714-926): sort_key = 2, from
+    binning (mlpsp_render_frame, tile pre-test on) and from given lists; every hit is evaluated."""
+    from mlp_splatting_b200 import _lib as L
+    from oracle import oracle as orc
+    scene, cam = small_case(**CASES[name])
+    f = oracle_frame(scene, cam, 5e-3, precision=precision, want_masks=False)
+    want_rgb, want_a, hits, ovf = orc.render_per_pixel(cam["rays_o"], f["rays_d_unit"], f["geom"], f["tile_offsets"],
+                                                       f["tile_prims"], cam["W"], cam["H"], 8, 5e-3,
+                                                       [scene[k] for k in WKEYS], scene["freq"], scene["att"],
+                                                       precision=precision)
+    assert not ovf
+    # the order matters: the tile-centre image is a different image
+    assert np.abs(want_rgb - f["render"].rgb).max() > 0.02
+    ps, r = _packed(scene, dev, pack_f16=bool(precision)), _renderer(cam, dev)
+    tol = IMG_TOL_F32 if precision == 0 else 1e-3
+    rgb, alpha = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, view=cam["view"], proj=cam["proj"],
+                          precision=precision, sort_key=L.ORDER_PER_PIXEL)
+    np.testing.assert_allclose(rgb.cpu().numpy(), want_rgb, atol=tol)
+    np.testing.assert_allclose(alpha.cpu().numpy().reshape(-1), want_a, atol=tol)
+    assert r.last_stats.records == int(hits.sum()) and r.last_stats.waves == 1
+    rgb2, alpha2 = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, precision=precision,
+                            tile_lists=(_t(f["tile_prims"], dev), _t(f["tile_offsets"], dev)), sort_key=L.ORDER_PER_PIXEL)
+    np.testing.assert_allclose(rgb2.cpu().numpy(), want_rgb, atol=tol)
+    # the next tile-centre frame is unaffected by the one-wave frame before it
+    rgb3, _a3 = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, view=cam["view"], proj=cam["proj"],
+                         precision=precision)
+    np.testing.assert_allclose(rgb3.cpu().numpy(), f["render"].rgb, atol=tol)
+
+
+def test_per_pixel_order_limits(dev):
+    """More than 256 hits in a pixel is an error like the reference's (np_tile_kernels.cu:4591-4599); depth,
+    features and the other extras belong to the tile-centre order."""
+    from mlp_splatting_b200 import _lib as L
+    from mlp_splatting_b200.engine import RenderError
+    from oracle import oracle as orc
+    scene, cam = small_case(n=1400, W=48, H=32, mu=-1.7, seed=32, az=250.0)
+    f = oracle_frame(scene, cam, 5e-3, want_masks=False)
+    assert f["status"][0] == 0
+    *_x, ovf = orc.render_per_pixel(cam["rays_o"], f["rays_d_unit"], f["geom"], f["tile_offsets"], f["tile_prims"], cam["W"],
+                                    cam["H"], 8, 5e-3, [scene[k] for k in WKEYS], scene["freq"], scene["att"])
+    assert ovf
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    args = (ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3)
+    with pytest.raises(RenderError, match="per-pixel intersection capacity 256 exceeded"):
+        r.render(*args, view=cam["view"], proj=cam["proj"], precision=0, sort_key=L.ORDER_PER_PIXEL)
+    r.render(*args, view=cam["view"], proj=cam["proj"], precision=0)          # the tile-centre order has no such limit
+    with pytest.raises(RuntimeError, match="rgb and alpha only"):
+        r.render(*args, view=cam["view"], proj=cam["proj"], precision=0, sort_key=L.ORDER_PER_PIXEL, want_depth=True)
+
+
+def test_module_per_pixel_order_mode(dev):
+    """tile_order_mode_override = 'per_pixel' (cumodel.py:792-803) routes forward through the per-pixel order."""
+    from mlp_splatting_b200.cumodel import NeuralPrimitiveSceneTileCUDA
+    from oracle import oracle as orc
+    scene, cam = small_case(**CASES["tiny"])
+    m = NeuralPrimitiveSceneTileCUDA(num_primitives=scene["positions"].shape[0], precision="fp32").to(dev)
+    with torch.no_grad():
+        for k in ("positions", "log_scales", "quats") + WKEYS:
+            getattr(m, k).copy_(_t(scene[k], dev))
+    m.set_image_size(cam["W"], cam["H"])
+    m.tile_order_mode_override = "per_pixel"
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    want_rgb, _a, _h, _o = orc.render_per_pixel(cam["rays_o"], f["rays_d_unit"], f["geom"], f["tile_offsets"], f["tile_prims"],
+                                                cam["W"], cam["H"], 8, 5e-3, [scene[k] for k in WKEYS], scene["freq"],
+                                                scene["att"])
+    rgb = m(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3,
+            view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
+    np.testing.assert_allclose(rgb.cpu().numpy(), want_rgb, atol=IMG_TOL_F32)
+    with pytest.raises(ValueError, match="rgb and alpha only"):
+        m.render_rgb_t_no_grad(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3,
+                               view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
+    m.tile_order_mode_override = "nonsense"
+    with pytest.raises(ValueError, match="Unknown tile order mode"):
+        m(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3,
+          view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))

@@ -177,3 +177,20 @@ def test_bf16_forward_matches_reference_wmma_kernel(ref):
     d = (rgb - rgb_r).abs()
     assert d.max().item() <= 1.5e-2 and d.mean().item() <= 3e-4, (d.max().item(), d.mean().item())
     assert (alpha - alpha_r).abs().max().item() <= 1.5e-2
+
+
+@pytest.mark.parametrize("name", ["tiny", "ragged", "dense"])
+def test_per_pixel_order_matches_reference_kernel(ref, name):
+    """render_tiles_forward (per-pixel sort, np_tile_kernels.cu:714-926) vs sort_key = 2 of this library, FP32."""
+    from mlp_splatting_b200 import _lib as L
+    dev = torch.device("cuda", 0)
+    scene, cam = small_case(**CASES[name])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    x = _inputs(scene, cam, f, dev)
+    rgb_r, alpha_r = ref.render_tiles_forward(*x, cam["W"], cam["H"], 8, 8, 5e-3)
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    rgb, alpha = r.render(ps, x[0], x[1], 5e-3, precision=0, tile_lists=(x[5], x[6]), rays_normalized=True,
+                          sort_key=L.ORDER_PER_PIXEL)
+    d_rgb = (rgb - rgb_r).abs().max().item()
+    d_a = (alpha - alpha_r).abs().max().item()
+    assert d_rgb <= 1e-4 and d_a <= 1e-4, (d_rgb, d_a)
