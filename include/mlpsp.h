@@ -122,7 +122,7 @@ typedef struct mlpsp_frame {
                              of render_tiles_kernel_tilecenter_order_with_t (np_tile_kernels.cu:5538-5543);
                              2 (MLPSP_ORDER_PER_PIXEL) = per-pixel exact ordering, render_tiles_kernel_with_sort
                              (np_tile_kernels.cu:714-926): every pixel blends its own hits in the order of its own
-                             hit distances; rgb and alpha only, every hit is evaluated (size max_records for all
+                             hit distances; rgb, alpha and the feature map only, every hit is evaluated (size max_records for all
                              hits of the frame), more than 256 hits in a pixel raise MLPSP_ST_PIXEL_HITS */
   int32_t tile_row_begin; /* binning keeps only tile rows [tile_row_begin, tile_row_end); both 0 = the whole image. */
   int32_t tile_row_end;   /* Used to share one view between GPUs by bands of tile rows: tiles outside the band get

@@ -517,12 +517,14 @@ __global__ void __launch_bounds__(64) k_composite(
 // (t, record slot) pairs in list order -- at most kPixelHits, one more raises MLPSP_ST_PIXEL_HITS and the pixel
 // blends what it has, as the reference's kernel does before its wrapper raises -- sorts them with the
 // reference's stable insertion sort (ties keep list order) and blends until the transmittance falls below 1e-3.
+// With a feature map (render_tiles_kernel_with_sort_and_feat) the consumed records and their weights are left for
+// k_feature_composite, whose sum does not depend on the order.
 constexpr int kPixelHits = 256;
 __global__ void __launch_bounds__(64) k_composite_per_pixel(
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, int T, int W, int H, int ntx,
     const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base, const float4* __restrict__ rec_out,
     const float* __restrict__ rec_t, float* __restrict__ rgb, float* __restrict__ alpha, float bgr, float bgg, float bgb,
-    int has_bg, int32_t* __restrict__ status) {
+    int has_bg, uint32_t* __restrict__ used32, float* __restrict__ rec_w, int32_t* __restrict__ status) {
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int lane = threadIdx.x & 31, half = threadIdx.x >> 5;
   const uint32_t lt = (1u << lane) - 1u;
@@ -531,6 +533,7 @@ __global__ void __launch_bounds__(64) k_composite_per_pixel(
     const TilePix tp = tile_pixel(tile, half * 32 + lane, ntx, W, H);
     float key[kPixelHits];
     uint32_t slot[kPixelHits];
+    uint16_t pair[kPixelHits];               // position in the tile's list (< 2048), for the consumed masks
     int cnt = 0;
     bool over = false;
     int used = 0;
@@ -542,6 +545,7 @@ __global__ void __launch_bounds__(64) k_composite_per_pixel(
           const uint32_t sl = pair_base[s + i] + (half ? __popc(m0) : 0) + __popc(mine & lt);
           key[cnt] = rec_t[sl];
           slot[cnt] = sl;
+          pair[cnt] = (uint16_t)i;
           ++cnt;
         } else {
           over = true;
@@ -552,16 +556,23 @@ __global__ void __launch_bounds__(64) k_composite_per_pixel(
     for (int i = 1; i < cnt; ++i) {
       const float kt = key[i];
       const uint32_t ks = slot[i];
+      const uint16_t kp = pair[i];
       int j = i - 1;
-      while (j >= 0 && key[j] > kt) { key[j + 1] = key[j]; slot[j + 1] = slot[j]; --j; }
+      while (j >= 0 && key[j] > kt) { key[j + 1] = key[j]; slot[j + 1] = slot[j]; pair[j + 1] = pair[j]; --j; }
       key[j + 1] = kt;
       slot[j + 1] = ks;
+      pair[j + 1] = kp;
     }
     float cr = 0.f, cg = 0.f, cb = 0.f, trans = 1.f;
     for (int i = 0; i < cnt; ++i) {
       const float4 r = rec_out[slot[i]];
       const float w = trans * r.w;
       cr = fmaf(w, r.x, cr); cg = fmaf(w, r.y, cg); cb = fmaf(w, r.z, cb);
+      if (rec_w) {
+        // the feature pass adds w * (gated attributes) for every consumed record, whatever their order
+        rec_w[slot[i]] = w;
+        atomicOr(used32 + 2 * (size_t)(s + pair[i]) + half, 1u << lane);
+      }
       trans *= (1.f - r.w);
       ++used;
       if (trans < MLPSP_TERM) break;
@@ -768,8 +779,8 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   const bool want_stats = fr->stat_sum_w != nullptr;
   const bool per_pixel = fr->sort_key == MLPSP_ORDER_PER_PIXEL;
   if (per_pixel) {
-    MLPSP_REQUIRE(!want_feat && !keep && !want_stats && !fr->mask_used && !want_t, MLPSP_E_ARG,
-                  "per-pixel ordering renders rgb and alpha only");
+    MLPSP_REQUIRE(!keep && !want_stats && !fr->mask_used && !want_t, MLPSP_E_ARG,
+                  "per-pixel ordering renders rgb, alpha and the feature map only");
     MLPSP_REQUIRE(fr->tile_capacity <= kWinMax, MLPSP_E_LIMIT, "per-pixel ordering needs tile_capacity <= %d", kWinMax);
   }
   if (want_stats)
@@ -839,7 +850,8 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
       LaunchScope scope(kKComposite, 1, st);
       k_composite_per_pixel<<<std::min(T, sms * 32), 64, 0, st>>>(fr->tile_offsets, s.tile_len, T, W, H, ntx, s.masks32, s.pair_base,
                                                                  s.rec_out, s.rec_t, fr->rgb, fr->alpha, bg[0], bg[1], bg[2],
-                                                                 has_bg, fr->status);
+                                                                 has_bg, want_feat ? used32 : nullptr,
+                                                                 want_feat ? s.rec_w : nullptr, fr->status);
       break;
     }
     { LaunchScope scope(kKComposite, 1, st);

@@ -203,9 +203,9 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
         device = self._activate_cuda_device()
         if self._resolve_tile_order_mode() == "per_pixel":
             # render_tiles_forward (np_tile_kernels.cu:714-926): every pixel blends its own hits in its own order
-            if want_depth or want_feat or stats is not None:
-                raise ValueError("per_pixel ordering renders rgb and alpha only here; use MLPSP_TILE_ORDER=tilecenter "
-                                 "for depth, feature maps and contribution statistics")
+            if want_depth or stats is not None:
+                raise ValueError("per_pixel ordering renders rgb, alpha and the feature map only here; use "
+                                 "MLPSP_TILE_ORDER=tilecenter for depth and contribution statistics")
             sort_key = L.ORDER_PER_PIXEL
         T = ((W + 7) // 8) * ((H + 7) // 8)
         lists = None

@@ -800,7 +800,8 @@ void orc_classify_features(const float* feat, int64_t P, int D, const float* tex
  * ------------------------------------------------------------------------------------------- */
 void orc_render_per_pixel(const float* rays_o, const float* rays_d, const float* geom, int n,
                           const int32_t* tile_offsets, const int32_t* prims, int W, int H, int ts, float thr,
-                          const mlp_t* mlp, float* rgb, float* alpha, int32_t* hits_per_pixel, int32_t* overflow) {
+                          const mlp_t* mlp, float* rgb, float* alpha, int32_t* hits_per_pixel, int32_t* overflow,
+                          const float* feat_attr, int feat_slots, int feat_dim, float beta, float tau, float* feat) {
   const int ntx = (W + ts - 1) / ts;
   int any_overflow = 0;
   #pragma omp parallel for schedule(dynamic, 64) reduction(|:any_overflow)
@@ -832,6 +833,24 @@ void orc_render_per_pixel(const float* rays_o, const float* rays_d, const float*
       const float al = 1.f - expf(-(mo.sigma_raw * hh[i].decay));
       const float w = trans * al;
       C0 = fmaf(w, mo.R, C0); C1 = fmaf(w, mo.G, C1); C2 = fmaf(w, mo.B, C2);
+      if (feat) {
+        /* the gated attribute mix of the tile-centre feature kernel (np_tile_kernels.cu:97-124, 6036-6075), which
+           render_tiles_kernel_with_sort_and_feat applies in the per-pixel order */
+        const int Cf = feat_dim, S = feat_slots;
+        float* dst = feat + pix * Cf;
+        const float* fa = feat_attr + (size_t)hp[i] * S * Cf;
+        if (S <= 1) { for (int c = 0; c < Cf; ++c) dst[c] = fmaf(w, fa[c], dst[c]); }
+        else {
+          float gt[4]; tetra_gates(&hh[i], geom + (size_t)hp[i] * 16, beta, tau, gt);
+          const int b = (S == 5) ? 1 : 0;
+          for (int c = 0; c < Cf; ++c) {
+            float mix = (S == 5) ? fa[c] : 0.f;
+            mix = fmaf(gt[0], fa[(b + 0) * Cf + c], mix); mix = fmaf(gt[1], fa[(b + 1) * Cf + c], mix);
+            mix = fmaf(gt[2], fa[(b + 2) * Cf + c], mix); mix = fmaf(gt[3], fa[(b + 3) * Cf + c], mix);
+            dst[c] = fmaf(w, mix, dst[c]);
+          }
+        }
+      }
       trans *= (1.f - al);
       if (trans < ORC_TERM) break;
     }

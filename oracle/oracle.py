@@ -322,9 +322,11 @@ def classify_features(feat, text):
     return labels.reshape(f.shape[:-1]), margin.reshape(f.shape[:-1])
 
 
-def render_per_pixel(rays_o, rays_d_unit, geom, tile_offsets, prims, W, H, tile, thr, weights, freq, att, precision=0):
+def render_per_pixel(rays_o, rays_d_unit, geom, tile_offsets, prims, W, H, tile, thr, weights, freq, att, precision=0,
+                     feat_attr=None, beta=1.5, tau=2.0):
     """Per-pixel exact ordering (render_tiles_kernel_with_sort, np_tile_kernels.cu:714-926).
-    Returns (rgb [P,3], alpha [P], hits per pixel [P], overflow flag)."""
+    Returns (rgb [P,3], alpha [P], hits per pixel [P], overflow flag), plus the feature map [P,C] when feat_attr
+    is given (render_tiles_kernel_with_sort_and_feat)."""
     ro, rd, geom = _f32(rays_o), _f32(rays_d_unit), _f32(geom)
     off, sp = _i32(tile_offsets), _i32(prims)
     W1, b1, W2, b2, W3, b3 = [_f32(w) for w in weights]
@@ -336,7 +338,19 @@ def render_per_pixel(rays_o, rays_d_unit, geom, tile_offsets, prims, W, H, tile,
     alpha = np.zeros(P, np.float32)
     hits = np.zeros(P, np.int32)
     ovf = C.c_int32(0)
+    fa = feat = None
+    S = Cf = 0
+    if feat_attr is not None:
+        fa = _f32(feat_attr)
+        if fa.ndim == 2:
+            fa = fa[:, None, :]
+        fa = np.ascontiguousarray(fa)
+        S, Cf = fa.shape[1], fa.shape[2]
+        feat = np.zeros((P, Cf), np.float32)
     lib().orc_render_per_pixel(_p(ro), _p(rd), _p(geom), C.c_int(geom.shape[0]), _p(off, C.c_int32), _p(sp, C.c_int32),
                                C.c_int(W), C.c_int(H), C.c_int(tile), C.c_float(thr), C.byref(mlp), _p(rgb), _p(alpha),
-                               _p(hits, C.c_int32), C.byref(ovf))
+                               _p(hits, C.c_int32), C.byref(ovf), _p(fa), C.c_int(S), C.c_int(Cf), C.c_float(beta),
+                               C.c_float(tau), _p(feat))
+    if feat_attr is not None:
+        return rgb, alpha, hits, bool(ovf.value), feat
     return rgb, alpha, hits, bool(ovf.value)

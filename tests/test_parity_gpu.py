@@ -726,7 +726,7 @@ def test_per_pixel_order_limits(dev):
     with pytest.raises(RenderError, match="per-pixel intersection capacity 256 exceeded"):
         r.render(*args, view=cam["view"], proj=cam["proj"], precision=0, sort_key=L.ORDER_PER_PIXEL)
     r.render(*args, view=cam["view"], proj=cam["proj"], precision=0)          # the tile-centre order has no such limit
-    with pytest.raises(RuntimeError, match="rgb and alpha only"):
+    with pytest.raises(RuntimeError, match="feature map only"):
         r.render(*args, view=cam["view"], proj=cam["proj"], precision=0, sort_key=L.ORDER_PER_PIXEL, want_depth=True)
 
 
@@ -748,10 +748,32 @@ def test_module_per_pixel_order_mode(dev):
     rgb = m(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3,
             view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
     np.testing.assert_allclose(rgb.cpu().numpy(), want_rgb, atol=IMG_TOL_F32)
-    with pytest.raises(ValueError, match="rgb and alpha only"):
+    with pytest.raises(ValueError, match="feature map only"):
         m.render_rgb_t_no_grad(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3,
                                view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
     m.tile_order_mode_override = "nonsense"
     with pytest.raises(ValueError, match="Unknown tile order mode"):
         m(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3,
           view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
+
+
+@pytest.mark.parametrize("slots,C", [(4, 64), (1, 20), (5, 300)])
+def test_per_pixel_feature_map_matches_oracle(dev, slots, C):
+    """render_tiles_kernel_with_sort_and_feat: the gated attribute sum over the records a pixel consumes in its own order."""
+    from mlp_splatting_b200 import _lib as L
+    from oracle import oracle as orc
+    scene, cam = small_case(**CASES["ragged"])
+    rng = np.random.default_rng(C)
+    fa = rng.normal(0, 0.2, (scene["positions"].shape[0], slots, C)).astype(np.float32)
+    scene = dict(scene, feat_attr=fa if slots > 1 else fa[:, 0, :])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    want_rgb, want_a, _hits, ovf, want_feat = orc.render_per_pixel(
+        cam["rays_o"], f["rays_d_unit"], f["geom"], f["tile_offsets"], f["tile_prims"], cam["W"], cam["H"], 8, 5e-3,
+        [scene[k] for k in WKEYS], scene["freq"], scene["att"], feat_attr=fa)
+    assert not ovf
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    rgb, _alpha = r.render(ps, _t(cam["rays_o"], dev), _t(cam["rays_d"], dev), 5e-3, view=cam["view"], proj=cam["proj"],
+                           precision=0, want_feat=True, sort_key=L.ORDER_PER_PIXEL)
+    np.testing.assert_allclose(rgb.cpu().numpy(), want_rgb, atol=IMG_TOL_F32)
+    np.testing.assert_allclose(r.feat.cpu().numpy(), want_feat, rtol=0, atol=2e-5)
+    assert np.abs(want_feat).max() > 0.05

@@ -194,3 +194,24 @@ def test_per_pixel_order_matches_reference_kernel(ref, name):
     d_rgb = (rgb - rgb_r).abs().max().item()
     d_a = (alpha - alpha_r).abs().max().item()
     assert d_rgb <= 1e-4 and d_a <= 1e-4, (d_rgb, d_a)
+
+
+@pytest.mark.parametrize("slots,C", [(4, 96), (1, 40), (5, 33)])
+def test_per_pixel_feature_map_matches_reference_kernel(ref, slots, C):
+    """render_tiles_forward_per_pixel_with_feat (per-pixel sort + gated attributes) vs sort_key = 2 with a feature map."""
+    from mlp_splatting_b200 import _lib as L
+    dev = torch.device("cuda", 0)
+    scene, cam = small_case(**CASES["ragged"])
+    rng = np.random.default_rng(7 + C)
+    fa = rng.normal(0, 0.2, (scene["positions"].shape[0], slots, C)).astype(np.float32)
+    scene = dict(scene, feat_attr=fa if slots > 1 else fa[:, 0, :])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    x = _inputs(scene, cam, f, dev)
+    fa_ref = _t(fa if slots > 1 else fa[:, 0, :], dev)          # one slot is a 2-D tensor for the reference
+    rgb_r, alpha_r, feat_r = ref.render_tiles_forward_per_pixel_with_feat(*x, fa_ref, 1.5, 2.0, cam["W"], cam["H"], 8, 8, 5e-3)
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    rgb, alpha = r.render(ps, x[0], x[1], 5e-3, precision=0, tile_lists=(x[5], x[6]), rays_normalized=True, want_feat=True,
+                          sort_key=L.ORDER_PER_PIXEL)
+    assert (rgb - rgb_r).abs().max().item() <= 1e-4 and (alpha - alpha_r).abs().max().item() <= 1e-4
+    assert (r.feat - feat_r.reshape(r.feat.shape)).abs().max().item() <= 1e-4
+    assert feat_r.abs().max().item() > 0.05
