@@ -603,6 +603,7 @@ constexpr int kFeatBatch = 256;    // consumed records staged per barrier (one p
 constexpr int kFeatChan = 256;     // channels per CTA: (tile, channel block) pairs make the grid
 
 // Shared memory: [64][CB] accumulators, then the tile's consumed masks and their record prefix.
+template <bool VEC4>
 __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
     const uint32_t* __restrict__ used32, const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base,
@@ -620,6 +621,9 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int tile = blockIdx.x, c0 = blockIdx.y * CB;
   const int nc = min(CB, C - c0);
+  // VEC4 (launched for maps of at least 256 channels, a multiple of 4): full 256-channel blocks take the
+  // four-channels-per-thread path; narrower blocks measured no faster with it and keep the leaner kernel
+  const bool vec4 = VEC4 && nc == kFeatChan;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < 64 * CB; i += kFeatThreads) s_acc[i] = 0.f;
   const int s = tile_offsets[tile];
@@ -683,6 +687,75 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
     // and split the records of a run between them (one primitive touches a pixel at most once, so the records
     // of a run hit distinct accumulator cells; runs follow one another in warp lockstep).  The attribute rows
     // of run r + 2 are requested before run r is accumulated, so their latency overlaps two runs of arithmetic.
+    if (vec4) {
+      // four adjacent channels per thread: one 16-byte accumulator update serves four channels, and the record
+      // coefficients are read once for them (same operations per channel as below, so the same bits)
+      const int ng = nc >> 2;
+      int RL = 1;
+      while (RL < 32 && 2 * RL * ng <= kFeatThreads) RL *= 2;
+      const int CPW = 32 / RL, rl = lane / CPW;
+      uint32_t wmask = 0xffffffffu;
+      for (int g = warp * CPW + lane % CPW;; g += (kFeatThreads / 32) * CPW) {
+        wmask = __ballot_sync(wmask, g < ng);
+        if (g >= ng) break;
+        const int c = g * 4;
+        const int C4 = C >> 2;
+        auto load_rows = [&](int r, float4 (&a)[5]) {
+          a[0] = a[1] = a[2] = a[3] = a[4] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (r >= nruns) return;
+          const float4* src = reinterpret_cast<const float4*>(feat_attr + (size_t)s_pr[s_run[r]] * S * C + c0 + c);
+          a[0] = __ldg(src);
+          if (S >= 4) { a[1] = __ldg(src + C4); a[2] = __ldg(src + 2 * C4); a[3] = __ldg(src + 3 * C4); }
+          if (S == 5) a[4] = __ldg(src + 4 * C4);
+        };
+        float4 a_cur[5], a_n1[5], a_n2[5];
+        load_rows(0, a_cur);
+        load_rows(1, a_n1);
+        for (int r = 0; r < nruns; ++r) {
+          load_rows(r + 2, a_n2);
+          const int j0 = s_run[r], j1 = s_run[r + 1];
+          auto mix = [&](const float (&cw)[5], float a0, float a1, float a2, float a3, float a4) {
+            float v;
+            if (S == 4) {
+              v = cw[1] * a0;
+              v = fmaf(cw[2], a1, v); v = fmaf(cw[3], a2, v); v = fmaf(cw[4], a3, v);
+            } else if (S == 5) {
+              v = cw[0] * a0;
+              v = fmaf(cw[1], a1, v); v = fmaf(cw[2], a2, v); v = fmaf(cw[3], a3, v); v = fmaf(cw[4], a4, v);
+            } else {
+              v = cw[0] * a0;
+            }
+            return v;
+          };
+          auto contribution = [&](int j) {
+            const float cw[5] = {s_cw[j][0], s_cw[j][1], s_cw[j][2], s_cw[j][3], s_cw[j][4]};
+            return make_float4(mix(cw, a_cur[0].x, a_cur[1].x, a_cur[2].x, a_cur[3].x, a_cur[4].x),
+                               mix(cw, a_cur[0].y, a_cur[1].y, a_cur[2].y, a_cur[3].y, a_cur[4].y),
+                               mix(cw, a_cur[0].z, a_cur[1].z, a_cur[2].z, a_cur[3].z, a_cur[4].z),
+                               mix(cw, a_cur[0].w, a_cur[1].w, a_cur[2].w, a_cur[3].w, a_cur[4].w));
+          };
+          int j = j0 + rl;
+          for (; j + RL < j1; j += 2 * RL) {
+            float4* q0 = reinterpret_cast<float4*>(s_acc + s_px[j] * CB + c);
+            float4* q1 = reinterpret_cast<float4*>(s_acc + s_px[j + RL] * CB + c);
+            const float4 v0 = contribution(j), v1 = contribution(j + RL);
+            const float4 x0 = *q0, x1 = *q1;
+            *q0 = make_float4(x0.x + v0.x, x0.y + v0.y, x0.z + v0.z, x0.w + v0.w);
+            *q1 = make_float4(x1.x + v1.x, x1.y + v1.y, x1.z + v1.z, x1.w + v1.w);
+          }
+          for (; j < j1; j += RL) {
+            float4* q0 = reinterpret_cast<float4*>(s_acc + s_px[j] * CB + c);
+            const float4 v0 = contribution(j), x0 = *q0;
+            *q0 = make_float4(x0.x + v0.x, x0.y + v0.y, x0.z + v0.z, x0.w + v0.w);
+          }
+          if (RL > 1) __syncwarp(wmask);
+#pragma unroll
+          for (int q = 0; q < 5; ++q) { a_cur[q] = a_n1[q]; a_n1[q] = a_n2[q]; }
+        }
+      }
+      __syncthreads();
+      continue;
+    }
     int RL = 1;
     while (RL < 32 && 2 * RL * nc <= kFeatThreads) RL *= 2;
     const int CPW = 32 / RL, rl = lane / CPW;
@@ -876,14 +949,21 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     const int CB = std::min(sc->feat_dim, kFeatChan);
     const size_t smem = sizeof(float) * 64 * (size_t)CB;
     if (!attr_set) {
-      MLPSP_CUDA_OK(cudaFuncSetAttribute(k_feature_composite, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * kFeatChan * 4));
+      MLPSP_CUDA_OK(cudaFuncSetAttribute(k_feature_composite<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * kFeatChan * 4));
+      MLPSP_CUDA_OK(cudaFuncSetAttribute(k_feature_composite<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * kFeatChan * 4));
       attr_set = true;
     }
     LaunchScope scope(kKComposite, 1, st);
     const dim3 grid(T, (sc->feat_dim + CB - 1) / CB);
-    k_feature_composite<<<grid, kFeatThreads, smem, st>>>(fr->tile_offsets, s.tile_len, fr->sorted_prims, W, H, ntx, used32, s.masks32,
-                                                         s.pair_base, s.rec_w, s.rec_gate, sc->feat_attr, sc->feat_slots,
-                                                         sc->feat_dim, CB, fr->feat, fr->status);
+    const bool vec = sc->feat_dim >= kFeatChan && (sc->feat_dim & 3) == 0 && (reinterpret_cast<uintptr_t>(sc->feat_attr) & 15) == 0;
+    if (vec)
+      k_feature_composite<true><<<grid, kFeatThreads, smem, st>>>(fr->tile_offsets, s.tile_len, fr->sorted_prims, W, H, ntx, used32, s.masks32,
+                                                                 s.pair_base, s.rec_w, s.rec_gate, sc->feat_attr, sc->feat_slots,
+                                                                 sc->feat_dim, CB, fr->feat, fr->status);
+    else
+      k_feature_composite<false><<<grid, kFeatThreads, smem, st>>>(fr->tile_offsets, s.tile_len, fr->sorted_prims, W, H, ntx, used32, s.masks32,
+                                                                  s.pair_base, s.rec_w, s.rec_gate, sc->feat_attr, sc->feat_slots,
+                                                                  sc->feat_dim, CB, fr->feat, fr->status);
   }
   return cuda_check(cudaGetLastError(), "render_sorted");
 }
