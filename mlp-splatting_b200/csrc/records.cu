@@ -612,7 +612,7 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
   extern __shared__ float s_acc[];                 // [64][CB]
   __shared__ uint32_t s_u[2][kWinMax];             // consumed masks of the tile's pairs
   __shared__ int32_t s_pref[kWinMax + 1];          // records before pair i
-  __shared__ float s_cw[kFeatBatch][5];            // per staged record: base weight + 4 gated weights
+  __shared__ __align__(16) float s_cw[kFeatBatch][8];   // per staged record: base weight + 4 gated weights (+ padding)
   __shared__ int s_px[kFeatBatch];                 // its pixel
   __shared__ int s_pr[kFeatBatch];                 // its primitive
   __shared__ int s_run[kFeatBatch + 1];            // first staged record of every run of equal primitives
@@ -728,7 +728,8 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
             return v;
           };
           auto contribution = [&](int j) {
-            const float cw[5] = {s_cw[j][0], s_cw[j][1], s_cw[j][2], s_cw[j][3], s_cw[j][4]};
+            const float4 c03 = *reinterpret_cast<const float4*>(&s_cw[j][0]);
+            const float cw[5] = {c03.x, c03.y, c03.z, c03.w, s_cw[j][4]};
             return make_float4(mix(cw, a_cur[0].x, a_cur[1].x, a_cur[2].x, a_cur[3].x, a_cur[4].x),
                                mix(cw, a_cur[0].y, a_cur[1].y, a_cur[2].y, a_cur[3].y, a_cur[4].y),
                                mix(cw, a_cur[0].z, a_cur[1].z, a_cur[2].z, a_cur[3].z, a_cur[4].z),
