@@ -6,7 +6,7 @@
 // text embeddings and takes the arg-max class per pixel (eval_lseg_table2.py:622-641).  With a 512-wide
 // output that is a 1.67 GB map per 1200x680 frame that exists only to be reduced to one label per pixel.
 //
-// k_decode_tc runs the whole chain per tile of 8 x 16 output pixels (two tiles per pass over the weights) on the tensor cores (tcgen05,
+// k_decode_tc runs the whole chain per tile of 8 x 16 output pixels on the tensor cores (tcgen05,
 // FP32 accumulators in tensor memory, binary16 operands as in the MLP evaluator):
 //   layer 1  D1[180 x Ch] = X[180 x Cin] . W1^T for the tile and its one-pixel halo (two M = 128 MMAs that
 //            overlap on rows 52..127), bias + ReLU, halo pixels outside the image forced to zero (they are
@@ -20,9 +20,9 @@
 //            arg-max_c (M h + T^ b3)_c because the normalisation is one positive factor per pixel, so the
 //            wide feature vector is never formed.
 // Weight blocks (W1, the nine taps, the output chunks; <= 32 KB each) stream from the packed image (L2
-// resident) through a two-deep ring of bulk copies, each block serving the two tiles a CTA works on at a
-// time; a block's buffer is released by the commit of the MMAs that read it.  One CTA per SM (206 KB of
-// shared memory, all 512 tensor-memory columns).
+// resident) through a three-deep ring of bulk copies; a block's buffer is released by the commit of the MMAs
+// that read it.  While the issuing lane walks the nine taps the other warps fetch the next tile's input.  One
+// CTA per SM (225 KB of shared memory, all 512 tensor-memory columns).
 //
 // Every wait on an mbarrier is bounded; when one gives up the CTA raises MLPSP_ST_TIMEOUT, waits
 // (bounded) for its own copies in flight, frees its tensor memory and returns.
@@ -40,7 +40,7 @@ constexpr int kDecThreads = 256;
 constexpr int kColGroups = kDecThreads / 128;                        // warps that share a tensor-memory lane quarter split the columns
 constexpr int kDecBlock = 32768;                                   // one weight block: <= 128 x 128 halves
 constexpr int kDecRing = 3;
-constexpr int kStagePitch = 36;                                    // floats per pixel row of an output staging tile
+constexpr int kStageFloats = 32 * 32;                               // one warp's output staging tile: 32 pixels x 32 columns, 16-byte units XOR-swizzled by pixel
 constexpr int kDecPieces = 8;                                      // bulk copies per weight block (block sizes are multiples of 1 KB)
 constexpr int kDecSub = 1;                                         // tiles that share one pass over the weights
 constexpr int kDecMaxBlocks = 16;                                  // per pass: W1, 9 taps, <= 6 output chunks
@@ -67,7 +67,8 @@ constexpr int kSmHdr = kSmBias + 4 * (2 * kDecMaxDim + kDecMaxOut);   // + 4,096
 constexpr int kSmBar = kSmHdr + 256;
 constexpr int kSmMisc = kSmBar + 16 * 8;
 constexpr int kSmArg = kSmMisc + 64;                                  // [2][128] (value, index) pairs
-constexpr int kDecSmem = kSmArg + kDecSub * kColGroups * 128 * 8;
+constexpr int kSmStage = kSmArg + kDecSub * kColGroups * 128 * 8;     // output staging tiles of the first eight warps
+constexpr int kDecSmem = kSmStage + 8 * kStageFloats * 4;
 static_assert(kDecSmem <= 227 * 1024, "shared memory of the decoder");
 
 static int round_up(int v, int m) { return (v + m - 1) / m * m; }
@@ -298,10 +299,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
   const int total_blocks = n_my * NB;
   const int out_chunks = (n_pad + 127) >> 7;
   const uint32_t idesc_h = instr_desc(128, Ch);
-  // decoded features leave through a staging tile in the input tile's space, so only a text query can fetch the
-  // next input early
   static_assert(kDecSub == 1, "the early fetch of the next input assumes one tile per pass");
-  const bool prefetch = classify;
+  const bool prefetch = true;
   int issued = 0, landed = 0;            // issuing thread only: copies requested / copies waited for
   uint32_t ph_m = 0, ph_o = 0;
   bool ok = true, bad = false;
@@ -396,7 +395,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
     if (!ok) break;
     // ---- layer 2: nine taps, each weight block serves every sub-tile; columns [256 + 128 sb, .. + Ch) ----
     // While one lane issues them, the other warps fetch the next tile's input: layer 1 has finished
-    // reading the input tile, and nothing else uses its space in a text query.
+    // reading the input tile.
     if (warp != 0) {
       if (prefetch && it + 1 < n_my) {
         const int nt = ((int)blockIdx.x + (it + 1) * (int)gridDim.x) * kDecSub;
@@ -476,13 +475,14 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
                 if (col0 + e < n_out && v > best[sb]) { best[sb] = v; arg[sb] = col0 + e; }
               }
             } else {
-              // 32 pixels x 32 columns of this warp go through a staging tile (the input tile's space: layer 1
-              // has long finished) so that eight lanes write one pixel's 128 contiguous bytes
-              float* stg = reinterpret_cast<float*>(smem + kSmA0) + warp * (32 * kStagePitch);
+              // 32 pixels x 32 columns of this warp go through a staging tile so that eight lanes write one pixel's
+              // 128 contiguous bytes; the 16-byte unit u of pixel row l sits at unit u ^ (l & 7): both the row
+              // writes and the transposed reads touch every bank once per eight lanes
+              float* stg = reinterpret_cast<float*>(smem + kSmStage) + warp * kStageFloats;
               __syncwarp();
 #pragma unroll
               for (int e = 0; e < 32; e += 4)
-                *reinterpret_cast<float4*>(stg + lane * kStagePitch + e) =
+                *reinterpret_cast<float4*>(stg + lane * 32 + (((e >> 2) ^ (lane & 7)) << 2)) =
                     make_float4(__uint_as_float(acc[e]) + b3[e], __uint_as_float(acc[e + 1]) + b3[e + 1],
                                 __uint_as_float(acc[e + 2]) + b3[e + 2], __uint_as_float(acc[e + 3]) + b3[e + 3]);
               __syncwarp();
@@ -492,7 +492,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) k_decode_tc(
                 const int ml = rr + (lane >> 3), mm = q * 32 + ml;            // pixel of the tile this lane writes for
                 const int oy = ty0[sb] + (mm >> 3), ox = tx0[sb] + (mm & 7);
                 if (oy < H && ox < W) {
-                  const float4 v = *reinterpret_cast<const float4*>(stg + ml * kStagePitch + cq);
+                  const float4 v = *reinterpret_cast<const float4*>(stg + ml * 32 + ((((cq >> 2)) ^ (ml & 7)) << 2));
                   float* dst = out + ((int64_t)oy * W + ox) * n_out + col0 + cq;
                   if ((n_out & 3) == 0) {
                     if (col0 + cq < n_out) *reinterpret_cast<float4*>(dst) = v;
