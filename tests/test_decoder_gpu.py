@@ -159,3 +159,21 @@ def test_text_query_view_of_a_scene_gives_the_full_width_labels(dev):
     assert empty.any() and (got[empty] == 0).all() and (want[empty] == 0).all()
     with pytest.raises(ValueError, match="Feature dim mismatch"):
         ps.with_text_query(torch.zeros(3, D + 1))
+
+
+def test_full_size_fused_query_agrees_with_decode_then_query(dev):
+    """At 1200x680 with the 128-128-512 decoder: the fused kernel (text product folded into the last layer) and the
+    two-step route (decoded 512-channel map, then the FP32 full-width query) must label the pixels alike -- they
+    differ only by the binary16 rounding of the folded matrix -- and both must be deterministic."""
+    from mlp_splatting_b200.feature_decoder import classify_feature_map
+    c = dict(in_dim=128, hidden=128, out_dim=512, classes=20, W=1200, H=680, seed=61)
+    dec, w, text, x = _decoder(c, dev)
+    xt, t = torch.from_numpy(x).to(dev), torch.from_numpy(text).to(dev)
+    fused = dec.classify(xt, t)
+    two_step = classify_feature_map(dec.decode_hwc(xt), t)
+    assert fused.shape == (680, 1200) and fused.dtype == torch.int64
+    agree = (fused == two_step).float().mean().item()
+    assert agree >= 0.995, agree
+    assert torch.equal(fused, dec.classify(xt, t))
+    counts = torch.bincount(fused.reshape(-1), minlength=20)
+    assert int((counts > 0).sum()) >= 10            # a real segmentation, not one label
