@@ -4,16 +4,22 @@
 
 A step is one frame of the named workload through the whole path (binning, per-tile sort, record
 waves with the per-primitive MLP, compositing).  `value` is whole-job frames/s with the scene and
-the rays resident in HBM; `e2e` is the same frame through the public host API with the rays
+the rays resident in HBM (the first block of K timed steps; `repeat` holds median and spread over
+further blocks of K steps); `e2e` is the same frame through the public host API with the rays
 arriving from pinned host memory and the image returning to it inside the timed region.  At N > 1
 every rank renders its own view of the replicated scene (weak scaling); the scene is generated on
-rank 0 and broadcast once with NCCL.  `--impl reference` times the CPU restatement of the
-reference's algorithm (oracle/) on the host cores over a bounded band of tile rows.
+rank 0 and broadcast once with NCCL.  The default run adds, under `other_workloads`, short
+measurements of the other named configurations (feature map, four views shared by view and by
+band of tile rows, the 2 M-primitive stress scene).  `--impl reference` times the CPU restatement
+of the reference's algorithm (oracle/) on all host cores over a bounded band of tile rows.
+`--workload decoder_<W>x<H>` (decoder_1200x680) times the step after the feature map alone: fused decoder +
+text query, decoder, full-width query (`--only` picks one).
 """
 from __future__ import annotations
 
 import argparse
 import ctypes as C
+import hashlib
 import json
 import os
 import statistics
@@ -28,12 +34,19 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WK = ("W1", "b1", "W2", "b2", "W3", "b3")
-FLOP_PER_RECORD = 6912          # 2*(72*32 + 32*32 + 32*4): algorithmic MLP work of one record (hidden 32)
+THRESHOLD = 5e-3                # score threshold of the reference's benchmark tool
+HEADLINE = "single_100k_1200x680"
+OTHER_WORKLOADS = ("feature_250k_1200x680", "fourview_500k_1200x680", "stress_2m_1920x1080")
 
 
 def flop_per_record(hidden):
-    return 2 * (72 * hidden + hidden * hidden + hidden * 4)     # 17,920 at hidden 64
-THRESHOLD = 5e-3                # score threshold of the reference's benchmark tool
+    """Algorithmic MLP work of one record: 2*(72*H + H*H + H*4); 6,912 at H = 32, 17,920 at H = 64."""
+    return 2 * (72 * hidden + hidden * hidden + hidden * 4)
+
+
+def weight_image_bytes(hidden):
+    """Bytes of one primitive's packed weight image (biases included), as the evaluator streams it per work item."""
+    return 9472 if hidden == 32 else 22784
 
 
 def peaks():
@@ -42,6 +55,26 @@ def peaks():
         p = json.load(open(path))
         return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+def source_digest(names):
+    h = {}
+    for n in names:
+        with open(os.path.join(ROOT, "mlp-splatting_b200", "csrc", n), "rb") as f:
+            h[n] = hashlib.sha256(f.read()).hexdigest()[:16]
+    return h
+
+
+def ncu_figures(workload):
+    """DRAM traffic and pipe utilisation of the evaluator from the ncu capture summarised under profiles/, or None
+    when there is none for this workload or the kernel's sources have changed since it was taken."""
+    path = os.path.join(ROOT, "profiles", f"k_mlp_tc_{workload}.json")
+    if not os.path.exists(path):
+        return None
+    rec = json.load(open(path))
+    if rec.get("sources_sha256") != source_digest(sorted(rec.get("sources_sha256", {}))):
+        return None
+    return rec
 
 
 class ClockSampler:
@@ -70,13 +103,12 @@ class ClockSampler:
         """Number of samples taken so far (marks the start of a window)."""
         return len(self.lines)
 
-    def stop(self, first=0):
-        """Summary of the samples from index `first` on."""
+    def summary(self, first=0, last=None):
+        """Summary of the samples [first, last)."""
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        self.proc.terminate()
         sm, mx, reasons = [], [], set()
-        for ln in self.lines[first:]:
+        for ln in self.lines[first:last]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -91,10 +123,16 @@ class ClockSampler:
         return dict(sm_mhz=statistics.median(hot) if hot else None, sm_max_mhz=max(mx) if mx else None,
                     reasons=sorted(reasons), samples=len(sm))
 
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
 
 def cpu_baseline(scene, cam, budget_s, steps=1, warmup=0):
-    """Oracle (CPU restatement of the reference algorithm) on a band of tile rows; frames/s scaled to a frame."""
+    """Oracle (CPU restatement of the reference algorithm) on a band of tile rows, on every host core this process
+    may use; frames/s scaled to a frame."""
     from oracle import oracle as orc
+    orc.set_num_threads(orc.host_cores())      # a launcher may have exported OMP_NUM_THREADS=1
     W, H = cam["W"], cam["H"]
     ntx, nty = (W + 7) // 8, (H + 7) // 8
     q = orc.normalize_rows(scene["quats"])
@@ -178,11 +216,13 @@ def run_reference(args):
     per_step = max(2.0, 150.0 / (args.steps + args.warmup + 1))
     cb = cpu_baseline(scene, cams[0], per_step, steps=args.steps, warmup=args.warmup)
     ref_gpu = reference_cuda_kernels(scene, cams[0], min(args.steps, 5))
+    # The job of this arm at N GPUs is the job of the other arm at N GPUs (N views per step when every rank renders
+    # one): the host renders the views one after the other, so its frames/s do not depend on N and one view is sampled.
     line = {
         "impl": "reference", "metric": "frames_per_sec", "value": cb["value"], "unit": "frames/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": workload_config(args.workload, cfg, 1, args.encoder),
+        "scaling": "weak" if int(cfg["views"]) == 1 else "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config(args.workload, cfg, args.gpus, args.encoder),
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "record_mlp_evals_per_sec": cb["evals_per_s"],
@@ -209,15 +249,299 @@ def workload_config(name, cfg, n_gpus, encoder="integrated"):
             "l2": "256 MB flush between timed steps"}
 
 
+def packed_scene_on_device(cfg, dev, lib, chunk=131072):
+    """A scene of the workload's distributions drawn on the device (synthetic.make_scene_device) and packed slice by
+    slice: geometry and the fp16 weight image are kept, the FP32 weight masters of a slice are dropped once packed
+    (2 M primitives with 64-wide layers would be 72 GB of masters)."""
+    import torch
+    from mlp_splatting_b200 import _lib as L
+    from mlp_splatting_b200 import synthetic as syn
+    from mlp_splatting_b200.engine import PackedScene
+    n, H = int(cfg["n"]), int(cfg.get("hidden", 32))
+    geo = syn.make_scene_device(n, cfg["seed"], dev, mu=cfg["mu"], hidden=H, parts=("geometry",))
+    wbytes = int(lib.mlpsp_packed_weight_bytes(H, 6))
+    image = torch.empty(n * wbytes, device=dev, dtype=torch.uint8)
+    status = torch.zeros(L.STATUS_WORDS, device=dev, dtype=torch.int32)
+    st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    for a in range(0, n, chunk):
+        m = min(chunk, n - a)
+        part = syn.make_scene_device(m, cfg["seed"] + 1 + a, dev, hidden=H, parts=("weights",))
+        s = L.Scene()
+        s.n, s.hidden, s.num_freq = m, H, 6
+        s.W1, s.b1, s.W2, s.b2, s.W3, s.b3 = (L.ptr(part[k]) for k in WK)
+        L.check(lib.mlpsp_pack_weights_f16(C.byref(s), image.data_ptr() + a * wbytes, L.ptr(status), st), "mlpsp_pack_weights_f16")
+        torch.cuda.synchronize()
+        del part
+    if int(status[0].item()):
+        raise SystemExit("packing the device-generated scene raised a status bit")
+    return PackedScene.from_packed_image(geo["positions"], geo["log_scales"], geo["quats"], geo["freq"], geo["att"], image, H,
+                                         device=dev)
+
+
+class Workload:
+    """One named workload set up on this rank: scene, work units (view, band of tile rows), renderer."""
+
+    def __init__(self, name, args, dev, world, rank, lib, timed_bcast=False):
+        import torch
+        from mlp_splatting_b200 import _lib as L
+        from mlp_splatting_b200 import sharding, synthetic as syn
+        from mlp_splatting_b200.engine import FrameRenderer, PackedScene
+        self.name, self.dev, self.world, self.rank, self.lib = name, dev, world, rank, lib
+        cfg = self.cfg = dict(syn.WORKLOADS[name])
+        self.prec = L.PRECISION_F16 if args.precision == "fp16" else L.PRECISION_F32
+        self.scene_np, self.bcast_s = None, 0.0
+        if cfg.get("on_device"):
+            if self.prec != L.PRECISION_F16:
+                raise SystemExit(f"{name} is generated on the device and keeps only the fp16 weight image")
+            self.ps = packed_scene_on_device(cfg, dev, lib)
+        else:
+            if rank == 0:
+                self.scene_np = syn.make_scene(cfg["n"], cfg["seed"], mu=cfg["mu"], hidden=cfg.get("hidden", 32),
+                                               feat_dim=cfg.get("feat_dim", 0), pe_sigma=0.01 if args.encoder == "integrated" else 0.0)
+            t_b0 = time.perf_counter()
+            scene_t = sharding.broadcast_scene(self.scene_np, dev, src=0)
+            torch.cuda.synchronize()
+            self.bcast_s = time.perf_counter() - t_b0 if world > 1 else 0.0
+            self.ps = PackedScene(*[scene_t[k] for k in ("positions", "log_scales", "quats") + WK], scene_t["freq"], scene_t["att"],
+                                  feat_attr=scene_t.get("feat_attr"), device=dev, pack_f16=(self.prec == L.PRECISION_F16))
+        # Work units of this rank.  Single-view workloads: one view per rank on the circle of radius 3 (weak
+        # scaling, per-GPU work fixed).  Multi-view workloads: the workload's views are shared between the
+        # ranks, by view and then by band of tile rows (strong scaling, total work fixed).
+        self.nviews = int(cfg["views"])
+        nty = (cfg["H"] + 7) // 8
+        self.want_feat = cfg.get("feat_dim", 0) > 0
+        if self.nviews == 1:
+            # face-on views only (0/90/180/270 degrees): seen along a diagonal the same cube puts more than
+            # 1,536 candidates into some tiles, which the path rejects exactly as the reference does
+            self.units = [(syn.make_camera(cfg["W"], cfg["H"], azimuth_deg=90.0 * (rank % 4)), None)]
+            self.frames_per_step, self.scaling = world, "weak"
+        else:
+            self.units = [(syn.make_camera(cfg["W"], cfg["H"], azimuth_deg=360.0 * v / self.nviews), (r0, r1) if (r0, r1) != (0, nty) else None)
+                          for v, r0, r1 in sharding.assign(self.nviews, nty, world, rank)]
+            self.frames_per_step, self.scaling = self.nviews, "strong"
+        self.cam = self.units[0][0] if self.units else syn.make_camera(cfg["W"], cfg["H"])
+        self.r = FrameRenderer(cfg["W"], cfg["H"], device=dev)
+        self.dev_rays = []
+        for c, _rows in self.units:
+            rd_dev = torch.from_numpy(c["rays_d"]).to(dev)
+            rd_u = torch.empty_like(rd_dev)
+            L.check(lib.mlpsp_normalize_rows(L.ptr(rd_dev), L.ptr(rd_u), self.r.P, 3, None), "normalize")
+            self.dev_rays.append((torch.from_numpy(c["rays_o"]).to(dev), rd_u))
+        # the step after the feature map, for workloads that name a decoder: decoder + text query in one kernel
+        self.dec = self.text = self.labels = None
+        if cfg.get("decoder"):
+            from mlp_splatting_b200.feature_decoder import FeatureUpsampleDecoder
+            dc = cfg["decoder"]
+            dw, dtext = syn.make_decoder(cfg["feat_dim"], dc["hidden"], dc["out_dim"], dc["classes"], seed=dc["seed"])
+            self.dec = FeatureUpsampleDecoder(cfg["feat_dim"], dc["out_dim"], dc["hidden"], device=dev)
+            self.dec.load_state_dict({k: torch.from_numpy(v) for k, v in dw.items()})
+            self.text = torch.from_numpy(dtext).to(dev)
+        self.score_dim = 0
+        if cfg.get("text_query"):
+            tq = cfg["text_query"]
+            qtext = torch.from_numpy(np.random.default_rng(tq["seed"]).normal(size=(tq["classes"], cfg["feat_dim"])).astype(np.float32))
+            self.ps = self.ps.with_text_query(qtext)
+            self.score_dim = tq["classes"]
+
+    def frame(self, check=False):
+        cfg, r = self.cfg, self.r
+        out = None
+        for (c, rows), (ro_u, rd_u) in zip(self.units, self.dev_rays):
+            out = r.render(self.ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=self.prec,
+                           rays_normalized=True, check=check, tile_rows=rows, want_feat=self.want_feat)
+            if self.dec is not None:
+                self.labels = self.dec.classify(r.feat.view(cfg["H"], cfg["W"], cfg["feat_dim"]), self.text, check=check)
+            if self.score_dim:
+                from mlp_splatting_b200.feature_decoder import score_labels
+                self.labels = score_labels(r.feat.view(cfg["H"], cfg["W"], self.score_dim))
+        return out
+
+    def size_and_count(self):
+        """Sizing pass (grows scratch if needed) and the per-step record totals of this rank."""
+        self.frame(check=True)
+        stats = self.r.last_stats
+        if len(self.units) > 1:
+            tot = dict(records=0, used=0, work_total=0)
+            for (c, rows), (ro_u, rd_u) in zip(self.units, self.dev_rays):
+                self.r.render(self.ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=self.prec,
+                              rays_normalized=True, tile_rows=rows, want_feat=self.want_feat)
+                for k in tot:
+                    tot[k] += getattr(self.r.last_stats, k)
+            stats.records, stats.used, stats.work_total = tot["records"], tot["used"], tot["work_total"]
+        self.stats = stats
+        return stats
+
+
+def barrier(world):
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def timed_block(wl, flush, steps, world):
+    """K frames, device time per frame by CUDA events, L2 flushed between frames; max over ranks of the summed time."""
+    import torch
+    import torch.distributed as dist
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    barrier(world)
+    wall0 = time.perf_counter()
+    for a, b in evs:
+        flush.fill_(1)
+        a.record(); wl.frame(); b.record()
+    barrier(world)
+    wall = time.perf_counter() - wall0
+    t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], dtype=torch.float64, device=wl.dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()), wall
+
+
+def class_times(wl, flush, steps):
+    """Per-kernel-class device time (separate pass: event pairs around every launch group)."""
+    import torch
+    from mlp_splatting_b200 import _lib as L
+    lib = wl.lib
+    lib.mlpsp_timing_enable(1)
+    per_class0 = (C.c_int64 * 8)()
+    lib.mlpsp_kernel_launches(per_class0, 8)
+    for _ in range(steps):
+        flush.fill_(1); wl.frame()
+    torch.cuda.synchronize()
+    ms_cls = (C.c_float * 8)()
+    L.check(lib.mlpsp_timing_collect(ms_cls, 8), "timing_collect")
+    lib.mlpsp_timing_enable(0)
+    per_class1 = (C.c_int64 * 8)()
+    lib.mlpsp_kernel_launches(per_class1, 8)
+    return {name: {"ms_per_step": ms_cls[i] / steps, "launches_per_step": (per_class1[i] - per_class0[i]) / steps}
+            for i, name in enumerate(L.KERNEL_CLASSES)}
+
+
+def evaluator_roofline(wl, classes, workload):
+    pk = peaks()
+    stats = wl.stats
+    hidden = int(wl.cfg.get("hidden", 32))
+    mlp_ms = classes["mlp"]["ms_per_step"]
+    n_launch = max(classes["mlp"]["launches_per_step"], 1)
+    flops_step = stats.records * flop_per_record(hidden)
+    achieved_tf = flops_step / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0
+    roofline = {"kernel": "k_mlp_tc (per-primitive MLP, tcgen05)", "bound": "tensor", "achieved": achieved_tf,
+                "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved_tf / pk["bf16_tflops"],
+                "peak_source": pk["source"] + " burst", "traffic": None,
+                "flop_per_launch": flops_step / n_launch, "avg_launch_ms": mlp_ms / n_launch,
+                "share_of_step": mlp_ms / max(sum(c["ms_per_step"] for c in classes.values()), 1e-9)}
+    # Algorithmic bytes of the evaluator: 32 B in + 16 B out per record, one weight image per work item.
+    alg_bytes = stats.records * 48 + stats.work_total * weight_image_bytes(hidden)
+    roofline["hbm_view"] = {"algorithmic_bytes_per_launch": alg_bytes / n_launch,
+                            "achieved_gbs": alg_bytes / (mlp_ms / 1e3) / 1e9 if mlp_ms > 0 else 0.0,
+                            "peak_gbs": pk["hbm_gbs"],
+                            "frac": (alg_bytes / (mlp_ms / 1e3) / 1e9 / pk["hbm_gbs"]) if mlp_ms > 0 else 0.0}
+    rec = ncu_figures(workload)
+    if rec is not None:
+        roofline["traffic"] = rec["dram_bytes_per_frame"] / n_launch
+        roofline["traffic_unit"] = "bytes per launch: ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over a frame's evaluator launches"
+        roofline["ncu_pipes_pct"] = dict(rec["pipes_pct"], source=rec["source"])
+    return roofline
+
+
+def short_measure(name, args, dev, world, rank, lib, flush, steps):
+    """frames/s, ms per step and the evaluator's rate of another named workload (no end-to-end arm)."""
+    import torch
+    import torch.distributed as dist
+    wl = Workload(name, args, dev, world, rank, lib)
+    stats = wl.size_and_count()
+    for _ in range(3):
+        flush.fill_(1); wl.frame()
+    dev_ms, _wall = timed_block(wl, flush, steps, world)
+    classes = class_times(wl, flush, min(steps, 5))
+    bits = int(wl.r.status.cpu()[0])
+    rec_t = torch.tensor([float(stats.records), float(stats.work_total)], dtype=torch.float64, device=dev)
+    if world > 1 and wl.nviews > 1:
+        dist.all_reduce(rec_t)
+    hidden = int(wl.cfg.get("hidden", 32))
+    mlp_ms = classes["mlp"]["ms_per_step"]
+    out = {"frames_per_sec": wl.frames_per_step * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps, "steps": steps,
+           "scaling": wl.scaling, "views_per_step": wl.frames_per_step, "hidden": hidden,
+           "evaluator_tflops_this_rank": stats.records * flop_per_record(hidden) / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0,
+           "records_per_step": float(rec_t[0]), "records_per_evaluator_block": float(rec_t[0]) / max(float(rec_t[1]), 1.0),
+           "kernel_classes_ms": {k: round(v["ms_per_step"], 4) for k, v in classes.items()},
+           "status_bits": bits, "data": "generated on the device" if wl.cfg.get("on_device") else "generated on the host"}
+    del wl
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_decoder(args):
+    """The step after the feature map on its own: fused decoder + text query, decoder alone, full-width query."""
+    import torch
+    from mlp_splatting_b200 import synthetic as syn
+    from mlp_splatting_b200.feature_decoder import FeatureUpsampleDecoder, classify_feature_map
+    dev = torch.device("cuda", 0)
+    cin, hid, cout, ncls = 128, 128, 512, 20
+    try:
+        W, H = (int(v) for v in args.workload.split("_")[-1].split("x"))
+    except ValueError:
+        raise SystemExit("decoder workloads are named decoder_<width>x<height>")
+    w, text = syn.make_decoder(cin, hid, cout, ncls, seed=1)
+    dec = FeatureUpsampleDecoder(cin, cout, hid, device=dev)
+    dec.load_state_dict({k: torch.from_numpy(v) for k, v in w.items()})
+    x = torch.from_numpy(syn.make_feature_map(W, H, cin, seed=2)).to(dev)
+    t = torch.from_numpy(text).to(dev)
+    P = W * H
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    only = args.only
+    flop = 2.0 * P * (cin * hid + 9 * hid * hid + hid * ncls)
+    line = {"metric": "frames_per_sec", "unit": "frames/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"decoder_{cin}_{hid}_{cout}_c{ncls}_{W}x{H}",
+                       "l2": f"input map {P * cin * 4 / 1e6:.0f} MB, decoded map {P * cout * 4 / 1e6:.0f} MB"}}
+    if only in (None, "query"):
+        ms_q = timed(lambda: dec.classify(x, t, check=False))
+        line["fused_query"] = {"ms": ms_q, "algorithmic_tflops": flop / ms_q / 1e9, "bytes_per_pixel": 4 * cin + 8,
+                               "gbs": P * (4 * cin + 8) / ms_q / 1e6}
+        line.update(value=1e3 / ms_q, ms_per_step=ms_q)
+    if only in (None, "decode", "full_width"):
+        y = dec.decode_hwc(x)
+    if only in (None, "decode"):
+        ms_d = timed(lambda: dec.decode_hwc(x, check=False))
+        line["decode"] = {"ms": ms_d, "bytes_per_pixel": 4 * (cin + cout), "gbs": P * 4 * (cin + cout) / ms_d / 1e6}
+        line.setdefault("value", 1e3 / ms_d); line.setdefault("ms_per_step", ms_d)
+    if only in (None, "full_width"):
+        ms_f = timed(lambda: classify_feature_map(y, t))
+        line["full_width_query"] = {"ms": ms_f, "bytes_per_pixel": 4 * cout + 8, "gbs": P * (4 * cout + 8) / ms_f / 1e6}
+        line.setdefault("value", 1e3 / ms_f); line.setdefault("ms_per_step", ms_f)
+    dec._check_status("bench")
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="single_100k_1200x680")
+    ap.add_argument("--workload", default=HEADLINE)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="fp16", choices=["fp16", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true",
+                    help="skip the short measurements of the other named workloads that the default run adds")
+    ap.add_argument("--only", default=None, choices=["query", "decode", "full_width"],
+                    help="decoder workloads: time one of the three steps only")
+    ap.add_argument("--e2e-image", default="f32", choices=["f32", "f16"],
+                    help="format of the image copied back to the host in the end-to-end arm")
     ap.add_argument("--encoder", default="integrated", choices=["integrated", "fourier"],
                     help="integrated: the reference default (bands attenuated by exp(-f^2 sigma^2 / 2), sigma 0.01); "
                          "fourier: unattenuated power-of-two bands")
@@ -225,12 +549,12 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload.startswith("decoder_"):
+        return run_decoder(args)
 
     import torch
     import torch.distributed as dist
     from mlp_splatting_b200 import _lib as L
-    from mlp_splatting_b200 import sharding, synthetic as syn
-    from mlp_splatting_b200.engine import FrameRenderer, PackedScene
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -246,229 +570,134 @@ def main():
     if rank == 0:
         sampler.start()
 
-    cfg = dict(syn.WORKLOADS[args.workload])
-    scene_np = None
-    if rank == 0:
-        scene_np = syn.make_scene(cfg["n"], cfg["seed"], mu=cfg["mu"], hidden=cfg.get("hidden", 32),
-                                  feat_dim=cfg.get("feat_dim", 0), pe_sigma=0.01 if args.encoder == "integrated" else 0.0)
-    t_b0 = time.perf_counter()
-    scene_t = sharding.broadcast_scene(scene_np, dev, src=0)
-    torch.cuda.synchronize()
-    bcast_s = time.perf_counter() - t_b0
-    prec = L.PRECISION_F16 if args.precision == "fp16" else L.PRECISION_F32
-    ps = PackedScene(*[scene_t[k] for k in ("positions", "log_scales", "quats") + WK], scene_t["freq"], scene_t["att"],
-                     feat_attr=scene_t.get("feat_attr"), device=dev, pack_f16=(prec == L.PRECISION_F16))
-    # Work units of this rank.  Single-view workloads: one view per rank on the circle of radius 3 (weak
-    # scaling, per-GPU work fixed).  Multi-view workloads: the workload's views are shared between the
-    # ranks, by view and then by band of tile rows (strong scaling, total work fixed).
-    nviews = int(cfg["views"])
-    nty = (cfg["H"] + 7) // 8
-    want_feat = cfg.get("feat_dim", 0) > 0
-    if nviews == 1:
-        # face-on views only (0/90/180/270 degrees): seen along a diagonal the same cube puts more than
-        # 1,536 candidates into some tiles, which the path rejects exactly as the reference does
-        units = [(syn.make_camera(cfg["W"], cfg["H"], azimuth_deg=90.0 * (rank % 4)), None)]
-        frames_per_step, scaling = world, "weak"
-    else:
-        units = [(syn.make_camera(cfg["W"], cfg["H"], azimuth_deg=360.0 * v / nviews), (r0, r1) if (r0, r1) != (0, nty) else None)
-                 for v, r0, r1 in sharding.assign(nviews, nty, world, rank)]
-        frames_per_step, scaling = nviews, "strong"
-    cam = units[0][0] if units else syn.make_camera(cfg["W"], cfg["H"])
-    r = FrameRenderer(cfg["W"], cfg["H"], device=dev)
-    dev_rays = []
-    for c, _rows in units:
-        rd_dev = torch.from_numpy(c["rays_d"]).to(dev)
-        rd_u = torch.empty_like(rd_dev)
-        L.check(lib.mlpsp_normalize_rows(L.ptr(rd_dev), L.ptr(rd_u), r.P, 3, None), "normalize")
-        dev_rays.append((torch.from_numpy(c["rays_o"]).to(dev), rd_u))
-    ro_h = torch.from_numpy(cam["rays_o"]).pin_memory()
-    rd_h = torch.from_numpy(cam["rays_d"]).pin_memory()
+    wl = Workload(args.workload, args, dev, world, rank, lib)
+    cfg, r, ps, prec = wl.cfg, wl.r, wl.ps, wl.prec
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-
-    # the step after the feature map, for workloads that name a decoder: decoder + text query in one kernel
-    dec = text = labels = None
-    if cfg.get("decoder"):
-        from mlp_splatting_b200.feature_decoder import FeatureUpsampleDecoder
-        dc = cfg["decoder"]
-        dw, dtext = syn.make_decoder(cfg["feat_dim"], dc["hidden"], dc["out_dim"], dc["classes"], seed=dc["seed"])
-        dec = FeatureUpsampleDecoder(cfg["feat_dim"], dc["out_dim"], dc["hidden"], device=dev)
-        dec.load_state_dict({k: torch.from_numpy(v) for k, v in dw.items()})
-        text = torch.from_numpy(dtext).to(dev)
-
-    score_dim = 0
-    if cfg.get("text_query"):
-        from mlp_splatting_b200.feature_decoder import score_labels
-        tq = cfg["text_query"]
-        qtext = torch.from_numpy(np.random.default_rng(tq["seed"]).normal(size=(tq["classes"], cfg["feat_dim"])).astype(np.float32))
-        ps = ps.with_text_query(qtext)
-        score_dim = tq["classes"]
-
-    def frame(check=False):
-        nonlocal labels
-        out = None
-        for (c, rows), (ro_u, rd_u) in zip(units, dev_rays):
-            out = r.render(ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=prec,
-                           rays_normalized=True, check=check, tile_rows=rows, want_feat=want_feat)
-            if dec is not None:
-                labels = dec.classify(r.feat.view(cfg["H"], cfg["W"], cfg["feat_dim"]), text, check=check)
-            if score_dim:
-                labels = score_labels(r.feat.view(cfg["H"], cfg["W"], score_dim))
-        return out
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # sizing pass (grows scratch if needed), then warm-up
-    frame(check=True)
-    stats = r.last_stats
-    if nviews > 1:   # per-step totals over this rank's units
-        tot_rec = tot_used = 0
-        for (c, rows), (ro_u, rd_u) in zip(units, dev_rays):
-            r.render(ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=prec, rays_normalized=True,
-                     tile_rows=rows, want_feat=want_feat)
-            tot_rec += r.last_stats.records; tot_used += r.last_stats.used
-        stats.records, stats.used = tot_rec, tot_used
+    stats = wl.size_and_count()
     for _ in range(args.warmup):
-        flush.fill_(1); frame()
-    barrier()
+        flush.fill_(1); wl.frame()
+    barrier(world)
 
-    # ---- timed region: K frames, device time per frame by CUDA events, L2 flushed between frames ----
+    # ---- timed region: K frames; then further blocks of K frames until a second of device time has been seen ----
     clock_mark = sampler.mark()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     launches0 = lib.mlpsp_kernel_launches(None, 0)
-    barrier()
-    wall0 = time.perf_counter()
-    for a, b in evs:
-        flush.fill_(1)
-        a.record(); frame(); b.record()
-    barrier()
-    wall = time.perf_counter() - wall0
+    dev_ms_max, wall = timed_block(wl, flush, args.steps, world)
     launches = lib.mlpsp_kernel_launches(None, 0) - launches0
-    dev_ms = sum(a.elapsed_time(b) for a, b in evs)
-    # nvidia-smi answers every 20-100 ms and the timed region may be shorter than that: the same frames keep
-    # running (untimed) until the window that opened with the timed region holds a handful of samples
-    clock_extra = 0
-    if rank == 0 and sampler.proc is not None:
-        t_c = time.perf_counter()
-        while sampler.mark() - clock_mark < 5 and time.perf_counter() - t_c < 1.5:
-            frame(); torch.cuda.synchronize(); clock_extra += 1
-    clocks = sampler.stop(clock_mark) if rank == 0 else None
-    if clocks is not None:
-        clocks["window"] = f"timed region + {clock_extra} further untimed frames of the same workload"
-    barrier()
+    clock_end = sampler.mark()
+    blocks = [dev_ms_max / args.steps]
+    spent = dev_ms_max
+    while spent < 1000.0 and len(blocks) < 64:
+        ms, _w = timed_block(wl, flush, args.steps, world)
+        blocks.append(ms / args.steps)
+        spent += ms
+    # nvidia-smi answers every 20-100 ms and the first block may be shorter than that: the window that opened with the
+    # timed region is read once it holds a handful of samples (the repeated blocks are the same frames)
+    t_c = time.perf_counter()
+    while rank == 0 and sampler.proc is not None and sampler.mark() - clock_mark < 5 and time.perf_counter() - t_c < 1.5:
+        wl.frame(); torch.cuda.synchronize()
+    clocks = None
+    if rank == 0:
+        clocks = sampler.summary(clock_mark)
+        clocks["window"] = (f"the timed block of {args.steps} steps and the {len(blocks) - 1} repeated blocks after it "
+                            f"({sampler.mark() - clock_mark} samples; {max(clock_end - clock_mark, 0)} of them inside the first block)")
+    barrier(world)
     bits = int(r.status.cpu()[0])
     if bits & ~L.BIT_NUMERIC:
         raise SystemExit(f"render status bits {bits} during the timed region")
-    t = torch.tensor([dev_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms_max = float(t.item())
     ms_per_step = dev_ms_max / args.steps
-    fps = frames_per_step * args.steps / (dev_ms_max / 1e3)
+    fps = wl.frames_per_step * args.steps / (dev_ms_max / 1e3)
     rec_t = torch.tensor([float(stats.records), float(stats.used)], dtype=torch.float64, device=dev)
-    if world > 1 and nviews > 1:
+    if world > 1 and wl.nviews > 1:
         dist.all_reduce(rec_t)   # records of the whole step (all views), summed over ranks
 
-    # ---- per-kernel-class device time (separate pass: event pairs around every launch group) ----
-    lib.mlpsp_timing_enable(1)
-    per_class0 = (C.c_int64 * 8)()
-    lib.mlpsp_kernel_launches(per_class0, 8)
-    tsteps = min(args.steps, 10)
-    for _ in range(tsteps):
-        flush.fill_(1); frame()
-    torch.cuda.synchronize()
-    ms_cls = (C.c_float * 8)()
-    L.check(lib.mlpsp_timing_collect(ms_cls, 8), "timing_collect")
-    lib.mlpsp_timing_enable(0)
-    per_class1 = (C.c_int64 * 8)()
-    lib.mlpsp_kernel_launches(per_class1, 8)
-    classes = {}
-    for i, name in enumerate(L.KERNEL_CLASSES):
-        n_l = (per_class1[i] - per_class0[i]) / tsteps
-        classes[name] = {"ms_per_step": ms_cls[i] / tsteps, "launches_per_step": n_l}
-    pk = peaks()
-    mlp_ms = classes["mlp"]["ms_per_step"]
-    mlp_launch_ms = mlp_ms / max(classes["mlp"]["launches_per_step"], 1)
-    hidden = int(cfg.get("hidden", 32))
-    flops_step = stats.records * flop_per_record(hidden)
-    achieved_tf = flops_step / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0
-    roofline = {"kernel": "k_mlp_tc (per-primitive MLP, tcgen05)", "bound": "tensor", "achieved": achieved_tf,
-                "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved_tf / pk["bf16_tflops"],
-                "peak_source": pk["source"] + " burst", "traffic": None,
-                "flop_per_launch": flops_step / max(classes["mlp"]["launches_per_step"], 1),
-                "avg_launch_ms": mlp_launch_ms, "share_of_step": mlp_ms / max(sum(c["ms_per_step"] for c in classes.values()), 1e-9)}
-    # Algorithmic bytes of the evaluator: 32 B in + 16 B out per record, one 8,464-byte weight image per work item.
-    n_launch = max(classes["mlp"]["launches_per_step"], 1)
-    alg_bytes = stats.records * 48 + stats.work_total * (8464 if hidden == 32 else 21008)
-    roofline["hbm_view"] = {"algorithmic_bytes_per_launch": alg_bytes / n_launch,
-                            "achieved_gbs": alg_bytes / (mlp_ms / 1e3) / 1e9 if mlp_ms > 0 else 0.0,
-                            "peak_gbs": pk["hbm_gbs"],
-                            "frac": (alg_bytes / (mlp_ms / 1e3) / 1e9 / pk["hbm_gbs"]) if mlp_ms > 0 else 0.0}
-    if args.workload == "single_100k_1200x680" and prec == L.PRECISION_F16 and args.encoder == "integrated" and nviews == 1:
-        # one ncu capture of the three busy evaluator launches of a frame of this workload: DRAM read + write bytes
-        # 386.7 + 272.7 + 86.5 MB; the other launches of the six-wave schedule move nothing
-        roofline["traffic"] = (386.7e6 + 272.7e6 + 86.5e6) / n_launch
-        roofline["traffic_unit"] = "bytes per launch: ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over a frame's evaluator launches"
-        roofline["ncu_pipes_pct"] = {"tensor": 10.2, "special_function": 48.0, "issue": 57.0, "dram": 16.6,
-                                     "source": "profiles/k_mlp_tc_single_100k_1200x680.md (largest wave)"}
+    classes = class_times(wl, flush, min(args.steps, 10))
+    roofline = evaluator_roofline(wl, classes, args.workload if (prec == L.PRECISION_F16 and args.encoder == "integrated") else "")
 
     # ---- end to end: pinned host rays in, image out, status checked, through the public host API.
     # Three frames are kept in flight (FramePipeline): every step still copies its own rays to the device
     # and its own image back inside the timed region; the copies of one frame overlap the kernels of others.
+    # A pinhole camera has one ray origin: it travels as a [1,3] tensor and is expanded on the device.
     from mlp_splatting_b200.engine import FramePipeline
     depth = 3
     pipe = FramePipeline(ps, cfg["W"], cfg["H"], depth=depth, max_records=r.max_records)
-    outs = [(torch.empty((r.P, 3), dtype=torch.float32).pin_memory(), torch.empty((r.P, 1), dtype=torch.float32).pin_memory())
+    img_dtype = torch.float16 if args.e2e_image == "f16" else torch.float32
+    outs = [(torch.empty((r.P, 3), dtype=img_dtype).pin_memory(), torch.empty((r.P, 1), dtype=img_dtype).pin_memory())
             for _ in range(depth)]
-
-    host_rays = [(torch.from_numpy(c["rays_o"]).pin_memory(), torch.from_numpy(c["rays_d"]).pin_memory()) for c, _ in units]
+    host_rays = []
+    for c, _rows in wl.units:
+        one_origin = bool((c["rays_o"] == c["rays_o"][:1]).all())
+        ro = torch.from_numpy(np.ascontiguousarray(c["rays_o"][:1] if one_origin else c["rays_o"])).pin_memory()
+        host_rays.append((ro, torch.from_numpy(c["rays_d"]).pin_memory()))
 
     def e2e_run(k):
         j = 0
         for _i in range(k):
-            for (c, rows), (roh, rdh) in zip(units, host_rays):
+            for (c, rows), (roh, rdh) in zip(wl.units, host_rays):
                 o = outs[j % depth]; j += 1
                 pipe.submit(roh, rdh, THRESHOLD, c["view"], c["proj"], out_rgb_host=o[0], out_alpha_host=o[1],
                             precision=prec, tile_rows=rows)
         pipe.drain()
 
     e2e_run(2 * depth)
-    barrier()
+    barrier(world)
     e0 = time.perf_counter()
     e2e_run(args.steps)
-    barrier()
+    barrier(world)
     e_t = torch.tensor([time.perf_counter() - e0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e_t, op=dist.ReduceOp.MAX)
-    e2e_fps = frames_per_step * args.steps / float(e_t.item())
-    last = (args.steps * max(len(units), 1) - 1) % depth
-    e2e_err = float((outs[last][0].to(dev) - r.rgb).abs().max()) if units else 0.0   # must reproduce the resident-input frame
+    e2e_fps = wl.frames_per_step * args.steps / float(e_t.item())
+    nunits = max(len(wl.units), 1)
+    last = (args.steps * nunits - 1) % depth
+    e2e_err = float((outs[last][0].to(dev).float() - r.rgb).abs().max()) if wl.units else 0.0   # must reproduce the resident-input frame
+    h2d = sum(int(a.numel() + b.numel()) * 4 for a, b in host_rays)
+    d2h = nunits * (r.P * 4 * img_dtype.itemsize + 64)
+
+    others = None
+    if args.workload == HEADLINE and not args.no_other_workloads and prec == L.PRECISION_F16:
+        del pipe
+        others = {}
+        for name in OTHER_WORKLOADS:
+            from mlp_splatting_b200 import synthetic as syn
+            views = int(syn.WORKLOADS[name]["views"])
+            if world > 1 and views == 1:
+                continue          # single-view workloads scale like the headline one
+            try:
+                others[name] = short_measure(name, args, dev, world, rank, lib, flush, steps=5 if views < 8 else 2)
+            except Exception as exc:     # the headline line must not be lost over an extra measurement
+                others[name] = {"failed": f"{type(exc).__name__}: {exc}"[:300]}
 
     if rank == 0:
         line = {
             "metric": "frames_per_sec", "value": fps, "unit": "frames/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": wl.scaling,
             "vs_baseline": None, "dtype": "f16" if prec == L.PRECISION_F16 else "f32", "data": "synthetic",
             "config": workload_config(args.workload, cfg, world, args.encoder),
-            "record_mlp_evals_per_sec": float(rec_t[0]) * (fps / frames_per_step if nviews > 1 else fps),
+            "repeat": {"blocks": len(blocks), "steps_per_block": args.steps, "ms_per_step_median": statistics.median(blocks),
+                       "ms_per_step_min": min(blocks), "ms_per_step_max": max(blocks),
+                       "note": "value and ms_per_step are the first block; the others repeat it until 1 s of device time"},
+            "record_mlp_evals_per_sec": float(rec_t[0]) * (fps / wl.frames_per_step if wl.nviews > 1 else fps),
             "records_per_frame": {"evaluated": stats.records, "composited": stats.used, "candidate_pairs": stats.pairs, "pairs_after_tile_pretest": stats.pairs_kept, "evaluator_blocks": stats.work_total,
+                                  "records_per_evaluator_block": stats.records / max(stats.work_total, 1),
                                   "waves": stats.waves, "max_tile_len": stats.max_tile_len},
-            "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": 2 * r.P * 12 * max(len(units), 1),
-                    "d2h_bytes_per_step": (r.P * 16 + 64) * max(len(units), 1),
-                    "frames_in_flight": depth, "max_abs_diff_vs_resident_frame": e2e_err},
+            "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "frames_in_flight": depth, "image": args.e2e_image, "max_abs_diff_vs_resident_frame": e2e_err,
+                    "note": "three frames in flight and no L2 flush between them, so this can exceed `value`, which times "
+                            "one frame at a time with L2 flushed; a single ray origin travels as [1,3]"},
             "gpu_launches": int(launches),
             "kernel_classes": classes,
             "roofline": roofline,
             "clocks": clocks,
-            "scene_broadcast_s": bcast_s if world > 1 else 0.0,
+            "scene_broadcast_s": wl.bcast_s,
             "wall_ms_per_step": wall * 1e3 / args.steps,
         }
-        if not args.no_cpu_baseline and world == 1:
-            cb = cpu_baseline(scene_np, cam, budget_s=15.0)
+        if others is not None:
+            line["other_workloads"] = others
+        if not args.no_cpu_baseline and world == 1 and wl.scene_np is not None:
+            cb = cpu_baseline(wl.scene_np, wl.cam, budget_s=15.0)
             line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
+    sampler.stop()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -73,7 +73,7 @@ extern "C" {
 typedef struct mlpsp_scene {
   const float* geom;      /* [n*16] from mlpsp_pack_geometry */
   int32_t n;
-  int32_t hidden;         /* H <= 64 (FP32 evaluator), 32 (fp16 evaluator) */
+  int32_t hidden;         /* H <= 64 (FP32 evaluator), 32 or 64 (fp16 / bf16 tensor-core evaluator) */
   int32_t num_freq;       /* F <= 8; encoded width IN = 12 F; fp16 evaluator needs F == 6 */
   int32_t reserved0;
   const float* W1; const float* b1; const float* W2; const float* b2; const float* W3; const float* b3;
@@ -259,8 +259,10 @@ int mlpsp_group_records(const int32_t* primitive_ids, int64_t num_records, int32
                         int64_t* order, void* scratch, int64_t scratch_bytes, void* stream);
 
 /* prepare_groups (primitive_gemm.py:186-203): split every primitive's records into segments of at
- * most segment_size.  group_offsets[n+1] int64 is always written; primitives/starts ([G] int64) are
- * written when non-NULL and max_groups >= G.  *num_groups_host receives G (the call synchronises). */
+ * most segment_size.  group_offsets[n+1] int64 is always written; of primitives/starts ([G] int64, may be
+ * NULL) the first min(G, max_groups) entries are written, so a caller may ask for G first (max_groups = 0)
+ * and call again.  *num_groups_host receives G (the call synchronises).  More than 2^31-1 groups in total
+ * are rejected with MLPSP_E_LIMIT (the outputs are then undefined). */
 int mlpsp_prepare_groups(const int64_t* offsets, int32_t n, int64_t segment_size, int64_t* group_offsets,
                          int64_t* primitives, int64_t* starts, int64_t max_groups,
                          int64_t* num_groups_host, void* stream);

@@ -269,22 +269,23 @@ extern "C" int mlpsp_grouped_weight_gradients(const mlpsp_scene* sc, const int64
                 "mlpsp_grouped_weight_gradients: FP32 weights missing");
   MLPSP_REQUIRE(loss_scale > 0.f && num_segments >= 0 && num_segments < (1ll << 31) && segment_size > 0, MLPSP_E_ARG,
                 "mlpsp_grouped_weight_gradients: bad loss scale, segment size or segment count");
+  // every pointer a launch below reads is checked before the first CUDA call
+  MLPSP_REQUIRE(sc->n == 0 || num_segments == 0 || (x6 && d4 && seg_prim && seg_start && seg_offsets && partial),
+                MLPSP_E_ARG, "mlpsp_grouped_weight_gradients: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   MLPSP_CUDA_OK(cudaMemsetAsync(nonfinite, 0, 4, st));
   if (sc->n == 0) return MLPSP_OK;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (num_segments == 0) {
+    // no records at all: every primitive's gradient row is zero
+    return cuda_check(cudaMemsetAsync(result, 0, sizeof(float) * (size_t)sc->n * kGradLen, st), "grouped_weight_gradients");
+  }
+  static DeviceOnce attr_once;
+  if (attr_once.first())
     MLPSP_CUDA_OK(cudaFuncSetAttribute(k_grouped_vjp, cudaFuncAttributeMaxDynamicSharedMemorySize, kGradSmem));
-    attr_set = true;
-  }
   LaunchScope scope(kKMisc, 2, st);
-  if (num_segments > 0) {
-    MLPSP_REQUIRE(x6 && d4 && seg_prim && seg_start && seg_offsets && partial, MLPSP_E_ARG,
-                  "mlpsp_grouped_weight_gradients: null pointer");
-    k_grouped_vjp<<<(unsigned)num_segments, kGSeg, kGradSmem, st>>>(x6, d4, relu_masks, offsets, seg_prim, seg_start, segment_size,
-                                                                    sc->freq, sc->att, sc->W1, sc->b1, sc->W2, sc->b2, sc->W3,
-                                                                    loss_scale, partial);
-  }
+  k_grouped_vjp<<<(unsigned)num_segments, kGSeg, kGradSmem, st>>>(x6, d4, relu_masks, offsets, seg_prim, seg_start, segment_size,
+                                                                  sc->freq, sc->att, sc->W1, sc->b1, sc->W2, sc->b2, sc->W3,
+                                                                  loss_scale, partial);
   const dim3 grid(sc->n, (kGradLen + 255) / 256);
   k_reduce_partials<<<grid, 256, 0, st>>>(partial, seg_offsets, sc->n, result, nonfinite);
   return cuda_check(cudaGetLastError(), "grouped_weight_gradients");

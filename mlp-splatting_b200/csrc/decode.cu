@@ -700,10 +700,9 @@ extern "C" int mlpsp_pack_decoder(const mlpsp_decoder* dec, int32_t mode, void* 
   if (mode == 1) {
     folded = reinterpret_cast<float*>((char*)packed + h.total_bytes);
     fb = folded + (size_t)dec->num_classes * dec->hidden;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce fold_once;
+    if (fold_once.first()) {
       MLPSP_CUDA_OK(cudaFuncSetAttribute(k_fold_text, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-      attr_set = true;
     }
     k_fold_text<<<dec->num_classes, 128, dec->out_dim * 4, st>>>(dec->text, dec->W3, dec->b3, dec->out_dim, dec->hidden, folded, fb);
   }
@@ -723,10 +722,9 @@ extern "C" int mlpsp_decode_features(const mlpsp_decoder* dec, int32_t mode, con
   MLPSP_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 15) == 0 && (reinterpret_cast<uintptr_t>(feat) & 15) == 0 &&
                 (mode == 1 || (reinterpret_cast<uintptr_t>(out) & 15) == 0), MLPSP_E_ARG,
                 "mlpsp_decode_features: buffers must be 16-byte aligned");
-  static bool attr_set = false;
-  if (!attr_set) {
+  static DeviceOnce decode_once;
+  if (decode_once.first()) {
     MLPSP_CUDA_OK(cudaFuncSetAttribute(k_decode_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
-    attr_set = true;
   }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);

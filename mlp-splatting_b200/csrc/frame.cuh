@@ -133,6 +133,20 @@ int cuda_check(cudaError_t e, const char* what);
     if (!(cond)) { ::mlpsp::set_error(__VA_ARGS__); return (code); }\
   } while (0)
 
+// Per-device "first use" marker for settings that CUDA keeps per device (the opt-in dynamic shared-memory
+// size of a kernel, for one): a process that drives several GPUs must apply them once on each.  The caller
+// keeps one DeviceOnce per setting; first() answers true the first time it is asked with a given device current.
+struct DeviceOnce {
+  bool seen[64] = {false};
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;   // unknown device: apply every time
+    if (seen[dev]) return false;
+    seen[dev] = true;
+    return true;
+  }
+};
+
 // stage launchers (defined in the .cu files)
 // order_lists = false leaves every tile list in scatter order for a following launch_sort(unordered_input = true).
 // pretest: write only the (tile, primitive) pairs that some ray of the tile can hit; s.tile_len receives the

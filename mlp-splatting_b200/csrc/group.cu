@@ -85,9 +85,20 @@ __global__ void k_gs_finish(const uint32_t* __restrict__ vals, int64_t n, int64_
   if (i <= nprim) offsets[i] = (int64_t)off32[i];
 }
 
-__global__ void k_groups_count(const int64_t* __restrict__ offsets, int n, int64_t seg, int32_t* __restrict__ cnt) {
+// total64 (zeroed by the caller) receives the exact number of groups: the per-primitive counts and their
+// prefix are 32-bit, and the host rejects a layout whose total does not fit
+__global__ void k_groups_count(const int64_t* __restrict__ offsets, int n, int64_t seg, int32_t* __restrict__ cnt,
+                               unsigned long long* __restrict__ total64) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) cnt[i] = (int32_t)((offsets[i + 1] - offsets[i] + seg - 1) / seg);
+  long long c = 0;
+  if (i < n) {
+    c = (offsets[i + 1] - offsets[i] + seg - 1) / seg;
+    if (c < 0) c = 0;
+    cnt[i] = (int32_t)(c > 2147483647LL ? 2147483647LL : c);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0 && c > 0) atomicAdd(total64, (unsigned long long)c);
 }
 
 __global__ void k_groups_fill(const int64_t* __restrict__ offsets, int n, int64_t seg, const int32_t* __restrict__ goff32,
@@ -173,21 +184,32 @@ extern "C" int mlpsp_prepare_groups(const int64_t* offsets, int32_t n, int64_t s
   cudaStream_t st = (cudaStream_t)stream;
   MLPSP_REQUIRE(offsets && group_offsets && n >= 0, MLPSP_E_ARG, "mlpsp_prepare_groups: null pointer");
   MLPSP_REQUIRE(segment_size > 0, MLPSP_E_ARG, "segment_size must be a positive integer");
-  int32_t *cnt = nullptr, *goff = nullptr, *blk = nullptr;
-  const size_t bytes = 4 * ((size_t)n + 2);
-  MLPSP_CUDA_OK(cudaMallocAsync(&cnt, bytes, st));
-  MLPSP_CUDA_OK(cudaMallocAsync(&goff, bytes, st));
-  MLPSP_CUDA_OK(cudaMallocAsync(&blk, 4 * ((size_t)n / kScanItems + 4), st));
-  MLPSP_CUDA_OK(cudaMemsetAsync(goff, 0, bytes, st));
-  if (n > 0) k_groups_count<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, segment_size, cnt);
-  int rc = launch_scan_i32(cnt, n, blk, goff, st);
-  if (rc) return rc;
-  k_groups_fill<<<(n + 256) / 256, 256, 0, st>>>(offsets, n, segment_size, goff, group_offsets, primitives, starts, max_groups);
+  // three small work arrays in one allocation: counts | prefix | scan blocks | 64-bit total
+  const size_t bytes = (size_t)align_up(4 * ((int64_t)n + 2), 256);
+  const size_t blk_bytes = (size_t)align_up(4 * ((int64_t)n / kScanItems + 4), 256);
+  char* work = nullptr;
+  MLPSP_CUDA_OK(cudaMallocAsync(&work, 2 * bytes + blk_bytes + 256, st));
+  int32_t* cnt = reinterpret_cast<int32_t*>(work);
+  int32_t* goff = reinterpret_cast<int32_t*>(work + bytes);
+  int32_t* blk = reinterpret_cast<int32_t*>(work + 2 * bytes);
+  unsigned long long* total64 = reinterpret_cast<unsigned long long*>(work + 2 * bytes + blk_bytes);
   int32_t G = 0;
-  MLPSP_CUDA_OK(cudaMemcpyAsync(&G, goff + n, 4, cudaMemcpyDeviceToHost, st));
-  MLPSP_CUDA_OK(cudaStreamSynchronize(st));
+  unsigned long long total = 0;
+  // the allocation is released on every path; the first error wins
+  int rc = cuda_check(cudaMemsetAsync(goff, 0, bytes + blk_bytes + 256, st), "prepare_groups");
+  if (!rc && n > 0) k_groups_count<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, segment_size, cnt, total64);
+  if (!rc) rc = launch_scan_i32(cnt, n, blk, goff, st);
+  if (!rc) {
+    k_groups_fill<<<(n + 256) / 256, 256, 0, st>>>(offsets, n, segment_size, goff, group_offsets, primitives, starts, max_groups);
+    rc = cuda_check(cudaMemcpyAsync(&G, goff + n, 4, cudaMemcpyDeviceToHost, st), "prepare_groups");
+  }
+  if (!rc) rc = cuda_check(cudaMemcpyAsync(&total, total64, 8, cudaMemcpyDeviceToHost, st), "prepare_groups");
+  if (!rc) rc = cuda_check(cudaStreamSynchronize(st), "prepare_groups");
+  cudaFreeAsync(work, st);
+  if (rc) return rc;
+  MLPSP_REQUIRE(total <= 2147483647ull, MLPSP_E_LIMIT,
+                "mlpsp_prepare_groups: %llu groups exceed the 32-bit group index (raise segment_size)", total);
   if (num_groups_host) *num_groups_host = G;
-  cudaFreeAsync(cnt, st); cudaFreeAsync(goff, st); cudaFreeAsync(blk, st);
   return cuda_check(cudaGetLastError(), "prepare_groups");
 }
 
@@ -212,7 +234,7 @@ namespace mlpsp {
 constexpr int kStaticGroupsMaxPrims = MLPSP_STATIC_GROUPS_MAX_PRIMITIVES;
 constexpr int64_t kSgCntBytes = (4ll * (kStaticGroupsMaxPrims + 2) + 255) / 256 * 256;
 constexpr int64_t kSgBlkBytes = (4ll * (kStaticGroupsMaxPrims / kScanItems + 4) + 255) / 256 * 256;
-constexpr int64_t kSgBytes = 2 * kSgCntBytes + kSgBlkBytes;
+constexpr int64_t kSgBytes = 2 * kSgCntBytes + kSgBlkBytes + 256;   // counts | prefix | scan blocks | 64-bit total
 
 static __device__ __align__(256) unsigned char g_static_groups_scratch[kSgBytes];
 static void* g_static_groups_ptr[64] = {nullptr};   // device address of the array, per device ordinal
@@ -248,16 +270,22 @@ extern "C" int mlpsp_prepare_groups_static(const int64_t* offsets, int32_t n, in
   int32_t* cnt = reinterpret_cast<int32_t*>(base);
   int32_t* goff = reinterpret_cast<int32_t*>(base + kSgCntBytes);
   int32_t* blk = reinterpret_cast<int32_t*>(base + 2 * kSgCntBytes);
+  unsigned long long* total64 = reinterpret_cast<unsigned long long*>(base + 2 * kSgCntBytes + kSgBlkBytes);
   // the prefix array must read zero where the scan does not write (n == 0) and must not show the
-  // previous call's totals
+  // previous call's totals; the 64-bit group total starts at zero as well
   MLPSP_CUDA_OK(cudaMemsetAsync(goff, 0, 4 * ((size_t)n + 2), st));
-  if (n > 0) k_groups_count<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, segment_size, cnt);
+  MLPSP_CUDA_OK(cudaMemsetAsync(total64, 0, 8, st));
+  if (n > 0) k_groups_count<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, segment_size, cnt, total64);
   rc = launch_scan_i32(cnt, n, blk, goff, st);
   if (rc) return rc;
   k_groups_fill<<<(n + 256) / 256, 256, 0, st>>>(offsets, n, segment_size, goff, group_offsets, primitives, starts, max_groups);
   int32_t G = 0;
+  unsigned long long total = 0;
   MLPSP_CUDA_OK(cudaMemcpyAsync(&G, goff + n, 4, cudaMemcpyDeviceToHost, st));
+  MLPSP_CUDA_OK(cudaMemcpyAsync(&total, total64, 8, cudaMemcpyDeviceToHost, st));
   MLPSP_CUDA_OK(cudaStreamSynchronize(st));
+  MLPSP_REQUIRE(total <= 2147483647ull, MLPSP_E_LIMIT,
+                "mlpsp_prepare_groups_static: %llu groups exceed the 32-bit group index (raise segment_size)", total);
   if (num_groups_host) *num_groups_host = G;
   return cuda_check(cudaGetLastError(), "prepare_groups_static");
 }

@@ -878,6 +878,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   }
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cnt, 0, 4 * (size_t)n, st));
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cursor, 0, 4 * (size_t)n, st));
+  const bool tc_path = fr->precision == MLPSP_PRECISION_F16 || fr->precision == MLPSP_PRECISION_BF16;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -913,7 +914,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                               s.prim_cursor, s.rec_in, (want_t || per_pixel) ? s.rec_t : nullptr,
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
                               sc->gate_tau, per_pixel ? 1 : 0, fr->status); }
-    if (fr->precision == MLPSP_PRECISION_F16 || fr->precision == MLPSP_PRECISION_BF16)
+    if (tc_path)
       rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
                           fr->status, st, fr->precision == MLPSP_PRECISION_BF16, cap_mlp);
     else
@@ -946,13 +947,12 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   if (fr->mask_used && used32 != (uint32_t*)fr->mask_used)
     MLPSP_CUDA_OK(cudaMemcpyAsync(fr->mask_used, used32, 8 * (size_t)fr->max_pairs, cudaMemcpyDeviceToDevice, st));
   if (want_feat) {
-    static bool attr_set = false;
+    static DeviceOnce attr_once;
     const int CB = std::min(sc->feat_dim, kFeatChan);
     const size_t smem = sizeof(float) * 64 * (size_t)CB;
-    if (!attr_set) {
+    if (attr_once.first()) {
       MLPSP_CUDA_OK(cudaFuncSetAttribute(k_feature_composite<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * kFeatChan * 4));
       MLPSP_CUDA_OK(cudaFuncSetAttribute(k_feature_composite<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * kFeatChan * 4));
-      attr_set = true;
     }
     LaunchScope scope(kKComposite, 1, st);
     const dim3 grid(T, (sc->feat_dim + CB - 1) / CB);

@@ -102,6 +102,39 @@ class PackedScene:
                     self.wbf16 = wb
                 self.c = self._struct()
 
+    @classmethod
+    def from_packed_image(cls, positions, log_scales, quats, freq, att, w16, hidden, feat_attr=None, gate_beta=1.5,
+                          gate_tau=2.0, device="cuda"):
+        """A scene that holds geometry and an already packed fp16 weight image (mlpsp_pack_weights_f16, biases
+        included) but no FP32 weight masters: it renders on the tensor-core evaluator only, and a frame that
+        overflows binary16 cannot be rendered again in FP32."""
+        lib = L.load()
+        self = cls.__new__(cls)
+        self.device = d = torch.device(device)
+        if d.type != "cuda":
+            raise RuntimeError("PackedScene must live on a CUDA device; there is no CPU path")
+        with torch.cuda.device(d):
+            self.positions, self.log_scales = _dev_f32(positions, d), _dev_f32(log_scales, d)
+            self.quats_unit = normalize_rows(_dev_f32(quats, d))
+            self.W1 = self.b1 = self.W2 = self.b2 = self.W3 = self.b3 = None
+            self.freq, self.att = _dev_f32(freq, d), _dev_f32(att, d)
+            self.n, self.hidden, self.num_freq = int(self.positions.shape[0]), int(hidden), int(self.freq.numel())
+            if int(w16.numel()) != self.n * int(lib.mlpsp_packed_weight_bytes(self.hidden, self.num_freq)):
+                raise ValueError("weight image size does not match the primitive count and hidden width")
+            self.geom = torch.empty((max(self.n, 1), L.GEOM_FLOATS), device=d, dtype=torch.float32)
+            L.check(lib.mlpsp_pack_geometry(L.ptr(self.positions), L.ptr(self.log_scales), L.ptr(self.quats_unit),
+                                            self.n, L.ptr(self.geom), _stream_ptr(d)), "mlpsp_pack_geometry")
+            self.feat_attr, self.feat_slots, self.feat_dim = None, 0, 0
+            if feat_attr is not None:
+                fa = _dev_f32(feat_attr, d)
+                if fa.dim() == 2:
+                    fa = fa[:, None, :].contiguous()
+                self.feat_attr, self.feat_slots, self.feat_dim = fa, int(fa.shape[1]), int(fa.shape[2])
+            self.gate_beta, self.gate_tau = float(gate_beta), float(gate_tau)
+            self.w16, self.wbf16, self.f16_rejected = w16, None, False
+            self.c = self._struct()
+        return self
+
     def _struct(self) -> L.Scene:
         s = L.Scene()
         s.geom, s.n, s.hidden, s.num_freq = L.ptr(self.geom), self.n, self.hidden, self.num_freq
@@ -382,6 +415,9 @@ class FrameRenderer:
                 if (bits & L.BIT_NUMERIC) and precision in (L.PRECISION_F16, L.PRECISION_BF16):
                     # operand/activation overflow in binary16: render the whole frame again in scalar
                     # FP32, as the reference does (rgb_wmma.cuh:260-272)
+                    if scene.W1 is None:
+                        raise RenderError(f"{path_name}: non-finite operand or activation in the fp16 evaluator and "
+                                          "the scene holds no FP32 weights to render the frame again with")
                     self.f32_fallbacks += 1
                     precision = L.PRECISION_F32
                     continue
@@ -515,7 +551,7 @@ class FramePipeline:
             r = FrameRenderer(width, height, device=d, **renderer_kw)
             self.slots.append(dict(r=r, stream=torch.cuda.Stream(device=d), busy=False,
                                    ro=torch.empty((r.P, 3), device=d), rd=torch.empty((r.P, 3), device=d),
-                                   kw=None))
+                                   ro1=torch.empty((1, 3), device=d), kw=None))
         self.next_slot = 0
 
     def submit(self, rays_o_host, rays_d_host, threshold, view, proj, out_rgb_host=None, out_alpha_host=None,
@@ -527,17 +563,28 @@ class FramePipeline:
         self.next_slot = (i + 1) % len(self.slots)
         r = s["r"]
         with torch.cuda.stream(s["stream"]):
-            s["ro"].copy_(rays_o_host, non_blocking=True)
+            if rays_o_host.shape[0] == 1 and r.P != 1:
+                # one origin for every ray (a pinhole camera): 12 bytes cross the bus, the rows are written on the device
+                s["ro1"].copy_(rays_o_host, non_blocking=True)
+                s["ro"].copy_(s["ro1"].expand(r.P, 3))
+            else:
+                s["ro"].copy_(rays_o_host, non_blocking=True)
             s["rd"].copy_(rays_d_host, non_blocking=True)
             kw = dict(view=view, proj=proj, precision=precision, bg=bg, tile_rows=tile_rows)
             rgb, alpha = r.render(self.scene, s["ro"], s["rd"], threshold, check=False, **kw)
-            if out_rgb_host is not None:
-                out_rgb_host.copy_(rgb, non_blocking=True)
-            if out_alpha_host is not None:
-                out_alpha_host.copy_(alpha, non_blocking=True)
+            self._to_host(rgb, out_rgb_host)
+            self._to_host(alpha, out_alpha_host)
             r.status_host.copy_(r.status, non_blocking=True)
         s["busy"], s["kw"] = True, (threshold, kw, out_rgb_host, out_alpha_host)
         return i
+
+    @staticmethod
+    def _to_host(src, dst):
+        """Device image -> (pinned) host tensor; a host tensor of another dtype (float16, say) is converted to on the
+        device first, so only its bytes cross the bus."""
+        if dst is None:
+            return
+        dst.copy_(src if dst.dtype == src.dtype else src.to(dst.dtype), non_blocking=True)
 
     def wait(self, i):
         s = self.slots[i]
@@ -554,10 +601,8 @@ class FramePipeline:
         threshold, kw, out_rgb, out_alpha = s["kw"]
         with torch.cuda.stream(s["stream"]):
             rgb, alpha = r.render(self.scene, s["ro"], s["rd"], threshold, check=True, **kw)
-            if out_rgb is not None:
-                out_rgb.copy_(rgb, non_blocking=True)
-            if out_alpha is not None:
-                out_alpha.copy_(alpha, non_blocking=True)
+            self._to_host(rgb, out_rgb)
+            self._to_host(alpha, out_alpha)
         s["stream"].synchronize()
 
     def drain(self):

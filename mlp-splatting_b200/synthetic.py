@@ -95,7 +95,9 @@ WORKLOADS = {
     "textquery_250k_1200x680": dict(n=250_000, W=1200, H=680, mu=-4.8, views=1, seed=2028, feat_dim=512,
                                     text_query=dict(classes=20, seed=2033)),
     "fourview_500k_1200x680": dict(n=500_000, W=1200, H=680, mu=-5.2, views=4, seed=2029),
-    "stress_2m_1920x1080": dict(n=2_000_000, W=1920, H=1080, mu=-6.4, views=32, seed=2030, hidden=32),
+    # 64-wide hidden layers as the stress configuration asks; drawn and packed on the device slice by slice
+    # (synthetic.make_scene_device), because its FP32 masters would be 72 GB
+    "stress_2m_1920x1080": dict(n=2_000_000, W=1920, H=1080, mu=-6.4, views=32, seed=2030, hidden=64, on_device=True),
     # the stress configuration's 64-wide hidden layers on a scene whose FP32 masters (36 KB per primitive) stay small
     "hidden64_250k_1200x680": dict(n=250_000, W=1200, H=680, mu=-4.8, views=1, seed=2031, hidden=64),
 }
@@ -136,3 +138,44 @@ def make_feature_map(width, height, dim, seed=0, scale=0.5):
     fy = rng.uniform(0.02, 0.3, size=(dim,)).astype(np.float32)
     base = np.sin(xx[..., None] * fx + yy[..., None] * fy + ph)
     return (scale * (base + 0.3 * rng.normal(size=base.shape))).astype(np.float32)
+
+
+def make_scene_device(n, seed, device, mu=-3.5, sigma=0.5, hidden=32, num_freq=6, extent=1.0, feat_dim=0, feat_slots=4,
+                      pe_sigma=0.01, chunk=65536, parts=("geometry", "weights")):
+    """The distributions of make_scene drawn on a CUDA device with torch's generator (another random stream, so not
+    the same scene): for scenes whose FP32 masters are too large to build on the host and copy (2 M primitives with
+    64-wide layers are 72 GB).  Returns a dict of device tensors with make_scene's keys; parts selects the geometry
+    (positions, log_scales, quats, freq, att, feat_attr) and / or the MLP weights."""
+    import torch
+
+    g = torch.Generator(device=device)
+    g.manual_seed(int(seed))
+    f32 = dict(device=device, dtype=torch.float32)
+    IN = 12 * num_freq
+    scene = {}
+    if "geometry" in parts:
+        scene["positions"] = (torch.rand((n, 3), generator=g, **f32) * 2.0 - 1.0) * extent
+        scene["log_scales"] = torch.randn((n, 3), generator=g, **f32) * sigma + mu
+        q = torch.randn((n, 4), generator=g, **f32)
+        scene["quats"] = q / q.norm(dim=1, keepdim=True).clamp_min(1e-12)
+        freq = (2.0 ** np.arange(num_freq, dtype=np.float64) * math.pi).astype(np.float32)
+        scene["freq"] = torch.from_numpy(freq).to(device)
+        scene["att"] = torch.from_numpy(np.exp(-0.5 * freq.astype(np.float64) ** 2 * pe_sigma ** 2).astype(np.float32)).to(device)
+        if feat_dim > 0:
+            fa = torch.randn((n, feat_slots, feat_dim), generator=g, **f32) * 0.2
+            scene["feat_attr"] = fa.half().float()
+    if "weights" in parts:
+        def xavier(fan_out, fan_in):
+            bound = math.sqrt(6.0 / (fan_in + fan_out))
+            w = torch.empty((n, fan_out, fan_in), **f32)
+            for a in range(0, n, chunk):            # in slices: the half-precision round trip needs a temporary
+                part = w[a:a + chunk]
+                part.uniform_(-bound, bound, generator=g)
+                part.copy_(part.half().float())
+            return w
+
+        scene.update(W1=xavier(hidden, IN), b1=torch.zeros((n, hidden), **f32),
+                     W2=xavier(hidden, hidden), b2=torch.zeros((n, hidden), **f32),
+                     W3=xavier(4, hidden), b3=torch.zeros((n, 4), **f32))
+        scene["b3"][:, 3] = math.log(4.0)
+    return scene

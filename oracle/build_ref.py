@@ -2,6 +2,9 @@
 
     python oracle/build_ref.py [/path/to/mlp-splatting]
 
+Without an argument the checkout is looked for in $MLPSP_REFERENCE_ROOT, then in a directory named
+"reference" beside this repository.
+
 The reference's single translation unit (scannet/cuda/np_tile_kernels.cu, which includes its three
 .cuh files) is compiled for sm_100a from where it lies, with the flags the reference's loader uses
 by default (-DMLPSP_MAX_TILE_PRIMS=1536, scannet/cumodel.py:96-130), as a torch extension module
@@ -17,8 +20,13 @@ OUT = os.path.join(HERE, "_ref")
 NAME = "mlpsp_ref_ext"
 
 
-def build(ref_root="/root/reference", verbose=False):
-    src = os.path.join(ref_root, "scannet", "cuda", "np_tile_kernels.cu")
+def reference_root():
+    """The reference checkout: $MLPSP_REFERENCE_ROOT, else ../reference relative to this repository."""
+    return os.environ.get("MLPSP_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root=None, verbose=False):
+    src = os.path.join(ref_root or reference_root(), "scannet", "cuda", "np_tile_kernels.cu")
     if not os.path.exists(src):
         return None
     so = os.path.join(OUT, NAME + ".so")
@@ -50,4 +58,4 @@ def load_module():
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", verbose=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, verbose=True))

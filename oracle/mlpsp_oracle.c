@@ -688,6 +688,14 @@ int orc_num_threads(void) {
   return 1;
 #endif
 }
+/* Thread count of the parallel loops from here on (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
 
 /* ---------------------------------------------------------------------------------------------
  * Feature decoder and text query: the step that follows the feature map.

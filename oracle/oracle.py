@@ -87,6 +87,20 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """Use n OpenMP threads from here on (launchers such as torch.distributed.run export OMP_NUM_THREADS=1)."""
+    lib().orc_set_num_threads(int(n))
+    return num_threads()
+
+
+def host_cores() -> int:
+    """Cores this process may run on."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def det_exp(x):
     f = lib().orc_det_exp
     return np.array([f(float(v)) for v in np.asarray(x, dtype=np.float32).ravel()], dtype=np.float32)

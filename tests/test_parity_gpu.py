@@ -262,6 +262,15 @@ def test_render_fp16_tensor_core_matches_oracle(dev, name):
     M = f16["tile_prims"].size
     used = r.mask_used.cpu().numpy()[:M].view(np.uint64)
     _compare_used(used, f16["render"], f16["tile_offsets"], cam, margin=5e-2)
+    # what the 5e-2 margin excuses: pixels whose transmittance passes within 5 % of the 1e-3 gate are few ...
+    res = f16["render"]
+    excused = res.min_margin < 5e-2
+    assert excused.mean() <= 0.03, f"{int(excused.sum())} of {excused.size} pixels lie within the fp16 margin"
+    # ... and the consumed masks of the others are exact (asserted above), so at most that share of pixels can
+    # differ in their record lists; the ones that actually differ are fewer still
+    diff = used ^ res.mask_used
+    changed = int(np.count_nonzero(diff))
+    assert changed <= max(4, int(0.002 * M)), f"{changed} of {M} pairs differ in a consumed bit"
     assert r.f32_fallbacks == 0
 
 

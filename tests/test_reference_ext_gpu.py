@@ -107,15 +107,22 @@ def test_records_and_csr_match_reference_kernel(ref, name):
     np.testing.assert_allclose(G["raw"][sg][keep][:, 4:7], R["raw"][sr][keep][:, 4:7], rtol=0, atol=3e-5)
     # gates depend on q = R^T (c - p), a difference of O(1) numbers of size ~1e-2: relative 1e-5 noise
     np.testing.assert_allclose(G["gates"][sg][keep], R["gates"][sr][keep], rtol=0, atol=2e-4)
-    # CSR offsets of the two record sets (group_records, primitive_csr.py:23-29)
+    # CSR offsets of the two record sets (group_records, primitive_csr.py:23-29).  The per-primitive record counts of
+    # the two sets differ by at most the records that are not common to both (every record of a pixel whose count
+    # differs, and both records of a position whose ids differ), and a prefix sum cannot differ by more than that.
     n = ps.n
     off_g, _ = primitive_csr.group_order(out[2], n)
     off_r, _ = primitive_csr.group_order(ref_out[2], n)
     diff = (off_g - off_r).abs().max().item()
-    if same.all() and ids_equal.all():
-        assert diff == 0
+    uncommon = int(cr[~same].sum() + cg[~same].sum() + 2 * (~ids_equal).sum())
+    assert uncommon <= 4e-3 * (R["ids"].size + G["ids"].size), (uncommon, R["ids"].size)
+    assert diff <= uncommon, (diff, uncommon)
+    if uncommon == 0:
+        assert torch.equal(off_g, off_r)
+    # record totals agree to the same bound
+    assert abs(int(R["ids"].size) - int(G["ids"].size)) <= uncommon
     print(f"{name}: records ref={R['ids'].size} here={G['ids'].size}, pixels with a different count: {(~same).sum()}, "
-          f"max CSR offset difference {diff}")
+          f"positions with a different id: {(~ids_equal).sum()}, max CSR offset difference {diff}")
 
 
 def test_feature_map_matches_reference_kernel(ref):
