@@ -56,6 +56,7 @@ extern "C" {
 #define MLPSP_ST_TIMEOUT 128         /* a bounded device-side wait gave up */
 #define MLPSP_ST_TILE_ORIGINS 256    /* ray-cone culling: a tile's rays do not share one origin */
 #define MLPSP_ST_CONE_TOO_WIDE 512   /* ray-cone culling: a tile's ray cone spans >= 90 degrees */
+#define MLPSP_ST_FEAT_INEXACT 1024   /* mlpsp_pack_features_f16: an attribute is not representable in binary16 */
 #define MLPSP_ST_FATAL (1 | 2 | 4 | 8 | 16 | 128 | 256 | 512)
 
 #define MLPSP_PRECISION_F32 0  /* scalar FP32 evaluator (np_tile_kernels.cu:312-380) */
@@ -86,6 +87,9 @@ typedef struct mlpsp_scene {
   float gate_beta;        /* semantic_tetra_gates norm_beta */
   float gate_tau;         /* semantic_tetra_gates logit_temp */
   const void* wbf16;      /* the same image with bfloat16 operands, from mlpsp_pack_weights_bf16, or NULL */
+  const void* feat16;     /* feat_attr as binary16 [n, feat_slots, feat_dim] from mlpsp_pack_features_f16, or NULL.  When
+                             set, and feat_dim is 128, 256, 384 or 512, the feature map is composited on the tensor
+                             cores from this copy (FP32 accumulation); otherwise from feat_attr on the FP32 path. */
 } mlpsp_scene;
 
 /* One frame.  Replaces (rays_o, rays_d, culled_prim_indices, tile_offsets, Wimg, Himg, TW, TH,
@@ -168,6 +172,12 @@ int64_t mlpsp_packed_weight_bytes(int32_t hidden, int32_t num_freq);
 int mlpsp_pack_weights_f16(const mlpsp_scene* scene, void* w16_out, int32_t* status, void* stream);
 /* The same image with bfloat16 operands (same size and layout); no reference kernel casts per scene either. */
 int mlpsp_pack_weights_bf16(const mlpsp_scene* scene, void* wbf16_out, int32_t* status, void* stream);
+
+/* binary16 copy of scene->feat_attr [n, feat_slots, feat_dim] (the storage format of the reference's inference
+ * export, scannet/checkpoints.py:358-359) for the tensor-core feature compositing.  status (optional):
+ * MLPSP_ST_FEAT_INEXACT is raised when some attribute does not survive the round trip, i.e. when rendering from
+ * the copy would differ from rendering from feat_attr by binary16 rounding of the attributes. */
+int mlpsp_pack_features_f16(const mlpsp_scene* scene, void* feat16_out, int32_t* status, void* stream);
 
 int mlpsp_status_reset(int32_t* status, void* stream);
 

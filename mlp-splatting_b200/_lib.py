@@ -16,7 +16,7 @@ ST_BITS, ST_MAX_TILE_LEN, ST_PAIRS, ST_WAVES = 0, 1, 2, 3
 ST_RECORDS_LO, ST_USED_LO, ST_WAVE_RECORDS, ST_WORK_ITEMS, ST_WORK_TOTAL, ST_PAIRS_KEPT = 4, 6, 8, 9, 10, 11
 BIT_BAD_OFFSETS, BIT_TILE_CAPACITY, BIT_BAD_IDS = 1, 2, 4
 BIT_PAIR_OVERFLOW, BIT_RECORD_OVERFLOW, BIT_NUMERIC, BIT_TIMEOUT = 8, 16, 64, 128
-BIT_TILE_ORIGINS, BIT_CONE_TOO_WIDE = 256, 512
+BIT_TILE_ORIGINS, BIT_CONE_TOO_WIDE, BIT_FEAT_INEXACT = 256, 512, 1024
 BIT_PIXEL_HITS = 32
 ORDER_PER_PIXEL = 2
 PRECISION_F32, PRECISION_F16, PRECISION_BF16 = 0, 1, 2
@@ -33,7 +33,7 @@ class Scene(C.Structure):
         ("W1", _fp), ("b1", _fp), ("W2", _fp), ("b2", _fp), ("W3", _fp), ("b3", _fp),
         ("w16", _fp), ("freq", _fp), ("att", _fp), ("feat_attr", _fp),
         ("feat_slots", C.c_int32), ("feat_dim", C.c_int32), ("gate_beta", C.c_float), ("gate_tau", C.c_float),
-        ("wbf16", _fp),
+        ("wbf16", _fp), ("feat16", _fp),
     ]
 
 
@@ -69,6 +69,7 @@ _SIGS = {
     "mlpsp_packed_weight_bytes": (C.c_int64, [C.c_int32, C.c_int32]),
     "mlpsp_pack_weights_f16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
     "mlpsp_pack_weights_bf16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
+    "mlpsp_pack_features_f16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
     "mlpsp_records_reverse": (C.c_int, [_fp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64, C.c_int32, _fp, _fp, _fp, _fp, _fp]),
     "mlpsp_grouped_gradient_floats": (C.c_int64, []),
     "mlpsp_grouped_weight_gradients": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64, C.c_int32,

@@ -287,6 +287,20 @@ __device__ __forceinline__ V3 load3(const float* __restrict__ p, int64_t i) {
   return r;
 }
 
+// pixel k (row-major inside the 8x8 tile) of a tile: image index and whether it lies inside the image
+struct TilePix {
+  int pix; bool valid;
+};
+
+__device__ __forceinline__ TilePix tile_pixel(int tile, int k, int ntx, int W, int H) {
+  const int tx = tile % ntx, ty = tile / ntx;
+  const int x = tx * 8 + (k & 7), y = ty * 8 + (k >> 3);
+  TilePix r;
+  r.valid = (x < W) && (y < H);
+  r.pix = r.valid ? y * W + x : 0;
+  return r;
+}
+
 // Output activations (np_tile_kernels.cu:75-83); values, not decisions, so hardware exp is fine.
 __device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float softplus_fast(float x) {

@@ -185,6 +185,11 @@ int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Sc
 constexpr int kOutAlpha = 0;     // (R,G,B, 1-exp(-softplus(o3)*decay)) scattered to rec.slot
 constexpr int kOutSigmaRaw = 1;  // (R,G,B, softplus(o3)) scattered to rec.slot
 
+// feature compositing on the tensor cores (feature_tc.cu): whether this scene's attributes qualify (a binary16 copy,
+// 128 / 256 / 384 / 512 channels, 1, 4 or 5 slots), and the launch for a rendered frame (consumed masks in used32)
+bool feature_tc_supported(const mlpsp_scene* sc);
+int launch_feature_tc(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, const uint32_t* used32, cudaStream_t st);
+
 // multi-block exclusive scan of per-primitive record counts plus evaluator work-item emission
 int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st);
 

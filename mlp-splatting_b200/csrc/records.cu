@@ -27,19 +27,6 @@ constexpr int kWinMax = 2048;
 // squared bounding radius in units of the largest scale, with the 2 % margin surely_misses() relies on
 static inline float miss_bound2(float thr) { return (float)(-2.0 * log((double)thr) * 1.02); }
 
-struct TilePix {
-  int pix; bool valid;
-};
-
-__device__ __forceinline__ TilePix tile_pixel(int tile, int k, int ntx, int W, int H) {
-  const int tx = tile % ntx, ty = tile / ntx;
-  const int x = tx * 8 + (k & 7), y = ty * 8 + (k >> 3);
-  TilePix r;
-  r.valid = (x < W) && (y < H);
-  r.pix = r.valid ? y * W + x : 0;
-  return r;
-}
-
 // -------------------------------------------------------------------------- frame init ----
 __global__ void k_init_pixels(int64_t P, float4* __restrict__ px_state, float2* __restrict__ px_depth,
                               float* __restrict__ rgb, float* __restrict__ alpha, float* __restrict__ depth_t,
@@ -946,7 +933,12 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   }
   if (fr->mask_used && used32 != (uint32_t*)fr->mask_used)
     MLPSP_CUDA_OK(cudaMemcpyAsync(fr->mask_used, used32, 8 * (size_t)fr->max_pairs, cudaMemcpyDeviceToDevice, st));
-  if (want_feat) {
+  if (want_feat && feature_tc_supported(sc)) {
+    // binary16 attributes and a channel count the tensor-core kernel takes: the contraction runs on tcgen05
+    LaunchScope scope(kKComposite, 1, st);
+    const int rc_ft = launch_feature_tc(sc, fr, s, used32, st);
+    if (rc_ft) return rc_ft;
+  } else if (want_feat) {
     static DeviceOnce attr_once;
     const int CB = std::min(sc->feat_dim, kFeatChan);
     const size_t smem = sizeof(float) * 64 * (size_t)CB;

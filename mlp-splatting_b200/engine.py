@@ -46,7 +46,10 @@ class PackedScene:
     """
 
     def __init__(self, positions, log_scales, quats, W1, b1, W2, b2, W3, b3, freq, att, feat_attr=None,
-                 gate_beta=1.5, gate_tau=2.0, device="cuda", pack_f16=True, pack_bf16=False):
+                 gate_beta=1.5, gate_tau=2.0, device="cuda", pack_f16=True, pack_bf16=False, feat_f16="exact"):
+        """feat_f16: "exact" keeps a binary16 copy of feat_attr for the tensor-core feature compositing when every
+        attribute is representable in binary16 (the reference's inference export stores them so,
+        scannet/checkpoints.py:358-359), "round" keeps it even when the copy rounds, "off" never."""
         lib = L.load()
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -77,8 +80,10 @@ class PackedScene:
             self.gate_beta, self.gate_tau = float(gate_beta), float(gate_tau)
             self.w16 = None
             self.wbf16 = None
+            self.feat16 = None
             self.f16_rejected = False
             self.c = self._struct()
+            self._pack_features(feat_f16)
             wbytes = int(lib.mlpsp_packed_weight_bytes(self.hidden, self.num_freq))
             if pack_f16 and wbytes > 0 and self.n > 0:
                 w16 = torch.empty(self.n * wbytes, device=d, dtype=torch.uint8)
@@ -132,8 +137,25 @@ class PackedScene:
                 self.feat_attr, self.feat_slots, self.feat_dim = fa, int(fa.shape[1]), int(fa.shape[2])
             self.gate_beta, self.gate_tau = float(gate_beta), float(gate_tau)
             self.w16, self.wbf16, self.f16_rejected = w16, None, False
+            self.feat16 = None
             self.c = self._struct()
+            self._pack_features("exact")
         return self
+
+    def _pack_features(self, mode):
+        """binary16 copy of feat_attr for the tensor-core feature compositing (see __init__)."""
+        self.feat16 = None
+        if self.feat_attr is None or mode == "off" or self.n == 0:
+            return
+        if mode not in ("exact", "round"):
+            raise ValueError("feat_f16 must be 'exact', 'round' or 'off'")
+        lib, d = L.load(), self.device
+        f16 = torch.empty(self.feat_attr.shape, device=d, dtype=torch.float16)
+        st = torch.zeros(L.STATUS_WORDS, device=d, dtype=torch.int32)
+        L.check(lib.mlpsp_pack_features_f16(C.byref(self.c), L.ptr(f16), L.ptr(st), _stream_ptr(d)), "mlpsp_pack_features_f16")
+        if mode == "round" or not (int(st[L.ST_BITS].item()) & L.BIT_FEAT_INEXACT):
+            self.feat16 = f16
+        self.c = self._struct()
 
     def _struct(self) -> L.Scene:
         s = L.Scene()
@@ -141,6 +163,7 @@ class PackedScene:
         s.W1, s.b1, s.W2, s.b2, s.W3, s.b3 = (L.ptr(t) for t in (self.W1, self.b1, self.W2, self.b2, self.W3, self.b3))
         s.w16 = L.ptr(self.w16)
         s.wbf16 = L.ptr(self.wbf16)
+        s.feat16 = L.ptr(getattr(self, "feat16", None))
         s.freq, s.att = L.ptr(self.freq), L.ptr(self.att)
         s.feat_attr, s.feat_slots, s.feat_dim = L.ptr(self.feat_attr), self.feat_slots, self.feat_dim
         s.gate_beta, s.gate_tau = self.gate_beta, self.gate_tau
@@ -164,6 +187,7 @@ class PackedScene:
         with torch.cuda.device(self.device):
             view.feat_attr = torch.matmul(self.feat_attr, tn.t()).contiguous()
         view.feat_dim = int(t.shape[0])
+        view.feat16 = None          # the projected scores are not binary16 values
         view.c = view._struct()
         return view
 

@@ -331,6 +331,36 @@ def test_feature_map_matches_oracle(dev, slots, C):
     assert np.abs(f["render"].feat).max() > 0.05
 
 
+@pytest.mark.parametrize("case,slots,C", [("ragged", 4, 512), ("dense", 4, 256), ("ragged", 5, 128), ("tiny", 1, 384),
+                                          ("one_tile", 4, 128)])
+def test_feature_map_on_tensor_cores_matches_oracle(dev, case, slots, C):
+    """Attributes that are binary16 values (the reference's inference storage, scannet/checkpoints.py:358-359) and a
+    channel count of 128 / 256 / 384 / 512: the feature map is composited by the tcgen05 kernel.  Same tolerance
+    against the oracle as the FP32 kernel, and the two kernels agree with each other."""
+    from mlp_splatting_b200.engine import PackedScene
+    scene, cam = small_case(**CASES[case])
+    rng = np.random.default_rng(100 + C + slots)
+    fa = rng.normal(0, 0.2, (scene["positions"].shape[0], slots, C)).astype(np.float16).astype(np.float32)
+    scene = dict(scene, feat_attr=fa if slots > 1 else fa[:, 0, :])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, feat=True, want_masks=False)
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    assert ps.feat16 is not None, "binary16-exact attributes must get the packed copy"
+    ro, rd = _t(cam["rays_o"], dev), _t(cam["rays_d"], dev)
+    r.render(ps, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"], precision=0, want_feat=True)
+    got = r.feat.cpu().numpy().copy()
+    np.testing.assert_allclose(got, f["render"].feat, rtol=0, atol=2e-5)
+    assert np.abs(f["render"].feat).max() > 0.05
+    ps32 = PackedScene(scene["positions"], scene["log_scales"], scene["quats"], *[scene[k] for k in WKEYS], scene["freq"],
+                       scene["att"], feat_attr=scene["feat_attr"], device=dev, pack_f16=False, feat_f16="off")
+    assert ps32.feat16 is None
+    r.render(ps32, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"], precision=0, want_feat=True)
+    np.testing.assert_allclose(got, r.feat.cpu().numpy(), rtol=0, atol=5e-6)
+    # attributes that binary16 would round keep the scene on the FP32 kernel unless the caller accepts the rounding
+    fb = scene["feat_attr"] + np.float32(1e-5)
+    assert PackedScene(scene["positions"], scene["log_scales"], scene["quats"], *[scene[k] for k in WKEYS], scene["freq"],
+                       scene["att"], feat_attr=fb, device=dev, pack_f16=False).feat16 is None
+
+
 @pytest.mark.parametrize("name,precision", [("tiny", 0), ("ragged", 0), ("dense", 0), ("tiny", 1)])
 def test_record_export_matches_oracle_records(dev, name, precision):
     """The 8-tensor record list (np_tile_kernels.cu:3138-3154) and the CSR built from it."""
