@@ -15,6 +15,7 @@
 //     two products together carry 22 mantissa bits (the attributes themselves are exact);
 //   * one thread issues the MMAs of the stage (128 x 64 x 16 each, FP32 accumulators in tensor memory) and commits
 //     them to the mbarrier that guards the stage's buffers; the other stage is filled meanwhile.
+// The copies and the record loads of the next stage are in flight while a stage is finished.
 // Afterwards each warp reads its 32 channels x 64 pixels from tensor memory and writes 128-byte lines of the map.
 //
 // Every wait on an mbarrier is bounded (MLPSP_ST_TIMEOUT), copies in flight are waited for, tensor memory is freed.
@@ -26,6 +27,16 @@ namespace mlpsp {
 constexpr int kFtThreads = 256;
 constexpr int kFtPairs = 16;          // touched primitives per stage
 constexpr int kFtListMax = 2048;      // candidates of a tile the kernel looks at (kWinMax of the wave kernels)
+constexpr int kFtMeta = 256;          // touched primitives whose masks and bases are held in shared memory at a time
+
+// what the kernel needs of one touched (tile, primitive) pair
+struct __align__(8) FtMeta {
+  int32_t prim;
+  uint32_t base;     // compositing slot of the pair's first record
+  uint32_t u0, u1;   // pixels that composited the primitive
+  uint32_t m0, m1;   // pixels whose hit was evaluated (the record's slot is its rank among them)
+};
+static_assert(sizeof(FtMeta) == 24, "shared-memory plan");
 
 __device__ __forceinline__ void ft_cp_async16(uint32_t dst, const void* src, bool valid) {
   const uint32_t n = valid ? 16u : 0u;   // source size 0: the 16 bytes are written as zeros
@@ -46,11 +57,11 @@ struct FtPlan {
   __host__ __device__ static constexpr int a_bytes(int CB) { return K * CB * 2; }
   static constexpr int kCoefBytes = 64 * K * 2;
   __host__ __device__ static constexpr int stage_bytes(int CB) { return a_bytes(CB) + 2 * kCoefBytes; }
-  __host__ __device__ static constexpr int smem_bytes(int CB) { return 2 * stage_bytes(CB) + 2 * kFtListMax + 64; }
+  __host__ __device__ static constexpr int smem_bytes(int CB) { return 2 * stage_bytes(CB) + 2 * kFtListMax + kFtMeta * 24 + 64; }
 };
 
 template <int S>
-__global__ void __launch_bounds__(kFtThreads) k_feature_tc(
+__global__ void __launch_bounds__(kFtThreads, 2) k_feature_tc(
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, const int32_t* __restrict__ sorted_prims,
     int W, int H, int ntx, const uint32_t* __restrict__ used32, const uint32_t* __restrict__ masks32,
     const uint32_t* __restrict__ pair_base, const float* __restrict__ rec_w, const float4* __restrict__ rec_gate,
@@ -64,7 +75,8 @@ __global__ void __launch_bounds__(kFtThreads) k_feature_tc(
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int stage_bytes = P::stage_bytes(CB);
   uint16_t* s_idx = reinterpret_cast<uint16_t*>(smem + 2 * stage_bytes);            // touched candidates of the tile
-  uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + 2 * stage_bytes + 2 * kFtListMax);   // [0..1] MMAs of a stage buffer done
+  FtMeta* s_meta = reinterpret_cast<FtMeta*>(smem + 2 * stage_bytes + 2 * kFtListMax);
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + 2 * stage_bytes + 2 * kFtListMax + kFtMeta * 24);   // [0..1] MMAs of a stage buffer done
   uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2);                        // [0] tmem base
   const uint32_t sb = smem_u32(smem);
   const uint32_t bar0 = smem_u32(&s_bar[0]);
@@ -97,60 +109,67 @@ __global__ void __launch_bounds__(kFtThreads) k_feature_tc(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_misc[0];
-  const int nst = (nt + kFtPairs - 1) / kFtPairs;
   const int a_bytes = P::a_bytes(CB);
   const uint32_t lbo_a = (uint32_t)CB * 16u;      // between groups of eight K rows
   const uint32_t idesc = ft_instr_desc(128, 64);
   bool ok = true;
+  int gs = 0;                                     // stages issued so far: buffer = gs & 1, use of that buffer = gs >> 1
+  const int px = tid & 63;
 
-  for (int st = 0; st < nst; ++st) {
-    const int buf = st & 1;
-    const uint32_t a_s = sb + buf * stage_bytes;
-    char* coef_hi = smem + buf * stage_bytes + a_bytes;
-    char* coef_lo = coef_hi + P::kCoefBytes;
-    if (st >= 2) {
-      // the MMAs that read this buffer two stages ago have finished
-      ok = mbar_wait(bar0 + 8 * buf, (uint32_t)((st >> 1) - 1) & 1u) && ok;
-    }
-    // ---- attribute rows of the stage's primitives: a warp copies eight K rows x four channel groups at a time, so
-    // that eight lanes fill one 128-byte core matrix (no bank conflicts) and four lanes read 64 contiguous bytes ----
+  // the MMAs that last read the buffer of stage g (two stages earlier) have finished
+  auto buffer_free = [&](int g) {
+    if (g >= 2) ok = mbar_wait(bar0 + 8 * (g & 1), (uint32_t)((g >> 1) - 1) & 1u) && ok;
+  };
+  // Attribute rows of the 16 primitives from touched index t0 on (batch-local index l0): a warp copies eight K rows x
+  // four channel groups at a time, so that eight lanes fill one 128-byte core matrix (no bank conflicts) and four
+  // lanes read 64 contiguous bytes.  One cp.async group per stage.
+  auto issue_copies = [&](int g, int l0, int nb) {
+    const uint32_t a_s = sb + (g & 1) * stage_bytes;
     const int gq_n = CB / 32;
     for (int task = warp; task < (K / 8) * gq_n; task += kFtThreads / 32) {
       const int kg = task / gq_n, gq = task - kg * gq_n;
-      const int k = kg * 8 + (lane & 7), g = gq * 4 + (lane >> 3);
+      const int k = kg * 8 + (lane & 7), grp = gq * 4 + (lane >> 3);
       const int pl = k / S, sl = k - pl * S;
-      const int t = st * kFtPairs + pl;
-      const bool valid = t < nt;
-      const int prim = valid ? __ldg(sorted_prims + s + s_idx[t]) : 0;
-      const __half* src = feat16 + ((size_t)prim * S + sl) * C + c0 + g * 8;
-      ft_cp_async16(a_s + kg * lbo_a + g * 128 + (lane & 7) * 16, src, valid);
+      const bool valid = l0 + pl < nb;
+      const int prim = valid ? s_meta[l0 + pl].prim : 0;
+      const __half* src = feat16 + ((size_t)prim * S + sl) * C + c0 + grp * 8;
+      ft_cp_async16(a_s + kg * lbo_a + grp * 128 + (lane & 7) * 16, src, valid);
     }
-    // ---- coefficients: thread = (pixel, four of the stage's primitives) ----
-    const int px = tid & 63;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // weight and gates of this thread's four (pixel, primitive) cells of a stage; zero where the pixel did not
+  // composite the primitive
+  auto load_cells = [&](int l0, int nb, float (&cw)[kFtPairs / 4], float4 (&cg)[kFtPairs / 4]) {
+#pragma unroll
+    for (int i = 0; i < kFtPairs / 4; ++i) {
+      const int l = l0 + (tid >> 6) + 4 * i;
+      cw[i] = 0.f;
+      cg[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (l < nb) {
+        const FtMeta m = s_meta[l];
+        const uint32_t u = px < 32 ? m.u0 : m.u1;
+        if ((u >> (px & 31)) & 1u) {
+          const uint32_t slot = m.base + (px < 32 ? __popc(m.m0 & ((1u << px) - 1u))
+                                                  : __popc(m.m0) + __popc(m.m1 & ((1u << (px - 32)) - 1u)));
+          cw[i] = __ldg(rec_w + slot);
+          if (S > 1) cg[i] = __ldg(rec_gate + slot);
+        }
+      }
+    }
+  };
+  // coefficients of the cells, head + tail in binary16; K index of slot sl of the stage's primitive pl is pl * S + sl,
+  // element (pixel, k) sits at (k / 8) * 1024 + pixel * 16 + (k % 8) * 2
+  auto write_coefs = [&](int g, const float (&cw)[kFtPairs / 4], const float4 (&cg)[kFtPairs / 4]) {
+    char* coef_hi = smem + (g & 1) * stage_bytes + a_bytes;
+    char* coef_lo = coef_hi + P::kCoefBytes;
 #pragma unroll
     for (int i = 0; i < kFtPairs / 4; ++i) {
       const int pl = (tid >> 6) + 4 * i;
-      const int t = st * kFtPairs + pl;
-      float cf[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
-      if (t < nt) {
-        const size_t pi = (size_t)(s + s_idx[t]);
-        const uint32_t u = __ldg(used32 + 2 * pi + (px >> 5));
-        if ((u >> (px & 31)) & 1u) {
-          const uint32_t m0 = __ldg(masks32 + 2 * pi), m1 = __ldg(masks32 + 2 * pi + 1);
-          const uint32_t slot = __ldg(pair_base + pi) +
-                                (px < 32 ? __popc(m0 & ((1u << px) - 1u)) : __popc(m0) + __popc(m1 & ((1u << (px - 32)) - 1u)));
-          const float w = __ldg(rec_w + slot);
-          if (S == 1) {
-            cf[0] = w;
-          } else {
-            const float4 g = __ldg(rec_gate + slot);
-            if (S == 4) { cf[0] = w * g.x; cf[1] = w * g.y; cf[2] = w * g.z; cf[3] = w * g.w; }
-            else { cf[0] = w; cf[1] = w * g.x; cf[2] = w * g.y; cf[3] = w * g.z; cf[4] = w * g.w; }
-          }
-        }
-      }
-      // head + tail in binary16; K index of slot sl is pl * S + sl, element (pixel, k) sits at
-      // (k / 8) * 1024 + pixel * 16 + (k % 8) * 2
+      const float w = cw[i];
+      float cf[5];
+      if (S == 1) { cf[0] = w; }
+      else if (S == 4) { cf[0] = w * cg[i].x; cf[1] = w * cg[i].y; cf[2] = w * cg[i].z; cf[3] = w * cg[i].w; }
+      else { cf[0] = w; cf[1] = w * cg[i].x; cf[2] = w * cg[i].y; cf[3] = w * cg[i].z; cf[4] = w * cg[i].w; }
       __half hi[5], lo[5];
 #pragma unroll
       for (int sl = 0; sl < S; ++sl) {
@@ -173,27 +192,63 @@ __global__ void __launch_bounds__(kFtThreads) k_feature_tc(
         }
       }
     }
-    ft_cp_async_wait_all();
-    fence_async_smem();
-    tc_fence_before();
-    if (!__syncthreads_and(ok)) { ok = false; break; }
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t hi_s = a_s + a_bytes, lo_s = hi_s + P::kCoefBytes;
-      for (int h = 0; h < nb128; ++h) {
-        // A: MN-major, 128 channels = 16 groups of eight (128 bytes apart), K groups of eight lbo_a apart
-        const uint64_t a_desc = smem_desc(a_s + h * 2048, lbo_a, 128);
-        const uint64_t bh_desc = smem_desc(hi_s, 1024, 128), bl_desc = smem_desc(lo_s, 1024, 128);
-#pragma unroll 1
-        for (int ks = 0; ks < K / 16; ++ks) {
-          const uint64_t a_k = a_desc + (uint64_t)((ks * 2 * lbo_a) >> 4);
-          mma_f16(tmem + h * 64, a_k, bh_desc + (uint64_t)((ks * 2 * 1024) >> 4), idesc, (st > 0 || ks > 0) ? 1u : 0u);
-          mma_f16(tmem + h * 64, a_k, bl_desc + (uint64_t)((ks * 2 * 1024) >> 4), idesc, 1u);
-        }
-      }
-      mma_commit(bar0 + 8 * buf);
+  };
+
+  for (int b0 = 0; b0 < nt && ok; b0 += kFtMeta) {
+    const int nb = min(kFtMeta, nt - b0);
+    // ---- the batch's primitives, consumed masks, hit masks and record bases ----
+    __syncthreads();
+    for (int l = tid; l < nb; l += kFtThreads) {
+      const size_t pi = (size_t)(s + s_idx[b0 + l]);
+      const uint2 u = *reinterpret_cast<const uint2*>(used32 + 2 * pi), m = *reinterpret_cast<const uint2*>(masks32 + 2 * pi);
+      FtMeta e;
+      e.prim = __ldg(sorted_prims + pi); e.base = __ldg(pair_base + pi); e.u0 = u.x; e.u1 = u.y; e.m0 = m.x; e.m1 = m.y;
+      s_meta[l] = e;
     }
+    __syncthreads();
+    // ---- stages of 16 primitives; the copies and the record loads of stage l+1 are in flight while stage l is
+    // finished and handed to the tensor cores ----
+    const int nsb = (nb + kFtPairs - 1) / kFtPairs;
+    float cw[kFtPairs / 4];
+    float4 cg[kFtPairs / 4];
+    buffer_free(gs);
+    issue_copies(gs, 0, nb);
+    load_cells(0, nb, cw, cg);
+    for (int ls = 0; ls < nsb; ++ls) {
+      const int g = gs + ls;
+      const bool more = ls + 1 < nsb;
+      if (more) {
+        buffer_free(g + 1);
+        issue_copies(g + 1, (ls + 1) * kFtPairs, nb);
+      }
+      write_coefs(g, cw, cg);
+      if (more) load_cells((ls + 1) * kFtPairs, nb, cw, cg);
+      if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
+      else asm volatile("cp.async.wait_group 0;" ::: "memory");
+      fence_async_smem();
+      tc_fence_before();
+      if (!__syncthreads_and(ok)) { ok = false; break; }
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t a_s = sb + (g & 1) * stage_bytes;
+        const uint32_t hi_s = a_s + a_bytes, lo_s = hi_s + P::kCoefBytes;
+        const uint64_t bh_desc = smem_desc(hi_s, 1024, 128), bl_desc = smem_desc(lo_s, 1024, 128);
+        for (int h = 0; h < nb128; ++h) {
+          // A: MN-major, 128 channels = 16 groups of eight (128 bytes apart), K groups of eight lbo_a apart
+          const uint64_t a_desc = smem_desc(a_s + h * 2048, lbo_a, 128);
+#pragma unroll
+          for (int ks = 0; ks < K / 16; ++ks) {
+            const uint64_t a_k = a_desc + (uint64_t)((ks * 2 * lbo_a) >> 4);
+            mma_f16(tmem + h * 64, a_k, bh_desc + (uint64_t)((ks * 2 * 1024) >> 4), idesc, (g > 0 || ks > 0) ? 1u : 0u);
+            mma_f16(tmem + h * 64, a_k, bl_desc + (uint64_t)((ks * 2 * 1024) >> 4), idesc, 1u);
+          }
+        }
+        mma_commit(bar0 + 8 * (g & 1));
+      }
+    }
+    gs += nsb;
   }
+  const int nst = gs;
 
   // ---- the last stage's MMAs (tensor-core instructions complete in order) ----
   if (ok && nst > 0) {
