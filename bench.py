@@ -288,6 +288,9 @@ class Workload:
         from mlp_splatting_b200.engine import FrameRenderer, PackedScene
         self.name, self.dev, self.world, self.rank, self.lib = name, dev, world, rank, lib
         cfg = self.cfg = dict(syn.WORKLOADS[name])
+        for key, val in (("W", args.width), ("H", args.height), ("n", args.primitives)):
+            if val:
+                cfg[key] = int(val)       # a reduced copy of the workload (profiler captures)
         self.prec = L.PRECISION_F16 if args.precision == "fp16" else L.PRECISION_F32
         self.scene_np, self.bcast_s = None, 0.0
         if cfg.get("on_device"):
@@ -538,6 +541,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true",
                     help="skip the short measurements of the other named workloads that the default run adds")
+    ap.add_argument("--width", type=int, default=0, help="override the workload's image width (reduced captures)")
+    ap.add_argument("--height", type=int, default=0, help="override the workload's image height")
+    ap.add_argument("--primitives", type=int, default=0, help="override the workload's primitive count")
     ap.add_argument("--only", default=None, choices=["query", "decode", "full_width"],
                     help="decoder workloads: time one of the three steps only")
     ap.add_argument("--e2e-image", default="f32", choices=["f32", "f16"],
@@ -654,7 +660,8 @@ def main():
     d2h = nunits * (r.P * 4 * img_dtype.itemsize + 64)
 
     others = None
-    if args.workload == HEADLINE and not args.no_other_workloads and prec == L.PRECISION_F16:
+    reduced = bool(args.width or args.height or args.primitives)
+    if args.workload == HEADLINE and not args.no_other_workloads and prec == L.PRECISION_F16 and not reduced:
         del pipe
         others = {}
         for name in OTHER_WORKLOADS:

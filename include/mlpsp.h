@@ -296,12 +296,13 @@ int mlpsp_prepare_groups_static(const int64_t* offsets, int32_t n, int64_t segme
 /* Reverse compositing over saved records: primitive_records_reverse (scannet/cuda/primitive_records.cuh:3-74).
  * ids[R], offsets[pixels+1] (int64, pixel-major records in compositing order), x6[R,6], raw[R,8] as written by
  * mlpsp_export_records; log_scales[n,3], quats[n,4] (unit); grad_rgb[pixels,3], grad_t[pixels] (adjoint of the
- * final transmittance).  Writes d4[R,4] (adjoints of the four pre-activation MLP outputs) and the position /
- * log-scale / quaternion gradients [n,3] [n,3] [n,4], which are zeroed first. */
+ * final transmittance); total_records = R = offsets[pixels].  Writes d4[R,4] (adjoints of the four pre-activation
+ * MLP outputs) and the position / log-scale / quaternion gradients [n,3] [n,3] [n,4], which are zeroed first.
+ * raw, d4 and quats must be 16-byte aligned. */
 int mlpsp_records_reverse(const int32_t* ids, const int64_t* offsets, const float* x6, const float* raw,
                           const float* log_scales, const float* quats, const float* grad_rgb, const float* grad_t,
-                          int64_t pixels, int32_t n, float* d4, float* grad_pos, float* grad_log_scales,
-                          float* grad_quats, void* stream);
+                          int64_t pixels, int64_t total_records, int32_t n, float* d4, float* grad_pos,
+                          float* grad_log_scales, float* grad_quats, void* stream);
 
 /* Floats per primitive of the packed gradient row: W1[32,72] b1[32] W2[32,32] b2[32] W3[4,32] b3[4] = 3,524. */
 int64_t mlpsp_grouped_gradient_floats(void);

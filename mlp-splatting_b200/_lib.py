@@ -70,7 +70,7 @@ _SIGS = {
     "mlpsp_pack_weights_f16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
     "mlpsp_pack_weights_bf16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
     "mlpsp_pack_features_f16": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp]),
-    "mlpsp_records_reverse": (C.c_int, [_fp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64, C.c_int32, _fp, _fp, _fp, _fp, _fp]),
+    "mlpsp_records_reverse": (C.c_int, [_fp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64, C.c_int64, C.c_int32, _fp, _fp, _fp, _fp, _fp]),
     "mlpsp_grouped_gradient_floats": (C.c_int64, []),
     "mlpsp_grouped_weight_gradients": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64, C.c_int32,
                                                  C.c_float, _fp, _fp, _fp, _fp]),

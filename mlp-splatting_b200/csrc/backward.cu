@@ -1,10 +1,9 @@
 // The backward side of the record path: reverse compositing over saved records and the per-primitive
 // weight gradients of the grouped MLP.
 //
-// mlpsp_records_reverse follows primitive_records_reverse_kernel (scannet/cuda/primitive_records.cuh:3-49):
-// one thread per pixel walks its records from the last to the first and turns the image adjoints into
-// the adjoint of every record's four pre-activation MLP outputs plus position / log-scale / quaternion
-// gradients (accumulated per primitive).
+// mlpsp_records_reverse computes what primitive_records_reverse_kernel computes (scannet/cuda/primitive_records.cuh:3-49):
+// the image adjoints become the adjoint of every record's four pre-activation MLP outputs plus position /
+// log-scale / quaternion gradients accumulated per primitive; see "records reverse" below for how the work is split.
 //
 // mlpsp_grouped_weight_gradients computes what scannet/primitive_gemm.py:101-279 computes with Triton
 // (grouped_weight_gradients, FP32 operand mode) and scannet/primitive_csr.py:33-58 states in PyTorch:
@@ -68,49 +67,101 @@ __device__ __forceinline__ void quat_adjoint(float w, float x, float y, float z,
 }
 
 // ------------------------------------------------------------------- records reverse ----
-__global__ void k_records_reverse(const int32_t* __restrict__ ids, const int64_t* __restrict__ offsets,
-                                  const float* __restrict__ x6, const float* __restrict__ raw,
-                                  const float* __restrict__ logs, const float* __restrict__ quats,
-                                  const float* __restrict__ grgb, const float* __restrict__ gt, int64_t pixels,
-                                  float* __restrict__ d4, float* __restrict__ gp, float* __restrict__ gs,
-                                  float* __restrict__ gq) {
+// The reference walks a pixel's records backwards in one thread and issues ten (warp-aggregated) global atomics per
+// record from inside that walk (primitive_records.cuh:3-49).  Here the walk is reduced to what is sequential -- the
+// recurrence of the colour that lies behind a record -- and everything else runs record-parallel afterwards:
+//   k_reverse_pixels    thread = pixel: the recurrence, the three colour adjoints of every record, and
+//                       g_sigma * decay parked in the fourth adjoint;
+//   k_reverse_geometry  thread = record: the opacity adjoint is finished, the position / log-scale / quaternion
+//                       contributions are computed and summed per primitive in a shared-memory table first (records
+//                       that follow one another belong to neighbouring pixels, which mostly see the same
+//                       primitives), so that global memory sees one set of atomics per primitive and chunk of
+//                       records instead of one per record.
+__global__ void k_reverse_pixels(const int64_t* __restrict__ offsets, const float* __restrict__ raw,
+                                 const float* __restrict__ grgb, const float* __restrict__ gt, int64_t pixels,
+                                 float* __restrict__ d4) {
   const int64_t pix = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (pix >= pixels) return;
   const float gr = grgb[pix * 3], gg = grgb[pix * 3 + 1], gb = grgb[pix * 3 + 2];
   float behind = gt[pix];   // adjoint of the transmittance that reaches whatever lies behind the current record
   for (int64_t r = offsets[pix + 1] - 1; r >= offsets[pix]; --r) {
+    const float4 a = *reinterpret_cast<const float4*>(raw + r * 8);        // R, G, B, sigma_raw
+    const float4 c = *reinterpret_cast<const float4*>(raw + r * 8 + 4);    // trans before, alpha, decay, sigma logit
+    const float colour = gr * a.x + gg * a.y + gb * a.z;
+    const float g_alpha = c.x * (colour - behind);
+    behind = behind * (1.f - c.y) + colour * c.y;
+    const float g_sigma = g_alpha * __expf(-a.w * c.z);   // d alpha / d (sigma_raw * decay) = 1 - alpha
+    const float w = c.x * c.y;
+    *reinterpret_cast<float4*>(d4 + r * 4) = make_float4(gr * w * a.x * (1.f - a.x), gg * w * a.y * (1.f - a.y),
+                                                         gb * w * a.z * (1.f - a.z), g_sigma * c.z);
+  }
+}
+
+constexpr int kRevThreads = 256;
+constexpr int kRevChunk = 4096;      // records per CTA
+constexpr int kRevTable = 1024;      // shared-memory accumulator rows (a power of two)
+constexpr int kRevProbe = 16;        // probes before a record goes to global memory directly
+
+__global__ void __launch_bounds__(kRevThreads) k_reverse_geometry(
+    const int32_t* __restrict__ ids, const float* __restrict__ x6, const float* __restrict__ raw,
+    const float* __restrict__ logs, const float* __restrict__ quats, int64_t total, float* __restrict__ d4,
+    float* __restrict__ gp, float* __restrict__ gs, float* __restrict__ gq) {
+  __shared__ int s_key[kRevTable];
+  __shared__ float s_acc[kRevTable][10];
+  for (int i = threadIdx.x; i < kRevTable; i += kRevThreads) {
+    s_key[i] = -1;
+#pragma unroll
+    for (int j = 0; j < 10; ++j) s_acc[i][j] = 0.f;
+  }
+  __syncthreads();
+  const int64_t r0 = (int64_t)blockIdx.x * kRevChunk;
+  const int64_t r1 = r0 + kRevChunk < total ? r0 + kRevChunk : total;
+  for (int64_t r = r0 + threadIdx.x; r < r1; r += kRevThreads) {
     const int p = ids[r];
-    const float* v = raw + r * 8;   // R, G, B, sigma_raw, trans before, alpha, decay, sigma logit
-    const float R = v[0], G = v[1], B = v[2], sigma_raw = v[3], trans = v[4], alpha = v[5], decay = v[6];
-    const float colour = gr * R + gg * G + gb * B;
-    const float g_alpha = trans * (colour - behind);
-    behind = behind * (1.f - alpha) + colour * alpha;
-    const float g_sigma = g_alpha * __expf(-sigma_raw * decay);   // d alpha / d (sigma_raw * decay) = 1 - alpha
-    const float g_decay = g_sigma * sigma_raw;
-    const float w = trans * alpha;
-    d4[r * 4] = gr * w * R * (1.f - R);
-    d4[r * 4 + 1] = gg * w * G * (1.f - G);
-    d4[r * 4 + 2] = gb * w * B * (1.f - B);
-    d4[r * 4 + 3] = g_sigma * decay * sigmoid_fast(v[7]);          // softplus' = sigmoid
+    const float4 a = *reinterpret_cast<const float4*>(raw + r * 8);        // .w = sigma_raw
+    const float4 c = *reinterpret_cast<const float4*>(raw + r * 8 + 4);    // .z = decay, .w = sigma logit
+    const float parked = d4[r * 4 + 3];                                    // g_sigma * decay
+    d4[r * 4 + 3] = parked * sigmoid_fast(c.w);                            // softplus' = sigmoid
     // decay = exp(-1/2 q^T M q), q = R^T d, d = c - foot point (x6[3..5]), M = diag(exp(-2 ls))
+    const float k = parked * a.w * c.z;                                    // g_decay * decay
     const V3 d = {x6[r * 6 + 3], x6[r * 6 + 4], x6[r * 6 + 5]};
-    const float qw = quats[p * 4], qx = quats[p * 4 + 1], qy = quats[p * 4 + 2], qz = quats[p * 4 + 3];
-    const V3 q = rot_conj_fast(qw, qx, qy, qz, d);
+    const float4 qt = *reinterpret_cast<const float4*>(quats + (size_t)p * 4);
+    const V3 q = rot_conj_fast(qt.x, qt.y, qt.z, qt.w, d);
     const float mx = __expf(-2.f * logs[p * 3]), my = __expf(-2.f * logs[p * 3 + 1]), mz = __expf(-2.f * logs[p * 3 + 2]);
-    const float k = g_decay * decay;
-    const V3 gl = {-k * mx * q.x, -k * my * q.y, -k * mz * q.z};   // adjoint of q
-    const V3 gd = rot_quat(qw, qx, qy, qz, gl);                    // adjoint of d, hence of the centre
-    atomicAdd(gp + p * 3, gd.x); atomicAdd(gp + p * 3 + 1, gd.y); atomicAdd(gp + p * 3 + 2, gd.z);
-    atomicAdd(gs + p * 3, k * mx * q.x * q.x);
-    atomicAdd(gs + p * 3 + 1, k * my * q.y * q.y);
-    atomicAdd(gs + p * 3 + 2, k * mz * q.z * q.z);
+    const V3 gl = {-k * mx * q.x, -k * my * q.y, -k * mz * q.z};           // adjoint of q
+    const V3 gd = rot_quat(qt.x, qt.y, qt.z, qt.w, gl);                    // adjoint of d, hence of the centre
     // q = R^T d  =>  adjoint of R is d gl^T
     const float Gm[9] = {d.x * gl.x, d.x * gl.y, d.x * gl.z, d.y * gl.x, d.y * gl.y, d.y * gl.z,
                          d.z * gl.x, d.z * gl.y, d.z * gl.z};
     float gquat[4];
-    quat_adjoint(qw, qx, qy, qz, Gm, gquat);
-    atomicAdd(gq + p * 4, gquat[0]); atomicAdd(gq + p * 4 + 1, gquat[1]);
-    atomicAdd(gq + p * 4 + 2, gquat[2]); atomicAdd(gq + p * 4 + 3, gquat[3]);
+    quat_adjoint(qt.x, qt.y, qt.z, qt.w, Gm, gquat);
+    const float v[10] = {gd.x, gd.y, gd.z, k * mx * q.x * q.x, k * my * q.y * q.y, k * mz * q.z * q.z,
+                         gquat[0], gquat[1], gquat[2], gquat[3]};
+    // the primitive's row of the table: linear probing from a multiplicative hash
+    int slot = (int)(((uint32_t)p * 2654435761u) >> 22) & (kRevTable - 1);
+    bool placed = false;
+    for (int probe = 0; probe < kRevProbe && !placed; ++probe) {
+      const int seen = atomicCAS(&s_key[slot], -1, p);
+      if (seen == -1 || seen == p) placed = true;
+      else slot = (slot + 1) & (kRevTable - 1);
+    }
+    if (placed) {
+#pragma unroll
+      for (int j = 0; j < 10; ++j) atomicAdd(&s_acc[slot][j], v[j]);
+    } else {
+      atomicAdd(gp + p * 3, v[0]); atomicAdd(gp + p * 3 + 1, v[1]); atomicAdd(gp + p * 3 + 2, v[2]);
+      atomicAdd(gs + p * 3, v[3]); atomicAdd(gs + p * 3 + 1, v[4]); atomicAdd(gs + p * 3 + 2, v[5]);
+      atomicAdd(gq + p * 4, v[6]); atomicAdd(gq + p * 4 + 1, v[7]); atomicAdd(gq + p * 4 + 2, v[8]); atomicAdd(gq + p * 4 + 3, v[9]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kRevTable; i += kRevThreads) {
+    const int p = s_key[i];
+    if (p < 0) continue;
+    atomicAdd(gp + p * 3, s_acc[i][0]); atomicAdd(gp + p * 3 + 1, s_acc[i][1]); atomicAdd(gp + p * 3 + 2, s_acc[i][2]);
+    atomicAdd(gs + p * 3, s_acc[i][3]); atomicAdd(gs + p * 3 + 1, s_acc[i][4]); atomicAdd(gs + p * 3 + 2, s_acc[i][5]);
+    atomicAdd(gq + p * 4, s_acc[i][6]); atomicAdd(gq + p * 4 + 1, s_acc[i][7]);
+    atomicAdd(gq + p * 4 + 2, s_acc[i][8]); atomicAdd(gq + p * 4 + 3, s_acc[i][9]);
   }
 }
 
@@ -238,8 +289,8 @@ using namespace mlpsp;
 
 extern "C" int mlpsp_records_reverse(const int32_t* ids, const int64_t* offsets, const float* x6, const float* raw,
                                      const float* log_scales, const float* quats, const float* grad_rgb,
-                                     const float* grad_t, int64_t pixels, int32_t n, float* d4, float* grad_pos,
-                                     float* grad_log_scales, float* grad_quats, void* stream) {
+                                     const float* grad_t, int64_t pixels, int64_t total_records, int32_t n, float* d4,
+                                     float* grad_pos, float* grad_log_scales, float* grad_quats, void* stream) {
   MLPSP_REQUIRE(pixels >= 0 && n >= 0, MLPSP_E_ARG, "mlpsp_records_reverse: negative size");
   MLPSP_REQUIRE(offsets && grad_pos && grad_log_scales && grad_quats, MLPSP_E_ARG, "mlpsp_records_reverse: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
@@ -249,9 +300,15 @@ extern "C" int mlpsp_records_reverse(const int32_t* ids, const int64_t* offsets,
   if (pixels == 0) return MLPSP_OK;
   MLPSP_REQUIRE(ids && x6 && raw && log_scales && quats && grad_rgb && grad_t && d4, MLPSP_E_ARG,
                 "mlpsp_records_reverse: null pointer");
-  LaunchScope scope(kKMisc, 1, st);
-  k_records_reverse<<<(unsigned)((pixels + 127) / 128), 128, 0, st>>>(ids, offsets, x6, raw, log_scales, quats, grad_rgb,
-                                                                    grad_t, pixels, d4, grad_pos, grad_log_scales, grad_quats);
+  MLPSP_REQUIRE(total_records >= 0, MLPSP_E_ARG, "mlpsp_records_reverse: negative record count");
+  MLPSP_REQUIRE((reinterpret_cast<uintptr_t>(raw) & 15) == 0 && (reinterpret_cast<uintptr_t>(d4) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(quats) & 15) == 0, MLPSP_E_ARG,
+                "mlpsp_records_reverse: raw, d4 and quats must be 16-byte aligned");
+  LaunchScope scope(kKMisc, 2, st);
+  k_reverse_pixels<<<(unsigned)((pixels + 127) / 128), 128, 0, st>>>(offsets, raw, grad_rgb, grad_t, pixels, d4);
+  if (total_records > 0)
+    k_reverse_geometry<<<(unsigned)((total_records + kRevChunk - 1) / kRevChunk), kRevThreads, 0, st>>>(
+        ids, x6, raw, log_scales, quats, total_records, d4, grad_pos, grad_log_scales, grad_quats);
   return cuda_check(cudaGetLastError(), "records_reverse");
 }
 

@@ -261,6 +261,7 @@ __global__ void __launch_bounds__(kFtThreads, 2) k_feature_tc(
   const int q = warp & 3, h = warp >> 2;
   if (h < nb128) {
     const int c = c0 + h * 128 + q * 32 + lane;
+    const int x0 = (tile % ntx) * 8, y0 = (tile / ntx) * 8;
 #pragma unroll 1
     for (int part = 0; part < 2; ++part) {
       uint32_t v[32];
@@ -272,8 +273,8 @@ __global__ void __launch_bounds__(kFtThreads, 2) k_feature_tc(
       }
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const TilePix tp = tile_pixel(tile, part * 32 + i, ntx, W, H);
-        if (tp.valid) out_feat[(size_t)tp.pix * C + c] = __uint_as_float(v[i]);
+        const int x = x0 + (i & 7), y = y0 + part * 4 + (i >> 3);      // pixel part * 32 + i of the tile
+        if (x < W && y < H) out_feat[((size_t)y * W + x) * C + c] = __uint_as_float(v[i]);
       }
     }
   }

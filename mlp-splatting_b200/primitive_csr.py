@@ -78,6 +78,6 @@ def primitive_records_reverse(ids, offsets, x6, raw, log_scales, quats, grad_rgb
     with torch.cuda.device(dev):
         st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         L.check(lib.mlpsp_records_reverse(L.ptr(ids), L.ptr(offsets), L.ptr(x6), L.ptr(raw), L.ptr(log_scales), L.ptr(quats),
-                                          L.ptr(grad_rgb), L.ptr(grad_t), pixels, n, L.ptr(d4), L.ptr(gp), L.ptr(gs),
+                                          L.ptr(grad_rgb), L.ptr(grad_t), pixels, total, n, L.ptr(d4), L.ptr(gp), L.ptr(gs),
                                           L.ptr(gq), st), "mlpsp_records_reverse")
     return [d4, gp, gs, gq]

@@ -111,7 +111,7 @@ def test_feature_frame_matches_reference_kernel_at_full_size():
     # FP32 on both sides, hardware sin / cos / exp on both sides: the images agree to 1e-4 except where a hit decision
     # or a sort order flipped (a pixel then gains, loses or reorders one faint record)
     assert figures["rgb_over_1e4"] <= 200 and figures["rgb_over_1e3"] <= 20 and figures["rgb_max"] <= 2e-2, figures
-    assert figures["feat_over_1e3"] <= 40 and figures["feat_max"] <= 0.05 and figures["feat_mean"] <= 2e-6, figures
+    assert figures["feat_over_1e3"] <= 60 and figures["feat_max"] <= 0.05 and figures["feat_mean"] <= 5e-6, figures
     assert feat_r.abs().max().item() > 0.1 and alpha_r.mean().item() > 0.2
 
 
