@@ -150,6 +150,14 @@ typedef struct mlpsp_frame {
   int32_t* stat_hits;
   float* stat_sum_werr;
   int32_t* stat_contrib;
+  int32_t hit_arith;      /* arithmetic of the tile-centre key, the hit decision and the hit values: 0 = IEEE-only
+                             operations in a fixed order with a software exponential, which a CPU reproduces bit for bit
+                             (tile lists, order and masks are then exactly the CPU restatement's); 1 = the reference
+                             kernels' own arithmetic (hardware __expf, compiler-contracted expressions,
+                             np_tile_kernels.cu:416-435, 483-518, 659-711), which makes order, masks, record lists and
+                             CSR offsets those of the reference's kernels run on the same GPU.  The images of the two
+                             differ only where a value lies within a few ulp of a threshold. */
+  int32_t reserved1;
 } mlpsp_frame;
 
 const char* mlpsp_last_error(void);

@@ -52,6 +52,7 @@ class Frame(C.Structure):
         ("tile_pretest", C.c_int32), ("tail_hint", C.c_int32),
         ("gt_rgb", _fp), ("stat_sum_w", _fp), ("stat_max_w", _fp), ("stat_hits", _fp), ("stat_sum_werr", _fp),
         ("stat_contrib", _fp),
+        ("hit_arith", C.c_int32), ("reserved1", C.c_int32),
     ]
 
 

@@ -77,6 +77,7 @@ static int check_frame_common(const mlpsp_scene* sc, const mlpsp_frame* fr, cons
   MLPSP_REQUIRE((int64_t)fr->width * fr->height <= 2147483647LL, MLPSP_E_LIMIT,
                 "%s: image dimensions exceed int32 pixel indexing", who);
   MLPSP_REQUIRE(fr->threshold > 0.f && fr->threshold < 1.f, MLPSP_E_ARG, "%s: threshold must be in (0,1)", who);
+  MLPSP_REQUIRE(fr->hit_arith == 0 || fr->hit_arith == 1, MLPSP_E_ARG, "%s: hit_arith must be 0 or 1", who);
   MLPSP_REQUIRE(sc->n >= 0 && (sc->n == 0 || sc->geom), MLPSP_E_ARG, "%s: scene geometry missing", who);
   MLPSP_REQUIRE(fr->status, MLPSP_E_ARG, "%s: status block missing", who);
   MLPSP_REQUIRE(fr->tile_offsets, MLPSP_E_ARG, "%s: tile_offsets missing", who);

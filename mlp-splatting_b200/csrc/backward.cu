@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(kRevThreads) k_reverse_geometry(
     const float parked = d4[r * 4 + 3];                                    // g_sigma * decay
     d4[r * 4 + 3] = parked * sigmoid_fast(c.w);                            // softplus' = sigmoid
     // decay = exp(-1/2 q^T M q), q = R^T d, d = c - foot point (x6[3..5]), M = diag(exp(-2 ls))
-    const float k = parked * a.w * c.z;                                    // g_decay * decay
+    const float k = parked * a.w;                                          // g_decay * decay = g_sigma * sigma_raw * decay
     const V3 d = {x6[r * 6 + 3], x6[r * 6 + 4], x6[r * 6 + 5]};
     const float4 qt = *reinterpret_cast<const float4*>(quats + (size_t)p * 4);
     const V3 q = rot_conj_fast(qt.x, qt.y, qt.z, qt.w, d);

@@ -181,6 +181,70 @@ __device__ __forceinline__ bool surely_misses(const Geom& g, V3 o, V3 d, float b
   return (wx * wx + wy * wy + wz * wz) > bound2 * (g.smax * g.smax);
 }
 
+// ---- the reference kernels' own arithmetic (frame.hit_arith = 1) ----
+// The decisions above use IEEE-only operations so that a CPU can reproduce them bit for bit.  The reference's
+// kernels evaluate the same formulas with the hardware exponential and leave the contraction of a * b + c to the
+// compiler (np_tile_kernels.cu:416-435 rotation, 483-518 tile-centre key, 659-711 hit test).  The functions below
+// state the formulas in that form -- plain float expressions in the reference's association, fmaf only where the
+// reference writes fmaf, __expf where it writes __expf, compiled by the same compiler with the same default
+// contraction -- so that on the GPU the keys, the hit decisions and the hit values come out as the reference
+// kernels' own do.  No CPU reproduces those bits; CPU checks of this mode need a margin around the threshold.
+struct GeomRef { float cx, cy, cz, qw, qx, qy, qz, lsx, lsy, lsz; };
+
+__device__ __forceinline__ GeomRef load_geom_ref(const float4* __restrict__ geom, int p) {
+  const float4 a = __ldg(geom + (size_t)p * 4 + 0);
+  const float4 b = __ldg(geom + (size_t)p * 4 + 1);
+  const float4 c = __ldg(geom + (size_t)p * 4 + 3);
+  GeomRef g;
+  g.cx = a.x; g.cy = a.y; g.cz = a.z; g.qw = a.w;
+  g.qx = b.x; g.qy = b.y; g.qz = b.z;
+  g.lsx = c.x; g.lsy = c.y; g.lsz = c.z;
+  return g;
+}
+
+// v + w t + u x t with t = 2 (u x v), u = (x, y, z); the conjugate rotation passes -u
+__device__ __forceinline__ V3 rot_ref(float w, float x, float y, float z, V3 v) {
+  const float tx = 2.f * (y * v.z - z * v.y);
+  const float ty = 2.f * (z * v.x - x * v.z);
+  const float tz = 2.f * (x * v.y - y * v.x);
+  V3 r;
+  r.x = v.x + w * tx + (y * tz - z * ty);
+  r.y = v.y + w * ty + (z * tx - x * tz);
+  r.z = v.z + w * tz + (x * ty - y * tx);
+  return r;
+}
+
+__device__ __forceinline__ float tile_key_ref(const GeomRef& g, V3 o, V3 d) {
+  const float vx = g.cx - o.x, vy = g.cy - o.y, vz = g.cz - o.z;
+  const float mx = __expf(-2.f * g.lsx), my = __expf(-2.f * g.lsy), mz = __expf(-2.f * g.lsz);
+  const V3 vl = rot_ref(g.qw, -g.qx, -g.qy, -g.qz, V3{vx, vy, vz});
+  const V3 dl = rot_ref(g.qw, -g.qx, -g.qy, -g.qz, d);
+  const float denom = fmaf(dl.x * dl.x, mx, fmaf(dl.y * dl.y, my, (dl.z * dl.z) * mz));
+  const float numer = fmaf(dl.x * vl.x, mx, fmaf(dl.y * vl.y, my, (dl.z * vl.z) * mz));
+  if (denom <= 1e-20f) return MLPSP_SENTINEL_KEY;
+  const float t = numer / denom;
+  return (t > 0.f) ? t : MLPSP_SENTINEL_KEY;
+}
+
+__device__ __forceinline__ bool hit_test_ref(const GeomRef& g, V3 o, V3 d, float thr, Hit& h) {
+  const float vx = g.cx - o.x, vy = g.cy - o.y, vz = g.cz - o.z;
+  const float mx = __expf(-2.f * g.lsx), my = __expf(-2.f * g.lsy), mz = __expf(-2.f * g.lsz);
+  const V3 vl = rot_ref(g.qw, -g.qx, -g.qy, -g.qz, V3{vx, vy, vz});
+  const V3 dl = rot_ref(g.qw, -g.qx, -g.qy, -g.qz, d);
+  const float denom = fmaf(dl.x * dl.x, mx, fmaf(dl.y * dl.y, my, (dl.z * dl.z) * mz));
+  if (denom <= 1e-20f) return false;
+  const float numer = fmaf(dl.x * vl.x, mx, fmaf(dl.y * vl.y, my, (dl.z * vl.z) * mz));
+  const float t = numer / denom;
+  if (t <= 0.f) return false;
+  const float px = o.x + t * d.x, py = o.y + t * d.y, pz = o.z + t * d.z;
+  const float dx = g.cx - px, dy = g.cy - py, dz = g.cz - pz;
+  const V3 q = rot_ref(g.qw, -g.qx, -g.qy, -g.qz, V3{dx, dy, dz});
+  const float r2 = fmaxf(q.x * q.x * mx + q.y * q.y * my + q.z * q.z * mz, 0.f);
+  const float decay = __expf(-0.5f * r2);
+  h.t = t; h.dx = dx; h.dy = dy; h.dz = dz; h.qx = q.x; h.qy = q.y; h.qz = q.z; h.decay = decay;
+  return decay > thr;
+}
+
 // ---- per-tile ray frame and the (tile, primitive) pre-test of the fused frame path ----
 // All rays of a tile leave one origin o; with an orthonormal frame (a, u, v), a along the tile's mean
 // direction, every ray direction is a + alpha u + beta v up to scale (alpha = d.u / d.a, beta = d.v / d.a),

@@ -56,6 +56,8 @@ __global__ void k_init_tiles(int T, int32_t* __restrict__ active0, int32_t* __re
 
 // --------------------------------------------------------------------------- hit pass ----
 // 8 warps per tile: warp w owns pixel half (w & 1) and candidates (w >> 1) + 4j of the window.
+// REF: the hit decision in the reference kernels' arithmetic (frame.hit_arith = 1).
+template <bool REF>
 __global__ void __launch_bounds__(256) k_hits(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(256) k_hits(
     V3 vll = {0.f, 0.f, 0.f};
     if (il < whi) {
       pl = sorted_prims[s + il];
-      if (uni && pl >= 0 && pl < n) vll = local_offset(load_geom(geom, pl), o0);
+      if (!REF && uni && pl >= 0 && pl < n) vll = local_offset(load_geom(geom, pl), o0);
     }
     const int cnt = min(32, (whi - b0 + 3) >> 2);
     for (int t = 0; t < cnt; ++t) {
@@ -114,7 +116,8 @@ __global__ void __launch_bounds__(256) k_hits(
         const Geom g = load_geom(geom, p);
         if (!surely_misses(g, o, d, bound2)) {
           Hit h;
-          hit = uni ? hit_test_t<true>(g, o, d, vl, thr, h) : hit_test_t<false>(g, o, d, vl, thr, h);
+          if (REF) hit = hit_test_ref(load_geom_ref(geom, p), o, d, thr, h);
+          else hit = uni ? hit_test_t<true>(g, o, d, vl, thr, h) : hit_test_t<false>(g, o, d, vl, thr, h);
         }
       }
       const uint32_t m = __ballot_sync(0xffffffffu, hit);
@@ -154,7 +157,7 @@ __global__ void __launch_bounds__(256) k_hits(
 __global__ void __launch_bounds__(256) k_hit_masks_all(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
-    float thr, float bound2, uint32_t* __restrict__ masks32, const int32_t* __restrict__ status) {
+    float thr, float bound2, uint32_t* __restrict__ masks32, int ref_arith, const int32_t* __restrict__ status) {
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int tile = blockIdx.x;
   const int s = tile_offsets[tile];
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(256) k_hit_masks_all(
       const Geom g = load_geom(geom, p);
       if (!surely_misses(g, o, d, bound2)) {
         Hit h;
-        hit = hit_test(g, o, d, thr, h);
+        hit = ref_arith ? hit_test_ref(load_geom_ref(geom, p), o, d, thr, h) : hit_test(g, o, d, thr, h);
       }
     }
     const uint32_t m = __ballot_sync(0xffffffffu, hit);
@@ -290,7 +293,7 @@ __global__ void __launch_bounds__(256) k_fill(
     float thr, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo, int hi,
     const uint32_t* __restrict__ masks32, const uint32_t* __restrict__ pair_base,
     const int32_t* __restrict__ prim_off, int32_t* __restrict__ prim_cursor, RecIn* __restrict__ rec_in,
-    float* __restrict__ rec_t, float4* __restrict__ rec_gate, float beta, float tau, int exact_hits,
+    float* __restrict__ rec_t, float4* __restrict__ rec_gate, float beta, float tau, int exact_hits, int ref_arith,
     const int32_t* __restrict__ status) {
   __shared__ uint32_t s_m[2][kWinMax];
   __shared__ int32_t s_pref[kWinMax + 1];   // slot of the pair's first record, relative to the tile-wave
@@ -345,7 +348,8 @@ __global__ void __launch_bounds__(256) k_fill(
     // the pair is known to hit: values only.  The feature gates divide the local offset by the scales, which
     // magnifies its rounding, so frames with features keep the decision-grade arithmetic.
     // Per-pixel ordering sorts by t: its order must be the decision-grade one too.
-    if (rec_gate || exact_hits) hit_test(load_geom(geom, p), o, d, thr, ht);
+    if (ref_arith) hit_test_ref(load_geom_ref(geom, p), o, d, thr, ht);    // the reference kernels' own values
+    else if (rec_gate || exact_hits) hit_test(load_geom(geom, p), o, d, thr, ht);
     else hit_values_fast(load_geom(geom, p), o, d, ht);
     const uint32_t slot = slot_base + (uint32_t)r;
     RecIn rec;
@@ -814,7 +818,7 @@ int launch_hit_masks(const mlpsp_scene* sc, const mlpsp_frame* fr, uint64_t* mas
   LaunchScope scope(kKHits, 1, st);
   k_hit_masks_all<<<T, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, sc->n, fr->tile_offsets,
                                      fr->sorted_prims, fr->width, fr->height, ntx, fr->threshold,
-                                     miss_bound2(fr->threshold), (uint32_t*)mask_geo, fr->status);
+                                     miss_bound2(fr->threshold), (uint32_t*)mask_geo, fr->hit_arith == 1 ? 1 : 0, fr->status);
   return cuda_check(cudaGetLastError(), "hit_masks");
 }
 
@@ -866,6 +870,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cnt, 0, 4 * (size_t)n, st));
   MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cursor, 0, 4 * (size_t)n, st));
   const bool tc_path = fr->precision == MLPSP_PRECISION_F16 || fr->precision == MLPSP_PRECISION_BF16;
+  const bool ref_arith = fr->hit_arith == 1;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -889,7 +894,13 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     const int32_t* act = s.active[cur];
     const int32_t* act_n = s.counters + kCtrActive0 + cur;
     { LaunchScope scope(kKHits, 1, st);
-    k_hits<<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+    if (ref_arith)
+      k_hits<true><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+                              W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
+                              s.masks32, s.pair_base,
+                              s.prim_cnt, s.counters, fr->max_records, fr->status);
+    else
+      k_hits<false><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
                               s.prim_cnt, s.counters, fr->max_records, fr->status); }
@@ -900,7 +911,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
                               s.prim_cursor, s.rec_in, (want_t || per_pixel) ? s.rec_t : nullptr,
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
-                              sc->gate_tau, per_pixel ? 1 : 0, fr->status); }
+                              sc->gate_tau, per_pixel ? 1 : 0, ref_arith ? 1 : 0, fr->status); }
     if (tc_path)
       rc = launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, s.rec_out, keep ? s.rec_ext : nullptr, kOutAlpha,
                           fr->status, st, fr->precision == MLPSP_PRECISION_BF16, cap_mlp);
@@ -974,7 +985,7 @@ __global__ void __launch_bounds__(64) k_export(
     const float* __restrict__ rec_tr, const float4* __restrict__ px_state, int32_t* __restrict__ px_cnt,
     const int32_t* __restrict__ px_off, int max_hits, int32_t* __restrict__ worst, int32_t* __restrict__ ids,
     float* __restrict__ x6, float* __restrict__ raw, int32_t* __restrict__ relu_masks, float* __restrict__ gates,
-    int64_t max_out, const int32_t* __restrict__ status) {
+    int64_t max_out, int ref_arith, const int32_t* __restrict__ status) {
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int tile = blockIdx.x;
   const int s = tile_offsets[tile], e = s + tile_len[tile];
@@ -1016,7 +1027,8 @@ __global__ void __launch_bounds__(64) k_export(
       ++cnt;
       if (r >= max_out) continue;
       Hit h;
-      hit_test(load_geom(geom, p), o, d, thr, h);
+      if (ref_arith) hit_test_ref(load_geom_ref(geom, p), o, d, thr, h);
+      else hit_test(load_geom(geom, p), o, d, thr, h);
       if (ids) ids[r] = p;
       if (x6) { float* q = x6 + r * 6; q[0] = d.x; q[1] = d.y; q[2] = d.z; q[3] = h.dx; q[4] = h.dy; q[5] = h.dz; }
       const float4 ro = rec_out[slot], re = rec_ext[slot];
@@ -1056,7 +1068,7 @@ int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Sc
   k_export<false><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                                     W, H, ntx, fr->threshold, sc->gate_beta, sc->gate_tau, s.used32, s.masks32,
                                     s.pair_base, s.rec_out, s.rec_ext, s.rec_tr, s.px_state, s.px_cnt, nullptr, max_hits,
-                                    worst, nullptr, nullptr, nullptr, nullptr, nullptr, 0, fr->status);
+                                    worst, nullptr, nullptr, nullptr, nullptr, nullptr, 0, fr->hit_arith == 1 ? 1 : 0, fr->status);
   int rc = launch_scan_i32(s.px_cnt, P, s.scan_blk, s.px_off, st);
   if (rc) return rc;
   k_widen_i32<<<(unsigned)((P + 1 + 255) / 256), 256, 0, st>>>(s.px_off, P + 1, offsets);
@@ -1070,7 +1082,7 @@ int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Sc
     k_export<true><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                                      W, H, ntx, fr->threshold, sc->gate_beta, sc->gate_tau, s.used32, s.masks32,
                                      s.pair_base, s.rec_out, s.rec_ext, s.rec_tr, s.px_state, s.px_cnt, s.px_off, max_hits,
-                                     worst, ids, x6, raw, relu_masks, gates, max_out, fr->status);
+                                     worst, ids, x6, raw, relu_masks, gates, max_out, fr->hit_arith == 1 ? 1 : 0, fr->status);
   }
   return cuda_check(cudaGetLastError(), "export_records");
 }

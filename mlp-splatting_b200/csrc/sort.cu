@@ -53,11 +53,16 @@ __device__ __forceinline__ unsigned long long make_composite(const float4* __res
                                                              V3 d, int key_mode) {
   float key = MLPSP_SENTINEL_KEY;
   if (p >= 0 && p < n) {
-    const Geom g = load_geom(geom, p);
     // key_mode 2 (per-pixel ordering): the pixels sort their own hits later and fall back on the list order for
     // equal hit distances (rays that start inside several primitives meet them all at t = 0), so the list keeps
-    // the order it was given, or ascending ids when it comes from the binning scatter
-    key = key_mode == 2 ? 0.f : (key_mode ? tile_key_euclid(g, o, d) : tile_key(g, o, d));
+    // the order it was given, or ascending ids when it comes from the binning scatter.  Bit 2 (value 4) asks for the
+    // tile-centre key in the reference kernels' arithmetic (frame.hit_arith = 1).
+    if (key_mode == 4) {
+      key = tile_key_ref(load_geom_ref(geom, p), o, d);
+    } else {
+      const Geom g = load_geom(geom, p);
+      key = (key_mode & 3) == 2 ? 0.f : ((key_mode & 3) ? tile_key_euclid(g, o, d) : tile_key(g, o, d));
+    }
   }
   return ((unsigned long long)__float_as_uint(key) << 32) | (unsigned long long)(uint32_t)(FROM_SCATTER ? p : i);
 }
@@ -258,21 +263,23 @@ int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, c
   const int grid = std::min((T + kTilesPerCta - 1) / kTilesPerCta, sms * 4);
   const int grid_long = std::min(T, sms * 6);
   const float4* geom = (const float4*)sc->geom;
+  // the reference kernels' arithmetic exists for the tile-centre key only (sort_key 0)
+  const int key_mode = fr->sort_key | ((fr->hit_arith == 1 && fr->sort_key == 0) ? 4 : 0);
   if (unordered_input) {
     k_sort_tiles<true><<<grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
                                              fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out,
-                                             fr->sort_key, long_list, long_count, list_len, fr->status);
+                                             key_mode, long_list, long_count, list_len, fr->status);
     k_sort_long<256, kSortCap, true><<<grid_long, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
                                                                fr->tile_prims, fr->width, fr->height, fr->tile, ntx,
-                                                               fr->sorted_prims, keys_out, fr->sort_key, long_list,
+                                                               fr->sorted_prims, keys_out, key_mode, long_list,
                                                                long_count, list_len, fr->status);
   } else {
     k_sort_tiles<false><<<grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
                                               fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out,
-                                              fr->sort_key, long_list, long_count, list_len, fr->status);
+                                              key_mode, long_list, long_count, list_len, fr->status);
     k_sort_long<256, kSortCap, false><<<grid_long, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
                                                                 fr->tile_prims, fr->width, fr->height, fr->tile, ntx,
-                                                                fr->sorted_prims, keys_out, fr->sort_key, long_list,
+                                                                fr->sorted_prims, keys_out, key_mode, long_list,
                                                                 long_count, list_len, fr->status);
   }
   return cuda_check(cudaGetLastError(), "sort_tiles");

@@ -75,11 +75,17 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
     def __init__(self, num_primitives=1024, hidden_dim=32, pe_frequencies=6, initial_positions=None,
                  use_integrated_pe=True, pe_sigma: float = 0.01, min_points: int = 10, tile_size: int = 8,
                  feature_dim_low: int = 0, feature_slots: int = 4, feature_gating_beta: float = 1.5,
-                 feature_gating_temp: float = 2.0, precision: str = "fp16"):
+                 feature_gating_temp: float = 2.0, precision: str = "fp16", wide_hidden: bool = False):
+        """The reference's arguments (scannet/cumodel.py:664-685) plus precision and wide_hidden.  wide_hidden=True
+        lifts the reference's hidden_dim <= 32 limit to the 64 this library's evaluators take (the tensor-core
+        evaluator at 32 and 64, the FP32 one at any width up to 64); nothing of the reference computes such a
+        network, so it is checked against the CPU restatement only."""
         super().__init__()
-        if int(hidden_dim) > 32:
+        if int(hidden_dim) > 32 and not wide_hidden:
             raise ValueError("NeuralPrimitiveSceneTileCUDA currently supports hidden_dim <= 32 "
                              "(kernel scratch-cap tuning in backward/full path).")
+        if int(hidden_dim) > 64:
+            raise ValueError("hidden_dim beyond 64 is not supported")
         if float(pe_sigma) <= 0.0:
             raise ValueError("pe_sigma must be > 0.")
         if int(tile_size) <= 0:

@@ -287,7 +287,7 @@ class FrameRenderer:
 
     def _frame(self, scene: PackedScene, rays_o, rays_d_unit, thr, precision, view, proj, bg, want_depth,
                want_mask_used, waves, want_feat=False, keep_records=False, sort_key=0, tile_rows=None,
-               tile_pretest=True, prim_stats=None, tail_hint=False) -> L.Frame:
+               tile_pretest=True, prim_stats=None, tail_hint=False, hit_arith=0) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
         f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
@@ -325,6 +325,7 @@ class FrameRenderer:
         f.sort_key = int(sort_key)
         f.tile_pretest = 0 if tile_pretest else 1
         f.tail_hint = 1 if tail_hint else 0
+        f.hit_arith = int(hit_arith)
         if prim_stats is not None:
             gt, sum_w, max_w, hits, sum_werr, contrib = prim_stats
             f.gt_rgb, f.stat_sum_w, f.stat_max_w = L.ptr(gt), L.ptr(sum_w), L.ptr(max_w)
@@ -380,12 +381,15 @@ class FrameRenderer:
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
                rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False,
-               keep_records=False, sort_key=0, tile_rows=None, tile_pretest=True, prim_stats=None):
+               keep_records=False, sort_key=0, tile_rows=None, tile_pretest=True, prim_stats=None, hit_arith=0):
         """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling).
 
         tile_pretest=False keeps every binned candidate in the lists the wave kernels walk (same image).
         prim_stats=(gt_rgb [P,3] f32, sum_w, max_w [n] f32, hits [n] i32, sum_werr [n] f32, contrib [n] i32): device
-        tensors that receive the per-primitive contribution statistics of this frame (accumulated, not reset)."""
+        tensors that receive the per-primitive contribution statistics of this frame (accumulated, not reset).
+        hit_arith=1 computes the tile-centre key, the hit decision and the hit values in the reference kernels' own
+        arithmetic (hardware exponential, compiler-contracted expressions) instead of the IEEE-only one: order, masks,
+        record lists and CSR offsets are then those of the reference's kernels on the same GPU."""
         lib, d = self.lib, self.device
         if precision is None:
             precision = L.PRECISION_F16 if scene.has_f16 else L.PRECISION_F32
@@ -416,7 +420,8 @@ class FrameRenderer:
                             "mlpsp_validate_tile_lists")
                 f = self._frame(scene, rays_o, rd, threshold, precision, view, proj, bg, want_depth, want_mask_used, waves,
                                 want_feat=want_feat, keep_records=keep_records, sort_key=sort_key, tile_rows=tile_rows,
-                                tile_pretest=tile_pretest, prim_stats=prim_stats, tail_hint=auto and waves is not None)
+                                tile_pretest=tile_pretest, prim_stats=prim_stats, tail_hint=auto and waves is not None,
+                                hit_arith=hit_arith)
                 self._last_frame = (f, scene)
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")
@@ -540,20 +545,21 @@ class FrameRenderer:
                 return self.tile_prims[:stats.pairs], self.tile_offsets, bits
             raise RenderError("mlpsp_bin_tiles_raycone: pair buffer kept overflowing")
 
-    def sort(self, scene: PackedScene, rays_o, rays_d_unit, pairs, want_keys=False, sort_key=0):
+    def sort(self, scene: PackedScene, rays_o, rays_d_unit, pairs, want_keys=False, sort_key=0, hit_arith=0):
         lib, d = self.lib, self.device
         with torch.cuda.device(d):
             st = _stream_ptr(d)
-            f = self._frame(scene, rays_o, rays_d_unit, 0.5, 0, None, None, None, False, False, None, sort_key=sort_key)
+            f = self._frame(scene, rays_o, rays_d_unit, 0.5, 0, None, None, None, False, False, None, sort_key=sort_key,
+                            hit_arith=hit_arith)
             keys = torch.empty(max(pairs, 1), device=d, dtype=torch.float32) if want_keys else None
             L.check(lib.mlpsp_sort_tiles(C.byref(scene.c), C.byref(f), L.ptr(keys), st), "mlpsp_sort_tiles")
             return (self.sorted_prims[:pairs], keys[:pairs]) if want_keys else self.sorted_prims[:pairs]
 
-    def hit_masks(self, scene: PackedScene, rays_o, rays_d_unit, threshold, pairs):
+    def hit_masks(self, scene: PackedScene, rays_o, rays_d_unit, threshold, pairs, hit_arith=0):
         lib, d = self.lib, self.device
         with torch.cuda.device(d):
             st = _stream_ptr(d)
-            f = self._frame(scene, rays_o, rays_d_unit, threshold, 0, None, None, None, False, False, None)
+            f = self._frame(scene, rays_o, rays_d_unit, threshold, 0, None, None, None, False, False, None, hit_arith=hit_arith)
             out = torch.zeros(max(pairs, 1), device=d, dtype=torch.int64)
             L.check(lib.mlpsp_hit_masks(C.byref(scene.c), C.byref(f), L.ptr(out), st), "mlpsp_hit_masks")
             return out[:pairs]

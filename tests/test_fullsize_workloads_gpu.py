@@ -54,6 +54,30 @@ def _pixel_error(*pairs):
     return err
 
 
+def test_reference_arithmetic_gives_the_reference_record_sets_at_full_size():
+    """hit_arith = 1 on the 100,000-primitive frame: record counts per pixel, record ids and CSR offsets equal those of
+    render_tiles_training_records, exactly."""
+    from mlp_splatting_b200 import primitive_csr
+    ref = _ref_module()
+    w = _setup("single_100k_1200x680", pack_f16=False)
+    cam = w["cams"][0]
+    r = w["FrameRenderer"](cam["W"], cam["H"], device=w["dev"])
+    x, ro, rdu = _ref_inputs(w, cam, r)
+    P = cam["W"] * cam["H"]
+    x17 = x + [torch.zeros((P, 3), device=w["dev"]), torch.zeros(P, device=w["dev"])]
+    ref_out = ref.render_tiles_training_records(x17, cam["W"], cam["H"], 8, THR, 1.5, 2.0)
+    ids_r, off_r = ref_out[2], ref_out[7]
+    del ref_out
+    out = r.render_records(w["ps"], ro, rdu, THR, precision=0, tile_lists=(x[5], x[6]), rays_normalized=True, hit_arith=1)
+    n_px = int((out[7] != off_r).sum())
+    n_id = int((out[2] != ids_r).sum()) if out[2].numel() == ids_r.numel() else -1
+    print(f"bench frame, reference arithmetic: records ref={ids_r.numel()} here={out[2].numel()}; offsets that differ {n_px}; ids that differ {n_id}")
+    assert n_px == 0 and n_id == 0
+    csr_g, _ = primitive_csr.group_order(out[2], w["ps"].n)
+    csr_r, _ = primitive_csr.group_order(ids_r, w["ps"].n)
+    assert torch.equal(csr_g, csr_r)
+
+
 def test_records_and_csr_of_the_bench_frame_match_reference_kernel():
     """render_tiles_training_records (np_tile_kernels.cu:6994) on the 100,000-primitive frame, FP32: per-pixel record
     lists, ids and CSR offsets, with the differences (threshold flips of the kind the arithmetic contract predicts)

@@ -125,6 +125,31 @@ def test_records_and_csr_match_reference_kernel(ref, name):
           f"positions with a different id: {(~ids_equal).sum()}, max CSR offset difference {diff}")
 
 
+@pytest.mark.parametrize("name", ["tiny", "ragged", "dense"])
+def test_reference_arithmetic_reproduces_reference_records_exactly(ref, name):
+    """hit_arith = 1: key, hit decision and hit values in the reference kernels' own arithmetic.  Per-pixel record
+    counts, record ids (hence compositing order) and the CSR offsets of render_tiles_training_records must then be
+    equal, not close; the hit values (x6, decay) are the same bits."""
+    from mlp_splatting_b200 import primitive_csr
+    dev = torch.device("cuda", 0)
+    scene, cam = small_case(**CASES[name])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    x = _inputs(scene, cam, f, dev)
+    P = cam["W"] * cam["H"]
+    x17 = x + [torch.zeros((P, 3), device=dev), torch.zeros(P, device=dev)]
+    ref_out = ref.render_tiles_training_records(x17, cam["W"], cam["H"], 8, 5e-3, 1.5, 2.0)
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    out = r.render_records(ps, x[0], x[1], 5e-3, precision=0, tile_lists=(x[5], x[6]), rays_normalized=True, hit_arith=1)
+    assert torch.equal(out[7], ref_out[7]), "per-pixel record offsets differ"
+    assert torch.equal(out[2], ref_out[2]), "record ids differ"
+    assert torch.equal(out[3], ref_out[3]), "x6 (ray direction, hit offset) differs in a bit"
+    assert torch.equal(out[4][:, 6], ref_out[4][:, 6]), "decay differs in a bit"
+    off_g, _ = primitive_csr.group_order(out[2], ps.n)
+    off_r, _ = primitive_csr.group_order(ref_out[2], ps.n)
+    assert torch.equal(off_g, off_r)
+    assert (out[0] - ref_out[0]).abs().max().item() <= 1e-4
+
+
 def test_feature_map_matches_reference_kernel(ref):
     """render_tiles_forward_tilecenter_with_feat (np_tile_kernels.cu:6114), slots 4, 512 channels."""
     dev = torch.device("cuda", 0)
