@@ -364,13 +364,13 @@ class Workload:
         self.frame(check=True)
         stats = self.r.last_stats
         if len(self.units) > 1:
-            tot = dict(records=0, used=0, work_total=0)
+            tot = dict(records=0, used=0, work_total=0, work_small=0)
             for (c, rows), (ro_u, rd_u) in zip(self.units, self.dev_rays):
                 self.r.render(self.ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=self.prec,
                               rays_normalized=True, tile_rows=rows, want_feat=self.want_feat)
                 for k in tot:
                     tot[k] += getattr(self.r.last_stats, k)
-            stats.records, stats.used, stats.work_total = tot["records"], tot["used"], tot["work_total"]
+            stats.records, stats.used, stats.work_total, stats.work_small = tot["records"], tot["used"], tot["work_total"], tot["work_small"]
         self.stats = stats
         return stats
 
@@ -459,7 +459,7 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
     dev_ms, _wall = timed_block(wl, flush, steps, world)
     classes = class_times(wl, flush, min(steps, 5))
     bits = int(wl.r.status.cpu()[0])
-    rec_t = torch.tensor([float(stats.records), float(stats.work_total)], dtype=torch.float64, device=dev)
+    rec_t = torch.tensor([float(stats.records), float(stats.work_total), float(stats.work_small)], dtype=torch.float64, device=dev)
     if world > 1 and wl.nviews > 1:
         dist.all_reduce(rec_t)
     hidden = int(wl.cfg.get("hidden", 32))
@@ -467,7 +467,9 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
     out = {"frames_per_sec": wl.frames_per_step * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps, "steps": steps,
            "scaling": wl.scaling, "views_per_step": wl.frames_per_step, "hidden": hidden,
            "evaluator_tflops_this_rank": stats.records * flop_per_record(hidden) / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0,
-           "records_per_step": float(rec_t[0]), "records_per_evaluator_block": float(rec_t[0]) / max(float(rec_t[1]), 1.0),
+           "records_per_step": float(rec_t[0]), "rows_per_evaluator_block": float(rec_t[0]) / max(float(rec_t[1]), 1.0),
+           "fill_of_evaluator_blocks": float(rec_t[0]) / max(128.0 * float(rec_t[1] - rec_t[2]) + 32.0 * float(rec_t[2]), 1.0),
+           "small_group_share_of_blocks": float(rec_t[2]) / max(float(rec_t[1]), 1.0),
            "kernel_classes_ms": {k: round(v["ms_per_step"], 4) for k, v in classes.items()},
            "status_bits": bits, "data": "generated on the device" if wl.cfg.get("on_device") else "generated on the host"}
     del wl
@@ -685,7 +687,9 @@ def main():
                        "note": "value and ms_per_step are the first block; the others repeat it until 1 s of device time"},
             "record_mlp_evals_per_sec": float(rec_t[0]) * (fps / wl.frames_per_step if wl.nviews > 1 else fps),
             "records_per_frame": {"evaluated": stats.records, "composited": stats.used, "candidate_pairs": stats.pairs, "pairs_after_tile_pretest": stats.pairs_kept, "evaluator_blocks": stats.work_total,
-                                  "records_per_evaluator_block": stats.records / max(stats.work_total, 1),
+                                  "small_group_blocks": stats.work_small,
+                                  "rows_per_evaluator_block": stats.records / max(stats.work_total, 1),
+                                  "fill_of_evaluator_blocks": stats.records / max(128 * (stats.work_total - stats.work_small) + 32 * stats.work_small, 1),
                                   "waves": stats.waves, "max_tile_len": stats.max_tile_len},
             "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "frames_in_flight": depth, "image": args.e2e_image, "max_abs_diff_vs_resident_frame": e2e_err,

@@ -42,8 +42,9 @@ extern "C" {
 #define MLPSP_ST_USED_HI 7
 #define MLPSP_ST_WAVE_RECORDS 8    /* largest record count of a single wave */
 #define MLPSP_ST_WORK_ITEMS 9      /* largest number of evaluator work items of a single wave */
-#define MLPSP_ST_WORK_TOTAL 10     /* evaluator work items (128-row blocks) of the whole frame */
+#define MLPSP_ST_WORK_TOTAL 10     /* evaluator work items (blocks of at most 128 rows) of the whole frame */
 #define MLPSP_ST_PAIRS_KEPT 11     /* mlpsp_render_frame: candidate pairs left after the tile pre-test */
+#define MLPSP_ST_WORK_SMALL 12     /* of MLPSP_ST_WORK_TOTAL: items of the small-group list (at most 32 rows) */
 
 /* bits 1,2,4 match the reference validator (np_tile_kernels.cu:4499-4519) */
 #define MLPSP_ST_BAD_OFFSETS 1       /* tile_offsets not 0-based / monotone / in bounds */

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libmlpsp_b200.so")
 
 STATUS_WORDS = 16
 ST_BITS, ST_MAX_TILE_LEN, ST_PAIRS, ST_WAVES = 0, 1, 2, 3
-ST_RECORDS_LO, ST_USED_LO, ST_WAVE_RECORDS, ST_WORK_ITEMS, ST_WORK_TOTAL, ST_PAIRS_KEPT = 4, 6, 8, 9, 10, 11
+ST_RECORDS_LO, ST_USED_LO, ST_WAVE_RECORDS, ST_WORK_ITEMS, ST_WORK_TOTAL, ST_PAIRS_KEPT, ST_WORK_SMALL = 4, 6, 8, 9, 10, 11, 12
 BIT_BAD_OFFSETS, BIT_TILE_CAPACITY, BIT_BAD_IDS = 1, 2, 4
 BIT_PAIR_OVERFLOW, BIT_RECORD_OVERFLOW, BIT_NUMERIC, BIT_TIMEOUT = 8, 16, 64, 128
 BIT_TILE_ORIGINS, BIT_CONE_TOO_WIDE, BIT_FEAT_INEXACT = 256, 512, 1024

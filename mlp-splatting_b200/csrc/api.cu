@@ -295,9 +295,11 @@ static Scratch grouped_layout(void* base, int64_t R, int n) {
   s.prim_cnt = (int32_t*)take(4 * ((int64_t)n + 1));
   s.prim_cursor = (int32_t*)take(4 * ((int64_t)n + 1));
   s.prim_off = (int32_t*)take(4 * ((int64_t)n + 2));
-  s.scan_blk = (int32_t*)take(4 * 2 * ((int64_t)n / kScanItems + 4));
+  s.scan_blk = (int32_t*)take(4 * 3 * ((int64_t)n / kScanItems + 4));
   s.max_work = (int64_t)n + R / kRowsPerItem + 2;
   s.work = (int4*)take(16 * s.max_work);
+  s.max_work_small = 2 * (int64_t)n + 2;
+  s.work_small = (int4*)take(16 * s.max_work_small);
   s.rec_in = (RecIn*)take(32 * std::max<int64_t>(R, 1));
   s.counters = (int32_t*)take(4 * kNumCounters);
   s.bytes = off;
@@ -328,11 +330,13 @@ extern "C" int mlpsp_mlp_grouped(const mlpsp_scene* sc, int32_t precision, const
   { LaunchScope scope(kKMisc, 2, st);
   k_grouped_counts<<<(n + 255) / 256, 256, 0, st>>>(offsets, n, s.prim_cnt);
   k_grouped_records<<<(unsigned)((num_records + 255) / 256), 256, 0, st>>>(x6, num_records, s.rec_in); }
-  int rc = launch_prim_scan(s, n, 0, status, st);
+  const bool tc = precision == MLPSP_PRECISION_F16 || precision == MLPSP_PRECISION_BF16;
+  const bool split_small = tc && num_records < 64 * (int64_t)n;     // fewer than 64 records per primitive on average
+  int rc = launch_prim_scan(s, n, 0, status, st, split_small);
   if (rc) return rc;
-  if (precision == MLPSP_PRECISION_F16 || precision == MLPSP_PRECISION_BF16)
+  if (tc)
     return launch_mlp_f16(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, nullptr, kOutSigmaRaw, status, st,
-                          precision == MLPSP_PRECISION_BF16);
+                          precision == MLPSP_PRECISION_BF16, 0, split_small ? s.work_small : nullptr);
   MLPSP_REQUIRE(precision == MLPSP_PRECISION_F32, MLPSP_E_ARG, "mlpsp_mlp_grouped: unknown precision %d", precision);
   return launch_mlp_f32(sc, s.rec_in, s.prim_off, s.work, s.counters, (float4*)out4, nullptr, kOutSigmaRaw, status, st);
 }

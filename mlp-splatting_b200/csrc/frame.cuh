@@ -7,8 +7,9 @@
 
 namespace mlpsp {
 
-// Rows handled by one evaluator work item (one tensor-core M tile).
+// Rows handled by one evaluator work item (one tensor-core M tile), and by an item of the small-group list.
 constexpr int kRowsPerItem = 128;
+constexpr int kRowsPerSmallItem = 32;
 // counters[] slots (device int32)
 enum Counter {
   kCtrRecords = 0,   // records appended by the hit pass of the current wave
@@ -17,7 +18,8 @@ enum Counter {
   kCtrActive0 = 3,   // active tile count, list 0
   kCtrActive1 = 4,   // active tile count, list 1
   kCtrPairs = 5,     // total candidate pairs (binning)
-  kCtrScratch = 6,
+  kCtrScratch = 6,   // three words (record export, long-tile list of the sort)
+  kCtrWorkSmall = 10, // small-group work items of the current wave
   kNumCounters = 16
 };
 
@@ -41,6 +43,7 @@ struct Scratch {
   int32_t* prim_cursor;  // [n]
   int32_t* prim_off;     // [n+1]
   int4* work;            // [max_work] (primitive, first record, rows, 0)
+  int4* work_small;      // [max_work_small] the same for items of at most kRowsPerSmallItem rows
   RecIn* rec_in;         // [max_records] primitive-major, reused by every wave
   float4* rec_out;       // [max_records] (R,G,B,alpha) at compositing slots (slots are unique per frame)
   float* rec_t;          // [max_records] t* at compositing slots
@@ -56,6 +59,7 @@ struct Scratch {
   int32_t* tile_len;     // [T] candidates per tile that the wave kernels traverse
   int32_t* counters;     // [kNumCounters]
   int64_t max_work;
+  int64_t max_work_small;
   int64_t bytes;
 };
 
@@ -77,7 +81,7 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.tile_fill = (int32_t*)take(4 * T);
   s.rect = (uint2*)take(8 * (int64_t)n);
   const int64_t nblk = (std::max<int64_t>(std::max<int64_t>(n, T), P + 1) + kScanItems - 1) / kScanItems + 2;
-  s.scan_blk = (int32_t*)take(4 * 2 * nblk);
+  s.scan_blk = (int32_t*)take(4 * 3 * nblk);
   s.px_state = (float4*)take(16 * P);
   s.px_depth = (float2*)take(8 * P);
   s.masks32 = (uint32_t*)take(8 * max_pairs);
@@ -87,6 +91,8 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.prim_off = (int32_t*)take(4 * ((int64_t)n + 1));
   s.max_work = (int64_t)n + max_records / kRowsPerItem + 2;
   s.work = (int4*)take(16 * s.max_work);
+  s.max_work_small = 2 * (int64_t)n + 2;
+  s.work_small = (int4*)take(16 * s.max_work_small);
   s.rec_in = (RecIn*)take(32 * max_records);
   s.rec_out = (float4*)take(16 * max_records);
   s.rec_t = (float*)take(4 * max_records);
@@ -173,9 +179,10 @@ int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
                    cudaStream_t st, int grid_cap = 0);
 // bf16: bfloat16 operands (sc->wbf16) instead of binary16 (sc->w16)
+// work_small: the wave's small-group list (launch_prim_scan with split_small), or null when every item is on `work`
 int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
-                   cudaStream_t st, bool bf16 = false, int grid_cap = 0);
+                   cudaStream_t st, bool bf16 = false, int grid_cap = 0, const int4* work_small = nullptr);
 int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cudaStream_t st);
 int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, int64_t* offsets, int32_t* ids,
                           float* x6, float* raw, int32_t* relu_masks, float* gates, int64_t max_out, int32_t max_hits,
@@ -191,6 +198,7 @@ bool feature_tc_supported(const mlpsp_scene* sc);
 int launch_feature_tc(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, const uint32_t* used32, cudaStream_t st);
 
 // multi-block exclusive scan of per-primitive record counts plus evaluator work-item emission
-int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st);
+// split_small: remainders of at most 64 records go to the small-group list (s.work_small)
+int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st, bool split_small = false);
 
 }  // namespace mlpsp

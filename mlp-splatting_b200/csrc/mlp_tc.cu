@@ -106,9 +106,10 @@ __device__ __forceinline__ void encode_coord(float v, const float (&mult)[6], ui
 __device__ __forceinline__ bool not_finite(float v) { return !(fabsf(v) < 1.0e30f); }
 
 // The first and the second part of a record's encoding, written to this thread's row of the layer-1 A tile
-// (row = generic pointer to the row's 16 bytes inside chunk 0).  q0 = (rdx, rdy, rdz, dx), q1 = (dy, dz, decay, slot)
-// are the record's two 16-byte halves; part 1 computes coordinates 0..3 (chunks 0..5), part 2 coordinates 4 and 5.
-template <bool LADDER, bool BF16>
+// (row = generic pointer to the row's 16 bytes inside chunk 0; kChunk = bytes between the K chunks of the tile).
+// q0 = (rdx, rdy, rdz, dx), q1 = (dy, dz, decay, slot) are the record's two 16-byte halves; part 1 computes
+// coordinates 0..3 (chunks 0..5), part 2 coordinates 4 and 5.
+template <bool LADDER, bool BF16, int kChunk = mlpsp::kChunk>
 __device__ __forceinline__ bool encode_part1(const float4 q0, const float (&mult)[6], char* row) {
   uint32_t a[6], b[6];
   encode_coord<LADDER, BF16>(q0.x, mult, a);
@@ -123,7 +124,7 @@ __device__ __forceinline__ bool encode_part1(const float4 q0, const float (&mult
   *reinterpret_cast<uint4*>(row + 5 * kChunk) = make_uint4(b[2], b[3], b[4], b[5]);
   return not_finite(q0.x) || not_finite(q0.y) || not_finite(q0.z) || not_finite(q0.w);
 }
-template <bool LADDER, bool BF16>
+template <bool LADDER, bool BF16, int kChunk = mlpsp::kChunk>
 __device__ __forceinline__ bool encode_part2(const float4 q1, const float (&mult)[6], char* row) {
   uint32_t a[6], b[6];
   encode_coord<LADDER, BF16>(q1.x, mult, a);
@@ -137,7 +138,7 @@ __device__ __forceinline__ bool encode_part2(const float4 q1, const float (&mult
 // hidden layer epilogue: ReLU, operand format (RN), write this thread's row of the hidden A tile.  The biases are
 // already in the accumulators.  Returns true when an activation rounded to +inf.  The FP32 sums themselves are
 // finite for finite operands (rgb_wmma.cuh:179-181 checks for a non-finite or overflowing activation per element).
-template <bool KEEP, bool BF16>
+template <bool KEEP, bool BF16, int kChunk = mlpsp::kChunk>
 __device__ __forceinline__ bool hidden_to_smem(const uint32_t (&acc)[32], char* a2, int row, uint32_t& relu_mask) {
   // running maximum of the packed activations (they are >= 0 after the ReLU, so for both formats the bit
   // patterns order like the values and one unsigned 16-bit-lane maximum serves either)
@@ -455,6 +456,233 @@ __global__ void __launch_bounds__(kMlpThreads, Net<H>::kCtas) k_mlp_tc(
   if (warp == kRows / 32) tmem_free(tmem, N::kTmemCols);
 }
 
+// ------------------------------------------------------------------ small groups ----
+// Work items of at most 32 records (the remainder of a primitive's records when it is small: most primitives of a
+// scene with millions of primitives own a few records per wave).  A 128-row item would carry one live warp and
+// three idle ones through the same chain of MMA round trips, and only five of them fit an SM.  Here one warp IS
+// the CTA: the operand tiles hold 32 rows (chunk stride 512 bytes; the MMA still has M = 128 and reads, as rows
+// 32..127, whatever follows -- those accumulator rows are never looked at), the accumulators of the three layers
+// share 32 (H = 64: 64) columns of tensor memory, lane 0 issues the MMAs between __syncwarp()s, and 12 (6) such
+// CTAs fit an SM.  Same weight pieces, same bias folding, same arithmetic as k_mlp_tc.
+constexpr int kMiniRows = kRowsPerSmallItem;
+constexpr int kMiniChunk = kMiniRows * 16;
+
+template <int H>
+struct MiniNet {
+  using N = Net<H>;
+  static constexpr int kOffConst = N::kWeightBytes;
+  static constexpr int kOffA1 = kOffConst + 256;
+  static constexpr int kOffA2 = kOffA1 + kA1Chunks * kMiniChunk;
+  static constexpr int kOffPad = kOffA2 + (H / 8) * kMiniChunk;     // rows 32..127 of the last hidden chunk land here
+  static constexpr int kOffBar = kOffPad + (kRows - kMiniRows) * 16;
+  static constexpr int kSmemBytes = kOffBar + 64;                   // 17,984 (H = 32) / 33,344 (H = 64)
+  static constexpr int kTmemCols = H;
+  static constexpr int kCtas = H == 32 ? 12 : 6;
+};
+
+template <bool BF16, int H>
+__global__ void __launch_bounds__(kMiniRows, MiniNet<H>::kCtas) k_mlp_tc_mini(
+    const char* __restrict__ w16, const float* __restrict__ freq, const float* __restrict__ att,
+    const float4* __restrict__ rec_in, const int4* __restrict__ work, const int32_t* __restrict__ counters,
+    float4* __restrict__ rec_out, int out_mode, int32_t* __restrict__ status) {
+  using N = Net<H>;
+  using M = MiniNet<H>;
+  extern __shared__ __align__(128) char smem[];
+  char* s_a1 = smem + M::kOffA1;
+  char* s_a2 = smem + M::kOffA2;
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + M::kOffBar);   // [0..2] weight pieces, [3] MMAs of a layer done
+  uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 4);
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  const int lane = threadIdx.x;
+  const int G = counters[kCtrWorkSmall];
+  int item = blockIdx.x;
+  if (item >= G) return;
+  const int stride = (int)gridDim.x;
+  const uint32_t wb = smem_u32(smem), a1 = wb + M::kOffA1, a2 = wb + M::kOffA2;
+  const uint32_t bar_w0 = smem_u32(&s_bar[0]), bar_m = smem_u32(&s_bar[3]);
+  if (lane == 0) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) mbar_init(bar_w0 + 8 * b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  tmem_alloc(smem_u32(&s_misc[0]), M::kTmemCols);
+  if (lane < 16) {
+    const uint32_t one2 = BF16 ? 0x3f803f80u : 0x3c003c00u;
+    const uint32_t v = lane < 8 ? one2 : 0u;
+    *reinterpret_cast<uint4*>(smem + M::kOffConst + lane * 16) = make_uint4(v, v, v, v);
+  }
+  // the hidden tile and the rows behind it start finite (they meet zero weights in the last layer-1 K step)
+  for (int i = lane; i < (M::kOffBar - M::kOffA2) / 16; i += kMiniRows) *reinterpret_cast<uint4*>(s_a2 + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+  fence_async_smem();
+  tc_fence_before();
+  __syncwarp();
+  tc_fence_after();
+  const uint32_t tmem = s_misc[0];
+  float mult[6];
+  bool ladder = true;
+#pragma unroll
+  for (int f = 0; f < 6; ++f) mult[f] = __ldg(freq + f) * __ldg(att + f);
+#pragma unroll
+  for (int f = 1; f < 6; ++f) ladder = ladder && mult[f] == 2.0f * mult[f - 1];
+  const uint64_t ones_desc = smem_desc(wb + M::kOffConst, 128, 0);
+  const uint32_t idesc_h = instr_desc(kRows, H, BF16), idesc_o = instr_desc(kRows, kN3, BF16);
+  const uint64_t a1_desc = smem_desc(a1, kMiniChunk, 128), a2_desc = smem_desc(a2, kMiniChunk, 128);
+  const uint64_t w1_desc = smem_desc(wb + N::kOffW1, N::kWChunk, 128), w2_desc = smem_desc(wb + N::kOffW2, N::kWChunk, 128);
+  const uint64_t w3_desc = smem_desc(wb + N::kOffW3, N::kW3Chunk, 128);
+  auto step = [](uint64_t desc, int bytes) { return desc + (uint64_t)(bytes >> 4); };
+  auto request = [&](int piece, int prim) {
+    const int off = piece == 0 ? N::kOffW1 : (piece == 1 ? N::kOffW2 : N::kOffW3);
+    const int bytes = piece == 0 ? N::kBytesW1 : (piece == 1 ? N::kBytesW2 : N::kBytesW3);
+    mbar_expect_tx(bar_w0 + 8 * piece, bytes);
+    bulk_g2s(wb + off, w16 + (size_t)prim * N::kWeightBytes + off, bytes, bar_w0 + 8 * piece);
+  };
+  auto load_rec = [&](const int4& w, float4& r0, float4& r1) {
+    r0 = make_float4(0.f, 0.f, 0.f, 0.f);
+    r1 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (lane < w.z) { r0 = __ldg(rec_in + 2 * (size_t)(w.y + lane)); r1 = __ldg(rec_in + 2 * (size_t)(w.y + lane) + 1); }
+  };
+  // the warp's writes to an operand tile are visible to the tensor core, its reads of tensor memory have retired
+  auto tile_done = [&]() {
+    fence_async_smem();
+    tc_fence_before();
+    __syncwarp();
+  };
+  int4 wk = __ldg(work + item);
+  int4 wk_n = (item + stride < G) ? __ldg(work + item + stride) : make_int4(0, 0, 0, 0);
+  uint32_t pend = 0u;
+  if (lane == 0) { request(0, wk.x); request(1, wk.x); request(2, wk.x); pend = 7u; }
+  char* my_row = s_a1 + lane * 16;
+  bool bad = false, ok = true;
+  float4 q0, q1;
+  load_rec(wk, q0, q1);
+  if (ladder) { bad |= encode_part1<true, BF16, kMiniChunk>(q0, mult, my_row); bad |= encode_part2<true, BF16, kMiniChunk>(q1, mult, my_row); }
+  else { bad |= encode_part1<false, BF16, kMiniChunk>(q0, mult, my_row); bad |= encode_part2<false, BF16, kMiniChunk>(q1, mult, my_row); }
+  float decay_c = q1.z;
+  uint32_t slot_c = __float_as_uint(q1.w);
+  load_rec(wk_n, q0, q1);
+  uint32_t li = 0u, ph = 0u, relu_unused = 0u;   // ph: phases of the MMA barrier completed so far
+  const uint32_t trow = tmem;   // warp 0 of the CTA: lanes 0..31
+
+  for (;;) {
+    const bool valid = lane < wk.z;
+    const int next = item + stride;
+    const bool has_next = next < G;
+    const uint32_t par = li & 1u;
+    const int next2 = next + stride;
+    int4 wk_n2 = make_int4(0, 0, 0, 0);
+    if (next2 < G) wk_n2 = __ldg(work + next2);
+    // ---- layer 1 ----
+    tile_done();
+    if (lane == 0) {
+      bool landed = mbar_wait(bar_w0, par);
+      pend &= ~1u;
+      if (li == 0u) landed = landed && mbar_wait(bar_w0 + 8, 0u) && mbar_wait(bar_w0 + 16, 0u);   // see k_mlp_tc
+      if (landed) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          mma_f16(tmem, step(a1_desc, ks * 2 * kMiniChunk), step(w1_desc, ks * 2 * N::kWChunk), idesc_h, ks > 0);
+        mma_f16(tmem, step(a1_desc, 8 * kMiniChunk), step(w1_desc, 8 * N::kWChunk), idesc_h, 1u);
+        mma_f16(tmem, ones_desc, step(w1_desc, 10 * N::kWChunk), idesc_h, 1u);
+      } else {
+        ok = false;
+      }
+      mma_commit(bar_m);
+    }
+    if (next2 < G && lane < wk_n2.z) asm volatile("prefetch.global.L2 [%0];" ::"l"(rec_in + 2 * (size_t)(wk_n2.y + lane)));
+    ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph++ & 1u) && ok);   // one completion per layer
+    tc_fence_after();
+    if (!ok) break;
+    if (lane == 0 && has_next) { request(0, wk_n.x); pend |= 1u; }
+#pragma unroll
+    for (int part = 0; part < H / 32; ++part) {
+      uint32_t acc[32];
+      tmem_ld32(trow + part * 32, acc);
+      bad |= hidden_to_smem<false, BF16, kMiniChunk>(acc, s_a2 + part * 4 * kMiniChunk, lane, relu_unused) && valid;
+    }
+    // ---- layer 2 (its accumulator takes the columns of layer 1) ----
+    tile_done();
+    if (lane == 0) {
+      const bool landed = mbar_wait(bar_w0 + 8, par);
+      pend &= ~2u;
+      if (landed) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < H / 16; ++ks)
+          mma_f16(tmem, step(a2_desc, ks * 2 * kMiniChunk), step(w2_desc, ks * 2 * N::kWChunk), idesc_h, ks > 0);
+        mma_f16(tmem, ones_desc, step(w2_desc, (H / 8) * N::kWChunk), idesc_h, 1u);
+      } else {
+        ok = false;
+      }
+      mma_commit(bar_m);
+    }
+    // first part of the next item's encoding while layer 2 runs (the layer-1 tile is free)
+    if (has_next)
+      bad |= ladder ? encode_part1<true, BF16, kMiniChunk>(q0, mult, my_row) : encode_part1<false, BF16, kMiniChunk>(q0, mult, my_row);
+    ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph++ & 1u) && ok);
+    tc_fence_after();
+    if (!ok) break;
+    if (lane == 0 && has_next) { request(1, wk_n.x); pend |= 2u; }
+#pragma unroll
+    for (int part = 0; part < H / 32; ++part) {
+      uint32_t acc[32];
+      tmem_ld32(trow + part * 32, acc);
+      bad |= hidden_to_smem<false, BF16, kMiniChunk>(acc, s_a2 + part * 4 * kMiniChunk, lane, relu_unused) && valid;
+    }
+    // ---- layer 3 ----
+    tile_done();
+    if (lane == 0) {
+      const bool landed = mbar_wait(bar_w0 + 16, par);
+      pend &= ~4u;
+      if (landed) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < H / 16; ++ks)
+          mma_f16(tmem, step(a2_desc, ks * 2 * kMiniChunk), step(w3_desc, ks * 2 * N::kW3Chunk), idesc_o, ks > 0);
+        mma_f16(tmem, ones_desc, step(w3_desc, (H / 8) * N::kW3Chunk), idesc_o, 1u);
+      } else {
+        ok = false;
+      }
+      mma_commit(bar_m);
+    }
+    if (has_next)
+      bad |= ladder ? encode_part2<true, BF16, kMiniChunk>(q1, mult, my_row) : encode_part2<false, BF16, kMiniChunk>(q1, mult, my_row);
+    ok = __all_sync(0xffffffffu, mbar_wait(bar_m, ph++ & 1u) && ok);
+    tc_fence_after();
+    if (!ok) break;
+    if (lane == 0 && has_next) { request(2, wk_n.x); pend |= 4u; }
+    {
+      uint32_t o[4];
+      tmem_ld4(trow, o);
+      if (valid) {
+        const float o0 = __uint_as_float(o[0]), o1 = __uint_as_float(o[1]), o2 = __uint_as_float(o[2]), o3 = __uint_as_float(o[3]);
+        const float sigma_raw = softplus_fast(o3);
+        float4 out;
+        out.x = sigmoid_fast(o0); out.y = sigmoid_fast(o1); out.z = sigmoid_fast(o2);
+        out.w = (out_mode == kOutAlpha) ? (1.f - __expf(-(sigma_raw * decay_c))) : sigma_raw;
+        rec_out[slot_c] = out;
+      }
+    }
+    if (!has_next) break;
+    decay_c = q1.z;
+    slot_c = __float_as_uint(q1.w);
+    item = next;
+    wk = wk_n;
+    wk_n = wk_n2;
+    load_rec(wk_n, q0, q1);
+    ++li;
+  }
+  if (!ok && lane == 0) {
+    atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_TIMEOUT);
+    for (int b = 0; b < 3; ++b)
+      if (pend & (1u << b)) mbar_wait(bar_w0 + 8 * b, li & 1u);
+  }
+  if (bad) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_NUMERIC);
+  tc_fence_before();
+  __syncwarp();
+  tmem_free(tmem, M::kTmemCols);
+}
+
 // ------------------------------------------------------------------------------ packing ----
 template <bool BF16>
 __device__ __forceinline__ uint16_t to_lp(float x, bool& bad) {
@@ -542,16 +770,29 @@ static int launch_one(const char* image, const mlpsp_scene* sc, const RecIn* rec
   return MLPSP_OK;
 }
 
+template <bool BF16, int H>
+static int launch_mini(const char* image, const mlpsp_scene* sc, const RecIn* rec_in, const int4* work_small,
+                       const int32_t* counters, float4* rec_out, int out_mode, int32_t* status, cudaStream_t st, int grid) {
+  using M = MiniNet<H>;
+  static DeviceOnce attr_once;
+  if (attr_once.first())
+    MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc_mini<BF16, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, M::kSmemBytes));
+  k_mlp_tc_mini<BF16, H><<<grid, kMiniRows, M::kSmemBytes, st>>>(image, sc->freq, sc->att, reinterpret_cast<const float4*>(rec_in),
+                                                                work_small, counters, rec_out, out_mode, status);
+  return MLPSP_OK;
+}
+
 template <int H>
-static int launch_tc(const mlpsp_scene* sc, const char* image, const RecIn* rec_in, const int4* work, const int32_t* counters,
-                     float4* rec_out, float4* rec_ext, int out_mode, int32_t* status, cudaStream_t st, bool bf16, int grid_cap) {
+static int launch_tc(const mlpsp_scene* sc, const char* image, const RecIn* rec_in, const int4* work, const int4* work_small,
+                     const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status, cudaStream_t st,
+                     bool bf16, int grid_cap) {
   using N = Net<H>;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int grid = sms * N::kCtas;
   if (grid_cap > 0) grid = std::min(grid, grid_cap);
-  LaunchScope scope(kKMlp, 1, st);
+  LaunchScope scope(kKMlp, (work_small && !rec_ext) ? 2 : 1, st);
   int rc;
   if (rec_ext) {
     if (H != 32) {
@@ -565,12 +806,20 @@ static int launch_tc(const mlpsp_scene* sc, const char* image, const RecIn* rec_
               : launch_one<false, false, H>(image, sc, rec_in, work, counters, rec_out, rec_ext, out_mode, status, st, grid);
   }
   if (rc) return rc;
+  if (work_small && !rec_ext) {
+    // the wave's small groups (at most 32 records) on their own kernel: one warp per item, twelve (six) items per SM
+    int grid_s = sms * MiniNet<H>::kCtas;
+    if (grid_cap > 0) grid_s = std::min(grid_s, grid_cap);
+    rc = bf16 ? launch_mini<true, H>(image, sc, rec_in, work_small, counters, rec_out, out_mode, status, st, grid_s)
+              : launch_mini<false, H>(image, sc, rec_in, work_small, counters, rec_out, out_mode, status, st, grid_s);
+    if (rc) return rc;
+  }
   return cuda_check(cudaGetLastError(), "mlp_f16");
 }
 
 int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
-                   cudaStream_t st, bool bf16, int grid_cap) {
+                   cudaStream_t st, bool bf16, int grid_cap, const int4* work_small) {
   MLPSP_REQUIRE((sc->hidden == 32 || sc->hidden == 64) && sc->num_freq == 6, MLPSP_E_LIMIT,
                 "the tensor-core evaluator is built for 72->H->H->4 networks with H = 32 or 64 (6 frequencies)");
   const char* image = (const char*)(bf16 ? sc->wbf16 : sc->w16);
@@ -579,8 +828,8 @@ int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
   MLPSP_REQUIRE((reinterpret_cast<uintptr_t>(image) & 15) == 0, MLPSP_E_ARG, "the packed weight image must be 16-byte aligned");
   (void)prim_off;
   if (sc->hidden == 64)
-    return launch_tc<64>(sc, image, rec_in, work, counters, rec_out, rec_ext, out_mode, status, st, bf16, grid_cap);
-  return launch_tc<32>(sc, image, rec_in, work, counters, rec_out, rec_ext, out_mode, status, st, bf16, grid_cap);
+    return launch_tc<64>(sc, image, rec_in, work, work_small, counters, rec_out, rec_ext, out_mode, status, st, bf16, grid_cap);
+  return launch_tc<32>(sc, image, rec_in, work, work_small, counters, rec_out, rec_ext, out_mode, status, st, bf16, grid_cap);
 }
 
 }  // namespace mlpsp

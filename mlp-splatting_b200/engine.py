@@ -213,8 +213,9 @@ class FrameStats:
     waves: int
     wave_records: int
     work_items: int
-    work_total: int = 0   # 128-row evaluator blocks of the whole frame
+    work_total: int = 0   # evaluator work items (blocks of at most 128 rows) of the whole frame
     pairs_kept: int = 0   # candidate pairs left after the tile pre-test (0 when it did not run)
+    work_small: int = 0   # of work_total: small-group items (at most 32 rows)
 
 
 class RenderError(RuntimeError):
@@ -347,7 +348,8 @@ class FrameRenderer:
         rec = int(u[L.ST_RECORDS_LO]) | (int(u[L.ST_RECORDS_LO + 1]) << 32)
         used = int(u[L.ST_USED_LO]) | (int(u[L.ST_USED_LO + 1]) << 32)
         stats = FrameStats(int(s[L.ST_PAIRS]), int(s[L.ST_MAX_TILE_LEN]), rec, used, int(s[L.ST_WAVES]),
-                           int(s[L.ST_WAVE_RECORDS]), int(s[L.ST_WORK_ITEMS]), int(s[L.ST_WORK_TOTAL]), int(s[L.ST_PAIRS_KEPT]))
+                           int(s[L.ST_WAVE_RECORDS]), int(s[L.ST_WORK_ITEMS]), int(s[L.ST_WORK_TOTAL]), int(s[L.ST_PAIRS_KEPT]),
+                           int(s[L.ST_WORK_SMALL]))
         return int(s[L.ST_BITS]), stats
 
     def _grow(self, bits, stats):
