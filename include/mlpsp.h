@@ -316,16 +316,23 @@ int mlpsp_records_reverse(const int32_t* ids, const int64_t* offsets, const floa
 /* Floats per primitive of the packed gradient row: W1[32,72] b1[32] W2[32,32] b2[32] W3[4,32] b3[4] = 3,524. */
 int64_t mlpsp_grouped_gradient_floats(void);
 
-/* Per-primitive MLP weight gradients from primitive-major records: grouped_weight_gradients in its FP32 operand
- * mode (scannet/primitive_gemm.py:101-279; the PyTorch statement is scannet/primitive_csr.py:33-58).
+/* Per-primitive MLP weight gradients from primitive-major records: one launch of grouped_weight_gradients
+ * (scannet/primitive_gemm.py:101-232; the PyTorch statement is scannet/primitive_csr.py:33-58).
  * offsets[n+1] / x6[R,6] / d4[R,4] / relu_masks[R,2] (or NULL: signs are recomputed) are a PrimitiveCSR; seg_prim,
  * seg_start [G] and seg_offsets [n+1] are a prepared group layout (mlpsp_prepare_groups) with segment_size records
- * per segment.  partial [G, 3524] is scratch; result [n, 3524]; *nonfinite becomes 1 when a sum is not finite.
- * loss_scale multiplies the adjoints before and divides the sums after (1 for FP32). */
+ * per segment.  partial [G, 3524] is scratch; result [n, 3524].
+ * precision: MLPSP_PRECISION_F32 = IEEE FP32 on the CUDA cores (the reference's float32 mode, no TF32);
+ * MLPSP_PRECISION_F16 / _BF16 = operands rounded to binary16 / bfloat16, products on the tensor cores (tcgen05),
+ * FP32 accumulation over the whole segment (the reference's tl.dot modes); d4 must then be 16-byte aligned.
+ * loss_scale multiplies the adjoints before the cast and divides the sums after (the reference uses 4096 for
+ * binary16, 1 otherwise).  *nonfinite: bit 0 = a sum is not finite -- the caller retries a mixed-precision call
+ * with MLPSP_PRECISION_F32 and loss_scale 1 as primitive_gemm.py:64-98 does (the host mirror does);
+ * bit 1 = a device-side wait gave up, results invalid. */
 int mlpsp_grouped_weight_gradients(const mlpsp_scene* scene, const int64_t* offsets, const float* x6, const float* d4,
                                    const int32_t* relu_masks, const int64_t* seg_prim, const int64_t* seg_start,
                                    const int64_t* seg_offsets, int64_t num_segments, int32_t segment_size,
-                                   float loss_scale, float* partial, float* result, int32_t* nonfinite, void* stream);
+                                   int32_t precision, float loss_scale, float* partial, float* result,
+                                   int32_t* nonfinite, void* stream);
 
 /* ---- the step after the feature map: feature decoder and text query ---- */
 

@@ -74,7 +74,7 @@ _SIGS = {
     "mlpsp_records_reverse": (C.c_int, [_fp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64, C.c_int64, C.c_int32, _fp, _fp, _fp, _fp, _fp]),
     "mlpsp_grouped_gradient_floats": (C.c_int64, []),
     "mlpsp_grouped_weight_gradients": (C.c_int, [C.POINTER(Scene), _fp, _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64, C.c_int32,
-                                                 C.c_float, _fp, _fp, _fp, _fp]),
+                                                 C.c_int32, C.c_float, _fp, _fp, _fp, _fp]),
     "mlpsp_decoder_packed_bytes": (C.c_int64, [C.POINTER(Decoder), C.c_int32]),
     "mlpsp_pack_decoder": (C.c_int, [C.POINTER(Decoder), C.c_int32, _fp, _fp, _fp]),
     "mlpsp_decode_features": (C.c_int, [C.POINTER(Decoder), C.c_int32, _fp, _fp, C.c_int32, C.c_int32, _fp, _fp, _fp, _fp]),

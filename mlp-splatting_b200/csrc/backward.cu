@@ -317,8 +317,8 @@ extern "C" int64_t mlpsp_grouped_gradient_floats(void) { return kGradLen; }
 extern "C" int mlpsp_grouped_weight_gradients(const mlpsp_scene* sc, const int64_t* offsets, const float* x6,
                                               const float* d4, const int32_t* relu_masks, const int64_t* seg_prim,
                                               const int64_t* seg_start, const int64_t* seg_offsets, int64_t num_segments,
-                                              int32_t segment_size, float loss_scale, float* partial, float* result, int32_t* nonfinite,
-                                              void* stream) {
+                                              int32_t segment_size, int32_t precision, float loss_scale, float* partial,
+                                              float* result, int32_t* nonfinite, void* stream) {
   MLPSP_REQUIRE(sc && offsets && result && nonfinite, MLPSP_E_ARG, "mlpsp_grouped_weight_gradients: null pointer");
   MLPSP_REQUIRE(sc->hidden == kGH && sc->num_freq == 6, MLPSP_E_LIMIT,
                 "grouped backward requires the 72->32->32->4 architecture");
@@ -326,6 +326,8 @@ extern "C" int mlpsp_grouped_weight_gradients(const mlpsp_scene* sc, const int64
                 "mlpsp_grouped_weight_gradients: FP32 weights missing");
   MLPSP_REQUIRE(loss_scale > 0.f && num_segments >= 0 && num_segments < (1ll << 31) && segment_size > 0, MLPSP_E_ARG,
                 "mlpsp_grouped_weight_gradients: bad loss scale, segment size or segment count");
+  MLPSP_REQUIRE(precision == MLPSP_PRECISION_F32 || precision == MLPSP_PRECISION_F16 || precision == MLPSP_PRECISION_BF16,
+                MLPSP_E_ARG, "mlpsp_grouped_weight_gradients: unsupported operand precision %d", precision);
   // every pointer a launch below reads is checked before the first CUDA call
   MLPSP_REQUIRE(sc->n == 0 || num_segments == 0 || (x6 && d4 && seg_prim && seg_start && seg_offsets && partial),
                 MLPSP_E_ARG, "mlpsp_grouped_weight_gradients: null pointer");
@@ -336,10 +338,21 @@ extern "C" int mlpsp_grouped_weight_gradients(const mlpsp_scene* sc, const int64
     // no records at all: every primitive's gradient row is zero
     return cuda_check(cudaMemsetAsync(result, 0, sizeof(float) * (size_t)sc->n * kGradLen, st), "grouped_weight_gradients");
   }
+  LaunchScope scope(kKMisc, 2, st);
+  if (precision != MLPSP_PRECISION_F32) {
+    // binary16 / bfloat16 operands on the tensor cores, FP32 accumulation over the segment
+    MLPSP_REQUIRE((reinterpret_cast<uintptr_t>(d4) & 15) == 0, MLPSP_E_ARG,
+                  "mlpsp_grouped_weight_gradients: d4 must be 16-byte aligned");
+    const int rc = launch_grouped_vjp_tc(precision == MLPSP_PRECISION_BF16, x6, d4, relu_masks, offsets, seg_prim, seg_start,
+                                         num_segments, segment_size, sc, loss_scale, partial, nonfinite, st);
+    if (rc) return rc;
+    const dim3 grid_r(sc->n, (kGradLen + 255) / 256);
+    k_reduce_partials<<<grid_r, 256, 0, st>>>(partial, seg_offsets, sc->n, result, nonfinite);
+    return cuda_check(cudaGetLastError(), "grouped_weight_gradients");
+  }
   static DeviceOnce attr_once;
   if (attr_once.first())
     MLPSP_CUDA_OK(cudaFuncSetAttribute(k_grouped_vjp, cudaFuncAttributeMaxDynamicSharedMemorySize, kGradSmem));
-  LaunchScope scope(kKMisc, 2, st);
   k_grouped_vjp<<<(unsigned)num_segments, kGSeg, kGradSmem, st>>>(x6, d4, relu_masks, offsets, seg_prim, seg_start, segment_size,
                                                                   sc->freq, sc->att, sc->W1, sc->b1, sc->W2, sc->b2, sc->W3,
                                                                   loss_scale, partial);

@@ -180,6 +180,10 @@ int launch_mlp_f32(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* pr
                    cudaStream_t st, int grid_cap = 0);
 // bf16: bfloat16 operands (sc->wbf16) instead of binary16 (sc->w16)
 // work_small: the wave's small-group list (launch_prim_scan with split_small), or null when every item is on `work`
+// per-primitive weight gradients with binary16 / bfloat16 operands on tcgen05 (vjp_tc.cu); flag bit 1 = a wait gave up
+int launch_grouped_vjp_tc(bool bf16, const float* x6, const float* d4, const int32_t* masks, const int64_t* offsets,
+                          const int64_t* seg_prim, const int64_t* seg_start, int64_t num_segments, int segment_size,
+                          const mlpsp_scene* sc, float scale, float* partial, int32_t* flag, cudaStream_t st);
 int launch_mlp_f16(const mlpsp_scene* sc, const RecIn* rec_in, const int32_t* prim_off, const int4* work,
                    const int32_t* counters, float4* rec_out, float4* rec_ext, int out_mode, int32_t* status,
                    cudaStream_t st, bool bf16 = false, int grid_cap = 0, const int4* work_small = nullptr);

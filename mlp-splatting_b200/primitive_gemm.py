@@ -4,11 +4,14 @@
 error texts (primitive_gemm.py:21-52, 186-212).  The reference's only grouped kernel is the
 backward VJP (Triton); the inference path needs its forward twin, `grouped_forward`: records
 grouped by primitive -> (R, G, B, sigma_raw) per record, evaluated per primitive group on the
-tcgen05 tensor cores (fp16 operands, FP32 accumulate) or in scalar FP32.
+tcgen05 tensor cores (fp16 operands, FP32 accumulate) or in scalar FP32.  `grouped_weight_gradients`
+is the VJP itself: IEEE FP32, or binary16 / bfloat16 operands on the tensor cores with the reference's
+loss scale and FP32 retry.
 """
 from __future__ import annotations
 
 import ctypes as C
+import warnings
 from dataclasses import dataclass
 
 import torch
@@ -132,15 +135,44 @@ def get_grouped_vjp_safety_stats(*, reset=False):
     return snapshot
 
 
+def _checked_grouped_vjp(launch, dtype, loss_scale):
+    """Never hand a non-finite MLP gradient to the caller's optimizer step (primitive_gemm.py:64-98): a finite
+    result is returned unchanged; a non-finite mixed-precision result is recomputed in unscaled IEEE FP32 from the
+    same masters and masks; a non-finite FP32 result raises and returns nothing."""
+    _SAFETY_STATS["calls"] += 1
+    mixed = dtype != torch.float32
+    _SAFETY_STATS["mixed_calls"] += int(mixed)
+    result, nonfinite = launch(dtype, loss_scale)
+    if not nonfinite:
+        return result
+    if mixed:
+        _SAFETY_STATS["fp32_fallbacks"] += 1
+        warnings.warn(
+            f"[CSR safety] Nonfinite {dtype} MLP VJP; retrying with IEEE FP32 "
+            f"before Adam (FP32 fallbacks={_SAFETY_STATS['fp32_fallbacks']}).",
+            RuntimeWarning, stacklevel=3)
+        result, nonfinite = launch(torch.float32, 1.0)
+        if not nonfinite:
+            return result
+    _SAFETY_STATS["fp32_nonfinite_failures"] += 1
+    raise FloatingPointError(
+        "[CSR safety] IEEE FP32 MLP VJP is nonfinite; no gradients were returned "
+        "and Adam must not step. Inspect the saved model, records and loss. "
+        f"Safety counters: {get_grouped_vjp_safety_stats()}")
+
+
 @torch.no_grad()
 def grouped_weight_gradients(csr, freq, attenuation, weights, *, dtype=torch.float16, segment_size=512, block_size=32,
                              loss_scale=None, groups=None):
     """[dW1, db1, dW2, db2, dW3, db3] of the 72->32->32->4 per-primitive MLP from primitive-major records.
 
-    Same arguments, checks and error texts as the reference function.  This build evaluates every operand dtype
-    in IEEE FP32 (the reference's float32 mode): float16 / bfloat16 requests are accepted and are
-    at least as accurate as the reference's mixed modes are required to be; loss_scale is applied and removed
-    as there.  A non-finite sum raises FloatingPointError and no gradients are returned."""
+    Same arguments, checks, error texts and safety policy as the reference function (primitive_gemm.py:236-279).
+    float32 is IEEE FP32 on the CUDA cores; float16 / bfloat16 round the operands (encoding, activations, adjoints,
+    weights) to that format and run every product on the tensor cores with FP32 accumulation over the segment;
+    float16 adjoints are scaled by 4096 before the cast and unscaled in FP32 afterwards unless loss_scale says
+    otherwise.  A non-finite mixed result is retried in unscaled FP32; a non-finite FP32 result raises
+    FloatingPointError and no gradients are returned.  block_size is the reference's Triton row block; it is
+    checked and otherwise unused (the kernels walk a segment 128 records at a time)."""
     import math
     w1, b1, w2, b2, w3, b3 = weights
     n = len(w1)
@@ -169,30 +201,33 @@ def grouped_weight_gradients(csr, freq, attenuation, weights, *, dtype=torch.flo
     scale = float(4096 if dtype == torch.float16 else 1) if loss_scale is None else float(loss_scale)
     if not math.isfinite(scale) or scale <= 0:
         raise ValueError("loss_scale must be finite and strictly positive")
-    _SAFETY_STATS["calls"] += 1
-    _SAFETY_STATS["mixed_calls"] += int(dtype != torch.float32)
     lib = L.load()
     dev = w1.device
     glen = int(lib.mlpsp_grouped_gradient_floats())
     G = int(groups.primitives.numel())
-    partial = torch.empty((max(G, 1), glen), device=dev, dtype=torch.float32)
-    result = torch.empty((n, glen), device=dev, dtype=torch.float32)
-    nonfinite = torch.zeros((), device=dev, dtype=torch.int32)
     sc = L.Scene()
     sc.n, sc.hidden, sc.num_freq = n, 32, 6
     sc.W1, sc.b1, sc.W2, sc.b2, sc.W3, sc.b3 = (L.ptr(t) for t in weights)
     sc.freq, sc.att = L.ptr(freq), L.ptr(attenuation)
-    with torch.cuda.device(dev):
-        st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-        L.check(lib.mlpsp_grouped_weight_gradients(
-            C.byref(sc), L.ptr(csr.offsets), L.ptr(csr.x6), L.ptr(csr.grad4), L.ptr(csr.relu_masks), L.ptr(groups.primitives),
-            L.ptr(groups.starts), L.ptr(groups.offsets), G, int(segment_size), scale, L.ptr(partial), L.ptr(result),
-            L.ptr(nonfinite), st), "mlpsp_grouped_weight_gradients")
-    if bool(nonfinite.item()):
-        _SAFETY_STATS["fp32_nonfinite_failures"] += 1
-        raise FloatingPointError(
-            "[CSR safety] IEEE FP32 MLP VJP is nonfinite; no gradients were returned "
-            "and Adam must not step. Inspect the saved model, records and loss. "
-            f"Safety counters: {get_grouped_vjp_safety_stats()}")
+    precisions = {torch.float32: L.PRECISION_F32, torch.float16: L.PRECISION_F16, torch.bfloat16: L.PRECISION_BF16}
+
+    def launch(operand_dtype, operand_scale):
+        """One unguarded launch, shared by the normal path and the FP32 retry (primitive_gemm.py:215-232)."""
+        partial = torch.empty((max(G, 1), glen), device=dev, dtype=torch.float32)
+        result = torch.empty((n, glen), device=dev, dtype=torch.float32)
+        nonfinite = torch.zeros((), device=dev, dtype=torch.int32)
+        with torch.cuda.device(dev):
+            st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+            L.check(lib.mlpsp_grouped_weight_gradients(
+                C.byref(sc), L.ptr(csr.offsets), L.ptr(csr.x6), L.ptr(csr.grad4), L.ptr(csr.relu_masks),
+                L.ptr(groups.primitives), L.ptr(groups.starts), L.ptr(groups.offsets), G, int(segment_size),
+                precisions[operand_dtype], float(operand_scale), L.ptr(partial), L.ptr(result), L.ptr(nonfinite), st),
+                "mlpsp_grouped_weight_gradients")
+        word = int(nonfinite.item())
+        if word & 2:
+            raise RuntimeError("grouped_weight_gradients: a device-side wait gave up; results discarded")
+        return result, bool(word & 1)
+
+    result = _checked_grouped_vjp(launch, dtype, scale)
     sizes = [2304, 32, 1024, 32, 128, 4]
     return [v.reshape(w.shape).contiguous() for v, w in zip(result.split(sizes, dim=1), weights)]

@@ -54,7 +54,7 @@ def test_null_segment_arrays_are_refused_before_any_launch():
     sc.n, sc.hidden, sc.num_freq = 4, 32, 6
     fake = 0x1000     # never dereferenced: the call must stop at its argument checks
     sc.W1 = sc.b1 = sc.W2 = sc.b2 = sc.W3 = sc.freq = sc.att = fake
-    rc = lib.mlpsp_grouped_weight_gradients(ctypes.byref(sc), fake, fake, fake, None, None, None, None, 3, 128, 1.0,
+    rc = lib.mlpsp_grouped_weight_gradients(ctypes.byref(sc), fake, fake, fake, None, None, None, None, 3, 128, 0, 1.0,
                                             None, fake, fake, None)
     assert rc == -1 and b"null pointer" in lib.mlpsp_last_error()
     assert lib.mlpsp_records_reverse(None, None, None, None, None, None, None, None, 0, 0, 0, None, None, None, None, None) == -1
