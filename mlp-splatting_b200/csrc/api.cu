@@ -292,7 +292,7 @@ static Scratch grouped_layout(void* base, int64_t R, int n) {
   char* p = (char*)base;
   int64_t off = 0;
   auto take = [&](int64_t bytes) { char* r = p ? p + off : nullptr; off += align_up(bytes, 256); return r; };
-  s.prim_cnt = (int32_t*)take(4 * ((int64_t)n + 1));
+  s.prim_cnt = (int32_t*)take(4 * 2 * ((int64_t)n + 4));
   s.prim_cursor = (int32_t*)take(4 * ((int64_t)n + 1));
   s.prim_off = (int32_t*)take(4 * ((int64_t)n + 2));
   s.scan_blk = (int32_t*)take(4 * 3 * ((int64_t)n / kScanItems + 4));

@@ -331,9 +331,30 @@ __global__ void __launch_bounds__(THREADS) k_sort_ids(const int32_t* __restrict_
   for (int i = threadIdx.x; i < n; i += THREADS) tile_prims[s + i] = sm.val[cur][i];
 }
 
+// The same scan by one CTA for inputs of at most 32,768 items (the tile counts of a frame up to 1920x1080):
+// thread t owns the items [t * per, t * per + per).  One launch instead of three.
+constexpr int kScanSmallMax = 32768;
+__global__ void __launch_bounds__(1024) k_scan_small(const int32_t* __restrict__ in, int n, int32_t* __restrict__ out) {
+  __shared__ int warp_sums[32];
+  const int per = (n + 1023) / 1024;
+  const int b = min(n, (int)threadIdx.x * per), e = min(n, b + per);
+  int s = 0;
+  for (int i = b; i < e; ++i) s += in[i];
+  int total;
+  int ex = block_exclusive_scan(s, warp_sums, total);
+  for (int i = b; i < e; ++i) { const int v = in[i]; out[i] = ex; ex += v; }
+  if (threadIdx.x == 0) out[n] = total;
+}
+
+int scan_launches(int64_t n) { return n <= 0 ? 0 : (n <= kScanSmallMax ? 1 : 3); }
+
 int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cudaStream_t st) {
   const int nblk = (int)((n + kScanItems - 1) / kScanItems);
   if (nblk == 0) return MLPSP_OK;
+  if (n <= kScanSmallMax && in != out) {
+    k_scan_small<<<1, 1024, 0, st>>>(in, (int)n, out);
+    return cuda_check(cudaGetLastError(), "scan");
+  }
   k_scan_partial<<<nblk, 1024, 0, st>>>(in, n, blk);
   k_scan_top<<<1, 1024, 0, st>>>(blk, nblk);
   k_scan_final<<<nblk, 1024, 0, st>>>(in, n, blk, out);
@@ -371,7 +392,7 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_cnt, 0, 4 * (size_t)(T + 1), st));
   MLPSP_CUDA_OK(cudaMemsetAsync(fill, 0, 4 * (size_t)T, st));
   const int n = sc->n;
-  LaunchScope scope(kKBin, (n > 0 ? (order_lists ? 7 : 6) : 4) + (pretest ? 1 : 0), st);
+  LaunchScope scope(kKBin, (n > 0 ? (order_lists ? 4 : 3) : 1) + scan_launches(T) + (pretest ? 1 : 0), st);
   if (pretest) launch_tile_frames(fr, s.tile_frame, st);
   if (n > 0) k_bin_count<<<(n + 255) / 256, 256, 0, st>>>((const float4*)sc->geom, n, cam, s.rect, s.tile_cnt);
   int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
@@ -493,7 +514,7 @@ int launch_bin_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scrat
   const int n = sc->n;
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_cnt, 0, 4 * (size_t)(T + 1), st));
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_fill, 0, 4 * (size_t)T, st));
-  LaunchScope scope(kKBin, 8, st);
+  LaunchScope scope(kKBin, 5 + scan_launches(T), st);
   k_tile_cones<<<(T + 127) / 128, 128, 0, st>>>(fr->rays_o, fr->rays_d, fr->width, fr->height, ntx, T, cones, fr->status);
   const dim3 grid((std::max(n, 1) + 255) / 256, (T + kConeChunk - 1) / kConeChunk);
   if (n > 0) k_cone_bin<false><<<grid, 256, 0, st>>>((const float4*)sc->geom, n, cones, T, rm, s.tile_cnt, nullptr, nullptr, fr->status);
@@ -532,7 +553,7 @@ int launch_bin_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratc
   MLPSP_CUDA_OK(cudaMemsetAsync(s.tile_fill, 0, 4 * (size_t)T, st));
   const int n = sc->n;
   const int batches = (num_views + kViewBatch - 1) / kViewBatch;
-  LaunchScope scope(kKBin, 2 * batches + 5, st);
+  LaunchScope scope(kKBin, 2 * batches + 2 + scan_launches(T), st);
   auto pass = [&](bool scatter) {
     for (int v0 = 0; v0 < num_views && n > 0; v0 += kViewBatch) {
       BinCams cams;

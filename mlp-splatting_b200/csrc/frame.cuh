@@ -39,7 +39,7 @@ struct Scratch {
   float2* px_depth;      // [P] (sum w t, sum w)
   uint32_t* masks32;     // [2*max_pairs] evaluated-hit mask halves per pair
   uint32_t* pair_base;   // [max_pairs] first compositing slot of the pair
-  int32_t* prim_cnt;     // [n] records per primitive in the current wave
+  int32_t* prim_cnt;     // [2][n] records per primitive in the current wave (even waves use the first half, odd the second)
   int32_t* prim_cursor;  // [n]
   int32_t* prim_off;     // [n+1]
   int4* work;            // [max_work] (primitive, first record, rows, 0)
@@ -86,7 +86,7 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.px_depth = (float2*)take(8 * P);
   s.masks32 = (uint32_t*)take(8 * max_pairs);
   s.pair_base = (uint32_t*)take(4 * max_pairs);
-  s.prim_cnt = (int32_t*)take(4 * (int64_t)n);
+  s.prim_cnt = (int32_t*)take(4 * 2 * ((int64_t)n + 4));
   s.prim_cursor = (int32_t*)take(4 * (int64_t)n);
   s.prim_off = (int32_t*)take(4 * ((int64_t)n + 1));
   s.max_work = (int64_t)n + max_records / kRowsPerItem + 2;
@@ -203,6 +203,9 @@ int launch_feature_tc(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratc
 
 // multi-block exclusive scan of per-primitive record counts plus evaluator work-item emission
 // split_small: remainders of at most 64 records go to the small-group list (s.work_small)
-int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st, bool split_small = false);
+// distance in elements between the count arrays of even and odd waves (keeps the second one 16-byte aligned)
+__host__ __device__ inline size_t prim_cnt_stride(int n) { return ((size_t)n + 3) & ~(size_t)3; }
+int scan_launches(int64_t n);   // kernels launch_scan_i32 launches for n items
+int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st, bool split_small = false, int wave = 0);
 
 }  // namespace mlpsp

@@ -28,27 +28,29 @@ constexpr int kWinMax = 2048;
 static inline float miss_bound2(float thr) { return (float)(-2.0 * log((double)thr) * 1.02); }
 
 // -------------------------------------------------------------------------- frame init ----
-__global__ void k_init_pixels(int64_t P, float4* __restrict__ px_state, float2* __restrict__ px_depth,
-                              float* __restrict__ rgb, float* __restrict__ alpha, float* __restrict__ depth_t,
-                              float bgr, float bgg, float bgb) {
+// One launch prepares a frame: pixel state and the output image, the list of live tiles and the wave counters,
+// and the per-primitive counts and cursors of the first wave.
+// tile_len (when not already written by the sort's tile pre-test) = the length of the caller's list.
+__global__ void k_init_frame(int64_t P, float4* __restrict__ px_state, float2* __restrict__ px_depth,
+                             float* __restrict__ rgb, float* __restrict__ alpha, float* __restrict__ depth_t,
+                             float bgr, float bgg, float bgb, int T, int32_t* __restrict__ active0,
+                             int32_t* __restrict__ counters, const int32_t* __restrict__ tile_offsets,
+                             int32_t* __restrict__ tile_len, int lists_refined, int n, int32_t* __restrict__ prim_cnt,
+                             int32_t* __restrict__ prim_cursor) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= P) return;
-  px_state[i] = make_float4(0.f, 0.f, 0.f, 1.f);
-  px_depth[i] = make_float2(0.f, 0.f);
-  rgb[i * 3] = bgr; rgb[i * 3 + 1] = bgg; rgb[i * 3 + 2] = bgb;
-  alpha[i] = 0.f;
-  if (depth_t) depth_t[i] = 0.f;
-}
-
-// tile_len (when not already written by the sort's tile pre-test) = the length of the caller's list
-__global__ void k_init_tiles(int T, int32_t* __restrict__ active0, int32_t* __restrict__ counters,
-                             const int32_t* __restrict__ tile_offsets, int32_t* __restrict__ tile_len, int lists_refined) {
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < T) {
-    active0[t] = t;
-    if (!lists_refined) tile_len[t] = tile_offsets[t + 1] - tile_offsets[t];
+  if (i < P) {
+    px_state[i] = make_float4(0.f, 0.f, 0.f, 1.f);
+    px_depth[i] = make_float2(0.f, 0.f);
+    rgb[i * 3] = bgr; rgb[i * 3 + 1] = bgg; rgb[i * 3 + 2] = bgb;
+    alpha[i] = 0.f;
+    if (depth_t) depth_t[i] = 0.f;
   }
-  if (t == 0) {
+  if (i < T) {
+    active0[i] = (int)i;
+    if (!lists_refined) tile_len[i] = tile_offsets[i + 1] - tile_offsets[i];
+  }
+  if (i < n) { prim_cnt[i] = 0; prim_cnt[prim_cnt_stride(n) + i] = 0; prim_cursor[i] = 0; }   // the counts of even and odd waves
+  if (i == 0) {
     counters[kCtrRecords] = 0; counters[kCtrWork] = 0; counters[kCtrWorkNext] = 0; counters[kCtrWorkSmall] = 0;
     counters[kCtrActive0] = T; counters[kCtrActive1] = 0;
   }
@@ -214,9 +216,12 @@ __global__ void k_prim_partial(const int32_t* __restrict__ prim_cnt, int n, int 
 }
 
 // Second pass: every block sums the partial totals of the blocks before it (a few hundred at most), scans
-// its own 4096 counts, writes the CSR offsets and the evaluator's work items and clears the counts for the
-// next wave; the last block also publishes the wave's totals.
-__global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict__ prim_cursor, int n, int split,
+// its own 4096 counts, writes the CSR offsets and the evaluator's work items and clears the counts the NEXT wave
+// will add to (waves alternate between two count arrays, so nothing this launch reads is written by it); the last
+// block also publishes the wave's totals.  blk == nullptr: there was no first pass -- the block sums the counts
+// of the blocks before it itself (worth it up to a few blocks: one launch instead of two).
+__global__ void k_prim_final(const int32_t* __restrict__ prim_cnt, int32_t* __restrict__ prim_cnt_next,
+                             int32_t* __restrict__ prim_cursor, int n, int split,
                              const int32_t* __restrict__ blk, int32_t* __restrict__ prim_off,
                              int4* __restrict__ work, int64_t max_work, int4* __restrict__ work_small, int64_t max_work_small,
                              int32_t* __restrict__ counters, int next_list, int32_t* __restrict__ status) {
@@ -228,7 +233,19 @@ __global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict
     return;
   }
   int pa = 0, pb = 0, pm = 0;
-  for (int i = threadIdx.x; i < (int)blockIdx.x; i += blockDim.x) { pa += blk[3 * i]; pb += blk[3 * i + 1]; pm += blk[3 * i + 2]; }
+  if (blk) {
+    for (int i = threadIdx.x; i < (int)blockIdx.x; i += blockDim.x) { pa += blk[3 * i]; pb += blk[3 * i + 1]; pm += blk[3 * i + 2]; }
+  } else {
+    const int4* c4 = reinterpret_cast<const int4*>(prim_cnt);     // both count arrays start 16-byte aligned
+    const int before4 = (int)blockIdx.x * (kScanItems / 4);
+#pragma unroll 2
+    for (int i = threadIdx.x; i < before4; i += blockDim.x) {
+      const int4 c = c4[i];
+      pa += c.x + c.y + c.z + c.w;
+      pb += items_of(c.x, split) + items_of(c.y, split) + items_of(c.z, split) + items_of(c.w, split);
+      pm += small_items_of(c.x, split) + small_items_of(c.y, split) + small_items_of(c.z, split) + small_items_of(c.w, split);
+    }
+  }
   int base_a, base_b, base_m;
   block_exclusive_scan(pa, warp_sums, base_a);
   block_exclusive_scan(pb, warp_sums, base_b);
@@ -258,7 +275,7 @@ __global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict
           work_small[em + q] = make_int4((int)(base + j), ea + first_small + q * kRowsPerSmallItem,
                                          min(kRowsPerSmallItem, c[j] - first_small - q * kRowsPerSmallItem), 0);
       ea += c[j]; eb += it; em += sm;
-      prim_cnt[base + j] = 0;
+      prim_cnt_next[base + j] = 0;
       prim_cursor[base + j] = 0;
     }
   }
@@ -283,14 +300,21 @@ __global__ void k_prim_final(int32_t* __restrict__ prim_cnt, int32_t* __restrict
   }
 }
 
-int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st, bool split_small) {
+// Up to 32,768 primitives the scan is one launch.  Beyond that the block that sums the most counts becomes the
+// launch's critical path (100,000 primitives: 23 us in one launch against 18 us in two).
+constexpr int kPrimScanSoloBlocks = 8;
+
+int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st, bool split_small, int wave) {
   const int nblk = (n + kScanItems - 1) / kScanItems;
   if (nblk == 0) return MLPSP_OK;
-  LaunchScope scope(kKScan, 2, st);
+  const bool solo = nblk <= kPrimScanSoloBlocks;
+  LaunchScope scope(kKScan, solo ? 1 : 2, st);
   const int split = split_small && s.work_small ? 1 : 0;
-  k_prim_partial<<<nblk, 1024, 0, st>>>(s.prim_cnt, n, split, s.scan_blk, status);
-  k_prim_final<<<nblk, 1024, 0, st>>>(s.prim_cnt, s.prim_cursor, n, split, s.scan_blk, s.prim_off, s.work, s.max_work,
-                                     s.work_small, s.max_work_small, s.counters, next_list, status);
+  const int32_t* cnt = s.prim_cnt + (size_t)(wave & 1) * prim_cnt_stride(n);
+  int32_t* cnt_next = s.prim_cnt + (size_t)((wave & 1) ^ 1) * prim_cnt_stride(n);
+  if (!solo) k_prim_partial<<<nblk, 1024, 0, st>>>(cnt, n, split, s.scan_blk, status);
+  k_prim_final<<<nblk, 1024, 0, st>>>(cnt, cnt_next, s.prim_cursor, n, split, solo ? nullptr : s.scan_blk, s.prim_off, s.work,
+                                     s.max_work, s.work_small, s.max_work_small, s.counters, next_list, status);
   return cuda_check(cudaGetLastError(), "prim_scan");
 }
 
@@ -882,18 +906,17 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   // filled by a device copy afterwards
   uint32_t* used32 = (keep || want_feat) ? s.used32 : (uint32_t*)fr->mask_used;
   {
-    LaunchScope scope(kKMisc, 2, st);
-    k_init_pixels<<<(unsigned)((P + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha,
-                                                               fr->depth_t, bg[0], bg[1], bg[2]);
-    k_init_tiles<<<(T + 255) / 256, 256, 0, st>>>(T, s.active[0], s.counters, fr->tile_offsets, s.tile_len, lists_refined ? 1 : 0);
+    LaunchScope scope(kKMisc, 1, st);
+    const int64_t span = std::max<int64_t>(std::max<int64_t>(P, T), n);
+    k_init_frame<<<(unsigned)((span + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha, fr->depth_t, bg[0], bg[1],
+                                                                bg[2], T, s.active[0], s.counters, fr->tile_offsets, s.tile_len,
+                                                                lists_refined ? 1 : 0, n, s.prim_cnt, s.prim_cursor);
   }
   if (used32) MLPSP_CUDA_OK(cudaMemsetAsync(used32, 0, 8 * (size_t)fr->max_pairs, st));
   if (n == 0) {
     if (want_feat) MLPSP_CUDA_OK(cudaMemsetAsync(fr->feat, 0, 4 * (size_t)P * sc->feat_dim, st));
     return cuda_check(cudaGetLastError(), "render_sorted");
   }
-  MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cnt, 0, 4 * (size_t)n, st));
-  MLPSP_CUDA_OK(cudaMemsetAsync(s.prim_cursor, 0, 4 * (size_t)n, st));
   const bool tc_path = fr->precision == MLPSP_PRECISION_F16 || fr->precision == MLPSP_PRECISION_BF16;
   const bool ref_arith = fr->hit_arith == 1;
   // Small groups get their own work list and kernel when the tensor-core evaluator runs and the scene is one whose
@@ -929,13 +952,13 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
       k_hits<true><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
-                              s.prim_cnt, s.counters, fr->max_records, fr->status);
+                              s.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n), s.counters, fr->max_records, fr->status);
     else
       k_hits<false><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
-                              s.prim_cnt, s.counters, fr->max_records, fr->status); }
-    int rc = launch_prim_scan(s, n, nxt, fr->status, st, split_small);
+                              s.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n), s.counters, fr->max_records, fr->status); }
+    int rc = launch_prim_scan(s, n, nxt, fr->status, st, split_small, w);
     if (rc) return rc;
     { LaunchScope scope(kKFill, 1, st);
     k_fill<<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
@@ -1095,7 +1118,7 @@ int launch_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, const Sc
   const int64_t P = (int64_t)W * H;
   int32_t* worst = s.counters + kCtrScratch;     // [0] largest per-pixel count, [1] capacity flag
   MLPSP_CUDA_OK(cudaMemsetAsync(worst, 0, 8, st));
-  LaunchScope scope(kKMisc, 6, st);
+  LaunchScope scope(kKMisc, 3 + scan_launches(P), st);
   k_export<false><<<T, 64, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                                     W, H, ntx, fr->threshold, sc->gate_beta, sc->gate_tau, s.used32, s.masks32,
                                     s.pair_base, s.rec_out, s.rec_ext, s.rec_tr, s.px_state, s.px_cnt, nullptr, max_hits,
