@@ -477,6 +477,50 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
     return out
 
 
+def weight_gradient_measure(dev, primitives=50000, per=100):
+    """Per-primitive weight gradients (the backward side of the record path) on synthetic primitive-major records:
+    ms per call of the IEEE FP32 kernel and of the tensor-core kernel with binary16 / bfloat16 operands."""
+    import torch
+    from mlp_splatting_b200.primitive_csr import PrimitiveCSR
+    from mlp_splatting_b200.primitive_gemm import grouped_weight_gradients, prepare_groups
+    g = torch.Generator().manual_seed(3)
+    counts = torch.poisson(torch.full((primitives,), float(per)), generator=g).to(torch.int64)
+    offsets = torch.cat((torch.zeros(1, dtype=torch.int64), counts.cumsum(0))).to(dev)
+    R = int(offsets[-1])
+    gd = torch.Generator(device=dev).manual_seed(4)
+    x6 = torch.randn((R, 6), device=dev, generator=gd) * 0.2
+    d3 = torch.randn((R, 4), device=dev, generator=gd)
+    weights = [torch.randn((primitives, *shape), device=dev, generator=gd) * 0.1
+               for shape in [(32, 72), (32,), (32, 32), (32,), (4, 32), (4,)]]
+    freq = (2.0 ** torch.arange(6, dtype=torch.float32)).to(dev)
+    att = torch.exp(-0.5 * freq.square() * 1e-4)
+    csr = PrimitiveCSR(offsets, torch.arange(R, device=dev), x6, d3, None)
+    groups = prepare_groups(csr, 512)
+    out = {"primitives": primitives, "records": R, "segment_size": 512,
+           "note": "ms per call through primitive_gemm.grouped_weight_gradients (host wrapper and flag read included)"}
+    ref = None
+    for name, dt in (("fp32_ms", torch.float32), ("f16_ms", torch.float16), ("bf16_ms", torch.bfloat16)):
+        for _ in range(2):
+            res = grouped_weight_gradients(csr, freq, att, weights, dtype=dt, groups=groups)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            res = grouped_weight_gradients(csr, freq, att, weights, dtype=dt, groups=groups)
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = e0.elapsed_time(e1) / 3
+        if ref is None:
+            ref = res[0]
+        else:
+            out[name.replace("_ms", "_rel_l2_dW1_vs_fp32")] = float((res[0] - ref).norm() / ref.norm())
+    # 2 (mul, add) x 3 products (forward, adjoint, gradient) x the network's multiply-adds
+    out["f16_tflops"] = R * 3 * 6912.0 / (out["f16_ms"] / 1e3) / 1e12
+    del csr, groups, weights, x6, d3, res, ref
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_decoder(args):
     """The step after the feature map on its own: fused decoder + text query, decoder alone, full-width query."""
     import torch
@@ -675,6 +719,11 @@ def main():
                 others[name] = short_measure(name, args, dev, world, rank, lib, flush, steps=5 if views < 8 else 2)
             except Exception as exc:     # the headline line must not be lost over an extra measurement
                 others[name] = {"failed": f"{type(exc).__name__}: {exc}"[:300]}
+        if world == 1:
+            try:
+                others["weight_gradients_50k_x100"] = weight_gradient_measure(dev)
+            except Exception as exc:
+                others["weight_gradients_50k_x100"] = {"failed": f"{type(exc).__name__}: {exc}"[:300]}
 
     if rank == 0:
         line = {

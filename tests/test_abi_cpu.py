@@ -74,3 +74,45 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libmlpsp_b200.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+def test_weight_gradient_safety_policy_on_a_fake_launch():
+    """The host policy of grouped_weight_gradients (scannet/primitive_gemm.py:64-98) without a GPU: a finite result
+    is returned as is, a non-finite mixed-precision result is recomputed once in unscaled FP32 with a warning, a
+    non-finite FP32 result raises, and the counters follow."""
+    import warnings
+
+    import pytest
+    import torch
+    from mlp_splatting_b200 import primitive_gemm as pg
+    pg.get_grouped_vjp_safety_stats(reset=True)
+    calls = []
+
+    def launch_ok(dtype, scale):
+        calls.append((dtype, scale))
+        return "result", False
+
+    assert pg._checked_grouped_vjp(launch_ok, torch.float16, 4096.0) == "result"
+    assert calls == [(torch.float16, 4096.0)]
+
+    def launch_mixed_bad(dtype, scale):
+        calls.append((dtype, scale))
+        return ("fp32 result", False) if dtype == torch.float32 else ("garbage", True)
+
+    calls.clear()
+    with pytest.warns(RuntimeWarning, match="retrying with IEEE FP32"):
+        assert pg._checked_grouped_vjp(launch_mixed_bad, torch.bfloat16, 1.0) == "fp32 result"
+    assert calls == [(torch.bfloat16, 1.0), (torch.float32, 1.0)]
+
+    def launch_bad(dtype, scale):
+        return "garbage", True
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        with pytest.raises(FloatingPointError, match="IEEE FP32 MLP VJP is nonfinite"):
+            pg._checked_grouped_vjp(launch_bad, torch.float16, 4096.0)
+        with pytest.raises(FloatingPointError):
+            pg._checked_grouped_vjp(launch_bad, torch.float32, 1.0)
+    stats = pg.get_grouped_vjp_safety_stats(reset=True)
+    assert stats == {"calls": 4, "mixed_calls": 3, "fp32_fallbacks": 2, "fp32_nonfinite_failures": 2}
+    assert pg.get_grouped_vjp_safety_stats()["calls"] == 0
