@@ -464,9 +464,20 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
         dist.all_reduce(rec_t)
     hidden = int(wl.cfg.get("hidden", 32))
     mlp_ms = classes["mlp"]["ms_per_step"]
+    # what the evaluator must move on this rank: 32 B in + 16 B out per record, one weight image per work item.  With
+    # few records per primitive the weight images dominate and this, not the tensor pipe, is the roof.
+    alg_bytes = stats.records * 48.0 + stats.work_total * weight_image_bytes(hidden)
+    pk = peaks()
+    hbm = {"algorithmic_gb_this_rank": alg_bytes / 1e9,
+           "achieved_gbs": alg_bytes / (mlp_ms / 1e3) / 1e9 if mlp_ms > 0 else 0.0,
+           "peak_gbs": pk["hbm_gbs"],
+           "flop_per_byte": stats.records * flop_per_record(hidden) / max(alg_bytes, 1.0)}
+    hbm["frac"] = hbm["achieved_gbs"] / pk["hbm_gbs"]
+    hbm["tflops_at_hbm_peak"] = hbm["flop_per_byte"] * pk["hbm_gbs"] / 1e3
     out = {"frames_per_sec": wl.frames_per_step * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps, "steps": steps,
            "scaling": wl.scaling, "views_per_step": wl.frames_per_step, "hidden": hidden,
            "evaluator_tflops_this_rank": stats.records * flop_per_record(hidden) / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0,
+           "evaluator_hbm_view": hbm,
            "records_per_step": float(rec_t[0]), "rows_per_evaluator_block": float(rec_t[0]) / max(float(rec_t[1]), 1.0),
            "fill_of_evaluator_blocks": float(rec_t[0]) / max(128.0 * float(rec_t[1] - rec_t[2]) + 32.0 * float(rec_t[2]), 1.0),
            "small_group_share_of_blocks": float(rec_t[2]) / max(float(rec_t[1]), 1.0),

@@ -22,7 +22,29 @@ import torch
 from torch import nn
 
 from . import _lib as L
-from .engine import TILE_CAPACITY, FrameRenderer, PackedScene
+from .engine import FrameRenderer, PackedScene
+
+
+def _tile_ext_build_config(tile_size=None):
+    """The reference's extension build configuration (cumodel.py:96-130) as run-time configuration.
+
+    The reference compiles one extension per combination of these environment variables (-D flags); this
+    library's kernels take the same quantities as arguments of a call, so the variables select arguments:
+      MLPSP_TILE_CANDIDATE_CAPACITY  768 or 1536 (default)  -> FrameRenderer(tile_capacity=...), and with it the
+                                                               "tile candidate capacity N exceeded" error
+      MLPSP_TRAINING_BACKEND=csr with MLPSP_CSR_MAX_HITS     128 (default), 256 or 512 -> max_hits of the record export
+      MLPSP_NVCC_MAXRREGCOUNT        accepted and ignored: the register budgets belong to this library's own kernels
+    Same checks and error texts as the reference."""
+    tile_candidates = int(os.environ.get("MLPSP_TILE_CANDIDATE_CAPACITY", "1536"))
+    if tile_candidates not in {768, 1536}:
+        raise ValueError("MLPSP_TILE_CANDIDATE_CAPACITY must be 768 or 1536")
+    max_hits = None
+    if os.environ.get("MLPSP_TRAINING_BACKEND", "legacy") == "csr":
+        max_hits = int(os.environ.get("MLPSP_CSR_MAX_HITS", "128"))
+        if max_hits not in {128, 256, 512}:
+            raise ValueError("MLPSP_CSR_MAX_HITS must be 128, 256 or 512; overflow is an error")
+    return {"tile_candidate_capacity": tile_candidates, "csr_max_hits": max_hits,
+            "tile_size": 8 if tile_size is None else int(tile_size)}
 
 
 class IntegratedPositionalEncoding(nn.Module):
@@ -194,9 +216,10 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
 
     def _renderer(self, device) -> FrameRenderer:
         W, H = self.image_size
-        key = (str(device), W, H)
+        capacity = _tile_ext_build_config(self.tile_size)["tile_candidate_capacity"]
+        key = (str(device), W, H, capacity)
         if key not in self._renderers:
-            self._renderers[key] = FrameRenderer(W, H, device=device, tile_capacity=TILE_CAPACITY)
+            self._renderers[key] = FrameRenderer(W, H, device=device, tile_capacity=capacity)
         return self._renderers[key]
 
     def _render(self, ray_o, ray_d, score_threshold, bg_color, view_matrix, proj_matrix, culled_prim_indices,
@@ -376,13 +399,17 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
 
 @torch.no_grad()
 def render_tiles_training_records(tensors, width, height, tile, threshold, beta, temperature, precision="float32",
-                                  max_hits=512):
+                                  max_hits=None):
     """Forward record list with the argument list of the reference's extension entry points
     render_tiles_training_records / render_tiles_training_records_wmma (np_tile_kernels.cu:6994,
     training_wmma.cuh:270): `tensors` = [rays_o, rays_d (unit), positions, log_scales, quats (unit),
     culled_prim_indices, tile_offsets, freq, att, W1, b1, W2, b2, W3, b3] (two trailing adjoint
     placeholders are accepted and ignored).  Returns [rgb, alpha, ids, x6, raw, masks, gates, offsets].
-    precision "float32" selects the scalar evaluator, "float16" the tensor-core one."""
+    precision "float32" selects the scalar evaluator, "float16" the tensor-core one.  max_hits (records per pixel;
+    more is an error) defaults to MLPSP_CSR_MAX_HITS when MLPSP_TRAINING_BACKEND=csr is set, else to 512."""
+    cfg = _tile_ext_build_config(tile)
+    if max_hits is None:
+        max_hits = cfg["csr_max_hits"] or 512
     if len(tensors) not in (15, 17):
         raise ValueError("expected the 15 scene tensors (optionally followed by two adjoint placeholders)")
     if int(tile) != 8:
@@ -393,7 +420,8 @@ def render_tiles_training_records(tensors, width, height, tile, threshold, beta,
     dev = ro.device
     scene = PackedScene(pos, ls, q, W1, b1, W2, b2, W3, b3, freq, att, gate_beta=float(beta), gate_tau=float(temperature),
                         device=dev, pack_f16=(precision == "float16"))
-    r = FrameRenderer(int(width), int(height), device=dev, max_pairs=max(int(culled.numel()), 1))
+    r = FrameRenderer(int(width), int(height), device=dev, max_pairs=max(int(culled.numel()), 1),
+                      tile_capacity=cfg["tile_candidate_capacity"])
     prec = L.PRECISION_F16 if (precision == "float16" and scene.has_f16) else L.PRECISION_F32
     return r.render_records(scene, ro.contiguous().float(), rd.contiguous().float(), float(threshold), max_hits=max_hits,
                             precision=prec, tile_lists=(culled, offs), rays_normalized=True,

@@ -116,3 +116,26 @@ def test_weight_gradient_safety_policy_on_a_fake_launch():
     stats = pg.get_grouped_vjp_safety_stats(reset=True)
     assert stats == {"calls": 4, "mixed_calls": 3, "fp32_fallbacks": 2, "fp32_nonfinite_failures": 2}
     assert pg.get_grouped_vjp_safety_stats()["calls"] == 0
+
+
+def test_build_configuration_variables_select_run_time_arguments(monkeypatch):
+    """The reference's build-time environment variables (scannet/cumodel.py:96-130), same checks and texts."""
+    import pytest
+    from mlp_splatting_b200.cumodel import _tile_ext_build_config
+    for k in ("MLPSP_TILE_CANDIDATE_CAPACITY", "MLPSP_TRAINING_BACKEND", "MLPSP_CSR_MAX_HITS", "MLPSP_NVCC_MAXRREGCOUNT"):
+        monkeypatch.delenv(k, raising=False)
+    assert _tile_ext_build_config() == {"tile_candidate_capacity": 1536, "csr_max_hits": None, "tile_size": 8}
+    monkeypatch.setenv("MLPSP_TILE_CANDIDATE_CAPACITY", "768")
+    monkeypatch.setenv("MLPSP_NVCC_MAXRREGCOUNT", "64")
+    assert _tile_ext_build_config()["tile_candidate_capacity"] == 768
+    monkeypatch.setenv("MLPSP_TILE_CANDIDATE_CAPACITY", "1000")
+    with pytest.raises(ValueError, match="MLPSP_TILE_CANDIDATE_CAPACITY must be 768 or 1536"):
+        _tile_ext_build_config()
+    monkeypatch.setenv("MLPSP_TILE_CANDIDATE_CAPACITY", "1536")
+    monkeypatch.setenv("MLPSP_TRAINING_BACKEND", "csr")
+    assert _tile_ext_build_config()["csr_max_hits"] == 128
+    monkeypatch.setenv("MLPSP_CSR_MAX_HITS", "256")
+    assert _tile_ext_build_config()["csr_max_hits"] == 256
+    monkeypatch.setenv("MLPSP_CSR_MAX_HITS", "300")
+    with pytest.raises(ValueError, match="MLPSP_CSR_MAX_HITS must be 128, 256 or 512"):
+        _tile_ext_build_config()

@@ -564,6 +564,31 @@ def test_module_surface_matches_reference_class(dev):
         NeuralPrimitiveSceneTileCUDA(num_primitives=4)._activate_cuda_device()
 
 
+def test_module_takes_the_tile_capacity_from_the_environment(dev, monkeypatch):
+    """MLPSP_TILE_CANDIDATE_CAPACITY=768 (a build flag of the reference, scannet/cumodel.py:102-104): the module's
+    frames then refuse a tile with 769 candidates with the reference's text and accept 768."""
+    from mlp_splatting_b200.cumodel import NeuralPrimitiveSceneTileCUDA
+    from mlp_splatting_b200.engine import RenderError
+    scene, cam = small_case(**CASES["tiny"])
+    n = scene["positions"].shape[0]
+    m = NeuralPrimitiveSceneTileCUDA(num_primitives=n, precision="fp32").to(dev)
+    with torch.no_grad():
+        for k in ("positions", "log_scales", "quats") + WKEYS:
+            getattr(m, k).copy_(_t(scene[k], dev))
+    m.set_image_size(cam["W"], cam["H"])
+    monkeypatch.setenv("MLPSP_TILE_CANDIDATE_CAPACITY", "768")
+    T = ((cam["W"] + 7) // 8) * ((cam["H"] + 7) // 8)
+    for count, ok in ((768, True), (769, False)):
+        offs = torch.zeros(T + 1, dtype=torch.int32, device=dev); offs[1:] = count
+        ids = (torch.arange(count, device=dev, dtype=torch.int32) % n).contiguous()
+        if ok:
+            rgb = m(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3, culled_prim_indices=ids, tile_offsets=offs)
+            assert torch.isfinite(rgb).all()
+        else:
+            with pytest.raises(RenderError, match="tile candidate capacity 768 exceeded \\(maximum observed tile length 769\\)"):
+                m(_t(cam["rays_o"], dev), _t(cam["rays_d"], dev), score_threshold=5e-3, culled_prim_indices=ids, tile_offsets=offs)
+
+
 def test_module_with_wide_hidden_layers(dev):
     """hidden_dim = 64 through the module class: refused like the reference unless wide_hidden is set; then the fp16
     frame agrees with the CPU restatement's fp16 model (there is no reference implementation of this width)."""
