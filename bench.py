@@ -324,6 +324,7 @@ class Workload:
             self.frames_per_step, self.scaling = self.nviews, "strong"
         self.cam = self.units[0][0] if self.units else syn.make_camera(cfg["W"], cfg["H"])
         self.r = FrameRenderer(cfg["W"], cfg["H"], device=dev)
+        self.batches, self.view_batch = [], int(getattr(args, "view_batch", 16))
         self.dev_rays = []
         for c, _rows in self.units:
             rd_dev = torch.from_numpy(c["rays_d"]).to(dev)
@@ -346,9 +347,31 @@ class Workload:
             self.ps = self.ps.with_text_query(qtext)
             self.score_dim = tq["classes"]
 
+    def make_batches(self, per_view):
+        """Multi-view workloads whose units are whole views render them in batches (mlpsp_render_frames): one
+        evaluator launch per wave serves every view of a batch, so a primitive's weights are fetched once per wave
+        instead of once per wave and view.  per_view = [(pairs, records)] of the views rendered alone (sizing)."""
+        from mlp_splatting_b200.engine import ViewBatchRenderer
+        self.batches = []
+        cap = self.view_batch
+        if cap < 2 or self.nviews == 1 or self.want_feat or len(self.units) < 2 or any(rows is not None for _c, rows in self.units):
+            return
+        for b0 in range(0, len(self.units), cap):
+            idx = list(range(b0, min(b0 + cap, len(self.units))))
+            pairs = int(1.25 * max(per_view[i][0] for i in idx)) + 4096
+            records = int(1.1 * sum(per_view[i][1] for i in idx)) + 65536
+            br = ViewBatchRenderer(self.cfg["W"], self.cfg["H"], len(idx), device=self.dev, max_pairs=pairs, max_records=records)
+            self.batches.append((br, idx))
+
     def frame(self, check=False):
         cfg, r = self.cfg, self.r
         out = None
+        if self.batches:
+            for br, idx in self.batches:
+                out = br.render(self.ps, [self.dev_rays[i][0] for i in idx], [self.dev_rays[i][1] for i in idx], THRESHOLD,
+                                [self.units[i][0]["view"] for i in idx], [self.units[i][0]["proj"] for i in idx],
+                                precision=self.prec, rays_normalized=True)[-1]
+            return out
         for (c, rows), (ro_u, rd_u) in zip(self.units, self.dev_rays):
             out = r.render(self.ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=self.prec,
                            rays_normalized=True, check=check, tile_rows=rows, want_feat=self.want_feat)
@@ -365,11 +388,20 @@ class Workload:
         stats = self.r.last_stats
         if len(self.units) > 1:
             tot = dict(records=0, used=0, work_total=0, work_small=0)
+            per_view = []
             for (c, rows), (ro_u, rd_u) in zip(self.units, self.dev_rays):
                 self.r.render(self.ps, ro_u, rd_u, THRESHOLD, view=c["view"], proj=c["proj"], precision=self.prec,
                               rays_normalized=True, tile_rows=rows, want_feat=self.want_feat)
                 for k in tot:
                     tot[k] += getattr(self.r.last_stats, k)
+                per_view.append((self.r.last_stats.pairs, self.r.last_stats.records))
+            self.make_batches(per_view)
+            if self.batches:
+                # the batches evaluate the same records in fewer, fuller work items
+                self.frame()
+                tot["work_total"] = sum(br.last_stats.work_total for br, _ in self.batches)
+                tot["work_small"] = sum(br.last_stats.work_small for br, _ in self.batches)
+                assert sum(br.last_stats.records for br, _ in self.batches) == tot["records"]
             stats.records, stats.used, stats.work_total, stats.work_small = tot["records"], tot["used"], tot["work_total"], tot["work_small"]
         self.stats = stats
         return stats
@@ -459,6 +491,8 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
     dev_ms, _wall = timed_block(wl, flush, steps, world)
     classes = class_times(wl, flush, min(steps, 5))
     bits = int(wl.r.status.cpu()[0])
+    for br, _idx in wl.batches:
+        bits |= int(br.lead.status.cpu()[0])
     rec_t = torch.tensor([float(stats.records), float(stats.work_total), float(stats.work_small)], dtype=torch.float64, device=dev)
     if world > 1 and wl.nviews > 1:
         dist.all_reduce(rec_t)
@@ -476,6 +510,7 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
     hbm["tflops_at_hbm_peak"] = hbm["flop_per_byte"] * pk["hbm_gbs"] / 1e3
     out = {"frames_per_sec": wl.frames_per_step * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps, "steps": steps,
            "scaling": wl.scaling, "views_per_step": wl.frames_per_step, "hidden": hidden,
+           "views_per_call": [len(idx) for _br, idx in wl.batches] if wl.batches else 1,
            "evaluator_tflops_this_rank": stats.records * flop_per_record(hidden) / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0,
            "evaluator_hbm_view": hbm,
            "records_per_step": float(rec_t[0]), "rows_per_evaluator_block": float(rec_t[0]) / max(float(rec_t[1]), 1.0),
@@ -593,6 +628,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=HEADLINE)
+    ap.add_argument("--view-batch", type=int, default=16,
+                    help="views of a multi-view workload rendered per call (0 or 1: view by view, as the reference does)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="fp16", choices=["fp16", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -250,6 +250,19 @@ int mlpsp_render_sorted(const mlpsp_scene* scene, const mlpsp_frame* frame, void
  * what sorted_prims holds afterwards. */
 int mlpsp_render_frame(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
 
+/* Several views of one scene in one call (no reference counterpart: the reference renders view by view,
+ * scannet/cumodel.py:951).  frames[0..num_frames) are complete frames as for mlpsp_render_frame -- own rays,
+ * matrices, tile-list buffers, outputs and scratch block each -- of one shape, threshold, precision, tile
+ * capacity and hit_arith, rgb and alpha only (no depth, features, masks, records, statistics, bands), and they
+ * share ONE status block (frames[v].status == frames[0].status; its words are then sums / maxima over the views,
+ * and an error bit of any view fails the batch).  Binning, sorting, hit masks, record fill and compositing run per
+ * view; the per-primitive record counts, CSR offsets, work list and record arrays are those of frames[0]'s
+ * scratch, so frames[0].max_records must cover the MLP evaluations of ALL views (the other frames may be sized
+ * with max_records = 0) and one evaluator launch per wave serves every view: a primitive's weights are fetched
+ * once per wave instead of once per wave and view.  Images are bit-identical to frames rendered alone. */
+#define MLPSP_MAX_BATCH 64
+int mlpsp_render_frames(const mlpsp_scene* scene, const mlpsp_frame* frames, int32_t num_frames, void* stream);
+
 /* Pixel-major records of the frame just rendered with frame->keep_records = 1 on the same scratch: the
  * 8-tensor schema of render_tiles_training_records (np_tile_kernels.cu:3138-3154, 6897-6986;
  * training_wmma.cuh:223-256).  Records of a pixel are in compositing order and hold only the hits that

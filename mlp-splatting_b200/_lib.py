@@ -91,6 +91,7 @@ _SIGS = {
     "mlpsp_sort_tiles": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp, _fp]),
     "mlpsp_hit_masks": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp, _fp]),
     "mlpsp_render_sorted": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp]),
+    "mlpsp_render_frames": (C.c_int, [C.POINTER(Scene), _fp, C.c_int32, _fp]),
     "mlpsp_render_frame": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp]),
     "mlpsp_export_records": (C.c_int, [C.POINTER(Scene), C.POINTER(Frame), _fp, _fp, _fp, _fp, _fp, _fp, C.c_int64,
                                        C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32), _fp]),

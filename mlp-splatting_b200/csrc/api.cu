@@ -254,6 +254,45 @@ extern "C" int mlpsp_render_frame(const mlpsp_scene* sc, const mlpsp_frame* fr, 
   return render_sorted_checked(sc, fr, s, st, pretest);
 }
 
+extern "C" int mlpsp_render_frames(const mlpsp_scene* sc, const mlpsp_frame* frames, int32_t num_frames, void* stream) {
+  MLPSP_REQUIRE(sc && frames && num_frames >= 1 && num_frames <= MLPSP_MAX_BATCH, MLPSP_E_ARG,
+                "mlpsp_render_frames: need 1..%d frames", MLPSP_MAX_BATCH);
+  std::vector<Scratch> ss((size_t)num_frames);
+  const mlpsp_frame* f0 = frames;
+  for (int v = 0; v < num_frames; ++v) {
+    const mlpsp_frame* fr = frames + v;
+    int rc = check_frame_common(sc, fr, "mlpsp_render_frames");
+    if (rc) return rc;
+    MLPSP_REQUIRE(fr->view && fr->proj && fr->rays_o && fr->rays_d && fr->rgb && fr->alpha, MLPSP_E_ARG,
+                  "mlpsp_render_frames: frame %d lacks matrices, rays or outputs", v);
+    MLPSP_REQUIRE(fr->width == f0->width && fr->height == f0->height && fr->threshold == f0->threshold &&
+                      fr->precision == f0->precision && fr->tile_capacity == f0->tile_capacity &&
+                      fr->hit_arith == f0->hit_arith && fr->status == f0->status, MLPSP_E_ARG,
+                  "mlpsp_render_frames: frame %d differs from frame 0 in shape, threshold, precision, capacity, "
+                  "arithmetic or status block", v);
+    MLPSP_REQUIRE(!fr->depth_t && !fr->feat && !fr->mask_used && !fr->keep_records && !fr->stat_sum_w &&
+                      fr->sort_key == 0 && fr->tile_row_begin == 0 && fr->tile_row_end == 0, MLPSP_E_ARG,
+                  "mlpsp_render_frames renders rgb and alpha of whole frames in tile-centre order only (frame %d)", v);
+    rc = get_scratch(sc, fr, ss[(size_t)v], "mlpsp_render_frames");
+    if (rc) return rc;
+  }
+  MLPSP_REQUIRE(f0->precision == MLPSP_PRECISION_F32 || f0->precision == MLPSP_PRECISION_F16 ||
+                    f0->precision == MLPSP_PRECISION_BF16, MLPSP_E_ARG, "render: unknown precision %d", f0->precision);
+  MLPSP_REQUIRE(f0->num_waves >= 0 && f0->num_waves <= MLPSP_MAX_WAVES, MLPSP_E_ARG, "render: bad num_waves");
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool pretest = f0->tile_pretest == 0;
+  for (int v = 0; v < num_frames; ++v) {
+    const mlpsp_frame* fr = frames + v;
+    const Scratch& s = ss[(size_t)v];
+    int rc = launch_bin(sc, fr, s, st, /*order_lists=*/false, pretest);
+    if (rc) return rc;
+    rc = launch_sort(sc, fr, nullptr, st, /*unordered_input=*/true, s.active[1], s.counters + kCtrScratch + 2,
+                     pretest ? s.tile_len : nullptr);
+    if (rc) return rc;
+  }
+  return launch_render_batch(sc, frames, ss.data(), num_frames, st, pretest);
+}
+
 extern "C" int mlpsp_export_records(const mlpsp_scene* sc, const mlpsp_frame* fr, int64_t* offsets, int32_t* ids,
                                     float* x6, float* raw, int32_t* relu_masks, float* gates, int64_t max_out,
                                     int32_t max_hits, int64_t* total_host, int32_t* worst_host, void* stream) {

@@ -205,6 +205,7 @@ int launch_feature_tc(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratc
 // split_small: remainders of at most 64 records go to the small-group list (s.work_small)
 // distance in elements between the count arrays of even and odd waves (keeps the second one 16-byte aligned)
 __host__ __device__ inline size_t prim_cnt_stride(int n) { return ((size_t)n + 3) & ~(size_t)3; }
+int launch_render_batch(const mlpsp_scene* sc, const mlpsp_frame* frs, const Scratch* ss, int V, cudaStream_t st, bool lists_refined);
 int scan_launches(int64_t n);   // kernels launch_scan_i32 launches for n items
 int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st, bool split_small = false, int wave = 0);
 

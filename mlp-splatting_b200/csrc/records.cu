@@ -66,12 +66,15 @@ __global__ void __launch_bounds__(256) k_hits(
     float thr, float bound2, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo,
     int hi, const float4* __restrict__ px_state, uint32_t* __restrict__ masks32, uint32_t* __restrict__ pair_base,
     int32_t* __restrict__ prim_cnt, int32_t* __restrict__ counters, int64_t max_records,
-    int32_t* __restrict__ status) {
+    int32_t* __restrict__ status, int32_t* __restrict__ reset_count) {
   __shared__ uint32_t s_m[2][kWinMax];
   __shared__ int32_t s_pref[kWinMax];
   __shared__ int warp_sums[32];
   __shared__ int s_tile_base;
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  // a view of a batch clears the count of the list its compositing pass of this wave will append to (the
+  // per-primitive scan does that for a frame rendered alone)
+  if (reset_count && blockIdx.x == 0 && threadIdx.x == 0) *reset_count = 0;
   const int n_active = *active_count;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int half = warp & 1;
@@ -952,12 +955,12 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
       k_hits<true><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
-                              s.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n), s.counters, fr->max_records, fr->status);
+                              s.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n), s.counters, fr->max_records, fr->status, nullptr);
     else
       k_hits<false><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
-                              s.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n), s.counters, fr->max_records, fr->status); }
+                              s.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n), s.counters, fr->max_records, fr->status, nullptr); }
     int rc = launch_prim_scan(s, n, nxt, fr->status, st, split_small, w);
     if (rc) return rc;
     { LaunchScope scope(kKFill, 1, st);
@@ -1024,6 +1027,116 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
                                                                   sc->feat_dim, CB, fr->feat, fr->status);
   }
   return cuda_check(cudaGetLastError(), "render_sorted");
+}
+
+// ----------------------------------------------------------------------- view batches ----
+// Several views of one scene rendered together (rgb and alpha only).  Binning, sorting, hit masks, record fill and
+// compositing run per view on the view's own scratch; what is shared is everything per primitive: the record
+// counts, the CSR offsets, the work list and the record arrays live in the first frame's scratch, compositing
+// slots are numbered across the views, and ONE evaluator launch per wave serves all views.  A primitive's weight
+// image is then fetched once per wave for the records of all views, which is what bounds many-primitive scenes
+// (a few records per primitive and view).  Every record goes through the same arithmetic as in a frame rendered
+// alone, so the images are bit-identical.
+int launch_render_batch(const mlpsp_scene* sc, const mlpsp_frame* frs, const Scratch* ss, int V, cudaStream_t st,
+                        bool lists_refined) {
+  const mlpsp_frame* f0 = frs;
+  const Scratch& lead = ss[0];
+  const int W = f0->width, H = f0->height;
+  const int T = num_tiles(W, H, 8);
+  const int ntx = (W + 7) / 8;
+  const int64_t P = (int64_t)W * H;
+  const int n = sc->n;
+  const PrimStats no_stats = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  {
+    LaunchScope scope(kKMisc, V, st);
+    for (int v = 0; v < V; ++v) {
+      const mlpsp_frame* fr = frs + v;
+      float bg[3] = {0.f, 0.f, 0.f};
+      if (fr->bg_color) { bg[0] = fr->bg_color[0]; bg[1] = fr->bg_color[1]; bg[2] = fr->bg_color[2]; }
+      const int nv = v == 0 ? n : 0;     // the per-primitive arrays are the first frame's
+      const int64_t span = std::max<int64_t>(std::max<int64_t>(P, T), nv);
+      k_init_frame<<<(unsigned)((span + 255) / 256), 256, 0, st>>>(P, ss[v].px_state, ss[v].px_depth, fr->rgb, fr->alpha, nullptr, bg[0], bg[1],
+                                                                  bg[2], T, ss[v].active[0], ss[v].counters, fr->tile_offsets,
+                                                                  ss[v].tile_len, lists_refined ? 1 : 0, nv, lead.prim_cnt, lead.prim_cursor);
+    }
+  }
+  if (n == 0) return cuda_check(cudaGetLastError(), "render_batch");
+  const bool tc_path = f0->precision == MLPSP_PRECISION_F16 || f0->precision == MLPSP_PRECISION_BF16;
+  const bool ref_arith = f0->hit_arith == 1;
+  // the second work list costs one launch per wave and batch, not per view, so it pays earlier than for one frame
+  // (measured with and without: fourview_500k in one batch of 4 views 2.51 -> 2.31 ms, stress_2m in batches of 16
+  // views 72.2 -> 65.8 ms of evaluator time)
+  const bool split_small = tc_path && (int64_t)n * 20 > P * V;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int wave_grid = std::min(T, sms * 16);
+  const int nw = f0->num_waves > 0 ? f0->num_waves : (int)(sizeof(kDefaultWaves) / sizeof(int));
+  int lo = 0;
+  for (int w = 0; w < nw && lo < f0->tile_capacity; ++w) {
+    const int wl = f0->num_waves > 0 ? f0->wave_len[w] : kDefaultWaves[w];
+    MLPSP_REQUIRE(wl > 0, MLPSP_E_ARG, "wave_len[%d] must be positive", w);
+    const int hi = (wl >= f0->tile_capacity - lo || w == nw - 1) ? f0->tile_capacity : lo + wl;
+    MLPSP_REQUIRE(hi - lo <= kWinMax, MLPSP_E_LIMIT, "wave window beyond %d candidates", kWinMax);
+    const int cur = w & 1, nxt = cur ^ 1;
+    const bool idle_tail = f0->tail_hint == 1 && hi == f0->tile_capacity && w > 0;
+    const int grid_hits = idle_tail ? sms : wave_grid;
+    const int grid_comp = idle_tail ? sms : std::min(T, sms * 32);
+    const int cap_mlp = idle_tail ? sms : 0;
+    int32_t* cnt = lead.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n);
+    {
+      LaunchScope scope(kKHits, V, st);
+      for (int v = 0; v < V; ++v) {
+        const mlpsp_frame* fr = frs + v;
+        const Scratch& s = ss[v];
+        if (ref_arith)
+          k_hits<true><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len,
+                                                  fr->sorted_prims, W, H, ntx, f0->threshold, miss_bound2(f0->threshold), s.active[cur],
+                                                  s.counters + kCtrActive0 + cur, lo, hi, s.px_state, s.masks32, s.pair_base, cnt,
+                                                  lead.counters, f0->max_records, f0->status, s.counters + kCtrActive0 + nxt);
+        else
+          k_hits<false><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len,
+                                                   fr->sorted_prims, W, H, ntx, f0->threshold, miss_bound2(f0->threshold), s.active[cur],
+                                                   s.counters + kCtrActive0 + cur, lo, hi, s.px_state, s.masks32, s.pair_base, cnt,
+                                                   lead.counters, f0->max_records, f0->status, s.counters + kCtrActive0 + nxt);
+      }
+    }
+    int rc = launch_prim_scan(lead, n, nxt, f0->status, st, split_small, w);
+    if (rc) return rc;
+    {
+      LaunchScope scope(kKFill, V, st);
+      for (int v = 0; v < V; ++v) {
+        const mlpsp_frame* fr = frs + v;
+        const Scratch& s = ss[v];
+        k_fill<<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+                                          W, H, ntx, f0->threshold, s.active[cur], s.counters + kCtrActive0 + cur, lo, hi, s.masks32,
+                                          s.pair_base, lead.prim_off, lead.prim_cursor, lead.rec_in, nullptr, nullptr, sc->gate_beta,
+                                          sc->gate_tau, 0, ref_arith ? 1 : 0, f0->status);
+      }
+    }
+    if (tc_path)
+      rc = launch_mlp_f16(sc, lead.rec_in, lead.prim_off, lead.work, lead.counters, lead.rec_out, nullptr, kOutAlpha, f0->status, st,
+                          f0->precision == MLPSP_PRECISION_BF16, cap_mlp, split_small ? lead.work_small : nullptr);
+    else
+      rc = launch_mlp_f32(sc, lead.rec_in, lead.prim_off, lead.work, lead.counters, lead.rec_out, nullptr, kOutAlpha, f0->status, st, cap_mlp);
+    if (rc) return rc;
+    {
+      LaunchScope scope(kKComposite, V, st);
+      for (int v = 0; v < V; ++v) {
+        const mlpsp_frame* fr = frs + v;
+        const Scratch& s = ss[v];
+        float bg[3] = {0.f, 0.f, 0.f};
+        const int has_bg = fr->bg_color != nullptr;
+        if (has_bg) { bg[0] = fr->bg_color[0]; bg[1] = fr->bg_color[1]; bg[2] = fr->bg_color[2]; }
+        k_composite<false><<<grid_comp, 64, 0, st>>>(no_stats, fr->tile_offsets, s.tile_len, W, H, ntx, s.active[cur],
+                                                     s.counters + kCtrActive0 + cur, lo, hi, s.masks32, s.pair_base, lead.rec_out, nullptr,
+                                                     s.px_state, s.px_depth, fr->rgb, fr->alpha, nullptr, nullptr, nullptr, nullptr, bg[0],
+                                                     bg[1], bg[2], has_bg, s.active[nxt], s.counters + kCtrActive0 + nxt, f0->status);
+      }
+    }
+    lo = hi;
+  }
+  return cuda_check(cudaGetLastError(), "render_batch");
 }
 
 // ----------------------------------------------------------------------- record export ----

@@ -567,6 +567,92 @@ class FrameRenderer:
             return out[:pairs]
 
 
+class ViewBatchRenderer:
+    """Several views of one scene per call (mlpsp_render_frames): one evaluator launch per wave serves all views.
+
+    The reference renders view by view.  In a scene with many primitives a primitive owns only a few records per
+    view, and the evaluator then spends its time streaming weight images (9.5 or 22.8 KB per primitive, wave and
+    view); rendering a batch of views together lets a primitive's records of all views share one fetch.  Every
+    view keeps its own tile lists, masks, pixel state and outputs (a FrameRenderer each); the per-primitive arrays
+    and the record arrays are the first view's, sized for the whole batch.  rgb and alpha only; images are
+    bit-identical to FrameRenderer.render.
+    """
+
+    def __init__(self, width, height, num_views, device="cuda", tile_capacity=TILE_CAPACITY, max_pairs=None,
+                 max_records=16_000_000):
+        if not 1 <= int(num_views) <= 64:
+            raise ValueError("num_views must be in [1, 64]")
+        self.V = int(num_views)
+        self.device = torch.device(device)
+        # the first renderer's scratch carries the record arrays of the batch; the others need none
+        self.views = [FrameRenderer(width, height, device=device, tile_capacity=tile_capacity, max_pairs=max_pairs,
+                                    max_records=(int(max_records) if v == 0 else 0)) for v in range(self.V)]
+        self.lead = self.views[0]
+        self.lib = self.lead.lib
+        self.last_stats: FrameStats | None = None
+        self.f32_fallbacks = 0
+        self._auto_waves = None
+
+    def render(self, scene: PackedScene, rays_o, rays_d, threshold, views, projs, precision=None, bg=None, waves=None,
+               rays_normalized=False, path_name="render_tiles_forward_tilecenter", hit_arith=0):
+        """rays_o / rays_d / views / projs: one entry per view.  Returns [(rgb [P,3], alpha [P,1])] per view (the
+        renderers' own buffers, valid until the next call)."""
+        if not (len(rays_o) == len(rays_d) == len(views) == len(projs) == self.V):
+            raise ValueError(f"expected {self.V} views")
+        lib, d, lead = self.lib, self.device, self.lead
+        if precision is None:
+            precision = L.PRECISION_F16 if scene.has_f16 else L.PRECISION_F32
+        auto = waves is None
+        if auto:
+            waves = self._auto_waves
+        with torch.cuda.device(d):
+            st = _stream_ptr(d)
+            rds = []
+            for v, r in enumerate(self.views):
+                if rays_normalized:
+                    rds.append(rays_d[v])
+                else:
+                    L.check(lib.mlpsp_normalize_rows(L.ptr(rays_d[v]), L.ptr(r.rays_d_unit), r.P, 3, st), "mlpsp_normalize_rows")
+                    rds.append(r.rays_d_unit)
+            for _attempt in range(10):
+                L.check(lib.mlpsp_status_reset(L.ptr(lead.status), st), "mlpsp_status_reset")
+                frames = (L.Frame * self.V)()
+                for v, r in enumerate(self.views):
+                    f = r._frame(scene, rays_o[v], rds[v], threshold, precision, views[v], projs[v], bg, False, False, waves,
+                                 tail_hint=auto and waves is not None, hit_arith=hit_arith)
+                    f.status = L.ptr(lead.status)
+                    frames[v] = f
+                L.check(lib.mlpsp_render_frames(C.byref(scene.c), frames, self.V, st), "mlpsp_render_frames")
+                bits, stats = lead._read_status()
+                self.last_stats = stats
+                if auto and bits == 0:
+                    n = int(stats.waves)
+                    self._auto_waves = (list(FrameRenderer.DEFAULT_WAVES[:n]) + [lead.capacity]
+                                        if 0 < n <= len(FrameRenderer.DEFAULT_WAVES) else None)
+                if bits & (L.BIT_BAD_OFFSETS | L.BIT_TILE_CAPACITY | L.BIT_BAD_IDS | L.BIT_TIMEOUT):
+                    raise_for_status(bits, stats.max_tile_len, lead.capacity, path_name)
+                if bits & L.BIT_PAIR_OVERFLOW:
+                    # the status block is shared, so which view ran out is not known: all lists grow
+                    grown = max(int(lead.max_pairs * 1.5) + 1024, int(stats.pairs * 1.1) + 1024)
+                    for r in self.views:
+                        r.max_pairs = min(grown, r.T * r.capacity)
+                        r.tile_prims = torch.empty(r.max_pairs, device=d, dtype=torch.int32)
+                        r.sorted_prims = torch.empty(r.max_pairs, device=d, dtype=torch.int32)
+                    continue
+                if bits & L.BIT_RECORD_OVERFLOW:
+                    lead.max_records = int(max(stats.wave_records, lead.max_records) * 2) + 4096
+                    continue
+                if (bits & L.BIT_NUMERIC) and precision in (L.PRECISION_F16, L.PRECISION_BF16):
+                    if scene.W1 is None:
+                        raise RenderError(f"{path_name}: non-finite operand or activation in the fp16 evaluator and "
+                                          "the scene holds no FP32 weights to render the frames again with")
+                    self.f32_fallbacks += 1
+                    precision = L.PRECISION_F32
+                    continue
+                return [(r.rgb, r.alpha) for r in self.views]
+            raise RenderError(f"{path_name}: scratch kept overflowing after 10 attempts")
+
+
 class FramePipeline:
     """Several frames in flight on one GPU: per slot a stream, a FrameRenderer and device ray buffers.
 

@@ -860,3 +860,34 @@ def test_per_pixel_feature_map_matches_oracle(dev, slots, C):
     np.testing.assert_allclose(rgb.cpu().numpy(), want_rgb, atol=IMG_TOL_F32)
     np.testing.assert_allclose(r.feat.cpu().numpy(), want_feat, rtol=0, atol=2e-5)
     assert np.abs(want_feat).max() > 0.05
+
+
+@pytest.mark.parametrize("precision", [0, 1])
+@pytest.mark.parametrize("n,mu", [(1500, -3.2), (16000, -5.0)])
+def test_view_batch_is_bit_identical_to_single_frames(dev, precision, n, mu):
+    """mlpsp_render_frames: five views of one scene in one call (one evaluator launch per wave for all of them)
+    against the same views rendered one by one.  The second scene has many primitives per pixel, so the
+    small-group evaluator takes part of the batch's records."""
+    from mlp_splatting_b200 import synthetic as syn
+    from mlp_splatting_b200.engine import FrameRenderer, PackedScene, ViewBatchRenderer
+    W, H, V = 96, 72, 5
+    scene = syn.make_scene(n, 77, mu=mu)
+    cams = [syn.make_camera(W, H, azimuth_deg=72.0 * v + 10.0) for v in range(V)]
+    ps = PackedScene(scene["positions"], scene["log_scales"], scene["quats"], *[scene[k] for k in WKEYS], scene["freq"],
+                     scene["att"], device=dev, pack_f16=True)
+    ros = [_t(c["rays_o"], dev) for c in cams]
+    rds = [_t(c["rays_d"], dev) for c in cams]
+    single = FrameRenderer(W, H, device=dev)
+    want = []
+    for c, ro, rd in zip(cams, ros, rds):
+        rgb, alpha = single.render(ps, ro, rd, 5e-3, view=c["view"], proj=c["proj"], precision=precision)
+        want.append((rgb.clone(), alpha.clone()))
+    batch = ViewBatchRenderer(W, H, V, device=dev, max_records=20000)      # small on purpose: the scratch has to grow
+    for _ in range(2):                                                      # second call: the carried wave schedule
+        got = batch.render(ps, ros, rds, 5e-3, [c["view"] for c in cams], [c["proj"] for c in cams], precision=precision)
+        for (rgb, alpha), (rgb_w, alpha_w) in zip(got, want):
+            assert torch.equal(rgb, rgb_w) and torch.equal(alpha, alpha_w)
+    assert want[0][1].mean().item() > 0.005 and batch.last_stats.records > 0
+    assert not torch.equal(want[0][0], want[1][0])
+    with pytest.raises(ValueError, match="expected 5 views"):
+        batch.render(ps, ros[:2], rds[:2], 5e-3, [c["view"] for c in cams[:2]], [c["proj"] for c in cams[:2]])
