@@ -165,6 +165,8 @@ __device__ __forceinline__ void for_each_tile_flat(bool has, int x0, int x1, int
 
 __global__ void __launch_bounds__(256) k_bin_count(const float4* __restrict__ geom, int n, BinCam cam,
                                                    uint2* __restrict__ rect, int32_t* __restrict__ tile_cnt) {
+  chain_wait();
+  chain_release();
   __shared__ WarpRects s_wr[8];
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   int r[4] = {1, 0, 1, 0};
@@ -187,6 +189,8 @@ __global__ void __launch_bounds__(256) k_bin_scatter(int n, int ntx, const uint2
                                                      const float4* __restrict__ geom,
                                                      const TileFrame* __restrict__ frames, float K0,
                                                      const int32_t* __restrict__ status) {
+  chain_wait();
+  chain_release();
   __shared__ WarpRects s_wr[8];
   __shared__ WarpWhiten s_ww[PRETEST ? 8 : 1];
   static_assert(!PRETEST || PPW <= 8, "WarpWhiten holds eight maps per warp");
@@ -244,6 +248,8 @@ __global__ void k_bin_views(const float4* __restrict__ geom, int n, BinCams cams
 
 // ------------------------------------------------------------- multi-block exclusive scan ----
 __global__ void k_scan_partial(const int32_t* __restrict__ in, int64_t n, int32_t* __restrict__ blk) {
+  chain_wait();
+  chain_release();
   __shared__ int warp_sums[32];
   const int64_t base = (int64_t)blockIdx.x * kScanItems;
   int v = 0;
@@ -258,6 +264,8 @@ __global__ void k_scan_partial(const int32_t* __restrict__ in, int64_t n, int32_
 
 // single block: exclusive scan of blk[0,nblk) in place, grand total -> blk[nblk]
 __global__ void k_scan_top(int32_t* __restrict__ blk, int nblk) {
+  chain_wait();
+  chain_release();
   __shared__ int warp_sums[32];
   __shared__ int carry;
   if (threadIdx.x == 0) carry = 0;
@@ -279,6 +287,8 @@ __global__ void k_scan_top(int32_t* __restrict__ blk, int nblk) {
 // out[i] = exclusive prefix; out[n] = total.  Thread t of a block owns 4 consecutive items.
 __global__ void k_scan_final(const int32_t* __restrict__ in, int64_t n, const int32_t* __restrict__ blk,
                              int32_t* __restrict__ out) {
+  chain_wait();
+  chain_release();
   __shared__ int warp_sums[32];
   const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
   int v[4], s = 0;
@@ -295,6 +305,8 @@ __global__ void k_scan_final(const int32_t* __restrict__ in, int64_t n, const in
 __global__ void k_bin_finish(const int32_t* __restrict__ tile_cnt, int T, const int32_t* __restrict__ tile_offsets,
                              int capacity, int64_t max_pairs, int32_t* __restrict__ status,
                              int32_t* __restrict__ counters) {
+  chain_wait();
+  chain_release();
   int mx = 0;
   for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x) mx = max(mx, tile_cnt[t]);
   mx = __reduce_max_sync(0xffffffffu, mx);
@@ -335,6 +347,8 @@ __global__ void __launch_bounds__(THREADS) k_sort_ids(const int32_t* __restrict_
 // thread t owns the items [t * per, t * per + per).  One launch instead of three.
 constexpr int kScanSmallMax = 32768;
 __global__ void __launch_bounds__(1024) k_scan_small(const int32_t* __restrict__ in, int n, int32_t* __restrict__ out) {
+  chain_wait();
+  chain_release();
   __shared__ int warp_sums[32];
   const int per = (n + 1023) / 1024;
   const int b = min(n, (int)threadIdx.x * per), e = min(n, b + per);
@@ -352,12 +366,12 @@ int launch_scan_i32(const int32_t* in, int64_t n, int32_t* blk, int32_t* out, cu
   const int nblk = (int)((n + kScanItems - 1) / kScanItems);
   if (nblk == 0) return MLPSP_OK;
   if (n <= kScanSmallMax && in != out) {
-    k_scan_small<<<1, 1024, 0, st>>>(in, (int)n, out);
+    launch_chained(k_scan_small, dim3(1), dim3(1024), 0, st, in, (int)n, out);
     return cuda_check(cudaGetLastError(), "scan");
   }
-  k_scan_partial<<<nblk, 1024, 0, st>>>(in, n, blk);
-  k_scan_top<<<1, 1024, 0, st>>>(blk, nblk);
-  k_scan_final<<<nblk, 1024, 0, st>>>(in, n, blk, out);
+  launch_chained(k_scan_partial, dim3(nblk), dim3(1024), 0, st, in, n, blk);
+  launch_chained(k_scan_top, dim3(1), dim3(1024), 0, st, blk, nblk);
+  launch_chained(k_scan_final, dim3(nblk), dim3(1024), 0, st, in, n, blk, out);
   return cuda_check(cudaGetLastError(), "scan");
 }
 
@@ -394,18 +408,18 @@ int launch_bin(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratch& s, c
   const int n = sc->n;
   LaunchScope scope(kKBin, (n > 0 ? (order_lists ? 4 : 3) : 1) + scan_launches(T) + (pretest ? 1 : 0), st);
   if (pretest) launch_tile_frames(fr, s.tile_frame, st);
-  if (n > 0) k_bin_count<<<(n + 255) / 256, 256, 0, st>>>((const float4*)sc->geom, n, cam, s.rect, s.tile_cnt);
+  if (n > 0) launch_chained(k_bin_count, dim3((n + 255) / 256), dim3(256), 0, st, (const float4*)sc->geom, n, cam, s.rect, s.tile_cnt);
   int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
   if (rc) return rc;
-  k_bin_finish<<<std::min(64, (T + 255) / 256), 256, 0, st>>>(s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
+  launch_chained(k_bin_finish, dim3(std::min(64, (T + 255) / 256)), dim3(256), 0, st, s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
                                                               fr->max_pairs, fr->status, s.counters);
   if (n > 0) {
     if (pretest)
-      k_bin_scatter<true, 8><<<(n + 63) / 64, 256, 0, st>>>(n, cam.ntx, s.rect, fr->tile_offsets, fill, fr->tile_prims,
+      launch_chained(k_bin_scatter<true, 8>, dim3((n + 63) / 64), dim3(256), 0, st, n, cam.ntx, s.rect, fr->tile_offsets, fill, fr->tile_prims,
                                                            (const float4*)sc->geom, s.tile_frame,
                                                            (float)(-2.0 * log((double)fr->threshold)), fr->status);
     else
-      k_bin_scatter<false, 32><<<(n + 255) / 256, 256, 0, st>>>(n, cam.ntx, s.rect, fr->tile_offsets, fill, fr->tile_prims,
+      launch_chained(k_bin_scatter<false, 32>, dim3((n + 255) / 256), dim3(256), 0, st, n, cam.ntx, s.rect, fr->tile_offsets, fill, fr->tile_prims,
                                                             nullptr, nullptr, 0.f, fr->status);
     if (order_lists) k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);
   }
@@ -520,7 +534,7 @@ int launch_bin_raycone(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scrat
   if (n > 0) k_cone_bin<false><<<grid, 256, 0, st>>>((const float4*)sc->geom, n, cones, T, rm, s.tile_cnt, nullptr, nullptr, fr->status);
   int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
   if (rc) return rc;
-  k_bin_finish<<<std::min(64, (T + 255) / 256), 256, 0, st>>>(s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
+  launch_chained(k_bin_finish, dim3(std::min(64, (T + 255) / 256)), dim3(256), 0, st, s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
                                                               fr->max_pairs, fr->status, s.counters);
   if (n > 0) {
     k_cone_bin<true><<<grid, 256, 0, st>>>((const float4*)sc->geom, n, cones, T, rm, s.tile_fill, fr->tile_offsets,
@@ -571,7 +585,7 @@ int launch_bin_mosaic(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scratc
   pass(false);
   int rc = launch_scan_i32(s.tile_cnt, T, s.scan_blk, fr->tile_offsets, st);
   if (rc) return rc;
-  k_bin_finish<<<std::min(64, (T + 255) / 256), 256, 0, st>>>(s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
+  launch_chained(k_bin_finish, dim3(std::min(64, (T + 255) / 256)), dim3(256), 0, st, s.tile_cnt, T, fr->tile_offsets, fr->tile_capacity,
                                                               fr->max_pairs, fr->status, s.counters);
   pass(true);
   if (n > 0) k_sort_ids<256, kSortCap><<<T, 256, 0, st>>>(fr->tile_offsets, fr->tile_prims, fr->status);

@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdarg>
+#include <utility>
 #include "common.cuh"
 
 namespace mlpsp {
@@ -110,6 +111,30 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.tile_len = (int32_t*)take(4 * T);
   s.bytes = off;
   return s;
+}
+
+// Programmatic dependent launch.  The kernels of a frame form one dependent chain of some thirty launches; with the
+// launch attribute below the next kernel of the chain is set up and its CTAs take their places while the previous
+// kernel's last CTAs are still running, instead of after the previous grid has drained.  Every kernel launched this
+// way begins with chain_wait(), which returns once the previous grid has completed and its writes are visible (so
+// the stream's order is kept exactly), and then lets its own successor be set up (chain_release()).  On a kernel
+// launched without the attribute both are no-ops.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
 }
 
 // Kernel classes for the launch counter and the optional per-class device timing.

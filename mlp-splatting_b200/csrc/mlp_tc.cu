@@ -187,6 +187,8 @@ __global__ void __launch_bounds__(kMlpThreads, Net<H>::kCtas) k_mlp_tc(
     int32_t* __restrict__ status) {
   using N = Net<H>;
   static_assert(!KEEP || H == 32, "the record export keeps 32-bit ReLU masks");
+  chain_wait();       // the work list and the records come from the previous kernels of the frame
+  chain_release();
   extern __shared__ __align__(128) char smem[];
   char* s_a1 = smem + N::kOffA1;
   char* s_a2 = smem + N::kOffA2;
@@ -487,6 +489,8 @@ __global__ void __launch_bounds__(kMiniRows, MiniNet<H>::kCtas) k_mlp_tc_mini(
     float4* __restrict__ rec_out, int out_mode, int32_t* __restrict__ status) {
   using N = Net<H>;
   using M = MiniNet<H>;
+  chain_wait();
+  chain_release();
   extern __shared__ __align__(128) char smem[];
   char* s_a1 = smem + M::kOffA1;
   char* s_a2 = smem + M::kOffA2;
@@ -765,7 +769,7 @@ static int launch_one(const char* image, const mlpsp_scene* sc, const RecIn* rec
   static DeviceOnce attr_once;
   if (attr_once.first())
     MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc<KEEP, BF16, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, N::kSmemBytes));
-  k_mlp_tc<KEEP, BF16, H><<<grid, kMlpThreads, N::kSmemBytes, st>>>(image, sc->freq, sc->att, reinterpret_cast<const float4*>(rec_in),
+  launch_chained(k_mlp_tc<KEEP, BF16, H>, dim3(grid), dim3(kMlpThreads), N::kSmemBytes, st, image, sc->freq, sc->att, reinterpret_cast<const float4*>(rec_in),
                                                                    work, counters, rec_out, rec_ext, out_mode, status);
   return MLPSP_OK;
 }
@@ -777,7 +781,7 @@ static int launch_mini(const char* image, const mlpsp_scene* sc, const RecIn* re
   static DeviceOnce attr_once;
   if (attr_once.first())
     MLPSP_CUDA_OK(cudaFuncSetAttribute(k_mlp_tc_mini<BF16, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, M::kSmemBytes));
-  k_mlp_tc_mini<BF16, H><<<grid, kMiniRows, M::kSmemBytes, st>>>(image, sc->freq, sc->att, reinterpret_cast<const float4*>(rec_in),
+  launch_chained(k_mlp_tc_mini<BF16, H>, dim3(grid), dim3(kMiniRows), M::kSmemBytes, st, image, sc->freq, sc->att, reinterpret_cast<const float4*>(rec_in),
                                                                 work_small, counters, rec_out, out_mode, status);
   return MLPSP_OK;
 }

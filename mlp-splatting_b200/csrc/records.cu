@@ -37,6 +37,8 @@ __global__ void k_init_frame(int64_t P, float4* __restrict__ px_state, float2* _
                              int32_t* __restrict__ counters, const int32_t* __restrict__ tile_offsets,
                              int32_t* __restrict__ tile_len, int lists_refined, int n, int32_t* __restrict__ prim_cnt,
                              int32_t* __restrict__ prim_cursor) {
+  chain_wait();
+  chain_release();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < P) {
     px_state[i] = make_float4(0.f, 0.f, 0.f, 1.f);
@@ -67,6 +69,8 @@ __global__ void __launch_bounds__(256) k_hits(
     int hi, const float4* __restrict__ px_state, uint32_t* __restrict__ masks32, uint32_t* __restrict__ pair_base,
     int32_t* __restrict__ prim_cnt, int32_t* __restrict__ counters, int64_t max_records,
     int32_t* __restrict__ status, int32_t* __restrict__ reset_count) {
+  chain_wait();
+  chain_release();
   __shared__ uint32_t s_m[2][kWinMax];
   __shared__ int32_t s_pref[kWinMax];
   __shared__ int warp_sums[32];
@@ -204,6 +208,8 @@ __device__ __forceinline__ int small_items_of(int cnt, int split) {
 
 __global__ void k_prim_partial(const int32_t* __restrict__ prim_cnt, int n, int split, int32_t* __restrict__ blk,
                                const int32_t* __restrict__ status) {
+  chain_wait();
+  chain_release();
   __shared__ int warp_sums[32];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
@@ -228,6 +234,8 @@ __global__ void k_prim_final(const int32_t* __restrict__ prim_cnt, int32_t* __re
                              const int32_t* __restrict__ blk, int32_t* __restrict__ prim_off,
                              int4* __restrict__ work, int64_t max_work, int4* __restrict__ work_small, int64_t max_work_small,
                              int32_t* __restrict__ counters, int next_list, int32_t* __restrict__ status) {
+  chain_wait();
+  chain_release();
   __shared__ int warp_sums[32];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) {
     // after a record overflow, leave the size the wave asked for so the caller can grow its scratch
@@ -315,8 +323,8 @@ int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cu
   const int split = split_small && s.work_small ? 1 : 0;
   const int32_t* cnt = s.prim_cnt + (size_t)(wave & 1) * prim_cnt_stride(n);
   int32_t* cnt_next = s.prim_cnt + (size_t)((wave & 1) ^ 1) * prim_cnt_stride(n);
-  if (!solo) k_prim_partial<<<nblk, 1024, 0, st>>>(cnt, n, split, s.scan_blk, status);
-  k_prim_final<<<nblk, 1024, 0, st>>>(cnt, cnt_next, s.prim_cursor, n, split, solo ? nullptr : s.scan_blk, s.prim_off, s.work,
+  if (!solo) launch_chained(k_prim_partial, dim3(nblk), dim3(1024), 0, st, cnt, n, split, s.scan_blk, status);
+  launch_chained(k_prim_final, dim3(nblk), dim3(1024), 0, st, cnt, cnt_next, s.prim_cursor, n, split, solo ? nullptr : s.scan_blk, s.prim_off, s.work,
                                      s.max_work, s.work_small, s.max_work_small, s.counters, next_list, status);
   return cuda_check(cudaGetLastError(), "prim_scan");
 }
@@ -347,6 +355,8 @@ __global__ void __launch_bounds__(256) k_fill(
     const int32_t* __restrict__ prim_off, int32_t* __restrict__ prim_cursor, RecIn* __restrict__ rec_in,
     float* __restrict__ rec_t, float4* __restrict__ rec_gate, float beta, float tau, int exact_hits, int ref_arith,
     const int32_t* __restrict__ status) {
+  chain_wait();
+  chain_release();
   __shared__ uint32_t s_m[2][kWinMax];
   __shared__ int32_t s_pref[kWinMax + 1];   // slot of the pair's first record, relative to the tile-wave
   __shared__ int32_t s_q0[kWinMax];         // primitive-major position of the pair's first record
@@ -436,6 +446,8 @@ __global__ void __launch_bounds__(64) k_composite(
     float* __restrict__ rec_w, float* __restrict__ rec_tr, float bgr, float bgg, float bgb, int has_bg,
     int32_t* __restrict__ next_active,
     int32_t* __restrict__ next_count, int32_t* __restrict__ status) {
+  chain_wait();
+  chain_release();
   __shared__ int s_live[2];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
   const int n_active = *active_count;
@@ -911,7 +923,7 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
   {
     LaunchScope scope(kKMisc, 1, st);
     const int64_t span = std::max<int64_t>(std::max<int64_t>(P, T), n);
-    k_init_frame<<<(unsigned)((span + 255) / 256), 256, 0, st>>>(P, s.px_state, s.px_depth, fr->rgb, fr->alpha, fr->depth_t, bg[0], bg[1],
+    launch_chained(k_init_frame, dim3((unsigned)((span + 255) / 256)), dim3(256), 0, st, P, s.px_state, s.px_depth, fr->rgb, fr->alpha, fr->depth_t, bg[0], bg[1],
                                                                 bg[2], T, s.active[0], s.counters, fr->tile_offsets, s.tile_len,
                                                                 lists_refined ? 1 : 0, n, s.prim_cnt, s.prim_cursor);
   }
@@ -952,19 +964,19 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     const int32_t* act_n = s.counters + kCtrActive0 + cur;
     { LaunchScope scope(kKHits, 1, st);
     if (ref_arith)
-      k_hits<true><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+      launch_chained(k_hits<true>, dim3(grid_hits), dim3(256), 0, st, fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
                               s.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n), s.counters, fr->max_records, fr->status, nullptr);
     else
-      k_hits<false><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+      launch_chained(k_hits<false>, dim3(grid_hits), dim3(256), 0, st, fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, miss_bound2(fr->threshold), act, act_n, lo, hi, s.px_state,
                               s.masks32, s.pair_base,
                               s.prim_cnt + (size_t)(w & 1) * prim_cnt_stride(n), s.counters, fr->max_records, fr->status, nullptr); }
     int rc = launch_prim_scan(s, n, nxt, fr->status, st, split_small, w);
     if (rc) return rc;
     { LaunchScope scope(kKFill, 1, st);
-    k_fill<<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+    launch_chained(k_fill, dim3(grid_hits), dim3(256), 0, st, fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                               W, H, ntx, fr->threshold, act, act_n, lo, hi, s.masks32, s.pair_base, s.prim_off,
                               s.prim_cursor, s.rec_in, (want_t || per_pixel) ? s.rec_t : nullptr,
                               (want_feat && sc->feat_slots > 1) ? s.rec_gate : nullptr, sc->gate_beta,
@@ -986,13 +998,13 @@ int launch_render_sorted(const mlpsp_scene* sc, const mlpsp_frame* fr, const Scr
     }
     { LaunchScope scope(kKComposite, 1, st);
     if (want_stats)
-      k_composite<true><<<grid_comp, 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+      launch_chained(k_composite<true>, dim3(grid_comp), dim3(64), 0, st, pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
                                   fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
                                   keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,
                                   s.active[nxt], s.counters + kCtrActive0 + nxt, fr->status);
     else
-    k_composite<false><<<grid_comp, 64, 0, st>>>(pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
+    launch_chained(k_composite<false>, dim3(grid_comp), dim3(64), 0, st, pstats, fr->tile_offsets, s.tile_len, W, H, ntx, act, act_n, lo, hi, s.masks32, s.pair_base,
                                   s.rec_out, want_t ? s.rec_t : nullptr, s.px_state, s.px_depth, fr->rgb,
                                   fr->alpha, fr->depth_t, used32, want_feat ? s.rec_w : nullptr,
                                   keep ? s.rec_tr : nullptr, bg[0], bg[1], bg[2], has_bg,
@@ -1055,7 +1067,7 @@ int launch_render_batch(const mlpsp_scene* sc, const mlpsp_frame* frs, const Scr
       if (fr->bg_color) { bg[0] = fr->bg_color[0]; bg[1] = fr->bg_color[1]; bg[2] = fr->bg_color[2]; }
       const int nv = v == 0 ? n : 0;     // the per-primitive arrays are the first frame's
       const int64_t span = std::max<int64_t>(std::max<int64_t>(P, T), nv);
-      k_init_frame<<<(unsigned)((span + 255) / 256), 256, 0, st>>>(P, ss[v].px_state, ss[v].px_depth, fr->rgb, fr->alpha, nullptr, bg[0], bg[1],
+      launch_chained(k_init_frame, dim3((unsigned)((span + 255) / 256)), dim3(256), 0, st, P, ss[v].px_state, ss[v].px_depth, fr->rgb, fr->alpha, nullptr, bg[0], bg[1],
                                                                   bg[2], T, ss[v].active[0], ss[v].counters, fr->tile_offsets,
                                                                   ss[v].tile_len, lists_refined ? 1 : 0, nv, lead.prim_cnt, lead.prim_cursor);
     }
@@ -1090,12 +1102,12 @@ int launch_render_batch(const mlpsp_scene* sc, const mlpsp_frame* frs, const Scr
         const mlpsp_frame* fr = frs + v;
         const Scratch& s = ss[v];
         if (ref_arith)
-          k_hits<true><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len,
+          launch_chained(k_hits<true>, dim3(grid_hits), dim3(256), 0, st, fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len,
                                                   fr->sorted_prims, W, H, ntx, f0->threshold, miss_bound2(f0->threshold), s.active[cur],
                                                   s.counters + kCtrActive0 + cur, lo, hi, s.px_state, s.masks32, s.pair_base, cnt,
                                                   lead.counters, f0->max_records, f0->status, s.counters + kCtrActive0 + nxt);
         else
-          k_hits<false><<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len,
+          launch_chained(k_hits<false>, dim3(grid_hits), dim3(256), 0, st, fr->rays_o, fr->rays_d, (const float4*)sc->geom, n, fr->tile_offsets, s.tile_len,
                                                    fr->sorted_prims, W, H, ntx, f0->threshold, miss_bound2(f0->threshold), s.active[cur],
                                                    s.counters + kCtrActive0 + cur, lo, hi, s.px_state, s.masks32, s.pair_base, cnt,
                                                    lead.counters, f0->max_records, f0->status, s.counters + kCtrActive0 + nxt);
@@ -1108,7 +1120,7 @@ int launch_render_batch(const mlpsp_scene* sc, const mlpsp_frame* frs, const Scr
       for (int v = 0; v < V; ++v) {
         const mlpsp_frame* fr = frs + v;
         const Scratch& s = ss[v];
-        k_fill<<<grid_hits, 256, 0, st>>>(fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
+        launch_chained(k_fill, dim3(grid_hits), dim3(256), 0, st, fr->rays_o, fr->rays_d, (const float4*)sc->geom, fr->tile_offsets, s.tile_len, fr->sorted_prims,
                                           W, H, ntx, f0->threshold, s.active[cur], s.counters + kCtrActive0 + cur, lo, hi, s.masks32,
                                           s.pair_base, lead.prim_off, lead.prim_cursor, lead.rec_in, nullptr, nullptr, sc->gate_beta,
                                           sc->gate_tau, 0, ref_arith ? 1 : 0, f0->status);
@@ -1128,7 +1140,7 @@ int launch_render_batch(const mlpsp_scene* sc, const mlpsp_frame* frs, const Scr
         float bg[3] = {0.f, 0.f, 0.f};
         const int has_bg = fr->bg_color != nullptr;
         if (has_bg) { bg[0] = fr->bg_color[0]; bg[1] = fr->bg_color[1]; bg[2] = fr->bg_color[2]; }
-        k_composite<false><<<grid_comp, 64, 0, st>>>(no_stats, fr->tile_offsets, s.tile_len, W, H, ntx, s.active[cur],
+        launch_chained(k_composite<false>, dim3(grid_comp), dim3(64), 0, st, no_stats, fr->tile_offsets, s.tile_len, W, H, ntx, s.active[cur],
                                                      s.counters + kCtrActive0 + cur, lo, hi, s.masks32, s.pair_base, lead.rec_out, nullptr,
                                                      s.px_state, s.px_depth, fr->rgb, fr->alpha, nullptr, nullptr, nullptr, nullptr, bg[0],
                                                      bg[1], bg[2], has_bg, s.active[nxt], s.counters + kCtrActive0 + nxt, f0->status);
