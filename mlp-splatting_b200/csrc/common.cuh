@@ -375,6 +375,18 @@ __device__ __forceinline__ float softplus_fast(float x) {
   return __logf(1.0f + __expf(x));
 }
 
+// position of the (k+1)-th set bit of m (k >= 0 and fewer than popc(m)): five halvings by population count, the
+// same number of steps for every lane of a warp (the library's __fns walks the set bits one by one)
+__device__ __forceinline__ int nth_set_bit(uint32_t m, int k) {
+  int pos = 0, c;
+  c = __popc(m & 0xffffu); if (k >= c) { k -= c; pos += 16; m >>= 16; }
+  c = __popc(m & 0xffu);   if (k >= c) { k -= c; pos += 8;  m >>= 8; }
+  c = __popc(m & 0xfu);    if (k >= c) { k -= c; pos += 4;  m >>= 4; }
+  c = __popc(m & 0x3u);    if (k >= c) { k -= c; pos += 2;  m >>= 2; }
+  c = (int)(m & 1u);       if (k >= c) { pos += 1; }
+  return pos;
+}
+
 // ---- block-wide exclusive scan of one int per thread (blockDim.x <= 1024, multiple of 32) ----
 __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums /* [32] shared */, int& total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

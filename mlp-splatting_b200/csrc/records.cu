@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(256) k_fill(
     const int j = a, k = r - s_pref[a];
     const uint32_t m0 = s_m[0][j], m1 = s_m[1][j];
     const int c0 = __popc(m0);
-    const int px = (k < c0) ? (int)__fns(m0, 0, k + 1) : 32 + (int)__fns(m1, 0, k - c0 + 1);
+    const int px = (k < c0) ? nth_set_bit(m0, k) : 32 + nth_set_bit(m1, k - c0);
     const int p = sorted_prims[s + wlo + j];
     const V3 o = {s_ray[px][0], s_ray[px][1], s_ray[px][2]}, d = {s_ray[px][3], s_ray[px][4], s_ray[px][5]};
     Hit ht;
@@ -708,7 +708,7 @@ __global__ void __launch_bounds__(kFeatThreads) k_feature_composite(
       const int k = r - s_pref[a];
       const uint32_t u0 = s_u[0][a], u1 = s_u[1][a];
       const int cu0 = __popc(u0);
-      const int px = (k < cu0) ? (int)__fns(u0, 0, k + 1) : 32 + (int)__fns(u1, 0, k - cu0 + 1);
+      const int px = (k < cu0) ? nth_set_bit(u0, k) : 32 + nth_set_bit(u1, k - cu0);
       const uint32_t m0 = masks32[2 * (size_t)(s + a)], m1 = masks32[2 * (size_t)(s + a) + 1];
       const uint32_t slot = pair_base[s + a] +
                             (px < 32 ? __popc(m0 & ((1u << px) - 1u)) : __popc(m0) + __popc(m1 & ((1u << (px - 32)) - 1u)));

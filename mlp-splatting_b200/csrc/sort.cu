@@ -87,8 +87,13 @@ __device__ __forceinline__ void write_sorted(const unsigned long long* buf, cons
 constexpr int kTilesPerCta = 8;
 constexpr int kWarpSortMax = 512;
 
-// Short lists: one warp per tile, eight tiles per CTA.  Tiles with more than kWarpSortMax candidates
-// are appended to long_list for k_sort_long, so that each of them gets a CTA of its own.
+// end of k_sort_tiles: the grid may not complete before the grid it was launched behind has
+__device__ __forceinline__ void sort_tiles_done() {
+  if ((threadIdx.x & 31) == 0) chain_wait();
+}
+
+// Short lists: one warp per tile, eight tiles per CTA.  Tiles with more than kWarpSortMax candidates are left to
+// k_sort_long, which gives each of them a CTA of its own.
 template <bool IDSORT>
 __global__ void __launch_bounds__(256, 4) k_sort_tiles(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
@@ -96,7 +101,11 @@ __global__ void __launch_bounds__(256, 4) k_sort_tiles(
     int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode, int32_t* __restrict__ long_list,
     int32_t* __restrict__ long_count, const int32_t* __restrict__ list_len, int32_t* __restrict__ status) {
   __shared__ __align__(16) unsigned long long s_buf[kTilesPerCta * kWarpSortMax];
-  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
+  // Launched behind k_sort_long as its programmatic dependent WITHOUT waiting for it here: the two kernels sort
+  // disjoint tiles and run side by side.  What this kernel reads (the binned lists, the status word) was complete
+  // before k_sort_long's CTAs got past their own wait, and none of this kernel's CTAs starts before all of them
+  // have.  The wait is at the end instead (sort_tiles_done), so that this grid's completion implies the other's.
+  if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) { sort_tiles_done(); return; }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // warps draw tiles from a shared cursor (long_count[1]): list lengths differ by two orders of magnitude, and
   // a fixed deal would leave most warps of a CTA waiting for the one with the longest list
@@ -104,15 +113,12 @@ __global__ void __launch_bounds__(256, 4) k_sort_tiles(
   int tile = 0;
   if (lane == 0) tile = atomicAdd(long_count + 1, 1);
   tile = __shfl_sync(0xffffffffu, tile, 0);
-  if (tile >= T) return;
+  if (tile >= T) { sort_tiles_done(); return; }
   const int s = tile_offsets[tile];
   const int span = min(tile_offsets[tile + 1] - s, cap);
   const int len = list_len ? min(list_len[tile], span) : span;
   if (list_len && lane == 0 && len > 0) atomicAdd(status + MLPSP_ST_PAIRS_KEPT, len);
-  if (len > kWarpSortMax) {
-    if (lane == 0) long_list[atomicAdd(long_count, 1)] = tile;
-    continue;
-  }
+  if (len > kWarpSortMax) continue;      // k_sort_long's
   if (len <= 0) {
     for (int i = lane; i < span; i += 32) sorted_prims[s + i] = -1;
     continue;
@@ -136,22 +142,23 @@ __global__ void __launch_bounds__(256, 4) k_sort_tiles(
   }
 }
 
-// Long lists: one CTA per tile of long_list (grid-stride), the same bitonic network run by the whole CTA.
+// Long lists (more than kWarpSortMax candidates): one CTA per such tile, found by a grid-stride walk over all tiles,
+// the same bitonic network run by the whole CTA.  Launched before k_sort_tiles, which runs beside it.
 template <int THREADS, int CAP, bool IDSORT>
 __global__ void __launch_bounds__(THREADS) k_sort_long(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* tile_prims, int W, int H, int ts, int ntx,
-    int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode,
-    const int32_t* __restrict__ long_list, const int32_t* __restrict__ long_count,
+    int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode, int T,
     const int32_t* __restrict__ list_len, const int32_t* __restrict__ status) {
   __shared__ __align__(16) unsigned long long s_buf[CAP];
+  chain_wait();
+  chain_release();
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
-  const int count = *long_count;
-  for (int q = blockIdx.x; q < count; q += gridDim.x) {
-    const int tile = long_list[q];
+  for (int tile = blockIdx.x; tile < T; tile += gridDim.x) {
     const int s = tile_offsets[tile];
     const int span = min(tile_offsets[tile + 1] - s, CAP);
     const int len = list_len ? min(list_len[tile], span) : span;
+    if (len <= kWarpSortMax) continue;        // k_sort_tiles' (uniform over the CTA)
     const int tx = tile % ntx, ty = tile / ntx;
     const int cx = min(tx * ts + (ts >> 1), W - 1), cy = min(ty * ts + (ts >> 1), H - 1);
     const int64_t pc = (int64_t)cy * W + cx;
@@ -258,7 +265,7 @@ int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, c
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  MLPSP_CUDA_OK(cudaMemsetAsync(long_count, 0, 8, st));   // [0] long tiles, [1] tile cursor of k_sort_tiles
+  MLPSP_CUDA_OK(cudaMemsetAsync(long_count, 0, 8, st));   // [1] tile cursor of k_sort_tiles
   LaunchScope scope(kKSort, 2, st);
   const int grid = std::min((T + kTilesPerCta - 1) / kTilesPerCta, sms * 4);
   const int grid_long = std::min(T, sms * 6);
@@ -266,21 +273,17 @@ int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, c
   // the reference kernels' arithmetic exists for the tile-centre key only (sort_key 0)
   const int key_mode = fr->sort_key | ((fr->hit_arith == 1 && fr->sort_key == 0) ? 4 : 0);
   if (unordered_input) {
-    k_sort_tiles<true><<<grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
-                                             fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out,
-                                             key_mode, long_list, long_count, list_len, fr->status);
-    k_sort_long<256, kSortCap, true><<<grid_long, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
-                                                               fr->tile_prims, fr->width, fr->height, fr->tile, ntx,
-                                                               fr->sorted_prims, keys_out, key_mode, long_list,
-                                                               long_count, list_len, fr->status);
+    launch_chained(k_sort_long<256, kSortCap, true>, dim3(grid_long), dim3(256), 0, st, fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
+                   fr->tile_prims, fr->width, fr->height, fr->tile, ntx, fr->sorted_prims, keys_out, key_mode, T, list_len, fr->status);
+    launch_chained(k_sort_tiles<true>, dim3(grid), dim3(256), 0, st, fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
+                   fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out, key_mode, long_list, long_count,
+                   list_len, fr->status);
   } else {
-    k_sort_tiles<false><<<grid, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
-                                              fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out,
-                                              key_mode, long_list, long_count, list_len, fr->status);
-    k_sort_long<256, kSortCap, false><<<grid_long, 256, 0, st>>>(fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
-                                                                fr->tile_prims, fr->width, fr->height, fr->tile, ntx,
-                                                                fr->sorted_prims, keys_out, key_mode, long_list,
-                                                                long_count, list_len, fr->status);
+    launch_chained(k_sort_long<256, kSortCap, false>, dim3(grid_long), dim3(256), 0, st, fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets,
+                   fr->tile_prims, fr->width, fr->height, fr->tile, ntx, fr->sorted_prims, keys_out, key_mode, T, list_len, fr->status);
+    launch_chained(k_sort_tiles<false>, dim3(grid), dim3(256), 0, st, fr->rays_o, fr->rays_d, geom, sc->n, fr->tile_offsets, fr->tile_prims,
+                   fr->width, fr->height, fr->tile, ntx, T, kSortCap, fr->sorted_prims, keys_out, key_mode, long_list, long_count,
+                   list_len, fr->status);
   }
   return cuda_check(cudaGetLastError(), "sort_tiles");
 }
