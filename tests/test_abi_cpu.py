@@ -60,6 +60,27 @@ def test_null_segment_arrays_are_refused_before_any_launch():
     assert lib.mlpsp_records_reverse(None, None, None, None, None, None, None, None, 0, 0, 0, None, None, None, None, None) == -1
 
 
+def test_batch_and_precision_arguments_are_checked_before_any_launch():
+    """mlpsp_render_frames and the precision argument of mlpsp_grouped_weight_gradients: argument errors come from the
+    host-side checks."""
+    from mlp_splatting_b200 import _lib
+    lib = _lib.load()
+    sc = _lib.Scene()
+    frames = (_lib.Frame * 2)()
+    assert lib.mlpsp_render_frames(ctypes.byref(sc), frames, 0, None) == -1
+    assert b"need 1..64 frames" in lib.mlpsp_last_error()
+    assert lib.mlpsp_render_frames(ctypes.byref(sc), frames, 65, None) == -1
+    frames[0].width, frames[0].height, frames[0].tile, frames[0].threshold = 64, 48, 16, 0.5
+    assert lib.mlpsp_render_frames(ctypes.byref(sc), frames, 2, None) == -1
+    assert b"8x8 tiles" in lib.mlpsp_last_error()
+    sc.n, sc.hidden, sc.num_freq = 4, 32, 6
+    fake = 0x1000
+    sc.W1 = sc.b1 = sc.W2 = sc.b2 = sc.W3 = sc.freq = sc.att = fake
+    rc = lib.mlpsp_grouped_weight_gradients(ctypes.byref(sc), fake, fake, fake, None, fake, fake, fake, 3, 128, 7, 1.0,
+                                            fake, fake, fake, None)
+    assert rc == -1 and b"unsupported operand precision 7" in lib.mlpsp_last_error()
+
+
 def test_product_never_imports_oracle():
     pkg = os.path.join(ROOT, "mlp-splatting_b200")
     for dirpath, _d, files in os.walk(pkg):
