@@ -206,7 +206,10 @@ int64_t mlpsp_frame_scratch_bytes(int32_t n, int32_t width, int32_t height, int3
                                   int64_t max_pairs, int64_t max_records);
 
 /* Screen-space culling: cumodel.py:994-1070 (overlap predicate, tile-major lists, ascending id).
- * Writes frame->tile_offsets, frame->tile_prims; status words 1,2 and bits 2,8. */
+ * Writes frame->tile_offsets, frame->tile_prims; status words 1,2 and bits 2,8.
+ * frame->tile may be 8 or 16 here and in mlpsp_sort_tiles (the reference's tile_size = 16: culling, capacity and
+ * tile-centre order per 16x16 tile); every other entry point works on 8x8 tiles, and a 16x16 frame is rendered by
+ * giving each 8x8 tile the ordered list of its 16x16 tile (pre-sorted lists into mlpsp_render_sorted). */
 int mlpsp_bin_tiles(const mlpsp_scene* scene, const mlpsp_frame* frame, void* stream);
 
 /* Culling for mosaic frames whose tiles come from different views

@@ -70,10 +70,12 @@ __global__ void k_validate_lists(const int32_t* __restrict__ tile_offsets, const
   if (bad) atomicOr(status + MLPSP_ST_BITS, MLPSP_ST_BAD_IDS);
 }
 
-static int check_frame_common(const mlpsp_scene* sc, const mlpsp_frame* fr, const char* who) {
+// coarse_ok: the stage also takes 16x16 tiles (culling and per-tile ordering; the wave kernels are 8x8 only)
+static int check_frame_common(const mlpsp_scene* sc, const mlpsp_frame* fr, const char* who, bool coarse_ok = false) {
   MLPSP_REQUIRE(sc && fr, MLPSP_E_ARG, "%s: null scene or frame", who);
   MLPSP_REQUIRE(fr->width > 0 && fr->height > 0, MLPSP_E_ARG, "%s: image and tile dimensions must be positive", who);
-  MLPSP_REQUIRE(fr->tile == 8, MLPSP_E_ARG, "%s: only 8x8 tiles are supported", who);
+  MLPSP_REQUIRE(fr->tile == 8 || (coarse_ok && fr->tile == 16), MLPSP_E_ARG,
+                coarse_ok ? "%s: tiles must be 8x8 or 16x16" : "%s: only 8x8 tiles are supported", who);
   MLPSP_REQUIRE((int64_t)fr->width * fr->height <= 2147483647LL, MLPSP_E_LIMIT,
                 "%s: image dimensions exceed int32 pixel indexing", who);
   MLPSP_REQUIRE(fr->threshold > 0.f && fr->threshold < 1.f, MLPSP_E_ARG, "%s: threshold must be in (0,1)", who);
@@ -177,7 +179,7 @@ extern "C" int mlpsp_validate_tile_lists(const int32_t* tile_offsets, const int3
 }
 
 extern "C" int mlpsp_bin_tiles(const mlpsp_scene* sc, const mlpsp_frame* fr, void* stream) {
-  int rc = check_frame_common(sc, fr, "mlpsp_bin_tiles");
+  int rc = check_frame_common(sc, fr, "mlpsp_bin_tiles", /*coarse_ok=*/true);
   if (rc) return rc;
   MLPSP_REQUIRE(fr->view && fr->proj, MLPSP_E_ARG, "mlpsp_bin_tiles: view/proj matrices missing");
   Scratch s;
@@ -209,7 +211,7 @@ extern "C" int mlpsp_bin_tiles_raycone(const mlpsp_scene* sc, const mlpsp_frame*
 }
 
 extern "C" int mlpsp_sort_tiles(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, void* stream) {
-  int rc = check_frame_common(sc, fr, "mlpsp_sort_tiles");
+  int rc = check_frame_common(sc, fr, "mlpsp_sort_tiles", /*coarse_ok=*/true);
   if (rc) return rc;
   MLPSP_REQUIRE(fr->rays_o && fr->rays_d, MLPSP_E_ARG, "mlpsp_sort_tiles: rays missing");
   Scratch s;

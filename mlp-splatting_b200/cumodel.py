@@ -7,7 +7,8 @@ no-grad helpers `render_feature_map`, `render_rgb_alpha_no_grad`, `render_rgb_t_
 no autograd (training is out of scope) and no CPU path.
 
 Differences a caller can see:
-  * tile_size must be 8 (the reference also accepts 16 for its scalar kernels);
+  * tile_size 16 (which the reference takes for its scalar kernels) culls and orders per 16x16 tile and renders on
+    8x8 tiles that inherit those lists: same candidates and order per pixel; mosaic culling stays 8x8;
   * `precision` ("fp16" default, or "fp32") selects the evaluator: fp16 matches the reference's
     tensor-core forward (scannet/cuda/rgb_wmma.cuh), fp32 its scalar forward;
   * culling, sorting and rendering are one asynchronous launch sequence followed by one status
@@ -114,8 +115,6 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
             raise ValueError("tile_size must be a positive integer.")
         if int(tile_size) not in (8, 16):
             raise ValueError("NeuralPrimitiveSceneTileCUDA supports tile_size in {8, 16}.")
-        if int(tile_size) != 8:
-            raise ValueError("this build renders 8x8 tiles only")
         if initial_positions is not None:
             raise ValueError("octree initialisation from a point cloud belongs to training and is not part of this build")
         if precision not in ("fp16", "bf16", "fp32"):
@@ -236,7 +235,10 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
                 raise ValueError("per_pixel ordering renders rgb, alpha and the feature map only here; use "
                                  "MLPSP_TILE_ORDER=tilecenter for depth and contribution statistics")
             sort_key = L.ORDER_PER_PIXEL
-        T = ((W + 7) // 8) * ((H + 7) // 8)
+        ts = int(self.tile_size)
+        if ts == 16 and (sort_key == L.ORDER_PER_PIXEL or getattr(self, "camera_mode", "legacy-centered") == "colmap-native"):
+            raise ValueError("tile_size = 16 renders the tile-centre order with screen-space or external culling only")
+        T = ((W + ts - 1) // ts) * ((H + ts - 1) // ts)
         lists = None
         if getattr(self, "camera_mode", "legacy-centered") == "colmap-native":
             if (culled_prim_indices is not None) or (tile_offsets is not None):
@@ -270,10 +272,11 @@ class NeuralPrimitiveSceneTileCUDA(nn.Module):
             prec = L.PRECISION_F16
         elif self.precision == "bf16" and scene.has_bf16:
             prec = L.PRECISION_BF16
-        rgb, alpha = r.render(scene, ray_o.detach().float().contiguous(), ray_d.detach().float().contiguous(),
-                              float(score_threshold), view=view, proj=proj, precision=prec, bg=bg,
-                              want_depth=want_depth, tile_lists=lists, path_name=path_name, want_feat=want_feat,
-                              sort_key=sort_key, prim_stats=stats)
+        render = r.render_tile16 if ts == 16 else r.render      # 16x16: culling and order per 16x16 tile, as the reference
+        rgb, alpha = render(scene, ray_o.detach().float().contiguous(), ray_d.detach().float().contiguous(),
+                            float(score_threshold), view=view, proj=proj, precision=prec, bg=bg,
+                            want_depth=want_depth, tile_lists=lists, path_name=path_name, want_feat=want_feat,
+                            sort_key=sort_key, prim_stats=stats)
         return r, rgb, alpha
 
     @torch.no_grad()

@@ -244,12 +244,17 @@ class FrameRenderer:
     """
 
     def __init__(self, width, height, device="cuda", tile_capacity=TILE_CAPACITY, max_pairs=None,
-                 max_records=16_000_000):
+                 max_records=16_000_000, tile=TILE):
+        """tile = 16 makes a renderer for the culling and ordering stages only (bin, sort): the wave kernels work on
+        8x8 tiles, and render_tile16 of an 8x8 renderer hands such a renderer's lists down to them."""
+        if int(tile) not in (8, 16):
+            raise ValueError("tiles are 8x8 or 16x16")
         self.lib = L.load()
         self.device = torch.device(device)
+        self.tile = int(tile)
         self.W, self.H = int(width), int(height)
         self.P = self.W * self.H
-        self.T = ((self.W + TILE - 1) // TILE) * ((self.H + TILE - 1) // TILE)
+        self.T = ((self.W + self.tile - 1) // self.tile) * ((self.H + self.tile - 1) // self.tile)
         self.capacity = int(tile_capacity)
         self.max_pairs = int(max_pairs) if max_pairs is not None else min(self.T * self.capacity, 2**31 - 2)
         self.max_records = int(max_records)
@@ -278,7 +283,7 @@ class FrameRenderer:
     def _ensure_scratch(self, n):
         key = (n, self.max_pairs, self.max_records)
         if self._scratch_key != key:
-            nbytes = int(self.lib.mlpsp_frame_scratch_bytes(n, self.W, self.H, TILE, self.max_pairs, self.max_records))
+            nbytes = int(self.lib.mlpsp_frame_scratch_bytes(n, self.W, self.H, self.tile, self.max_pairs, self.max_records))
             if nbytes < 0:
                 raise RuntimeError("mlpsp_frame_scratch_bytes rejected the frame shape")
             self.scratch = None
@@ -291,7 +296,7 @@ class FrameRenderer:
                tile_pretest=True, prim_stats=None, tail_hint=False, hit_arith=0) -> L.Frame:
         f = L.Frame()
         f.rays_o, f.rays_d = L.ptr(rays_o), L.ptr(rays_d_unit)
-        f.width, f.height, f.tile, f.threshold = self.W, self.H, TILE, float(thr)
+        f.width, f.height, f.tile, f.threshold = self.W, self.H, self.tile, float(thr)
         f.tile_capacity, f.precision = self.capacity, int(precision)
         if view is not None:
             self._view[:] = np.asarray(view, dtype=np.float32).reshape(16)
@@ -383,8 +388,10 @@ class FrameRenderer:
     def render(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, precision=None,
                bg=None, want_depth=False, want_mask_used=False, waves=None, tile_lists=None,
                rays_normalized=False, check=True, path_name="render_tiles_forward_tilecenter", want_feat=False,
-               keep_records=False, sort_key=0, tile_rows=None, tile_pretest=True, prim_stats=None, hit_arith=0):
-        """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling).
+               keep_records=False, sort_key=0, tile_rows=None, tile_pretest=True, prim_stats=None, hit_arith=0,
+               presorted=False):
+        """One frame.  tile_lists=(culled_prim_indices, tile_offsets) replaces binning (external culling);
+        presorted=True says those lists are already in compositing order (no per-tile sort).
 
         tile_pretest=False keeps every binned candidate in the lists the wave kernels walk (same image).
         prim_stats=(gt_rgb [P,3] f32, sum_w, max_w [n] f32, hits [n] i32, sum_werr [n] f32, contrib [n] i32): device
@@ -416,6 +423,8 @@ class FrameRenderer:
                         self.sorted_prims = torch.empty(max(m, 1), device=d, dtype=torch.int32)
                         self.mask_used = None
                     self.tile_prims[:m].copy_(prims)
+                    if presorted:
+                        self.sorted_prims[:m].copy_(prims)
                     self.tile_offsets.copy_(offs)
                     L.check(lib.mlpsp_validate_tile_lists(L.ptr(self.tile_offsets), L.ptr(self.tile_prims), self.T, m,
                                                           self.capacity, scene.n, L.ptr(self.status), st),
@@ -428,7 +437,8 @@ class FrameRenderer:
                 if tile_lists is None:
                     L.check(lib.mlpsp_render_frame(C.byref(scene.c), C.byref(f), st), "mlpsp_render_frame")
                 else:
-                    L.check(lib.mlpsp_sort_tiles(C.byref(scene.c), C.byref(f), None, st), "mlpsp_sort_tiles")
+                    if not presorted:
+                        L.check(lib.mlpsp_sort_tiles(C.byref(scene.c), C.byref(f), None, st), "mlpsp_sort_tiles")
                     L.check(lib.mlpsp_render_sorted(C.byref(scene.c), C.byref(f), st), "mlpsp_render_sorted")
                 if not check:
                     return self.rgb, self.alpha
@@ -454,6 +464,71 @@ class FrameRenderer:
                     continue
                 return self.rgb, self.alpha
             raise RenderError(f"{path_name}: scratch kept overflowing after 8 attempts")
+
+    def tile16_lists(self, scene: PackedScene, rays_o, rays_d_unit, threshold, view, proj, sort_key=0,
+                     path_name="render_tiles_forward_tilecenter", lists16=None):
+        """Culling and per-tile ordering on 16x16 tiles (the reference's tile_size = 16: np_tile_kernels.cu:483-518 keys
+        on the centre ray of the 16x16 tile, candidate capacity per 16x16 tile), handed down to the 8x8 tiles the wave
+        kernels work on: every 8x8 tile receives the ordered list of the 16x16 tile that contains it, so each pixel
+        walks the same candidates in the same order as in the reference's 16x16 kernel.
+        lists16 = (culled_prim_indices, tile_offsets) on the 16x16 grid replaces the culling (external lists).
+        Returns (prims [M8] int32, tile_offsets [T8+1] int32) for render(..., tile_lists=..., presorted=True)."""
+        if self.tile != 8:
+            raise ValueError("tile16_lists belongs to the 8x8 renderer")
+        d = self.device
+        c = getattr(self, "_coarse", None)
+        if c is None:
+            c = self._coarse = FrameRenderer(self.W, self.H, device=d, tile_capacity=self.capacity, max_records=0, tile=16)
+            ntx8, nty8 = (self.W + 7) // 8, (self.H + 7) // 8
+            ntx16 = (self.W + 15) // 16
+            ty8, tx8 = torch.meshgrid(torch.arange(nty8, device=d), torch.arange(ntx8, device=d), indexing="ij")
+            self._parent16 = ((ty8 // 2) * ntx16 + tx8 // 2).reshape(-1)
+        if lists16 is None:
+            prims16, offs16 = c.bin(scene, view, proj, threshold, check=False)
+            bits, stats = c._read_status()
+        else:
+            prims16, offs16 = lists16
+            m = int(prims16.numel())
+            if offs16.numel() != c.T + 1:
+                raise ValueError(f"tile_offsets length mismatch: got {offs16.numel()}, expected {c.T + 1}")
+            if m > c.max_pairs:
+                c.max_pairs = m
+                c.tile_prims = torch.empty(max(m, 1), device=d, dtype=torch.int32)
+                c.sorted_prims = torch.empty(max(m, 1), device=d, dtype=torch.int32)
+            c.tile_prims[:m].copy_(prims16)
+            c.tile_offsets.copy_(offs16)
+            with torch.cuda.device(d):
+                st = _stream_ptr(d)
+                L.check(self.lib.mlpsp_status_reset(L.ptr(c.status), st), "mlpsp_status_reset")
+                L.check(self.lib.mlpsp_validate_tile_lists(L.ptr(c.tile_offsets), L.ptr(c.tile_prims), c.T, m, c.capacity,
+                                                           scene.n, L.ptr(c.status), st), "mlpsp_validate_tile_lists")
+            bits, stats = c._read_status()
+            prims16, offs16 = c.tile_prims[:m], c.tile_offsets
+        if bits & (L.BIT_TILE_CAPACITY | L.BIT_BAD_IDS | L.BIT_BAD_OFFSETS):
+            raise_for_status(bits, stats.max_tile_len, self.capacity, path_name)
+        pairs16 = int(prims16.numel())
+        sorted16 = c.sort(scene, rays_o, rays_d_unit, pairs16, sort_key=sort_key)
+        offs16 = offs16.to(torch.int64)
+        len8 = (offs16[1:] - offs16[:-1])[self._parent16]
+        offs8 = torch.zeros(self.T + 1, device=d, dtype=torch.int64)
+        torch.cumsum(len8, 0, out=offs8[1:])
+        total8 = int(offs8[-1])
+        if total8 >= 2**31:
+            raise RenderError(f"{path_name}: candidate list is too large for int32 offsets")
+        tile8 = torch.repeat_interleave(torch.arange(self.T, device=d), len8, output_size=total8)
+        src = offs16[self._parent16[tile8]] + (torch.arange(total8, device=d) - offs8[tile8])
+        return sorted16[src].contiguous(), offs8.to(torch.int32)
+
+    def render_tile16(self, scene: PackedScene, rays_o, rays_d, threshold, view=None, proj=None, rays_normalized=False,
+                      sort_key=0, path_name="render_tiles_forward_tilecenter", tile_lists=None, **kw):
+        """One frame with the reference's tile_size = 16 semantics (see tile16_lists); other arguments as render(),
+        tile_lists on the 16x16 grid."""
+        with torch.cuda.device(self.device):
+            rd = rays_d if rays_normalized else normalize_rows(rays_d)
+            prims8, offs8 = self.tile16_lists(scene, rays_o, rd, threshold, view, proj, sort_key=sort_key, path_name=path_name,
+                                              lists16=tile_lists)
+            return self.render(scene, rays_o, rd, threshold, tile_lists=(prims8, offs8), presorted=True, rays_normalized=True,
+                               sort_key=sort_key, path_name=path_name, **kw)
 
     def render_records(self, scene: PackedScene, rays_o, rays_d, threshold, max_hits=512, **kw):
         """Render and return the reference's record list [rgb, alpha, ids, x6, raw, masks, gates, offsets]

@@ -891,3 +891,44 @@ def test_view_batch_is_bit_identical_to_single_frames(dev, precision, n, mu):
     assert not torch.equal(want[0][0], want[1][0])
     with pytest.raises(ValueError, match="expected 5 views"):
         batch.render(ps, ros[:2], rds[:2], 5e-3, [c["view"] for c in cams[:2]], [c["proj"] for c in cams[:2]])
+
+
+@pytest.mark.parametrize("name", ["tiny", "ragged"])
+def test_tile16_matches_oracle(dev, name):
+    """tile_size = 16 of the reference (culling and tile-centre order per 16x16 tile): the coarse lists are bit-equal
+    to the CPU restatement's at tile 16, and the frame rendered on 8x8 tiles that inherit them equals its 16x16 frame;
+    through the renderer and through the module class (screen-space culling and external 16x16 lists)."""
+    from mlp_splatting_b200.cumodel import NeuralPrimitiveSceneTileCUDA
+    from mlp_splatting_b200.engine import normalize_rows
+    scene, cam = small_case(**CASES[name])
+    f16 = oracle_frame(scene, cam, 5e-3, precision=0, tile=16, want_masks=False)
+    f8 = oracle_frame(scene, cam, 5e-3, precision=0, want_masks=False)
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    ro, rd = _t(cam["rays_o"], dev), _t(cam["rays_d"], dev)
+    prims8, offs8 = r.tile16_lists(ps, ro, normalize_rows(rd), 5e-3, cam["view"], cam["proj"])
+    c = r._coarse
+    np.testing.assert_array_equal(c.tile_offsets.cpu().numpy(), f16["tile_offsets"])
+    M = int(f16["tile_offsets"][-1])
+    np.testing.assert_array_equal(c.sorted_prims[:M].cpu().numpy(), f16["sorted_prims"])
+    # every 8x8 tile holds its 16x16 tile's list
+    ntx8, ntx16 = (cam["W"] + 7) // 8, (cam["W"] + 15) // 16
+    o8, o16 = offs8.cpu().numpy(), f16["tile_offsets"]
+    for t8 in (0, ntx8 - 1, len(o8) // 2, len(o8) - 2):
+        t16 = (t8 // ntx8 // 2) * ntx16 + (t8 % ntx8) // 2
+        np.testing.assert_array_equal(prims8[o8[t8]:o8[t8 + 1]].cpu().numpy(), f16["sorted_prims"][o16[t16]:o16[t16 + 1]])
+    rgb, alpha = r.render_tile16(ps, ro, rd, 5e-3, view=cam["view"], proj=cam["proj"], precision=0)
+    np.testing.assert_allclose(rgb.cpu().numpy(), f16["render"].rgb, atol=IMG_TOL_F32)
+    np.testing.assert_allclose(alpha.cpu().numpy()[:, 0], f16["render"].alpha, atol=IMG_TOL_F32)
+    assert np.abs(f16["render"].rgb - f8["render"].rgb).max() > 1e-4      # the 16x16 order is a different image
+    m = NeuralPrimitiveSceneTileCUDA(num_primitives=scene["positions"].shape[0], precision="fp32", tile_size=16).to(dev)
+    with torch.no_grad():
+        for k in ("positions", "log_scales", "quats") + WKEYS:
+            getattr(m, k).copy_(_t(scene[k], dev))
+    m.set_image_size(cam["W"], cam["H"])
+    rgb_m = m(ro, rd, score_threshold=5e-3, view_matrix=_t(cam["view"], dev), proj_matrix=_t(cam["proj"], dev))
+    # (the module computes its own attenuation table, so its frames agree with the renderer's to rounding, not bitwise)
+    np.testing.assert_allclose(rgb_m.cpu().numpy(), f16["render"].rgb, atol=IMG_TOL_F32)
+    rgb_x = m(ro, rd, score_threshold=5e-3, culled_prim_indices=_t(f16["tile_prims"], dev), tile_offsets=_t(f16["tile_offsets"], dev))
+    assert torch.equal(rgb_x, rgb_m)
+    with pytest.raises(ValueError, match="tile_offsets length mismatch"):
+        m(ro, rd, score_threshold=5e-3, culled_prim_indices=_t(f8["tile_prims"], dev), tile_offsets=_t(f8["tile_offsets"], dev))

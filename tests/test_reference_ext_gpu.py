@@ -36,6 +36,23 @@ def _inputs(scene, cam, f, dev):
     return base
 
 
+@pytest.mark.parametrize("name", ["tiny", "ragged"])
+def test_tile16_forward_matches_reference_kernel(ref, name):
+    """render_tiles_forward_tilecenter with 16x16 tiles (the reference's tile_size = 16, scalar kernels) on lists
+    culled per 16x16 tile, against render_tile16: 8x8 tiles that inherit the 16x16 tile's ordered list."""
+    dev = torch.device("cuda", 0)
+    scene, cam = small_case(**CASES[name])
+    f = oracle_frame(scene, cam, 5e-3, precision=0, tile=16, want_masks=False)
+    x = _inputs(scene, cam, f, dev)
+    rgb_r, alpha_r = ref.render_tiles_forward_tilecenter(*x, cam["W"], cam["H"], 16, 16, 5e-3)
+    ps, r = _packed(scene, dev), _renderer(cam, dev)
+    rgb, alpha = r.render_tile16(ps, x[0], x[1], 5e-3, precision=0, tile_lists=(x[5], x[6]), rays_normalized=True)
+    d_rgb = (rgb - rgb_r).abs().max().item()
+    d_a = (alpha - alpha_r).abs().max().item()
+    assert d_rgb <= 1e-4 and d_a <= 1e-4, (d_rgb, d_a)
+    assert alpha_r.mean().item() > 0.05
+
+
 @pytest.mark.parametrize("name", ["tiny", "ragged", "dense"])
 def test_fp32_forward_matches_reference_kernel(ref, name):
     """render_tiles_forward_tilecenter (np_tile_kernels.cu:5225) vs the FP32 path of this library."""
