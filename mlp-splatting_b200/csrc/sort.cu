@@ -2,7 +2,7 @@
 // (scannet/cuda/np_tile_kernels.cu:483-518), stable ascending order (1914-1990).
 // Keys are positive floats (or the 1e30 sentinel), so their bit patterns order like the values and the
 // sort runs on the raw bits: a bitonic network in shared memory over the 64-bit composite (key bits,
-// tie-break); lists of up to 512 candidates are sorted by one warp (eight tiles per CTA), longer
+// tie-break); lists of up to 256 candidates are sorted by one warp (eight tiles per CTA), longer
 // lists by a whole CTA.
 #include "frame.cuh"
 
@@ -85,7 +85,7 @@ __device__ __forceinline__ void write_sorted(const unsigned long long* buf, cons
 }
 
 constexpr int kTilesPerCta = 8;
-constexpr int kWarpSortMax = 512;
+constexpr int kWarpSortMax = 256;
 
 // end of k_sort_tiles: the grid may not complete before the grid it was launched behind has
 __device__ __forceinline__ void sort_tiles_done() {
@@ -95,7 +95,7 @@ __device__ __forceinline__ void sort_tiles_done() {
 // Short lists: one warp per tile, eight tiles per CTA.  Tiles with more than kWarpSortMax candidates are left to
 // k_sort_long, which gives each of them a CTA of its own.
 template <bool IDSORT>
-__global__ void __launch_bounds__(256, 4) k_sort_tiles(
+__global__ void __launch_bounds__(256, 6) k_sort_tiles(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* tile_prims, int W, int H, int ts, int ntx, int T, int cap,
     int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode, int32_t* __restrict__ long_list,
@@ -128,15 +128,14 @@ __global__ void __launch_bounds__(256, 4) k_sort_tiles(
   const int64_t pc = (int64_t)cy * W + cx;
   const V3 o = load3(rays_o, pc), d = load3(rays_d, pc);
   unsigned long long* buf = s_buf + warp * kWarpSortMax;
-  const int N = len <= 32 ? 32 : (len <= 64 ? 64 : (len <= 128 ? 128 : (len <= 256 ? 256 : 512)));
+  const int N = len <= 32 ? 32 : (len <= 64 ? 64 : (len <= 128 ? 128 : 256));
   for (int i = lane; i < N; i += 32)
     buf[i] = (i < len) ? make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode) : ~0ull;
   __syncwarp();
   if (N == 32) warp_bitonic<unsigned long long, 32>(buf);
   else if (N == 64) warp_bitonic<unsigned long long, 64>(buf);
   else if (N == 128) warp_bitonic<unsigned long long, 128>(buf);
-  else if (N == 256) warp_bitonic<unsigned long long, 256>(buf);
-  else warp_bitonic<unsigned long long, 512>(buf);
+  else warp_bitonic<unsigned long long, 256>(buf);
   write_sorted<IDSORT>(buf, tile_prims, sorted_prims, keys_out, s, len, span, lane, 32);
   __syncwarp();   // the slice is reused by this warp's next tile
   }
@@ -163,11 +162,12 @@ __global__ void __launch_bounds__(THREADS) k_sort_long(
     const int cx = min(tx * ts + (ts >> 1), W - 1), cy = min(ty * ts + (ts >> 1), H - 1);
     const int64_t pc = (int64_t)cy * W + cx;
     const V3 o = load3(rays_o, pc), d = load3(rays_d, pc);
-    const int N = len <= CAP / 2 ? CAP / 2 : CAP;
+    const int N = len <= CAP / 4 ? CAP / 4 : (len <= CAP / 2 ? CAP / 2 : CAP);
     for (int i = threadIdx.x; i < N; i += THREADS)
       s_buf[i] = (i < len) ? make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode) : ~0ull;
     __syncthreads();
-    if (N == CAP / 2) warp_bitonic<unsigned long long, CAP / 2, THREADS>(s_buf);
+    if (N == CAP / 4) warp_bitonic<unsigned long long, CAP / 4, THREADS>(s_buf);
+    else if (N == CAP / 2) warp_bitonic<unsigned long long, CAP / 2, THREADS>(s_buf);
     else warp_bitonic<unsigned long long, CAP, THREADS>(s_buf);
     write_sorted<IDSORT>(s_buf, tile_prims, sorted_prims, keys_out, s, len, span, threadIdx.x, THREADS);
     __syncthreads();
@@ -267,7 +267,7 @@ int launch_sort(const mlpsp_scene* sc, const mlpsp_frame* fr, float* keys_out, c
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   MLPSP_CUDA_OK(cudaMemsetAsync(long_count, 0, 8, st));   // [1] tile cursor of k_sort_tiles
   LaunchScope scope(kKSort, 2, st);
-  const int grid = std::min((T + kTilesPerCta - 1) / kTilesPerCta, sms * 4);
+  const int grid = std::min((T + kTilesPerCta - 1) / kTilesPerCta, sms * 6);
   const int grid_long = std::min(T, sms * 6);
   const float4* geom = (const float4*)sc->geom;
   // the reference kernels' arithmetic exists for the tile-centre key only (sort_key 0)
