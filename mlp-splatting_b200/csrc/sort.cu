@@ -1,9 +1,9 @@
 // Per-tile depth sort: key = t* of the tile-centre ray against each candidate
 // (scannet/cuda/np_tile_kernels.cu:483-518), stable ascending order (1914-1990).
 // Keys are positive floats (or the 1e30 sentinel), so their bit patterns order like the values and the
-// sort runs on the raw bits: a bitonic network in shared memory over the 64-bit composite (key bits,
-// tie-break); lists of up to 256 candidates are sorted by one warp (eight tiles per CTA), longer
-// lists by a whole CTA.
+// sort runs on the raw bits: a bitonic network over the 64-bit composite (key bits, tie-break); lists of up
+// to 256 candidates are sorted by one warp in registers (eight tiles per CTA), longer lists by a whole CTA in
+// shared memory.
 #include "frame.cuh"
 
 namespace mlpsp {
@@ -87,6 +87,74 @@ __device__ __forceinline__ void write_sorted(const unsigned long long* buf, cons
 constexpr int kTilesPerCta = 8;
 constexpr int kWarpSortMax = 256;
 
+// ---- warp-level bitonic sort in registers: lane l holds the elements r * 32 + l, r < PER ----
+// A compare-exchange at distance j >= 32 pairs two registers of the same lane; at distance j < 32 it pairs the same
+// register of the lanes l and l ^ j, one shuffle each way.  Ascending where the element index has bit k clear.
+// No shared memory and no barrier: the stages of a tile follow one another at the latency of a shuffle.
+__device__ __forceinline__ unsigned long long shfl_xor_u64(unsigned long long v, int j) {
+  const uint32_t lo = __shfl_xor_sync(0xffffffffu, (uint32_t)v, j);
+  const uint32_t hi = __shfl_xor_sync(0xffffffffu, (uint32_t)(v >> 32), j);
+  return ((unsigned long long)hi << 32) | lo;
+}
+
+template <int PER>
+__device__ __forceinline__ void warp_bitonic_regs(unsigned long long (&v)[PER], int lane) {
+  constexpr int N = PER * 32;
+#pragma unroll
+  for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j >= 32) {
+        const int jr = j >> 5;
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+          if ((r & jr) == 0) {
+            const bool up = ((r * 32) & k) == 0;          // k >= 64 here: the lane bits do not reach it
+            const unsigned long long a = v[r], b = v[r | jr];
+            const bool swap = up ? (a > b) : (a < b);
+            v[r] = swap ? b : a;
+            v[r | jr] = swap ? a : b;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+          const unsigned long long a = v[r];
+          const unsigned long long b = shfl_xor_u64(a, j);
+          const bool up = ((r * 32 + lane) & k) == 0;
+          const bool lower = (lane & j) == 0;
+          const bool keep_min = lower == up;
+          const unsigned long long mn = a < b ? a : b, mx = a < b ? b : a;
+          v[r] = keep_min ? mn : mx;
+        }
+      }
+    }
+  }
+}
+
+// One tile's list (len <= PER * 32) sorted by one warp in registers and written out.
+template <int PER, bool FROM_SCATTER>
+__device__ __forceinline__ void sort_tile_in_registers(const float4* __restrict__ geom, int n, const int32_t* tile_prims,
+                                                       int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out,
+                                                       int s, int len, int span, V3 o, V3 d, int key_mode, int lane) {
+  unsigned long long v[PER];
+#pragma unroll
+  for (int r = 0; r < PER; ++r) {
+    const int e = r * 32 + lane;
+    v[r] = e < len ? make_composite<FROM_SCATTER>(geom, n, tile_prims[s + e], e, o, d, key_mode) : ~0ull;
+  }
+  warp_bitonic_regs<PER>(v, lane);
+#pragma unroll
+  for (int r = 0; r < PER; ++r) {
+    const int e = r * 32 + lane;
+    if (e < len) {
+      sorted_prims[s + e] = FROM_SCATTER ? (int32_t)(uint32_t)v[r] : tile_prims[s + (int)(uint32_t)v[r]];
+      if (keys_out) keys_out[s + e] = __uint_as_float((uint32_t)(v[r] >> 32));
+    }
+  }
+  for (int i = len + lane; i < span; i += 32) sorted_prims[s + i] = -1;
+}
+
 // end of k_sort_tiles: the grid may not complete before the grid it was launched behind has
 __device__ __forceinline__ void sort_tiles_done() {
   if ((threadIdx.x & 31) == 0) chain_wait();
@@ -100,13 +168,12 @@ __global__ void __launch_bounds__(256, 6) k_sort_tiles(
     const int32_t* __restrict__ tile_offsets, const int32_t* tile_prims, int W, int H, int ts, int ntx, int T, int cap,
     int32_t* __restrict__ sorted_prims, float* __restrict__ keys_out, int key_mode, int32_t* __restrict__ long_list,
     int32_t* __restrict__ long_count, const int32_t* __restrict__ list_len, int32_t* __restrict__ status) {
-  __shared__ __align__(16) unsigned long long s_buf[kTilesPerCta * kWarpSortMax];
   // Launched behind k_sort_long as its programmatic dependent WITHOUT waiting for it here: the two kernels sort
   // disjoint tiles and run side by side.  What this kernel reads (the binned lists, the status word) was complete
   // before k_sort_long's CTAs got past their own wait, and none of this kernel's CTAs starts before all of them
   // have.  The wait is at the end instead (sort_tiles_done), so that this grid's completion implies the other's.
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) { sort_tiles_done(); return; }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31;
   // warps draw tiles from a shared cursor (long_count[1]): list lengths differ by two orders of magnitude, and
   // a fixed deal would leave most warps of a CTA waiting for the one with the longest list
   for (;;) {
@@ -127,17 +194,10 @@ __global__ void __launch_bounds__(256, 6) k_sort_tiles(
   const int cx = min(tx * ts + (ts >> 1), W - 1), cy = min(ty * ts + (ts >> 1), H - 1);
   const int64_t pc = (int64_t)cy * W + cx;
   const V3 o = load3(rays_o, pc), d = load3(rays_d, pc);
-  unsigned long long* buf = s_buf + warp * kWarpSortMax;
-  const int N = len <= 32 ? 32 : (len <= 64 ? 64 : (len <= 128 ? 128 : 256));
-  for (int i = lane; i < N; i += 32)
-    buf[i] = (i < len) ? make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode) : ~0ull;
-  __syncwarp();
-  if (N == 32) warp_bitonic<unsigned long long, 32>(buf);
-  else if (N == 64) warp_bitonic<unsigned long long, 64>(buf);
-  else if (N == 128) warp_bitonic<unsigned long long, 128>(buf);
-  else warp_bitonic<unsigned long long, 256>(buf);
-  write_sorted<IDSORT>(buf, tile_prims, sorted_prims, keys_out, s, len, span, lane, 32);
-  __syncwarp();   // the slice is reused by this warp's next tile
+  if (len <= 32) sort_tile_in_registers<1, IDSORT>(geom, n, tile_prims, sorted_prims, keys_out, s, len, span, o, d, key_mode, lane);
+  else if (len <= 64) sort_tile_in_registers<2, IDSORT>(geom, n, tile_prims, sorted_prims, keys_out, s, len, span, o, d, key_mode, lane);
+  else if (len <= 128) sort_tile_in_registers<4, IDSORT>(geom, n, tile_prims, sorted_prims, keys_out, s, len, span, o, d, key_mode, lane);
+  else sort_tile_in_registers<8, IDSORT>(geom, n, tile_prims, sorted_prims, keys_out, s, len, span, o, d, key_mode, lane);
   }
 }
 
