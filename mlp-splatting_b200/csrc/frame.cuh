@@ -33,6 +33,7 @@ struct __align__(16) RecIn {
 
 struct Scratch {
   int32_t* tile_cnt;     // [T+1]
+  int32_t* tile_diff;    // [(nty+1)*(ntx+1)] rectangle corners of the count pass (2-D difference array)
   int32_t* tile_fill;    // [T]
   uint2* rect;           // [n]  (x0 | x1<<16, y0 | y1<<16); x0 > x1 marks "culled"
   int32_t* scan_blk;     // block sums of the multi-block scans
@@ -79,6 +80,7 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   const int64_t P = (int64_t)W * H;
   auto take = [&](int64_t bytes) { char* r = p ? p + off : nullptr; off += align_up(bytes, 256); return r; };
   s.tile_cnt = (int32_t*)take(4 * (T + 1));
+  s.tile_diff = (int32_t*)take(4 * (int64_t)((W + ts - 1) / ts + 1) * ((H + ts - 1) / ts + 1));
   s.tile_fill = (int32_t*)take(4 * T);
   s.rect = (uint2*)take(8 * (int64_t)n);
   const int64_t nblk = (std::max<int64_t>(std::max<int64_t>(n, T), P + 1) + kScanItems - 1) / kScanItems + 2;
