@@ -336,7 +336,7 @@ static Scratch grouped_layout(void* base, int64_t R, int n) {
   s.prim_cnt = (int32_t*)take(4 * 2 * ((int64_t)n + 4));
   s.prim_cursor = (int32_t*)take(4 * ((int64_t)n + 1));
   s.prim_off = (int32_t*)take(4 * ((int64_t)n + 2));
-  s.scan_blk = (int32_t*)take(4 * 3 * ((int64_t)n / kScanItems + 4));
+  s.scan_blk = (int32_t*)take(4 * 3 * ((int64_t)n / kPrimScanItems + 4));
   s.max_work = (int64_t)n + R / kRowsPerItem + 2;
   s.work = (int4*)take(16 * s.max_work);
   s.max_work_small = 2 * (int64_t)n + 2;

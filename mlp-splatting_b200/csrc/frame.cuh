@@ -70,6 +70,7 @@ inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 inline int num_tiles(int W, int H, int ts) { return ((W + ts - 1) / ts) * ((H + ts - 1) / ts); }
 
 constexpr int kScanItems = 4096;  // elements per block of the multi-block scans
+constexpr int kPrimScanItems = 1024;   // primitives per block of the per-primitive scan (256 threads, four each)
 
 // Carve the scratch block.  base may be null (size query).
 inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t max_pairs, int64_t max_records) {
@@ -83,7 +84,8 @@ inline Scratch carve_scratch(void* base, int n, int W, int H, int ts, int64_t ma
   s.tile_diff = (int32_t*)take(4 * (int64_t)((W + ts - 1) / ts + 1) * ((H + ts - 1) / ts + 1));
   s.tile_fill = (int32_t*)take(4 * T);
   s.rect = (uint2*)take(8 * (int64_t)n);
-  const int64_t nblk = (std::max<int64_t>(std::max<int64_t>(n, T), P + 1) + kScanItems - 1) / kScanItems + 2;
+  const int64_t nblk = std::max<int64_t>((std::max<int64_t>(T, P + 1) + kScanItems - 1) / kScanItems,
+                                         ((int64_t)n + kPrimScanItems - 1) / kPrimScanItems) + 2;
   s.scan_blk = (int32_t*)take(4 * 3 * nblk);
   s.px_state = (float4*)take(16 * P);
   s.px_depth = (float2*)take(8 * P);

@@ -212,7 +212,7 @@ __global__ void k_prim_partial(const int32_t* __restrict__ prim_cnt, int n, int 
   chain_release();
   __shared__ int warp_sums[32];
   if (status[MLPSP_ST_BITS] & MLPSP_ST_FATAL) return;
-  const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
+  const int64_t base = (int64_t)blockIdx.x * kPrimScanItems + (int64_t)threadIdx.x * 4;
   int a = 0, b = 0, m = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j)
@@ -225,7 +225,7 @@ __global__ void k_prim_partial(const int32_t* __restrict__ prim_cnt, int n, int 
 }
 
 // Second pass: every block sums the partial totals of the blocks before it (a few hundred at most), scans
-// its own 4096 counts, writes the CSR offsets and the evaluator's work items and clears the counts the NEXT wave
+// its own 1,024 counts, writes the CSR offsets and the evaluator's work items and clears the counts the NEXT wave
 // will add to (waves alternate between two count arrays, so nothing this launch reads is written by it); the last
 // block also publishes the wave's totals.  blk == nullptr: there was no first pass -- the block sums the counts
 // of the blocks before it itself (worth it up to a few blocks: one launch instead of two).
@@ -248,7 +248,7 @@ __global__ void k_prim_final(const int32_t* __restrict__ prim_cnt, int32_t* __re
     for (int i = threadIdx.x; i < (int)blockIdx.x; i += blockDim.x) { pa += blk[3 * i]; pb += blk[3 * i + 1]; pm += blk[3 * i + 2]; }
   } else {
     const int4* c4 = reinterpret_cast<const int4*>(prim_cnt);     // both count arrays start 16-byte aligned
-    const int before4 = (int)blockIdx.x * (kScanItems / 4);
+    const int before4 = (int)blockIdx.x * (kPrimScanItems / 4);
 #pragma unroll 2
     for (int i = threadIdx.x; i < before4; i += blockDim.x) {
       const int4 c = c4[i];
@@ -261,7 +261,7 @@ __global__ void k_prim_final(const int32_t* __restrict__ prim_cnt, int32_t* __re
   block_exclusive_scan(pa, warp_sums, base_a);
   block_exclusive_scan(pb, warp_sums, base_b);
   block_exclusive_scan(pm, warp_sums, base_m);
-  const int64_t base = (int64_t)blockIdx.x * kScanItems + (int64_t)threadIdx.x * 4;
+  const int64_t base = (int64_t)blockIdx.x * kPrimScanItems + (int64_t)threadIdx.x * 4;
   int c[4], a = 0, b = 0, m = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -311,20 +311,20 @@ __global__ void k_prim_final(const int32_t* __restrict__ prim_cnt, int32_t* __re
   }
 }
 
-// Up to 32,768 primitives the scan is one launch.  Beyond that the block that sums the most counts becomes the
+// Up to 8,192 primitives the scan is one launch.  Beyond that the block that sums the most counts becomes the
 // launch's critical path (100,000 primitives: 23 us in one launch against 18 us in two).
 constexpr int kPrimScanSoloBlocks = 8;
 
 int launch_prim_scan(const Scratch& s, int n, int next_list, int32_t* status, cudaStream_t st, bool split_small, int wave) {
-  const int nblk = (n + kScanItems - 1) / kScanItems;
+  const int nblk = (n + kPrimScanItems - 1) / kPrimScanItems;
   if (nblk == 0) return MLPSP_OK;
   const bool solo = nblk <= kPrimScanSoloBlocks;
   LaunchScope scope(kKScan, solo ? 1 : 2, st);
   const int split = split_small && s.work_small ? 1 : 0;
   const int32_t* cnt = s.prim_cnt + (size_t)(wave & 1) * prim_cnt_stride(n);
   int32_t* cnt_next = s.prim_cnt + (size_t)((wave & 1) ^ 1) * prim_cnt_stride(n);
-  if (!solo) launch_chained(k_prim_partial, dim3(nblk), dim3(1024), 0, st, cnt, n, split, s.scan_blk, status);
-  launch_chained(k_prim_final, dim3(nblk), dim3(1024), 0, st, cnt, cnt_next, s.prim_cursor, n, split, solo ? nullptr : s.scan_blk, s.prim_off, s.work,
+  if (!solo) launch_chained(k_prim_partial, dim3(nblk), dim3(kPrimScanItems / 4), 0, st, cnt, n, split, s.scan_blk, status);
+  launch_chained(k_prim_final, dim3(nblk), dim3(kPrimScanItems / 4), 0, st, cnt, cnt_next, s.prim_cursor, n, split, solo ? nullptr : s.scan_blk, s.prim_off, s.work,
                                      s.max_work, s.work_small, s.max_work_small, s.counters, next_list, status);
   return cuda_check(cudaGetLastError(), "prim_scan");
 }
