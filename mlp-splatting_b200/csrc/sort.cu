@@ -132,6 +132,65 @@ __device__ __forceinline__ void warp_bitonic_regs(unsigned long long (&v)[PER], 
   }
 }
 
+// ---- CTA-level bitonic sort, PER elements per thread in registers: thread t holds the elements t * PER + r ----
+// Distances below PER stay inside a thread, distances below 32 * PER pair two lanes of a warp (shuffles); only the
+// remaining distances (6 of the 45 stages of a 512-element sort, 10 of 55 at 1,024) cross warps and go through
+// shared memory between two CTA barriers.  buf holds the elements on entry and, sorted, on return.
+template <int PER, int THREADS>
+__device__ __forceinline__ void cta_bitonic_hybrid(unsigned long long* buf) {
+  constexpr int N = PER * THREADS;
+  const int tid = threadIdx.x;
+  unsigned long long v[PER];
+#pragma unroll
+  for (int r = 0; r < PER; ++r) v[r] = buf[tid * PER + r];
+  __syncthreads();
+#pragma unroll
+  for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j < PER) {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+          if ((r & j) == 0) {
+            const bool up = ((tid * PER + r) & k) == 0;
+            const unsigned long long a = v[r], b = v[r | j];
+            const bool swap = up ? (a > b) : (a < b);
+            v[r] = swap ? b : a;
+            v[r | j] = swap ? a : b;
+          }
+        }
+      } else if (j < 32 * PER) {
+        const int jl = j / PER;
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+          const unsigned long long a = v[r];
+          const unsigned long long b = shfl_xor_u64(a, jl);
+          const bool up = ((tid * PER + r) & k) == 0;
+          const bool keep_min = ((tid & jl) == 0) == up;
+          const unsigned long long mn = a < b ? a : b, mx = a < b ? b : a;
+          v[r] = keep_min ? mn : mx;
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) buf[tid * PER + r] = v[r];
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+          const int e = tid * PER + r;
+          const unsigned long long a = v[r], b = buf[e ^ j];
+          const bool keep_min = ((e & j) == 0) == ((e & k) == 0);
+          const unsigned long long mn = a < b ? a : b, mx = a < b ? b : a;
+          v[r] = keep_min ? mn : mx;
+        }
+        __syncthreads();
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < PER; ++r) buf[tid * PER + r] = v[r];
+  __syncthreads();
+}
+
 // One tile's list (len <= PER * 32) sorted by one warp in registers and written out.
 template <int PER, bool FROM_SCATTER>
 __device__ __forceinline__ void sort_tile_in_registers(const float4* __restrict__ geom, int n, const int32_t* tile_prims,
@@ -201,8 +260,8 @@ __global__ void __launch_bounds__(256, 6) k_sort_tiles(
   }
 }
 
-// Long lists (more than kWarpSortMax candidates): one CTA per such tile, the same bitonic network in shared memory
-// run by the whole CTA.  Launched before k_sort_tiles, which runs beside it.
+// Long lists (more than kWarpSortMax candidates): one CTA per such tile, the same bitonic network with the elements in
+// the registers of the CTA's threads (cta_bitonic_hybrid).  Launched before k_sort_tiles, which runs beside it.
 template <int THREADS, int CAP, bool IDSORT>
 __global__ void __launch_bounds__(THREADS) k_sort_long(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
@@ -235,9 +294,9 @@ __global__ void __launch_bounds__(THREADS) k_sort_long(
     for (int i = threadIdx.x; i < N; i += THREADS)
       s_buf[i] = (i < len) ? make_composite<IDSORT>(geom, n, tile_prims[s + i], i, o, d, key_mode) : ~0ull;
     __syncthreads();
-    if (N == CAP / 4) warp_bitonic<unsigned long long, CAP / 4, THREADS>(s_buf);
-    else if (N == CAP / 2) warp_bitonic<unsigned long long, CAP / 2, THREADS>(s_buf);
-    else warp_bitonic<unsigned long long, CAP, THREADS>(s_buf);
+    if (N == CAP / 4) cta_bitonic_hybrid<CAP / 4 / THREADS, THREADS>(s_buf);
+    else if (N == CAP / 2) cta_bitonic_hybrid<CAP / 2 / THREADS, THREADS>(s_buf);
+    else warp_bitonic<unsigned long long, CAP, THREADS>(s_buf);      // beyond 1,024 candidates: rare, in shared memory
     write_sorted<IDSORT>(s_buf, tile_prims, sorted_prims, keys_out, s, len, span, threadIdx.x, THREADS);
     __syncthreads();
   }
