@@ -62,7 +62,7 @@ __global__ void k_init_frame(int64_t P, float4* __restrict__ px_state, float2* _
 // 8 warps per tile: warp w owns pixel half (w & 1) and candidates (w >> 1) + 4j of the window.
 // REF: the hit decision in the reference kernels' arithmetic (frame.hit_arith = 1).
 template <bool REF>
-__global__ void __launch_bounds__(256) k_hits(
+__global__ void __launch_bounds__(256, 6) k_hits(
     const float* __restrict__ rays_o, const float* __restrict__ rays_d, const float4* __restrict__ geom, int n,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ tile_len, const int32_t* __restrict__ sorted_prims, int W, int H, int ntx,
     float thr, float bound2, const int32_t* __restrict__ active, const int32_t* __restrict__ active_count, int lo,
