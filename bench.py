@@ -8,9 +8,10 @@ the rays resident in HBM (the first block of K timed steps; `repeat` holds media
 further blocks of K steps); `e2e` is the same frame through the public host API with the rays
 arriving from pinned host memory and the image returning to it inside the timed region.  At N > 1
 every rank renders its own view of the replicated scene (weak scaling); the scene is generated on
-rank 0 and broadcast once with NCCL.  The default run adds, under `other_workloads`, short
-measurements of the other named configurations (feature map, four views shared by view and by
-band of tile rows, the 2 M-primitive stress scene).  `--impl reference` times the CPU restatement
+rank 0 and broadcast once with NCCL.  The default one-GPU run adds, under `other_workloads`, short
+measurements of the other named configurations (feature map, four views in one batch, the 2 M-primitive
+stress scene in view batches, per-primitive weight gradients); with several ranks they are opt-in
+(`--other-workloads-multi`, every rank measures its share without collectives, the shares are put together at the end).  `--impl reference` times the CPU restatement
 of the reference's algorithm (oracle/) on all host cores over a bounded band of tile rows.
 `--workload decoder_<W>x<H>` (decoder_1200x680) times the step after the feature map alone: fused decoder +
 text query, decoder, full-width query (`--only` picks one).
@@ -281,7 +282,7 @@ def packed_scene_on_device(cfg, dev, lib, chunk=131072):
 class Workload:
     """One named workload set up on this rank: scene, work units (view, band of tile rows), renderer."""
 
-    def __init__(self, name, args, dev, world, rank, lib, timed_bcast=False):
+    def __init__(self, name, args, dev, world, rank, lib, timed_bcast=False, own_scene=False):
         import torch
         from mlp_splatting_b200 import _lib as L
         from mlp_splatting_b200 import sharding, synthetic as syn
@@ -298,11 +299,17 @@ class Workload:
                 raise SystemExit(f"{name} is generated on the device and keeps only the fp16 weight image")
             self.ps = packed_scene_on_device(cfg, dev, lib)
         else:
-            if rank == 0:
+            # own_scene: every rank draws the (seeded) scene itself instead of receiving it from rank 0, so that setting
+            # the workload up involves no collective (the side measurements must not be able to desynchronise the ranks)
+            if rank == 0 or own_scene:
                 self.scene_np = syn.make_scene(cfg["n"], cfg["seed"], mu=cfg["mu"], hidden=cfg.get("hidden", 32),
                                                feat_dim=cfg.get("feat_dim", 0), pe_sigma=0.01 if args.encoder == "integrated" else 0.0)
             t_b0 = time.perf_counter()
-            scene_t = sharding.broadcast_scene(self.scene_np, dev, src=0)
+            if own_scene:
+                scene_t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in self.scene_np.items()
+                           if isinstance(v, np.ndarray)}
+            else:
+                scene_t = sharding.broadcast_scene(self.scene_np, dev, src=0)
             torch.cuda.synchronize()
             self.bcast_s = time.perf_counter() - t_b0 if world > 1 else 0.0
             self.ps = PackedScene(*[scene_t[k] for k in ("positions", "log_scales", "quats") + WK], scene_t["freq"], scene_t["att"],
@@ -484,18 +491,18 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
     """frames/s, ms per step and the evaluator's rate of another named workload (no end-to-end arm)."""
     import torch
     import torch.distributed as dist
-    wl = Workload(name, args, dev, world, rank, lib)
+    # no collective anywhere in here: a rank that fails must not leave the others waiting (the ranks' figures are
+    # put together afterwards, combine_other_workloads)
+    wl = Workload(name, args, dev, world, rank, lib, own_scene=True)
     stats = wl.size_and_count()
     for _ in range(3):
         flush.fill_(1); wl.frame()
-    dev_ms, _wall = timed_block(wl, flush, steps, world)
+    dev_ms, _wall = timed_block(wl, flush, steps, 1)
     classes = class_times(wl, flush, min(steps, 5))
     bits = int(wl.r.status.cpu()[0])
     for br, _idx in wl.batches:
         bits |= int(br.lead.status.cpu()[0])
-    rec_t = torch.tensor([float(stats.records), float(stats.work_total), float(stats.work_small)], dtype=torch.float64, device=dev)
-    if world > 1 and wl.nviews > 1:
-        dist.all_reduce(rec_t)
+    rec_t = [float(stats.records), float(stats.work_total), float(stats.work_small)]
     hidden = int(wl.cfg.get("hidden", 32))
     mlp_ms = classes["mlp"]["ms_per_step"]
     # what the evaluator must move on this rank: 32 B in + 16 B out per record, one weight image per work item.  With
@@ -509,6 +516,7 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
     hbm["frac"] = hbm["achieved_gbs"] / pk["hbm_gbs"]
     hbm["tflops_at_hbm_peak"] = hbm["flop_per_byte"] * pk["hbm_gbs"] / 1e3
     out = {"frames_per_sec": wl.frames_per_step * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps, "steps": steps,
+           "local": {"dev_ms": dev_ms, "records": rec_t[0], "work_total": rec_t[1], "work_small": rec_t[2]},
            "scaling": wl.scaling, "views_per_step": wl.frames_per_step, "hidden": hidden,
            "views_per_call": [len(idx) for _br, idx in wl.batches] if wl.batches else 1,
            "evaluator_tflops_this_rank": stats.records * flop_per_record(hidden) / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else 0.0,
@@ -520,6 +528,37 @@ def short_measure(name, args, dev, world, rank, lib, flush, steps):
            "status_bits": bits, "data": "generated on the device" if wl.cfg.get("on_device") else "generated on the host"}
     del wl
     torch.cuda.empty_cache()
+    return out
+
+
+def combine_other_workloads(per_rank):
+    """Rank 0: one record per workload from the ranks' local ones (gathered objects).  The step time is the slowest
+    rank's, the record counts are sums; a failure on any rank is reported instead of figures."""
+    out = {}
+    for name in per_rank[0]:
+        recs = [pr.get(name) for pr in per_rank]
+        if all(isinstance(r, dict) and "failed" not in r and "local" not in r for r in recs):
+            out[name] = recs[0]          # a measurement of rank 0 alone
+            continue
+        failed = [f"rank {i}: {r.get('failed', 'missing') if isinstance(r, dict) else 'missing'}" for i, r in enumerate(recs)
+                  if not isinstance(r, dict) or "failed" in r or "local" not in r]
+        if failed:
+            out[name] = {"failed": "; ".join(failed)[:600]}
+            continue
+        r0 = dict(recs[0])
+        loc = [r.pop("local") if r is r0 else r["local"] for r in [r0] + recs[1:]]
+        dev_ms = max(l["dev_ms"] for l in loc)
+        rec, wt, ws = (sum(l[k] for l in loc) for k in ("records", "work_total", "work_small"))
+        r0["frames_per_sec"] = r0["views_per_step"] * r0["steps"] / (dev_ms / 1e3)
+        r0["ms_per_step"] = dev_ms / r0["steps"]
+        r0["records_per_step"] = rec
+        r0["rows_per_evaluator_block"] = rec / max(wt, 1.0)
+        r0["fill_of_evaluator_blocks"] = rec / max(128.0 * (wt - ws) + 32.0 * ws, 1.0)
+        r0["small_group_share_of_blocks"] = ws / max(wt, 1.0)
+        r0["status_bits"] = 0
+        for r in recs:
+            r0["status_bits"] |= int(r["status_bits"])
+        out[name] = r0
     return out
 
 
@@ -628,6 +667,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=HEADLINE)
+    ap.add_argument("--other-workloads-multi", action="store_true",
+                    help="also run the other workloads' short measurements when several ranks are used")
     ap.add_argument("--e2e-depth", type=int, default=6,
                     help="frames in flight in the end-to-end arm (measured on one B200: 2 -> 731, 3 -> 867, 4 -> 899, "
                          "6 -> 971, 8 -> 984, 12 -> 990 frames/s)")
@@ -821,7 +862,11 @@ def main():
 
     others = None
     reduced = bool(args.width or args.height or args.primitives)
-    if args.workload == HEADLINE and not args.no_other_workloads and prec == L.PRECISION_F16 and not reduced:
+    # The side measurements run on one GPU by default.  With several ranks they are opt-in (--other-workloads-multi):
+    # they add minutes of work in which any rank-local failure could cost the whole line, and the headline figures of
+    # a scaling run do not need them.
+    if (args.workload == HEADLINE and not args.no_other_workloads and prec == L.PRECISION_F16 and not reduced
+            and (world == 1 or args.other_workloads_multi)):
         del pipe
         others = {}
         for name in OTHER_WORKLOADS:
@@ -838,6 +883,13 @@ def main():
                 others["weight_gradients_50k_x100"] = weight_gradient_measure(dev)
             except Exception as exc:
                 others["weight_gradients_50k_x100"] = {"failed": f"{type(exc).__name__}: {exc}"[:300]}
+        # the one collective of the side measurements: every rank reaches it, whatever happened above
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, others)
+            others = combine_other_workloads(gathered) if rank == 0 else None
+        else:
+            others = combine_other_workloads([others])
 
     if rank == 0:
         line = {
