@@ -160,3 +160,21 @@ def test_build_configuration_variables_select_run_time_arguments(monkeypatch):
     monkeypatch.setenv("MLPSP_CSR_MAX_HITS", "300")
     with pytest.raises(ValueError, match="MLPSP_CSR_MAX_HITS must be 128, 256 or 512"):
         _tile_ext_build_config()
+
+
+def test_bench_combines_the_ranks_side_measurements():
+    """bench.combine_other_workloads: the slowest rank sets the step time, record counts add up, a failure on any rank
+    is reported in place of figures, and a record measured by rank 0 alone passes through."""
+    import bench
+    def rec(dev_ms, records, wt, ws, bits=0):
+        return {"frames_per_sec": -1.0, "ms_per_step": -1.0, "steps": 2, "views_per_step": 32, "status_bits": bits,
+                "local": {"dev_ms": dev_ms, "records": records, "work_total": wt, "work_small": ws}}
+    out = bench.combine_other_workloads([{"a": rec(100.0, 1000.0, 10.0, 4.0), "b": rec(5.0, 1.0, 1.0, 0.0), "g": {"fp32_ms": 1.0}},
+                                         {"a": rec(160.0, 3000.0, 30.0, 6.0, bits=8), "b": {"failed": "RuntimeError: boom"},
+                                          "g": {"fp32_ms": 1.0}}])
+    a = out["a"]
+    assert a["ms_per_step"] == 80.0 and a["frames_per_sec"] == 32 * 2 / 0.160 and a["records_per_step"] == 4000.0
+    assert a["rows_per_evaluator_block"] == 100.0 and a["status_bits"] == 8 and "local" not in a
+    assert abs(a["fill_of_evaluator_blocks"] - 4000.0 / (128 * 30 + 32 * 10)) < 1e-12
+    assert "rank 1: RuntimeError: boom" in out["b"]["failed"]
+    assert out["g"] == {"fp32_ms": 1.0}
