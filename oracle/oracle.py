@@ -368,3 +368,58 @@ def render_per_pixel(rays_o, rays_d_unit, geom, tile_offsets, prims, W, H, tile,
     if feat_attr is not None:
         return rgb, alpha, hits, bool(ovf.value), feat
     return rgb, alpha, hits, bool(ovf.value)
+
+
+def bf16_round(x):
+    """float32 -> bfloat16 -> float32, round to nearest even (NaN kept)."""
+    a = np.ascontiguousarray(x, dtype=np.float32)
+    u = a.view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    out = r.view(np.float32).copy()
+    out[np.isnan(a)] = np.nan
+    return out.reshape(a.shape)
+
+
+def grouped_weight_gradients_model(offsets, x6, d3, masks, freq, att, weights, dtype="float16", scale=None):
+    """Mixed-precision statement of grouped_weight_gradients (scannet/primitive_gemm.py:101-166, the Triton kernel's
+    arithmetic): encoding, weights, activations and adjoints rounded to the operand format, FP32 products and sums,
+    adjoints scaled before the cast and the sums unscaled afterwards.  dtype "float32" is the unrounded statement
+    (scannet/primitive_csr.py:33-58).  masks [R,2] int32 (saved activation signs) or None (signs of the recomputed
+    activations, primitive_gemm.py:149-151).  Returns [dW1, db1, dW2, db2, dW3, db3] as float32 arrays."""
+    q = {"float32": lambda a: np.asarray(a, np.float32),
+         "float16": lambda a: np.asarray(a, np.float32).astype(np.float16).astype(np.float32),     # round to nearest even
+         "bfloat16": bf16_round}[dtype]
+    if scale is None:
+        scale = 4096.0 if dtype == "float16" else 1.0
+    W1, b1, W2, b2, W3, b3 = [np.asarray(w, np.float32) for w in weights]
+    n = W1.shape[0]
+    mult = (np.asarray(freq, np.float32) * np.asarray(att, np.float32)).astype(np.float32)
+    out = [np.zeros_like(w) for w in (W1, b1, W2, b2, W3, b3)]
+    bit = (1 << np.arange(32, dtype=np.int64))
+    for p in range(n):
+        b, e = int(offsets[p]), int(offsets[p + 1])
+        if b == e:
+            continue
+        ph = (np.asarray(x6[b:e], np.float32)[:, :, None] * mult[None, None, :]).astype(np.float32)
+        enc = q(np.concatenate((np.sin(ph).reshape(e - b, -1), np.cos(ph).reshape(e - b, -1)), axis=1).astype(np.float32))
+        w1, w2, w3 = q(W1[p]), q(W2[p]), q(W3[p])
+        h1f = (enc.astype(np.float64) @ w1.T.astype(np.float64)).astype(np.float32) + b1[p]
+        h1 = q(np.maximum(h1f, 0.0).astype(np.float32))
+        h2f = (h1.astype(np.float64) @ w2.T.astype(np.float64)).astype(np.float32) + b2[p]
+        h2 = q(np.maximum(h2f, 0.0).astype(np.float32))
+        if masks is None:
+            a1, a2 = h1f > 0, h2f > 0
+        else:
+            m = np.asarray(masks[b:e]).astype(np.int64) & 0xFFFFFFFF
+            a1, a2 = (m[:, 0:1] & bit[None, :]) != 0, (m[:, 1:2] & bit[None, :]) != 0
+        d3q = q((np.asarray(d3[b:e], np.float32) * np.float32(scale)).astype(np.float32))
+        d2 = q(((d3q.astype(np.float64) @ w3.astype(np.float64)).astype(np.float32) * a2).astype(np.float32))
+        d1 = q(((d2.astype(np.float64) @ w2.astype(np.float64)).astype(np.float32) * a1).astype(np.float32))
+        inv = 1.0 / scale
+        out[0][p] = (d1.T.astype(np.float64) @ enc.astype(np.float64) * inv).astype(np.float32)
+        out[1][p] = (d1.astype(np.float64).sum(0) * inv).astype(np.float32)
+        out[2][p] = (d2.T.astype(np.float64) @ h1.astype(np.float64) * inv).astype(np.float32)
+        out[3][p] = (d2.astype(np.float64).sum(0) * inv).astype(np.float32)
+        out[4][p] = (d3q.T.astype(np.float64) @ h2.astype(np.float64) * inv).astype(np.float32)
+        out[5][p] = (d3q.astype(np.float64).sum(0) * inv).astype(np.float32)
+    return out

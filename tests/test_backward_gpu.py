@@ -143,6 +143,30 @@ def test_tensor_core_gradients_match_fp32_kernel(dtype, bound, segment_size):
         assert relative_l2 < 3 * bound, (k, relative_l2)
 
 
+@pytest.mark.parametrize("dtype,name,bound", [(torch.float16, "float16", 3e-4), (torch.bfloat16, "bfloat16", 2e-3)])
+def test_tensor_core_gradients_match_operand_model(dtype, name, bound):
+    """The tcgen05 kernel against the CPU statement of the mixed-precision arithmetic (operands rounded to the format,
+    FP32 sums): what is left between the two is the order of the FP32 sums and the rare encoding entry that the
+    hardware sine rounds to the neighbouring operand value -- an order of magnitude below the distance to FP32."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from oracle import oracle as orc
+    from mlp_splatting_b200.primitive_gemm import grouped_weight_gradients
+    dev = torch.device("cuda", 0)
+    csr, freq, att, weights = _random_csr(dev, 120, 70, 21)
+    got = grouped_weight_gradients(csr, freq, att, weights, dtype=dtype, segment_size=128)
+    cpu = lambda t: t.detach().cpu().numpy()
+    want = orc.grouped_weight_gradients_model(cpu(csr.offsets), cpu(csr.x6), cpu(csr.grad4), cpu(csr.relu_masks), cpu(freq),
+                                              cpu(att), [cpu(w) for w in weights], dtype=name)
+    f32 = orc.grouped_weight_gradients_model(cpu(csr.offsets), cpu(csr.x6), cpu(csr.grad4), cpu(csr.relu_masks), cpu(freq),
+                                             cpu(att), [cpu(w) for w in weights], dtype="float32")
+    for g, w, f, k in zip(got, want, f32, ("W1", "b1", "W2", "b2", "W3", "b3")):
+        rel = float(np.linalg.norm(cpu(g) - w) / np.linalg.norm(w))
+        to_f32 = float(np.linalg.norm(w - f) / np.linalg.norm(f))
+        print(name, k, "kernel vs operand model", f"{rel:.2e}", "operand model vs FP32", f"{to_f32:.2e}")
+        assert rel < bound and rel < to_f32, (k, rel, to_f32)
+
+
 def test_nonfinite_mixed_result_is_retried_in_fp32():
     """Adjoints that overflow binary16 once scaled by 4096: the mixed launch raises the flag, the call warns, retries
     in unscaled IEEE FP32 and returns that result (primitive_gemm.py:64-98)."""
