@@ -234,3 +234,26 @@ def test_per_pixel_order_oracle_invariants():
     *_x, hits, ovf = orc.render_per_pixel(cam["rays_o"], f["rays_d_unit"], f["geom"], f["tile_offsets"], f["tile_prims"],
                                           cam["W"], cam["H"], 8, 5e-3, [scene[k] for k in WKEYS], scene["freq"], scene["att"])
     assert ovf and hits.max() == 256
+
+
+def test_weight_gradient_model_reproduces_reference_statement():
+    """oracle.grouped_weight_gradients_model in its FP32 form against the gradients of the reference's own PyTorch
+    statement (reference_weight_gradients, scannet/primitive_csr.py:33-58; tests/golden/backward.npz), and the
+    operand-rounded forms inside the reference test's bounds (tests/test_primitive_csr.py:128-130)."""
+    import os
+    import numpy as np
+    from oracle import oracle as orc
+    fx = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "backward.npz"))
+    keys = ("W1", "b1", "W2", "b2", "W3", "b3")
+    w = [fx["vjp_" + k] for k in keys]
+    args = (fx["vjp_offsets"], fx["vjp_x6"], fx["vjp_d3"], fx["vjp_masks"], fx["vjp_freq"], fx["vjp_att"], w)
+    for g, k in zip(orc.grouped_weight_gradients_model(*args, dtype="float32"), keys):
+        want = fx["vjp_g" + k]
+        assert np.linalg.norm(g - want) / np.linalg.norm(want) < 1e-6, k
+        assert not g[0].any() and not g[9].any()              # primitives without records
+    for dtype, bound in (("float16", 0.01), ("bfloat16", 0.04)):
+        for g, k in zip(orc.grouped_weight_gradients_model(*args, dtype=dtype), keys):
+            want = fx["vjp_g" + k]
+            assert np.linalg.norm(g - want) / np.linalg.norm(want) < bound, (dtype, k)
+    np.testing.assert_array_equal(orc.bf16_round(np.array([1.0, 1.00390625, 1.01171875], np.float32)),
+                                  np.array([1.0, 1.0, 1.015625], np.float32))      # ties to even, then up
