@@ -669,7 +669,7 @@ def main():
     ap.add_argument("--workload", default=HEADLINE)
     ap.add_argument("--other-workloads-multi", action="store_true",
                     help="also run the other workloads' short measurements when several ranks are used")
-    ap.add_argument("--e2e-depth", type=int, default=6,
+    ap.add_argument("--e2e-depth", type=int, default=8,
                     help="frames in flight in the end-to-end arm (measured on one B200: 2 -> 731, 3 -> 867, 4 -> 899, "
                          "6 -> 971, 8 -> 984, 12 -> 990 frames/s)")
     ap.add_argument("--view-batch", type=int, default=16,
