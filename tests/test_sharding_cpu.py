@@ -47,3 +47,31 @@ def test_assignment_covers_every_tile_row_once():
                 for row in range(r0, r1):
                     cover[(v, row)] = cover.get((v, row), 0) + 1
         assert set(cover.values()) == {1} and len(cover) == views * 85, (views, world)
+
+
+def _gather_worker(rank, world, port, out):
+    """The side measurements of bench.py with several ranks: every rank brings its own record (one of them a failure),
+    the only collective is the gather at the end, and rank 0 puts the records together."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import bench
+    mine = {"stress": {"frames_per_sec": 0.0, "ms_per_step": 0.0, "steps": 2, "views_per_step": 32, "status_bits": 0,
+                       "local": {"dev_ms": 100.0 + 50.0 * rank, "records": 1000.0 * (rank + 1), "work_total": 10.0, "work_small": 2.0}},
+            "fourview": ({"failed": "RuntimeError: rank-local failure"} if rank == 1 else
+                         {"frames_per_sec": 0.0, "ms_per_step": 0.0, "steps": 5, "views_per_step": 4, "status_bits": 0,
+                          "local": {"dev_ms": 10.0, "records": 1.0, "work_total": 1.0, "work_small": 0.0}})}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
+    out[rank] = bench.combine_other_workloads(gathered) if rank == 0 else None
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_side_measurements_are_gathered_once_gloo_world2():
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_gather_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = out[0]
+    assert res["stress"]["ms_per_step"] == 75.0 and res["stress"]["records_per_step"] == 3000.0
+    assert res["stress"]["frames_per_sec"] == 32 * 2 / 0.150
+    assert "rank 1: RuntimeError: rank-local failure" in res["fourview"]["failed"]
