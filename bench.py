@@ -695,6 +695,14 @@ def main():
         return run_reference(args)
     if args.workload.startswith("decoder_"):
         return run_decoder(args)
+    if args.workload == "weight_gradients":
+        # the backward side of the record path alone: FP32 kernel beside the tensor-core kernel (one GPU)
+        import torch
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        print(json.dumps(dict(metric="weight_gradient_ms", n_gpus=1, data="synthetic",
+                              **weight_gradient_measure(dev, primitives=args.primitives or 50000))), flush=True)
+        return
 
     import torch
     import torch.distributed as dist
